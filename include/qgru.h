@@ -1,0 +1,263 @@
+/*
+ * qgru.h - C ABI of the B200-native integer quantized GRU forward.
+ *
+ * This is the boundary a maintainer of CX9898/quant-gru-pytorch binds in place of the
+ * library's own `ForwardPassQuant` machinery: plain pointers, sizes and status codes,
+ * no C++ or torch types.  Each entry point names the reference interface it replaces
+ * (paths are relative to the reference project's root).
+ *
+ * Conventions shared by every entry point
+ *   - Layouts are the reference's "haste" layouts: W [I,3H], R [H,3H], bw/br [3H],
+ *     gate order along 3H is (update z, reset r, new n); x [T,B,I]; h [(T+1),B,H] with the
+ *     initial state in slot 0 (include/gru_interface.h:389-413).
+ *   - Quantized tensors crossing the boundary are int32 containers whose values are
+ *     already clamped to the operator's bit width, exactly as in the reference.
+ *   - `stream` is a cudaStream_t passed as void*; NULL means the legacy default stream.
+ *     Calls are asynchronous with respect to the host unless stated otherwise.
+ *   - Every function returns a qgru_status; no exception crosses this boundary.
+ *   - Nothing here falls back to a CPU path: without a CUDA device the device entry
+ *     points return QGRU_ERR_CUDA.
+ */
+#ifndef QGRU_H_
+#define QGRU_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define QGRU_API
+#else
+#define QGRU_API __attribute__((visibility("default")))
+#endif
+
+/* ------------------------------------------------------------------ status */
+typedef enum qgru_status {
+    QGRU_OK = 0,
+    QGRU_ERR_BAD_ARG = 1,      /* null pointer, non-positive size, mismatched shape   */
+    QGRU_ERR_CUDA = 2,         /* a CUDA runtime/driver call failed (see last_error)   */
+    QGRU_ERR_TIMEOUT = 3,      /* a bounded device-side wait ran out                   */
+    QGRU_ERR_UNSUPPORTED = 4,  /* bit width / shape outside what the kernels implement */
+    QGRU_ERR_NOT_READY = 5,    /* params or weights were not set before a forward      */
+    QGRU_ERR_NOMEM = 6,        /* device or host allocation failed                     */
+    QGRU_ERR_RANGE = 7         /* a scale cannot be encoded (<=0, shift outside int8)  */
+} qgru_status;
+
+/* ------------------------------------------------------------- data model */
+
+/* Operator order of `qgru_params.op[]`.  One entry per quantized operator of
+ * include/quantize_param_types.h:100-146 (GRUQuantParams) and
+ * include/quantize_bitwidth_config.h:68-75 (OperatorQuantConfig). */
+enum {
+    QGRU_OP_X = 0,
+    QGRU_OP_H = 1,
+    QGRU_OP_W = 2,   /* per-channel scales live in the scale_W array  */
+    QGRU_OP_R = 3,
+    QGRU_OP_BW = 4,
+    QGRU_OP_BR = 5,
+    QGRU_OP_IH_LINEAR = 6,  /* weight_ih_linear = W*x + bw */
+    QGRU_OP_HH_LINEAR = 7,  /* weight_hh_linear = R*h + br */
+    QGRU_OP_UPDATE_IN = 8,
+    QGRU_OP_UPDATE_OUT = 9,
+    QGRU_OP_RESET_IN = 10,
+    QGRU_OP_RESET_OUT = 11,
+    QGRU_OP_NEW_IN = 12,
+    QGRU_OP_NEW_OUT = 13,
+    QGRU_OP_MUL_RESET_HIDDEN = 14,   /* calibrated and exported, unused by the datapath */
+    QGRU_OP_MUL_NEW_CONTRIB = 15,    /* idem */
+    QGRU_OP_MUL_OLD_CONTRIB = 16,    /* idem */
+    QGRU_NUM_OPS = 17
+};
+
+enum { QGRU_PER_TENSOR = 0, QGRU_PER_GATE = 1, QGRU_PER_CHANNEL = 2 };
+enum { QGRU_LUT_UPDATE = 0, QGRU_LUT_RESET = 1, QGRU_LUT_NEW = 2 };
+#define QGRU_LUT_SEGMENTS 16
+
+/* QuantParam + QuantBitWidth + symmetric flag of one operator
+ * (include/quantize_param_types.h:63-66, include/quantize_bitwidth_config.h:6-22). */
+typedef struct qgru_op {
+    float scale;          /* authoritative scale: continuous (M+shift mode) or 2^-n (POT2) */
+    int32_t zero_point;
+    int8_t bits;          /* 1..32 */
+    uint8_t is_unsigned;
+    uint8_t symmetric;
+    uint8_t reserved;
+} qgru_op;
+
+/* One SegmentParams (include/quantize_lut_types.h:31-36). */
+typedef struct qgru_lut_segment {
+    int32_t q_b;
+    int32_t n_bx;        /* reference stores int8; widened, same value */
+    int32_t term_c;
+    int32_t threshold;
+} qgru_lut_segment;
+
+/* The part of SigmoidLUT the datapath reads (include/quantize_lut_types.h:47-55). */
+typedef struct qgru_lut {
+    qgru_lut_segment seg[QGRU_LUT_SEGMENTS];
+    int32_t zp_x;
+    int32_t reserved[3];
+} qgru_lut;
+
+/* Everything of GRUQuantParams except the four per-channel scale arrays. */
+typedef struct qgru_params {
+    int32_t hidden;
+    int32_t use_pot2;                 /* OperatorQuantConfig::usePOT2_ */
+    qgru_op op[QGRU_NUM_OPS];
+    int32_t granularity[4];           /* W, R, bw, br: QGRU_PER_* (informational) */
+    qgru_lut lut[3];                  /* update, reset, new */
+} qgru_params;
+
+/* GRUQuantizationRanges (include/gru_quantization_ranges.h:20-71) as a POD.
+ * Scalars are indexed by the QGRU_OP_* ids (W/R/BW/BR slots unused); per-channel
+ * ranges are caller-owned arrays of 3H floats. */
+typedef struct qgru_ranges {
+    int32_t hidden;
+    int32_t reserved;
+    float min_v[QGRU_NUM_OPS];
+    float max_v[QGRU_NUM_OPS];
+    float *min_W, *max_W, *min_R, *max_R, *min_bw, *max_bw, *min_br, *max_br; /* [3H] host */
+} qgru_ranges;
+
+typedef struct qgru_handle qgru_handle;
+
+/* ----------------------------------------------------------- host helpers */
+/* Pure host functions: no CUDA call is made, they work without a GPU. */
+
+QGRU_API const char *qgru_status_string(int status);
+QGRU_API const char *qgru_version(void);
+
+/* encodeMShift (include/quantize_ops_helper.h:245-264): scale ~= M * 2^-shift, M in
+ * [32768, 65535].  Returns QGRU_ERR_RANGE where the reference throws. */
+QGRU_API int qgru_encode_mshift(float scale, uint16_t *multiplier, int8_t *shift);
+
+/* rshift_round(int64) (include/quantize_ops_helper.h:183-206). */
+QGRU_API int64_t qgru_rshift_round(int64_t x, int n);
+
+/* Evaluate one LUT the way piecewise_linear does (include/quantize_ops_helper.h:600-606). */
+QGRU_API int32_t qgru_lut_eval(const qgru_lut *lut, int32_t q_x, const qgru_op *in_bw,
+                               const qgru_op *out_bw);
+
+/* generate_piecewise_linear_lut_to_params (src/quantize_ops.cu:21-52): fills p->lut[0..2]
+ * from the six gate input/output operators of p. */
+QGRU_API int qgru_generate_luts(qgru_params *p);
+
+/* calculateGRUQuantitativeParameters (src/gru_interface.cc:51-158), MinMax path:
+ * ranges + bit-width config (the bits/is_unsigned/symmetric/granularity/use_pot2 fields
+ * of `p`) -> scales, zero points and LUTs.  scale_* are host arrays of 3H floats. */
+QGRU_API int qgru_calc_params_from_ranges(const qgru_ranges *ranges, qgru_params *p,
+                                          float *scale_W, float *scale_R, float *scale_bw,
+                                          float *scale_br);
+
+/* --------------------------------------------------------------- lifecycle */
+
+/* One handle per (device, direction).  Replaces the per-call construction of
+ * gru::ForwardPassQuant (src/gru_forward_gpu_quant.cu:412-442): streams, events and the
+ * workspace live as long as the handle and grow on demand. */
+QGRU_API int qgru_create(qgru_handle **out, int device, int input_size, int hidden_size);
+QGRU_API void qgru_destroy(qgru_handle *h);
+QGRU_API const char *qgru_last_error(const qgru_handle *h);
+
+/* ForwardPassQuant::setRescaleParam (src/gru_forward_gpu_quant.cu:672-748): derives every
+ * execution-time rescale from the (scale, zero_point) seeds and uploads the tables.
+ * Host pointers.  Must precede set_weights and forward. */
+QGRU_API int qgru_set_params(qgru_handle *h, const qgru_params *p, const float *scale_W,
+                             const float *scale_R, const float *scale_bw,
+                             const float *scale_br);
+
+/* quantitativeWeight<false> (src/gru_interface.cc:294-328): per-channel quantize of the
+ * float master weights (device pointers) and packing into the kernels' layout.  The
+ * packed copy is kept until the next set_weights/set_params call. */
+QGRU_API int qgru_set_weights_f32(qgru_handle *h, const float *W, const float *R,
+                                  const float *bw, const float *br, void *stream);
+
+/* Same, for weights that are already quantized (the W_q/R_q/bw_q/br_q arguments of
+ * quantGRUForwardInt32, include/gru_interface.h:389). Device pointers. */
+QGRU_API int qgru_set_weights_i32(qgru_handle *h, const int32_t *W_q, const int32_t *R_q,
+                                  const int32_t *bw_q, const int32_t *br_q, void *stream);
+
+/* Copy the quantized weights out as int32 containers (the W_q_out..br_q_out outputs of
+ * quantGRUForwardInt, include/gru_interface.h:266-299).  Any pointer may be NULL. */
+QGRU_API int qgru_get_weights_i32(qgru_handle *h, int32_t *W_q, int32_t *R_q, int32_t *bw_q,
+                                  int32_t *br_q, void *stream);
+
+/* ----------------------------------------------------------------- forward */
+
+#define QGRU_FLAG_REVERSE 1u /* consume x and produce h in reversed time order */
+
+/* quantGRUForwardInt32 (src/gru_interface.cc:551-603), inference mode.
+ *   x_q  [T,B,I] int32 device, h0_q [B,H] int32 device or NULL (-> zero point of h),
+ *   h_q  [(T+1),B,H] int32 device out.
+ * With QGRU_FLAG_REVERSE timestep s of the recurrence reads x_q[T-1-s] and writes
+ * h_q[T-s]; slot T holds the initial state.  This equals the reference's
+ * flip -> forward -> flip for the reverse direction (pytorch/quant_gru.py:2143-2158)
+ * without the two copies. */
+QGRU_API int qgru_forward_i32(qgru_handle *h, int T, int B, const int32_t *x_q,
+                              const int32_t *h0_q, int32_t *h_q, unsigned flags, void *stream);
+
+/* quantGRUForwardInt (src/gru_interface.cc:610-725), inference mode: float in, float out.
+ *   x [T,B,I] f32 device, h0 [B,H] f32 device or NULL, h [(T+1),B,H] f32 device out,
+ *   x_q_out [T,B,I] int32 device or NULL. */
+QGRU_API int qgru_forward_f32(qgru_handle *h, int T, int B, const float *x, const float *h0,
+                              float *h_out, int32_t *x_q_out, unsigned flags, void *stream);
+
+/* The same two calls for callers that hold HOST buffers (pinned or pageable): the library
+ * stages x to the device, runs the forward and copies h back, all on `stream`; returns
+ * after the stream has been synchronised. */
+QGRU_API int qgru_forward_i32_host(qgru_handle *h, int T, int B, const int32_t *x_q,
+                                   const int32_t *h0_q, int32_t *h_q, unsigned flags,
+                                   void *stream);
+QGRU_API int qgru_forward_f32_host(qgru_handle *h, int T, int B, const float *x,
+                                   const float *h0, float *h_out, unsigned flags,
+                                   void *stream);
+
+/* Blocks until the work queued on `stream` by this handle is done and reports a device-side
+ * bounded-wait expiry (QGRU_ERR_TIMEOUT) or CUDA error, as the reference's
+ * cudaDeviceSynchronize + cudaGetLastError + throw does (src/gru_interface.cc:594-602). */
+QGRU_API int qgru_synchronize(qgru_handle *h, void *stream);
+
+/* Timing of the two kernels of the most recent forward, measured with CUDA events on the
+ * launching stream (milliseconds; synchronises).  Any pointer may be NULL. */
+QGRU_API int qgru_last_timing(qgru_handle *h, float *ms_input_gemm, float *ms_recurrence,
+                              float *ms_total);
+
+/* Number of kernels launched by this handle since creation. */
+QGRU_API uint64_t qgru_launch_count(const qgru_handle *h);
+
+/* Which implementation the next forward will use, as a short human-readable string
+ * ("gemm=tcgen05_i8 rec=mma ..."), for benchmarks and tests. */
+QGRU_API const char *qgru_describe_plan(qgru_handle *h, int T, int B);
+
+/* Restrict or force kernel choices (testing): name/value pairs such as
+ * ("gemm","simt"), ("rec","generic").  Unknown names return QGRU_ERR_BAD_ARG. */
+QGRU_API int qgru_set_option(qgru_handle *h, const char *name, const char *value);
+
+/* ------------------------------------------------------- float mode / calibration */
+
+/* hasteGRUForward (src/gru_interface.cc:173-207): unquantized fp32 GRU.
+ *   h [(T+1),B,H] f32 out; v [T,B,4H] f32 out or NULL (z, r, n, Rh_n+br_n as the
+ *   reference's training buffer). */
+QGRU_API int qgru_forward_float(qgru_handle *h, int T, int B, const float *W, const float *R,
+                                const float *bw, const float *br, const float *x,
+                                const float *h0, float *h_out, float *v_out, void *stream);
+
+/* forwardWithCalibrationGPU, MinMax branch (src/gru_interface.cc:1283-1372 with
+ * updateGRUQuantizationRangesGPU, src/calibration_gpu.cu:1847-1953): float forward, then
+ * fold the batch's min/max of every operator into `ranges` (host, in/out).  Synchronous.
+ *   h_out [(T+1),B,H] f32 device or NULL. */
+QGRU_API int qgru_calibrate_minmax(qgru_handle *h, int T, int B, const float *W,
+                                   const float *R, const float *bw, const float *br,
+                                   const float *x, const float *h0, qgru_ranges *ranges,
+                                   float *h_out, void *stream);
+
+/* Initialise a qgru_ranges to "empty" (min=+FLT_MAX, max=-FLT_MAX), as
+ * GRUQuantizationRanges::reset does (include/gru_quantization_ranges.h:75-123). */
+QGRU_API void qgru_ranges_reset(qgru_ranges *r, int hidden);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QGRU_H_ */

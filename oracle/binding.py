@@ -1,0 +1,181 @@
+"""TEST INFRASTRUCTURE: ctypes bindings of the two checkers.
+
+``Oracle``    libqgru_oracle.so - the plain-C restatement (oracle/qgru_oracle.c)
+``Reference`` _ref/libqgru_ref.so - the unmodified reference sources + oracle/ref_shim.cc
+
+Both expose the same method names so a test can run either.  Only tests/, the smoke test and
+the CPU-baseline leg of bench.py may import this module; the product never does.
+"""
+import ctypes as C
+import os
+import subprocess
+import sys
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_ROOT = os.path.dirname(_HERE)
+REF_ROOT = os.environ.get("QGRU_REF_ROOT", "/root/reference")
+
+
+def _pkg():
+    sys.path.insert(0, _ROOT) if _ROOT not in sys.path else None
+    from __graft_entry__ import load_package
+    return load_package()
+
+
+def _f(a):
+    return a.ctypes.data_as(C.POINTER(C.c_float))
+
+
+def _i(a):
+    return a.ctypes.data_as(C.POINTER(C.c_int32))
+
+
+def build_oracle():
+    so = os.path.join(_HERE, "libqgru_oracle.so")
+    src = os.path.join(_HERE, "qgru_oracle.c")
+    if not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+        subprocess.run(["make", "-C", _HERE, "oracle"], check=True, capture_output=True)
+    return so
+
+
+def build_ref():
+    """Compile the reference where it lies; returns None if the tree is absent (GPU box)."""
+    so = os.path.join(_HERE, "_ref", "libqgru_ref.so")
+    if os.path.isdir(os.path.join(REF_ROOT, "src")):
+        subprocess.run(["make", "-C", _HERE, "-j8", "ref", "REF_ROOT=" + REF_ROOT], check=True,
+                       capture_output=True)
+    return so if os.path.exists(so) else None
+
+
+class _Checker:
+    prefix = ""
+
+    def __init__(self, path):
+        self.cabi = _pkg()._cabi
+        self.lib = C.CDLL(path)
+        p = self.prefix
+        self.lib[p + "rshift_round"].restype = C.c_int64
+        self.lib[p + "rshift_round"].argtypes = [C.c_int64, C.c_int]
+        self.lib[p + "lut_eval"].restype = C.c_int32
+
+    def _fn(self, name):
+        return self.lib[self.prefix + name]
+
+    def rshift_round(self, x, n):
+        return int(self._fn("rshift_round")(int(x), int(n)))
+
+    def encode_mshift(self, scale):
+        m, s = C.c_uint16(), C.c_int8()
+        rc = self._fn("encode_mshift")(C.c_float(scale), C.byref(m), C.byref(s))
+        return None if rc else (m.value, s.value)
+
+    def lut_eval(self, lut, q, in_op, out_op):
+        return int(self._fn("lut_eval")(C.byref(lut), C.c_int32(int(q)), C.byref(in_op), C.byref(out_op)))
+
+    def generate_luts(self, params):
+        rc = self._fn("generate_luts")(C.byref(params))
+        if rc:
+            raise RuntimeError("generate_luts failed")
+
+    def calc_params_from_ranges(self, ranges, params):
+        """ranges: params.Ranges-like object with .struct(); returns the 4 scale arrays."""
+        Cn = 3 * ranges.hidden
+        sc = [np.zeros(Cn, np.float32) for _ in range(4)]
+        rs = ranges.struct()
+        rc = self._fn("calc_params_from_ranges")(C.byref(rs), C.byref(params), *[_f(a) for a in sc])
+        if rc:
+            raise RuntimeError("calc_params_from_ranges failed")
+        return sc
+
+    def quantize_weights(self, I, H, W, R, bw, br, params, sc):
+        Cn = 3 * H
+        out = [np.zeros((I, Cn), np.int32), np.zeros((H, Cn), np.int32), np.zeros(Cn, np.int32),
+               np.zeros(Cn, np.int32)]
+        rc = self._fn("quantize_weights")(I, H, _f(W), _f(R), _f(bw), _f(br), C.byref(params),
+                                          *[_f(a) for a in sc], *[_i(a) for a in out])
+        if rc:
+            raise RuntimeError("quantize_weights failed")
+        return out
+
+    def quantize(self, x, params, op):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.zeros(x.shape, np.int32)
+        rc = self._fn("quantize")(_f(x), _i(out), C.c_size_t(x.size), C.byref(params), int(op))
+        if rc:
+            raise RuntimeError("quantize failed")
+        return out
+
+    def dequantize(self, q, params, op):
+        q = np.ascontiguousarray(q, np.int32)
+        out = np.zeros(q.shape, np.float32)
+        rc = self._fn("dequantize")(_i(q), _f(out), C.c_size_t(q.size), C.byref(params), int(op))
+        if rc:
+            raise RuntimeError("dequantize failed")
+        return out
+
+    def forward_i32(self, T, B, I, H, wq, x_q, h0_q, params, sc, threads=1):
+        x_q = np.ascontiguousarray(x_q, np.int32)
+        h = np.zeros((T + 1, B, H), np.int32)
+        h0p = _i(np.ascontiguousarray(h0_q, np.int32)) if h0_q is not None else None
+        args = [T, B, I, H, *[_i(np.ascontiguousarray(a, np.int32)) for a in wq], _i(x_q), h0p,
+                C.byref(params), *[_f(a) for a in sc], _i(h)]
+        if threads > 1:
+            rc = self._fn("forward_i32_mt")(*args, int(threads))
+        else:
+            rc = self._fn("forward_i32")(*args)
+        if rc:
+            raise RuntimeError("forward_i32 failed")
+        return h
+
+    def forward_f32(self, T, B, I, H, wq, x, h0, params, sc):
+        x = np.ascontiguousarray(x, np.float32)
+        h = np.zeros((T + 1, B, H), np.float32)
+        h0p = _f(np.ascontiguousarray(h0, np.float32)) if h0 is not None else None
+        rc = self._fn("forward_f32")(T, B, I, H, *[_i(np.ascontiguousarray(a, np.int32)) for a in wq],
+                                     _f(x), h0p, C.byref(params), *[_f(a) for a in sc], _f(h))
+        if rc:
+            raise RuntimeError("forward_f32 failed")
+        return h
+
+
+class Oracle(_Checker):
+    prefix = "orc_"
+    kind = "port"
+
+    def __init__(self):
+        super().__init__(build_oracle())
+
+    def forward_float(self, T, B, I, H, W, R, bw, br, x, h0=None, ranges=None, want_v=False):
+        """fp32 GRU; optionally folds the MinMax ranges (orc_forward_float)."""
+        h = np.zeros((T + 1, B, H), np.float32)
+        v = np.zeros((T, B, 4 * H), np.float32) if want_v else None
+        rs = ranges.struct() if ranges is not None else None
+        rc = self.lib.orc_forward_float(
+            T, B, I, H, _f(W), _f(R), _f(bw), _f(br), _f(np.ascontiguousarray(x, np.float32)),
+            _f(np.ascontiguousarray(h0, np.float32)) if h0 is not None else None, _f(h),
+            _f(v) if v is not None else None, C.byref(rs) if rs is not None else None)
+        if rc:
+            raise RuntimeError("forward_float failed")
+        if ranges is not None:
+            ranges.load(rs)
+        return (h, v) if want_v else h
+
+
+class Reference(_Checker):
+    prefix = "ref_"
+    kind = "reference"
+
+    def __init__(self):
+        so = build_ref()
+        if so is None:
+            raise FileNotFoundError("oracle/_ref/libqgru_ref.so has not been built")
+        super().__init__(so)
+
+
+def reference_or_none():
+    try:
+        return Reference()
+    except (FileNotFoundError, OSError, subprocess.CalledProcessError):
+        return None

@@ -1,0 +1,350 @@
+// ref_shim.cc - TEST INFRASTRUCTURE, not product code.
+//
+// A thin extern "C" driver around the UNMODIFIED reference sources (compiled where they
+// lie by oracle/Makefile into oracle/_ref/).  It lets the tests, the golden-vector
+// generator and the CPU-baseline leg of the benchmark call the reference's own CPU
+// integer path through ctypes, using the POD types of include/qgru.h as the exchange
+// format.  Only host functions of the reference are reached: the CPU forward
+// (src/gru_forward_cpu_quant.cc), quantitativeWeightCPU / quantGRUForwardCPU /
+// calculateGRUQuantitativeParameters (src/gru_interface.cc) and the LUT generator
+// (src/quantize_ops.cu:21-52).  No CUDA call is made by anything reached from here.
+#include <cstring>
+#include <stdexcept>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "gru_interface.h"
+#include "gru_quant_cpu.h"
+#include "pot_sqnr_calibrator.h"
+#include "quantize_ops_helper.h"
+
+#include "qgru.h"
+
+namespace {
+
+thread_local std::string g_err;
+
+QuantBitWidth bwOf(const qgru_op &o) { return QuantBitWidth(o.bits, o.is_unsigned != 0); }
+
+void fillConfig(const qgru_params &p, OperatorQuantConfig &c) {
+    c.x_ = bwOf(p.op[QGRU_OP_X]);
+    c.h_ = bwOf(p.op[QGRU_OP_H]);
+    c.W_ = bwOf(p.op[QGRU_OP_W]);
+    c.R_ = bwOf(p.op[QGRU_OP_R]);
+    c.bw_ = bwOf(p.op[QGRU_OP_BW]);
+    c.br_ = bwOf(p.op[QGRU_OP_BR]);
+    c.weight_ih_linear_ = bwOf(p.op[QGRU_OP_IH_LINEAR]);
+    c.weight_hh_linear_ = bwOf(p.op[QGRU_OP_HH_LINEAR]);
+    c.update_gate_input_ = bwOf(p.op[QGRU_OP_UPDATE_IN]);
+    c.update_gate_output_ = bwOf(p.op[QGRU_OP_UPDATE_OUT]);
+    c.reset_gate_input_ = bwOf(p.op[QGRU_OP_RESET_IN]);
+    c.reset_gate_output_ = bwOf(p.op[QGRU_OP_RESET_OUT]);
+    c.new_gate_input_ = bwOf(p.op[QGRU_OP_NEW_IN]);
+    c.new_gate_output_ = bwOf(p.op[QGRU_OP_NEW_OUT]);
+    c.mul_reset_hidden_ = bwOf(p.op[QGRU_OP_MUL_RESET_HIDDEN]);
+    c.mul_new_contribution_ = bwOf(p.op[QGRU_OP_MUL_NEW_CONTRIB]);
+    c.mul_old_contribution_ = bwOf(p.op[QGRU_OP_MUL_OLD_CONTRIB]);
+    c.x_symmetric_ = p.op[QGRU_OP_X].symmetric;
+    c.h_symmetric_ = p.op[QGRU_OP_H].symmetric;
+    c.W_symmetric_ = p.op[QGRU_OP_W].symmetric;
+    c.R_symmetric_ = p.op[QGRU_OP_R].symmetric;
+    c.bw_symmetric_ = p.op[QGRU_OP_BW].symmetric;
+    c.br_symmetric_ = p.op[QGRU_OP_BR].symmetric;
+    c.weight_ih_linear_symmetric_ = p.op[QGRU_OP_IH_LINEAR].symmetric;
+    c.weight_hh_linear_symmetric_ = p.op[QGRU_OP_HH_LINEAR].symmetric;
+    c.update_gate_input_symmetric_ = p.op[QGRU_OP_UPDATE_IN].symmetric;
+    c.update_gate_output_symmetric_ = p.op[QGRU_OP_UPDATE_OUT].symmetric;
+    c.reset_gate_input_symmetric_ = p.op[QGRU_OP_RESET_IN].symmetric;
+    c.reset_gate_output_symmetric_ = p.op[QGRU_OP_RESET_OUT].symmetric;
+    c.new_gate_input_symmetric_ = p.op[QGRU_OP_NEW_IN].symmetric;
+    c.new_gate_output_symmetric_ = p.op[QGRU_OP_NEW_OUT].symmetric;
+    c.mul_reset_hidden_symmetric_ = p.op[QGRU_OP_MUL_RESET_HIDDEN].symmetric;
+    c.mul_new_contribution_symmetric_ = p.op[QGRU_OP_MUL_NEW_CONTRIB].symmetric;
+    c.mul_old_contribution_symmetric_ = p.op[QGRU_OP_MUL_OLD_CONTRIB].symmetric;
+    using G = OperatorQuantConfig::QuantizationGranularity;
+    c.W_granularity_ = static_cast<G>(p.granularity[0]);
+    c.R_granularity_ = static_cast<G>(p.granularity[1]);
+    c.bw_granularity_ = static_cast<G>(p.granularity[2]);
+    c.br_granularity_ = static_cast<G>(p.granularity[3]);
+    c.usePOT2_ = p.use_pot2 != 0;
+}
+
+QuantParam qpOf(const qgru_op &o) { return QuantParam{o.scale, o.zero_point}; }
+
+void lutFromPod(const qgru_lut &in, SigmoidLUT &out) {
+    std::memset(&out, 0, sizeof(out));
+    for (int i = 0; i < NUM_SEGMENTS; ++i) {
+        out.segments[i].q_b = in.seg[i].q_b;
+        out.segments[i].n_BX_total = static_cast<int8_t>(in.seg[i].n_bx);
+        out.segments[i].term_c_precomputed = in.seg[i].term_c;
+        out.segments[i].threshold = in.seg[i].threshold;
+    }
+    out.zp_x = in.zp_x;
+}
+
+void lutToPod(const SigmoidLUT &in, qgru_lut &out) {
+    std::memset(&out, 0, sizeof(out));
+    for (int i = 0; i < NUM_SEGMENTS; ++i) {
+        out.seg[i].q_b = in.segments[i].q_b;
+        out.seg[i].n_bx = in.segments[i].n_BX_total;
+        out.seg[i].term_c = in.segments[i].term_c_precomputed;
+        out.seg[i].threshold = in.segments[i].threshold;
+    }
+    out.zp_x = in.zp_x;
+}
+
+void channelFromPod(ChannelQuantParam &c, int hidden, int gran, const float *scales) {
+    c.granularity = static_cast<OperatorQuantConfig::QuantizationGranularity>(gran);
+    c.hidden = hidden;
+    c.resize(hidden * 3);
+    for (int i = 0; i < hidden * 3; ++i) c.channel(i) = QuantParam{scales[i], 0};
+}
+
+GRUQuantParams fromPod(const qgru_params &p, const float *sW, const float *sR, const float *sbw,
+                       const float *sbr) {
+    GRUQuantParams q;
+    fillConfig(p, q.bitwidth_config_);
+    q.hidden_ = p.hidden;
+    q.x_ = qpOf(p.op[QGRU_OP_X]);
+    q.h_ = qpOf(p.op[QGRU_OP_H]);
+    channelFromPod(q.W_, p.hidden, p.granularity[0], sW);
+    channelFromPod(q.R_, p.hidden, p.granularity[1], sR);
+    channelFromPod(q.bw_, p.hidden, p.granularity[2], sbw);
+    channelFromPod(q.br_, p.hidden, p.granularity[3], sbr);
+    q.weight_ih_linear_ = qpOf(p.op[QGRU_OP_IH_LINEAR]);
+    q.weight_hh_linear_ = qpOf(p.op[QGRU_OP_HH_LINEAR]);
+    q.update_gate_input_ = qpOf(p.op[QGRU_OP_UPDATE_IN]);
+    q.update_gate_output_ = qpOf(p.op[QGRU_OP_UPDATE_OUT]);
+    q.reset_gate_input_ = qpOf(p.op[QGRU_OP_RESET_IN]);
+    q.reset_gate_output_ = qpOf(p.op[QGRU_OP_RESET_OUT]);
+    q.new_gate_input_ = qpOf(p.op[QGRU_OP_NEW_IN]);
+    q.new_gate_output_ = qpOf(p.op[QGRU_OP_NEW_OUT]);
+    q.mul_reset_hidden_ = qpOf(p.op[QGRU_OP_MUL_RESET_HIDDEN]);
+    q.mul_new_contribution_ = qpOf(p.op[QGRU_OP_MUL_NEW_CONTRIB]);
+    q.mul_old_contribution_ = qpOf(p.op[QGRU_OP_MUL_OLD_CONTRIB]);
+    lutFromPod(p.lut[QGRU_LUT_UPDATE], q.sigmoid_update_gate_lut_);
+    lutFromPod(p.lut[QGRU_LUT_RESET], q.sigmoid_reset_gate_lut_);
+    lutFromPod(p.lut[QGRU_LUT_NEW], q.tanh_new_gate_lut_);
+    return q;
+}
+
+void scalarToPod(const QuantParam &q, qgru_op &o) {
+    o.scale = q.scale;
+    o.zero_point = q.zero_point;
+}
+
+void toPod(const GRUQuantParams &q, qgru_params &p, float *sW, float *sR, float *sbw, float *sbr) {
+    p.hidden = q.hidden_;
+    scalarToPod(q.x_, p.op[QGRU_OP_X]);
+    scalarToPod(q.h_, p.op[QGRU_OP_H]);
+    scalarToPod(q.W_.tensor(), p.op[QGRU_OP_W]);
+    scalarToPod(q.R_.tensor(), p.op[QGRU_OP_R]);
+    scalarToPod(q.bw_.tensor(), p.op[QGRU_OP_BW]);
+    scalarToPod(q.br_.tensor(), p.op[QGRU_OP_BR]);
+    scalarToPod(q.weight_ih_linear_, p.op[QGRU_OP_IH_LINEAR]);
+    scalarToPod(q.weight_hh_linear_, p.op[QGRU_OP_HH_LINEAR]);
+    scalarToPod(q.update_gate_input_, p.op[QGRU_OP_UPDATE_IN]);
+    scalarToPod(q.update_gate_output_, p.op[QGRU_OP_UPDATE_OUT]);
+    scalarToPod(q.reset_gate_input_, p.op[QGRU_OP_RESET_IN]);
+    scalarToPod(q.reset_gate_output_, p.op[QGRU_OP_RESET_OUT]);
+    scalarToPod(q.new_gate_input_, p.op[QGRU_OP_NEW_IN]);
+    scalarToPod(q.new_gate_output_, p.op[QGRU_OP_NEW_OUT]);
+    scalarToPod(q.mul_reset_hidden_, p.op[QGRU_OP_MUL_RESET_HIDDEN]);
+    scalarToPod(q.mul_new_contribution_, p.op[QGRU_OP_MUL_NEW_CONTRIB]);
+    scalarToPod(q.mul_old_contribution_, p.op[QGRU_OP_MUL_OLD_CONTRIB]);
+    for (int c = 0; c < q.hidden_ * 3; ++c) {
+        if (sW) sW[c] = q.W_.channel(c).scale;
+        if (sR) sR[c] = q.R_.channel(c).scale;
+        if (sbw) sbw[c] = q.bw_.channel(c).scale;
+        if (sbr) sbr[c] = q.br_.channel(c).scale;
+    }
+    lutToPod(q.sigmoid_update_gate_lut_, p.lut[QGRU_LUT_UPDATE]);
+    lutToPod(q.sigmoid_reset_gate_lut_, p.lut[QGRU_LUT_RESET]);
+    lutToPod(q.tanh_new_gate_lut_, p.lut[QGRU_LUT_NEW]);
+}
+
+template <class F>
+int guarded(F &&f) {
+    try {
+        f();
+        return 0;
+    } catch (const std::exception &e) {
+        g_err = e.what();
+        return 1;
+    } catch (...) {
+        g_err = "unknown exception";
+        return 1;
+    }
+}
+
+// The reference's integer core with int32 inputs and outputs: what quantGRUForwardCPU
+// (src/gru_interface.cc:796-835) does between quantising x and dequantising h.
+void forwardI32(int T, int B, int I, int H, const int32_t *W, const int32_t *R, const int32_t *bw,
+                const int32_t *br, const int32_t *x_q, const int32_t *h0_q,
+                const GRUQuantParams &q, int32_t *h_q) {
+    const int NH = B * H;
+    for (int i = 0; i < NH; ++i) h_q[i] = h0_q ? h0_q[i] : q.h_.zero_point;
+    cpu::ForwardPassQuantCPU fwd(false, B, I, H);
+    fwd.setRescaleParam(q);
+    fwd.Run(T, W, R, bw, br, x_q, h_q, nullptr, 0.0f, nullptr);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *ref_last_error() { return g_err.c_str(); }
+
+int ref_encode_mshift(float scale, uint16_t *m, int8_t *s) {
+    return guarded([&] {
+        FixedPointScale f = encodeMShift(scale);
+        *m = f.multiplier;
+        *s = f.shift;
+    });
+}
+
+int64_t ref_rshift_round(int64_t x, int n) { return rshift_round(x, static_cast<int8_t>(n)); }
+
+int32_t ref_lut_eval(const qgru_lut *lut, int32_t q_x, const qgru_op *in_bw, const qgru_op *out_bw) {
+    SigmoidLUT l;
+    lutFromPod(*lut, l);
+    return piecewise_linear(q_x, l, bwOf(*in_bw), bwOf(*out_bw));
+}
+
+int ref_generate_luts(qgru_params *p) {
+    return guarded([&] {
+        std::vector<float> ones(p->hidden * 3, 1.0f);
+        GRUQuantParams q = fromPod(*p, ones.data(), ones.data(), ones.data(), ones.data());
+        generate_piecewise_linear_lut_to_params(q);
+        lutToPod(q.sigmoid_update_gate_lut_, p->lut[QGRU_LUT_UPDATE]);
+        lutToPod(q.sigmoid_reset_gate_lut_, p->lut[QGRU_LUT_RESET]);
+        lutToPod(q.tanh_new_gate_lut_, p->lut[QGRU_LUT_NEW]);
+    });
+}
+
+int ref_calc_params_from_ranges(const qgru_ranges *r, qgru_params *p, float *sW, float *sR,
+                                float *sbw, float *sbr) {
+    return guarded([&] {
+        OperatorQuantConfig cfg;
+        fillConfig(*p, cfg);
+        GRUQuantizationRanges g(r->hidden);
+        const int C = r->hidden * 3;
+        g.min_x_ = r->min_v[QGRU_OP_X]; g.max_x_ = r->max_v[QGRU_OP_X];
+        g.min_h_ = r->min_v[QGRU_OP_H]; g.max_h_ = r->max_v[QGRU_OP_H];
+        g.min_Wx_ = r->min_v[QGRU_OP_IH_LINEAR]; g.max_Wx_ = r->max_v[QGRU_OP_IH_LINEAR];
+        g.min_Rh_ = r->min_v[QGRU_OP_HH_LINEAR]; g.max_Rh_ = r->max_v[QGRU_OP_HH_LINEAR];
+        g.min_update_gate_input_ = r->min_v[QGRU_OP_UPDATE_IN]; g.max_update_gate_input_ = r->max_v[QGRU_OP_UPDATE_IN];
+        g.min_update_gate_output_ = r->min_v[QGRU_OP_UPDATE_OUT]; g.max_update_gate_output_ = r->max_v[QGRU_OP_UPDATE_OUT];
+        g.min_reset_gate_input_ = r->min_v[QGRU_OP_RESET_IN]; g.max_reset_gate_input_ = r->max_v[QGRU_OP_RESET_IN];
+        g.min_reset_gate_output_ = r->min_v[QGRU_OP_RESET_OUT]; g.max_reset_gate_output_ = r->max_v[QGRU_OP_RESET_OUT];
+        g.min_new_gate_input_ = r->min_v[QGRU_OP_NEW_IN]; g.max_new_gate_input_ = r->max_v[QGRU_OP_NEW_IN];
+        g.min_new_gate_output_ = r->min_v[QGRU_OP_NEW_OUT]; g.max_new_gate_output_ = r->max_v[QGRU_OP_NEW_OUT];
+        g.min_mul_reset_hidden_ = r->min_v[QGRU_OP_MUL_RESET_HIDDEN]; g.max_mul_reset_hidden_ = r->max_v[QGRU_OP_MUL_RESET_HIDDEN];
+        g.min_mul_new_contribution_ = r->min_v[QGRU_OP_MUL_NEW_CONTRIB]; g.max_mul_new_contribution_ = r->max_v[QGRU_OP_MUL_NEW_CONTRIB];
+        g.min_mul_old_contribution_ = r->min_v[QGRU_OP_MUL_OLD_CONTRIB]; g.max_mul_old_contribution_ = r->max_v[QGRU_OP_MUL_OLD_CONTRIB];
+        g.min_W_.assign(r->min_W, r->min_W + C); g.max_W_.assign(r->max_W, r->max_W + C);
+        g.min_R_.assign(r->min_R, r->min_R + C); g.max_R_.assign(r->max_R, r->max_R + C);
+        g.min_bw_.assign(r->min_bw, r->min_bw + C); g.max_bw_.assign(r->max_bw, r->max_bw + C);
+        g.min_br_.assign(r->min_br, r->min_br + C); g.max_br_.assign(r->max_br, r->max_br + C);
+        GRUQuantParams q = calculateGRUQuantitativeParameters(g, cfg);
+        toPod(q, *p, sW, sR, sbw, sbr);
+    });
+}
+
+int ref_quantize_weights(int I, int H, const float *W, const float *R, const float *bw,
+                         const float *br, const qgru_params *p, const float *sW, const float *sR,
+                         const float *sbw, const float *sbr, int32_t *W_q, int32_t *R_q,
+                         int32_t *bw_q, int32_t *br_q) {
+    return guarded([&] {
+        GRUQuantParams q = fromPod(*p, sW, sR, sbw, sbr);
+        quantitativeWeightCPU(I, H, W, R, bw, br, q, W_q, R_q, bw_q, br_q);
+    });
+}
+
+// quantize() of one activation tensor with operator `op` of p (src/gru_interface.cc:806-809).
+int ref_quantize(const float *x, int32_t *out, size_t n, const qgru_params *p, int op) {
+    return guarded([&] {
+        const QuantParam qp = qpOf(p->op[op]);
+        const FixedPointScale fs = toFixedScale(qp, p->use_pot2 != 0);
+        const QuantBitWidth bw = bwOf(p->op[op]);
+        for (size_t i = 0; i < n; ++i) out[i] = quantize(x[i], fs, qp.zero_point, bw);
+    });
+}
+
+int ref_dequantize(const int32_t *q_in, float *out, size_t n, const qgru_params *p, int op) {
+    return guarded([&] {
+        const QuantParam qp = qpOf(p->op[op]);
+        const FixedPointScale fs = toFixedScale(qp, p->use_pot2 != 0);
+        for (size_t i = 0; i < n; ++i) out[i] = dequantize(q_in[i], fs, qp.zero_point);
+    });
+}
+
+int ref_forward_i32(int T, int B, int I, int H, const int32_t *W, const int32_t *R,
+                    const int32_t *bw, const int32_t *br, const int32_t *x_q, const int32_t *h0_q,
+                    const qgru_params *p, const float *sW, const float *sR, const float *sbw,
+                    const float *sbr, int32_t *h_q) {
+    return guarded([&] {
+        GRUQuantParams q = fromPod(*p, sW, sR, sbw, sbr);
+        forwardI32(T, B, I, H, W, R, bw, br, x_q, h0_q, q, h_q);
+    });
+}
+
+// Same result as ref_forward_i32, computed on `nthreads` host threads by cutting the batch
+// into independent slices (rows of a batch never interact in a GRU).  Used as the
+// all-cores CPU baseline; the reference itself is single threaded.
+int ref_forward_i32_mt(int T, int B, int I, int H, const int32_t *W, const int32_t *R,
+                       const int32_t *bw, const int32_t *br, const int32_t *x_q,
+                       const int32_t *h0_q, const qgru_params *p, const float *sW,
+                       const float *sR, const float *sbw, const float *sbr, int32_t *h_q,
+                       int nthreads) {
+    return guarded([&] {
+        GRUQuantParams q = fromPod(*p, sW, sR, sbw, sbr);
+        if (nthreads < 1) nthreads = 1;
+        if (nthreads > B) nthreads = B;
+        std::vector<std::thread> th;
+        std::vector<std::string> errs(nthreads);
+        for (int w = 0; w < nthreads; ++w) {
+            th.emplace_back([&, w] {
+                try {
+                    const int b0 = static_cast<int>(static_cast<int64_t>(B) * w / nthreads);
+                    const int b1 = static_cast<int>(static_cast<int64_t>(B) * (w + 1) / nthreads);
+                    const int Bs = b1 - b0;
+                    if (Bs <= 0) return;
+                    std::vector<int32_t> xs(static_cast<size_t>(T) * Bs * I);
+                    std::vector<int32_t> hs(static_cast<size_t>(T + 1) * Bs * H);
+                    std::vector<int32_t> h0s;
+                    for (int t = 0; t < T; ++t)
+                        std::memcpy(&xs[static_cast<size_t>(t) * Bs * I],
+                                    &x_q[(static_cast<size_t>(t) * B + b0) * I],
+                                    sizeof(int32_t) * Bs * I);
+                    if (h0_q) h0s.assign(h0_q + static_cast<size_t>(b0) * H, h0_q + static_cast<size_t>(b1) * H);
+                    forwardI32(T, Bs, I, H, W, R, bw, br, xs.data(), h0_q ? h0s.data() : nullptr, q,
+                               hs.data());
+                    for (int t = 0; t <= T; ++t)
+                        std::memcpy(&h_q[(static_cast<size_t>(t) * B + b0) * H],
+                                    &hs[static_cast<size_t>(t) * Bs * H], sizeof(int32_t) * Bs * H);
+                } catch (const std::exception &e) {
+                    errs[w] = e.what();
+                }
+            });
+        }
+        for (auto &t : th) t.join();
+        for (auto &e : errs)
+            if (!e.empty()) throw std::runtime_error(e);
+    });
+}
+
+// quantGRUForwardCPU, int32-weights overload (src/gru_interface.cc:796-867): float x in,
+// float h out.
+int ref_forward_f32(int T, int B, int I, int H, const int32_t *W, const int32_t *R,
+                    const int32_t *bw, const int32_t *br, const float *x, const float *h0,
+                    const qgru_params *p, const float *sW, const float *sR, const float *sbw,
+                    const float *sbr, float *h) {
+    return guarded([&] {
+        GRUQuantParams q = fromPod(*p, sW, sR, sbw, sbr);
+        quantGRUForwardCPU(false, T, B, I, H, W, R, bw, br, x, h0, q, h, nullptr);
+    });
+}
+
+}  // extern "C"

@@ -1,0 +1,812 @@
+// qgru_api.cu - the device half of the C ABI (include/qgru.h): handle, parameter derivation,
+// weight packing and the forward orchestration.  Replaces, for the integer inference path,
+// gru::ForwardPassQuant (src/gru_forward_gpu_quant.cu:412-831 of the reference) and the three
+// quantGRUForwardInt* drivers (src/gru_interface.cc:551-790): the per-call stream creation,
+// device allocations and device-wide synchronisations of the reference become a handle with a
+// growing workspace; all work is queued on the caller's stream.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "qgru_gemm_tc.cuh"
+#include "qgru_internal.h"
+#include "qgru_kernels.cuh"
+
+using namespace qgru;
+
+namespace {
+
+struct DevBuf {
+    void *p = nullptr;
+    size_t cap = 0;
+};
+
+}  // namespace
+
+struct qgru_handle {
+    int device = 0, I = 0, H = 0, C = 0, Ipad = 0, Hpad = 0;
+    int sm_count = 0, smem_optin = 0, coop = 0;
+    std::string err;
+    std::string plan_text;
+    bool params_set = false, weights_set = false;
+    qgru_params p{};
+    std::vector<float> sc[4];  // W, R, bw, br scales
+    // storage plan
+    bool fast = false;         // 8-bit operands, int32 accumulation
+    bool x_uns = false, h_uns = false;
+    int ih_bytes = 1;
+    float x_scale = 1.f, h_scale = 1.f;
+    GateConsts gc_host{};
+    // options
+    int opt_gemm = 0;      // 0 auto, 1 simt, 2 tcgen05
+    int opt_rec = 0;       // 0 auto, 1 dp4a, 3 generic
+    int opt_sm_limit = 0;  // 0: all SMs
+    unsigned spin_limit = 1u << 24;
+    // device state that lives with the handle
+    GateConsts *d_gc = nullptr;
+    int32_t *d_tables = nullptr;
+    int n_table = 0;
+    Rescale *d_rs[2] = {nullptr, nullptr};    // gemm rescale: x side, h side
+    Rescale *d_brs[2] = {nullptr, nullptr};   // bias rescale
+    float *d_wscale[4] = {nullptr, nullptr, nullptr, nullptr};
+    int64_t *d_corr[2] = {nullptr, nullptr};
+    int32_t *d_wq[4] = {nullptr, nullptr, nullptr, nullptr};  // W_q, R_q, bw_q, br_q
+    int32_t *d_wsum[2] = {nullptr, nullptr};
+    int8_t *d_w8[2] = {nullptr, nullptr};     // W8 [3H][Ipad], R8 [3H][Hpad]
+    int *d_flags = nullptr;                   // [0] data errors, [1] barrier abort
+    int *h_flags = nullptr;                   // pinned mirror
+    unsigned *d_bar = nullptr;
+    int bar_groups = 0;
+    // workspace
+    DevBuf x8, ih, h8, x32, ih32, hh32, hq32, stage_in, stage_h0, stage_out;
+    cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+    bool timing_valid = false;
+    uint64_t launches = 0;
+    TcGemmState tc;
+};
+
+namespace {
+
+#define CK(call)                                                                          \
+    do {                                                                                  \
+        cudaError_t e_ = (call);                                                          \
+        if (e_ != cudaSuccess) {                                                          \
+            h->err = std::string(#call) + ": " + cudaGetErrorString(e_);                  \
+            return QGRU_ERR_CUDA;                                                         \
+        }                                                                                 \
+    } while (0)
+
+int fail(qgru_handle *h, int code, const std::string &msg) {
+    h->err = msg;
+    return code;
+}
+
+int ensure(qgru_handle *h, DevBuf &b, size_t bytes) {
+    if (bytes <= b.cap) return QGRU_OK;
+    if (b.p) cudaFree(b.p);
+    b.p = nullptr;
+    b.cap = 0;
+    const size_t want = bytes + bytes / 8 + 256;
+    cudaError_t e = cudaMalloc(&b.p, want);
+    if (e != cudaSuccess) {
+        h->err = std::string("cudaMalloc(workspace): ") + cudaGetErrorString(e);
+        cudaGetLastError();
+        return QGRU_ERR_NOMEM;
+    }
+    b.cap = want;
+    return QGRU_OK;
+}
+
+template <class T>
+int alloc_dev(qgru_handle *h, T **p, size_t n) {
+    if (*p) {
+        cudaFree(*p);
+        *p = nullptr;
+    }
+    cudaError_t e = cudaMalloc(reinterpret_cast<void **>(p), std::max<size_t>(n, 1) * sizeof(T));
+    if (e != cudaSuccess) {
+        h->err = std::string("cudaMalloc: ") + cudaGetErrorString(e);
+        cudaGetLastError();
+        return QGRU_ERR_NOMEM;
+    }
+    return QGRU_OK;
+}
+
+int grid_for(long long n, int block, int sm_count) {
+    long long g = (n + block - 1) / block;
+    const long long cap = (long long)sm_count * 16;
+    return (int)std::max<long long>(1, std::min(g, cap));
+}
+
+bool shift_ok(Rescale r) { return r.shift >= -62 && r.shift <= 62; }
+
+// Largest |q - zp| an operator's clamped value can reach.
+int64_t max_abs_diff(const qgru_op &o) {
+    const int64_t lo = op_qmin(o), hi = op_qmax(o), zp = o.zero_point;
+    return std::max(std::llabs(hi - zp), std::llabs(lo - zp));
+}
+
+bool narrow_ok(Rescale r, int64_t max_abs) {
+    return r.shift >= 1 && r.shift <= 31 && max_abs * (int64_t)r.mult < (int64_t)0x7fffffff - ((int64_t)1 << 30);
+}
+
+struct RecPlan {
+    int Hs = 0, Bt = 0, P = 0, G = 0;
+    size_t smem = 0;
+};
+
+size_t rec_smem(const qgru_handle *h, int Hs, int Bt) {
+    size_t s = (sizeof(GateConsts) + 15) & ~size_t(15);
+    s += ((size_t)h->n_table * 4 + 15) & ~size_t(15);
+    s += (size_t)3 * Hs * 16;
+    s += (size_t)3 * Hs * h->Hpad;
+    s += (size_t)Bt * h->Hpad;
+    return s;
+}
+
+bool plan_recurrence(const qgru_handle *h, int B, RecPlan *out) {
+    const int sms = h->opt_sm_limit > 0 ? std::min(h->opt_sm_limit, h->sm_count) : h->sm_count;
+    static const int cand[4] = {256, 128, 64, 32};
+    for (int Hs : cand) {
+        if (Hs > 32 && Hs >= 2 * ((h->H + 31) / 32 * 32)) continue;  // no slice wider than needed
+        const int P = (h->H + Hs - 1) / Hs;
+        if (P > sms) continue;
+        const int groups_max = std::max(1, sms / P);
+        const int Bt = (B + groups_max - 1) / groups_max;
+        const size_t s = rec_smem(h, Hs, Bt);
+        if (s > (size_t)h->smem_optin) continue;
+        out->Hs = Hs;
+        out->Bt = Bt;
+        out->P = P;
+        out->G = (B + Bt - 1) / Bt;
+        out->smem = s;
+        return true;
+    }
+    return false;
+}
+
+}  // namespace
+
+extern "C" {
+
+int qgru_create(qgru_handle **out, int device, int input_size, int hidden_size) {
+    if (!out || input_size <= 0 || hidden_size <= 0) return QGRU_ERR_BAD_ARG;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) {
+        cudaGetLastError();
+        return QGRU_ERR_CUDA;
+    }
+    qgru_handle *h = new qgru_handle();
+    h->device = device;
+    h->I = input_size;
+    h->H = hidden_size;
+    h->C = 3 * hidden_size;
+    h->Ipad = (input_size + 31) / 32 * 32;
+    h->Hpad = (hidden_size + 31) / 32 * 32;
+    bool ok = cudaSetDevice(device) == cudaSuccess;
+    ok = ok && cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, device) == cudaSuccess;
+    ok = ok && cudaDeviceGetAttribute(&h->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) == cudaSuccess;
+    ok = ok && cudaDeviceGetAttribute(&h->coop, cudaDevAttrCooperativeLaunch, device) == cudaSuccess;
+    ok = ok && cudaMalloc(&h->d_flags, 2 * sizeof(int)) == cudaSuccess;
+    ok = ok && cudaMemset(h->d_flags, 0, 2 * sizeof(int)) == cudaSuccess;
+    ok = ok && cudaMallocHost(&h->h_flags, 2 * sizeof(int)) == cudaSuccess;
+    for (int i = 0; i < 4 && ok; ++i) ok = cudaEventCreate(&h->ev[i]) == cudaSuccess;
+    if (!ok) {
+        cudaGetLastError();
+        qgru_destroy(h);
+        return QGRU_ERR_CUDA;
+    }
+    h->h_flags[0] = h->h_flags[1] = 0;
+    *out = h;
+    return QGRU_OK;
+}
+
+void qgru_destroy(qgru_handle *h) {
+    if (!h) return;
+    cudaSetDevice(h->device);
+    cudaDeviceSynchronize();
+    cudaFree(h->d_gc);
+    cudaFree(h->d_tables);
+    for (int i = 0; i < 2; ++i) {
+        cudaFree(h->d_rs[i]);
+        cudaFree(h->d_brs[i]);
+        cudaFree(h->d_corr[i]);
+        cudaFree(h->d_wsum[i]);
+        cudaFree(h->d_w8[i]);
+    }
+    for (int i = 0; i < 4; ++i) {
+        cudaFree(h->d_wscale[i]);
+        cudaFree(h->d_wq[i]);
+        if (h->ev[i]) cudaEventDestroy(h->ev[i]);
+    }
+    cudaFree(h->d_flags);
+    if (h->h_flags) cudaFreeHost(h->h_flags);
+    cudaFree(h->d_bar);
+    for (DevBuf *b : {&h->x8, &h->ih, &h->h8, &h->x32, &h->ih32, &h->hh32, &h->hq32, &h->stage_in,
+                      &h->stage_h0, &h->stage_out})
+        cudaFree(b->p);
+    cudaGetLastError();
+    delete h;
+}
+
+const char *qgru_last_error(const qgru_handle *h) { return h ? h->err.c_str() : "null handle"; }
+
+uint64_t qgru_launch_count(const qgru_handle *h) { return h ? h->launches : 0; }
+
+int qgru_set_option(qgru_handle *h, const char *name, const char *value) {
+    if (!h || !name || !value) return QGRU_ERR_BAD_ARG;
+    const std::string n(name), v(value);
+    if (n == "gemm") {
+        if (v == "auto") h->opt_gemm = 0;
+        else if (v == "simt") h->opt_gemm = 1;
+        else if (v == "tcgen05") h->opt_gemm = 2;
+        else return fail(h, QGRU_ERR_BAD_ARG, "gemm: auto|simt|tcgen05");
+    } else if (n == "rec") {
+        if (v == "auto") h->opt_rec = 0;
+        else if (v == "dp4a") h->opt_rec = 1;
+        else if (v == "generic") h->opt_rec = 3;
+        else return fail(h, QGRU_ERR_BAD_ARG, "rec: auto|dp4a|generic");
+    } else if (n == "sm_limit") {
+        h->opt_sm_limit = std::max(0, atoi(value));
+    } else if (n == "spin_limit") {
+        h->spin_limit = (unsigned)std::max(1, atoi(value));
+    } else {
+        return fail(h, QGRU_ERR_BAD_ARG, "unknown option " + n);
+    }
+    return QGRU_OK;
+}
+
+int qgru_set_params(qgru_handle *h, const qgru_params *p, const float *scale_W,
+                    const float *scale_R, const float *scale_bw, const float *scale_br) {
+    if (!h || !p || !scale_W || !scale_R || !scale_bw || !scale_br) return QGRU_ERR_BAD_ARG;
+    if (p->hidden != h->H) return fail(h, QGRU_ERR_BAD_ARG, "params.hidden != handle hidden_size");
+    CK(cudaSetDevice(h->device));
+    const int C = h->C;
+    const bool pot2 = p->use_pot2 != 0;
+    for (int i = 0; i < QGRU_NUM_OPS; ++i)
+        if (p->op[i].bits < 1 || p->op[i].bits > 32) return fail(h, QGRU_ERR_BAD_ARG, "bits outside 1..32");
+    // W/R/bw/br are symmetric with zp = 0 (ensureSymmetricWeightBiasConfig, src/gru_interface.cc:26-32)
+    for (int k : {QGRU_OP_W, QGRU_OP_R, QGRU_OP_BW, QGRU_OP_BR})
+        if (!p->op[k].symmetric) return fail(h, QGRU_ERR_UNSUPPORTED, "W/R/bw/br must be symmetric");
+
+    h->params_set = false;
+    h->weights_set = false;
+    h->p = *p;
+    const float *src[4] = {scale_W, scale_R, scale_bw, scale_br};
+    for (int k = 0; k < 4; ++k) h->sc[k].assign(src[k], src[k] + C);
+
+    const qgru_op *op = p->op;
+    const float s_x = op[QGRU_OP_X].scale, s_h = op[QGRU_OP_H].scale;
+    const float s_ih = op[QGRU_OP_IH_LINEAR].scale, s_hh = op[QGRU_OP_HH_LINEAR].scale;
+
+    // fillLinearParams (src/gru_forward_gpu_quant.cu:672-700)
+    std::vector<Rescale> rs_x(C), rs_h(C), brs_x(C), brs_h(C);
+    std::vector<float> wscale[4];
+    for (int k = 0; k < 4; ++k) wscale[k].resize(C);
+    bool ok = true;
+    for (int c = 0; c < C && ok; ++c) {
+        ok = ok && make_rescale_product(scale_W[c], s_x, s_ih, pot2, &rs_x[c]);
+        ok = ok && make_rescale_to_product(scale_bw[c], scale_W[c], s_x, pot2, &brs_x[c]);
+        ok = ok && make_rescale_product(scale_R[c], s_h, s_hh, pot2, &rs_h[c]);
+        ok = ok && make_rescale_to_product(scale_br[c], scale_R[c], s_h, pot2, &brs_h[c]);
+        for (int k = 0; k < 4 && ok; ++k) {
+            Rescale fs;
+            ok = to_fixed_scale(src[k][c], pot2, &fs);
+            wscale[k][c] = decode_scale(fs);
+        }
+        ok = ok && shift_ok(rs_x[c]) && shift_ok(rs_h[c]) && shift_ok(brs_x[c]) && shift_ok(brs_h[c]);
+    }
+    if (!ok) return fail(h, QGRU_ERR_RANGE, "a per-channel scale cannot be encoded as M*2^-shift");
+
+    // fillGateParams (src/gru_forward_gpu_quant.cu:702-735)
+    GateConsts &g = h->gc_host;
+    std::memset(&g, 0, sizeof(g));
+    g.zp_ih = op[QGRU_OP_IH_LINEAR].zero_point;
+    g.zp_hh = op[QGRU_OP_HH_LINEAR].zero_point;
+    g.zp_h = op[QGRU_OP_H].zero_point;
+    static const int in_op[3] = {QGRU_OP_UPDATE_IN, QGRU_OP_RESET_IN, QGRU_OP_NEW_IN};
+    static const int out_op[3] = {QGRU_OP_UPDATE_OUT, QGRU_OP_RESET_OUT, QGRU_OP_NEW_OUT};
+    for (int a = 0; a < 3; ++a) {
+        g.zp_in[a] = op[in_op[a]].zero_point;
+        g.zp_out[a] = op[out_op[a]].zero_point;
+        g.in_lo[a] = op_qmin(op[in_op[a]]);
+        g.in_hi[a] = op_qmax(op[in_op[a]]);
+        g.out_lo[a] = op_qmin(op[out_op[a]]);
+        g.out_hi[a] = op_qmax(op[out_op[a]]);
+        ok = ok && make_rescale(s_ih, op[in_op[a]].scale, pot2, &g.ih_to[a]);
+        g.lut[a] = p->lut[a];
+    }
+    ok = ok && make_rescale(s_hh, op[QGRU_OP_UPDATE_IN].scale, pot2, &g.hh_to[ACT_Z]);
+    ok = ok && make_rescale(s_hh, op[QGRU_OP_RESET_IN].scale, pot2, &g.hh_to[ACT_R]);
+    ok = ok && make_rescale_product(op[QGRU_OP_RESET_OUT].scale, s_hh, op[QGRU_OP_NEW_IN].scale, pot2, &g.rh_to_n);
+    ok = ok && make_rescale(op[QGRU_OP_NEW_OUT].scale, s_h, pot2, &g.n_to_h);
+    ok = ok && make_rescale_product(op[QGRU_OP_UPDATE_OUT].scale, s_h, s_h, pot2, &g.uh_to_h);
+    if (!ok) return fail(h, QGRU_ERR_RANGE, "a gate scale cannot be encoded as M*2^-shift");
+    for (Rescale r : {g.ih_to[0], g.ih_to[1], g.ih_to[2], g.hh_to[0], g.hh_to[1], g.rh_to_n, g.n_to_h, g.uh_to_h})
+        if (!shift_ok(r)) return fail(h, QGRU_ERR_UNSUPPORTED, "rescale shift outside [-62, 62]");
+    for (int a = 0; a < 3; ++a)
+        for (int s = 0; s < QGRU_LUT_SEGMENTS; ++s) {
+            const int n = (int)(int8_t)p->lut[a].seg[s].n_bx;
+            if (n > 62 || n < -62) return fail(h, QGRU_ERR_UNSUPPORTED, "LUT shift outside [-62, 62]");
+        }
+    // quant_one_in_update_gate_scale_ (src/gru_forward_gpu_quant.cu:719-720)
+    g.one_q = (int32_t)rintf(1.0f / op[QGRU_OP_UPDATE_OUT].scale) + op[QGRU_OP_UPDATE_OUT].zero_point;
+    g.h_lo = op_qmin(op[QGRU_OP_H]);
+    g.h_hi = op_qmax(op[QGRU_OP_H]);
+    g.ih_lo = op_qmin(op[QGRU_OP_IH_LINEAR]);
+    g.ih_hi = op_qmax(op[QGRU_OP_IH_LINEAR]);
+    g.hh_lo = op_qmin(op[QGRU_OP_HH_LINEAR]);
+    g.hh_hi = op_qmax(op[QGRU_OP_HH_LINEAR]);
+    {
+        Rescale fx, fh;
+        if (!to_fixed_scale(s_x, pot2, &fx) || !to_fixed_scale(s_h, pot2, &fh))
+            return fail(h, QGRU_ERR_RANGE, "x or h scale cannot be encoded");
+        h->x_scale = decode_scale(fx);
+        h->h_scale = decode_scale(fh);
+        g.h_scale = h->h_scale;
+    }
+    g.narrow = narrow_ok(g.ih_to[0], max_abs_diff(op[QGRU_OP_IH_LINEAR])) &&
+               narrow_ok(g.ih_to[1], max_abs_diff(op[QGRU_OP_IH_LINEAR])) &&
+               narrow_ok(g.ih_to[2], max_abs_diff(op[QGRU_OP_IH_LINEAR])) &&
+               narrow_ok(g.hh_to[0], max_abs_diff(op[QGRU_OP_HH_LINEAR])) &&
+               narrow_ok(g.hh_to[1], max_abs_diff(op[QGRU_OP_HH_LINEAR])) &&
+               narrow_ok(g.n_to_h, max_abs_diff(op[QGRU_OP_NEW_OUT]));
+
+    // Tabulate each activation over its whole clamped input range when that range is small.
+    std::vector<int32_t> tables;
+    for (int a = 0; a < 3; ++a) {
+        g.table_size[a] = 0;
+        g.table_off[a] = 0;
+        if (op[in_op[a]].bits <= 10) {
+            const int n = g.in_hi[a] - g.in_lo[a] + 1;
+            g.table_off[a] = (int32_t)tables.size();
+            g.table_size[a] = n;
+            for (int q = g.in_lo[a]; q <= g.in_hi[a]; ++q)
+                tables.push_back(lut_eval(p->lut[a], q, op[in_op[a]], op[out_op[a]]));
+        }
+    }
+    h->n_table = (int)tables.size();
+
+    // storage plan of the 8-bit path
+    const auto fits8 = [](const qgru_op &o) { return o.bits <= 8; };
+    h->x_uns = op[QGRU_OP_X].bits < 32 && op[QGRU_OP_X].is_unsigned;
+    h->h_uns = op[QGRU_OP_H].bits < 32 && op[QGRU_OP_H].is_unsigned;
+    const qgru_op &ihop = op[QGRU_OP_IH_LINEAR];
+    const bool ih8 = ihop.bits <= 8 && !ihop.is_unsigned;
+    const bool ih16 = ihop.bits <= 15 || (ihop.bits == 16 && !ihop.is_unsigned);
+    h->ih_bytes = ih8 ? 1 : 2;
+    h->fast = fits8(op[QGRU_OP_X]) && fits8(op[QGRU_OP_H]) && fits8(op[QGRU_OP_W]) &&
+              !op[QGRU_OP_W].is_unsigned && fits8(op[QGRU_OP_R]) && !op[QGRU_OP_R].is_unsigned &&
+              (ih8 || ih16) && (int64_t)std::max(h->I, h->H) * 128 * 255 < (int64_t)0x7fffffff;
+
+    int rc;
+    if ((rc = alloc_dev(h, &h->d_gc, 1))) return rc;
+    if ((rc = alloc_dev(h, &h->d_tables, tables.size()))) return rc;
+    for (int s = 0; s < 2; ++s) {
+        if ((rc = alloc_dev(h, &h->d_rs[s], C))) return rc;
+        if ((rc = alloc_dev(h, &h->d_brs[s], C))) return rc;
+        if ((rc = alloc_dev(h, &h->d_corr[s], C))) return rc;
+        if ((rc = alloc_dev(h, &h->d_wsum[s], C))) return rc;
+    }
+    for (int k = 0; k < 4; ++k)
+        if ((rc = alloc_dev(h, &h->d_wscale[k], C))) return rc;
+    CK(cudaMemcpy(h->d_gc, &g, sizeof(g), cudaMemcpyHostToDevice));
+    if (!tables.empty())
+        CK(cudaMemcpy(h->d_tables, tables.data(), tables.size() * 4, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(h->d_rs[0], rs_x.data(), C * sizeof(Rescale), cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(h->d_rs[1], rs_h.data(), C * sizeof(Rescale), cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(h->d_brs[0], brs_x.data(), C * sizeof(Rescale), cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(h->d_brs[1], brs_h.data(), C * sizeof(Rescale), cudaMemcpyHostToDevice));
+    for (int k = 0; k < 4; ++k)
+        CK(cudaMemcpy(h->d_wscale[k], wscale[k].data(), C * sizeof(float), cudaMemcpyHostToDevice));
+    h->params_set = true;
+    return QGRU_OK;
+}
+
+}  // extern "C"
+
+namespace {
+
+// Pack int32 weights already resident in h->d_wq[] and derive the per-channel corrections.
+int finish_weights(qgru_handle *h, cudaStream_t st) {
+    const int C = h->C;
+    int rc;
+    if (h->fast) {
+        if ((rc = alloc_dev(h, &h->d_w8[0], (size_t)C * h->Ipad))) return rc;
+        if ((rc = alloc_dev(h, &h->d_w8[1], (size_t)C * h->Hpad))) return rc;
+    }
+    CK(cudaMemsetAsync(h->d_flags, 0, 2 * sizeof(int), st));
+    k_pack_weights<<<C, 128, 0, st>>>(h->d_wq[0], h->fast ? h->d_w8[0] : nullptr, h->d_wsum[0], h->I,
+                                      h->Ipad, C, h->d_flags);
+    k_pack_weights<<<C, 128, 0, st>>>(h->d_wq[1], h->fast ? h->d_w8[1] : nullptr, h->d_wsum[1], h->H,
+                                      h->Hpad, C, h->d_flags);
+    const int gb = (C + 127) / 128;
+    k_channel_consts<<<gb, 128, 0, st>>>(h->d_wq[2], h->d_brs[0], h->d_wsum[0],
+                                         h->p.op[QGRU_OP_X].zero_point, h->d_corr[0], C);
+    k_channel_consts<<<gb, 128, 0, st>>>(h->d_wq[3], h->d_brs[1], h->d_wsum[1],
+                                         h->p.op[QGRU_OP_H].zero_point, h->d_corr[1], C);
+    h->launches += 4;
+    CK(cudaGetLastError());
+    CK(cudaMemcpyAsync(h->h_flags, h->d_flags, 2 * sizeof(int), cudaMemcpyDeviceToHost, st));
+    CK(cudaStreamSynchronize(st));
+    if (h->fast && (h->h_flags[0] & 2))
+        return fail(h, QGRU_ERR_BAD_ARG, "quantized weight outside the 8-bit range its operator declares");
+    h->tc.valid = false;
+    h->weights_set = true;
+    return QGRU_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int qgru_set_weights_f32(qgru_handle *h, const float *W, const float *R, const float *bw,
+                         const float *br, void *stream) {
+    if (!h || !W || !R || !bw || !br) return QGRU_ERR_BAD_ARG;
+    if (!h->params_set) return fail(h, QGRU_ERR_NOT_READY, "set_params first");
+    CK(cudaSetDevice(h->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const int C = h->C;
+    const size_t n[4] = {(size_t)h->I * C, (size_t)h->H * C, (size_t)C, (size_t)C};
+    const float *src[4] = {W, R, bw, br};
+    const int opi[4] = {QGRU_OP_W, QGRU_OP_R, QGRU_OP_BW, QGRU_OP_BR};
+    int rc;
+    for (int k = 0; k < 4; ++k) {
+        if ((rc = alloc_dev(h, &h->d_wq[k], n[k]))) return rc;
+        k_quantize_weights<<<grid_for((long long)n[k], 256, h->sm_count), 256, 0, st>>>(
+            src[k], h->d_wq[k], (long long)n[k], C, h->d_wscale[k], op_qmin(h->p.op[opi[k]]),
+            op_qmax(h->p.op[opi[k]]));
+        h->launches++;
+    }
+    CK(cudaGetLastError());
+    return finish_weights(h, st);
+}
+
+int qgru_set_weights_i32(qgru_handle *h, const int32_t *W_q, const int32_t *R_q,
+                         const int32_t *bw_q, const int32_t *br_q, void *stream) {
+    if (!h || !W_q || !R_q || !bw_q || !br_q) return QGRU_ERR_BAD_ARG;
+    if (!h->params_set) return fail(h, QGRU_ERR_NOT_READY, "set_params first");
+    CK(cudaSetDevice(h->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const int C = h->C;
+    const size_t n[4] = {(size_t)h->I * C, (size_t)h->H * C, (size_t)C, (size_t)C};
+    const int32_t *src[4] = {W_q, R_q, bw_q, br_q};
+    int rc;
+    for (int k = 0; k < 4; ++k) {
+        if ((rc = alloc_dev(h, &h->d_wq[k], n[k]))) return rc;
+        CK(cudaMemcpyAsync(h->d_wq[k], src[k], n[k] * 4, cudaMemcpyDeviceToDevice, st));
+    }
+    return finish_weights(h, st);
+}
+
+int qgru_get_weights_i32(qgru_handle *h, int32_t *W_q, int32_t *R_q, int32_t *bw_q, int32_t *br_q,
+                         void *stream) {
+    if (!h) return QGRU_ERR_BAD_ARG;
+    if (!h->weights_set) return fail(h, QGRU_ERR_NOT_READY, "set_weights first");
+    CK(cudaSetDevice(h->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const int C = h->C;
+    const size_t n[4] = {(size_t)h->I * C, (size_t)h->H * C, (size_t)C, (size_t)C};
+    int32_t *dst[4] = {W_q, R_q, bw_q, br_q};
+    for (int k = 0; k < 4; ++k)
+        if (dst[k]) CK(cudaMemcpyAsync(dst[k], h->d_wq[k], n[k] * 4, cudaMemcpyDeviceToDevice, st));
+    return QGRU_OK;
+}
+
+}  // extern "C"
+
+namespace {
+
+LinearConsts linear_consts(const qgru_handle *h, int side) {
+    LinearConsts lc;
+    lc.corr = h->d_corr[side];
+    lc.rs = h->d_rs[side];
+    const qgru_op &o = h->p.op[side == 0 ? QGRU_OP_IH_LINEAR : QGRU_OP_HH_LINEAR];
+    lc.zp_out = o.zero_point;
+    lc.lo = op_qmin(o);
+    lc.hi = op_qmax(o);
+    return lc;
+}
+
+bool use_generic(const qgru_handle *h) { return !h->fast || h->opt_rec == 3; }
+
+template <bool HU, typename IhT>
+int launch_rec(qgru_handle *h, RecArgs &a, const RecPlan &pl, cudaStream_t st) {
+    auto kern = h->gc_host.narrow ? k_recurrence_dp4a<HU, IhT, true> : k_recurrence_dp4a<HU, IhT, false>;
+    CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+    const int grid = pl.G * pl.P;
+    if (pl.P > 1) {
+        if (!h->coop) return fail(h, QGRU_ERR_UNSUPPORTED, "device lacks cooperative launch");
+        int per_sm = 0;
+        CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 256, pl.smem));
+        if ((long long)per_sm * h->sm_count < grid)
+            return fail(h, QGRU_ERR_UNSUPPORTED, "recurrence grid cannot be co-resident");
+        void *args[] = {&a};
+        CK(cudaLaunchCooperativeKernel((void *)kern, dim3(grid), dim3(256), args, pl.smem, st));
+    } else {
+        kern<<<grid, 256, pl.smem, st>>>(a);
+        CK(cudaGetLastError());
+    }
+    h->launches++;
+    return QGRU_OK;
+}
+
+// Shared tail of the two device entry points, 8-bit path: x8 and the initial state are ready.
+int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsigned flags,
+             cudaStream_t st) {
+    const long long N = (long long)T * B;
+    const int C = h->C;
+    int rc;
+    if ((rc = ensure(h, h->ih, (size_t)N * C * h->ih_bytes))) return rc;
+
+    CK(cudaEventRecord(h->ev[1], st));
+    const LinearConsts lcx = linear_consts(h, 0);
+    bool used_tc = false;
+    if (h->opt_gemm != 1) {
+        rc = tc_gemm_launch(h->tc, h->device, h->sm_count, (const uint8_t *)h->x8.p, h->d_w8[0], h->ih.p,
+                            N, C, h->Ipad, h->x_uns, h->ih_bytes, lcx, st, &h->err);
+        if (rc == QGRU_OK) {
+            used_tc = true;
+            h->launches++;
+        } else if (rc != QGRU_ERR_UNSUPPORTED || h->opt_gemm == 2) {
+            return rc;
+        }
+    }
+    if (!used_tc) {
+        dim3 grid((unsigned)((N + 63) / 64), (unsigned)((C + 63) / 64));
+        const uint8_t *x8 = (const uint8_t *)h->x8.p;
+        if (h->ih_bytes == 1) {
+            if (h->x_uns) k_gemm_wx_simt<true, int8_t><<<grid, 256, 0, st>>>(x8, h->d_w8[0], (int8_t *)h->ih.p, N, C, h->Ipad, lcx);
+            else k_gemm_wx_simt<false, int8_t><<<grid, 256, 0, st>>>(x8, h->d_w8[0], (int8_t *)h->ih.p, N, C, h->Ipad, lcx);
+        } else {
+            if (h->x_uns) k_gemm_wx_simt<true, int16_t><<<grid, 256, 0, st>>>(x8, h->d_w8[0], (int16_t *)h->ih.p, N, C, h->Ipad, lcx);
+            else k_gemm_wx_simt<false, int16_t><<<grid, 256, 0, st>>>(x8, h->d_w8[0], (int16_t *)h->ih.p, N, C, h->Ipad, lcx);
+        }
+        CK(cudaGetLastError());
+        h->launches++;
+    }
+    CK(cudaEventRecord(h->ev[2], st));
+
+    RecPlan pl;
+    if (!plan_recurrence(h, B, &pl)) return fail(h, QGRU_ERR_UNSUPPORTED, "no recurrence plan fits shared memory");
+    if (pl.G > h->bar_groups) {
+        if ((rc = alloc_dev(h, &h->d_bar, (size_t)pl.G * 32))) return rc;
+        h->bar_groups = pl.G;
+    }
+    CK(cudaMemsetAsync(h->d_bar, 0, (size_t)pl.G * 32 * sizeof(unsigned), st));
+    RecArgs a;
+    a.T = T; a.B = B; a.H = h->H; a.Hpad = h->Hpad; a.C = C;
+    a.Hs = pl.Hs; a.Bt = pl.Bt; a.P = pl.P;
+    a.reverse = (flags & QGRU_FLAG_REVERSE) ? 1 : 0;
+    a.r8 = h->d_w8[1];
+    a.ih = h->ih.p;
+    a.h8 = (uint8_t *)h->h8.p;
+    a.hq_out = hq_out;
+    a.hf_out = hf_out;
+    a.lc = linear_consts(h, 1);
+    a.gc = h->d_gc;
+    a.tables = h->d_tables;
+    a.n_table = h->n_table;
+    a.bar = h->d_bar;
+    a.abort_flag = h->d_flags + 1;
+    a.spin_limit = h->spin_limit;
+    if (h->ih_bytes == 1) rc = h->h_uns ? launch_rec<true, int8_t>(h, a, pl, st) : launch_rec<false, int8_t>(h, a, pl, st);
+    else rc = h->h_uns ? launch_rec<true, int16_t>(h, a, pl, st) : launch_rec<false, int16_t>(h, a, pl, st);
+    if (rc) return rc;
+    CK(cudaEventRecord(h->ev[3], st));
+    h->timing_valid = true;
+    char buf[256];
+    snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=dp4a Hs=%d Bt=%d P=%d G=%d smem=%zu narrow=%d ih_bytes=%d",
+             used_tc ? "tcgen05_i8" : "simt_dp4a", pl.Hs, pl.Bt, pl.P, pl.G, pl.smem, h->gc_host.narrow, h->ih_bytes);
+    h->plan_text = buf;
+    return QGRU_OK;
+}
+
+// Generic path: int32 operands, 64-bit accumulation, one launch pair per step.
+int run_generic(qgru_handle *h, int T, int B, const int32_t *x32, int32_t *hq, unsigned flags,
+                cudaStream_t st) {
+    const long long N = (long long)T * B;
+    const int C = h->C, H = h->H;
+    int rc;
+    if ((rc = ensure(h, h->ih32, (size_t)N * C * 4))) return rc;
+    if ((rc = ensure(h, h->hh32, (size_t)B * C * 4))) return rc;
+    CK(cudaEventRecord(h->ev[1], st));
+    const LinearConsts lcx = linear_consts(h, 0), lch = linear_consts(h, 1);
+    {
+        dim3 grid((C + 127) / 128, (unsigned)N);
+        k_linear_generic<<<grid, 128, 0, st>>>(h->d_wq[0], x32, (int32_t *)h->ih32.p, N, h->I, C, lcx);
+        h->launches++;
+    }
+    CK(cudaEventRecord(h->ev[2], st));
+    const bool rev = flags & QGRU_FLAG_REVERSE;
+    const size_t BH = (size_t)B * H;
+    for (int s = 0; s < T; ++s) {
+        const int t = rev ? T - 1 - s : s;
+        const size_t in_slot = rev ? (size_t)(T - s) : (size_t)s;
+        const size_t out_slot = rev ? (size_t)(T - 1 - s) : (size_t)(s + 1);
+        dim3 g1((C + 127) / 128, B);
+        k_linear_generic<<<g1, 128, 0, st>>>(h->d_wq[1], hq + in_slot * BH, (int32_t *)h->hh32.p, B, H, C, lch);
+        dim3 g2((H + 127) / 128, B);
+        k_gates_generic<<<g2, 128, 0, st>>>((const int32_t *)h->ih32.p + (size_t)t * B * C,
+                                            (const int32_t *)h->hh32.p, hq + in_slot * BH,
+                                            hq + out_slot * BH, B, H, h->d_gc, h->d_tables);
+        h->launches += 2;
+    }
+    CK(cudaGetLastError());
+    CK(cudaEventRecord(h->ev[3], st));
+    h->timing_valid = true;
+    h->plan_text = "path=generic_i32 gemm=simt_i64 rec=per_step_i64";
+    return QGRU_OK;
+}
+
+int check_forward_args(qgru_handle *h, int T, int B) {
+    if (T <= 0 || B <= 0) return fail(h, QGRU_ERR_BAD_ARG, "T and B must be positive");
+    if (!h->params_set || !h->weights_set) return fail(h, QGRU_ERR_NOT_READY, "set_params and set_weights first");
+    if ((long long)T * B * std::max(h->C, h->I) > (1ll << 40)) return fail(h, QGRU_ERR_BAD_ARG, "problem too large");
+    return QGRU_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int qgru_forward_i32(qgru_handle *h, int T, int B, const int32_t *x_q, const int32_t *h0_q,
+                     int32_t *h_q, unsigned flags, void *stream) {
+    if (!h || !x_q || !h_q) return QGRU_ERR_BAD_ARG;
+    int rc = check_forward_args(h, T, B);
+    if (rc) return rc;
+    CK(cudaSetDevice(h->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const long long N = (long long)T * B;
+    const qgru_op &xo = h->p.op[QGRU_OP_X], &ho = h->p.op[QGRU_OP_H];
+    const long long init_slot = (flags & QGRU_FLAG_REVERSE) ? T : 0;
+    CK(cudaEventRecord(h->ev[0], st));
+    CK(cudaMemsetAsync(h->d_flags, 0, 2 * sizeof(int), st));
+    if (use_generic(h)) {
+        k_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
+            h0_q, nullptr, nullptr, h_q, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale, ho.zero_point,
+            op_qmin(ho), op_qmax(ho), h->d_flags);
+        h->launches++;
+        return run_generic(h, T, B, x_q, h_q, flags, st);
+    }
+    if ((rc = ensure(h, h->x8, (size_t)N * h->Ipad))) return rc;
+    if ((rc = ensure(h, h->h8, (size_t)2 * B * h->Hpad))) return rc;
+    k_narrow_rows_i32<<<grid_for(N * (h->Ipad / 4), 256, h->sm_count), 256, 0, st>>>(
+        x_q, (uint8_t *)h->x8.p, N, h->I, h->Ipad, op_qmin(xo), op_qmax(xo), h->d_flags);
+    CK(cudaMemsetAsync(h->h8.p, 0, (size_t)2 * B * h->Hpad, st));
+    k_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
+        h0_q, nullptr, (uint8_t *)h->h8.p, h_q, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale,
+        ho.zero_point, op_qmin(ho), op_qmax(ho), h->d_flags);
+    h->launches += 2;
+    CK(cudaGetLastError());
+    return run_fast(h, T, B, h_q, nullptr, flags, st);
+}
+
+int qgru_forward_f32(qgru_handle *h, int T, int B, const float *x, const float *h0, float *h_out,
+                     int32_t *x_q_out, unsigned flags, void *stream) {
+    if (!h || !x || !h_out) return QGRU_ERR_BAD_ARG;
+    int rc = check_forward_args(h, T, B);
+    if (rc) return rc;
+    CK(cudaSetDevice(h->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const long long N = (long long)T * B;
+    const qgru_op &xo = h->p.op[QGRU_OP_X], &ho = h->p.op[QGRU_OP_H];
+    const long long init_slot = (flags & QGRU_FLAG_REVERSE) ? T : 0;
+    CK(cudaEventRecord(h->ev[0], st));
+    CK(cudaMemsetAsync(h->d_flags, 0, 2 * sizeof(int), st));
+    if (use_generic(h)) {
+        const size_t nh = (size_t)(T + 1) * B * h->H;
+        int32_t *x32 = x_q_out;
+        if (!x32) {
+            if ((rc = ensure(h, h->x32, (size_t)N * h->I * 4))) return rc;
+            x32 = (int32_t *)h->x32.p;
+        }
+        if ((rc = ensure(h, h->hq32, nh * 4))) return rc;
+        k_quantize_f32_i32<<<grid_for(N * h->I, 256, h->sm_count), 256, 0, st>>>(
+            x, x32, N * h->I, h->x_scale, xo.zero_point, op_qmin(xo), op_qmax(xo));
+        k_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
+            nullptr, h0, nullptr, (int32_t *)h->hq32.p, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale,
+            ho.zero_point, op_qmin(ho), op_qmax(ho), h->d_flags);
+        h->launches += 2;
+        if ((rc = run_generic(h, T, B, x32, (int32_t *)h->hq32.p, flags, st))) return rc;
+        k_dequantize<<<grid_for((long long)nh, 256, h->sm_count), 256, 0, st>>>(
+            (const int32_t *)h->hq32.p, h_out, (long long)nh, h->h_scale, ho.zero_point);
+        h->launches++;
+        CK(cudaGetLastError());
+        return QGRU_OK;
+    }
+    if ((rc = ensure(h, h->x8, (size_t)N * h->Ipad))) return rc;
+    if ((rc = ensure(h, h->h8, (size_t)2 * B * h->Hpad))) return rc;
+    k_quantize_rows_f32<<<grid_for(N * (h->Ipad / 4), 256, h->sm_count), 256, 0, st>>>(
+        x, (uint8_t *)h->x8.p, x_q_out, N, h->I, h->Ipad, h->x_scale, xo.zero_point, op_qmin(xo), op_qmax(xo));
+    CK(cudaMemsetAsync(h->h8.p, 0, (size_t)2 * B * h->Hpad, st));
+    k_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
+        nullptr, h0, (uint8_t *)h->h8.p, nullptr, h_out, B, h->H, h->Hpad, init_slot, h->h_scale,
+        ho.zero_point, op_qmin(ho), op_qmax(ho), h->d_flags);
+    h->launches += 2;
+    CK(cudaGetLastError());
+    return run_fast(h, T, B, nullptr, h_out, flags, st);
+}
+
+int qgru_synchronize(qgru_handle *h, void *stream) {
+    if (!h) return QGRU_ERR_BAD_ARG;
+    CK(cudaSetDevice(h->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    CK(cudaMemcpyAsync(h->h_flags, h->d_flags, 2 * sizeof(int), cudaMemcpyDeviceToHost, st));
+    CK(cudaStreamSynchronize(st));
+    CK(cudaGetLastError());
+    if (h->h_flags[1]) return fail(h, QGRU_ERR_TIMEOUT, "a per-step barrier wait of the recurrence kernel ran out");
+    if (h->h_flags[0] & 1) return fail(h, QGRU_ERR_BAD_ARG, "quantized input outside the range its operator declares");
+    return QGRU_OK;
+}
+
+int qgru_forward_i32_host(qgru_handle *h, int T, int B, const int32_t *x_q, const int32_t *h0_q,
+                          int32_t *h_q, unsigned flags, void *stream) {
+    if (!h || !x_q || !h_q) return QGRU_ERR_BAD_ARG;
+    int rc = check_forward_args(h, T, B);
+    if (rc) return rc;
+    CK(cudaSetDevice(h->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t nx = (size_t)T * B * h->I * 4, nh = (size_t)(T + 1) * B * h->H * 4, n0 = (size_t)B * h->H * 4;
+    if ((rc = ensure(h, h->stage_in, nx))) return rc;
+    if ((rc = ensure(h, h->stage_out, nh))) return rc;
+    if (h0_q && (rc = ensure(h, h->stage_h0, n0))) return rc;
+    CK(cudaMemcpyAsync(h->stage_in.p, x_q, nx, cudaMemcpyHostToDevice, st));
+    if (h0_q) CK(cudaMemcpyAsync(h->stage_h0.p, h0_q, n0, cudaMemcpyHostToDevice, st));
+    if ((rc = qgru_forward_i32(h, T, B, (const int32_t *)h->stage_in.p,
+                               h0_q ? (const int32_t *)h->stage_h0.p : nullptr,
+                               (int32_t *)h->stage_out.p, flags, stream)))
+        return rc;
+    CK(cudaMemcpyAsync(h_q, h->stage_out.p, nh, cudaMemcpyDeviceToHost, st));
+    return qgru_synchronize(h, stream);
+}
+
+int qgru_forward_f32_host(qgru_handle *h, int T, int B, const float *x, const float *h0,
+                          float *h_out, unsigned flags, void *stream) {
+    if (!h || !x || !h_out) return QGRU_ERR_BAD_ARG;
+    int rc = check_forward_args(h, T, B);
+    if (rc) return rc;
+    CK(cudaSetDevice(h->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t nx = (size_t)T * B * h->I * 4, nh = (size_t)(T + 1) * B * h->H * 4, n0 = (size_t)B * h->H * 4;
+    if ((rc = ensure(h, h->stage_in, nx))) return rc;
+    if ((rc = ensure(h, h->stage_out, nh))) return rc;
+    if (h0 && (rc = ensure(h, h->stage_h0, n0))) return rc;
+    CK(cudaMemcpyAsync(h->stage_in.p, x, nx, cudaMemcpyHostToDevice, st));
+    if (h0) CK(cudaMemcpyAsync(h->stage_h0.p, h0, n0, cudaMemcpyHostToDevice, st));
+    if ((rc = qgru_forward_f32(h, T, B, (const float *)h->stage_in.p,
+                               h0 ? (const float *)h->stage_h0.p : nullptr, (float *)h->stage_out.p,
+                               nullptr, flags, stream)))
+        return rc;
+    CK(cudaMemcpyAsync(h_out, h->stage_out.p, nh, cudaMemcpyDeviceToHost, st));
+    return qgru_synchronize(h, stream);
+}
+
+int qgru_last_timing(qgru_handle *h, float *ms_input_gemm, float *ms_recurrence, float *ms_total) {
+    if (!h) return QGRU_ERR_BAD_ARG;
+    if (!h->timing_valid) return fail(h, QGRU_ERR_NOT_READY, "no forward has run");
+    CK(cudaSetDevice(h->device));
+    CK(cudaEventSynchronize(h->ev[3]));
+    float a = 0, b = 0, c = 0;
+    CK(cudaEventElapsedTime(&a, h->ev[1], h->ev[2]));
+    CK(cudaEventElapsedTime(&b, h->ev[2], h->ev[3]));
+    CK(cudaEventElapsedTime(&c, h->ev[0], h->ev[3]));
+    if (ms_input_gemm) *ms_input_gemm = a;
+    if (ms_recurrence) *ms_recurrence = b;
+    if (ms_total) *ms_total = c;
+    return QGRU_OK;
+}
+
+const char *qgru_describe_plan(qgru_handle *h, int T, int B) {
+    (void)T;
+    (void)B;
+    if (!h) return "null handle";
+    return h->plan_text.c_str();
+}
+
+}  // extern "C"

@@ -1,0 +1,58 @@
+// qgru_internal.h - declarations shared by the host set-up code and the CUDA translation
+// units of libqgru_b200.  Nothing here is part of the public ABI (include/qgru.h).
+#pragma once
+#include <stdint.h>
+
+#include <string>
+
+#include "qgru.h"
+#include "qgru_math.h"
+
+namespace qgru {
+
+// ---- host helpers implemented in qgru_host.cc
+bool encode_mshift(float scale, Rescale *out);
+int pot2_shift(float scale);
+bool to_fixed_scale(float scale, bool pot2, Rescale *out);
+float decode_scale(Rescale r);
+bool make_rescale(float src, float dst, bool pot2, Rescale *out);
+bool make_rescale_product(float a, float b, float dst, bool pot2, Rescale *out);
+bool make_rescale_to_product(float src, float a, float b, bool pot2, Rescale *out);
+int32_t op_qmin(const qgru_op &o);
+int32_t op_qmax(const qgru_op &o);
+int32_t lut_eval(const qgru_lut &lut, int32_t q_x, const qgru_op &in_bw, const qgru_op &out_bw);
+
+// ---- device-visible constants of the gate datapath: the scalar part of
+// GateQuantParamsT<R> (include/quantize_param_types.h:148-193), derived once per
+// set_params instead of being passed by value (968 bytes) on every launch.
+enum { ACT_Z = 0, ACT_R = 1, ACT_N = 2 };
+
+struct GateConsts {
+    int32_t zp_ih, zp_hh, zp_h;
+    int32_t zp_in[3], zp_out[3];          // gate input / output zero points (z, r, n)
+    int32_t one_q;                        // round(1/s_z) + zp_z
+    Rescale ih_to[3];                     // weight_ih_linear -> gate input (z, r, n)
+    Rescale hh_to[2];                     // weight_hh_linear -> gate input (z, r)
+    Rescale rh_to_n;                      // (r - zp)(hh_n - zp) -> new gate input
+    Rescale n_to_h;                       // new gate output -> h
+    Rescale uh_to_h;                      // s_z * s_h -> h
+    int32_t in_lo[3], in_hi[3], out_lo[3], out_hi[3];
+    int32_t h_lo, h_hi, ih_lo, ih_hi, hh_lo, hh_hi;
+    int32_t table_size[3];                // > 0: direct table over the clamped input range
+    int32_t table_off[3];                 // offset of that table in the table array (ints)
+    int32_t narrow;                       // 1: every gate rescale fits the 32-bit fast form
+    float h_scale;                        // decode_scale(toFixedScale(h)) for the float output
+    qgru_lut lut[3];
+};
+
+// Per output channel constants of one fused linear layer:
+//   out = clamp( int32( rescale( acc + corr[m], rs[m] ) ) + zp_out )
+// with corr[m] = rescale(bias_q[m], bias_rs[m]) - zp_in * sum_k W_q[k][m]
+// (src/gru_forward_cpu_quant.cc:92-99,125-138).
+struct LinearConsts {
+    const int64_t *corr;  // [3H] device
+    const Rescale *rs;    // [3H] device
+    int32_t zp_out, lo, hi;
+};
+
+}  // namespace qgru

@@ -1,0 +1,497 @@
+// qgru_kernels.cuh - device code of the integer GRU forward: boundary quantize kernels,
+// the SIMT input-projection GEMM, the persistent recurrence kernel and the generic
+// (any bit width) fallback kernels.  Written for sm_100a; one CTA per SM is assumed for the
+// persistent kernel (it claims most of the 227 KB of shared memory).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "qgru_internal.h"
+
+namespace qgru {
+
+// ------------------------------------------------------------------ small helpers
+
+__device__ __forceinline__ int dp4a_ss(int a, int b, int c) { return __dp4a(a, b, c); }
+// a: four signed bytes, b: four unsigned bytes
+__device__ __forceinline__ int dp4a_su(int a, unsigned b, int c) {
+    int d;
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+template <bool BUnsigned>
+__device__ __forceinline__ int dp4a_w(int w, unsigned act, int c) {
+    if constexpr (BUnsigned) return dp4a_su(w, act, c);
+    else return dp4a_ss(w, (int)act, c);
+}
+
+__device__ __forceinline__ unsigned ld_acquire(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// ------------------------------------------------------------ gate datapath (a4-a8)
+
+// piecewise_linear with its two clamps (include/quantize_ops_helper.h:600-606).  Where the
+// gate input is narrow enough the host tabulated the function over the whole clamped input
+// range; the table holds exactly the values the segment evaluation produces.
+__device__ __forceinline__ int32_t activation(const GateConsts &gc, const int32_t *tables,
+                                              int which, int32_t pre) {
+    const int32_t q = clampi(pre, gc.in_lo[which], gc.in_hi[which]);
+    if (gc.table_size[which] > 0) return tables[gc.table_off[which] + (q - gc.in_lo[which])];
+    return clampi(lut_raw(gc.lut[which], q), gc.out_lo[which], gc.out_hi[which]);
+}
+
+template <bool Narrow>
+__device__ __forceinline__ int32_t rescale_diff(int32_t v, int32_t zp, Rescale r) {
+    if constexpr (Narrow) return rescale_narrow(v - zp, r);
+    else return (int32_t)rescale64((int64_t)v - (int64_t)zp, r);
+}
+
+// computeUpdateGate / computeResetGate / computeNewGate / computeHiddenState, inference
+// branch (include/quantize_ops_helper.h:749-1084).  ih_* and hh_* are the clamped outputs of
+// the two fused linear layers; h_old is the quantized previous state.
+template <bool Narrow>
+__device__ __forceinline__ int32_t gru_cell(const GateConsts &gc, const int32_t *tables,
+                                            int32_t ih_z, int32_t ih_r, int32_t ih_n,
+                                            int32_t hh_z, int32_t hh_r, int32_t hh_n,
+                                            int32_t h_old) {
+    const int32_t z_pre = rescale_diff<Narrow>(ih_z, gc.zp_ih, gc.ih_to[ACT_Z]) +
+                          rescale_diff<Narrow>(hh_z, gc.zp_hh, gc.hh_to[ACT_Z]) + gc.zp_in[ACT_Z];
+    const int32_t z = activation(gc, tables, ACT_Z, z_pre);
+    const int32_t r_pre = rescale_diff<Narrow>(ih_r, gc.zp_ih, gc.ih_to[ACT_R]) +
+                          rescale_diff<Narrow>(hh_r, gc.zp_hh, gc.hh_to[ACT_R]) + gc.zp_in[ACT_R];
+    const int32_t r = activation(gc, tables, ACT_R, r_pre);
+
+    const int64_t r_hh = ((int64_t)r - gc.zp_out[ACT_R]) * ((int64_t)hh_n - gc.zp_hh);
+    const int32_t n_pre = rescale_diff<Narrow>(ih_n, gc.zp_ih, gc.ih_to[ACT_N]) +
+                          (int32_t)rescale64(r_hh, gc.rh_to_n) + gc.zp_in[ACT_N];
+    const int32_t n = activation(gc, tables, ACT_N, n_pre);
+
+    const int32_t n_h = rescale_diff<Narrow>(n, gc.zp_out[ACT_N], gc.n_to_h) + gc.zp_h;
+    const int64_t z_d = (int64_t)z - gc.zp_out[ACT_Z];
+    const int64_t old_c = z_d * ((int64_t)h_old - gc.zp_h);
+    const int64_t one_minus = ((int64_t)gc.one_q - z) - gc.zp_out[ACT_Z];
+    const int64_t new_c = one_minus * ((int64_t)n_h - gc.zp_h);
+    const int32_t h_new = (int32_t)rescale64(old_c + new_c, gc.uh_to_h) + gc.zp_h;
+    return clampi(h_new, gc.h_lo, gc.h_hi);
+}
+
+// Epilogue of a fused linear layer (src/gru_forward_cpu_quant.cc:130-138).
+__device__ __forceinline__ int32_t linear_epilogue(int64_t acc, int64_t corr, Rescale rs,
+                                                   int32_t zp_out, int32_t lo, int32_t hi) {
+    const int32_t v = (int32_t)rescale64(acc + corr, rs) + zp_out;
+    return clampi(v, lo, hi);
+}
+
+// --------------------------------------------------------- boundary kernels (a12, a13)
+
+// quantize(float, FixedPointScale, zp, bw) (include/quantize_ops_helper.h:528-533): IEEE
+// division by the decoded 16-bit-mantissa scale, round half to even, add zp in float.
+__device__ __forceinline__ int32_t quantize_one(float x, float scale, int32_t zp, int32_t lo,
+                                                int32_t hi) {
+    const float q = rintf(__fdiv_rn(x, scale)) + (float)zp;
+    return clampi((int32_t)q, lo, hi);
+}
+
+// fp32 activations -> 8-bit rows padded to Kpad (zeros), optionally also int32 containers.
+// One thread per group of 4 padded columns.
+__global__ void k_quantize_rows_f32(const float *__restrict__ x, uint8_t *__restrict__ out8,
+                                    int32_t *__restrict__ out32, long long rows, int K, int Kpad,
+                                    float scale, int32_t zp, int32_t lo, int32_t hi) {
+    const int kw = Kpad >> 2;
+    const long long total = rows * kw;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long row = i / kw;
+        const int k0 = (int)(i - row * kw) * 4;
+        unsigned packed = 0;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int k = k0 + u;
+            int32_t q = 0;
+            if (k < K) {
+                q = quantize_one(x[row * K + k], scale, zp, lo, hi);
+                if (out32) out32[row * K + k] = q;
+            }
+            packed |= ((unsigned)q & 0xffu) << (8 * u);
+        }
+        if (out8) reinterpret_cast<unsigned *>(out8)[i] = packed;
+    }
+}
+
+// int32 containers -> 8-bit rows padded to Kpad.  Values outside [lo, hi] (they would have
+// been clamped by the reference's quantize step) raise bit 0 of *err.
+__global__ void k_narrow_rows_i32(const int32_t *__restrict__ x, uint8_t *__restrict__ out8,
+                                  long long rows, int K, int Kpad, int32_t lo, int32_t hi,
+                                  int *err) {
+    const int kw = Kpad >> 2;
+    const long long total = rows * kw;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long row = i / kw;
+        const int k0 = (int)(i - row * kw) * 4;
+        unsigned packed = 0;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int k = k0 + u;
+            int32_t q = 0;
+            if (k < K) {
+                q = x[row * K + k];
+                if (q < lo || q > hi) atomicOr(err, 1);
+            }
+            packed |= ((unsigned)q & 0xffu) << (8 * u);
+        }
+        reinterpret_cast<unsigned *>(out8)[i] = packed;
+    }
+}
+
+// fp32 -> int32 containers (generic path and x_q_out).
+__global__ void k_quantize_f32_i32(const float *__restrict__ x, int32_t *__restrict__ out,
+                                   long long n, float scale, int32_t zp, int32_t lo, int32_t hi) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x)
+        out[i] = quantize_one(x[i], scale, zp, lo, hi);
+}
+
+// Per-channel weight quantize, zp = 0 (quantificationPerChannelBitwidth,
+// src/quantize_ops.cu:313; channel = idx % C).
+__global__ void k_quantize_weights(const float *__restrict__ w, int32_t *__restrict__ out,
+                                   long long n, int C, const float *__restrict__ scales, int32_t lo,
+                                   int32_t hi) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x)
+        out[i] = quantize_one(w[i], scales[i % C], 0, lo, hi);
+}
+
+// dequantize (include/quantize_ops_helper.h:504-508).
+__global__ void k_dequantize(const int32_t *__restrict__ q, float *__restrict__ out, long long n,
+                             float scale, int32_t zp) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x)
+        out[i] = (float)(q[i] - zp) * scale;
+}
+
+// Weight repack: int32 [K][C] (haste layout) -> int8 [C][Kpad] (K contiguous, zero padded)
+// plus the column sums used by the zero-point correction.  One CTA per channel.
+__global__ void k_pack_weights(const int32_t *__restrict__ wq, int8_t *__restrict__ w8,
+                               int32_t *__restrict__ wsum, int K, int Kpad, int C, int *err) {
+    const int m = blockIdx.x;
+    int local = 0;
+    for (int k = threadIdx.x; k < Kpad; k += blockDim.x) {
+        int32_t v = 0;
+        if (k < K) {
+            v = wq[(size_t)k * C + m];
+            local += v;
+            if (v < -128 || v > 127) atomicOr(err, 2);
+        }
+        if (w8) w8[(size_t)m * Kpad + k] = (int8_t)v;
+    }
+    __shared__ int red[32];
+    for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = local;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int s = 0;
+        for (int i = 0; i < (int)((blockDim.x + 31) >> 5); ++i) s += red[i];
+        wsum[m] = s;
+    }
+}
+
+// corr[m] = rescale(bias_q[m], bias_rs[m]) - zp_in * sum_k W_q[k][m]
+__global__ void k_channel_consts(const int32_t *__restrict__ bias_q,
+                                 const Rescale *__restrict__ bias_rs,
+                                 const int32_t *__restrict__ wsum, int32_t zp_in,
+                                 int64_t *__restrict__ corr, int C) {
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m < C) corr[m] = rescale64((int64_t)bias_q[m], bias_rs[m]) - (int64_t)zp_in * (int64_t)wsum[m];
+}
+
+// ------------------------------------------------ input projection, SIMT dp4a form (a1)
+
+// ih[n][m] = epilogue( sum_k W8[m][k] * x8[n][k] ), n < N tokens, m < C channels.
+// 64x64 output tile per CTA, 256 threads, 4x4 outputs per thread, K staged in 64-byte slabs.
+template <bool XUnsigned, typename IhT>
+__global__ void __launch_bounds__(256)
+k_gemm_wx_simt(const uint8_t *__restrict__ x8, const int8_t *__restrict__ w8, IhT *__restrict__ ih,
+               long long N, int C, int Kpad, LinearConsts lc) {
+    __shared__ unsigned xs[64][17];
+    __shared__ unsigned ws[64][17];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const long long n0 = (long long)blockIdx.x * 64;
+    const int m0 = blockIdx.y * 64;
+    int acc[4][4] = {};
+    for (int k0 = 0; k0 < Kpad; k0 += 64) {
+        for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+            const int r = i >> 4, c = i & 15;
+            const int kb = k0 + c * 4;
+            unsigned xv = 0, wv = 0;
+            if (kb < Kpad) {
+                if (n0 + r < N) xv = *reinterpret_cast<const unsigned *>(x8 + (n0 + r) * Kpad + kb);
+                if (m0 + r < C) wv = *reinterpret_cast<const unsigned *>(w8 + (size_t)(m0 + r) * Kpad + kb);
+            }
+            xs[r][c] = xv;
+            ws[r][c] = wv;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            unsigned xv[4];
+            int wv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xv[i] = xs[ty * 4 + i][c];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wv[j] = (int)ws[tx + 16 * j][c];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = dp4a_w<XUnsigned>(wv[j], xv[i], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const long long n = n0 + ty * 4 + i;
+        if (n >= N) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int m = m0 + tx + 16 * j;
+            if (m >= C) continue;
+            ih[n * C + m] = (IhT)linear_epilogue(acc[i][j], lc.corr[m], lc.rs[m], lc.zp_out, lc.lo, lc.hi);
+        }
+    }
+}
+
+// ------------------------------------------------------------ h slot 0 / state init
+
+// Writes the initial state: the 8-bit state buffer (padded rows), and slot `slot` of the
+// int32 / float outputs (quantGRUForwardInt32's h_q[0] fill, src/gru_interface.cc:568-574;
+// the float entry point dequantizes that slot like every other, :704).
+__global__ void k_init_state(const int32_t *__restrict__ h0_q, const float *__restrict__ h0_f,
+                             uint8_t *__restrict__ h8, int32_t *__restrict__ hq_out,
+                             float *__restrict__ hf_out, int B, int H, int Hpad, long long slot,
+                             float scale, int32_t zp, int32_t lo, int32_t hi, int *err) {
+    const long long total = (long long)B * Hpad;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int b = (int)(i / Hpad), j = (int)(i % Hpad);
+        int32_t q = 0;
+        if (j < H) {
+            if (h0_q) {
+                q = h0_q[(size_t)b * H + j];
+                if (q < lo || q > hi) atomicOr(err, 1);
+            } else if (h0_f) {
+                q = quantize_one(h0_f[(size_t)b * H + j], scale, zp, lo, hi);
+            } else {
+                q = zp;
+            }
+            const long long o = slot * B * H + (long long)b * H + j;
+            if (hq_out) hq_out[o] = q;
+            if (hf_out) hf_out[o] = (float)(q - zp) * scale;
+        }
+        if (h8) h8[i] = (uint8_t)q;
+    }
+}
+
+// ------------------------------------------------ persistent recurrence, dp4a form (a2+a3)
+
+struct RecArgs {
+    int T, B, H, Hpad, C;
+    int Hs;        // hidden units per CTA (multiple of 32)
+    int Bt;        // batch rows per group
+    int P;         // CTAs per group (slices of the hidden dimension)
+    int reverse;
+    const int8_t *r8;      // [3H][Hpad]
+    const void *ih;        // [T*B][3H] int8 or int16
+    uint8_t *h8;           // [2][B][Hpad] ping-pong state
+    int32_t *hq_out;       // [(T+1)][B][H] or null
+    float *hf_out;         // [(T+1)][B][H] or null
+    LinearConsts lc;       // R*h + br epilogue
+    const GateConsts *gc;  // device copy
+    const int32_t *tables; // activation tables, gc->table_off indexes into it
+    int n_table;           // ints in tables
+    unsigned *bar;         // one counter per group, 32 words apart
+    int *abort_flag;       // set when a barrier wait ran out; every CTA then leaves
+    unsigned spin_limit;
+};
+
+// One CTA owns Hs hidden units (all three gates) of one group of Bt batch rows and keeps its
+// slice of R in shared memory for all T steps.  Per step: fetch h_{t-1} of the group's rows,
+// R*h with dp4a, requantize, gates, write h_t.  Groups never interact; the P CTAs of a group
+// meet once per step at a counter in global memory (bounded spin).
+template <bool HUnsigned, typename IhT, bool Narrow>
+__global__ void __launch_bounds__(256, 1) k_recurrence_dp4a(RecArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int kw = a.Hpad >> 2;  // words per row
+    // layout: GateConsts | tables | corr[3*Hs] i64 | rs[3*Hs] | Rs[3][kw][Hs] words | hs[Bt][kw] words
+    GateConsts *gc = reinterpret_cast<GateConsts *>(smem_raw);
+    size_t off = (sizeof(GateConsts) + 15) & ~size_t(15);
+    int32_t *tables = reinterpret_cast<int32_t *>(smem_raw + off);
+    off += ((size_t)a.n_table * 4 + 15) & ~size_t(15);
+    int64_t *corr = reinterpret_cast<int64_t *>(smem_raw + off);
+    off += (size_t)3 * a.Hs * 8;
+    Rescale *rs = reinterpret_cast<Rescale *>(smem_raw + off);
+    off += (size_t)3 * a.Hs * 8;
+    unsigned *Rs = reinterpret_cast<unsigned *>(smem_raw + off);
+    off += (size_t)3 * kw * a.Hs * 4;
+    unsigned *hs = reinterpret_cast<unsigned *>(smem_raw + off);
+
+    const int grp = blockIdx.x / a.P, p = blockIdx.x % a.P;
+    const int j0 = p * a.Hs, b0 = grp * a.Bt;
+    const int nb = min(a.Bt, a.B - b0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    for (int i = tid; i < (int)(sizeof(GateConsts) / 4); i += 256)
+        reinterpret_cast<int *>(gc)[i] = reinterpret_cast<const int *>(a.gc)[i];
+    for (int i = tid; i < a.n_table; i += 256) tables[i] = a.tables[i];
+    for (int i = tid; i < 3 * a.Hs; i += 256) {
+        const int g = i / a.Hs, jl = i % a.Hs, j = j0 + jl;
+        const bool ok = j < a.H;
+        corr[i] = ok ? a.lc.corr[g * a.H + j] : 0;
+        rs[i] = ok ? a.lc.rs[g * a.H + j] : Rescale{1, 1};
+    }
+    {
+        const unsigned *r8w = reinterpret_cast<const unsigned *>(a.r8);
+        const int total = 3 * a.Hs * kw;
+        for (int i = tid; i < total; i += 256) {
+            const int k4 = i % kw, gj = i / kw;
+            const int g = gj / a.Hs, jl = gj % a.Hs, j = j0 + jl;
+            Rs[(g * kw + k4) * a.Hs + jl] = (j < a.H) ? r8w[(size_t)(g * a.H + j) * kw + k4] : 0u;
+        }
+    }
+    __syncthreads();
+
+    const int JW = a.Hs >> 5;        // warps along the hidden dimension
+    const int BW = 8 / JW;           // warps along the batch dimension
+    const int wj = warp % JW, wb = warp / JW;
+    const int jl = wj * 32 + lane, j = j0 + jl;
+    const bool j_ok = j < a.H;
+    constexpr int NB = 4;
+    const size_t BH = (size_t)a.B * a.H;
+    const IhT *ihp = reinterpret_cast<const IhT *>(a.ih);
+    unsigned *bar = a.bar + grp * 32;
+    bool dead = false;
+
+    for (int s = 0; s < a.T; ++s) {
+        const int t = a.reverse ? (a.T - 1 - s) : s;                  // x / ih time index
+        const long long out_slot = a.reverse ? (a.T - 1 - s) : (s + 1);
+        const uint8_t *h_cur = a.h8 + (size_t)(s & 1) * a.B * a.Hpad;
+        uint8_t *h_nxt = a.h8 + (size_t)((s + 1) & 1) * a.B * a.Hpad;
+
+        if (a.P > 1 && s > 0) {
+            if (tid == 0) {
+                const unsigned want = (unsigned)a.P * (unsigned)s;
+                unsigned it = 0;
+                while (ld_acquire(bar) < want) {
+                    if (++it > a.spin_limit || (it % 1024 == 0 && *(volatile int *)a.abort_flag)) {
+                        atomicOr(a.abort_flag, 1);
+                        break;
+                    }
+                }
+            }
+            __syncthreads();
+            if (tid == 0 && *(volatile int *)a.abort_flag) dead = true;
+            if (__syncthreads_or(dead)) break;
+        }
+
+        // h_{t-1} rows of this group -> shared (L2 loads: other CTAs wrote them)
+        {
+            const uint4 *src = reinterpret_cast<const uint4 *>(h_cur + (size_t)b0 * a.Hpad);
+            uint4 *dst = reinterpret_cast<uint4 *>(hs);
+            const int total = nb * (a.Hpad >> 4);
+            for (int i = tid; i < total; i += 256) dst[i] = __ldcg(src + i);
+        }
+        __syncthreads();
+
+        for (int bb = wb * NB; bb < nb; bb += BW * NB) {
+            int acc[NB][3];
+#pragma unroll
+            for (int u = 0; u < NB; ++u) acc[u][0] = acc[u][1] = acc[u][2] = 0;
+            // ih loads are issued first so they fly under the dot products
+            int32_t ihv[NB][3];
+#pragma unroll
+            for (int u = 0; u < NB; ++u) {
+                const int b = bb + u;
+#pragma unroll
+                for (int g = 0; g < 3; ++g)
+                    ihv[u][g] = (b < nb && j_ok)
+                                    ? (int32_t)ihp[((size_t)t * a.B + b0 + b) * a.C + g * a.H + j]
+                                    : 0;
+            }
+            for (int k4 = 0; k4 < kw; k4 += 4) {
+                uint4 hv[NB];
+#pragma unroll
+                for (int u = 0; u < NB; ++u) {
+                    const int b = min(bb + u, nb - 1);
+                    hv[u] = *reinterpret_cast<const uint4 *>(hs + (size_t)b * kw + k4);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int wz = (int)Rs[(0 * kw + k4 + q) * a.Hs + jl];
+                    const int wr = (int)Rs[(1 * kw + k4 + q) * a.Hs + jl];
+                    const int wn = (int)Rs[(2 * kw + k4 + q) * a.Hs + jl];
+#pragma unroll
+                    for (int u = 0; u < NB; ++u) {
+                        const unsigned h4 = q == 0 ? hv[u].x : q == 1 ? hv[u].y : q == 2 ? hv[u].z : hv[u].w;
+                        acc[u][0] = dp4a_w<HUnsigned>(wz, h4, acc[u][0]);
+                        acc[u][1] = dp4a_w<HUnsigned>(wr, h4, acc[u][1]);
+                        acc[u][2] = dp4a_w<HUnsigned>(wn, h4, acc[u][2]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < NB; ++u) {
+                const int b = bb + u;
+                if (b >= nb || !j_ok) continue;
+                int32_t hh[3];
+#pragma unroll
+                for (int g = 0; g < 3; ++g)
+                    hh[g] = linear_epilogue(acc[u][g], corr[g * a.Hs + jl], rs[g * a.Hs + jl],
+                                            a.lc.zp_out, a.lc.lo, a.lc.hi);
+                const uint8_t hb = reinterpret_cast<const uint8_t *>(hs)[(size_t)b * a.Hpad + j];
+                const int32_t h_old = HUnsigned ? (int32_t)hb : (int32_t)(int8_t)hb;
+                const int32_t hn = gru_cell<Narrow>(*gc, tables, ihv[u][0], ihv[u][1], ihv[u][2],
+                                                    hh[0], hh[1], hh[2], h_old);
+                h_nxt[(size_t)(b0 + b) * a.Hpad + j] = (uint8_t)hn;
+                const size_t o = (size_t)out_slot * BH + (size_t)(b0 + b) * a.H + j;
+                if (a.hq_out) a.hq_out[o] = hn;
+                if (a.hf_out) a.hf_out[o] = (float)(hn - gc->zp_h) * gc->h_scale;
+            }
+        }
+        __syncthreads();
+        if (a.P > 1 && tid == 0) {
+            __threadfence();
+            atomicAdd(bar, 1u);
+        }
+    }
+}
+
+// --------------------------------------------- generic fallback (any bit width, int32 data)
+
+// out[n][m] = epilogue( sum_k W_q[k][m] * in[n][k] ) with 64-bit accumulation
+// (quantizedGemmBiasFused's arithmetic, src/gru_forward_gpu_quant.cu:110-180).
+__global__ void k_linear_generic(const int32_t *__restrict__ wq, const int32_t *__restrict__ in,
+                                 int32_t *__restrict__ out, long long N, int K, int C,
+                                 LinearConsts lc) {
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    const long long n = blockIdx.y;
+    if (m >= C || n >= N) return;
+    int64_t acc = 0;
+    for (int k = 0; k < K; ++k) acc += (int64_t)wq[(size_t)k * C + m] * (int64_t)in[n * K + k];
+    out[n * C + m] = linear_epilogue(acc, lc.corr[m], lc.rs[m], lc.zp_out, lc.lo, lc.hi);
+}
+
+__global__ void k_gates_generic(const int32_t *__restrict__ ih, const int32_t *__restrict__ hh,
+                                const int32_t *__restrict__ h_in, int32_t *__restrict__ h_out, int B,
+                                int H, const GateConsts *__restrict__ gcp,
+                                const int32_t *__restrict__ tables) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = blockIdx.y;
+    if (j >= H || b >= B) return;
+    const size_t w = (size_t)b * 3 * H + j;
+    h_out[(size_t)b * H + j] = gru_cell<false>(*gcp, tables, ih[w], ih[w + H], ih[w + 2 * H], hh[w],
+                                               hh[w + H], hh[w + 2 * H], h_in[(size_t)b * H + j]);
+}
+
+}  // namespace qgru
