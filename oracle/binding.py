@@ -55,13 +55,13 @@ class _Checker:
     def __init__(self, path):
         self.cabi = _pkg()._cabi
         self.lib = C.CDLL(path)
-        p = self.prefix
-        self.lib[p + "rshift_round"].restype = C.c_int64
-        self.lib[p + "rshift_round"].argtypes = [C.c_int64, C.c_int]
-        self.lib[p + "lut_eval"].restype = C.c_int32
+        # getattr caches the function object (CDLL.__getitem__ would make a new one per use)
+        self._fn("rshift_round").restype = C.c_int64
+        self._fn("rshift_round").argtypes = [C.c_int64, C.c_int]
+        self._fn("lut_eval").restype = C.c_int32
 
     def _fn(self, name):
-        return self.lib[self.prefix + name]
+        return getattr(self.lib, self.prefix + name)
 
     def rshift_round(self, x, n):
         return int(self._fn("rshift_round")(int(x), int(n)))

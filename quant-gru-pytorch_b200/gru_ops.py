@@ -1,0 +1,301 @@
+"""Python host side of the C ABI, shaped like the reference's ``gru_ops`` pybind module.
+
+``Handle`` is a thin object over ``qgru_handle``.  The module-level functions keep the names,
+argument order and return conventions of the reference binding for the integer path
+(pytorch/lib/gru_interface_binding.cc): ``forward_quant_int_storage`` (:436),
+``forward_quantized_int_io`` (:573), ``forward_fp`` (:629), ``forward_calibrate`` (:683) and
+``calculate_gru_quantitative_parameters`` (:209).  Tensors are torch CUDA tensors; torch is
+used for device memory and streams only - every computation happens in libqgru_b200.so.
+"""
+import ctypes as C
+
+import torch
+
+from . import _cabi
+from .params import GRUQuantParams, OperatorQuantConfig, Ranges, WEIGHT_OPS  # noqa: F401
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream(device):
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _check_tensor(t, name, dtype, shape=None, cuda=True):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if cuda and not t.is_cuda:
+        raise ValueError(f"{name} must be CUDA {dtype} tensor")
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must be CUDA {dtype} tensor")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise ValueError(f"{name} must have shape {list(shape)}, got {list(t.shape)}")
+    return t.contiguous()
+
+
+class Handle:
+    """One (device, direction) instance of the integer GRU forward.
+
+    Owns the packed weights, the derived rescale tables and a growing device workspace, so
+    repeated forwards allocate nothing and never synchronise the device."""
+
+    def __init__(self, input_size, hidden_size, device=0):
+        self._lib = _cabi.lib()
+        self.input_size, self.hidden_size, self.device = input_size, hidden_size, int(device)
+        h = C.c_void_p()
+        st = self._lib.qgru_create(C.byref(h), self.device, input_size, hidden_size)
+        if st != _cabi.QGRU_OK:
+            raise _cabi.QgruError(st, "qgru_create", "no usable CUDA device" if st == 2 else "")
+        self._h = h
+        self._tdev = torch.device("cuda", self.device)
+
+    # -- lifecycle
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.qgru_destroy(self._h)
+            self._h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _ck(self, st, where):
+        _cabi.check(st, where, self._h)
+
+    # -- configuration
+    def set_option(self, name, value):
+        self._ck(self._lib.qgru_set_option(self._h, name.encode(), str(value).encode()), "qgru_set_option")
+
+    def set_params(self, params):
+        fp = C.POINTER(C.c_float)
+        self._params = params
+        self._ck(self._lib.qgru_set_params(self._h, C.byref(params.c),
+                                           *[params.scales[n].ctypes.data_as(fp) for n in WEIGHT_OPS]),
+                 "qgru_set_params")
+
+    def set_weights_f32(self, W, R, bw, br):
+        I, H = self.input_size, self.hidden_size
+        W = _check_tensor(W, "W", torch.float32, (I, 3 * H))
+        R = _check_tensor(R, "R", torch.float32, (H, 3 * H))
+        bw = _check_tensor(bw, "bw", torch.float32, (3 * H,))
+        br = _check_tensor(br, "br", torch.float32, (3 * H,))
+        self._ck(self._lib.qgru_set_weights_f32(self._h, _ptr(W), _ptr(R), _ptr(bw), _ptr(br),
+                                                _stream(self._tdev)), "qgru_set_weights_f32")
+
+    def set_weights_i32(self, W_q, R_q, bw_q, br_q):
+        I, H = self.input_size, self.hidden_size
+        W_q = _check_tensor(W_q, "W_q", torch.int32, (I, 3 * H))
+        R_q = _check_tensor(R_q, "R_q", torch.int32, (H, 3 * H))
+        bw_q = _check_tensor(bw_q, "bw_q", torch.int32, (3 * H,))
+        br_q = _check_tensor(br_q, "br_q", torch.int32, (3 * H,))
+        self._ck(self._lib.qgru_set_weights_i32(self._h, _ptr(W_q), _ptr(R_q), _ptr(bw_q), _ptr(br_q),
+                                                _stream(self._tdev)), "qgru_set_weights_i32")
+
+    def get_weights_i32(self):
+        I, H = self.input_size, self.hidden_size
+        o = dict(dtype=torch.int32, device=self._tdev)
+        out = [torch.empty((I, 3 * H), **o), torch.empty((H, 3 * H), **o),
+               torch.empty(3 * H, **o), torch.empty(3 * H, **o)]
+        self._ck(self._lib.qgru_get_weights_i32(self._h, *[_ptr(t) for t in out], _stream(self._tdev)),
+                 "qgru_get_weights_i32")
+        return out
+
+    # -- forward (device tensors)
+    def forward_i32(self, x_q, h0_q=None, reverse=False, out=None, sync=True):
+        """x_q [T,B,I] int32 -> h_q [(T+1),B,H] int32 (slot layout as in include/qgru.h)."""
+        x_q = _check_tensor(x_q, "x_q", torch.int32)
+        if x_q.dim() != 3 or x_q.shape[2] != self.input_size:
+            raise ValueError("x_q must have shape [time_steps, batch_size, input_size]")
+        T, B = int(x_q.shape[0]), int(x_q.shape[1])
+        if h0_q is not None:
+            h0_q = _check_tensor(h0_q, "h0_q", torch.int32, (B, self.hidden_size))
+        h_q = out if out is not None else torch.empty((T + 1, B, self.hidden_size), dtype=torch.int32,
+                                                      device=self._tdev)
+        self._ck(self._lib.qgru_forward_i32(self._h, T, B, _ptr(x_q), _ptr(h0_q), _ptr(h_q),
+                                            _cabi.FLAG_REVERSE if reverse else 0, _stream(self._tdev)),
+                 "qgru_forward_i32")
+        if sync:
+            self.synchronize()
+        return h_q
+
+    def forward_f32(self, x, h0=None, reverse=False, want_x_q=False, out=None, sync=True):
+        x = _check_tensor(x, "x", torch.float32)
+        if x.dim() != 3 or x.shape[2] != self.input_size:
+            raise ValueError("x must have shape [time_steps, batch_size, input_size]")
+        T, B = int(x.shape[0]), int(x.shape[1])
+        if h0 is not None:
+            h0 = _check_tensor(h0, "h0", torch.float32, (B, self.hidden_size))
+        h = out if out is not None else torch.empty((T + 1, B, self.hidden_size), dtype=torch.float32,
+                                                    device=self._tdev)
+        x_q = torch.empty((T, B, self.input_size), dtype=torch.int32, device=self._tdev) if want_x_q else None
+        self._ck(self._lib.qgru_forward_f32(self._h, T, B, _ptr(x), _ptr(h0), _ptr(h), _ptr(x_q),
+                                            _cabi.FLAG_REVERSE if reverse else 0, _stream(self._tdev)),
+                 "qgru_forward_f32")
+        if sync:
+            self.synchronize()
+        return (h, x_q) if want_x_q else h
+
+    # -- forward (host tensors; copies are part of the call)
+    def forward_i32_host(self, x_q, h0_q=None, reverse=False, out=None):
+        x_q = _check_tensor(x_q, "x_q", torch.int32, cuda=False)
+        T, B = int(x_q.shape[0]), int(x_q.shape[1])
+        h_q = out if out is not None else torch.empty((T + 1, B, self.hidden_size), dtype=torch.int32)
+        self._ck(self._lib.qgru_forward_i32_host(self._h, T, B, _ptr(x_q), _ptr(h0_q), _ptr(h_q),
+                                                 _cabi.FLAG_REVERSE if reverse else 0,
+                                                 _stream(self._tdev)), "qgru_forward_i32_host")
+        return h_q
+
+    def forward_f32_host(self, x, h0=None, reverse=False, out=None):
+        x = _check_tensor(x, "x", torch.float32, cuda=False)
+        T, B = int(x.shape[0]), int(x.shape[1])
+        h = out if out is not None else torch.empty((T + 1, B, self.hidden_size), dtype=torch.float32)
+        self._ck(self._lib.qgru_forward_f32_host(self._h, T, B, _ptr(x), _ptr(h0), _ptr(h),
+                                                 _cabi.FLAG_REVERSE if reverse else 0,
+                                                 _stream(self._tdev)), "qgru_forward_f32_host")
+        return h
+
+    # -- float mode / calibration
+    def forward_float(self, W, R, bw, br, x, h0=None, want_v=False):
+        T, B = int(x.shape[0]), int(x.shape[1])
+        H = self.hidden_size
+        h = torch.empty((T + 1, B, H), dtype=torch.float32, device=self._tdev)
+        v = torch.empty((T, B, 4 * H), dtype=torch.float32, device=self._tdev) if want_v else None
+        args = [_check_tensor(t, n, torch.float32) for t, n in
+                ((W, "W"), (R, "R"), (bw, "bw"), (br, "br"), (x, "x"))]
+        if h0 is not None:
+            h0 = _check_tensor(h0, "h0", torch.float32, (B, H))
+        self._ck(self._lib.qgru_forward_float(self._h, T, B, *[_ptr(t) for t in args], _ptr(h0),
+                                              _ptr(h), _ptr(v), _stream(self._tdev)), "qgru_forward_float")
+        self.synchronize()
+        return (h, v) if want_v else h
+
+    def calibrate_minmax(self, W, R, bw, br, x, ranges, h0=None, want_h=False):
+        """Float forward + fold of this batch's min/max into ``ranges`` (in place)."""
+        T, B = int(x.shape[0]), int(x.shape[1])
+        H = self.hidden_size
+        args = [_check_tensor(t, n, torch.float32) for t, n in
+                ((W, "W"), (R, "R"), (bw, "bw"), (br, "br"), (x, "x"))]
+        if h0 is not None:
+            h0 = _check_tensor(h0, "h0", torch.float32, (B, H))
+        h = torch.empty((T + 1, B, H), dtype=torch.float32, device=self._tdev) if want_h else None
+        rs = ranges.struct()
+        self._ck(self._lib.qgru_calibrate_minmax(self._h, T, B, *[_ptr(t) for t in args], _ptr(h0),
+                                                 C.byref(rs), _ptr(h), _stream(self._tdev)),
+                 "qgru_calibrate_minmax")
+        ranges.load(rs)
+        return h
+
+    # -- introspection
+    def synchronize(self):
+        self._ck(self._lib.qgru_synchronize(self._h, _stream(self._tdev)), "qgru_synchronize")
+
+    def last_timing(self):
+        a, b, c = C.c_float(), C.c_float(), C.c_float()
+        self._ck(self._lib.qgru_last_timing(self._h, C.byref(a), C.byref(b), C.byref(c)), "qgru_last_timing")
+        return {"input_gemm_ms": a.value, "recurrence_ms": b.value, "total_ms": c.value}
+
+    def launch_count(self):
+        return int(self._lib.qgru_launch_count(self._h))
+
+    def describe_plan(self):
+        return self._lib.qgru_describe_plan(self._h, 0, 0).decode()
+
+
+# --------------------------------------------------------------------------------------
+# Functions with the reference binding's names.  A small cache keeps one Handle per
+# (device, I, H, slot) so that, unlike the reference, repeated calls reuse packed weights'
+# storage, streams and workspace.  `slot` separates the two directions.
+# --------------------------------------------------------------------------------------
+_handles = {}
+
+
+def _handle_for(device, I, H, slot=0):
+    key = (int(device), int(I), int(H), slot)
+    hd = _handles.get(key)
+    if hd is None:
+        hd = _handles[key] = Handle(I, H, device=device)
+    return hd
+
+
+def release_handles():
+    for hd in _handles.values():
+        hd.close()
+    _handles.clear()
+
+
+def init_gru_cublas():
+    """Kept for drop-in compatibility; the integer path uses no cuBLAS handle."""
+    return None
+
+
+def calculate_gru_quantitative_parameters(quant_ranges, bitwidth_config):
+    """MinMax ranges + bit-width config -> GRUQuantParams with LUTs (binding :209-231)."""
+    return GRUQuantParams.from_ranges(quant_ranges, bitwidth_config)
+
+
+def forward_quant_int_storage(is_training, time_steps, batch_size, input_size, hidden_size,
+                              W, R, bw, br, x, h0, quant_params, slot=0, reverse=False):
+    """Integer forward with float interface (binding :436-571, inference mode).
+
+    Returns (h [(T+1),B,H] f32, v (empty), W_q, R_q, bw_q, br_q, x_q) like the reference;
+    training-mode masks are not produced (is_training must be False)."""
+    if is_training:
+        raise NotImplementedError("training-mode outputs (v, clamp masks) are outside the inference hot path")
+    x = _check_tensor(x, "x", torch.float32, (time_steps, batch_size, input_size))
+    hd = _handle_for(x.device.index or 0, input_size, hidden_size, slot)
+    hd.set_params(quant_params)
+    hd.set_weights_f32(W, R, bw, br)
+    h0 = h0 if (h0 is not None and h0.numel() > 0) else None
+    h, x_q = hd.forward_f32(x, h0, reverse=reverse, want_x_q=True)
+    W_q, R_q, bw_q, br_q = hd.get_weights_i32()
+    v = torch.empty(0, dtype=torch.float32, device=x.device)
+    return h, v, W_q, R_q, bw_q, br_q, x_q
+
+
+def forward_quantized_int_io(time_steps, batch_size, input_size, hidden_size, W, R, bw, br, x_q,
+                             h0_q, quant_params, slot=0, reverse=False):
+    """int32 in / int32 out inference (binding :573-618): returns (output_q [T,B,H], h_n_q [1,B,H])."""
+    x_q = _check_tensor(x_q, "x_q", torch.int32, (time_steps, batch_size, input_size))
+    hd = _handle_for(x_q.device.index or 0, input_size, hidden_size, slot)
+    hd.set_params(quant_params)
+    hd.set_weights_f32(W, R, bw, br)
+    h0_q = h0_q if (h0_q is not None and h0_q.numel() > 0) else None
+    h_q = hd.forward_i32(x_q, h0_q, reverse=reverse)
+    if reverse:
+        return h_q[:time_steps].contiguous(), h_q[0:1].contiguous()
+    return h_q[1:].contiguous(), h_q[time_steps:time_steps + 1].contiguous()
+
+
+def forward_fp(is_training, time_steps, batch_size, input_size, hidden_size, W, R, bw, br, x, h0):
+    """Unquantized fp32 GRU (binding :629-681): returns (h [(T+1),B,H], v [T,B,4H])."""
+    x = _check_tensor(x, "x", torch.float32, (time_steps, batch_size, input_size))
+    hd = _handle_for(x.device.index or 0, input_size, hidden_size, "fp")
+    h0 = h0 if (h0 is not None and h0.numel() > 0) else None
+    return hd.forward_float(W, R, bw, br, x, h0, want_v=True)
+
+
+def forward_calibrate(is_training, time_steps, batch_size, input_size, hidden_size, W, R, bw, br,
+                      x, h0, calib_method_str, bitwidth_config, quant_ranges=None,
+                      hist_collectors=None):
+    """Calibration forward (binding :683-790), MinMax method: float forward whose ranges are
+    folded into ``quant_ranges`` in place; returns (h, v)."""
+    if calib_method_str.lower() != "minmax":
+        raise NotImplementedError("only the 'minmax' calibration method is built")
+    if quant_ranges is None:
+        raise ValueError("quant_ranges is required for minmax calibration")
+    x = _check_tensor(x, "x", torch.float32, (time_steps, batch_size, input_size))
+    hd = _handle_for(x.device.index or 0, input_size, hidden_size, "fp")
+    h0 = h0 if (h0 is not None and h0.numel() > 0) else None
+    h = hd.calibrate_minmax(W, R, bw, br, x, quant_ranges, h0, want_h=True)
+    v = torch.empty(0, dtype=torch.float32, device=x.device)
+    return h, v

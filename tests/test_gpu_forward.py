@@ -1,0 +1,177 @@
+"""Parity of the CUDA path with the oracle, through the C ABI, bit for bit.
+
+Every case is built on the CPU (seeded floats -> MinMax calibration -> quantized operands),
+run once by the oracle and once by libqgru_b200.so on cuda:0, and compared with array_equal:
+every timestep of h_q, hence `output` and `h_n`."""
+import importlib
+
+import numpy as np
+import pytest
+
+from __graft_entry__ import PKG_NAME
+from tests.cases import config_named, make_case
+
+gru_ops = importlib.import_module(PKG_NAME + ".gru_ops")
+pytestmark = pytest.mark.gpu
+
+SHAPES = [  # (T, B, I, H)
+    (6, 5, 20, 40),      # nothing a multiple of anything
+    (1, 1, 1, 1),        # degenerate
+    (3, 2, 7, 8),
+    (9, 33, 64, 128),    # config-1 shape, shortened
+    (5, 70, 48, 96),
+    (4, 3, 80, 256),     # H = 256: R exactly fills one CTA's shared memory
+    (3, 17, 33, 300),    # ragged H above 256: two CTAs per group, per-step barrier
+    (4, 40, 64, 512),    # config-2 hidden size: eight CTAs per group
+]
+CONFIGS = ["default", "sym8_tensor", "cfg2", "cfg3", "cfg5", "pot2", "pot2_asym", "ih16", "gate_in16",
+           "unsigned_x"]
+
+
+def _t(a, dev):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+def _run(case, dev, reverse=False, opts=(), f32=False, host=False):
+    import torch
+    with gru_ops.Handle(case.I, case.H, device=dev.index or 0) as hd:
+        for k, v in opts:
+            hd.set_option(k, v)
+        hd.set_params(case.params)
+        hd.set_weights_i32(*[_t(a, dev) for a in case.wq])
+        if f32:
+            if host:
+                out = hd.forward_f32_host(torch.from_numpy(case.x), torch.from_numpy(case.h0) if case.h0 is not None else None, reverse=reverse)
+            else:
+                out = hd.forward_f32(_t(case.x, dev), _t(case.h0, dev) if case.h0 is not None else None, reverse=reverse)
+        elif host:
+            out = hd.forward_i32_host(torch.from_numpy(case.x_q), torch.from_numpy(case.h0_q) if case.h0_q is not None else None, reverse=reverse)
+        else:
+            out = hd.forward_i32(_t(case.x_q, dev), _t(case.h0_q, dev) if case.h0_q is not None else None, reverse=reverse)
+        plan = hd.describe_plan()
+        launches = hd.launch_count()
+    return out.cpu().numpy(), plan, launches
+
+
+def _want(oracle, case):
+    return oracle.forward_i32(case.T, case.B, case.I, case.H, case.wq, case.x_q, case.h0_q, case.params.c,
+                              case.params.scale_list())
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_shapes_default_config(oracle, cuda_device, shape):
+    T, B, I, H = shape
+    case = make_case(11, T, B, I, H, oracle, config_named("default"))
+    got, plan, launches = _run(case, cuda_device)
+    assert "path=int8" in plan and launches > 0
+    assert np.array_equal(got, _want(oracle, case)), plan
+
+
+@pytest.mark.parametrize("name", CONFIGS)
+def test_bitwidth_configs(oracle, cuda_device, name):
+    for seed, (T, B, I, H) in enumerate([(7, 6, 24, 48), (4, 9, 40, 72)]):
+        case = make_case(20 + seed, T, B, I, H, oracle, config_named(name), with_h0=(seed == 1))
+        got, plan, _ = _run(case, cuda_device)
+        assert "path=int8" in plan
+        assert np.array_equal(got, _want(oracle, case)), (name, plan)
+
+
+@pytest.mark.parametrize("name", ["wide16", "default", "cfg2"])
+def test_generic_path(oracle, cuda_device, name):
+    """16-bit activations cannot use 8-bit storage: the int32 / 64-bit-accumulate kernels run.
+    They are also forced on 8-bit configs as a second, independent GPU implementation."""
+    case = make_case(31, 5, 4, 12, 24, oracle, config_named(name), with_h0=True)
+    got, plan, _ = _run(case, cuda_device, opts=(("rec", "generic"),))
+    assert "path=generic" in plan
+    assert np.array_equal(got, _want(oracle, case))
+    if name == "wide16":
+        got2, plan2, _ = _run(case, cuda_device)
+        assert "path=generic" in plan2 and np.array_equal(got2, got)
+
+
+@pytest.mark.parametrize("name", ["default", "cfg2", "wide16"])
+def test_reverse_direction_equals_flip(oracle, cuda_device, name):
+    """QGRU_FLAG_REVERSE == the reference's flip -> forward -> flip for the reverse direction."""
+    case = make_case(41, 6, 5, 16, 40, oracle, config_named(name), with_h0=True)
+    got, _, _ = _run(case, cuda_device, reverse=True)
+    flipped = oracle.forward_i32(case.T, case.B, case.I, case.H, case.wq, case.x_q[::-1].copy(), case.h0_q,
+                                 case.params.c, case.params.scale_list())
+    assert np.array_equal(got[:case.T], flipped[1:][::-1])       # output
+    assert np.array_equal(got[0], flipped[case.T])               # h_n
+    assert np.array_equal(got[case.T], flipped[0])               # the initial state slot
+
+
+@pytest.mark.parametrize("name", ["default", "cfg2", "pot2", "wide16"])
+def test_float_interface_bitwise(oracle, cuda_device, name):
+    """Float in / float out (quantGRUForwardInt): quantize, forward and dequantize must give the
+    very same floats as the CPU path; includes h0 and values that saturate the x range."""
+    case = make_case(51, 6, 7, 20, 40, oracle, config_named(name), with_h0=True, sigma=1.5)
+    want = oracle.forward_f32(case.T, case.B, case.I, case.H, case.wq, case.x, case.h0, case.params.c,
+                              case.params.scale_list())
+    got, _, _ = _run(case, cuda_device, f32=True)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_host_buffer_entry_points(oracle, cuda_device):
+    case = make_case(61, 5, 6, 24, 48, oracle, config_named("cfg2"), with_h0=True)
+    got, _, _ = _run(case, cuda_device, host=True)
+    assert np.array_equal(got, _want(oracle, case))
+    want_f = oracle.forward_f32(case.T, case.B, case.I, case.H, case.wq, case.x, case.h0, case.params.c,
+                                case.params.scale_list())
+    got_f, _, _ = _run(case, cuda_device, f32=True, host=True)
+    assert np.array_equal(got_f.view(np.uint32), want_f.view(np.uint32))
+
+
+def test_weight_quantize_on_device_matches(oracle, cuda_device):
+    """set_weights_f32 (per-channel quantize on the GPU) == quantitativeWeightCPU."""
+    for name in ("default", "cfg3", "cfg5", "pot2"):
+        case = make_case(71, 3, 2, 40, 24, oracle, config_named(name))
+        with gru_ops.Handle(case.I, case.H, device=0) as hd:
+            hd.set_params(case.params)
+            hd.set_weights_f32(*[_t(a, cuda_device) for a in (case.W, case.R, case.bw, case.br)])
+            got = [t.cpu().numpy() for t in hd.get_weights_i32()]
+            h = hd.forward_i32(_t(case.x_q, cuda_device)).cpu().numpy()
+        for a, b in zip(got, case.wq):
+            assert np.array_equal(a, b), name
+        assert np.array_equal(h, _want(oracle, case))
+
+
+def test_repeated_calls_and_handle_reuse(oracle, cuda_device):
+    """Two calls in a row, then a different (T, B) and new params on the same handle."""
+    import torch
+    a = make_case(81, 5, 4, 16, 32, oracle, config_named("default"))
+    b = make_case(82, 9, 7, 16, 32, oracle, config_named("cfg2"))
+    with gru_ops.Handle(16, 32, device=0) as hd:
+        for case in (a, a, b, a):
+            hd.set_params(case.params)
+            hd.set_weights_i32(*[_t(w, cuda_device) for w in case.wq])
+            got = hd.forward_i32(_t(case.x_q, cuda_device)).cpu().numpy()
+            assert np.array_equal(got, _want(oracle, case))
+    torch.cuda.synchronize()
+
+
+def test_argument_errors(oracle, cuda_device):
+    import torch
+    case = make_case(91, 3, 2, 8, 16, oracle, config_named("default"))
+    with gru_ops.Handle(8, 16, device=0) as hd:
+        with pytest.raises(Exception):   # forward before params / weights
+            hd.forward_i32(_t(case.x_q, cuda_device))
+        hd.set_params(case.params)
+        with pytest.raises(ValueError):  # wrong weight shape
+            hd.set_weights_i32(*[_t(w, cuda_device) for w in (case.wq[1], case.wq[1], case.wq[2], case.wq[3])])
+        hd.set_weights_i32(*[_t(w, cuda_device) for w in case.wq])
+        with pytest.raises(ValueError):  # wrong dtype
+            hd.forward_i32(_t(case.x, cuda_device))
+        bad = case.x_q.copy()
+        bad[0, 0, 0] = 1000            # outside the 8-bit range x declares
+        with pytest.raises(ValueError):
+            hd.forward_i32(_t(bad, cuda_device))
+        got = hd.forward_i32(_t(case.x_q, cuda_device)).cpu().numpy()   # handle still usable
+        assert np.array_equal(got, _want(oracle, case))
+    with pytest.raises(Exception):
+        bad_cfg = config_named("default")
+        bad_cfg.symmetric["R"] = False
+        p = importlib.import_module(PKG_NAME + ".params").GRUQuantParams(16, bad_cfg)
+        with gru_ops.Handle(8, 16, device=0) as hd:
+            hd.set_params(p)

@@ -1,0 +1,146 @@
+"""CPU-only checks of the product library: it loads, exports every symbol include/qgru.h
+declares, and its host-side helpers (scale encoding, LUT generation, MinMax parameter
+derivation) agree bit for bit with the oracle and, where built, the reference."""
+import ctypes as C
+import importlib
+import os
+import re
+
+import numpy as np
+import pytest
+
+from __graft_entry__ import PKG_NAME
+from tests.cases import OP, config_named, make_case, params_mod
+
+_cabi = importlib.import_module(PKG_NAME + "._cabi")
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    hdr = open(os.path.join(ROOT, "include", "qgru.h")).read()
+    declared = set(re.findall(r"QGRU_API\s+[\w\s\*]+?\b(qgru_\w+)\s*\(", hdr))
+    assert len(declared) >= 25
+    assert declared == set(_cabi.SYMBOLS), declared ^ set(_cabi.SYMBOLS)
+    lib = _cabi.lib()
+    for name in declared:
+        assert getattr(lib, name) is not None
+    assert lib.qgru_version().decode().startswith("qgru-b200")
+    assert lib.qgru_status_string(3).decode() == "device-side wait timed out"
+
+
+def test_struct_sizes_match_header():
+    assert C.sizeof(_cabi.Op) == 12
+    assert C.sizeof(_cabi.LutSegment) == 16
+    assert C.sizeof(_cabi.Lut) == 16 * 16 + 16
+    assert C.sizeof(_cabi.Params) == 8 + 17 * 12 + 16 + 3 * 272
+
+
+def test_create_without_gpu_fails_loudly():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    h = C.c_void_p()
+    assert _cabi.lib().qgru_create(C.byref(h), 0, 8, 8) == _cabi.QGRU_ERR_CUDA
+    assert not h.value
+
+
+def test_host_primitives_match_oracle(oracle):
+    lib = _cabi.lib()
+    rng = np.random.default_rng(1)
+    for _ in range(5000):
+        x = int(rng.integers(-2 ** 45, 2 ** 45))
+        n = int(rng.integers(-6, 50))
+        assert lib.qgru_rshift_round(x, n) == oracle.rshift_round(x, n)
+    for _ in range(5000):
+        s = float(np.float32(10 ** rng.uniform(-9, 4)))
+        m, sh = C.c_uint16(), C.c_int8()
+        st = lib.qgru_encode_mshift(C.c_float(s), C.byref(m), C.byref(sh))
+        want = oracle.encode_mshift(s)
+        assert (st == 0 and (m.value, sh.value) == want) or (st == _cabi.QGRU_ERR_RANGE and want is None)
+    m, sh = C.c_uint16(), C.c_int8()
+    assert lib.qgru_encode_mshift(C.c_float(0.0), C.byref(m), C.byref(sh)) == _cabi.QGRU_ERR_RANGE
+
+
+@pytest.mark.parametrize("name", ["default", "sym8_tensor", "cfg2", "cfg3", "cfg5", "pot2", "pot2_asym",
+                                  "wide16", "gate_in16"])
+def test_params_from_ranges_and_luts_match(oracle, name):
+    from oracle.binding import reference_or_none
+    checkers = [oracle] + ([reference_or_none()] if reference_or_none() else [])
+    for seed, (T, B, I, H) in enumerate([(6, 4, 10, 16), (4, 2, 7, 40)]):
+        case = make_case(seed, T, B, I, H, oracle, config_named(name))
+        rng = np.random.default_rng(seed)
+        ranges = params_mod.Ranges(H)
+        oracle.forward_float(T, B, I, H, case.W, case.R, case.bw, case.br,
+                             rng.standard_normal((T, B, I)).astype(np.float32), None, ranges=ranges)
+        mine = params_mod.GRUQuantParams.from_ranges(ranges, config_named(name))
+        for chk in checkers:
+            theirs = params_mod.GRUQuantParams(H, config_named(name))
+            sc = chk.calc_params_from_ranges(ranges, theirs.c)
+            assert bytes(mine.c) == bytes(theirs.c), f"{chk.kind}: params/LUTs differ"
+            for a, b in zip(mine.scale_list(), sc):
+                assert np.array_equal(a, b)
+        # LUT evaluation over the clamped domain and beyond
+        lib = _cabi.lib()
+        p = mine.c
+        for lut, i_in, i_out in ((0, OP["update_gate_input"], OP["update_gate_output"]),
+                                 (2, OP["new_gate_input"], OP["new_gate_output"])):
+            for q in list(range(-260, 260, 3)) + [-40000, 40000]:
+                assert lib.qgru_lut_eval(C.byref(p.lut[lut]), q, C.byref(p.op[i_in]), C.byref(p.op[i_out])) == \
+                    oracle.lut_eval(p.lut[lut], q, p.op[i_in], p.op[i_out])
+
+
+def test_asymmetric_weights_are_rejected(oracle):
+    cfg = config_named("default")
+    cfg.symmetric["W"] = False
+    ranges = params_mod.Ranges(8)
+    ranges.min_v[:] = -1
+    ranges.max_v[:] = 1
+    for n in params_mod.WEIGHT_OPS:
+        ranges.ch_min[n][:] = -1
+        ranges.ch_max[n][:] = 1
+    with pytest.raises(Exception):
+        params_mod.GRUQuantParams.from_ranges(ranges, cfg)
+
+
+def test_bitwidth_json_round_trip(tmp_path):
+    import json
+    cfg = config_named("cfg5")
+    path = tmp_path / "bw.json"
+    path.write_text(json.dumps(cfg.to_json_dict()))
+    back = params_mod.OperatorQuantConfig.from_json(str(path))
+    assert back.bits == cfg.bits and back.symmetric == cfg.symmetric and back.unsigned == cfg.unsigned
+    assert back.granularity == cfg.granularity and back.use_pot2 == cfg.use_pot2
+    # legacy aliases and error behaviour of the reference's loader
+    d = cfg.to_json_dict()
+    d["GRU_config"]["operator_config"]["W"] = d["GRU_config"]["operator_config"].pop("weight_ih")
+    assert params_mod.OperatorQuantConfig.from_json(d).bits["W"] == 4
+    d["GRU_config"]["operator_config"]["bogus"] = {"bitwidth": 8}
+    with pytest.raises(ValueError):
+        params_mod.OperatorQuantConfig.from_json(d)
+    d["GRU_config"]["operator_config"].pop("bogus")
+    d["GRU_config"]["operator_config"]["input"]["bitwidth"] = 40
+    with pytest.raises(ValueError):
+        params_mod.OperatorQuantConfig.from_json(d)
+
+
+def test_reference_shipped_bitwidth_json_loads():
+    path = "/root/reference/pytorch/config/gru_quant_bitwidth_config.json"
+    if not os.path.exists(path):
+        pytest.skip("reference tree not present")
+    cfg = params_mod.OperatorQuantConfig.from_json(path)
+    assert cfg.bits["x"] == 8 and cfg.unsigned["update_gate_output"] and cfg.symmetric["x"]
+
+
+def test_quant_param_export_round_trip(oracle):
+    case = make_case(2, 5, 3, 9, 12, oracle, config_named("cfg2"))
+    d = case.params.to_export_dict()
+    assert d["weight_ih"]["enc_type"] == "PER_CHANNEL" and len(d["weight_ih"]["scale"]) == 36
+    assert d["update_gate_output"]["dtype"] == "UINT16"
+    back = params_mod.GRUQuantParams.from_export_dict(d, 12, use_pot2=False)
+    back.c.granularity[:] = case.params.c.granularity[:]
+    assert bytes(back.c) == bytes(case.params.c)
+    for a, b in zip(back.scale_list(), case.params.scale_list()):
+        assert np.array_equal(a, b)
+    blob = case.params.to_bytes()
+    again = params_mod.GRUQuantParams.from_bytes(blob, 12)
+    assert bytes(again.c) == bytes(case.params.c)

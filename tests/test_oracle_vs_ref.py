@@ -1,0 +1,71 @@
+"""The oracle is pinned here: the C restatement (oracle/qgru_oracle.c) must agree bit for bit
+with the unmodified reference sources compiled into oracle/_ref/ on every function it
+restates.  Skipped where the reference tree was never compiled (then tests/golden/ pins it)."""
+import numpy as np
+import pytest
+
+from tests.cases import OP, config_named, make_case
+
+CONFIGS = ["default", "sym8_tensor", "cfg2", "cfg3", "cfg5", "pot2", "pot2_asym", "ih16", "wide16",
+           "gate_in16", "unsigned_x"]
+
+
+def test_rshift_round_and_encode(oracle, reference):
+    rng = np.random.default_rng(0)
+    for _ in range(5000):
+        x = int(rng.integers(-2 ** 45, 2 ** 45))
+        n = int(rng.integers(-6, 50))
+        assert oracle.rshift_round(x, n) == reference.rshift_round(x, n)
+    # the survey's known answers (banker's rounding on the magnitude, negative n = left shift)
+    for (x, n, want) in [(5, 1, 2), (7, 1, 4), (-5, 1, -2), (3, -2, 12), (6, 2, 2), (10, 2, 2), (-6, 2, -2)]:
+        assert oracle.rshift_round(x, n) == want == reference.rshift_round(x, n)
+    for _ in range(5000):
+        s = float(np.float32(10 ** rng.uniform(-9, 4)))
+        assert oracle.encode_mshift(s) == reference.encode_mshift(s)
+    assert oracle.encode_mshift(42.0) == (43008, 10) == reference.encode_mshift(42.0)
+    assert oracle.encode_mshift(2.0 ** -7) == (32768, 22) == reference.encode_mshift(2.0 ** -7)
+    assert oracle.encode_mshift(0.0) is None and reference.encode_mshift(0.0) is None
+    assert oracle.encode_mshift(-1.0) is None and reference.encode_mshift(-1.0) is None
+
+
+@pytest.mark.parametrize("name", CONFIGS)
+def test_params_quantize_forward(oracle, reference, name):
+    for seed, (T, B, I, H) in enumerate([(7, 5, 12, 24), (3, 1, 9, 8), (5, 3, 33, 40)]):
+        cr = make_case(seed, T, B, I, H, reference, config_named(name), with_h0=(seed == 1), oracle=oracle)
+        co = make_case(seed, T, B, I, H, oracle, config_named(name), with_h0=(seed == 1), oracle=oracle)
+        assert bytes(cr.params.c) == bytes(co.params.c), "scales / zero points / LUTs differ"
+        for a, b in zip(cr.params.scale_list(), co.params.scale_list()):
+            assert np.array_equal(a, b)
+        for a, b in zip(cr.wq, co.wq):
+            assert np.array_equal(a, b)
+        assert np.array_equal(cr.x_q, co.x_q)
+        args = (cr.T, cr.B, cr.I, cr.H, cr.wq)
+        sc = cr.params.scale_list()
+        hr = reference.forward_i32(*args, cr.x_q, cr.h0_q, cr.params.c, sc)
+        ho = oracle.forward_i32(*args, cr.x_q, cr.h0_q, cr.params.c, sc)
+        assert np.array_equal(hr, ho)
+        fr = reference.forward_f32(*args, cr.x, cr.h0, cr.params.c, sc)
+        fo = oracle.forward_f32(*args, cr.x, cr.h0, cr.params.c, sc)
+        assert np.array_equal(fr, fo)
+        assert np.array_equal(reference.dequantize(hr, cr.params.c, OP["h"]), fr)
+
+
+def test_multithreaded_slices_are_identical(oracle, reference):
+    c = make_case(3, 6, 11, 10, 16, oracle, config_named("cfg2"), with_h0=True)
+    sc = c.params.scale_list()
+    one = oracle.forward_i32(c.T, c.B, c.I, c.H, c.wq, c.x_q, c.h0_q, c.params.c, sc)
+    for chk in (oracle, reference):
+        for th in (2, 4, 11, 16):
+            got = chk.forward_i32(c.T, c.B, c.I, c.H, c.wq, c.x_q, c.h0_q, c.params.c, sc, threads=th)
+            assert np.array_equal(got, one)
+
+
+def test_lut_eval_whole_domain(oracle, reference):
+    c = make_case(5, 4, 4, 8, 16, reference, config_named("cfg2"), oracle=oracle)
+    p = c.params.c
+    for lut, i_in, i_out in ((0, OP["update_gate_input"], OP["update_gate_output"]),
+                             (1, OP["reset_gate_input"], OP["reset_gate_output"]),
+                             (2, OP["new_gate_input"], OP["new_gate_output"])):
+        for q in range(-300, 300):
+            assert oracle.lut_eval(p.lut[lut], q, p.op[i_in], p.op[i_out]) == \
+                reference.lut_eval(p.lut[lut], q, p.op[i_in], p.op[i_out])
