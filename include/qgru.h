@@ -192,7 +192,8 @@ QGRU_API int qgru_get_weights_i32(qgru_handle *h, int32_t *W_q, int32_t *R_q, in
  *   x_q  [T,B,I] int32 device, h0_q [B,H] int32 device or NULL (-> zero point of h),
  *   h_q  [(T+1),B,H] int32 device out.
  * With QGRU_FLAG_REVERSE timestep s of the recurrence reads x_q[T-1-s] and writes
- * h_q[T-s]; slot T holds the initial state.  This equals the reference's
+ * h_q[T-1-s]; slot T holds the initial state, slots 0..T-1 the outputs in input time order
+ * and slot 0 is h_n.  This equals the reference's
  * flip -> forward -> flip for the reverse direction (pytorch/quant_gru.py:2143-2158)
  * without the two copies. */
 QGRU_API int qgru_forward_i32(qgru_handle *h, int T, int B, const int32_t *x_q,
@@ -223,6 +224,12 @@ QGRU_API int qgru_synchronize(qgru_handle *h, void *stream);
  * launching stream (milliseconds; synchronises).  Any pointer may be NULL. */
 QGRU_API int qgru_last_timing(qgru_handle *h, float *ms_input_gemm, float *ms_recurrence,
                               float *ms_total);
+
+/* Sums of the same three durations over the last `n_calls` forwards of this handle (at most
+ * 64 are remembered), so a benchmark can queue steps back to back and read per-kernel time
+ * afterwards.  *n_calls returns how many calls were summed.  Synchronises. */
+QGRU_API int qgru_timing_window(qgru_handle *h, int *n_calls, float *ms_input_gemm,
+                                float *ms_recurrence, float *ms_total);
 
 /* Number of kernels launched by this handle since creation. */
 QGRU_API uint64_t qgru_launch_count(const qgru_handle *h);

@@ -73,6 +73,7 @@ SYMBOLS = {
     "qgru_forward_f32_host": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, C.c_uint, _P]),
     "qgru_synchronize": (C.c_int, [_P, _P]),
     "qgru_last_timing": (C.c_int, [_P, _F, _F, _F]),
+    "qgru_timing_window": (C.c_int, [_P, C.POINTER(C.c_int), _F, _F, _F]),
     "qgru_launch_count": (C.c_uint64, [_P]),
     "qgru_describe_plan": (C.c_char_p, [_P, C.c_int, C.c_int]),
     "qgru_set_option": (C.c_int, [_P, C.c_char_p, C.c_char_p]),

@@ -92,7 +92,8 @@ int qgru_create(qgru_handle **out, int device, int input_size, int hidden_size) 
     ok = ok && cudaMalloc(&h->d_flags, 2 * sizeof(int)) == cudaSuccess;
     ok = ok && cudaMemset(h->d_flags, 0, 2 * sizeof(int)) == cudaSuccess;
     ok = ok && cudaMallocHost(&h->h_flags, 2 * sizeof(int)) == cudaSuccess;
-    for (int i = 0; i < 4 && ok; ++i) ok = cudaEventCreate(&h->ev[i]) == cudaSuccess;
+    for (int r = 0; r < qgru_handle::kRing && ok; ++r)
+        for (int i = 0; i < 4 && ok; ++i) ok = cudaEventCreate(&h->ring[r][i]) == cudaSuccess;
     if (!ok) {
         cudaGetLastError();
         qgru_destroy(h);
@@ -119,8 +120,10 @@ void qgru_destroy(qgru_handle *h) {
     for (int i = 0; i < 4; ++i) {
         cudaFree(h->d_wscale[i]);
         cudaFree(h->d_wq[i]);
-        if (h->ev[i]) cudaEventDestroy(h->ev[i]);
     }
+    for (int r = 0; r < qgru_handle::kRing; ++r)
+        for (int i = 0; i < 4; ++i)
+            if (h->ring[r][i]) cudaEventDestroy(h->ring[r][i]);
     cudaFree(h->d_flags);
     if (h->h_flags) cudaFreeHost(h->h_flags);
     cudaFree(h->d_bar);
@@ -562,6 +565,8 @@ int qgru_forward_i32(qgru_handle *h, int T, int B, const int32_t *x_q, const int
     const long long N = (long long)T * B;
     const qgru_op &xo = h->p.op[QGRU_OP_X], &ho = h->p.op[QGRU_OP_H];
     const long long init_slot = (flags & QGRU_FLAG_REVERSE) ? T : 0;
+    h->ev = h->ring[h->calls % qgru_handle::kRing];
+    h->calls++;
     CK(cudaEventRecord(h->ev[0], st));
     CK(cudaMemsetAsync(h->d_flags, 0, 2 * sizeof(int), st));
     if (use_generic(h)) {
@@ -594,6 +599,8 @@ int qgru_forward_f32(qgru_handle *h, int T, int B, const float *x, const float *
     const long long N = (long long)T * B;
     const qgru_op &xo = h->p.op[QGRU_OP_X], &ho = h->p.op[QGRU_OP_H];
     const long long init_slot = (flags & QGRU_FLAG_REVERSE) ? T : 0;
+    h->ev = h->ring[h->calls % qgru_handle::kRing];
+    h->calls++;
     CK(cudaEventRecord(h->ev[0], st));
     CK(cudaMemsetAsync(h->d_flags, 0, 2 * sizeof(int), st));
     if (use_generic(h)) {
@@ -696,6 +703,29 @@ int qgru_last_timing(qgru_handle *h, float *ms_input_gemm, float *ms_recurrence,
     if (ms_input_gemm) *ms_input_gemm = a;
     if (ms_recurrence) *ms_recurrence = b;
     if (ms_total) *ms_total = c;
+    return QGRU_OK;
+}
+
+int qgru_timing_window(qgru_handle *h, int *n_calls, float *ms_input_gemm, float *ms_recurrence,
+                       float *ms_total) {
+    if (!h || !n_calls) return QGRU_ERR_BAD_ARG;
+    if (!h->timing_valid) return fail(h, QGRU_ERR_NOT_READY, "no forward has run");
+    CK(cudaSetDevice(h->device));
+    int n = std::min<long long>(std::min<long long>(*n_calls, qgru_handle::kRing), (long long)h->calls);
+    float sa = 0, sb = 0, sc = 0;
+    for (int k = 0; k < n; ++k) {
+        cudaEvent_t *e = h->ring[(h->calls - 1 - k) % qgru_handle::kRing];
+        CK(cudaEventSynchronize(e[3]));
+        float a = 0, b = 0, c = 0;
+        CK(cudaEventElapsedTime(&a, e[1], e[2]));
+        CK(cudaEventElapsedTime(&b, e[2], e[3]));
+        CK(cudaEventElapsedTime(&c, e[0], e[3]));
+        sa += a; sb += b; sc += c;
+    }
+    *n_calls = n;
+    if (ms_input_gemm) *ms_input_gemm = sa;
+    if (ms_recurrence) *ms_recurrence = sb;
+    if (ms_total) *ms_total = sc;
     return QGRU_OK;
 }
 

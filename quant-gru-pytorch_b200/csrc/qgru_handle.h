@@ -56,7 +56,10 @@ struct qgru_handle {
     // workspace
     DevBuf x8, ih, h8, x32, ih32, hh32, hq32, stage_in, stage_h0, stage_out;
     DevBuf f_wx, f_h, f_v, f_acc;  // float mode / calibration
-    cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+    static constexpr int kRing = 64;
+    cudaEvent_t ring[kRing][4] = {};   // per forward: start, gemm start, gemm end, recurrence end
+    cudaEvent_t *ev = ring[0];          // the slot the current forward records into
+    uint64_t calls = 0;                 // forwards issued
     bool timing_valid = false;
     uint64_t launches = 0;
     TcGemmState tc;

@@ -204,6 +204,13 @@ class Handle:
         self._ck(self._lib.qgru_last_timing(self._h, C.byref(a), C.byref(b), C.byref(c)), "qgru_last_timing")
         return {"input_gemm_ms": a.value, "recurrence_ms": b.value, "total_ms": c.value}
 
+    def timing_window(self, n_calls):
+        """Sums of the per-kernel durations over the last n_calls forwards (<= 64)."""
+        n, a, b, c = C.c_int(int(n_calls)), C.c_float(), C.c_float(), C.c_float()
+        self._ck(self._lib.qgru_timing_window(self._h, C.byref(n), C.byref(a), C.byref(b), C.byref(c)),
+                 "qgru_timing_window")
+        return {"calls": n.value, "input_gemm_ms": a.value, "recurrence_ms": b.value, "total_ms": c.value}
+
     def launch_count(self):
         return int(self._lib.qgru_launch_count(self._h))
 
