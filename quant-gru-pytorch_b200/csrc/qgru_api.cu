@@ -83,8 +83,8 @@ int qgru_create(qgru_handle **out, int device, int input_size, int hidden_size) 
     h->I = input_size;
     h->H = hidden_size;
     h->C = 3 * hidden_size;
-    h->Ipad = (input_size + 31) / 32 * 32;
-    h->Hpad = (hidden_size + 31) / 32 * 32;
+    h->Ipad = (input_size + 127) / 128 * 128;   // K padded to whole 128-byte swizzle rows
+    h->Hpad = (hidden_size + 127) / 128 * 128;
     bool ok = cudaSetDevice(device) == cudaSuccess;
     ok = ok && cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, device) == cudaSuccess;
     ok = ok && cudaDeviceGetAttribute(&h->smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device) == cudaSuccess;
@@ -317,8 +317,13 @@ int finish_weights(qgru_handle *h, cudaStream_t st) {
     const int C = h->C;
     int rc;
     if (h->fast) {
-        if ((rc = alloc_dev(h, &h->d_w8[0], (size_t)C * h->Ipad))) return rc;
-        if ((rc = alloc_dev(h, &h->d_w8[1], (size_t)C * h->Hpad))) return rc;
+        // rows are allocated (and zeroed) past 3H so that every 128-row tile load stays inside
+        h->w8_rows[0] = (C + 127) / 128 * 128;
+        h->w8_rows[1] = C + 256;
+        if ((rc = alloc_dev(h, &h->d_w8[0], (size_t)h->w8_rows[0] * h->Ipad))) return rc;
+        if ((rc = alloc_dev(h, &h->d_w8[1], (size_t)h->w8_rows[1] * h->Hpad))) return rc;
+        CK(cudaMemsetAsync(h->d_w8[0], 0, (size_t)h->w8_rows[0] * h->Ipad, st));
+        CK(cudaMemsetAsync(h->d_w8[1], 0, (size_t)h->w8_rows[1] * h->Hpad, st));
     }
     CK(cudaMemsetAsync(h->d_flags, 0, 2 * sizeof(int), st));
     k_pack_weights<<<C, 128, 0, st>>>(h->d_wq[0], h->fast ? h->d_w8[0] : nullptr, h->d_wsum[0], h->I,
@@ -448,8 +453,8 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
     const LinearConsts lcx = linear_consts(h, 0);
     bool used_tc = false;
     if (h->opt_gemm != 1) {
-        rc = tc_gemm_launch(h->tc, h->device, h->sm_count, (const uint8_t *)h->x8.p, h->d_w8[0], h->ih.p,
-                            N, C, h->Ipad, h->x_uns, h->ih_bytes, lcx, st, &h->err);
+        rc = tc_gemm_launch(h->tc, (const uint8_t *)h->x8.p, (N + 127) / 128 * 128, h->d_w8[0], h->w8_rows[0],
+                            h->ih.p, N, C, h->Ipad, h->x_uns, h->ih_bytes, lcx, h->d_flags + 1, st, &h->err);
         if (rc == QGRU_OK) {
             used_tc = true;
             h->launches++;
@@ -576,7 +581,7 @@ int qgru_forward_i32(qgru_handle *h, int T, int B, const int32_t *x_q, const int
         h->launches++;
         return run_generic(h, T, B, x_q, h_q, flags, st);
     }
-    if ((rc = ensure(h, h->x8, (size_t)N * h->Ipad))) return rc;
+    if ((rc = ensure(h, h->x8, (size_t)((N + 127) / 128 * 128) * h->Ipad))) return rc;
     if ((rc = ensure(h, h->h8, (size_t)2 * B * h->Hpad))) return rc;
     k_narrow_rows_i32<<<grid_for(N * (h->Ipad / 4), 256, h->sm_count), 256, 0, st>>>(
         x_q, (uint8_t *)h->x8.p, N, h->I, h->Ipad, op_qmin(xo), op_qmax(xo), h->d_flags);
@@ -624,7 +629,7 @@ int qgru_forward_f32(qgru_handle *h, int T, int B, const float *x, const float *
         CK(cudaGetLastError());
         return QGRU_OK;
     }
-    if ((rc = ensure(h, h->x8, (size_t)N * h->Ipad))) return rc;
+    if ((rc = ensure(h, h->x8, (size_t)((N + 127) / 128 * 128) * h->Ipad))) return rc;
     if ((rc = ensure(h, h->h8, (size_t)2 * B * h->Hpad))) return rc;
     k_quantize_rows_f32<<<grid_for(N * (h->Ipad / 4), 256, h->sm_count), 256, 0, st>>>(
         x, (uint8_t *)h->x8.p, x_q_out, N, h->I, h->Ipad, h->x_scale, xo.zero_point, op_qmin(xo), op_qmax(xo));

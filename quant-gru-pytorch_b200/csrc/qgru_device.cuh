@@ -1,0 +1,87 @@
+// qgru_device.cuh - __device__ building blocks shared by every kernel file: dp4a wrappers,
+// the gate datapath and the fused-linear epilogue.  Only inline device functions live here,
+// so any translation unit may include it.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "qgru_internal.h"
+
+namespace qgru {
+
+// ------------------------------------------------------------------ small helpers
+
+__device__ __forceinline__ int dp4a_ss(int a, int b, int c) { return __dp4a(a, b, c); }
+// a: four signed bytes, b: four unsigned bytes
+__device__ __forceinline__ int dp4a_su(int a, unsigned b, int c) {
+    int d;
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+template <bool BUnsigned>
+__device__ __forceinline__ int dp4a_w(int w, unsigned act, int c) {
+    if constexpr (BUnsigned) return dp4a_su(w, act, c);
+    else return dp4a_ss(w, (int)act, c);
+}
+
+__device__ __forceinline__ unsigned ld_acquire(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// ------------------------------------------------------------ gate datapath (a4-a8)
+
+// piecewise_linear with its two clamps (include/quantize_ops_helper.h:600-606).  Where the
+// gate input is narrow enough the host tabulated the function over the whole clamped input
+// range; the table holds exactly the values the segment evaluation produces.
+__device__ __forceinline__ int32_t activation(const GateConsts &gc, const int32_t *tables,
+                                              int which, int32_t pre) {
+    const int32_t q = clampi(pre, gc.in_lo[which], gc.in_hi[which]);
+    if (gc.table_size[which] > 0) return tables[gc.table_off[which] + (q - gc.in_lo[which])];
+    return clampi(lut_raw(gc.lut[which], q), gc.out_lo[which], gc.out_hi[which]);
+}
+
+template <bool Narrow>
+__device__ __forceinline__ int32_t rescale_diff(int32_t v, int32_t zp, Rescale r) {
+    if constexpr (Narrow) return rescale_narrow(v - zp, r);
+    else return (int32_t)rescale64((int64_t)v - (int64_t)zp, r);
+}
+
+// computeUpdateGate / computeResetGate / computeNewGate / computeHiddenState, inference
+// branch (include/quantize_ops_helper.h:749-1084).  ih_* and hh_* are the clamped outputs of
+// the two fused linear layers; h_old is the quantized previous state.
+template <bool Narrow>
+__device__ __forceinline__ int32_t gru_cell(const GateConsts &gc, const int32_t *tables,
+                                            int32_t ih_z, int32_t ih_r, int32_t ih_n,
+                                            int32_t hh_z, int32_t hh_r, int32_t hh_n,
+                                            int32_t h_old) {
+    const int32_t z_pre = rescale_diff<Narrow>(ih_z, gc.zp_ih, gc.ih_to[ACT_Z]) +
+                          rescale_diff<Narrow>(hh_z, gc.zp_hh, gc.hh_to[ACT_Z]) + gc.zp_in[ACT_Z];
+    const int32_t z = activation(gc, tables, ACT_Z, z_pre);
+    const int32_t r_pre = rescale_diff<Narrow>(ih_r, gc.zp_ih, gc.ih_to[ACT_R]) +
+                          rescale_diff<Narrow>(hh_r, gc.zp_hh, gc.hh_to[ACT_R]) + gc.zp_in[ACT_R];
+    const int32_t r = activation(gc, tables, ACT_R, r_pre);
+
+    const int64_t r_hh = ((int64_t)r - gc.zp_out[ACT_R]) * ((int64_t)hh_n - gc.zp_hh);
+    const int32_t n_pre = rescale_diff<Narrow>(ih_n, gc.zp_ih, gc.ih_to[ACT_N]) +
+                          (int32_t)rescale64(r_hh, gc.rh_to_n) + gc.zp_in[ACT_N];
+    const int32_t n = activation(gc, tables, ACT_N, n_pre);
+
+    const int32_t n_h = rescale_diff<Narrow>(n, gc.zp_out[ACT_N], gc.n_to_h) + gc.zp_h;
+    const int64_t z_d = (int64_t)z - gc.zp_out[ACT_Z];
+    const int64_t old_c = z_d * ((int64_t)h_old - gc.zp_h);
+    const int64_t one_minus = ((int64_t)gc.one_q - z) - gc.zp_out[ACT_Z];
+    const int64_t new_c = one_minus * ((int64_t)n_h - gc.zp_h);
+    const int32_t h_new = (int32_t)rescale64(old_c + new_c, gc.uh_to_h) + gc.zp_h;
+    return clampi(h_new, gc.h_lo, gc.h_hi);
+}
+
+// Epilogue of a fused linear layer (src/gru_forward_cpu_quant.cc:130-138).
+__device__ __forceinline__ int32_t linear_epilogue(int64_t acc, int64_t corr, Rescale rs,
+                                                   int32_t zp_out, int32_t lo, int32_t hi) {
+    const int32_t v = (int32_t)rescale64(acc + corr, rs) + zp_out;
+    return clampi(v, lo, hi);
+}
+
+}  // namespace qgru

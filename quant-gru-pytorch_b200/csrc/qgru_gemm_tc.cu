@@ -1,8 +1,211 @@
+// qgru_gemm_tc.cu - the input projection W*x + bw for all timesteps as one int8 tensor-core
+// GEMM (tcgen05.mma kind::i8, TMA-fed, int32 accumulators in tensor memory) with the
+// zero-point / bias correction and the requantization fused into its epilogue.  Replaces the
+// reference's quantizedGemmBiasFused launch of ComputeLinearX
+// (src/gru_forward_gpu_quant.cu:110-180, 527-562), which multiplies int32 operands on CUDA
+// cores with 64-bit accumulation.
+//
+// Tile: 128 output channels (TMEM lanes) x 128 tokens (TMEM columns); K streamed in 128-byte
+// slabs through a 3-stage shared-memory ring.  Warp roles: warp 0 issues the TMA loads, warp 1
+// owns tensor memory and issues the MMAs, warps 2-5 run the epilogue (one TMEM lane = one
+// output channel per thread, so each thread keeps its channel's constants in registers and a
+// warp's stores cover 32 consecutive channels of a token).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
 #include "qgru_gemm_tc.cuh"
+#include "qgru_device.cuh"
+#include "qgru_tc.cuh"
+
 namespace qgru {
-int tc_gemm_launch(TcGemmState &, int, int, const uint8_t *, const int8_t *, void *, long long, int,
-                   int, bool, int, LinearConsts, cudaStream_t, std::string *err) {
-    if (err) *err = "tcgen05 GEMM not built";
-    return QGRU_ERR_UNSUPPORTED;
+
+EncodeTiledFn get_encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        else
+            cudaGetLastError();
+    });
+    return fn;
 }
+
+bool make_map_u8_sw128(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes,
+                       uint32_t box_rows) {
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {128, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+namespace {
+
+constexpr int GM = 128;      // channels per tile
+constexpr int GN = 128;      // tokens per tile
+constexpr int KB = 128;      // K bytes per stage
+constexpr int STAGES = 3;
+constexpr int STAGE_BYTES = (GM + GN) * KB;
+constexpr long long WAIT_BUDGET = 2000000000ll;  // ~1 s of SM clocks
+constexpr size_t GEMM_SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+
+template <bool XUnsigned, typename IhT>
+__global__ void __launch_bounds__(192, 1)
+k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+             IhT *__restrict__ ih, long long N, int C, int Kpad, LinearConsts lc, int *abort_flag) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *tiles = reinterpret_cast<unsigned char *>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tiles + (size_t)STAGES * STAGE_BYTES);
+    uint64_t *full = bars, *empty = bars + STAGES, *acc_full = bars + 2 * STAGES;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 1);
+    int *failed = reinterpret_cast<int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * GM;
+    const long long n0 = (long long)blockIdx.y * GN;
+    const int num_kb = Kpad / KB;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            tc::mbar_init(&full[s], 1);
+            tc::mbar_init(&empty[s], 1);
+        }
+        tc::mbar_init(acc_full, 1);
+        *failed = 0;
+        tc::fence_barrier_init();
+        tc::tma_prefetch_desc(&map_w);
+        tc::tma_prefetch_desc(&map_x);
+    }
+    if (warp == 1) tc::tmem_alloc(tmem_slot, GN);
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!tc::mbar_wait(&empty[s], ph ^ 1, WAIT_BUDGET)) { atomicExch(failed, 1); break; }
+                unsigned char *a = tiles + (size_t)s * STAGE_BYTES;
+                tc::mbar_expect_tx(&full[s], STAGE_BYTES);
+                tc::tma_load_2d(a, &map_w, &full[s], kb * KB, m0);
+                tc::tma_load_2d(a + GM * KB, &map_x, &full[s], kb * KB, (int)n0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = tc::idesc_i8(GM, GN, true, !XUnsigned);
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!tc::mbar_wait(&full[s], ph, WAIT_BUDGET)) { atomicExch(failed, 1); ok = false; break; }
+                tc::tc_fence_after_sync();
+                const uint32_t a_addr = tc::smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                const uint64_t a_desc = tc::smem_desc_sw128(a_addr);
+                const uint64_t b_desc = tc::smem_desc_sw128(a_addr + GM * KB);
+#pragma unroll
+                for (int ks = 0; ks < KB / 32; ++ks)
+                    tc::mma_i8(tmem_base, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (kb | ks) != 0);
+                tc::mma_commit(&empty[s]);
+            }
+            tc::mma_commit(acc_full);
+        }
+    } else {
+        const int q = warp & 3;                     // TMEM lane quadrant of this warp
+        const int m = m0 + q * 32 + lane;
+        const bool m_ok = m < C;
+        const int64_t corr = m_ok ? lc.corr[m] : 0;
+        const Rescale rs = m_ok ? lc.rs[m] : Rescale{1, 1};
+        const bool ready = tc::mbar_wait(acc_full, 0, WAIT_BUDGET);
+        if (!ready && lane == 0) atomicExch(failed, 1);
+        tc::tc_fence_after_sync();
+        if (ready) {
+            for (int c0 = 0; c0 < GN; c0 += 16) {
+                int32_t v[16];
+                tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const long long n = n0 + c0 + i;
+                    if (m_ok && n < N)
+                        ih[n * C + m] = (IhT)linear_epilogue(v[i], corr, rs, lc.zp_out, lc.lo, lc.hi);
+                }
+            }
+        }
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0 && *failed) atomicOr(abort_flag, 2);
+    if (warp == 1) tc::tmem_dealloc(tmem_base, GN);
+}
+
+template <bool XU, typename IhT>
+cudaError_t launch(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long long N, int C, int Kpad,
+                   LinearConsts lc, int *abort_flag, cudaStream_t st) {
+    auto kern = k_gemm_wx_tc<XU, IhT>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
+    if (e != cudaSuccess) return e;
+    dim3 grid((unsigned)((C + GM - 1) / GM), (unsigned)((N + GN - 1) / GN));
+    kern<<<grid, 192, GEMM_SMEM, st>>>(mw, mx, (IhT *)ih, N, C, Kpad, lc, abort_flag);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+int tc_gemm_launch(TcGemmState &s, const uint8_t *x8, long long x_rows_alloc, const int8_t *w8,
+                   long long w_rows_alloc, void *ih, long long N, int C, int Kpad, bool x_unsigned,
+                   int ih_bytes, LinearConsts lc, int *abort_flag, cudaStream_t stream, std::string *err) {
+    if (Kpad % KB != 0 || x_rows_alloc < (N + GN - 1) / GN * GN || w_rows_alloc < (C + GM - 1) / GM * GM) {
+        if (err) *err = "tcgen05 GEMM needs K padded to 128 and operand rows padded to the tile";
+        return QGRU_ERR_UNSUPPORTED;
+    }
+    if ((N + GN - 1) / GN > 65535) {
+        if (err) *err = "too many token tiles for one launch";
+        return QGRU_ERR_UNSUPPORTED;
+    }
+    if (!s.valid || s.x8 != x8 || s.w8 != w8 || s.x_rows != x_rows_alloc || s.w_rows != w_rows_alloc ||
+        s.Kpad != Kpad) {
+        static_assert(sizeof(CUtensorMap) <= sizeof(s.map_w), "tensor map storage too small");
+        if (!make_map_u8_sw128(reinterpret_cast<CUtensorMap *>(s.map_w), w8, (uint64_t)w_rows_alloc, (uint64_t)Kpad, GM) ||
+            !make_map_u8_sw128(reinterpret_cast<CUtensorMap *>(s.map_x), x8, (uint64_t)x_rows_alloc, (uint64_t)Kpad, GN)) {
+            if (err) *err = "cuTensorMapEncodeTiled failed";
+            return QGRU_ERR_CUDA;
+        }
+        s.valid = true;
+        s.x8 = x8;
+        s.w8 = w8;
+        s.x_rows = x_rows_alloc;
+        s.w_rows = w_rows_alloc;
+        s.Kpad = Kpad;
+    }
+    const CUtensorMap &mw = *reinterpret_cast<const CUtensorMap *>(s.map_w);
+    const CUtensorMap &mx = *reinterpret_cast<const CUtensorMap *>(s.map_x);
+    cudaError_t e;
+    if (ih_bytes == 1)
+        e = x_unsigned ? launch<true, int8_t>(mw, mx, ih, N, C, Kpad, lc, abort_flag, stream)
+                       : launch<false, int8_t>(mw, mx, ih, N, C, Kpad, lc, abort_flag, stream);
+    else
+        e = x_unsigned ? launch<true, int16_t>(mw, mx, ih, N, C, Kpad, lc, abort_flag, stream)
+                       : launch<false, int16_t>(mw, mx, ih, N, C, Kpad, lc, abort_flag, stream);
+    if (e != cudaSuccess) {
+        if (err) *err = std::string("tcgen05 GEMM launch: ") + cudaGetErrorString(e);
+        return QGRU_ERR_CUDA;
+    }
+    return QGRU_OK;
+}
+
 }  // namespace qgru

@@ -1,4 +1,4 @@
-// qgru_gemm_tc.cuh - input projection on the 5th-generation tensor cores (tcgen05, kind::i8).
+// qgru_gemm_tc.cuh - launch interface of the tcgen05 input-projection GEMM (qgru_gemm_tc.cu).
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -9,12 +9,22 @@
 
 namespace qgru {
 
+// Cached tensor maps of the two operands (opaque 128-byte CUtensorMap objects).
 struct TcGemmState {
     bool valid = false;
+    const void *x8 = nullptr, *w8 = nullptr;
+    long long x_rows = 0, w_rows = 0;
+    int Kpad = 0;
+    alignas(64) unsigned char map_w[128];
+    alignas(64) unsigned char map_x[128];
 };
 
-int tc_gemm_launch(TcGemmState &st, int device, int sm_count, const uint8_t *x8, const int8_t *w8,
-                   void *ih, long long N, int C, int Kpad, bool x_unsigned, int ih_bytes,
-                   LinearConsts lc, cudaStream_t stream, std::string *err);
+// ih[n][m] = requant( sum_k w8[m][k] * x8[n][k] ) for n < N tokens, m < C channels.
+// Both operands are [rows][Kpad] bytes with Kpad a multiple of 128 and rows ALLOCATED up to a
+// multiple of 128 (x_rows_alloc, w_rows_alloc) so that no tile load leaves the allocation.
+// Returns QGRU_ERR_UNSUPPORTED when the shapes do not meet that, QGRU_ERR_CUDA on failure.
+int tc_gemm_launch(TcGemmState &st, const uint8_t *x8, long long x_rows_alloc, const int8_t *w8,
+                   long long w_rows_alloc, void *ih, long long N, int C, int Kpad, bool x_unsigned,
+                   int ih_bytes, LinearConsts lc, int *abort_flag, cudaStream_t stream, std::string *err);
 
 }  // namespace qgru

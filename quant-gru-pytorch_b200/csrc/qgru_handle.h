@@ -48,7 +48,8 @@ struct qgru_handle {
     int64_t *d_corr[2] = {nullptr, nullptr};
     int32_t *d_wq[4] = {nullptr, nullptr, nullptr, nullptr};  // W_q, R_q, bw_q, br_q
     int32_t *d_wsum[2] = {nullptr, nullptr};
-    int8_t *d_w8[2] = {nullptr, nullptr};     // W8 [3H][Ipad], R8 [3H][Hpad]
+    int8_t *d_w8[2] = {nullptr, nullptr};     // W8 [3H][Ipad], R8 [3H][Hpad] (rows over-allocated)
+    long long w8_rows[2] = {0, 0};
     int *d_flags = nullptr;                   // [0] data errors, [1] barrier abort
     int *h_flags = nullptr;                   // pinned mirror
     unsigned *d_bar = nullptr;
