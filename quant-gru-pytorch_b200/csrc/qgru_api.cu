@@ -14,6 +14,7 @@
 
 #include "qgru_handle.h"
 #include "qgru_kernels.cuh"
+#include "qgru_rec_mma.cuh"
 
 using namespace qgru;
 
@@ -149,8 +150,9 @@ int qgru_set_option(qgru_handle *h, const char *name, const char *value) {
     } else if (n == "rec") {
         if (v == "auto") h->opt_rec = 0;
         else if (v == "dp4a") h->opt_rec = 1;
+        else if (v == "mma") h->opt_rec = 2;
         else if (v == "generic") h->opt_rec = 3;
-        else return fail(h, QGRU_ERR_BAD_ARG, "rec: auto|dp4a|generic");
+        else return fail(h, QGRU_ERR_BAD_ARG, "rec: auto|dp4a|mma|generic");
     } else if (n == "sm_limit") {
         h->opt_sm_limit = std::max(0, atoi(value));
     } else if (n == "spin_limit") {
@@ -342,6 +344,7 @@ int finish_weights(qgru_handle *h, cudaStream_t st) {
     if (h->fast && (h->h_flags[0] & 2))
         return fail(h, QGRU_ERR_BAD_ARG, "quantized weight outside the 8-bit range its operator declares");
     h->tc.valid = false;
+    h->rec.valid = false;
     h->weights_set = true;
     return QGRU_OK;
 }
@@ -477,37 +480,73 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
     }
     CK(cudaEventRecord(h->ev[2], st));
 
+    const int sms = h->opt_sm_limit > 0 ? std::min(h->opt_sm_limit, h->sm_count) : h->sm_count;
     RecPlan pl;
-    if (!plan_recurrence(h, B, &pl)) return fail(h, QGRU_ERR_UNSUPPORTED, "no recurrence plan fits shared memory");
-    if (pl.G > h->bar_groups) {
-        if ((rc = alloc_dev(h, &h->d_bar, (size_t)pl.G * 32))) return rc;
-        h->bar_groups = pl.G;
+    const bool dp4a_ok = plan_recurrence(h, B, &pl);
+    RecMmaPlan mp;
+    const bool mma_ok = h->opt_rec != 1 && rec_mma_plan(h->H, h->Hpad, B, sms, h->smem_optin, h->n_table, &mp);
+    if (h->opt_rec == 2 && !mma_ok) return fail(h, QGRU_ERR_UNSUPPORTED, "tensor-core recurrence needs H <= 512");
+    // Tiny batches whose R fits one SM run barrier-free on one CTA per batch row: lower latency
+    // than tensor-core tiles of 16 batch columns.
+    const bool use_mma = mma_ok && (h->opt_rec == 2 || !(dp4a_ok && pl.P == 1 && B <= 4));
+    if (!use_mma && !dp4a_ok) return fail(h, QGRU_ERR_UNSUPPORTED, "no recurrence plan fits shared memory");
+    const int groups = use_mma ? mp.G : pl.G;
+    if (groups > h->bar_groups) {
+        if ((rc = alloc_dev(h, &h->d_bar, (size_t)groups * 32))) return rc;
+        h->bar_groups = groups;
     }
-    CK(cudaMemsetAsync(h->d_bar, 0, (size_t)pl.G * 32 * sizeof(unsigned), st));
-    RecArgs a;
-    a.T = T; a.B = B; a.H = h->H; a.Hpad = h->Hpad; a.C = C;
-    a.Hs = pl.Hs; a.Bt = pl.Bt; a.P = pl.P;
-    a.reverse = (flags & QGRU_FLAG_REVERSE) ? 1 : 0;
-    a.r8 = h->d_w8[1];
-    a.ih = h->ih.p;
-    a.h8 = (uint8_t *)h->h8.p;
-    a.hq_out = hq_out;
-    a.hf_out = hf_out;
-    a.lc = linear_consts(h, 1);
-    a.gc = h->d_gc;
-    a.tables = h->d_tables;
-    a.n_table = h->n_table;
-    a.bar = h->d_bar;
-    a.abort_flag = h->d_flags + 1;
-    a.spin_limit = h->spin_limit;
-    if (h->ih_bytes == 1) rc = h->h_uns ? launch_rec<true, int8_t>(h, a, pl, st) : launch_rec<false, int8_t>(h, a, pl, st);
-    else rc = h->h_uns ? launch_rec<true, int16_t>(h, a, pl, st) : launch_rec<false, int16_t>(h, a, pl, st);
-    if (rc) return rc;
+    CK(cudaMemsetAsync(h->d_bar, 0, (size_t)groups * 32 * sizeof(unsigned), st));
+    char buf[320];
+    if (use_mma) {
+        RecMmaArgs a;
+        a.T = T; a.B = B; a.H = h->H; a.Hpad = h->Hpad; a.C = C;
+        a.P = mp.P; a.NB = mp.NB; a.b_off = 0; a.b_cnt = B;
+        a.reverse = (flags & QGRU_FLAG_REVERSE) ? 1 : 0;
+        a.tmem_cols = (uint32_t)mp.tmem_cols;
+        a.ih = h->ih.p;
+        a.h8 = (uint8_t *)h->h8.p;
+        a.hq_out = hq_out;
+        a.hf_out = hf_out;
+        a.lc = linear_consts(h, 1);
+        a.gc = h->d_gc;
+        a.tables = h->d_tables;
+        a.n_table = h->n_table;
+        a.bar = h->d_bar;
+        a.abort_flag = h->d_flags + 1;
+        a.spin_limit = h->spin_limit;
+        const unsigned long long before = h->rec.launches;
+        rc = rec_mma_launch(h->rec, mp, a, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256, h->h_uns,
+                            h->ih_bytes, h->gc_host.narrow != 0, h->coop != 0, st, &h->err);
+        if (rc) return rc;
+        h->launches += h->rec.launches - before;
+        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 MT=%d NB=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d narrow=%d ih_bytes=%d",
+                 used_tc ? "tcgen05_i8" : "simt_dp4a", mp.MT, mp.NB, mp.P, mp.G, mp.groups_per_launch, mp.smem,
+                 mp.tmem_cols, h->gc_host.narrow, h->ih_bytes);
+    } else {
+        RecArgs a;
+        a.T = T; a.B = B; a.H = h->H; a.Hpad = h->Hpad; a.C = C;
+        a.Hs = pl.Hs; a.Bt = pl.Bt; a.P = pl.P;
+        a.reverse = (flags & QGRU_FLAG_REVERSE) ? 1 : 0;
+        a.r8 = h->d_w8[1];
+        a.ih = h->ih.p;
+        a.h8 = (uint8_t *)h->h8.p;
+        a.hq_out = hq_out;
+        a.hf_out = hf_out;
+        a.lc = linear_consts(h, 1);
+        a.gc = h->d_gc;
+        a.tables = h->d_tables;
+        a.n_table = h->n_table;
+        a.bar = h->d_bar;
+        a.abort_flag = h->d_flags + 1;
+        a.spin_limit = h->spin_limit;
+        if (h->ih_bytes == 1) rc = h->h_uns ? launch_rec<true, int8_t>(h, a, pl, st) : launch_rec<false, int8_t>(h, a, pl, st);
+        else rc = h->h_uns ? launch_rec<true, int16_t>(h, a, pl, st) : launch_rec<false, int16_t>(h, a, pl, st);
+        if (rc) return rc;
+        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=dp4a Hs=%d Bt=%d P=%d G=%d smem=%zu narrow=%d ih_bytes=%d",
+                 used_tc ? "tcgen05_i8" : "simt_dp4a", pl.Hs, pl.Bt, pl.P, pl.G, pl.smem, h->gc_host.narrow, h->ih_bytes);
+    }
     CK(cudaEventRecord(h->ev[3], st));
     h->timing_valid = true;
-    char buf[256];
-    snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=dp4a Hs=%d Bt=%d P=%d G=%d smem=%zu narrow=%d ih_bytes=%d",
-             used_tc ? "tcgen05_i8" : "simt_dp4a", pl.Hs, pl.Bt, pl.P, pl.G, pl.smem, h->gc_host.narrow, h->ih_bytes);
     h->plan_text = buf;
     return QGRU_OK;
 }
@@ -582,10 +621,10 @@ int qgru_forward_i32(qgru_handle *h, int T, int B, const int32_t *x_q, const int
         return run_generic(h, T, B, x_q, h_q, flags, st);
     }
     if ((rc = ensure(h, h->x8, (size_t)((N + 127) / 128 * 128) * h->Ipad))) return rc;
-    if ((rc = ensure(h, h->h8, (size_t)2 * B * h->Hpad))) return rc;
+    if ((rc = ensure(h, h->h8, (size_t)(2 * B + 256) * h->Hpad))) return rc;
     k_narrow_rows_i32<<<grid_for(N * (h->Ipad / 4), 256, h->sm_count), 256, 0, st>>>(
         x_q, (uint8_t *)h->x8.p, N, h->I, h->Ipad, op_qmin(xo), op_qmax(xo), h->d_flags);
-    CK(cudaMemsetAsync(h->h8.p, 0, (size_t)2 * B * h->Hpad, st));
+    CK(cudaMemsetAsync(h->h8.p, 0, (size_t)(2 * B + 256) * h->Hpad, st));
     k_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
         h0_q, nullptr, (uint8_t *)h->h8.p, h_q, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale,
         ho.zero_point, op_qmin(ho), op_qmax(ho), h->d_flags);
@@ -630,10 +669,10 @@ int qgru_forward_f32(qgru_handle *h, int T, int B, const float *x, const float *
         return QGRU_OK;
     }
     if ((rc = ensure(h, h->x8, (size_t)((N + 127) / 128 * 128) * h->Ipad))) return rc;
-    if ((rc = ensure(h, h->h8, (size_t)2 * B * h->Hpad))) return rc;
+    if ((rc = ensure(h, h->h8, (size_t)(2 * B + 256) * h->Hpad))) return rc;
     k_quantize_rows_f32<<<grid_for(N * (h->Ipad / 4), 256, h->sm_count), 256, 0, st>>>(
         x, (uint8_t *)h->x8.p, x_q_out, N, h->I, h->Ipad, h->x_scale, xo.zero_point, op_qmin(xo), op_qmax(xo));
-    CK(cudaMemsetAsync(h->h8.p, 0, (size_t)2 * B * h->Hpad, st));
+    CK(cudaMemsetAsync(h->h8.p, 0, (size_t)(2 * B + 256) * h->Hpad, st));
     k_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
         nullptr, h0, (uint8_t *)h->h8.p, nullptr, h_out, B, h->H, h->Hpad, init_slot, h->h_scale,
         ho.zero_point, op_qmin(ho), op_qmax(ho), h->d_flags);

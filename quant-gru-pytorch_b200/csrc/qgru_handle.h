@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "qgru_gemm_tc.cuh"
+#include "qgru_rec_mma.cuh"
 #include "qgru_internal.h"
 
 using qgru::GateConsts;
@@ -64,6 +65,7 @@ struct qgru_handle {
     bool timing_valid = false;
     uint64_t launches = 0;
     TcGemmState tc;
+    qgru::RecMmaState rec;
 };
 
 #define CK(call)                                                                          \

@@ -1,0 +1,57 @@
+// qgru_rec_mma.cuh - plan and launch interface of the tensor-core recurrence kernel
+// (qgru_rec_mma.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <algorithm>
+#include <string>
+
+#include "qgru_internal.h"
+
+namespace qgru {
+
+struct RecMmaArgs {
+    int T, B, H, Hpad, C;
+    int P;            // CTAs per group (slices of the hidden dimension); set by the launcher
+    int NB;           // batch rows per group (multiple of 16); set by the launcher
+    int b_off, b_cnt; // batch rows [b_off, b_off + b_cnt) are handled by this launch
+    int reverse;
+    uint32_t tmem_cols;
+    const void *ih;         // [T*B][3H] int8 or int16
+    uint8_t *h8;            // [2][B][Hpad] ping-pong state (+ slack rows)
+    int32_t *hq_out;        // [(T+1)][B][H] or null
+    float *hf_out;          // [(T+1)][B][H] or null
+    LinearConsts lc;        // R*h + br epilogue
+    const GateConsts *gc;
+    const int32_t *tables;
+    int n_table;
+    unsigned *bar;          // one counter per group, 32 words apart, zeroed before the launch
+    int *abort_flag;
+    unsigned spin_limit;
+};
+
+struct RecMmaPlan {
+    int MT = 1, P = 1, NB = 16, G = 1, tmem_cols = 32, groups_per_launch = 1;
+    size_t smem = 0;
+};
+
+struct RecMmaState {
+    bool valid = false;
+    const void *r8 = nullptr, *h8 = nullptr;
+    long long r_rows = 0, h_rows = 0;
+    int Hpad = 0, NB = 0;
+    unsigned long long launches = 0;
+    alignas(64) unsigned char map_r[128];
+    alignas(64) unsigned char map_h[128];
+};
+
+// False when the shape cannot use this kernel (the slice of R for 128 hidden units must fit
+// one SM's shared memory: H <= 512 with 8-bit weights).
+bool rec_mma_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, RecMmaPlan *out);
+
+int rec_mma_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const int8_t *r8, long long r_rows_alloc,
+                   long long h_rows_alloc, bool h_unsigned, int ih_bytes, bool narrow, bool have_coop,
+                   cudaStream_t stream, std::string *err);
+
+}  // namespace qgru

@@ -59,22 +59,45 @@ def _want(oracle, case):
                               case.params.scale_list())
 
 
+@pytest.mark.parametrize("rec", ["dp4a", "mma"])
 @pytest.mark.parametrize("shape", SHAPES)
-def test_shapes_default_config(oracle, cuda_device, shape):
+def test_shapes_default_config(oracle, cuda_device, shape, rec):
+    """Both recurrence kernels (dp4a and tcgen05) on every shape; the GEMM is tcgen05."""
     T, B, I, H = shape
     case = make_case(11, T, B, I, H, oracle, config_named("default"))
-    got, plan, launches = _run(case, cuda_device)
+    got, plan, launches = _run(case, cuda_device, opts=(("rec", rec),))
     assert "path=int8" in plan and launches > 0
+    assert ("rec=tcgen05_i8" in plan) == (rec == "mma") and "gemm=tcgen05_i8" in plan
     assert np.array_equal(got, _want(oracle, case)), plan
+
+
+def test_simt_gemm_and_wide_hidden_fallback(oracle, cuda_device):
+    """The SIMT GEMM stays available (option), and H > 512 runs on the dp4a recurrence."""
+    case = make_case(12, 5, 9, 72, 136, oracle, config_named("cfg2"))
+    got, plan, _ = _run(case, cuda_device, opts=(("gemm", "simt"),))
+    assert "gemm=simt_dp4a" in plan and np.array_equal(got, _want(oracle, case))
+    wide = make_case(13, 3, 5, 40, 640, oracle, config_named("default"))
+    got, plan, _ = _run(wide, cuda_device)
+    assert "rec=dp4a" in plan and np.array_equal(got, _want(oracle, wide)), plan
+    with pytest.raises(Exception):
+        _run(wide, cuda_device, opts=(("rec", "mma"),))
+
+
+def test_large_batch_many_groups(oracle, cuda_device):
+    """More batch rows than one wave of groups holds at H = 512: consecutive launches."""
+    case = make_case(14, 3, 700, 32, 384, oracle, config_named("default"), calib_batches=1)
+    got, plan, _ = _run(case, cuda_device, opts=(("sm_limit", "12"),))
+    assert "rec=tcgen05_i8" in plan and np.array_equal(got, _want(oracle, case)), plan
 
 
 @pytest.mark.parametrize("name", CONFIGS)
 def test_bitwidth_configs(oracle, cuda_device, name):
     for seed, (T, B, I, H) in enumerate([(7, 6, 24, 48), (4, 9, 40, 72)]):
         case = make_case(20 + seed, T, B, I, H, oracle, config_named(name), with_h0=(seed == 1))
-        got, plan, _ = _run(case, cuda_device)
-        assert "path=int8" in plan
-        assert np.array_equal(got, _want(oracle, case)), (name, plan)
+        for rec in ("mma", "dp4a"):
+            got, plan, _ = _run(case, cuda_device, opts=(("rec", rec),))
+            assert "path=int8" in plan
+            assert np.array_equal(got, _want(oracle, case)), (name, plan)
 
 
 @pytest.mark.parametrize("name", ["wide16", "default", "cfg2"])
