@@ -50,6 +50,10 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--calib-batches", type=int, default=0,
+                    help="override the number of calibration batches (profiling runs only)")
+    ap.add_argument("--rows", type=int, default=0,
+                    help="override the batch rows per GPU-unit (small profiling cases only)")
     return ap.parse_args()
 
 
@@ -140,6 +144,10 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     I, H, B_unit, T, bidir, cfg_name, xdist, n_calib = WORKLOADS[args.workload]
+    if args.calib_batches > 0:
+        n_calib = args.calib_batches
+    if args.rows > 0:
+        B_unit = args.rows
     B_global = B_unit * world
     shards = sharding.plan_shards(world, B_global, bidir)
     me = shards[rank]
@@ -256,7 +264,7 @@ def run_ours(args):
                        "l2": "inputs larger than L2: x, W*x+bw and the fp32 outputs of one step "
                              f"total {(rows * T * bytes_per_token(I, H, ih_bytes) * len(handles)) / 1e6:.0f} MB > 126 MB",
                        "plan": plan},
-            "roofline": {"bound": "hbm", "kernel": "k_recurrence_dp4a (one direction)", "achieved": achieved,
+            "roofline": {"bound": "hbm", "kernel": ("k_recurrence_mma" if "rec=tcgen05" in plan else "k_recurrence_dp4a") + " (one direction)", "achieved": achieved,
                          "peak": hbm, "unit": "GB/s", "frac": achieved / hbm, "peak_kind": peak_kind,
                          "traffic": None, "us_per_timestep": rec_ms * 1e3 / T,
                          "input_gemm_ms": gemm_ms, "recurrence_ms": rec_ms,

@@ -111,6 +111,7 @@ void qgru_destroy(qgru_handle *h) {
     cudaDeviceSynchronize();
     cudaFree(h->d_gc);
     cudaFree(h->d_tables);
+    cudaFree(h->d_ftables);
     for (int i = 0; i < 2; ++i) {
         cudaFree(h->d_rs[i]);
         cudaFree(h->d_brs[i]);
@@ -153,6 +154,13 @@ int qgru_set_option(qgru_handle *h, const char *name, const char *value) {
         else if (v == "mma") h->opt_rec = 2;
         else if (v == "generic") h->opt_rec = 3;
         else return fail(h, QGRU_ERR_BAD_ARG, "rec: auto|dp4a|mma|generic");
+    } else if (n == "cell") {
+        if (v == "auto") h->opt_cell = 0;
+        else if (v == "generic") h->opt_cell = 1;
+        else return fail(h, QGRU_ERR_BAD_ARG, "cell: auto|generic");
+    } else if (n == "debug_stamps") {
+        // address (decimal) of a device buffer of T*8 int64 clock stamps, 0 to switch off
+        h->dbg_stamps = reinterpret_cast<long long *>(strtoull(value, nullptr, 10));
     } else if (n == "sm_limit") {
         h->opt_sm_limit = std::max(0, atoi(value));
     } else if (n == "spin_limit") {
@@ -274,6 +282,56 @@ int qgru_set_params(qgru_handle *h, const qgru_params *p, const float *scale_W,
     }
     h->n_table = (int)tables.size();
 
+    // Tables of the fused cell (gru_cell_fused): every entry is computed with the same host
+    // functions the kernels' generic path uses, so both forms give identical results.
+    std::vector<int32_t> ft;
+    {
+        bool fused = g.table_size[0] > 0 && g.table_size[1] > 0 && g.table_size[2] > 0 &&
+                     op[QGRU_OP_HH_LINEAR].bits <= 10 && op[QGRU_OP_IH_LINEAR].bits <= 16;
+        const auto resc = [](int64_t v, Rescale r) { return (int32_t)rescale64(v, r); };
+        int64_t max_zd = 0, max_omz = 0, max_rd = 0, max_nd = 0, max_pre = 0;
+        g.k1 = g.one_q - 2 * g.zp_out[ACT_Z];
+        if (fused) {
+            for (int a = 0; a < 3; ++a) {
+                g.ft_off[a] = (int32_t)ft.size();
+                for (int q = g.in_lo[a]; q <= g.in_hi[a]; ++q) {
+                    const int32_t y = lut_eval(p->lut[a], q, op[in_op[a]], op[out_op[a]]);
+                    if (a == ACT_N) {
+                        const int32_t nd = resc((int64_t)y - g.zp_out[ACT_N], g.n_to_h);
+                        max_nd = std::max<int64_t>(max_nd, std::llabs((long long)nd));
+                        ft.push_back(nd);
+                    } else {
+                        const int32_t d = y - g.zp_out[a];
+                        if (a == ACT_Z) {
+                            max_zd = std::max<int64_t>(max_zd, std::llabs((long long)d));
+                            max_omz = std::max<int64_t>(max_omz, std::llabs((long long)g.k1 - d));
+                        } else {
+                            max_rd = std::max<int64_t>(max_rd, std::llabs((long long)d));
+                        }
+                        ft.push_back(d);
+                    }
+                }
+            }
+            for (int a = 0; a < 2; ++a) {
+                g.ft_off[3 + a] = (int32_t)ft.size();
+                for (int v = g.hh_lo; v <= g.hh_hi; ++v) ft.push_back(resc((int64_t)v - g.zp_hh, g.hh_to[a]));
+            }
+            for (int a = 0; a < 3; ++a)
+                for (int64_t v = g.ih_lo; v <= g.ih_hi; v += std::max<int64_t>(1, ((int64_t)g.ih_hi - g.ih_lo))) {
+                    // rescale is monotone: the extremes of the range bound every value
+                    const int64_t y = (int64_t)resc(v - g.zp_ih, g.ih_to[a]) + g.zp_in[a];
+                    max_pre = std::max<int64_t>(max_pre, std::llabs((long long)y));
+                }
+            const int64_t max_hd = max_abs_diff(op[QGRU_OP_H]), max_hhd = max_abs_diff(op[QGRU_OP_HH_LINEAR]);
+            const int64_t lim = 0x7fffffffll;
+            if (max_zd * max_hd + max_omz * max_nd >= lim || max_rd * max_hhd >= lim || max_pre >= lim) fused = false;
+        }
+        g.fused_ok = fused ? 1 : 0;
+        g.ih_pre_bytes = max_pre < 32768 ? 2 : 4;
+        if (!fused) ft.clear();
+    }
+    h->n_ftable = (int)ft.size();
+
     // storage plan of the 8-bit path
     const auto fits8 = [](const qgru_op &o) { return o.bits <= 8; };
     h->x_uns = op[QGRU_OP_X].bits < 32 && op[QGRU_OP_X].is_unsigned;
@@ -289,6 +347,8 @@ int qgru_set_params(qgru_handle *h, const qgru_params *p, const float *scale_W,
     int rc;
     if ((rc = alloc_dev(h, &h->d_gc, 1))) return rc;
     if ((rc = alloc_dev(h, &h->d_tables, tables.size()))) return rc;
+    if ((rc = alloc_dev(h, &h->d_ftables, ft.size()))) return rc;
+    if (!ft.empty()) CK(cudaMemcpy(h->d_ftables, ft.data(), ft.size() * 4, cudaMemcpyHostToDevice));
     for (int s = 0; s < 2; ++s) {
         if ((rc = alloc_dev(h, &h->d_rs[s], C))) return rc;
         if ((rc = alloc_dev(h, &h->d_brs[s], C))) return rc;
@@ -334,15 +394,19 @@ int finish_weights(qgru_handle *h, cudaStream_t st) {
                                       h->Hpad, C, h->d_flags);
     const int gb = (C + 127) / 128;
     k_channel_consts<<<gb, 128, 0, st>>>(h->d_wq[2], h->d_brs[0], h->d_wsum[0],
-                                         h->p.op[QGRU_OP_X].zero_point, h->d_corr[0], C);
+                                         h->p.op[QGRU_OP_X].zero_point, h->d_corr[0], C,
+                                         (long long)h->I * 128 * 255, h->d_flags, 8);
     k_channel_consts<<<gb, 128, 0, st>>>(h->d_wq[3], h->d_brs[1], h->d_wsum[1],
-                                         h->p.op[QGRU_OP_H].zero_point, h->d_corr[1], C);
+                                         h->p.op[QGRU_OP_H].zero_point, h->d_corr[1], C,
+                                         (long long)h->H * 128 * 255, h->d_flags, 16);
     h->launches += 4;
     CK(cudaGetLastError());
     CK(cudaMemcpyAsync(h->h_flags, h->d_flags, 2 * sizeof(int), cudaMemcpyDeviceToHost, st));
     CK(cudaStreamSynchronize(st));
     if (h->fast && (h->h_flags[0] & 2))
         return fail(h, QGRU_ERR_BAD_ARG, "quantized weight outside the 8-bit range its operator declares");
+    h->lin_fits32[0] = !(h->h_flags[0] & 8);
+    h->lin_fits32[1] = !(h->h_flags[0] & 16);
     h->tc.valid = false;
     h->rec.valid = false;
     h->weights_set = true;
@@ -418,6 +482,7 @@ LinearConsts linear_consts(const qgru_handle *h, int side) {
     lc.zp_out = o.zero_point;
     lc.lo = op_qmin(o);
     lc.hi = op_qmax(o);
+    lc.fits32 = h->fast && h->lin_fits32[side] ? 1 : 0;
     return lc;
 }
 
@@ -450,18 +515,44 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
     const long long N = (long long)T * B;
     const int C = h->C;
     int rc;
-    if ((rc = ensure(h, h->ih, (size_t)N * C * h->ih_bytes))) return rc;
+
+    // ---- plan the recurrence first: it decides the form in which W*x+bw is stored
+    const int sms = h->opt_sm_limit > 0 ? std::min(h->opt_sm_limit, h->sm_count) : h->sm_count;
+    RecPlan pl;
+    const bool dp4a_ok = plan_recurrence(h, B, &pl);
+    RecMmaPlan mp;
+    const int n_tab_mma = std::max(h->n_table, h->n_ftable);
+    const bool mma_ok = h->opt_rec != 1 && rec_mma_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, &mp);
+    if (h->opt_rec == 2 && !mma_ok) return fail(h, QGRU_ERR_UNSUPPORTED, "tensor-core recurrence needs H <= 512");
+    // Tiny batches whose R fits one SM run barrier-free on one CTA per batch row: lower latency
+    // than tensor-core tiles of 16 batch columns.
+    const bool use_mma = mma_ok && (h->opt_rec == 2 || !(dp4a_ok && pl.P == 1 && B <= 4));
+    if (!use_mma && !dp4a_ok) return fail(h, QGRU_ERR_UNSUPPORTED, "no recurrence plan fits shared memory");
+    // the fused cell needs the GEMM epilogue to pre-rescale W*x+bw: tensor-core GEMM only
+    const bool fused = use_mma && h->gc_host.fused_ok && h->opt_gemm != 1 && h->opt_cell != 1;
+    const int ih_bytes = fused ? h->gc_host.ih_pre_bytes : h->ih_bytes;
+    PreScale ps{};
+    if (fused) {
+        ps.enabled = 1;
+        ps.H = h->H;
+        ps.zp_ih = h->gc_host.zp_ih;
+        for (int a = 0; a < 3; ++a) {
+            ps.to[a] = h->gc_host.ih_to[a];
+            ps.zp_in[a] = h->gc_host.zp_in[a];
+        }
+    }
+    if ((rc = ensure(h, h->ih, (size_t)N * C * ih_bytes))) return rc;
 
     CK(cudaEventRecord(h->ev[1], st));
     const LinearConsts lcx = linear_consts(h, 0);
     bool used_tc = false;
     if (h->opt_gemm != 1) {
         rc = tc_gemm_launch(h->tc, (const uint8_t *)h->x8.p, (N + 127) / 128 * 128, h->d_w8[0], h->w8_rows[0],
-                            h->ih.p, N, C, h->Ipad, h->x_uns, h->ih_bytes, lcx, h->d_flags + 1, st, &h->err);
+                            h->ih.p, N, C, h->Ipad, h->x_uns, ih_bytes, lcx, ps, h->d_flags + 1, st, &h->err);
         if (rc == QGRU_OK) {
             used_tc = true;
             h->launches++;
-        } else if (rc != QGRU_ERR_UNSUPPORTED || h->opt_gemm == 2) {
+        } else if (rc != QGRU_ERR_UNSUPPORTED || h->opt_gemm == 2 || fused) {
             return rc;
         }
     }
@@ -480,16 +571,6 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
     }
     CK(cudaEventRecord(h->ev[2], st));
 
-    const int sms = h->opt_sm_limit > 0 ? std::min(h->opt_sm_limit, h->sm_count) : h->sm_count;
-    RecPlan pl;
-    const bool dp4a_ok = plan_recurrence(h, B, &pl);
-    RecMmaPlan mp;
-    const bool mma_ok = h->opt_rec != 1 && rec_mma_plan(h->H, h->Hpad, B, sms, h->smem_optin, h->n_table, &mp);
-    if (h->opt_rec == 2 && !mma_ok) return fail(h, QGRU_ERR_UNSUPPORTED, "tensor-core recurrence needs H <= 512");
-    // Tiny batches whose R fits one SM run barrier-free on one CTA per batch row: lower latency
-    // than tensor-core tiles of 16 batch columns.
-    const bool use_mma = mma_ok && (h->opt_rec == 2 || !(dp4a_ok && pl.P == 1 && B <= 4));
-    if (!use_mma && !dp4a_ok) return fail(h, QGRU_ERR_UNSUPPORTED, "no recurrence plan fits shared memory");
     const int groups = use_mma ? mp.G : pl.G;
     if (groups > h->bar_groups) {
         if ((rc = alloc_dev(h, &h->d_bar, (size_t)groups * 32))) return rc;
@@ -508,20 +589,20 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
         a.hq_out = hq_out;
         a.hf_out = hf_out;
         a.lc = linear_consts(h, 1);
-        a.gc = h->d_gc;
-        a.tables = h->d_tables;
-        a.n_table = h->n_table;
+        a.tables = fused ? h->d_ftables : h->d_tables;
+        a.n_table = fused ? h->n_ftable : h->n_table;
         a.bar = h->d_bar;
         a.abort_flag = h->d_flags + 1;
         a.spin_limit = h->spin_limit;
+        a.dbg = h->dbg_stamps;
         const unsigned long long before = h->rec.launches;
-        rc = rec_mma_launch(h->rec, mp, a, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256, h->h_uns,
-                            h->ih_bytes, h->gc_host.narrow != 0, h->coop != 0, st, &h->err);
+        rc = rec_mma_launch(h->rec, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256, h->h_uns,
+                            ih_bytes, h->gc_host.narrow != 0, fused, h->coop != 0, st, &h->err);
         if (rc) return rc;
         h->launches += h->rec.launches - before;
-        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 MT=%d NB=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d narrow=%d ih_bytes=%d",
-                 used_tc ? "tcgen05_i8" : "simt_dp4a", mp.MT, mp.NB, mp.P, mp.G, mp.groups_per_launch, mp.smem,
-                 mp.tmem_cols, h->gc_host.narrow, h->ih_bytes);
+        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 cell=%s MT=%d NB=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d narrow=%d ih_bytes=%d",
+                 used_tc ? "tcgen05_i8" : "simt_dp4a", fused ? "fused" : "generic", mp.MT, mp.NB, mp.P, mp.G,
+                 mp.groups_per_launch, mp.smem, mp.tmem_cols, h->gc_host.narrow, ih_bytes);
     } else {
         RecArgs a;
         a.T = T; a.B = B; a.H = h->H; a.Hpad = h->Hpad; a.C = C;

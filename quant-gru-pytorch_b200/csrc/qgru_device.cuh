@@ -77,10 +77,36 @@ __device__ __forceinline__ int32_t gru_cell(const GateConsts &gc, const int32_t 
     return clampi(h_new, gc.h_lo, gc.h_hi);
 }
 
+// The same cell with everything that depends on one narrow operand tabulated on the host:
+//   a_*   W*x+bw already rescaled to the gate's input scale, zp_in included (GEMM epilogue)
+//   THZ/THR[hh - hh_lo]      = rescale(hh - zp_hh -> z / r input scale)
+//   TZ/TR[clamp(pre) - lo]   = sigmoid LUT output minus its zero point
+//   TN[clamp(pre) - lo]      = rescale(tanh LUT output - zp_n -> h scale)
+// Each table entry is produced by the very functions above, so the result is identical; the
+// host checks that the two products below fit 32 bits before enabling this form.
+__device__ __forceinline__ int32_t gru_cell_fused(const GateConsts &gc, const int32_t *ft, int32_t a_z,
+                                                  int32_t a_r, int32_t a_n, int32_t hh_z, int32_t hh_r,
+                                                  int32_t hh_n, int32_t h_old) {
+    const int32_t z_pre = a_z + ft[gc.ft_off[3] + (hh_z - gc.hh_lo)];
+    const int32_t z_d = ft[gc.ft_off[0] + (clampi(z_pre, gc.in_lo[ACT_Z], gc.in_hi[ACT_Z]) - gc.in_lo[ACT_Z])];
+    const int32_t r_pre = a_r + ft[gc.ft_off[4] + (hh_r - gc.hh_lo)];
+    const int32_t r_d = ft[gc.ft_off[1] + (clampi(r_pre, gc.in_lo[ACT_R], gc.in_hi[ACT_R]) - gc.in_lo[ACT_R])];
+    const int32_t n_pre = a_n + (int32_t)rescale32(r_d * (hh_n - gc.zp_hh), gc.rh_to_n);
+    const int32_t n_d = ft[gc.ft_off[2] + (clampi(n_pre, gc.in_lo[ACT_N], gc.in_hi[ACT_N]) - gc.in_lo[ACT_N])];
+    const int32_t comb = z_d * (h_old - gc.zp_h) + (gc.k1 - z_d) * n_d;
+    return clampi((int32_t)rescale32(comb, gc.uh_to_h) + gc.zp_h, gc.h_lo, gc.h_hi);
+}
+
 // Epilogue of a fused linear layer (src/gru_forward_cpu_quant.cc:130-138).
 __device__ __forceinline__ int32_t linear_epilogue(int64_t acc, int64_t corr, Rescale rs,
                                                    int32_t zp_out, int32_t lo, int32_t hi) {
     const int32_t v = (int32_t)rescale64(acc + corr, rs) + zp_out;
+    return clampi(v, lo, hi);
+}
+// The same when acc + corr is known to fit int32 (LinearConsts::fits32).
+__device__ __forceinline__ int32_t linear_epilogue32(int32_t acc, int32_t corr, Rescale rs,
+                                                     int32_t zp_out, int32_t lo, int32_t hi) {
+    const int32_t v = (int32_t)rescale32(acc + corr, rs) + zp_out;
     return clampi(v, lo, hi);
 }
 

@@ -7,7 +7,7 @@
 //
 // Tile: 128 output channels (TMEM lanes) x 128 tokens (TMEM columns); K streamed in 128-byte
 // slabs through a 3-stage shared-memory ring.  Warp roles: warp 0 issues the TMA loads, warp 1
-// owns tensor memory and issues the MMAs, warps 2-5 run the epilogue (one TMEM lane = one
+// owns tensor memory and issues the MMAs, warps 2-9 run the epilogue (one TMEM lane = one
 // output channel per thread, so each thread keeps its channel's constants in registers and a
 // warp's stores cover 32 consecutive channels of a token).
 #include <cuda.h>
@@ -55,14 +55,17 @@ constexpr int GM = 128;      // channels per tile
 constexpr int GN = 128;      // tokens per tile
 constexpr int KB = 128;      // K bytes per stage
 constexpr int STAGES = 3;
+constexpr int EPI_WARPS = 8;                       // two warps per TMEM lane quadrant
+constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int STAGE_BYTES = (GM + GN) * KB;
 constexpr long long WAIT_BUDGET = 2000000000ll;  // ~1 s of SM clocks
 constexpr size_t GEMM_SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
 
 template <bool XUnsigned, typename IhT>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-             IhT *__restrict__ ih, long long N, int C, int Kpad, LinearConsts lc, int *abort_flag) {
+             IhT *__restrict__ ih, long long N, int C, int Kpad, LinearConsts lc, PreScale ps,
+             int *abort_flag) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *tiles = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -126,23 +129,33 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
         }
     } else {
         const int q = warp & 3;                     // TMEM lane quadrant of this warp
+        const int part = (warp - 2) >> 2;           // which share of the token columns
+        constexpr int COLS = GN / (EPI_WARPS / 4);
         const int m = m0 + q * 32 + lane;
         const bool m_ok = m < C;
         const int64_t corr = m_ok ? lc.corr[m] : 0;
         const Rescale rs = m_ok ? lc.rs[m] : Rescale{1, 1};
+        // fused-cell mode: the channel's gate decides the second rescale (to its input scale)
+        const int gate = (ps.enabled && m_ok) ? m / ps.H : 0;
+        const Rescale pre_rs = ps.to[gate];
+        const int32_t pre_zp = ps.zp_in[gate];
         const bool ready = tc::mbar_wait(acc_full, 0, WAIT_BUDGET);
         if (!ready && lane == 0) atomicExch(failed, 1);
         tc::tc_fence_after_sync();
         if (ready) {
-            for (int c0 = 0; c0 < GN; c0 += 16) {
+            IhT *out = ih + m;
+            for (int c0 = part * COLS; c0 < (part + 1) * COLS; c0 += 16) {
                 int32_t v[16];
                 tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
                 tc::tmem_ld_wait();
+                const int32_t c32 = (int32_t)corr;
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const long long n = n0 + c0 + i;
-                    if (m_ok && n < N)
-                        ih[n * C + m] = (IhT)linear_epilogue(v[i], corr, rs, lc.zp_out, lc.lo, lc.hi);
+                    int32_t y = lc.fits32 ? linear_epilogue32(v[i], c32, rs, lc.zp_out, lc.lo, lc.hi)
+                                          : linear_epilogue(v[i], corr, rs, lc.zp_out, lc.lo, lc.hi);
+                    if (ps.enabled) y = (int32_t)rescale32(y - ps.zp_ih, pre_rs) + pre_zp;
+                    if (m_ok && n < N) out[n * C] = (IhT)y;
                 }
             }
         }
@@ -155,12 +168,12 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
 
 template <bool XU, typename IhT>
 cudaError_t launch(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long long N, int C, int Kpad,
-                   LinearConsts lc, int *abort_flag, cudaStream_t st) {
+                   LinearConsts lc, PreScale ps, int *abort_flag, cudaStream_t st) {
     auto kern = k_gemm_wx_tc<XU, IhT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
     if (e != cudaSuccess) return e;
     dim3 grid((unsigned)((C + GM - 1) / GM), (unsigned)((N + GN - 1) / GN));
-    kern<<<grid, 192, GEMM_SMEM, st>>>(mw, mx, (IhT *)ih, N, C, Kpad, lc, abort_flag);
+    kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(mw, mx, (IhT *)ih, N, C, Kpad, lc, ps, abort_flag);
     return cudaGetLastError();
 }
 
@@ -168,7 +181,8 @@ cudaError_t launch(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long 
 
 int tc_gemm_launch(TcGemmState &s, const uint8_t *x8, long long x_rows_alloc, const int8_t *w8,
                    long long w_rows_alloc, void *ih, long long N, int C, int Kpad, bool x_unsigned,
-                   int ih_bytes, LinearConsts lc, int *abort_flag, cudaStream_t stream, std::string *err) {
+                   int ih_bytes, LinearConsts lc, PreScale ps, int *abort_flag, cudaStream_t stream,
+                   std::string *err) {
     if (Kpad % KB != 0 || x_rows_alloc < (N + GN - 1) / GN * GN || w_rows_alloc < (C + GM - 1) / GM * GM) {
         if (err) *err = "tcgen05 GEMM needs K padded to 128 and operand rows padded to the tile";
         return QGRU_ERR_UNSUPPORTED;
@@ -196,11 +210,14 @@ int tc_gemm_launch(TcGemmState &s, const uint8_t *x8, long long x_rows_alloc, co
     const CUtensorMap &mx = *reinterpret_cast<const CUtensorMap *>(s.map_x);
     cudaError_t e;
     if (ih_bytes == 1)
-        e = x_unsigned ? launch<true, int8_t>(mw, mx, ih, N, C, Kpad, lc, abort_flag, stream)
-                       : launch<false, int8_t>(mw, mx, ih, N, C, Kpad, lc, abort_flag, stream);
+        e = x_unsigned ? launch<true, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, stream)
+                       : launch<false, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, stream);
+    else if (ih_bytes == 2)
+        e = x_unsigned ? launch<true, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, stream)
+                       : launch<false, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, stream);
     else
-        e = x_unsigned ? launch<true, int16_t>(mw, mx, ih, N, C, Kpad, lc, abort_flag, stream)
-                       : launch<false, int16_t>(mw, mx, ih, N, C, Kpad, lc, abort_flag, stream);
+        e = x_unsigned ? launch<true, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, stream)
+                       : launch<false, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, stream);
     if (e != cudaSuccess) {
         if (err) *err = std::string("tcgen05 GEMM launch: ") + cudaGetErrorString(e);
         return QGRU_ERR_CUDA;

@@ -19,12 +19,15 @@ struct TcGemmState {
     alignas(64) unsigned char map_x[128];
 };
 
-// ih[n][m] = requant( sum_k w8[m][k] * x8[n][k] ) for n < N tokens, m < C channels.
+// ih[n][m] = requant( sum_k w8[m][k] * x8[n][k] ) for n < N tokens, m < C channels, stored as
+// ih_bytes-wide integers (1, 2 or 4).  With ps.enabled the value is further rescaled to the input
+// scale of the channel's gate (the form the fused recurrence cell consumes).
 // Both operands are [rows][Kpad] bytes with Kpad a multiple of 128 and rows ALLOCATED up to a
 // multiple of 128 (x_rows_alloc, w_rows_alloc) so that no tile load leaves the allocation.
 // Returns QGRU_ERR_UNSUPPORTED when the shapes do not meet that, QGRU_ERR_CUDA on failure.
 int tc_gemm_launch(TcGemmState &st, const uint8_t *x8, long long x_rows_alloc, const int8_t *w8,
                    long long w_rows_alloc, void *ih, long long N, int C, int Kpad, bool x_unsigned,
-                   int ih_bytes, LinearConsts lc, int *abort_flag, cudaStream_t stream, std::string *err);
+                   int ih_bytes, LinearConsts lc, PreScale ps, int *abort_flag, cudaStream_t stream,
+                   std::string *err);
 
 }  // namespace qgru

@@ -38,11 +38,15 @@ struct qgru_handle {
     int opt_gemm = 0;      // 0 auto, 1 simt, 2 tcgen05
     int opt_rec = 0;       // 0 auto, 1 dp4a, 3 generic
     int opt_sm_limit = 0;  // 0: all SMs
+    int opt_cell = 0;      // 0 auto (fused cell where valid), 1 generic cell
     unsigned spin_limit = 1u << 24;
+    long long *dbg_stamps = nullptr;  // profiling aid of the tensor-core recurrence kernel
     // device state that lives with the handle
     GateConsts *d_gc = nullptr;
     int32_t *d_tables = nullptr;
     int n_table = 0;
+    int32_t *d_ftables = nullptr;  // tables of the fused cell
+    int n_ftable = 0;
     Rescale *d_rs[2] = {nullptr, nullptr};    // gemm rescale: x side, h side
     Rescale *d_brs[2] = {nullptr, nullptr};   // bias rescale
     float *d_wscale[4] = {nullptr, nullptr, nullptr, nullptr};
@@ -51,6 +55,7 @@ struct qgru_handle {
     int32_t *d_wsum[2] = {nullptr, nullptr};
     int8_t *d_w8[2] = {nullptr, nullptr};     // W8 [3H][Ipad], R8 [3H][Hpad] (rows over-allocated)
     long long w8_rows[2] = {0, 0};
+    bool lin_fits32[2] = {false, false};      // acc + corr fits int32 (x side, h side)
     int *d_flags = nullptr;                   // [0] data errors, [1] barrier abort
     int *h_flags = nullptr;                   // pinned mirror
     unsigned *d_bar = nullptr;

@@ -42,7 +42,21 @@ struct GateConsts {
     int32_t table_off[3];                 // offset of that table in the table array (ints)
     int32_t narrow;                       // 1: every gate rescale fits the 32-bit fast form
     float h_scale;                        // decode_scale(toFixedScale(h)) for the float output
+    // "fused" form of the cell used by the tensor-core recurrence when every gate input and
+    // the R*h+br output are narrow enough to tabulate (see build_fused_tables in qgru_api.cu)
+    int32_t fused_ok;
+    int32_t k1;                           // one_q - 2*zp_z : (1 - z) numerator minus z_d
+    int32_t ft_off[5];                    // offsets of TZ, TR, TN, THZ, THR in the fused table block
+    int32_t ih_pre_bytes;                 // storage width (2 or 4) of the pre-rescaled W*x+bw values
     qgru_lut lut[3];
+};
+
+// What the input-projection GEMM applies after the requantization when the recurrence runs the
+// fused cell: out = rescale(ih - zp_ih -> gate input scale of the channel's gate) + zp_in[gate].
+struct PreScale {
+    int32_t enabled, H, zp_ih;
+    Rescale to[3];
+    int32_t zp_in[3];
 };
 
 // Per output channel constants of one fused linear layer:
@@ -53,6 +67,7 @@ struct LinearConsts {
     const int64_t *corr;  // [3H] device
     const Rescale *rs;    // [3H] device
     int32_t zp_out, lo, hi;
+    int32_t fits32;       // 1: acc + corr fits int32 for every channel (one widening multiply)
 };
 
 }  // namespace qgru

@@ -130,9 +130,15 @@ __global__ void k_pack_weights(const int32_t *__restrict__ wq, int8_t *__restric
 __global__ void k_channel_consts(const int32_t *__restrict__ bias_q,
                                  const Rescale *__restrict__ bias_rs,
                                  const int32_t *__restrict__ wsum, int32_t zp_in,
-                                 int64_t *__restrict__ corr, int C) {
+                                 int64_t *__restrict__ corr, int C, long long acc_bound, int *flags,
+                                 int flag_bit) {
     const int m = blockIdx.x * blockDim.x + threadIdx.x;
-    if (m < C) corr[m] = rescale64((int64_t)bias_q[m], bias_rs[m]) - (int64_t)zp_in * (int64_t)wsum[m];
+    if (m >= C) return;
+    const int64_t c = rescale64((int64_t)bias_q[m], bias_rs[m]) - (int64_t)zp_in * (int64_t)wsum[m];
+    corr[m] = c;
+    // acc + corr must stay inside int32 for the one-multiply epilogue
+    const int64_t mag = c < 0 ? -c : c;
+    if (mag + acc_bound >= 0x7fffffffll) atomicOr(flags, flag_bit);
 }
 
 // ------------------------------------------------ input projection, SIMT dp4a form (a1)

@@ -17,18 +17,19 @@ struct RecMmaArgs {
     int NB;           // batch rows per group (multiple of 16); set by the launcher
     int b_off, b_cnt; // batch rows [b_off, b_off + b_cnt) are handled by this launch
     int reverse;
+    int h_unsigned;   // the state h is stored as uint8 (else int8)
     uint32_t tmem_cols;
-    const void *ih;         // [T*B][3H] int8 or int16
+    const void *ih;         // [T*B][3H]: raw W*x+bw (int8/int16) or pre-rescaled for the fused cell (int16/int32)
     uint8_t *h8;            // [2][B][Hpad] ping-pong state (+ slack rows)
     int32_t *hq_out;        // [(T+1)][B][H] or null
     float *hf_out;          // [(T+1)][B][H] or null
     LinearConsts lc;        // R*h + br epilogue
-    const GateConsts *gc;
-    const int32_t *tables;
+    const int32_t *tables;  // activation tables (table_off) or, fused, the fused-cell tables (ft_off)
     int n_table;
     unsigned *bar;          // one counter per group, 32 words apart, zeroed before the launch
     int *abort_flag;
     unsigned spin_limit;
+    long long *dbg;         // optional [T][8] clock stamps of CTA 0 (profiling aid), else null
 };
 
 struct RecMmaPlan {
@@ -50,8 +51,9 @@ struct RecMmaState {
 // one SM's shared memory: H <= 512 with 8-bit weights).
 bool rec_mma_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, RecMmaPlan *out);
 
-int rec_mma_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const int8_t *r8, long long r_rows_alloc,
-                   long long h_rows_alloc, bool h_unsigned, int ih_bytes, bool narrow, bool have_coop,
+int rec_mma_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const GateConsts &gc_host,
+                   const int8_t *r8, long long r_rows_alloc,
+                   long long h_rows_alloc, bool h_unsigned, int ih_bytes, bool narrow, bool fused, bool have_coop,
                    cudaStream_t stream, std::string *err);
 
 }  // namespace qgru

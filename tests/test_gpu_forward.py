@@ -94,8 +94,8 @@ def test_large_batch_many_groups(oracle, cuda_device):
 def test_bitwidth_configs(oracle, cuda_device, name):
     for seed, (T, B, I, H) in enumerate([(7, 6, 24, 48), (4, 9, 40, 72)]):
         case = make_case(20 + seed, T, B, I, H, oracle, config_named(name), with_h0=(seed == 1))
-        for rec in ("mma", "dp4a"):
-            got, plan, _ = _run(case, cuda_device, opts=(("rec", rec),))
+        for opts in ((("rec", "mma"),), (("rec", "mma"), ("cell", "generic")), (("rec", "dp4a"),)):
+            got, plan, _ = _run(case, cuda_device, opts=opts)
             assert "path=int8" in plan
             assert np.array_equal(got, _want(oracle, case)), (name, plan)
 
