@@ -205,6 +205,24 @@ QGRU_API int qgru_forward_i32(qgru_handle *h, int T, int B, const int32_t *x_q,
 QGRU_API int qgru_forward_f32(qgru_handle *h, int T, int B, const float *x, const float *h0,
                               float *h_out, int32_t *x_q_out, unsigned flags, void *stream);
 
+/* No counterpart in the reference.  The same result as qgru_forward_i32 for callers that must
+ * not allocate device memory at call time (a serving loop with a fixed memory budget, a process
+ * whose allocator belongs to another framework, a real-time thread that cannot tolerate the
+ * implicit synchronisation of cudaMalloc).  The whole workspace is a fixed array of 8 MiB inside
+ * the library image - every GPU that loads the library holds it until the process exits - so the
+ * call makes no cudaMalloc / cudaFree and grows nothing.  Problems whose workspace
+ * (T*B*(Kpad(I) + 3H*b) + 2*B*Kpad(H) bytes, Kpad = round up to 128, b = 1 or 2) does not fit
+ * are rejected with QGRU_ERR_BAD_ARG and a message naming both sizes.  It needs the 8-bit
+ * storage plan (x, h, W, R at most 8 bits) and runs the SIMT GEMM and the dp4a recurrence.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make
+ * that first call before any stream capture.  All handles and calls on one GPU share the array
+ * and it keeps the previous call's contents (what must start at zero is cleared by the call
+ * itself), so two calls that overlap on the GPU - different streams or handles - race: serialise
+ * them. */
+QGRU_API int qgru_forward_i32_static(qgru_handle *h, int T, int B, const int32_t *x_q,
+                                     const int32_t *h0_q, int32_t *h_q, unsigned flags,
+                                     void *stream);
+
 /* The same two calls for callers that hold HOST buffers (pinned or pageable): the library
  * stages x to the device, runs the forward and copies h back, all on `stream`; returns
  * after the stream has been synchronised. */

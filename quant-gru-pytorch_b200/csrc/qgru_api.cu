@@ -9,6 +9,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -862,3 +863,133 @@ const char *qgru_describe_plan(qgru_handle *h, int T, int B) {
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// Forward without any allocation.
+//
+// Some callers are not allowed to allocate device memory when they call a forward: a serving
+// loop whose memory budget was fixed at start-up, a process whose allocator is owned by another
+// framework, code running between the capture and the replay of a CUDA graph, or a real-time
+// thread for which cudaMalloc's implicit device synchronisation is not acceptable.  For them
+// the workspace of the integer forward (8-bit input rows, the W*x+bw buffer, the ping-pong
+// state and the per-group step counters) lives in the array below, which is part of the
+// library image: every GPU that loads the library holds these bytes until the process exits.
+// ------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticWorkspaceBytes = size_t(8) << 20;   // 8 MiB per device
+static __device__ __align__(256) unsigned char g_static_workspace[kStaticWorkspaceBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+unsigned char *g_static_ptr[kMaxDevices] = {};   // device address of the array, per device
+
+// In host code `g_static_workspace` is only a handle for the runtime, not an address a kernel
+// can use: the device address is asked for once per device, with that device current.
+int static_workspace(qgru_handle *h, unsigned char **out) {
+    if (h->device < 0 || h->device >= kMaxDevices) return fail(h, QGRU_ERR_UNSUPPORTED, "device index too large");
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[h->device]) {
+        void *p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_workspace);
+        if (e != cudaSuccess || !p) {
+            h->err = std::string("cudaGetSymbolAddress(static workspace): ") + cudaGetErrorString(e);
+            cudaGetLastError();
+            return QGRU_ERR_CUDA;
+        }
+        g_static_ptr[h->device] = static_cast<unsigned char *>(p);
+    }
+    *out = g_static_ptr[h->device];
+    return QGRU_OK;
+}
+
+size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+}  // namespace
+
+extern "C" int qgru_forward_i32_static(qgru_handle *h, int T, int B, const int32_t *x_q, const int32_t *h0_q,
+                                       int32_t *h_q, unsigned flags, void *stream) {
+    if (!h || !x_q || !h_q) return QGRU_ERR_BAD_ARG;
+    int rc = check_forward_args(h, T, B);
+    if (rc) return rc;
+    if (!h->fast) return fail(h, QGRU_ERR_UNSUPPORTED, "the static-workspace forward needs the 8-bit storage plan");
+    CK(cudaSetDevice(h->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const long long N = (long long)T * B;
+    const int C = h->C;
+
+    RecPlan pl;
+    if (!plan_recurrence(h, B, &pl)) return fail(h, QGRU_ERR_UNSUPPORTED, "no recurrence plan fits shared memory");
+    // carve the array: x8 | ih | h8 (two state buffers) | step counters
+    const size_t off_x8 = 0;
+    const size_t off_ih = align256(off_x8 + (size_t)N * h->Ipad);
+    const size_t off_h8 = align256(off_ih + (size_t)N * C * h->ih_bytes);
+    const size_t off_bar = align256(off_h8 + (size_t)2 * B * h->Hpad);
+    const size_t need = off_bar + (size_t)pl.G * 32 * sizeof(unsigned);
+    if (need > kStaticWorkspaceBytes) {
+        char msg[200];
+        snprintf(msg, sizeof(msg), "static workspace too small: T=%d B=%d needs %zu bytes, the library holds %zu",
+                 T, B, need, kStaticWorkspaceBytes);
+        return fail(h, QGRU_ERR_BAD_ARG, msg);
+    }
+    unsigned char *ws = nullptr;
+    if ((rc = static_workspace(h, &ws))) return rc;
+    uint8_t *x8 = ws + off_x8;
+    void *ih = ws + off_ih;
+    uint8_t *h8 = ws + off_h8;
+    unsigned *bar = reinterpret_cast<unsigned *>(ws + off_bar);
+
+    const qgru_op &xo = h->p.op[QGRU_OP_X], &ho = h->p.op[QGRU_OP_H];
+    const long long init_slot = (flags & QGRU_FLAG_REVERSE) ? T : 0;
+    h->ev = h->ring[h->calls % qgru_handle::kRing];
+    h->calls++;
+    CK(cudaEventRecord(h->ev[0], st));
+    CK(cudaMemsetAsync(h->d_flags, 0, 2 * sizeof(int), st));
+    // the array keeps what the previous call left: the state buffers' padding columns and the
+    // step counters must start at zero
+    CK(cudaMemsetAsync(h8, 0, (size_t)2 * B * h->Hpad, st));
+    CK(cudaMemsetAsync(bar, 0, (size_t)pl.G * 32 * sizeof(unsigned), st));
+    k_narrow_rows_i32<<<grid_for(N * (h->Ipad / 4), 256, h->sm_count), 256, 0, st>>>(
+        x_q, x8, N, h->I, h->Ipad, op_qmin(xo), op_qmax(xo), h->d_flags);
+    k_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
+        h0_q, nullptr, h8, h_q, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale, ho.zero_point, op_qmin(ho),
+        op_qmax(ho), h->d_flags);
+    CK(cudaEventRecord(h->ev[1], st));
+    const LinearConsts lcx = linear_consts(h, 0);
+    {
+        dim3 grid((unsigned)((N + 63) / 64), (unsigned)((C + 63) / 64));
+        if (h->ih_bytes == 1) {
+            if (h->x_uns) k_gemm_wx_simt<true, int8_t><<<grid, 256, 0, st>>>(x8, h->d_w8[0], (int8_t *)ih, N, C, h->Ipad, lcx);
+            else k_gemm_wx_simt<false, int8_t><<<grid, 256, 0, st>>>(x8, h->d_w8[0], (int8_t *)ih, N, C, h->Ipad, lcx);
+        } else {
+            if (h->x_uns) k_gemm_wx_simt<true, int16_t><<<grid, 256, 0, st>>>(x8, h->d_w8[0], (int16_t *)ih, N, C, h->Ipad, lcx);
+            else k_gemm_wx_simt<false, int16_t><<<grid, 256, 0, st>>>(x8, h->d_w8[0], (int16_t *)ih, N, C, h->Ipad, lcx);
+        }
+    }
+    CK(cudaGetLastError());
+    CK(cudaEventRecord(h->ev[2], st));
+    RecArgs a;
+    a.T = T; a.B = B; a.H = h->H; a.Hpad = h->Hpad; a.C = C;
+    a.Hs = pl.Hs; a.Bt = pl.Bt; a.P = pl.P;
+    a.reverse = (flags & QGRU_FLAG_REVERSE) ? 1 : 0;
+    a.r8 = h->d_w8[1];
+    a.ih = ih;
+    a.h8 = h8;
+    a.hq_out = h_q;
+    a.hf_out = nullptr;
+    a.lc = linear_consts(h, 1);
+    a.gc = h->d_gc;
+    a.tables = h->d_tables;
+    a.n_table = h->n_table;
+    a.bar = bar;
+    a.abort_flag = h->d_flags + 1;
+    a.spin_limit = h->spin_limit;
+    if (h->ih_bytes == 1) rc = h->h_uns ? launch_rec<true, int8_t>(h, a, pl, st) : launch_rec<false, int8_t>(h, a, pl, st);
+    else rc = h->h_uns ? launch_rec<true, int16_t>(h, a, pl, st) : launch_rec<false, int16_t>(h, a, pl, st);
+    if (rc) return rc;
+    h->launches += 3;
+    CK(cudaEventRecord(h->ev[3], st));
+    h->timing_valid = true;
+    h->plan_text = "path=int8 gemm=simt_dp4a rec=dp4a workspace=static";
+    return QGRU_OK;
+}

@@ -128,6 +128,26 @@ class Handle:
             self.synchronize()
         return h_q
 
+    def forward_i32_static(self, x_q, h0_q=None, reverse=False, out=None, sync=True):
+        """forward_i32 for callers that may not allocate device memory at call time: the
+        workspace is a fixed 8 MiB array inside the library (shared by every call on the GPU, so
+        overlapping calls race); sizes that do not fit raise ValueError.  Pass `out` to avoid
+        the allocation of the result tensor too."""
+        x_q = _check_tensor(x_q, "x_q", torch.int32)
+        if x_q.dim() != 3 or x_q.shape[2] != self.input_size:
+            raise ValueError("x_q must have shape [time_steps, batch_size, input_size]")
+        T, B = int(x_q.shape[0]), int(x_q.shape[1])
+        if h0_q is not None:
+            h0_q = _check_tensor(h0_q, "h0_q", torch.int32, (B, self.hidden_size))
+        h_q = out if out is not None else torch.empty((T + 1, B, self.hidden_size), dtype=torch.int32,
+                                                      device=self._tdev)
+        self._ck(self._lib.qgru_forward_i32_static(self._h, T, B, _ptr(x_q), _ptr(h0_q), _ptr(h_q),
+                                                   _cabi.FLAG_REVERSE if reverse else 0,
+                                                   _stream(self._tdev)), "qgru_forward_i32_static")
+        if sync:
+            self.synchronize()
+        return h_q
+
     def forward_f32(self, x, h0=None, reverse=False, want_x_q=False, out=None, sync=True):
         x = _check_tensor(x, "x", torch.float32)
         if x.dim() != 3 or x.shape[2] != self.input_size:
