@@ -549,7 +549,7 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
     bool used_tc = false;
     if (h->opt_gemm != 1) {
         rc = tc_gemm_launch(h->tc, (const uint8_t *)h->x8.p, (N + 127) / 128 * 128, h->d_w8[0], h->w8_rows[0],
-                            h->ih.p, N, C, h->Ipad, h->x_uns, ih_bytes, lcx, ps, h->d_flags + 1, st, &h->err);
+                            h->ih.p, N, C, h->Ipad, h->x_uns, ih_bytes, lcx, ps, h->d_flags + 1, sms, st, &h->err);
         if (rc == QGRU_OK) {
             used_tc = true;
             h->launches++;

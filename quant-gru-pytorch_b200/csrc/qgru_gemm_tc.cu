@@ -5,14 +5,17 @@
 // (src/gru_forward_gpu_quant.cu:110-180, 527-562), which multiplies int32 operands on CUDA
 // cores with 64-bit accumulation.
 //
-// Tile: 128 output channels (TMEM lanes) x 128 tokens (TMEM columns); K streamed in 128-byte
-// slabs through a 3-stage shared-memory ring.  Warp roles: warp 0 issues the TMA loads, warp 1
-// owns tensor memory and issues the MMAs, warps 2-9 run the epilogue (one TMEM lane = one
+// Persistent kernel, one CTA per SM looping over tiles of 128 output channels (TMEM lanes) x 128
+// tokens (TMEM columns); K streamed in 128-byte slabs through a 4-stage shared-memory ring that
+// runs ahead across tiles; two accumulators in tensor memory so that the MMAs of tile i+1
+// overlap the epilogue of tile i.  Warp roles: warp 0 issues the TMA loads, warp 1
+// owns tensor memory and issues the MMAs, warps 2-17 run the epilogue (one TMEM lane = one
 // output channel per thread, so each thread keeps its channel's constants in registers and a
 // warp's stores cover 32 consecutive channels of a token).
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "qgru_gemm_tc.cuh"
@@ -54,8 +57,8 @@ namespace {
 constexpr int GM = 128;      // channels per tile
 constexpr int GN = 128;      // tokens per tile
 constexpr int KB = 128;      // K bytes per stage
-constexpr int STAGES = 3;
-constexpr int EPI_WARPS = 8;                       // two warps per TMEM lane quadrant
+constexpr int STAGES = 4;
+constexpr int EPI_WARPS = 16;                      // four warps per TMEM lane quadrant
 constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int STAGE_BYTES = (GM + GN) * KB;
 constexpr long long WAIT_BUDGET = 2000000000ll;  // ~1 s of SM clocks
@@ -70,27 +73,32 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     unsigned char *tiles = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t *bars = reinterpret_cast<uint64_t *>(tiles + (size_t)STAGES * STAGE_BYTES);
-    uint64_t *full = bars, *empty = bars + STAGES, *acc_full = bars + 2 * STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 1);
+    uint64_t *full = bars, *empty = bars + STAGES;
+    uint64_t *acc_full = bars + 2 * STAGES, *acc_empty = bars + 2 * STAGES + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
     int *failed = reinterpret_cast<int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * GM;
-    const long long n0 = (long long)blockIdx.y * GN;
     const int num_kb = Kpad / KB;
+    const int m_tiles = (C + GM - 1) / GM;
+    const long long n_tiles = (N + GN - 1) / GN;
+    const long long total = (long long)m_tiles * n_tiles;   // consecutive tiles share the token tile
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             tc::mbar_init(&full[s], 1);
             tc::mbar_init(&empty[s], 1);
         }
-        tc::mbar_init(acc_full, 1);
+        for (int b = 0; b < 2; ++b) {
+            tc::mbar_init(&acc_full[b], 1);
+            tc::mbar_init(&acc_empty[b], EPI_WARPS);
+        }
         *failed = 0;
         tc::fence_barrier_init();
         tc::tma_prefetch_desc(&map_w);
         tc::tma_prefetch_desc(&map_x);
     }
-    if (warp == 1) tc::tmem_alloc(tmem_slot, GN);
+    if (warp == 1) tc::tmem_alloc(tmem_slot, 2 * GN);   // two accumulators: MMA of tile i+1 overlaps epilogue of tile i
     tc::tc_fence_before_sync();
     __syncthreads();
     tc::tc_fence_after_sync();
@@ -98,57 +106,81 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
-                if (!tc::mbar_wait(&empty[s], ph ^ 1, WAIT_BUDGET)) { atomicExch(failed, 1); break; }
-                unsigned char *a = tiles + (size_t)s * STAGE_BYTES;
-                tc::mbar_expect_tx(&full[s], STAGE_BYTES);
-                tc::tma_load_2d(a, &map_w, &full[s], kb * KB, m0);
-                tc::tma_load_2d(a + GM * KB, &map_x, &full[s], kb * KB, (int)n0);
+            long long it = 0;   // k-slab counter across tiles: ring position and phase
+            bool ok = true;
+            for (long long tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+                const int m0 = (int)(tile % m_tiles) * GM;
+                const long long n0 = (tile / m_tiles) * GN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = (int)(it % STAGES);
+                    const uint32_t ph = (uint32_t)((it / STAGES) & 1);
+                    if (!tc::mbar_wait(&empty[s], ph ^ 1, WAIT_BUDGET)) { ok = false; break; }
+                    unsigned char *a = tiles + (size_t)s * STAGE_BYTES;
+                    tc::mbar_expect_tx(&full[s], STAGE_BYTES);
+                    tc::tma_load_2d(a, &map_w, &full[s], kb * KB, m0);
+                    tc::tma_load_2d(a + GM * KB, &map_x, &full[s], kb * KB, (int)n0);
+                }
             }
+            if (!ok) atomicExch(failed, 1);
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = tc::idesc_i8(GM, GN, true, !XUnsigned);
+            long long it = 0, local = 0;
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
-                if (!tc::mbar_wait(&full[s], ph, WAIT_BUDGET)) { atomicExch(failed, 1); ok = false; break; }
+            for (long long tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++local) {
+                const int buf = (int)(local & 1);
+                if (!tc::mbar_wait(&acc_empty[buf], (uint32_t)(((local >> 1) & 1) ^ 1), WAIT_BUDGET)) { ok = false; break; }
                 tc::tc_fence_after_sync();
-                const uint32_t a_addr = tc::smem_u32(tiles + (size_t)s * STAGE_BYTES);
-                const uint64_t a_desc = tc::smem_desc_sw128(a_addr);
-                const uint64_t b_desc = tc::smem_desc_sw128(a_addr + GM * KB);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = (int)(it % STAGES);
+                    const uint32_t ph = (uint32_t)((it / STAGES) & 1);
+                    if (!tc::mbar_wait(&full[s], ph, WAIT_BUDGET)) { ok = false; break; }
+                    tc::tc_fence_after_sync();
+                    const uint32_t a_addr = tc::smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                    const uint64_t a_desc = tc::smem_desc_sw128(a_addr);
+                    const uint64_t b_desc = tc::smem_desc_sw128(a_addr + GM * KB);
 #pragma unroll
-                for (int ks = 0; ks < KB / 32; ++ks)
-                    tc::mma_i8(tmem_base, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (kb | ks) != 0);
-                tc::mma_commit(&empty[s]);
+                    for (int ks = 0; ks < KB / 32; ++ks)
+                        tc::mma_i8(tmem_base + buf * GN, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (kb | ks) != 0);
+                    tc::mma_commit(&empty[s]);
+                }
+                if (ok) tc::mma_commit(&acc_full[buf]);
             }
-            tc::mma_commit(acc_full);
+            if (!ok) atomicExch(failed, 1);
         }
     } else {
         const int q = warp & 3;                     // TMEM lane quadrant of this warp
         const int part = (warp - 2) >> 2;           // which share of the token columns
         constexpr int COLS = GN / (EPI_WARPS / 4);
-        const int m = m0 + q * 32 + lane;
-        const bool m_ok = m < C;
-        const int64_t corr = m_ok ? lc.corr[m] : 0;
-        const Rescale rs = m_ok ? lc.rs[m] : Rescale{1, 1};
-        // fused-cell mode: the channel's gate decides the second rescale (to its input scale)
-        const int gate = (ps.enabled && m_ok) ? m / ps.H : 0;
-        const Rescale pre_rs = ps.to[gate];
-        const int32_t pre_zp = ps.zp_in[gate];
-        const bool ready = tc::mbar_wait(acc_full, 0, WAIT_BUDGET);
-        if (!ready && lane == 0) atomicExch(failed, 1);
-        tc::tc_fence_after_sync();
-        if (ready) {
+        long long local = 0;
+        bool ok = true;
+        for (long long tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++local) {
+            const int m0 = (int)(tile % m_tiles) * GM;
+            const long long n0 = (tile / m_tiles) * GN;
+            const int buf = (int)(local & 1);
+            const int m = m0 + q * 32 + lane;
+            const bool m_ok = m < C;
+            const int64_t corr = m_ok ? lc.corr[m] : 0;
+            const Rescale rs = m_ok ? lc.rs[m] : Rescale{1, 1};
+            // fused-cell mode: the channel's gate decides the second rescale (to its input scale)
+            const int gate = (ps.enabled && m_ok) ? m / ps.H : 0;
+            const Rescale pre_rs = ps.to[gate];
+            const int32_t pre_zp = ps.zp_in[gate];
+            const int32_t c32 = (int32_t)corr;
+            ok = tc::mbar_wait(&acc_full[buf], (uint32_t)((local >> 1) & 1), WAIT_BUDGET);
+            if (!ok) break;
+            tc::tc_fence_after_sync();
             IhT *out = ih + m;
             for (int c0 = part * COLS; c0 < (part + 1) * COLS; c0 += 16) {
                 int32_t v[16];
-                tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
+                tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * GN + c0), v);
                 tc::tmem_ld_wait();
-                const int32_t c32 = (int32_t)corr;
+                if (c0 + 16 >= (part + 1) * COLS) {
+                    // this warp has read its last accumulator columns: hand the buffer back
+                    tc::tc_fence_before_sync();
+                    if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
+                }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const long long n = n0 + c0 + i;
@@ -159,20 +191,22 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                 }
             }
         }
+        if (!ok && lane == 0) atomicExch(failed, 1);
     }
     tc::tc_fence_before_sync();
     __syncthreads();
     if (threadIdx.x == 0 && *failed) atomicOr(abort_flag, 2);
-    if (warp == 1) tc::tmem_dealloc(tmem_base, GN);
+    if (warp == 1) tc::tmem_dealloc(tmem_base, 2 * GN);
 }
 
 template <bool XU, typename IhT>
 cudaError_t launch(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long long N, int C, int Kpad,
-                   LinearConsts lc, PreScale ps, int *abort_flag, cudaStream_t st) {
+                   LinearConsts lc, PreScale ps, int *abort_flag, int sms, cudaStream_t st) {
     auto kern = k_gemm_wx_tc<XU, IhT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
     if (e != cudaSuccess) return e;
-    dim3 grid((unsigned)((C + GM - 1) / GM), (unsigned)((N + GN - 1) / GN));
+    const long long tiles = (long long)((C + GM - 1) / GM) * ((N + GN - 1) / GN);
+    const unsigned grid = (unsigned)std::min<long long>(tiles, sms);   // persistent: one CTA per SM
     kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(mw, mx, (IhT *)ih, N, C, Kpad, lc, ps, abort_flag);
     return cudaGetLastError();
 }
@@ -181,14 +215,10 @@ cudaError_t launch(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long 
 
 int tc_gemm_launch(TcGemmState &s, const uint8_t *x8, long long x_rows_alloc, const int8_t *w8,
                    long long w_rows_alloc, void *ih, long long N, int C, int Kpad, bool x_unsigned,
-                   int ih_bytes, LinearConsts lc, PreScale ps, int *abort_flag, cudaStream_t stream,
+                   int ih_bytes, LinearConsts lc, PreScale ps, int *abort_flag, int sms, cudaStream_t stream,
                    std::string *err) {
     if (Kpad % KB != 0 || x_rows_alloc < (N + GN - 1) / GN * GN || w_rows_alloc < (C + GM - 1) / GM * GM) {
         if (err) *err = "tcgen05 GEMM needs K padded to 128 and operand rows padded to the tile";
-        return QGRU_ERR_UNSUPPORTED;
-    }
-    if ((N + GN - 1) / GN > 65535) {
-        if (err) *err = "too many token tiles for one launch";
         return QGRU_ERR_UNSUPPORTED;
     }
     if (!s.valid || s.x8 != x8 || s.w8 != w8 || s.x_rows != x_rows_alloc || s.w_rows != w_rows_alloc ||
@@ -210,14 +240,14 @@ int tc_gemm_launch(TcGemmState &s, const uint8_t *x8, long long x_rows_alloc, co
     const CUtensorMap &mx = *reinterpret_cast<const CUtensorMap *>(s.map_x);
     cudaError_t e;
     if (ih_bytes == 1)
-        e = x_unsigned ? launch<true, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, stream)
-                       : launch<false, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, stream);
+        e = x_unsigned ? launch<true, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, stream)
+                       : launch<false, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, stream);
     else if (ih_bytes == 2)
-        e = x_unsigned ? launch<true, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, stream)
-                       : launch<false, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, stream);
+        e = x_unsigned ? launch<true, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, stream)
+                       : launch<false, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, stream);
     else
-        e = x_unsigned ? launch<true, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, stream)
-                       : launch<false, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, stream);
+        e = x_unsigned ? launch<true, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, stream)
+                       : launch<false, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, stream);
     if (e != cudaSuccess) {
         if (err) *err = std::string("tcgen05 GEMM launch: ") + cudaGetErrorString(e);
         return QGRU_ERR_CUDA;
