@@ -155,6 +155,11 @@ int qgru_set_option(qgru_handle *h, const char *name, const char *value) {
         else if (v == "mma") h->opt_rec = 2;
         else if (v == "generic") h->opt_rec = 3;
         else return fail(h, QGRU_ERR_BAD_ARG, "rec: auto|dp4a|mma|generic");
+    } else if (n == "exchange") {
+        if (v == "auto") h->opt_exchange = 0;
+        else if (v == "global") h->opt_exchange = 1;
+        else if (v == "cluster") h->opt_exchange = 2;
+        else return fail(h, QGRU_ERR_BAD_ARG, "exchange: auto|global|cluster");
     } else if (n == "cell") {
         if (v == "auto") h->opt_cell = 0;
         else if (v == "generic") h->opt_cell = 1;
@@ -323,6 +328,14 @@ int qgru_set_params(qgru_handle *h, const qgru_params *p, const float *scale_W,
                     const int64_t y = (int64_t)resc(v - g.zp_ih, g.ih_to[a]) + g.zp_in[a];
                     max_pre = std::max<int64_t>(max_pre, std::llabs((long long)y));
                 }
+            g.ft_ih_off = (int32_t)ft.size();
+            g.ft_ih_n = 0;
+            if (op[QGRU_OP_IH_LINEAR].bits <= 10) {
+                g.ft_ih_n = g.ih_hi - g.ih_lo + 1;
+                for (int a = 0; a < 3; ++a)
+                    for (int v = g.ih_lo; v <= g.ih_hi; ++v)
+                        ft.push_back(resc((int64_t)v - g.zp_ih, g.ih_to[a]) + g.zp_in[a]);
+            }
             const int64_t max_hd = max_abs_diff(op[QGRU_OP_H]), max_hhd = max_abs_diff(op[QGRU_OP_HH_LINEAR]);
             const int64_t lim = 0x7fffffffll;
             if (max_zd * max_hd + max_omz * max_nd >= lim || max_rd * max_hhd >= lim || max_pre >= lim) fused = false;
@@ -410,6 +423,7 @@ int finish_weights(qgru_handle *h, cudaStream_t st) {
     h->lin_fits32[1] = !(h->h_flags[0] & 16);
     h->tc.valid = false;
     h->rec.valid = false;
+    h->rec_cl.valid = false;
     h->weights_set = true;
     return QGRU_OK;
 }
@@ -522,12 +536,19 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
     RecPlan pl;
     const bool dp4a_ok = plan_recurrence(h, B, &pl);
     RecMmaPlan mp;
-    const int n_tab_mma = std::max(h->n_table, h->n_ftable);
+    const int n_tab_mma = std::max(h->n_table, h->gc_host.fused_ok ? h->gc_host.ft_ih_off : 0);
     const bool mma_ok = h->opt_rec != 1 && rec_mma_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, &mp);
     if (h->opt_rec == 2 && !mma_ok) return fail(h, QGRU_ERR_UNSUPPORTED, "tensor-core recurrence needs H <= 512");
     // Tiny batches whose R fits one SM run barrier-free on one CTA per batch row: lower latency
     // than tensor-core tiles of 16 batch columns.
-    const bool use_mma = mma_ok && (h->opt_rec == 2 || !(dp4a_ok && pl.P == 1 && B <= 4));
+    bool use_mma = mma_ok && (h->opt_rec == 2 || !(dp4a_ok && pl.P == 1 && B <= 4));
+    // state exchange through distributed shared memory (one cluster per group) where it fits
+    RecMmaPlan cp;
+    const bool use_cluster = use_mma && h->opt_exchange != 1 &&
+                             rec_cluster_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, &cp);
+    if (h->opt_exchange == 2 && use_mma && !use_cluster)
+        return fail(h, QGRU_ERR_UNSUPPORTED, "cluster exchange does not fit shared memory");
+    if (use_cluster) mp = cp;
     if (!use_mma && !dp4a_ok) return fail(h, QGRU_ERR_UNSUPPORTED, "no recurrence plan fits shared memory");
     // the fused cell needs the GEMM epilogue to pre-rescale W*x+bw: tensor-core GEMM only
     const bool fused = use_mma && h->gc_host.fused_ok && h->opt_gemm != 1 && h->opt_cell != 1;
@@ -540,6 +561,11 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
         for (int a = 0; a < 3; ++a) {
             ps.to[a] = h->gc_host.ih_to[a];
             ps.zp_in[a] = h->gc_host.zp_in[a];
+        }
+        if (h->gc_host.ft_ih_n > 0) {
+            ps.table = h->d_ftables + h->gc_host.ft_ih_off;
+            ps.table_n = h->gc_host.ft_ih_n;
+            ps.lo = h->gc_host.ih_lo;
         }
     }
     if ((rc = ensure(h, h->ih, (size_t)N * C * ih_bytes))) return rc;
@@ -591,18 +617,22 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
         a.hf_out = hf_out;
         a.lc = linear_consts(h, 1);
         a.tables = fused ? h->d_ftables : h->d_tables;
-        a.n_table = fused ? h->n_ftable : h->n_table;
+        a.n_table = fused ? h->gc_host.ft_ih_off : h->n_table;   // the GEMM-side table stays out of smem
         a.bar = h->d_bar;
         a.abort_flag = h->d_flags + 1;
         a.spin_limit = h->spin_limit;
         a.dbg = h->dbg_stamps;
-        const unsigned long long before = h->rec.launches;
-        rc = rec_mma_launch(h->rec, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256, h->h_uns,
-                            ih_bytes, h->gc_host.narrow != 0, fused, h->coop != 0, st, &h->err);
+        const unsigned long long before = h->rec.launches + h->rec_cl.launches;
+        if (use_cluster)
+            rc = rec_cluster_launch(h->rec_cl, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256,
+                                    h->h_uns, ih_bytes, h->gc_host.narrow != 0, fused, st, &h->err);
+        else
+            rc = rec_mma_launch(h->rec, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256,
+                                h->h_uns, ih_bytes, h->gc_host.narrow != 0, fused, h->coop != 0, st, &h->err);
         if (rc) return rc;
-        h->launches += h->rec.launches - before;
-        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 cell=%s MT=%d NB=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d narrow=%d ih_bytes=%d",
-                 used_tc ? "tcgen05_i8" : "simt_dp4a", fused ? "fused" : "generic", mp.MT, mp.NB, mp.P, mp.G,
+        h->launches += h->rec.launches + h->rec_cl.launches - before;
+        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 exchange=%s cell=%s MT=%d NB=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d narrow=%d ih_bytes=%d",
+                 used_tc ? "tcgen05_i8" : "simt_dp4a", use_cluster ? "cluster_dsmem" : "global", fused ? "fused" : "generic", mp.MT, mp.NB, mp.P, mp.G,
                  mp.groups_per_launch, mp.smem, mp.tmem_cols, h->gc_host.narrow, ih_bytes);
     } else {
         RecArgs a;

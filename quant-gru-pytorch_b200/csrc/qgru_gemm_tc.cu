@@ -62,7 +62,8 @@ constexpr int EPI_WARPS = 16;                      // four warps per TMEM lane q
 constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int STAGE_BYTES = (GM + GN) * KB;
 constexpr long long WAIT_BUDGET = 2000000000ll;  // ~1 s of SM clocks
-constexpr size_t GEMM_SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int PRE_TAB_MAX = 3 * 1024;              // pre-rescale table entries kept in shared memory
+constexpr size_t GEMM_SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256 + PRE_TAB_MAX * 4;
 
 template <bool XUnsigned, typename IhT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -77,6 +78,10 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     uint64_t *acc_full = bars + 2 * STAGES, *acc_empty = bars + 2 * STAGES + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
     int *failed = reinterpret_cast<int *>(tmem_slot + 1);
+    int32_t *pre_tab = reinterpret_cast<int32_t *>(tiles + (size_t)STAGES * STAGE_BYTES + 256);
+    const bool use_tab = ps.enabled && ps.table != nullptr && 3 * ps.table_n <= PRE_TAB_MAX;
+    if (use_tab)
+        for (int i = threadIdx.x; i < 3 * ps.table_n; i += blockDim.x) pre_tab[i] = ps.table[i];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = Kpad / KB;
@@ -186,7 +191,8 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                     const long long n = n0 + c0 + i;
                     int32_t y = lc.fits32 ? linear_epilogue32(v[i], c32, rs, lc.zp_out, lc.lo, lc.hi)
                                           : linear_epilogue(v[i], corr, rs, lc.zp_out, lc.lo, lc.hi);
-                    if (ps.enabled) y = (int32_t)rescale32(y - ps.zp_ih, pre_rs) + pre_zp;
+                    if (use_tab) y = pre_tab[gate * ps.table_n + (y - ps.lo)];
+                    else if (ps.enabled) y = (int32_t)rescale32(y - ps.zp_ih, pre_rs) + pre_zp;
                     if (m_ok && n < N) out[n * C] = (IhT)y;
                 }
             }

@@ -38,6 +38,7 @@ struct qgru_handle {
     int opt_gemm = 0;      // 0 auto, 1 simt, 2 tcgen05
     int opt_rec = 0;       // 0 auto, 1 dp4a, 3 generic
     int opt_sm_limit = 0;  // 0: all SMs
+    int opt_exchange = 0;  // 0 auto (cluster where it fits), 1 global counter, 2 cluster only
     int opt_cell = 0;      // 0 auto (fused cell where valid), 1 generic cell
     unsigned spin_limit = 1u << 24;
     long long *dbg_stamps = nullptr;  // profiling aid of the tensor-core recurrence kernel
@@ -70,7 +71,8 @@ struct qgru_handle {
     bool timing_valid = false;
     uint64_t launches = 0;
     TcGemmState tc;
-    qgru::RecMmaState rec;
+    qgru::RecMmaState rec;       // tensor maps of the global-exchange recurrence
+    qgru::RecMmaState rec_cl;    // tensor maps of the cluster-exchange recurrence
 };
 
 #define CK(call)                                                                          \

@@ -48,6 +48,7 @@ struct GateConsts {
     int32_t k1;                           // one_q - 2*zp_z : (1 - z) numerator minus z_d
     int32_t ft_off[5];                    // offsets of TZ, TR, TN, THZ, THR in the fused table block
     int32_t ih_pre_bytes;                 // storage width (2 or 4) of the pre-rescaled W*x+bw values
+    int32_t ft_ih_off, ft_ih_n;           // table of the GEMM-side pre-rescale in the same block (n per gate, 0: none)
     qgru_lut lut[3];
 };
 
@@ -57,6 +58,10 @@ struct PreScale {
     int32_t enabled, H, zp_ih;
     Rescale to[3];
     int32_t zp_in[3];
+    // optional table of that function over the clamped W*x+bw range (gate-major, n entries per
+    // gate, index = value - lo); null when the range is too wide to tabulate
+    const int32_t *table;
+    int32_t table_n, lo;
 };
 
 // Per output channel constants of one fused linear layer:

@@ -1,0 +1,396 @@
+// qgru_rec_cluster.cu - the tensor-core recurrence with the state exchanged through distributed
+// shared memory.
+//
+// Same work split as k_recurrence_mma (qgru_rec_mma.cu): a CTA owns 128*MT hidden units of one
+// group of NB batch rows and keeps its slice of R in shared memory for all T steps.  Here the P
+// CTAs of a group form one thread-block cluster.  After the gates every epilogue thread stores
+// its 8-bit h_t value straight into the B-operand tile of EVERY CTA of the cluster
+// (st.shared::cluster, in the 128-byte-swizzled K-major layout the MMA reads), and the cluster
+// meets at the hardware cluster barrier.  Compared with the global-memory exchange this removes,
+// per step, the gpu-scope fence, the atomic counter and its polling, the proxy fence for TMA and
+// the TMA reload of the state: h_t never leaves the SMs.  Only the outputs go to global memory.
+//
+// The tile is double buffered: step s multiplies buffer s&1 while the epilogues of the cluster
+// fill buffer (s+1)&1.  Step 0's state is loaded from global memory by TMA.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "qgru_device.cuh"
+#include "qgru_rec_mma.cuh"
+#include "qgru_tc.cuh"
+
+namespace qgru {
+namespace {
+
+constexpr long long WAIT_BUDGET = 2000000000ll;  // ~1 s of SM clocks
+constexpr int EPW = 4;                           // epilogue warps per TMEM lane quadrant
+constexpr int EPI_THREADS = 32 * 4 * EPW;
+constexpr int REC_THREADS = 32 + EPI_THREADS;
+constexpr int CH = 4;                            // batch columns per chunk
+
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_u8(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u8 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+
+// Byte offset of element (row b, byte k) inside a K-major tile of `rows` rows stored as 128-byte
+// rows with the 128-byte swizzle: slabs of 128 K-bytes follow each other; inside a slab, groups
+// of 8 rows take 1024 bytes and the 16-byte chunk index is XORed with the row index modulo 8.
+__device__ __forceinline__ uint32_t sw128_offset(int b, int k, int rows) {
+    return (uint32_t)((k >> 7) * rows * 128 + (b >> 3) * 1024 + (b & 7) * 128 +
+                      ((((k & 127) >> 4) ^ (b & 7)) << 4) + (k & 15));
+}
+
+}  // namespace
+
+struct ClusterSmem {
+    size_t r_tiles, h_tile, bars, tables, total;
+};
+
+__host__ __device__ inline ClusterSmem cluster_smem_layout(int MT, int KBn, int NB, int n_table) {
+    ClusterSmem s;
+    s.r_tiles = 0;
+    s.h_tile = (size_t)MT * 3 * KBn * 16384;
+    s.bars = s.h_tile + (size_t)2 * KBn * NB * 128;   // two state buffers
+    s.tables = s.bars + 64;
+    s.total = s.tables + (((size_t)n_table * 4 + 15) & ~size_t(15));
+    return s;
+}
+
+
+namespace {
+
+template <typename IhT, bool Narrow, bool Fused, int MT>
+__global__ void __launch_bounds__(REC_THREADS, 1)
+k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_h,
+                     const __grid_constant__ GateConsts gc, RecMmaArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    // every CTA of the cluster must compute the same offsets: the dynamic shared window starts at
+    // the same shared address in all of them, so the aligned base is the same too
+    const uint32_t raw = tc::smem_u32(smem_raw);
+    unsigned char *base = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+    const int KBn = a.Hpad >> 7;
+    const ClusterSmem L = cluster_smem_layout(MT, KBn, a.NB, a.n_table);
+    unsigned char *r_tiles = base + L.r_tiles;
+    unsigned char *h_tile = base + L.h_tile;
+    const uint32_t h_buf_bytes = (uint32_t)(KBn * a.NB * 128);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(base + L.bars);
+    uint64_t *r_full = bars, *h_full = bars + 1, *mma_done = bars + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 4);
+    int32_t *tables = reinterpret_cast<int32_t *>(base + L.tables);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    const int grp = blockIdx.x / a.P;
+    const int p = (int)cluster_rank();               // == blockIdx.x % P: clusters are P consecutive CTAs
+    const int j0 = p * 128 * MT;
+    const int b0 = a.b_off + grp * a.NB;
+    const int nb = min(a.NB, a.b_off + a.b_cnt - b0);
+    const uint32_t tmem_cols = a.tmem_cols;
+
+    for (int i = tid; i < a.n_table; i += blockDim.x) tables[i] = a.tables[i];
+    if (tid == 0) {
+        tc::mbar_init(r_full, 1);
+        tc::mbar_init(h_full, 1);
+        tc::mbar_init(mma_done, 1);
+        tc::fence_barrier_init();
+        tc::tma_prefetch_desc(&map_r);
+        tc::tma_prefetch_desc(&map_h);
+    }
+    if (warp == 0) tc::tmem_alloc(tmem_slot, tmem_cols);
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    // no CTA may receive remote stores before it has finished setting up
+    cluster_arrive();
+    cluster_wait();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ control warp
+        bool ok = true;
+        uint32_t idesc = 0, r_lo0 = 0, h_lo0 = 0, desc_hi = 0, desc_lo = 0;
+        if (lane == 0) {
+            tc::mbar_expect_tx(r_full, (uint32_t)(MT * 3 * KBn) * 16384u);
+            for (int mt = 0; mt < MT; ++mt)
+                for (int g = 0; g < 3; ++g)
+                    for (int kb = 0; kb < KBn; ++kb)
+                        tc::tma_load_2d(r_tiles + (size_t)((mt * 3 + g) * KBn + kb) * 16384, &map_r, r_full,
+                                        kb * 128, g * a.H + j0 + mt * 128);
+            // the initial state (written by the preceding kernel) into buffer 0
+            tc::mbar_expect_tx(h_full, h_buf_bytes);
+            for (int kb = 0; kb < KBn; ++kb)
+                tc::tma_load_2d(h_tile + (size_t)kb * a.NB * 128, &map_h, h_full, kb * 128, b0);
+            ok = tc::mbar_wait(r_full, 0, WAIT_BUDGET) && tc::mbar_wait(h_full, 0, WAIT_BUDGET);
+            idesc = tc::idesc_i8(128, a.NB, true, !a.h_unsigned);
+            r_lo0 = (tc::smem_u32(r_tiles) & 0x3FFFFu) >> 4;
+            h_lo0 = (tc::smem_u32(h_tile) & 0x3FFFFu) >> 4;
+            desc_hi = (uint32_t)(tc::smem_desc_sw128(0) >> 32);
+            desc_lo = (uint32_t)tc::smem_desc_sw128(0);
+            if (!ok) atomicOr(a.abort_flag, 1);
+        }
+        for (int s = 0; s < a.T; ++s) {
+            if (lane == 0 && ok) {
+                if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 1] = clock64();
+                // the tile of this step was written by generic-proxy stores of the whole cluster
+                fence_proxy_async_all();
+                tc::tc_fence_after_sync();
+                const uint32_t hbuf = h_lo0 + (uint32_t)(s & 1) * (h_buf_bytes >> 4);
+                for (int mt = 0; mt < MT; ++mt)
+                    for (int kb = 0; kb < KBn; ++kb) {
+                        const uint32_t hb = hbuf + (uint32_t)(kb * a.NB * 8);
+#pragma unroll
+                        for (int g = 0; g < 3; ++g) {
+                            const uint32_t d = tmem_base + (uint32_t)((mt * 3 + g) * a.NB);
+                            const uint32_t rb = r_lo0 + (uint32_t)(((mt * 3 + g) * KBn + kb) * 1024);
+#pragma unroll
+                            for (int ks = 0; ks < 4; ++ks)
+                                tc::mma_i8(d, ((uint64_t)desc_hi << 32) | (desc_lo | (rb + 2 * ks)),
+                                           ((uint64_t)desc_hi << 32) | (desc_lo | (hb + 2 * ks)), idesc,
+                                           (kb | ks) != 0);
+                        }
+                    }
+                tc::mma_commit(mma_done);
+                if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 3] = clock64();
+            }
+            __syncwarp();
+            // end of step: every CTA of the cluster has filled the next buffer everywhere
+            cluster_arrive();
+            cluster_wait();
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue warps
+        const int q = warp & 3;                      // TMEM lane quadrant this warp may read
+        const int rank = (warp - 1) >> 2;            // 0..EPW-1 among the warps of that quadrant
+        const int u = q * 32 + lane;                 // unit within a 128-unit tile = TMEM lane
+        const size_t BH = (size_t)a.B * a.H;
+        const IhT *ihp = reinterpret_cast<const IhT *>(a.ih);
+        const int nchunks = a.NB / CH;
+        const uint32_t h_tile_addr = tc::smem_u32(h_tile);
+        int64_t corr[MT][3];
+        Rescale rs[MT][3];
+        bool j_ok[MT];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            const int j = j0 + mt * 128 + u;
+            j_ok[mt] = j < a.H;
+#pragma unroll
+            for (int g = 0; g < 3; ++g) {
+                corr[mt][g] = j_ok[mt] ? a.lc.corr[g * a.H + j] : 0;
+                rs[mt][g] = j_ok[mt] ? a.lc.rs[g * a.H + j] : Rescale{1, 1};
+            }
+        }
+        // the TMA-written initial state must be complete before h_{t-1} is read from the tile
+        bool ok = tc::mbar_wait(h_full, 0, WAIT_BUDGET);
+        for (int s = 0; s < a.T; ++s) {
+            const int t = a.reverse ? (a.T - 1 - s) : s;
+            const long long out_slot = a.reverse ? (a.T - 1 - s) : (s + 1);
+            const unsigned char *h_cur = h_tile + (size_t)(s & 1) * h_buf_bytes;
+            const uint32_t h_nxt_addr = h_tile_addr + (uint32_t)((s + 1) & 1) * h_buf_bytes;
+            bool waited = false;
+            for (int c = rank; c < nchunks && ok; c += EPW) {
+                const int c0 = c * CH;
+                // operands that do not depend on this step's MMA: issued first
+                int32_t ihv[MT][CH][3];
+                int32_t hold[MT][CH];
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const int j = j0 + mt * 128 + u;
+#pragma unroll
+                    for (int i = 0; i < CH; ++i) {
+                        const int b = c0 + i;
+                        const bool v_ok = b < nb && j_ok[mt];
+                        const size_t row = (size_t)t * a.B + b0 + b;
+#pragma unroll
+                        for (int g = 0; g < 3; ++g)
+                            ihv[mt][i][g] = v_ok ? (int32_t)ihp[row * a.C + g * a.H + j] : 0;
+                        const uint8_t hb = v_ok ? h_cur[sw128_offset(b, j, a.NB)] : (uint8_t)0;
+                        hold[mt][i] = a.h_unsigned ? (int32_t)hb : (int32_t)(int8_t)hb;
+                    }
+                }
+                if (!waited) {
+                    ok = tc::mbar_wait(mma_done, (uint32_t)(s & 1), WAIT_BUDGET);
+                    if (!ok) break;
+                    tc::tc_fence_after_sync();
+                    waited = true;
+                    if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0) a.dbg[s * 8 + 4] = clock64();
+                }
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const int j = j0 + mt * 128 + u;
+                    int32_t az[CH], ar[CH], an[CH];
+                    const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * 3 * a.NB + c0);
+                    tc::tmem_ld4(ta, az);
+                    tc::tmem_ld4(ta + a.NB, ar);
+                    tc::tmem_ld4(ta + 2 * a.NB, an);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < CH; ++i) {
+                        const int b = c0 + i;
+                        if (b >= nb || !j_ok[mt]) continue;
+                        int32_t hh_z, hh_r, hh_n;
+                        if (a.lc.fits32) {
+                            hh_z = linear_epilogue32(az[i], (int32_t)corr[mt][0], rs[mt][0], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                            hh_r = linear_epilogue32(ar[i], (int32_t)corr[mt][1], rs[mt][1], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                            hh_n = linear_epilogue32(an[i], (int32_t)corr[mt][2], rs[mt][2], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                        } else {
+                            hh_z = linear_epilogue(az[i], corr[mt][0], rs[mt][0], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                            hh_r = linear_epilogue(ar[i], corr[mt][1], rs[mt][1], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                            hh_n = linear_epilogue(an[i], corr[mt][2], rs[mt][2], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                        }
+                        int32_t hn;
+                        if constexpr (Fused)
+                            hn = gru_cell_fused(gc, tables, ihv[mt][i][0], ihv[mt][i][1], ihv[mt][i][2], hh_z, hh_r,
+                                                hh_n, hold[mt][i]);
+                        else
+                            hn = gru_cell<Narrow>(gc, tables, ihv[mt][i][0], ihv[mt][i][1], ihv[mt][i][2], hh_z,
+                                                  hh_r, hh_n, hold[mt][i]);
+                        // h_t[b][j] becomes element (row b, K index j) of every CTA's next B tile
+                        const uint32_t dst = h_nxt_addr + sw128_offset(b, j, a.NB);
+                        for (int r = 0; r < a.P; ++r) st_cluster_u8(map_to_rank(dst, (uint32_t)r), (uint32_t)hn & 0xffu);
+                        const size_t o = (size_t)out_slot * BH + (size_t)(b0 + b) * a.H + j;
+                        if (a.hq_out) a.hq_out[o] = hn;
+                        if (a.hf_out) a.hf_out[o] = (float)(hn - gc.zp_h) * gc.h_scale;
+                    }
+                }
+            }
+            if (ok && !waited) {   // a warp without a chunk still follows the phase of the MMA barrier
+                ok = tc::mbar_wait(mma_done, (uint32_t)(s & 1), WAIT_BUDGET);
+                tc::tc_fence_after_sync();
+            }
+            if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0) a.dbg[s * 8 + 7] = clock64();
+            // the next MMA reads these generic-proxy stores through the async proxy
+            fence_proxy_async_all();
+            tc::tc_fence_before_sync();
+            __syncwarp();
+            cluster_arrive();
+            cluster_wait();
+            if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0) {
+                a.dbg[s * 8 + 5] = clock64();
+                a.dbg[(s + 1 < a.T ? s + 1 : s) * 8 + 0] = a.dbg[s * 8 + 5];
+            }
+        }
+        if (!ok && lane == 0) atomicOr(a.abort_flag, 1);
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
+}
+
+template <typename IhT, bool Narrow, bool Fused, int MT>
+cudaError_t launch_one(const CUtensorMap &mr, const CUtensorMap &mh, const GateConsts &gc, RecMmaArgs &a,
+                       int grid, size_t smem, cudaStream_t st) {
+    auto kern = k_recurrence_cluster<IhT, Narrow, Fused, MT>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(REC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)a.P;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, mr, mh, gc, a);
+}
+
+template <typename IhT, bool Narrow, bool Fused>
+cudaError_t launch_mt(int MT, const CUtensorMap &mr, const CUtensorMap &mh, const GateConsts &gc,
+                      RecMmaArgs &a, int grid, size_t smem, cudaStream_t st) {
+    return MT == 2 ? launch_one<IhT, Narrow, Fused, 2>(mr, mh, gc, a, grid, smem, st)
+                   : launch_one<IhT, Narrow, Fused, 1>(mr, mh, gc, a, grid, smem, st);
+}
+
+cudaError_t launch_any(bool fused, bool narrow, int ih_bytes, int MT, const CUtensorMap &mr,
+                       const CUtensorMap &mh, const GateConsts &gc, RecMmaArgs &a, int grid, size_t smem,
+                       cudaStream_t st) {
+    if (fused)
+        return ih_bytes == 2 ? launch_mt<int16_t, false, true>(MT, mr, mh, gc, a, grid, smem, st)
+                             : launch_mt<int32_t, false, true>(MT, mr, mh, gc, a, grid, smem, st);
+    if (ih_bytes == 1)
+        return narrow ? launch_mt<int8_t, true, false>(MT, mr, mh, gc, a, grid, smem, st)
+                      : launch_mt<int8_t, false, false>(MT, mr, mh, gc, a, grid, smem, st);
+    return narrow ? launch_mt<int16_t, true, false>(MT, mr, mh, gc, a, grid, smem, st)
+                  : launch_mt<int16_t, false, false>(MT, mr, mh, gc, a, grid, smem, st);
+}
+
+}  // namespace
+
+bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, RecMmaPlan *out) {
+    if (Hpad > 512) return false;                  // the R slice of 128 units must fit one SM
+    const int KBn = Hpad / 128;
+    const int MT = (H > 128 && H <= 256) ? 2 : 1;
+    const int P = (H + 128 * MT - 1) / (128 * MT);  // cluster size: 1..4
+    if (P > 8 || P > sms) return false;
+    const int groups_max = std::max(1, sms / P);
+    int NB = ((B + groups_max - 1) / groups_max + 15) / 16 * 16;
+    const int nb_cap = MT == 2 ? 64 : 128;         // 3*MT*NB accumulator columns <= 512
+    NB = std::min(NB, nb_cap);
+    while (NB > 16 && cluster_smem_layout(MT, KBn, NB, n_table).total + 1024 > (size_t)smem_optin) NB -= 16;
+    const size_t smem = cluster_smem_layout(MT, KBn, NB, n_table).total + 1024;
+    if (smem > (size_t)smem_optin) return false;
+    uint32_t cols = 32;
+    while ((int)cols < 3 * MT * NB) cols <<= 1;
+    out->MT = MT;
+    out->P = P;
+    out->NB = NB;
+    out->G = (B + NB - 1) / NB;
+    out->smem = smem;
+    out->tmem_cols = (int)cols;
+    out->groups_per_launch = out->G;               // clusters are scheduled as SMs free up
+    return true;
+}
+
+int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const GateConsts &gc_host,
+                       const int8_t *r8, long long r_rows_alloc, long long h_rows_alloc, bool h_unsigned,
+                       int ih_bytes, bool narrow, bool fused, cudaStream_t stream, std::string *err) {
+    if (!s.valid || s.r8 != r8 || s.h8 != a.h8 || s.r_rows != r_rows_alloc || s.h_rows != h_rows_alloc ||
+        s.Hpad != a.Hpad || s.NB != pl.NB) {
+        if (!make_map_u8_sw128(reinterpret_cast<CUtensorMap *>(s.map_r), r8, (uint64_t)r_rows_alloc, (uint64_t)a.Hpad, 128) ||
+            !make_map_u8_sw128(reinterpret_cast<CUtensorMap *>(s.map_h), a.h8, (uint64_t)h_rows_alloc, (uint64_t)a.Hpad, (uint32_t)pl.NB)) {
+            if (err) *err = "cuTensorMapEncodeTiled failed";
+            return QGRU_ERR_CUDA;
+        }
+        s.valid = true;
+        s.r8 = r8;
+        s.h8 = a.h8;
+        s.r_rows = r_rows_alloc;
+        s.h_rows = h_rows_alloc;
+        s.Hpad = a.Hpad;
+        s.NB = pl.NB;
+    }
+    const CUtensorMap &mr = *reinterpret_cast<const CUtensorMap *>(s.map_r);
+    const CUtensorMap &mh = *reinterpret_cast<const CUtensorMap *>(s.map_h);
+    a.P = pl.P;
+    a.NB = pl.NB;
+    a.h_unsigned = h_unsigned ? 1 : 0;
+    a.tmem_cols = (uint32_t)pl.tmem_cols;
+    a.b_off = 0;
+    a.b_cnt = a.B;
+    const cudaError_t e = launch_any(fused, narrow, ih_bytes, pl.MT, mr, mh, gc_host, a, pl.G * pl.P, pl.smem, stream);
+    if (e != cudaSuccess) {
+        if (err) *err = std::string("recurrence (cluster) launch: ") + cudaGetErrorString(e);
+        cudaGetLastError();
+        return QGRU_ERR_CUDA;
+    }
+    ++s.launches;
+    return QGRU_OK;
+}
+
+}  // namespace qgru

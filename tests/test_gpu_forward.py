@@ -59,15 +59,20 @@ def _want(oracle, case):
                               case.params.scale_list())
 
 
-@pytest.mark.parametrize("rec", ["dp4a", "mma"])
+@pytest.mark.parametrize("rec", ["dp4a", "mma_cluster", "mma_global"])
 @pytest.mark.parametrize("shape", SHAPES)
 def test_shapes_default_config(oracle, cuda_device, shape, rec):
-    """Both recurrence kernels (dp4a and tcgen05) on every shape; the GEMM is tcgen05."""
+    """The dp4a recurrence and the tcgen05 recurrence with both ways of exchanging the state
+    (distributed shared memory in a cluster, global counter) on every shape; tcgen05 GEMM."""
     T, B, I, H = shape
     case = make_case(11, T, B, I, H, oracle, config_named("default"))
-    got, plan, launches = _run(case, cuda_device, opts=(("rec", rec),))
+    opts = {"dp4a": (("rec", "dp4a"),), "mma_cluster": (("rec", "mma"), ("exchange", "cluster")),
+            "mma_global": (("rec", "mma"), ("exchange", "global"))}[rec]
+    got, plan, launches = _run(case, cuda_device, opts=opts)
     assert "path=int8" in plan and launches > 0
-    assert ("rec=tcgen05_i8" in plan) == (rec == "mma") and "gemm=tcgen05_i8" in plan
+    assert ("rec=tcgen05_i8" in plan) == (rec != "dp4a") and "gemm=tcgen05_i8" in plan
+    if rec != "dp4a":
+        assert ("exchange=cluster_dsmem" in plan) == (rec == "mma_cluster")
     assert np.array_equal(got, _want(oracle, case)), plan
 
 
@@ -94,7 +99,9 @@ def test_large_batch_many_groups(oracle, cuda_device):
 def test_bitwidth_configs(oracle, cuda_device, name):
     for seed, (T, B, I, H) in enumerate([(7, 6, 24, 48), (4, 9, 40, 72)]):
         case = make_case(20 + seed, T, B, I, H, oracle, config_named(name), with_h0=(seed == 1))
-        for opts in ((("rec", "mma"),), (("rec", "mma"), ("cell", "generic")), (("rec", "dp4a"),)):
+        for opts in ((("rec", "mma"),), (("rec", "mma"), ("cell", "generic")), (("rec", "dp4a"),),
+                     (("rec", "mma"), ("exchange", "global")),
+                     (("rec", "mma"), ("exchange", "global"), ("cell", "generic"))):
             got, plan, _ = _run(case, cuda_device, opts=opts)
             assert "path=int8" in plan
             assert np.array_equal(got, _want(oracle, case)), (name, plan)
