@@ -3,15 +3,19 @@
 //
 // Same work split as k_recurrence_mma (qgru_rec_mma.cu): a CTA owns 128*MT hidden units of one
 // group of NB batch rows and keeps its slice of R in shared memory for all T steps.  Here the P
-// CTAs of a group form one thread-block cluster.  After the gates every epilogue thread stores
-// its 8-bit h_t value straight into the B-operand tile of EVERY CTA of the cluster
-// (st.shared::cluster, in the 128-byte-swizzled K-major layout the MMA reads), and the cluster
-// meets at the hardware cluster barrier.  Compared with the global-memory exchange this removes,
-// per step, the gpu-scope fence, the atomic counter and its polling, the proxy fence for TMA and
-// the TMA reload of the state: h_t never leaves the SMs.  Only the outputs go to global memory.
+// CTAs of a group form one thread-block cluster and h_t never leaves the SMs.  The 128 units of
+// CTA p are exactly K-slab p of the B-operand tile (NB rows x 128 bytes, 128-byte swizzle), a
+// contiguous NB*128-byte block.  Each epilogue thread stores its 8-bit h_t value into that block
+// of its OWN tile; one thread then pushes the block into the same place of every peer's tile
+// with a bulk asynchronous copy (cp.async.bulk.shared::cluster) that signals the peer's
+// mbarrier.  A CTA starts the MMAs of a step when its own block is written and the P-1 peer
+// blocks have arrived: no cluster-wide barrier, no global-memory round trip, no gpu-scope
+// fence, no polling.  Only the outputs go to global memory.
 //
-// The tile is double buffered: step s multiplies buffer s&1 while the epilogues of the cluster
-// fill buffer (s+1)&1.  Step 0's state is loaded from global memory by TMA.
+// The tile is double buffered: step s multiplies buffer s&1 while the blocks of h_{s+1} land in
+// buffer (s+1)&1.  A peer can never be more than one step ahead (its MMAs of step s+1 need this
+// CTA's block of h_{s+1}), which is what makes two buffers enough.  Step 0's state is loaded
+// from global memory by TMA.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -28,7 +32,6 @@ constexpr int EPI_THREADS = 32 * 4 * EPW;
 constexpr int REC_THREADS = 32 + EPI_THREADS;
 constexpr int CH = 4;                            // batch columns per chunk
 
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -42,9 +45,15 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t ran
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
     return r;
 }
-__device__ __forceinline__ void st_cluster_u8(uint32_t addr, uint32_t v) {
-    asm volatile("st.shared::cluster.u8 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+// bulk copy of `bytes` (multiple of 16) from own shared memory into a peer's; completion is
+// counted in bytes on the peer's mbarrier (both destination addresses are cluster addresses)
+__device__ __forceinline__ void bulk_push(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes,
+                                          uint32_t mbar_cluster) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_cluster), "r"(src_cta), "r"(bytes), "r"(mbar_cluster)
+                 : "memory");
 }
+__device__ __forceinline__ void fence_proxy_async_cta() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Byte offset of element (row b, byte k) inside a K-major tile of `rows` rows stored as 128-byte
 // rows with the 128-byte swizzle: slabs of 128 K-bytes follow each other; inside a slab, groups
@@ -88,8 +97,9 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
     unsigned char *h_tile = base + L.h_tile;
     const uint32_t h_buf_bytes = (uint32_t)(KBn * a.NB * 128);
     uint64_t *bars = reinterpret_cast<uint64_t *>(base + L.bars);
-    uint64_t *r_full = bars, *h_full = bars + 1, *mma_done = bars + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 4);
+    uint64_t *r_full = bars, *h_full = bars + 1, *mma_done = bars + 2, *h_written = bars + 3;
+    uint64_t *h_ready = bars + 4;                    // [2]: peer blocks of the tile buffer have landed
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 6);
     int32_t *tables = reinterpret_cast<int32_t *>(base + L.tables);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
@@ -105,6 +115,9 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
         tc::mbar_init(r_full, 1);
         tc::mbar_init(h_full, 1);
         tc::mbar_init(mma_done, 1);
+        tc::mbar_init(h_written, EPI_THREADS);
+        tc::mbar_init(&h_ready[0], 1);
+        tc::mbar_init(&h_ready[1], 1);
         tc::fence_barrier_init();
         tc::tma_prefetch_desc(&map_r);
         tc::tma_prefetch_desc(&map_h);
@@ -114,7 +127,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    // no CTA may receive remote stores before it has finished setting up
+    // no CTA may receive a peer's block before its barriers are initialised
     cluster_arrive();
     cluster_wait();
 
@@ -141,34 +154,50 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
             desc_lo = (uint32_t)tc::smem_desc_sw128(0);
             if (!ok) atomicOr(a.abort_flag, 1);
         }
-        for (int s = 0; s < a.T; ++s) {
-            if (lane == 0 && ok) {
+        if (lane == 0) {
+            const uint32_t blk_bytes = (uint32_t)(a.NB * 128);           // one K-slab of the tile
+            const uint32_t my_blk = (uint32_t)p * blk_bytes;             // MT == 1 whenever P > 1
+            for (int s = 0; s < a.T && ok; ++s) {
+                const uint32_t buf_off = (uint32_t)(s & 1) * h_buf_bytes;
+                if (s > 0) {
+                    // own block of h_s: written by this CTA's epilogue threads in step s-1
+                    if (!tc::mbar_wait(h_written, (uint32_t)((s - 1) & 1), WAIT_BUDGET)) { ok = false; break; }
+                    if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 0] = clock64();
+                    if (a.P > 1) {
+                        const uint32_t src = tc::smem_u32(h_tile) + buf_off + my_blk;
+                        const uint32_t bar_local = tc::smem_u32(&h_ready[s & 1]);
+                        for (int r = 0; r < a.P; ++r)
+                            if (r != p) bulk_push(map_to_rank(src, (uint32_t)r), src, blk_bytes, map_to_rank(bar_local, (uint32_t)r));
+                        // the P-1 peer blocks of h_s
+                        tc::mbar_expect_tx(&h_ready[s & 1], (uint32_t)(a.P - 1) * blk_bytes);
+                        if (!tc::mbar_wait(&h_ready[s & 1], (uint32_t)(((s - 1) >> 1) & 1), WAIT_BUDGET)) { ok = false; break; }
+                    }
+                }
                 if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 1] = clock64();
-                // the tile of this step was written by generic-proxy stores of the whole cluster
-                fence_proxy_async_all();
                 tc::tc_fence_after_sync();
-                const uint32_t hbuf = h_lo0 + (uint32_t)(s & 1) * (h_buf_bytes >> 4);
-                for (int mt = 0; mt < MT; ++mt)
-                    for (int kb = 0; kb < KBn; ++kb) {
-                        const uint32_t hb = hbuf + (uint32_t)(kb * a.NB * 8);
+                const uint32_t hbuf = h_lo0 + (buf_off >> 4);
+                // consecutive MMAs go to different accumulators (3*MT independent chains)
+                for (int kb = 0; kb < KBn; ++kb) {
+                    const uint32_t hb = hbuf + (uint32_t)(kb * a.NB * 8);
 #pragma unroll
-                        for (int g = 0; g < 3; ++g) {
-                            const uint32_t d = tmem_base + (uint32_t)((mt * 3 + g) * a.NB);
-                            const uint32_t rb = r_lo0 + (uint32_t)(((mt * 3 + g) * KBn + kb) * 1024);
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint64_t bd = ((uint64_t)desc_hi << 32) | (desc_lo | (hb + 2 * ks));
 #pragma unroll
-                            for (int ks = 0; ks < 4; ++ks)
-                                tc::mma_i8(d, ((uint64_t)desc_hi << 32) | (desc_lo | (rb + 2 * ks)),
-                                           ((uint64_t)desc_hi << 32) | (desc_lo | (hb + 2 * ks)), idesc,
+                        for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                            for (int g = 0; g < 3; ++g) {
+                                const uint32_t d = tmem_base + (uint32_t)((mt * 3 + g) * a.NB);
+                                const uint32_t rb = r_lo0 + (uint32_t)(((mt * 3 + g) * KBn + kb) * 1024);
+                                tc::mma_i8(d, ((uint64_t)desc_hi << 32) | (desc_lo | (rb + 2 * ks)), bd, idesc,
                                            (kb | ks) != 0);
+                            }
                         }
                     }
+                }
                 tc::mma_commit(mma_done);
                 if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 3] = clock64();
             }
-            __syncwarp();
-            // end of step: every CTA of the cluster has filled the next buffer everywhere
-            cluster_arrive();
-            cluster_wait();
+            if (!ok) atomicOr(a.abort_flag, 1);
         }
     } else {
         // ---------------------------------------------------------------- epilogue warps
@@ -178,7 +207,6 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
         const size_t BH = (size_t)a.B * a.H;
         const IhT *ihp = reinterpret_cast<const IhT *>(a.ih);
         const int nchunks = a.NB / CH;
-        const uint32_t h_tile_addr = tc::smem_u32(h_tile);
         int64_t corr[MT][3];
         Rescale rs[MT][3];
         bool j_ok[MT];
@@ -198,7 +226,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
             const int t = a.reverse ? (a.T - 1 - s) : s;
             const long long out_slot = a.reverse ? (a.T - 1 - s) : (s + 1);
             const unsigned char *h_cur = h_tile + (size_t)(s & 1) * h_buf_bytes;
-            const uint32_t h_nxt_addr = h_tile_addr + (uint32_t)((s + 1) & 1) * h_buf_bytes;
+            unsigned char *h_nxt = h_tile + (size_t)((s + 1) & 1) * h_buf_bytes;
             bool waited = false;
             for (int c = rank; c < nchunks && ok; c += EPW) {
                 const int c0 = c * CH;
@@ -238,8 +266,10 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     tc::tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < CH; ++i) {
+                        // computed for every lane (inputs of absent rows/units are zeros and every
+                        // table index is clamped), so the four chains interleave; only stores are guarded
                         const int b = c0 + i;
-                        if (b >= nb || !j_ok[mt]) continue;
+                        const bool v_ok = b < nb && j_ok[mt];
                         int32_t hh_z, hh_r, hh_n;
                         if (a.lc.fits32) {
                             hh_z = linear_epilogue32(az[i], (int32_t)corr[mt][0], rs[mt][0], a.lc.zp_out, a.lc.lo, a.lc.hi);
@@ -258,11 +288,13 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                             hn = gru_cell<Narrow>(gc, tables, ihv[mt][i][0], ihv[mt][i][1], ihv[mt][i][2], hh_z,
                                                   hh_r, hh_n, hold[mt][i]);
                         // h_t[b][j] becomes element (row b, K index j) of every CTA's next B tile
-                        const uint32_t dst = h_nxt_addr + sw128_offset(b, j, a.NB);
-                        for (int r = 0; r < a.P; ++r) st_cluster_u8(map_to_rank(dst, (uint32_t)r), (uint32_t)hn & 0xffu);
-                        const size_t o = (size_t)out_slot * BH + (size_t)(b0 + b) * a.H + j;
-                        if (a.hq_out) a.hq_out[o] = hn;
-                        if (a.hf_out) a.hf_out[o] = (float)(hn - gc.zp_h) * gc.h_scale;
+                        if (v_ok) {
+                            // h_t[b][j] = element (row b, K index j) of the next B tile: own K-slab
+                            h_nxt[sw128_offset(b, j, a.NB)] = (unsigned char)hn;
+                            const size_t o = (size_t)out_slot * BH + (size_t)(b0 + b) * a.H + j;
+                            if (a.hq_out) a.hq_out[o] = hn;
+                            if (a.hf_out) a.hf_out[o] = (float)(hn - gc.zp_h) * gc.h_scale;
+                        }
                     }
                 }
             }
@@ -271,21 +303,19 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                 tc::tc_fence_after_sync();
             }
             if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0) a.dbg[s * 8 + 7] = clock64();
-            // the next MMA reads these generic-proxy stores through the async proxy
-            fence_proxy_async_all();
+            // the bulk copy and the next MMA read these generic-proxy stores through the async proxy
+            fence_proxy_async_cta();
             tc::tc_fence_before_sync();
-            __syncwarp();
-            cluster_arrive();
-            cluster_wait();
-            if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0) {
-                a.dbg[s * 8 + 5] = clock64();
-                a.dbg[(s + 1 < a.T ? s + 1 : s) * 8 + 0] = a.dbg[s * 8 + 5];
-            }
+            tc::mbar_arrive(h_written);
+            if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0) a.dbg[s * 8 + 5] = clock64();
         }
         if (!ok && lane == 0) atomicOr(a.abort_flag, 1);
     }
     tc::tc_fence_before_sync();
     __syncthreads();
+    // nobody leaves while a peer's copy into, or out of, its shared memory may be in flight
+    cluster_arrive();
+    cluster_wait();
     if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
 }
 
