@@ -137,6 +137,12 @@ QGRU_API int qgru_encode_mshift(float scale, uint16_t *multiplier, int8_t *shift
 /* rshift_round(int64) (include/quantize_ops_helper.h:183-206). */
 QGRU_API int64_t qgru_rshift_round(int64_t x, int n);
 
+/* applyRescale (include/quantize_ops_helper.h:228-230) for a 32-bit operand, computed by the
+ * very routine the kernels use: rshift_round(x * multiplier, shift), through the shift-free
+ * form (one 32x32->64 multiply by the left-aligned multiplier, rounding on the high word) for
+ * shifts 17..48 (2..33 when multiplier is 1), else through 64-bit shifts. */
+QGRU_API int32_t qgru_apply_rescale(int32_t x, uint16_t multiplier, int shift);
+
 /* Evaluate one LUT the way piecewise_linear does (include/quantize_ops_helper.h:600-606). */
 QGRU_API int32_t qgru_lut_eval(const qgru_lut *lut, int32_t q_x, const qgru_op *in_bw,
                                const qgru_op *out_bw);
@@ -256,8 +262,14 @@ QGRU_API uint64_t qgru_launch_count(const qgru_handle *h);
  * ("gemm=tcgen05_i8 rec=mma ..."), for benchmarks and tests. */
 QGRU_API const char *qgru_describe_plan(qgru_handle *h, int T, int B);
 
-/* Restrict or force kernel choices (testing): name/value pairs such as
- * ("gemm","simt"), ("rec","generic").  Unknown names return QGRU_ERR_BAD_ARG. */
+/* Restrict or force kernel choices (testing).  Names and values:
+ *   "gemm"     auto | simt | tcgen05        W*x kernel
+ *   "rec"      auto | dp4a | mma | generic  recurrence kernel (generic = int32 storage path)
+ *   "exchange" auto | global | cluster      how the CTAs of a batch group exchange h_t
+ *   "cell"     auto | fused | generic       gate datapath: tabulated (auto also allows its
+ *                                           shift-free form), or the reference's step by step
+ *   "sm_limit" n   use at most n SMs (0 = all);  "spin_limit" n   bound of the group barrier
+ * Unknown names or values return QGRU_ERR_BAD_ARG. */
 QGRU_API int qgru_set_option(qgru_handle *h, const char *name, const char *value);
 
 /* ------------------------------------------------------- float mode / calibration */

@@ -57,6 +57,7 @@ SYMBOLS = {
     "qgru_version": (C.c_char_p, []),
     "qgru_encode_mshift": (C.c_int, [C.c_float, C.POINTER(C.c_uint16), C.POINTER(C.c_int8)]),
     "qgru_rshift_round": (C.c_int64, [C.c_int64, C.c_int]),
+    "qgru_apply_rescale": (C.c_int32, [C.c_int32, C.c_uint16, C.c_int]),
     "qgru_lut_eval": (C.c_int32, [C.POINTER(Lut), C.c_int32, C.POINTER(Op), C.POINTER(Op)]),
     "qgru_generate_luts": (C.c_int, [C.POINTER(Params)]),
     "qgru_calc_params_from_ranges": (C.c_int, [C.POINTER(Ranges), C.POINTER(Params), _F, _F, _F, _F]),

@@ -41,7 +41,7 @@ struct RecPlan {
 size_t rec_smem(const qgru_handle *h, int Hs, int Bt) {
     size_t s = (sizeof(GateConsts) + 15) & ~size_t(15);
     s += ((size_t)h->n_table * 4 + 15) & ~size_t(15);
-    s += (size_t)3 * Hs * 16;
+    s += (size_t)3 * Hs * (8 + sizeof(Rescale));
     s += (size_t)3 * Hs * h->Hpad;
     s += (size_t)Bt * h->Hpad;
     return s;
@@ -163,7 +163,8 @@ int qgru_set_option(qgru_handle *h, const char *name, const char *value) {
     } else if (n == "cell") {
         if (v == "auto") h->opt_cell = 0;
         else if (v == "generic") h->opt_cell = 1;
-        else return fail(h, QGRU_ERR_BAD_ARG, "cell: auto|generic");
+        else if (v == "fused") h->opt_cell = 2;   // tabulated cell, but never its shift-free form
+        else return fail(h, QGRU_ERR_BAD_ARG, "cell: auto|generic|fused");
     } else if (n == "debug_stamps") {
         // address (decimal) of a device buffer of T*8 int64 clock stamps, 0 to switch off
         h->dbg_stamps = reinterpret_cast<long long *>(strtoull(value, nullptr, 10));
@@ -250,6 +251,15 @@ int qgru_set_params(qgru_handle *h, const qgru_params *p, const float *scale_W,
             const int n = (int)(int8_t)p->lut[a].seg[s].n_bx;
             if (n > 62 || n < -62) return fail(h, QGRU_ERR_UNSUPPORTED, "LUT shift outside [-62, 62]");
         }
+    for (Rescale *r : {&g.ih_to[0], &g.ih_to[1], &g.ih_to[2], &g.hh_to[0], &g.hh_to[1], &g.rh_to_n, &g.n_to_h, &g.uh_to_h})
+        set_fast_form(r);
+    h->rs_fast[0] = h->rs_fast[1] = true;
+    for (int c = 0; c < C; ++c) {
+        set_fast_form(&rs_x[c]);
+        set_fast_form(&rs_h[c]);
+        h->rs_fast[0] = h->rs_fast[0] && rs_x[c].mq != 0;
+        h->rs_fast[1] = h->rs_fast[1] && rs_h[c].mq != 0;
+    }
     // quant_one_in_update_gate_scale_ (src/gru_forward_gpu_quant.cu:719-720)
     g.one_q = (int32_t)rintf(1.0f / op[QGRU_OP_UPDATE_OUT].scale) + op[QGRU_OP_UPDATE_OUT].zero_point;
     g.h_lo = op_qmin(op[QGRU_OP_H]);
@@ -623,17 +633,21 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
         a.spin_limit = h->spin_limit;
         a.dbg = h->dbg_stamps;
         const unsigned long long before = h->rec.launches + h->rec_cl.launches;
+        // the branch-free fused cell: every scale of the step in shift-free form, 32-bit sums
+        const bool fast_cell = fused && use_cluster && h->opt_cell != 2 && a.lc.fits32 && h->rs_fast[1] &&
+                               h->gc_host.rh_to_n.mq != 0 && h->gc_host.uh_to_h.mq != 0;
         if (use_cluster)
             rc = rec_cluster_launch(h->rec_cl, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256,
-                                    h->h_uns, ih_bytes, h->gc_host.narrow != 0, fused, st, &h->err);
+                                    h->h_uns, ih_bytes, fused ? fast_cell : h->gc_host.narrow != 0, fused, st, &h->err);
         else
             rc = rec_mma_launch(h->rec, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256,
                                 h->h_uns, ih_bytes, h->gc_host.narrow != 0, fused, h->coop != 0, st, &h->err);
         if (rc) return rc;
         h->launches += h->rec.launches + h->rec_cl.launches - before;
-        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 exchange=%s cell=%s MT=%d NB=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d narrow=%d ih_bytes=%d",
-                 used_tc ? "tcgen05_i8" : "simt_dp4a", use_cluster ? "cluster_dsmem" : "global", fused ? "fused" : "generic", mp.MT, mp.NB, mp.P, mp.G,
-                 mp.groups_per_launch, mp.smem, mp.tmem_cols, h->gc_host.narrow, ih_bytes);
+        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 exchange=%s cell=%s MT=%d NB=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d narrow=%d ih_bytes=%d shiftfree=%d%d%d%d",
+                 used_tc ? "tcgen05_i8" : "simt_dp4a", use_cluster ? "cluster_dsmem" : "global", fast_cell ? "fused_shiftfree" : fused ? "fused" : "generic", mp.MT, mp.NB, mp.P, mp.G,
+                 mp.groups_per_launch, mp.smem, mp.tmem_cols, h->gc_host.narrow, ih_bytes, (int)a.lc.fits32,
+                 (int)h->rs_fast[1], h->gc_host.rh_to_n.mq != 0, h->gc_host.uh_to_h.mq != 0);
     } else {
         RecArgs a;
         a.T = T; a.B = B; a.H = h->H; a.Hpad = h->Hpad; a.C = C;

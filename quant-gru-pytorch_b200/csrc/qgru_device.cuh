@@ -97,6 +97,22 @@ __device__ __forceinline__ int32_t gru_cell_fused(const GateConsts &gc, const in
     return clampi((int32_t)rescale32(comb, gc.uh_to_h) + gc.zp_h, gc.h_lo, gc.h_hi);
 }
 
+// gru_cell_fused for scales that all have the shift-free form (Rescale::mq != 0, checked on the
+// host): no branch anywhere, so the compiler can interleave the dependency chains of several
+// cells, which is what hides the table-lookup latency at four warps per scheduler.
+__device__ __forceinline__ int32_t gru_cell_fused_fast(const GateConsts &gc, const int32_t *ft, int32_t a_z,
+                                                       int32_t a_r, int32_t a_n, int32_t hh_z, int32_t hh_r,
+                                                       int32_t hh_n, int32_t h_old) {
+    const int32_t z_pre = a_z + ft[gc.ft_off[3] + (hh_z - gc.hh_lo)];
+    const int32_t z_d = ft[gc.ft_off[0] + (clampi(z_pre, gc.in_lo[ACT_Z], gc.in_hi[ACT_Z]) - gc.in_lo[ACT_Z])];
+    const int32_t r_pre = a_r + ft[gc.ft_off[4] + (hh_r - gc.hh_lo)];
+    const int32_t r_d = ft[gc.ft_off[1] + (clampi(r_pre, gc.in_lo[ACT_R], gc.in_hi[ACT_R]) - gc.in_lo[ACT_R])];
+    const int32_t n_pre = a_n + mul_round_hi(r_d * (hh_n - gc.zp_hh), gc.rh_to_n);
+    const int32_t n_d = ft[gc.ft_off[2] + (clampi(n_pre, gc.in_lo[ACT_N], gc.in_hi[ACT_N]) - gc.in_lo[ACT_N])];
+    const int32_t comb = z_d * (h_old - gc.zp_h) + (gc.k1 - z_d) * n_d;
+    return clampi(mul_round_hi(comb, gc.uh_to_h) + gc.zp_h, gc.h_lo, gc.h_hi);
+}
+
 // Epilogue of a fused linear layer (src/gru_forward_cpu_quant.cc:130-138).
 __device__ __forceinline__ int32_t linear_epilogue(int64_t acc, int64_t corr, Rescale rs,
                                                    int32_t zp_out, int32_t lo, int32_t hi) {
@@ -108,6 +124,12 @@ __device__ __forceinline__ int32_t linear_epilogue32(int32_t acc, int32_t corr, 
                                                      int32_t zp_out, int32_t lo, int32_t hi) {
     const int32_t v = (int32_t)rescale32(acc + corr, rs) + zp_out;
     return clampi(v, lo, hi);
+}
+
+// linear_epilogue32 for a scale with the shift-free form.
+__device__ __forceinline__ int32_t linear_epilogue_fast(int32_t acc, int32_t corr, const Rescale &rs,
+                                                        int32_t zp_out, int32_t lo, int32_t hi) {
+    return clampi(mul_round_hi(acc + corr, rs) + zp_out, lo, hi);
 }
 
 }  // namespace qgru

@@ -167,7 +167,7 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             const int m = m0 + q * 32 + lane;
             const bool m_ok = m < C;
             const int64_t corr = m_ok ? lc.corr[m] : 0;
-            const Rescale rs = m_ok ? lc.rs[m] : Rescale{1, 1};
+            const Rescale rs = m_ok ? lc.rs[m] : Rescale{1, 1, 0, 0, 0, 0};
             // fused-cell mode: the channel's gate decides the second rescale (to its input scale)
             const int gate = (ps.enabled && m_ok) ? m / ps.H : 0;
             const Rescale pre_rs = ps.to[gate];

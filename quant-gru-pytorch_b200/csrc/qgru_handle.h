@@ -57,6 +57,7 @@ struct qgru_handle {
     int8_t *d_w8[2] = {nullptr, nullptr};     // W8 [3H][Ipad], R8 [3H][Hpad] (rows over-allocated)
     long long w8_rows[2] = {0, 0};
     bool lin_fits32[2] = {false, false};      // acc + corr fits int32 (x side, h side)
+    bool rs_fast[2] = {false, false};   // every per-channel GEMM rescale has the shift-free form
     int *d_flags = nullptr;                   // [0] data errors, [1] barrier abort
     int *h_flags = nullptr;                   // pinned mirror
     unsigned *d_bar = nullptr;

@@ -265,7 +265,7 @@ __global__ void __launch_bounds__(256, 1) k_recurrence_dp4a(RecArgs a) {
     int64_t *corr = reinterpret_cast<int64_t *>(smem_raw + off);
     off += (size_t)3 * a.Hs * 8;
     Rescale *rs = reinterpret_cast<Rescale *>(smem_raw + off);
-    off += (size_t)3 * a.Hs * 8;
+    off += (size_t)3 * a.Hs * sizeof(Rescale);
     unsigned *Rs = reinterpret_cast<unsigned *>(smem_raw + off);
     off += (size_t)3 * kw * a.Hs * 4;
     unsigned *hs = reinterpret_cast<unsigned *>(smem_raw + off);
@@ -282,7 +282,7 @@ __global__ void __launch_bounds__(256, 1) k_recurrence_dp4a(RecArgs a) {
         const int g = i / a.Hs, jl = i % a.Hs, j = j0 + jl;
         const bool ok = j < a.H;
         corr[i] = ok ? a.lc.corr[g * a.H + j] : 0;
-        rs[i] = ok ? a.lc.rs[g * a.H + j] : Rescale{1, 1};
+        rs[i] = ok ? a.lc.rs[g * a.H + j] : Rescale{1, 1, 0, 0, 0, 0};
     }
     {
         const unsigned *r8w = reinterpret_cast<const unsigned *>(a.r8);

@@ -20,8 +20,13 @@ namespace qgru {
 
 // FixedPointScale / Pot2Rescale (include/quantize_param_types.h:37-46), widened to ints.
 struct Rescale {
-    int32_t mult;   // 1 in POT2 mode, else 32768..65535
-    int32_t shift;  // > 0: rounding right shift; <= 0: left shift
+    int32_t mult;    // 1 in POT2 mode, else 32768..65535
+    int32_t shift;   // > 0: rounding right shift; <= 0: left shift
+    // Shift-free form (set_fast_form; mq == 0 where it does not exist), see mul_round_hi:
+    int32_t mq;      // mult << k, k chosen so that 2^30 <= mq < 2^31
+    int32_t e;       // shift + k - 32, 0..31: the quotient is the high product word >> e
+    int32_t add_hi;  // high and low word of 2^(31+e) - 1, the rounding addend
+    uint32_t add_lo;
 };
 
 // rshift_round(int64_t, int8_t) (include/quantize_ops_helper.h:183-206): round half to even
@@ -39,11 +44,45 @@ QG_HD int64_t rshift_round64(int64_t x, int n) {
 // applyRescale(int64_t, FixedPointScale) (include/quantize_ops_helper.h:228-230).
 QG_HD int64_t rescale64(int64_t x, Rescale r) { return rshift_round64(x * (int64_t)r.mult, r.shift); }
 
-// The same for an operand known to fit in int32: one widening multiply.  (A hand-split
-// version that rounds on 32-bit halves measured slower on sm_100a than the compiler's 64-bit
-// shifts: its n < 32 / n >= 32 branch diverges per channel.)
-QG_HD int64_t rescale32(int32_t x, Rescale r) {
-    return rshift_round64((int64_t)x * (int64_t)r.mult, r.shift);
+// Fill the shift-free form (host, once per scale).  With k = 30 - floor(log2(mult)) the
+// product x * (mult << k) of a 32-bit x stays below 2^62 and equals x * mult * 2^k, so
+// x * mult / 2^shift == product / 2^(32 + e) with e = shift + k - 32.  The form exists for
+// 0 <= e <= 31: shifts 17..48 of a 16-bit multiplier, 2..33 in POT2 mode (mult = 1).
+inline void set_fast_form(Rescale *r) {
+    r->mq = 0;
+    r->e = 0;
+    r->add_hi = 0;
+    r->add_lo = 0;
+    if (r->mult <= 0 || r->mult > 65535) return;
+    int lg = 0;
+    while ((r->mult >> (lg + 1)) != 0) ++lg;
+    const int k = 30 - lg, e = r->shift + k - 32;
+    if (e < 0 || e > 31) return;
+    const uint64_t add = ((uint64_t)1 << (31 + e)) - 1;
+    r->mq = (int32_t)((uint32_t)r->mult << k);
+    r->e = e;
+    r->add_hi = (int32_t)(add >> 32);
+    r->add_lo = (uint32_t)add;
+}
+
+// Round-half-even of x * mult / 2^shift through the shift-free form: the floor quotient is
+// the high word of the 64-bit product shifted right by e, its parity decides ties, and the
+// addend 2^(31+e) - 1 (+1 for an odd floor) carries into bit 32+e exactly when the remainder
+// is above one half, or equal to it with an odd floor - the rule of rshift_round64 with
+// n = 32 + e.  Only 32-bit shifts by a uniform amount; no branch.
+QG_HD int32_t mul_round_hi(int32_t x, const Rescale &r) {
+    const int64_t p = (int64_t)x * (int64_t)r.mq;
+    const int32_t odd = ((int32_t)(p >> 32) >> r.e) & 1;
+    const int64_t add = (int64_t)(((uint64_t)(uint32_t)r.add_hi << 32) | (uint64_t)r.add_lo);
+    const int64_t t = p + add + (int64_t)odd;
+    return (int32_t)(t >> 32) >> r.e;
+}
+
+// applyRescale for an operand known to fit in int32.  Scales without the shift-free form
+// fall back to the 64-bit shifts.
+QG_HD int32_t rescale32(int32_t x, Rescale r) {
+    if (r.mq != 0) return mul_round_hi(x, r);
+    return (int32_t)rshift_round64((int64_t)x * (int64_t)r.mult, r.shift);
 }
 
 // Fast form for 0 < shift < 32 and |x * mult| < 2^30 (checked on the host when a plan is

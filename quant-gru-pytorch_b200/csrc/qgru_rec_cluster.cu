@@ -82,6 +82,9 @@ __host__ __device__ inline ClusterSmem cluster_smem_layout(int MT, int KBn, int 
 
 namespace {
 
+// Cell variants: Fused = false: the generic datapath (Narrow picks its 32-bit rescales);
+// Fused = true: the tabulated cell, where Narrow = true selects the branch-free form that needs
+// every scale of the step in shift-free form and 32-bit linear sums.
 template <typename IhT, bool Narrow, bool Fused, int MT>
 __global__ void __launch_bounds__(REC_THREADS, 1)
 k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_h,
@@ -217,7 +220,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
 #pragma unroll
             for (int g = 0; g < 3; ++g) {
                 corr[mt][g] = j_ok[mt] ? a.lc.corr[g * a.H + j] : 0;
-                rs[mt][g] = j_ok[mt] ? a.lc.rs[g * a.H + j] : Rescale{1, 1};
+                rs[mt][g] = j_ok[mt] ? a.lc.rs[g * a.H + j] : Rescale{1, 1, 0, 0, 0, 0};
             }
         }
         // the TMA-written initial state must be complete before h_{t-1} is read from the tile
@@ -264,14 +267,21 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     tc::tmem_ld4(ta + a.NB, ar);
                     tc::tmem_ld4(ta + 2 * a.NB, an);
                     tc::tmem_ld_wait();
+                    if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0) a.dbg[s * 8 + 2] = clock64();
+                    // All CH cells are computed before anything is stored: a byte store into the
+                    // state tile may alias the tables as far as the compiler knows, so a store between
+                    // two cells would keep the second cell's table reads behind it and serialise the
+                    // four dependency chains.  Inputs of absent rows/units are zeros and every table
+                    // index is clamped, so every lane computes; only the stores are guarded.
+                    int32_t hn[CH];
 #pragma unroll
                     for (int i = 0; i < CH; ++i) {
-                        // computed for every lane (inputs of absent rows/units are zeros and every
-                        // table index is clamped), so the four chains interleave; only stores are guarded
-                        const int b = c0 + i;
-                        const bool v_ok = b < nb && j_ok[mt];
                         int32_t hh_z, hh_r, hh_n;
-                        if (a.lc.fits32) {
+                        if constexpr (Fused && Narrow) {
+                            hh_z = linear_epilogue_fast(az[i], (int32_t)corr[mt][0], rs[mt][0], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                            hh_r = linear_epilogue_fast(ar[i], (int32_t)corr[mt][1], rs[mt][1], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                            hh_n = linear_epilogue_fast(an[i], (int32_t)corr[mt][2], rs[mt][2], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                        } else if (a.lc.fits32) {
                             hh_z = linear_epilogue32(az[i], (int32_t)corr[mt][0], rs[mt][0], a.lc.zp_out, a.lc.lo, a.lc.hi);
                             hh_r = linear_epilogue32(ar[i], (int32_t)corr[mt][1], rs[mt][1], a.lc.zp_out, a.lc.lo, a.lc.hi);
                             hh_n = linear_epilogue32(an[i], (int32_t)corr[mt][2], rs[mt][2], a.lc.zp_out, a.lc.lo, a.lc.hi);
@@ -280,20 +290,30 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                             hh_r = linear_epilogue(ar[i], corr[mt][1], rs[mt][1], a.lc.zp_out, a.lc.lo, a.lc.hi);
                             hh_n = linear_epilogue(an[i], corr[mt][2], rs[mt][2], a.lc.zp_out, a.lc.lo, a.lc.hi);
                         }
-                        int32_t hn;
-                        if constexpr (Fused)
-                            hn = gru_cell_fused(gc, tables, ihv[mt][i][0], ihv[mt][i][1], ihv[mt][i][2], hh_z, hh_r,
-                                                hh_n, hold[mt][i]);
+                        if constexpr (Fused && Narrow)
+                            hn[i] = gru_cell_fused_fast(gc, tables, ihv[mt][i][0], ihv[mt][i][1], ihv[mt][i][2], hh_z,
+                                                        hh_r, hh_n, hold[mt][i]);
+                        else if constexpr (Fused)
+                            hn[i] = gru_cell_fused(gc, tables, ihv[mt][i][0], ihv[mt][i][1], ihv[mt][i][2], hh_z, hh_r,
+                                                   hh_n, hold[mt][i]);
                         else
-                            hn = gru_cell<Narrow>(gc, tables, ihv[mt][i][0], ihv[mt][i][1], ihv[mt][i][2], hh_z,
-                                                  hh_r, hh_n, hold[mt][i]);
-                        // h_t[b][j] becomes element (row b, K index j) of every CTA's next B tile
-                        if (v_ok) {
+                            hn[i] = gru_cell<Narrow>(gc, tables, ihv[mt][i][0], ihv[mt][i][1], ihv[mt][i][2], hh_z,
+                                                     hh_r, hh_n, hold[mt][i]);
+                    }
+                    if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0) {
+                        long long tck;   // reads the clock only once every cell value exists
+                        asm volatile("mov.u64 %0, %%clock64;" : "=l"(tck) : "r"(hn[0]), "r"(hn[CH - 1]), "r"(hn[1]), "r"(hn[2]) : "memory");
+                        a.dbg[s * 8 + 6] = tck;
+                    }
+#pragma unroll
+                    for (int i = 0; i < CH; ++i) {
+                        const int b = c0 + i;
+                        if (b < nb && j_ok[mt]) {
                             // h_t[b][j] = element (row b, K index j) of the next B tile: own K-slab
-                            h_nxt[sw128_offset(b, j, a.NB)] = (unsigned char)hn;
+                            h_nxt[sw128_offset(b, j, a.NB)] = (unsigned char)hn[i];
                             const size_t o = (size_t)out_slot * BH + (size_t)(b0 + b) * a.H + j;
-                            if (a.hq_out) a.hq_out[o] = hn;
-                            if (a.hf_out) a.hf_out[o] = (float)(hn - gc.zp_h) * gc.h_scale;
+                            if (a.hq_out) a.hq_out[o] = hn[i];
+                            if (a.hf_out) a.hf_out[o] = (float)(hn[i] - gc.zp_h) * gc.h_scale;
                         }
                     }
                 }
@@ -350,6 +370,9 @@ cudaError_t launch_mt(int MT, const CUtensorMap &mr, const CUtensorMap &mh, cons
 cudaError_t launch_any(bool fused, bool narrow, int ih_bytes, int MT, const CUtensorMap &mr,
                        const CUtensorMap &mh, const GateConsts &gc, RecMmaArgs &a, int grid, size_t smem,
                        cudaStream_t st) {
+    if (fused && narrow)   // for the fused cell `narrow` carries "every scale is shift-free"
+        return ih_bytes == 2 ? launch_mt<int16_t, true, true>(MT, mr, mh, gc, a, grid, smem, st)
+                             : launch_mt<int32_t, true, true>(MT, mr, mh, gc, a, grid, smem, st);
     if (fused)
         return ih_bytes == 2 ? launch_mt<int16_t, false, true>(MT, mr, mh, gc, a, grid, smem, st)
                              : launch_mt<int32_t, false, true>(MT, mr, mh, gc, a, grid, smem, st);

@@ -61,6 +61,33 @@ def test_host_primitives_match_oracle(oracle):
     assert lib.qgru_encode_mshift(C.c_float(0.0), C.byref(m), C.byref(sh)) == _cabi.QGRU_ERR_RANGE
 
 
+def test_apply_rescale_fast_form_matches_oracle(oracle):
+    """The shift-free form (x * (M << k), rounding on the high word) against the oracle's
+    rshift_round(x * M, n): ties, signs, POT2 (M = 1) and shifts outside the form's range."""
+    lib = _cabi.lib()
+    rng = np.random.default_rng(7)
+    checked = 0
+    for _ in range(20000):
+        u = rng.random()
+        mult = 1 if u < 0.2 else (32768 + 16384 * int(rng.integers(0, 2))) if u < 0.4 else int(rng.integers(32768, 65536))
+        n = int(rng.integers(1, 52))
+        if rng.random() < 0.3:
+            # an exact tie: x * mult = (2k + 1) * 2^(n-1)
+            k = int(rng.integers(-2 ** 12, 2 ** 12))
+            num = (2 * k + 1) << (n - 1)
+            if num % mult:
+                continue
+            x = num // mult
+        else:
+            x = int(rng.integers(-2 ** 31, 2 ** 31))
+        want = oracle.rshift_round(x * mult, n)
+        if not (-2 ** 31 <= x < 2 ** 31) or not (-2 ** 31 <= want < 2 ** 31):
+            continue
+        assert lib.qgru_apply_rescale(x, mult, n) == want, (x, mult, n)
+        checked += 1
+    assert checked > 10000
+
+
 @pytest.mark.parametrize("name", ["default", "sym8_tensor", "cfg2", "cfg3", "cfg5", "pot2", "pot2_asym",
                                   "wide16", "gate_in16"])
 def test_params_from_ranges_and_luts_match(oracle, name):
