@@ -268,6 +268,7 @@ QGRU_API const char *qgru_describe_plan(qgru_handle *h, int T, int B);
  *   "exchange" auto | global | cluster      how the CTAs of a batch group exchange h_t
  *   "cell"     auto | fused | generic       gate datapath: tabulated (auto also allows its
  *                                           shift-free form), or the reference's step by step
+ *   "r_resident" auto | smem | tmem       where the cluster recurrence keeps its slice of R
  *   "sm_limit" n   use at most n SMs (0 = all);  "spin_limit" n   bound of the group barrier
  * Unknown names or values return QGRU_ERR_BAD_ARG. */
 QGRU_API int qgru_set_option(qgru_handle *h, const char *name, const char *value);

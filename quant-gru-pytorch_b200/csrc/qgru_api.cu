@@ -160,6 +160,11 @@ int qgru_set_option(qgru_handle *h, const char *name, const char *value) {
         else if (v == "global") h->opt_exchange = 1;
         else if (v == "cluster") h->opt_exchange = 2;
         else return fail(h, QGRU_ERR_BAD_ARG, "exchange: auto|global|cluster");
+    } else if (n == "r_resident") {
+        if (v == "auto") h->opt_r_where = 0;
+        else if (v == "smem") h->opt_r_where = 1;
+        else if (v == "tmem") h->opt_r_where = 2;
+        else return fail(h, QGRU_ERR_BAD_ARG, "r_resident: auto|smem|tmem");
     } else if (n == "cell") {
         if (v == "auto") h->opt_cell = 0;
         else if (v == "generic") h->opt_cell = 1;
@@ -555,7 +560,7 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
     // state exchange through distributed shared memory (one cluster per group) where it fits
     RecMmaPlan cp;
     const bool use_cluster = use_mma && h->opt_exchange != 1 &&
-                             rec_cluster_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, &cp);
+                             rec_cluster_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, h->opt_r_where, &cp);
     if (h->opt_exchange == 2 && use_mma && !use_cluster)
         return fail(h, QGRU_ERR_UNSUPPORTED, "cluster exchange does not fit shared memory");
     if (use_cluster) mp = cp;
@@ -644,9 +649,10 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
                                 h->h_uns, ih_bytes, h->gc_host.narrow != 0, fused, h->coop != 0, st, &h->err);
         if (rc) return rc;
         h->launches += h->rec.launches + h->rec_cl.launches - before;
-        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 exchange=%s cell=%s MT=%d NB=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d narrow=%d ih_bytes=%d shiftfree=%d%d%d%d",
+        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 exchange=%s cell=%s MT=%d NB=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d r_in=%s narrow=%d ih_bytes=%d shiftfree=%d%d%d%d",
                  used_tc ? "tcgen05_i8" : "simt_dp4a", use_cluster ? "cluster_dsmem" : "global", fast_cell ? "fused_shiftfree" : fused ? "fused" : "generic", mp.MT, mp.NB, mp.P, mp.G,
-                 mp.groups_per_launch, mp.smem, mp.tmem_cols, h->gc_host.narrow, ih_bytes, (int)a.lc.fits32,
+                 mp.groups_per_launch, mp.smem, mp.tmem_cols, (use_cluster && mp.r_tmem_col > 0) ? "tmem" : "smem",
+                 h->gc_host.narrow, ih_bytes, (int)a.lc.fits32,
                  (int)h->rs_fast[1], h->gc_host.rh_to_n.mq != 0, h->gc_host.uh_to_h.mq != 0);
     } else {
         RecArgs a;

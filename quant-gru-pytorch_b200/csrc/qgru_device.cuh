@@ -99,14 +99,17 @@ __device__ __forceinline__ int32_t gru_cell_fused(const GateConsts &gc, const in
 
 // gru_cell_fused for scales that all have the shift-free form (Rescale::mq != 0, checked on the
 // host): no branch anywhere, so the compiler can interleave the dependency chains of several
-// cells, which is what hides the table-lookup latency at four warps per scheduler.
-__device__ __forceinline__ int32_t gru_cell_fused_fast(const GateConsts &gc, const int32_t *ft, int32_t a_z,
-                                                       int32_t a_r, int32_t a_n, int32_t hh_z, int32_t hh_r,
-                                                       int32_t hh_n, int32_t h_old) {
-    const int32_t z_pre = a_z + ft[gc.ft_off[3] + (hh_z - gc.hh_lo)];
-    const int32_t z_d = ft[gc.ft_off[0] + (clampi(z_pre, gc.in_lo[ACT_Z], gc.in_hi[ACT_Z]) - gc.in_lo[ACT_Z])];
-    const int32_t r_pre = a_r + ft[gc.ft_off[4] + (hh_r - gc.hh_lo)];
-    const int32_t r_d = ft[gc.ft_off[1] + (clampi(r_pre, gc.in_lo[ACT_R], gc.in_hi[ACT_R]) - gc.in_lo[ACT_R])];
+// cells, which is what hides the table-lookup latency at four warps per scheduler.  In three
+// pieces, so that a kernel can start on the update and reset gates while the tensor core still
+// works on the rows of the new gate.
+//   which = ACT_Z / ACT_R: sigmoid LUT output minus its zero point
+__device__ __forceinline__ int32_t fused_gate_fast(const GateConsts &gc, const int32_t *ft, int which,
+                                                   int32_t a_pre, int32_t hh) {
+    const int32_t pre = a_pre + ft[gc.ft_off[3 + which] + (hh - gc.hh_lo)];
+    return ft[gc.ft_off[which] + (clampi(pre, gc.in_lo[which], gc.in_hi[which]) - gc.in_lo[which])];
+}
+__device__ __forceinline__ int32_t fused_finish_fast(const GateConsts &gc, const int32_t *ft, int32_t a_n,
+                                                     int32_t hh_n, int32_t z_d, int32_t r_d, int32_t h_old) {
     const int32_t n_pre = a_n + mul_round_hi(r_d * (hh_n - gc.zp_hh), gc.rh_to_n);
     const int32_t n_d = ft[gc.ft_off[2] + (clampi(n_pre, gc.in_lo[ACT_N], gc.in_hi[ACT_N]) - gc.in_lo[ACT_N])];
     const int32_t comb = z_d * (h_old - gc.zp_h) + (gc.k1 - z_d) * n_d;

@@ -74,7 +74,7 @@ __host__ __device__ inline ClusterSmem cluster_smem_layout(int MT, int KBn, int 
     s.r_tiles = 0;
     s.h_tile = (size_t)MT * 3 * KBn * 16384;
     s.bars = s.h_tile + (size_t)2 * KBn * NB * 128;   // two state buffers
-    s.tables = s.bars + 64;
+    s.tables = s.bars + 128;
     s.total = s.tables + (((size_t)n_table * 4 + 15) & ~size_t(15));
     return s;
 }
@@ -100,9 +100,10 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
     unsigned char *h_tile = base + L.h_tile;
     const uint32_t h_buf_bytes = (uint32_t)(KBn * a.NB * 128);
     uint64_t *bars = reinterpret_cast<uint64_t *>(base + L.bars);
-    uint64_t *r_full = bars, *h_full = bars + 1, *mma_done = bars + 2, *h_written = bars + 3;
+    uint64_t *r_full = bars, *h_full = bars + 1, *h_written = bars + 2, *r_ready = bars + 3;
     uint64_t *h_ready = bars + 4;                    // [2]: peer blocks of the tile buffer have landed
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 6);
+    uint64_t *mma_done = bars + 6;                   // [3]: the rows of gate z / r / n are accumulated
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 9);
     int32_t *tables = reinterpret_cast<int32_t *>(base + L.tables);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
@@ -117,10 +118,11 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
     if (tid == 0) {
         tc::mbar_init(r_full, 1);
         tc::mbar_init(h_full, 1);
-        tc::mbar_init(mma_done, 1);
+        for (int g = 0; g < 3; ++g) tc::mbar_init(&mma_done[g], 1);
         tc::mbar_init(h_written, EPI_THREADS);
         tc::mbar_init(&h_ready[0], 1);
         tc::mbar_init(&h_ready[1], 1);
+        tc::mbar_init(r_ready, EPI_THREADS);
         tc::fence_barrier_init();
         tc::tma_prefetch_desc(&map_r);
         tc::tma_prefetch_desc(&map_h);
@@ -150,6 +152,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
             for (int kb = 0; kb < KBn; ++kb)
                 tc::tma_load_2d(h_tile + (size_t)kb * a.NB * 128, &map_h, h_full, kb * 128, b0);
             ok = tc::mbar_wait(r_full, 0, WAIT_BUDGET) && tc::mbar_wait(h_full, 0, WAIT_BUDGET);
+            if (ok && a.r_tmem_col > 0) ok = tc::mbar_wait(r_ready, 0, WAIT_BUDGET);
             idesc = tc::idesc_i8(128, a.NB, true, !a.h_unsigned);
             r_lo0 = (tc::smem_u32(r_tiles) & 0x3FFFFu) >> 4;
             h_lo0 = (tc::smem_u32(h_tile) & 0x3FFFFu) >> 4;
@@ -179,25 +182,53 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                 if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 1] = clock64();
                 tc::tc_fence_after_sync();
                 const uint32_t hbuf = h_lo0 + (buf_off >> 4);
-                // consecutive MMAs go to different accumulators (3*MT independent chains)
-                for (int kb = 0; kb < KBn; ++kb) {
-                    const uint32_t hb = hbuf + (uint32_t)(kb * a.NB * 8);
+                // Gate by gate, with a commit after each: the epilogue starts on the update gate while
+                // the reset and new gates are still being multiplied.  The epilogue warps that share
+                // this warp's scheduler are busy by then, so every operand is prepared up front and
+                // the loops are fully unrolled: one independent add per MMA, no dependent chain.
+                uint32_t bdl[4][4];   // low descriptor words of the state tile: K-slab kb, 32-byte step ks
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t bd = ((uint64_t)desc_hi << 32) | (desc_lo | (hb + 2 * ks));
+                for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) bdl[kb][ks] = desc_lo | (hbuf + (uint32_t)(kb * a.NB * 8 + 2 * ks));
+                const uint64_t dhi = (uint64_t)desc_hi << 32;
+                if (a.r_tmem_col > 0) {   // A operand from tensor memory
+#pragma unroll
+                    for (int g = 0; g < 3; ++g) {
 #pragma unroll
                         for (int mt = 0; mt < MT; ++mt) {
+                            const uint32_t d = tmem_base + (uint32_t)((mt * 3 + g) * a.NB);
+                            const uint32_t ra = tmem_base + (uint32_t)(a.r_tmem_col + (mt * 3 + g) * KBn * 32);
 #pragma unroll
-                            for (int g = 0; g < 3; ++g) {
-                                const uint32_t d = tmem_base + (uint32_t)((mt * 3 + g) * a.NB);
-                                const uint32_t rb = r_lo0 + (uint32_t)(((mt * 3 + g) * KBn + kb) * 1024);
-                                tc::mma_i8(d, ((uint64_t)desc_hi << 32) | (desc_lo | (rb + 2 * ks)), bd, idesc,
-                                           (kb | ks) != 0);
-                            }
+                            for (int kb = 0; kb < 4; ++kb)
+                                if (kb < KBn) {
+#pragma unroll
+                                    for (int ks = 0; ks < 4; ++ks)
+                                        tc::mma_i8_ts(d, ra + (uint32_t)(kb * 32 + ks * 8), dhi | bdl[kb][ks], idesc,
+                                                      (kb | ks) != 0);
+                                }
                         }
+                        tc::mma_commit(&mma_done[g]);
+                    }
+                } else {
+#pragma unroll
+                    for (int g = 0; g < 3; ++g) {
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            const uint32_t d = tmem_base + (uint32_t)((mt * 3 + g) * a.NB);
+                            const uint32_t rb = desc_lo | (r_lo0 + (uint32_t)((mt * 3 + g) * KBn * 1024));
+#pragma unroll
+                            for (int kb = 0; kb < 4; ++kb)
+                                if (kb < KBn) {
+#pragma unroll
+                                    for (int ks = 0; ks < 4; ++ks)
+                                        tc::mma_i8(d, dhi | (rb + (uint32_t)(kb * 1024 + 2 * ks)), dhi | bdl[kb][ks], idesc,
+                                                   (kb | ks) != 0);
+                                }
+                        }
+                        tc::mma_commit(&mma_done[g]);
                     }
                 }
-                tc::mma_commit(mma_done);
                 if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 3] = clock64();
             }
             if (!ok) atomicOr(a.abort_flag, 1);
@@ -223,14 +254,43 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                 rs[mt][g] = j_ok[mt] ? a.lc.rs[g * a.H + j] : Rescale{1, 1, 0, 0, 0, 0};
             }
         }
+        bool ok = true;
+        if (a.r_tmem_col > 0) {
+            // Move the R slice from its TMA-written tiles into tensor memory, where the MMA reads
+            // its A operand without touching shared memory.  This thread owns row u of every
+            // 128-row tile: eight 16-byte chunks per 128-byte row, un-swizzled on the way (chunk c
+            // of row u lies at chunk c ^ (u & 7)), written to 32 columns of TMEM lane u.
+            ok = tc::mbar_wait(r_full, 0, WAIT_BUDGET);
+            const int n_tiles = MT * 3 * KBn;
+            for (int tile = rank; tile < n_tiles && ok; tile += EPW) {
+                const unsigned char *row = r_tiles + (size_t)tile * 16384 + (size_t)(u >> 3) * 1024 + (size_t)(u & 7) * 128;
+                uint32_t w[32];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(row + ((c ^ (u & 7)) << 4));
+                    w[4 * c + 0] = v.x;
+                    w[4 * c + 1] = v.y;
+                    w[4 * c + 2] = v.z;
+                    w[4 * c + 3] = v.w;
+                }
+                tc::tmem_st32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a.r_tmem_col + tile * 32), w);
+            }
+            tc::tmem_st_wait();
+            tc::tc_fence_before_sync();
+            tc::mbar_arrive(r_ready);
+        }
         // the TMA-written initial state must be complete before h_{t-1} is read from the tile
-        bool ok = tc::mbar_wait(h_full, 0, WAIT_BUDGET);
+        ok = tc::mbar_wait(h_full, 0, WAIT_BUDGET) && ok;
         for (int s = 0; s < a.T; ++s) {
             const int t = a.reverse ? (a.T - 1 - s) : s;
             const long long out_slot = a.reverse ? (a.T - 1 - s) : (s + 1);
             const unsigned char *h_cur = h_tile + (size_t)(s & 1) * h_buf_bytes;
             unsigned char *h_nxt = h_tile + (size_t)((s + 1) & 1) * h_buf_bytes;
+            const uint32_t par = (uint32_t)(s & 1);
+            const bool stamp = a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0;
             bool waited = false;
+            int32_t hn_last[MT][CH];   // the warp's last chunk: its outputs go to global memory after the arrive
+            int c_last = -1;
             for (int c = rank; c < nchunks && ok; c += EPW) {
                 const int c0 = c * CH;
                 // operands that do not depend on this step's MMA: issued first
@@ -251,83 +311,160 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         hold[mt][i] = a.h_unsigned ? (int32_t)hb : (int32_t)(int8_t)hb;
                     }
                 }
-                if (!waited) {
-                    ok = tc::mbar_wait(mma_done, (uint32_t)(s & 1), WAIT_BUDGET);
-                    if (!ok) break;
-                    tc::tc_fence_after_sync();
-                    waited = true;
-                    if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0) a.dbg[s * 8 + 4] = clock64();
+                // All CH cells of a tile are computed before anything is stored: a byte store into
+                // the state tile may alias the tables as far as the compiler knows, so a store
+                // between two cells would keep the second cell's table reads behind it and serialise
+                // the dependency chains.  Inputs of absent rows/units are zeros and every table index
+                // is clamped, so every lane computes; only the stores are guarded.
+                int32_t hn[MT][CH];
+                const uint32_t ta0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+                if constexpr (Fused && Narrow) {
+                    int32_t acc[MT][CH], zd[MT][CH], rd[MT][CH];
+                    // update gate
+                    if (!waited) {
+                        ok = tc::mbar_wait(&mma_done[0], par, WAIT_BUDGET);
+                        if (!ok) break;
+                        tc::tc_fence_after_sync();
+                        if (stamp) a.dbg[s * 8 + 4] = clock64();
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 0) * a.NB), acc[mt]);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                        for (int i = 0; i < CH; ++i)
+                            zd[mt][i] = fused_gate_fast(gc, tables, ACT_Z, ihv[mt][i][0],
+                                                        linear_epilogue_fast(acc[mt][i], (int32_t)corr[mt][0], rs[mt][0],
+                                                                             a.lc.zp_out, a.lc.lo, a.lc.hi));
+                    // reset gate
+                    if (!waited) {
+                        ok = tc::mbar_wait(&mma_done[1], par, WAIT_BUDGET);
+                        if (!ok) break;
+                        tc::tc_fence_after_sync();
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 1) * a.NB), acc[mt]);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                        for (int i = 0; i < CH; ++i)
+                            rd[mt][i] = fused_gate_fast(gc, tables, ACT_R, ihv[mt][i][1],
+                                                        linear_epilogue_fast(acc[mt][i], (int32_t)corr[mt][1], rs[mt][1],
+                                                                             a.lc.zp_out, a.lc.lo, a.lc.hi));
+                    // new gate and the state update
+                    if (!waited) {
+                        ok = tc::mbar_wait(&mma_done[2], par, WAIT_BUDGET);
+                        if (!ok) break;
+                        tc::tc_fence_after_sync();
+                        waited = true;
+                        if (stamp) a.dbg[s * 8 + 2] = clock64();
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 2) * a.NB), acc[mt]);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                        for (int i = 0; i < CH; ++i)
+                            hn[mt][i] = fused_finish_fast(gc, tables, ihv[mt][i][2],
+                                                          linear_epilogue_fast(acc[mt][i], (int32_t)corr[mt][2], rs[mt][2],
+                                                                               a.lc.zp_out, a.lc.lo, a.lc.hi),
+                                                          zd[mt][i], rd[mt][i], hold[mt][i]);
+                } else {
+                    if (!waited) {
+                        ok = tc::mbar_wait(&mma_done[0], par, WAIT_BUDGET) && tc::mbar_wait(&mma_done[1], par, WAIT_BUDGET) &&
+                             tc::mbar_wait(&mma_done[2], par, WAIT_BUDGET);
+                        if (!ok) break;
+                        tc::tc_fence_after_sync();
+                        waited = true;
+                        if (stamp) a.dbg[s * 8 + 4] = a.dbg[s * 8 + 2] = clock64();
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        int32_t az[CH], ar[CH], an[CH];
+                        const uint32_t ta = ta0 + (uint32_t)(mt * 3 * a.NB);
+                        tc::tmem_ld4(ta, az);
+                        tc::tmem_ld4(ta + a.NB, ar);
+                        tc::tmem_ld4(ta + 2 * a.NB, an);
+                        tc::tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < CH; ++i) {
+                            int32_t hh_z, hh_r, hh_n;
+                            if (a.lc.fits32) {
+                                hh_z = linear_epilogue32(az[i], (int32_t)corr[mt][0], rs[mt][0], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                                hh_r = linear_epilogue32(ar[i], (int32_t)corr[mt][1], rs[mt][1], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                                hh_n = linear_epilogue32(an[i], (int32_t)corr[mt][2], rs[mt][2], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                            } else {
+                                hh_z = linear_epilogue(az[i], corr[mt][0], rs[mt][0], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                                hh_r = linear_epilogue(ar[i], corr[mt][1], rs[mt][1], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                                hh_n = linear_epilogue(an[i], corr[mt][2], rs[mt][2], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                            }
+                            if constexpr (Fused)
+                                hn[mt][i] = gru_cell_fused(gc, tables, ihv[mt][i][0], ihv[mt][i][1], ihv[mt][i][2], hh_z,
+                                                           hh_r, hh_n, hold[mt][i]);
+                            else
+                                hn[mt][i] = gru_cell<Narrow>(gc, tables, ihv[mt][i][0], ihv[mt][i][1], ihv[mt][i][2], hh_z,
+                                                             hh_r, hh_n, hold[mt][i]);
+                        }
+                    }
                 }
+                if (stamp) {
+                    long long tck;   // reads the clock only once the cell values exist
+                    asm volatile("mov.u64 %0, %%clock64;" : "=l"(tck) : "r"(hn[0][0]), "r"(hn[MT - 1][CH - 1]), "r"(hn[0][1]), "r"(hn[0][2]) : "memory");
+                    a.dbg[s * 8 + 6] = tck;
+                }
+                // h_t[b][j] = element (row b, K index j) of the next B tile: this CTA's own K-slab
+                const bool last = c + EPW >= nchunks;
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
                     const int j = j0 + mt * 128 + u;
-                    int32_t az[CH], ar[CH], an[CH];
-                    const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * 3 * a.NB + c0);
-                    tc::tmem_ld4(ta, az);
-                    tc::tmem_ld4(ta + a.NB, ar);
-                    tc::tmem_ld4(ta + 2 * a.NB, an);
-                    tc::tmem_ld_wait();
-                    if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0) a.dbg[s * 8 + 2] = clock64();
-                    // All CH cells are computed before anything is stored: a byte store into the
-                    // state tile may alias the tables as far as the compiler knows, so a store between
-                    // two cells would keep the second cell's table reads behind it and serialise the
-                    // four dependency chains.  Inputs of absent rows/units are zeros and every table
-                    // index is clamped, so every lane computes; only the stores are guarded.
-                    int32_t hn[CH];
-#pragma unroll
-                    for (int i = 0; i < CH; ++i) {
-                        int32_t hh_z, hh_r, hh_n;
-                        if constexpr (Fused && Narrow) {
-                            hh_z = linear_epilogue_fast(az[i], (int32_t)corr[mt][0], rs[mt][0], a.lc.zp_out, a.lc.lo, a.lc.hi);
-                            hh_r = linear_epilogue_fast(ar[i], (int32_t)corr[mt][1], rs[mt][1], a.lc.zp_out, a.lc.lo, a.lc.hi);
-                            hh_n = linear_epilogue_fast(an[i], (int32_t)corr[mt][2], rs[mt][2], a.lc.zp_out, a.lc.lo, a.lc.hi);
-                        } else if (a.lc.fits32) {
-                            hh_z = linear_epilogue32(az[i], (int32_t)corr[mt][0], rs[mt][0], a.lc.zp_out, a.lc.lo, a.lc.hi);
-                            hh_r = linear_epilogue32(ar[i], (int32_t)corr[mt][1], rs[mt][1], a.lc.zp_out, a.lc.lo, a.lc.hi);
-                            hh_n = linear_epilogue32(an[i], (int32_t)corr[mt][2], rs[mt][2], a.lc.zp_out, a.lc.lo, a.lc.hi);
-                        } else {
-                            hh_z = linear_epilogue(az[i], corr[mt][0], rs[mt][0], a.lc.zp_out, a.lc.lo, a.lc.hi);
-                            hh_r = linear_epilogue(ar[i], corr[mt][1], rs[mt][1], a.lc.zp_out, a.lc.lo, a.lc.hi);
-                            hh_n = linear_epilogue(an[i], corr[mt][2], rs[mt][2], a.lc.zp_out, a.lc.lo, a.lc.hi);
-                        }
-                        if constexpr (Fused && Narrow)
-                            hn[i] = gru_cell_fused_fast(gc, tables, ihv[mt][i][0], ihv[mt][i][1], ihv[mt][i][2], hh_z,
-                                                        hh_r, hh_n, hold[mt][i]);
-                        else if constexpr (Fused)
-                            hn[i] = gru_cell_fused(gc, tables, ihv[mt][i][0], ihv[mt][i][1], ihv[mt][i][2], hh_z, hh_r,
-                                                   hh_n, hold[mt][i]);
-                        else
-                            hn[i] = gru_cell<Narrow>(gc, tables, ihv[mt][i][0], ihv[mt][i][1], ihv[mt][i][2], hh_z,
-                                                     hh_r, hh_n, hold[mt][i]);
-                    }
-                    if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0) {
-                        long long tck;   // reads the clock only once every cell value exists
-                        asm volatile("mov.u64 %0, %%clock64;" : "=l"(tck) : "r"(hn[0]), "r"(hn[CH - 1]), "r"(hn[1]), "r"(hn[2]) : "memory");
-                        a.dbg[s * 8 + 6] = tck;
-                    }
 #pragma unroll
                     for (int i = 0; i < CH; ++i) {
                         const int b = c0 + i;
                         if (b < nb && j_ok[mt]) {
-                            // h_t[b][j] = element (row b, K index j) of the next B tile: own K-slab
-                            h_nxt[sw128_offset(b, j, a.NB)] = (unsigned char)hn[i];
-                            const size_t o = (size_t)out_slot * BH + (size_t)(b0 + b) * a.H + j;
-                            if (a.hq_out) a.hq_out[o] = hn[i];
-                            if (a.hf_out) a.hf_out[o] = (float)(hn[i] - gc.zp_h) * gc.h_scale;
+                            h_nxt[sw128_offset(b, j, a.NB)] = (unsigned char)hn[mt][i];
+                            if (!last) {
+                                const size_t o = (size_t)out_slot * BH + (size_t)(b0 + b) * a.H + j;
+                                if (a.hq_out) a.hq_out[o] = hn[mt][i];
+                                if (a.hf_out) a.hf_out[o] = (float)(hn[mt][i] - gc.zp_h) * gc.h_scale;
+                            }
                         }
+                        hn_last[mt][i] = hn[mt][i];
                     }
                 }
+                if (last) c_last = c;
             }
-            if (ok && !waited) {   // a warp without a chunk still follows the phase of the MMA barrier
-                ok = tc::mbar_wait(mma_done, (uint32_t)(s & 1), WAIT_BUDGET);
+            if (ok && !waited) {
+                // A warp without a chunk still waits for this step's MMAs: it must not arrive on
+                // h_written twice within one phase.
+                ok = tc::mbar_wait(&mma_done[2], par, WAIT_BUDGET);
                 tc::tc_fence_after_sync();
             }
-            if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0) a.dbg[s * 8 + 7] = clock64();
+            if (stamp) a.dbg[s * 8 + 7] = clock64();
             // the bulk copy and the next MMA read these generic-proxy stores through the async proxy
             fence_proxy_async_cta();
             tc::tc_fence_before_sync();
             tc::mbar_arrive(h_written);
-            if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0) a.dbg[s * 8 + 5] = clock64();
+            if (stamp) a.dbg[s * 8 + 5] = clock64();
+            // Outputs of the last chunk leave for global memory after the arrive: nothing in the next
+            // step waits for them, so they overlap the exchange and the next MMAs.
+            if (c_last >= 0) {
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const int j = j0 + mt * 128 + u;
+#pragma unroll
+                    for (int i = 0; i < CH; ++i) {
+                        const int b = c_last * CH + i;
+                        if (b < nb && j_ok[mt]) {
+                            const size_t o = (size_t)out_slot * BH + (size_t)(b0 + b) * a.H + j;
+                            if (a.hq_out) a.hq_out[o] = hn_last[mt][i];
+                            if (a.hf_out) a.hf_out[o] = (float)(hn_last[mt][i] - gc.zp_h) * gc.h_scale;
+                        }
+                    }
+                }
+            }
         }
         if (!ok && lane == 0) atomicOr(a.abort_flag, 1);
     }
@@ -385,7 +522,8 @@ cudaError_t launch_any(bool fused, bool narrow, int ih_bytes, int MT, const CUte
 
 }  // namespace
 
-bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, RecMmaPlan *out) {
+bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, int r_where,
+                      RecMmaPlan *out) {
     if (Hpad > 512) return false;                  // the R slice of 128 units must fit one SM
     const int KBn = Hpad / 128;
     const int MT = (H > 128 && H <= 256) ? 2 : 1;
@@ -398,8 +536,15 @@ bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_tab
     while (NB > 16 && cluster_smem_layout(MT, KBn, NB, n_table).total + 1024 > (size_t)smem_optin) NB -= 16;
     const size_t smem = cluster_smem_layout(MT, KBn, NB, n_table).total + 1024;
     if (smem > (size_t)smem_optin) return false;
+    // R resident in tensor memory when it fits beside the accumulators (r_where: 0 auto, 1 shared
+    // memory, 2 tensor memory): 32 columns per 128x128 tile
+    const int acc_cols = (3 * MT * NB + 31) / 32 * 32;
+    const int r_cols = MT * 3 * KBn * 32;
+    const bool r_tmem = r_where != 1 && acc_cols + r_cols <= 512;
+    if (r_where == 2 && !r_tmem) return false;
     uint32_t cols = 32;
-    while ((int)cols < 3 * MT * NB) cols <<= 1;
+    while ((int)cols < (r_tmem ? acc_cols + r_cols : 3 * MT * NB)) cols <<= 1;
+    out->r_tmem_col = r_tmem ? acc_cols : 0;
     out->MT = MT;
     out->P = P;
     out->NB = NB;
@@ -434,6 +579,7 @@ int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const
     a.NB = pl.NB;
     a.h_unsigned = h_unsigned ? 1 : 0;
     a.tmem_cols = (uint32_t)pl.tmem_cols;
+    a.r_tmem_col = pl.r_tmem_col;
     a.b_off = 0;
     a.b_cnt = a.B;
     const cudaError_t e = launch_any(fused, narrow, ih_bytes, pl.MT, mr, mh, gc_host, a, pl.G * pl.P, pl.smem, stream);

@@ -19,6 +19,7 @@ struct RecMmaArgs {
     int reverse;
     int h_unsigned;   // the state h is stored as uint8 (else int8)
     uint32_t tmem_cols;
+    int r_tmem_col;   // first tensor-memory column of the resident R slice, 0: R stays in shared memory
     const void *ih;         // [T*B][3H]: raw W*x+bw (int8/int16) or pre-rescaled for the fused cell (int16/int32)
     uint8_t *h8;            // [2][B][Hpad] ping-pong state (+ slack rows)
     int32_t *hq_out;        // [(T+1)][B][H] or null
@@ -34,6 +35,7 @@ struct RecMmaArgs {
 
 struct RecMmaPlan {
     int MT = 1, P = 1, NB = 16, G = 1, tmem_cols = 32, groups_per_launch = 1;
+    int r_tmem_col = 0;
     size_t smem = 0;
 };
 
@@ -58,7 +60,8 @@ int rec_mma_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const Gat
 
 // The same kernel with the P CTAs of a group as one thread-block cluster exchanging h_t through
 // distributed shared memory (qgru_rec_cluster.cu).  Same plan fields; no cooperative launch.
-bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, RecMmaPlan *out);
+bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, int r_where,
+                      RecMmaPlan *out);
 
 int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const GateConsts &gc_host,
                        const int8_t *r8, long long r_rows_alloc, long long h_rows_alloc, bool h_unsigned,

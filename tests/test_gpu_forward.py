@@ -59,7 +59,7 @@ def _want(oracle, case):
                               case.params.scale_list())
 
 
-@pytest.mark.parametrize("rec", ["dp4a", "mma_cluster", "mma_global"])
+@pytest.mark.parametrize("rec", ["dp4a", "mma_cluster", "mma_cluster_smem", "mma_global"])
 @pytest.mark.parametrize("shape", SHAPES)
 def test_shapes_default_config(oracle, cuda_device, shape, rec):
     """The dp4a recurrence and the tcgen05 recurrence with both ways of exchanging the state
@@ -67,12 +67,15 @@ def test_shapes_default_config(oracle, cuda_device, shape, rec):
     T, B, I, H = shape
     case = make_case(11, T, B, I, H, oracle, config_named("default"))
     opts = {"dp4a": (("rec", "dp4a"),), "mma_cluster": (("rec", "mma"), ("exchange", "cluster")),
+            "mma_cluster_smem": (("rec", "mma"), ("exchange", "cluster"), ("r_resident", "smem")),
             "mma_global": (("rec", "mma"), ("exchange", "global"))}[rec]
     got, plan, launches = _run(case, cuda_device, opts=opts)
     assert "path=int8" in plan and launches > 0
     assert ("rec=tcgen05_i8" in plan) == (rec != "dp4a") and "gemm=tcgen05_i8" in plan
     if rec != "dp4a":
-        assert ("exchange=cluster_dsmem" in plan) == (rec == "mma_cluster")
+        assert ("exchange=cluster_dsmem" in plan) == rec.startswith("mma_cluster")
+    if rec.startswith("mma_cluster"):   # the R slice sits in tensor memory unless told otherwise
+        assert ("r_in=tmem" in plan) == (rec == "mma_cluster")
     assert np.array_equal(got, _want(oracle, case)), plan
 
 
