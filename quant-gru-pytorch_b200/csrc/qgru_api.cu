@@ -589,8 +589,12 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
     const LinearConsts lcx = linear_consts(h, 0);
     bool used_tc = false;
     if (h->opt_gemm != 1) {
+        // branch-free epilogue: 32-bit sums and every scale it applies in shift-free form
+        // (the launcher also looks at how the second rescale is applied: table or shift-free scale)
+        const bool gemm_fast = lcx.fits32 && h->rs_fast[0] && h->opt_cell != 2;
         rc = tc_gemm_launch(h->tc, (const uint8_t *)h->x8.p, (N + 127) / 128 * 128, h->d_w8[0], h->w8_rows[0],
-                            h->ih.p, N, C, h->Ipad, h->x_uns, ih_bytes, lcx, ps, h->d_flags + 1, sms, st, &h->err);
+                            h->ih.p, N, C, h->Ipad, h->x_uns, ih_bytes, lcx, ps, gemm_fast, h->d_flags + 1, sms, st,
+                            &h->err);
         if (rc == QGRU_OK) {
             used_tc = true;
             h->launches++;

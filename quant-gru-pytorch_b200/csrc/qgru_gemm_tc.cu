@@ -65,7 +65,9 @@ constexpr long long WAIT_BUDGET = 2000000000ll;  // ~1 s of SM clocks
 constexpr int PRE_TAB_MAX = 3 * 1024;              // pre-rescale table entries kept in shared memory
 constexpr size_t GEMM_SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256 + PRE_TAB_MAX * 4;
 
-template <bool XUnsigned, typename IhT>
+// Fast: every scale of the epilogue has the shift-free form and the sums fit 32 bits, so the
+// epilogue is branch-free (Rescale::mq, checked by the caller).
+template <bool XUnsigned, typename IhT, bool Fast>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
              IhT *__restrict__ ih, long long N, int C, int Kpad, LinearConsts lc, PreScale ps,
@@ -186,14 +188,35 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                     tc::tc_fence_before_sync();
                     if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
                 }
+                int32_t y[16];
+                if constexpr (Fast) {
+                    // all 16 values first, stores afterwards: the chains interleave
+                    if (use_tab) {
+                        const int32_t *tb = pre_tab + gate * ps.table_n - ps.lo;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) y[i] = tb[linear_epilogue_fast(v[i], c32, rs, lc.zp_out, lc.lo, lc.hi)];
+                    } else if (ps.enabled) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            y[i] = mul_round_hi(linear_epilogue_fast(v[i], c32, rs, lc.zp_out, lc.lo, lc.hi) - ps.zp_ih, pre_rs) + pre_zp;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) y[i] = linear_epilogue_fast(v[i], c32, rs, lc.zp_out, lc.lo, lc.hi);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        int32_t t = lc.fits32 ? linear_epilogue32(v[i], c32, rs, lc.zp_out, lc.lo, lc.hi)
+                                              : linear_epilogue(v[i], corr, rs, lc.zp_out, lc.lo, lc.hi);
+                        if (use_tab) t = pre_tab[gate * ps.table_n + (t - ps.lo)];
+                        else if (ps.enabled) t = (int32_t)rescale32(t - ps.zp_ih, pre_rs) + pre_zp;
+                        y[i] = t;
+                    }
+                }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const long long n = n0 + c0 + i;
-                    int32_t y = lc.fits32 ? linear_epilogue32(v[i], c32, rs, lc.zp_out, lc.lo, lc.hi)
-                                          : linear_epilogue(v[i], corr, rs, lc.zp_out, lc.lo, lc.hi);
-                    if (use_tab) y = pre_tab[gate * ps.table_n + (y - ps.lo)];
-                    else if (ps.enabled) y = (int32_t)rescale32(y - ps.zp_ih, pre_rs) + pre_zp;
-                    if (m_ok && n < N) out[n * C] = (IhT)y;
+                    if (m_ok && n < N) out[n * C] = (IhT)y[i];
                 }
             }
         }
@@ -205,10 +228,10 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     if (warp == 1) tc::tmem_dealloc(tmem_base, 2 * GN);
 }
 
-template <bool XU, typename IhT>
-cudaError_t launch(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long long N, int C, int Kpad,
-                   LinearConsts lc, PreScale ps, int *abort_flag, int sms, cudaStream_t st) {
-    auto kern = k_gemm_wx_tc<XU, IhT>;
+template <bool XU, typename IhT, bool Fast>
+cudaError_t launch_f(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long long N, int C, int Kpad,
+                     LinearConsts lc, PreScale ps, int *abort_flag, int sms, cudaStream_t st) {
+    auto kern = k_gemm_wx_tc<XU, IhT, Fast>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
     if (e != cudaSuccess) return e;
     const long long tiles = (long long)((C + GM - 1) / GM) * ((N + GN - 1) / GN);
@@ -217,12 +240,19 @@ cudaError_t launch(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long 
     return cudaGetLastError();
 }
 
+template <bool XU, typename IhT>
+cudaError_t launch(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long long N, int C, int Kpad,
+                   LinearConsts lc, PreScale ps, bool fast, int *abort_flag, int sms, cudaStream_t st) {
+    return fast ? launch_f<XU, IhT, true>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, st)
+                : launch_f<XU, IhT, false>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, st);
+}
+
 }  // namespace
 
 int tc_gemm_launch(TcGemmState &s, const uint8_t *x8, long long x_rows_alloc, const int8_t *w8,
                    long long w_rows_alloc, void *ih, long long N, int C, int Kpad, bool x_unsigned,
-                   int ih_bytes, LinearConsts lc, PreScale ps, int *abort_flag, int sms, cudaStream_t stream,
-                   std::string *err) {
+                   int ih_bytes, LinearConsts lc, PreScale ps, bool fast, int *abort_flag, int sms,
+                   cudaStream_t stream, std::string *err) {
     if (Kpad % KB != 0 || x_rows_alloc < (N + GN - 1) / GN * GN || w_rows_alloc < (C + GM - 1) / GM * GM) {
         if (err) *err = "tcgen05 GEMM needs K padded to 128 and operand rows padded to the tile";
         return QGRU_ERR_UNSUPPORTED;
@@ -244,16 +274,19 @@ int tc_gemm_launch(TcGemmState &s, const uint8_t *x8, long long x_rows_alloc, co
     }
     const CUtensorMap &mw = *reinterpret_cast<const CUtensorMap *>(s.map_w);
     const CUtensorMap &mx = *reinterpret_cast<const CUtensorMap *>(s.map_x);
+    // the branch-free epilogue applies the second rescale from the table, or needs its shift-free form
+    const bool tab = ps.enabled && ps.table != nullptr && 3 * ps.table_n <= PRE_TAB_MAX;
+    fast = fast && (!ps.enabled || tab || (ps.to[0].mq != 0 && ps.to[1].mq != 0 && ps.to[2].mq != 0));
     cudaError_t e;
     if (ih_bytes == 1)
-        e = x_unsigned ? launch<true, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, stream)
-                       : launch<false, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, stream);
+        e = x_unsigned ? launch<true, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, stream)
+                       : launch<false, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, stream);
     else if (ih_bytes == 2)
-        e = x_unsigned ? launch<true, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, stream)
-                       : launch<false, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, stream);
+        e = x_unsigned ? launch<true, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, stream)
+                       : launch<false, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, stream);
     else
-        e = x_unsigned ? launch<true, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, stream)
-                       : launch<false, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, stream);
+        e = x_unsigned ? launch<true, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, stream)
+                       : launch<false, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, stream);
     if (e != cudaSuccess) {
         if (err) *err = std::string("tcgen05 GEMM launch: ") + cudaGetErrorString(e);
         return QGRU_ERR_CUDA;
