@@ -192,9 +192,10 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                 if constexpr (Fast) {
                     // all 16 values first, stores afterwards: the chains interleave
                     if (use_tab) {
-                        const int32_t *tb = pre_tab + gate * ps.table_n - ps.lo;
+                        const uint32_t tb = tc::smem_u32(pre_tab) + (uint32_t)((gate * ps.table_n - ps.lo) * 4);
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) y[i] = tb[linear_epilogue_fast(v[i], c32, rs, lc.zp_out, lc.lo, lc.hi)];
+                        for (int i = 0; i < 16; ++i)
+                            y[i] = tc::lds_i32(tb + 4u * (uint32_t)linear_epilogue_fast(v[i], c32, rs, lc.zp_out, lc.lo, lc.hi));
                     } else if (ps.enabled) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
@@ -213,10 +214,15 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                         y[i] = t;
                     }
                 }
+                // token n of channel m lives at ih[n * C + m]: one pointer walked by C elements
+                IhT *po = out + (n0 + c0) * C;
+                if (m_ok && n0 + c0 + 16 <= N) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const long long n = n0 + c0 + i;
-                    if (m_ok && n < N) out[n * C] = (IhT)y[i];
+                    for (int i = 0; i < 16; ++i, po += C) *po = (IhT)y[i];
+                } else if (m_ok) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i, po += C)
+                        if (n0 + c0 + i < N) *po = (IhT)y[i];
                 }
             }
         }
