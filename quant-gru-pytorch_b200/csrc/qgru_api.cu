@@ -116,6 +116,7 @@ void qgru_destroy(qgru_handle *h) {
     for (int i = 0; i < 2; ++i) {
         cudaFree(h->d_rs[i]);
         cudaFree(h->d_brs[i]);
+        cudaFree(h->d_fl[i]);
         cudaFree(h->d_corr[i]);
         cudaFree(h->d_wsum[i]);
         cudaFree(h->d_w8[i]);
@@ -381,6 +382,7 @@ int qgru_set_params(qgru_handle *h, const qgru_params *p, const float *scale_W,
     for (int s = 0; s < 2; ++s) {
         if ((rc = alloc_dev(h, &h->d_rs[s], C))) return rc;
         if ((rc = alloc_dev(h, &h->d_brs[s], C))) return rc;
+        if ((rc = alloc_dev(h, &h->d_fl[s], C))) return rc;
         if ((rc = alloc_dev(h, &h->d_corr[s], C))) return rc;
         if ((rc = alloc_dev(h, &h->d_wsum[s], C))) return rc;
     }
@@ -423,10 +425,10 @@ int finish_weights(qgru_handle *h, cudaStream_t st) {
                                       h->Hpad, C, h->d_flags);
     const int gb = (C + 127) / 128;
     k_channel_consts<<<gb, 128, 0, st>>>(h->d_wq[2], h->d_brs[0], h->d_wsum[0],
-                                         h->p.op[QGRU_OP_X].zero_point, h->d_corr[0], C,
+                                         h->p.op[QGRU_OP_X].zero_point, h->d_corr[0], h->d_rs[0], h->d_fl[0], C,
                                          (long long)h->I * 128 * 255, h->d_flags, 8);
     k_channel_consts<<<gb, 128, 0, st>>>(h->d_wq[3], h->d_brs[1], h->d_wsum[1],
-                                         h->p.op[QGRU_OP_H].zero_point, h->d_corr[1], C,
+                                         h->p.op[QGRU_OP_H].zero_point, h->d_corr[1], h->d_rs[1], h->d_fl[1], C,
                                          (long long)h->H * 128 * 255, h->d_flags, 16);
     h->launches += 4;
     CK(cudaGetLastError());
@@ -508,6 +510,7 @@ LinearConsts linear_consts(const qgru_handle *h, int side) {
     LinearConsts lc;
     lc.corr = h->d_corr[side];
     lc.rs = h->d_rs[side];
+    lc.fl = h->d_fl[side];
     const qgru_op &o = h->p.op[side == 0 ? QGRU_OP_IH_LINEAR : QGRU_OP_HH_LINEAR];
     lc.zp_out = o.zero_point;
     lc.lo = op_qmin(o);

@@ -130,9 +130,9 @@ __device__ __forceinline__ int32_t linear_epilogue32(int32_t acc, int32_t corr, 
 }
 
 // linear_epilogue32 for a scale with the shift-free form.
-__device__ __forceinline__ int32_t linear_epilogue_fast(int32_t acc, int32_t corr, const Rescale &rs,
-                                                        int32_t zp_out, int32_t lo, int32_t hi) {
-    return clampi(mul_round_hi(acc + corr, rs) + zp_out, lo, hi);
+__device__ __forceinline__ int32_t linear_epilogue_fast(int32_t acc, const FastLin &f, int32_t zp_out,
+                                                        int32_t lo, int32_t hi) {
+    return clampi(lin_round(acc, f) + zp_out, lo, hi);
 }
 
 }  // namespace qgru

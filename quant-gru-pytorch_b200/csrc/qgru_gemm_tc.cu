@@ -169,7 +169,8 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             const int m = m0 + q * 32 + lane;
             const bool m_ok = m < C;
             const int64_t corr = m_ok ? lc.corr[m] : 0;
-            const Rescale rs = m_ok ? lc.rs[m] : Rescale{1, 1, 0, 0, 0, 0};
+            const Rescale rs = m_ok ? lc.rs[m] : Rescale{1, 1, 0, 0, 0, 0, 0, 0};
+            const FastLin fl = m_ok ? lc.fl[m] : FastLin{0, 0, 0, 0, 0, 0};
             // fused-cell mode: the channel's gate decides the second rescale (to its input scale)
             const int gate = (ps.enabled && m_ok) ? m / ps.H : 0;
             const Rescale pre_rs = ps.to[gate];
@@ -195,14 +196,14 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                         const uint32_t tb = tc::smem_u32(pre_tab) + (uint32_t)((gate * ps.table_n - ps.lo) * 4);
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
-                            y[i] = tc::lds_i32(tb + 4u * (uint32_t)linear_epilogue_fast(v[i], c32, rs, lc.zp_out, lc.lo, lc.hi));
+                            y[i] = tc::lds_i32(tb + 4u * (uint32_t)linear_epilogue_fast(v[i], fl, lc.zp_out, lc.lo, lc.hi));
                     } else if (ps.enabled) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
-                            y[i] = mul_round_hi(linear_epilogue_fast(v[i], c32, rs, lc.zp_out, lc.lo, lc.hi) - ps.zp_ih, pre_rs) + pre_zp;
+                            y[i] = mul_round_hi(linear_epilogue_fast(v[i], fl, lc.zp_out, lc.lo, lc.hi) - ps.zp_ih, pre_rs) + pre_zp;
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) y[i] = linear_epilogue_fast(v[i], c32, rs, lc.zp_out, lc.lo, lc.hi);
+                        for (int i = 0; i < 16; ++i) y[i] = linear_epilogue_fast(v[i], fl, lc.zp_out, lc.lo, lc.hi);
                     }
                 } else {
 #pragma unroll

@@ -51,6 +51,7 @@ struct qgru_handle {
     int n_ftable = 0;
     Rescale *d_rs[2] = {nullptr, nullptr};    // gemm rescale: x side, h side
     Rescale *d_brs[2] = {nullptr, nullptr};   // bias rescale
+    qgru::FastLin *d_fl[2] = {nullptr, nullptr};  // rs + corr folded (filled with the weights)
     float *d_wscale[4] = {nullptr, nullptr, nullptr, nullptr};
     int64_t *d_corr[2] = {nullptr, nullptr};
     int32_t *d_wq[4] = {nullptr, nullptr, nullptr, nullptr};  // W_q, R_q, bw_q, br_q

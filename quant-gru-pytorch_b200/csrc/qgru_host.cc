@@ -36,6 +36,8 @@ bool encode_mshift(float scale, Rescale *out) {
     out->e = 0;
     out->add_hi = 0;
     out->add_lo = 0;
+    out->emask = 0;
+    out->pad = 0;
     return true;
 }
 
@@ -48,7 +50,7 @@ int pot2_shift(float scale) {
 // toFixedScale, include/quantize_ops_helper.h:280-283.
 bool to_fixed_scale(float scale, bool pot2, Rescale *out) {
     if (pot2) {
-        *out = Rescale{1, pot2_shift(scale), 0, 0, 0, 0};
+        *out = Rescale{1, pot2_shift(scale), 0, 0, 0, 0, 0, 0};
         return true;
     }
     return encode_mshift(scale, out);
@@ -62,7 +64,7 @@ float decode_scale(Rescale r) {
 // makeRescale<R>, include/quantize_ops_helper.h:296-312.
 bool make_rescale(float src, float dst, bool pot2, Rescale *out) {
     if (pot2) {
-        *out = Rescale{1, static_cast<int8_t>(pot2_shift(src) - pot2_shift(dst)), 0, 0, 0, 0};
+        *out = Rescale{1, static_cast<int8_t>(pot2_shift(src) - pot2_shift(dst)), 0, 0, 0, 0, 0, 0};
         return true;
     }
     return encode_mshift(src / dst, out);
@@ -70,7 +72,7 @@ bool make_rescale(float src, float dst, bool pot2, Rescale *out) {
 // makeRescaleProduct<R>, include/quantize_ops_helper.h:315-331.
 bool make_rescale_product(float a, float b, float dst, bool pot2, Rescale *out) {
     if (pot2) {
-        *out = Rescale{1, static_cast<int8_t>(pot2_shift(a) + pot2_shift(b) - pot2_shift(dst)), 0, 0, 0, 0};
+        *out = Rescale{1, static_cast<int8_t>(pot2_shift(a) + pot2_shift(b) - pot2_shift(dst)), 0, 0, 0, 0, 0, 0};
         return true;
     }
     return encode_mshift((a * b) / dst, out);
@@ -78,7 +80,7 @@ bool make_rescale_product(float a, float b, float dst, bool pot2, Rescale *out) 
 // makeRescaleToProduct<R>, include/quantize_ops_helper.h:334-350.
 bool make_rescale_to_product(float src, float a, float b, bool pot2, Rescale *out) {
     if (pot2) {
-        *out = Rescale{1, static_cast<int8_t>(pot2_shift(src) - (pot2_shift(a) + pot2_shift(b))), 0, 0, 0, 0};
+        *out = Rescale{1, static_cast<int8_t>(pot2_shift(src) - (pot2_shift(a) + pot2_shift(b))), 0, 0, 0, 0, 0, 0};
         return true;
     }
     return encode_mshift(src / (a * b), out);
@@ -335,7 +337,7 @@ int qgru_encode_mshift(float scale, uint16_t *multiplier, int8_t *shift) {
 int64_t qgru_rshift_round(int64_t x, int n) { return rshift_round64(x, n); }
 
 int32_t qgru_apply_rescale(int32_t x, uint16_t multiplier, int shift) {
-    Rescale r{(int32_t)multiplier, shift, 0, 0, 0, 0};
+    Rescale r{(int32_t)multiplier, shift, 0, 0, 0, 0, 0, 0};
     set_fast_form(&r);
     return rescale32(x, r);
 }

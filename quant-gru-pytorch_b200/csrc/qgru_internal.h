@@ -71,6 +71,7 @@ struct PreScale {
 struct LinearConsts {
     const int64_t *corr;  // [3H] device
     const Rescale *rs;    // [3H] device
+    const FastLin *fl;    // [3H] device: rs and corr in the folded shift-free form (mq == 0: none)
     int32_t zp_out, lo, hi;
     int32_t fits32;       // 1: acc + corr fits int32 for every channel (one widening multiply)
 };

@@ -130,12 +130,14 @@ __global__ void k_pack_weights(const int32_t *__restrict__ wq, int8_t *__restric
 __global__ void k_channel_consts(const int32_t *__restrict__ bias_q,
                                  const Rescale *__restrict__ bias_rs,
                                  const int32_t *__restrict__ wsum, int32_t zp_in,
-                                 int64_t *__restrict__ corr, int C, long long acc_bound, int *flags,
+                                 int64_t *__restrict__ corr, const Rescale *__restrict__ rs,
+                                 FastLin *__restrict__ fl, int C, long long acc_bound, int *flags,
                                  int flag_bit) {
     const int m = blockIdx.x * blockDim.x + threadIdx.x;
     if (m >= C) return;
     const int64_t c = rescale64((int64_t)bias_q[m], bias_rs[m]) - (int64_t)zp_in * (int64_t)wsum[m];
     corr[m] = c;
+    fl[m] = make_fast_lin(rs[m], c);
     // acc + corr must stay inside int32 for the one-multiply epilogue
     const int64_t mag = c < 0 ? -c : c;
     if (mag + acc_bound >= 0x7fffffffll) atomicOr(flags, flag_bit);
@@ -282,7 +284,7 @@ __global__ void __launch_bounds__(256, 1) k_recurrence_dp4a(RecArgs a) {
         const int g = i / a.Hs, jl = i % a.Hs, j = j0 + jl;
         const bool ok = j < a.H;
         corr[i] = ok ? a.lc.corr[g * a.H + j] : 0;
-        rs[i] = ok ? a.lc.rs[g * a.H + j] : Rescale{1, 1, 0, 0, 0, 0};
+        rs[i] = ok ? a.lc.rs[g * a.H + j] : Rescale{1, 1, 0, 0, 0, 0, 0, 0};
     }
     {
         const unsigned *r8w = reinterpret_cast<const unsigned *>(a.r8);

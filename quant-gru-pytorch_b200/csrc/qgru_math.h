@@ -25,8 +25,19 @@ struct Rescale {
     // Shift-free form (set_fast_form; mq == 0 where it does not exist), see mul_round_hi:
     int32_t mq;      // mult << k, k chosen so that 2^30 <= mq < 2^31
     int32_t e;       // shift + k - 32, 0..31: the quotient is the high product word >> e
-    int32_t add_hi;  // high and low word of 2^(31+e) - 1, the rounding addend
+    int32_t add_hi;  // high and low word of 2^(31+e): one half in units of the quotient
     uint32_t add_lo;
+    int32_t emask;   // 2^e - 1: the bits of the high word that belong to the remainder
+    int32_t pad;
+};
+
+// A fused linear layer's requantization with its per-channel constant folded into the rounding
+// addend: k = corr * mq + 2^(31+e), so that out = round(acc * mq + k) handles acc + corr in the
+// one multiply-add (see lin_round).  mq == 0: the channel has no such form.
+struct FastLin {
+    int32_t mq, e, emask, k_hi;
+    uint32_t k_lo;
+    int32_t pad;
 };
 
 // rshift_round(int64_t, int8_t) (include/quantize_ops_helper.h:183-206): round half to even
@@ -48,34 +59,63 @@ QG_HD int64_t rescale64(int64_t x, Rescale r) { return rshift_round64(x * (int64
 // product x * (mult << k) of a 32-bit x stays below 2^62 and equals x * mult * 2^k, so
 // x * mult / 2^shift == product / 2^(32 + e) with e = shift + k - 32.  The form exists for
 // 0 <= e <= 31: shifts 17..48 of a 16-bit multiplier, 2..33 in POT2 mode (mult = 1).
-inline void set_fast_form(Rescale *r) {
+QG_HD void set_fast_form(Rescale *r) {
     r->mq = 0;
     r->e = 0;
     r->add_hi = 0;
     r->add_lo = 0;
+    r->emask = 0;
+    r->pad = 0;
     if (r->mult <= 0 || r->mult > 65535) return;
     int lg = 0;
     while ((r->mult >> (lg + 1)) != 0) ++lg;
     const int k = 30 - lg, e = r->shift + k - 32;
     if (e < 0 || e > 31) return;
-    const uint64_t add = ((uint64_t)1 << (31 + e)) - 1;
+    const uint64_t add = (uint64_t)1 << (31 + e);
     r->mq = (int32_t)((uint32_t)r->mult << k);
     r->e = e;
     r->add_hi = (int32_t)(add >> 32);
     r->add_lo = (uint32_t)add;
+    r->emask = (int32_t)(((uint32_t)1 << e) - 1u);
 }
 
-// Round-half-even of x * mult / 2^shift through the shift-free form: the floor quotient is
-// the high word of the 64-bit product shifted right by e, its parity decides ties, and the
-// addend 2^(31+e) - 1 (+1 for an odd floor) carries into bit 32+e exactly when the remainder
-// is above one half, or equal to it with an odd floor - the rule of rshift_round64 with
-// n = 32 + e.  Only 32-bit shifts by a uniform amount; no branch.
+// Round-half-even of t / 2^(32+e), where t already holds the value plus one half (2^(31+e)):
+// the arithmetic shift gives round-half-up; the value was an exact tie precisely when the low
+// 32+e bits of t are all zero, and then the even neighbour is the result with its lowest bit
+// cleared.  Equal to rshift_round64(value, 32 + e); a 32-bit shift by a uniform amount, one
+// compare, one select.
+QG_HD int32_t round_tie_even(int64_t t, int32_t e, int32_t emask) {
+    const int32_t hi = (int32_t)(t >> 32);
+    const uint32_t lo = (uint32_t)t;
+    const int32_t q = hi >> e;
+    return ((((uint32_t)hi & (uint32_t)emask) | lo) == 0u) ? (q & ~1) : q;
+}
+
+// Round-half-even of x * mult / 2^shift through the shift-free form.
 QG_HD int32_t mul_round_hi(int32_t x, const Rescale &r) {
-    const int64_t p = (int64_t)x * (int64_t)r.mq;
-    const int32_t odd = ((int32_t)(p >> 32) >> r.e) & 1;
     const int64_t add = (int64_t)(((uint64_t)(uint32_t)r.add_hi << 32) | (uint64_t)r.add_lo);
-    const int64_t t = p + add + (int64_t)odd;
-    return (int32_t)(t >> 32) >> r.e;
+    return round_tie_even((int64_t)x * (int64_t)r.mq + add, r.e, r.emask);
+}
+
+// Round-half-even of (acc + corr) * mult / 2^shift with corr folded into f's addend.
+QG_HD int32_t lin_round(int32_t acc, const FastLin &f) {
+    const int64_t k = (int64_t)(((uint64_t)(uint32_t)f.k_hi << 32) | (uint64_t)f.k_lo);
+    return round_tie_even((int64_t)acc * (int64_t)f.mq + k, f.e, f.emask);
+}
+
+// FastLin of a channel: the scale's shift-free form and its constant corr (|corr| < 2^31).
+QG_HD FastLin make_fast_lin(const Rescale &r, int64_t corr) {
+    FastLin f;
+    f.mq = 0; f.e = 0; f.emask = 0; f.k_hi = 0; f.k_lo = 0; f.pad = 0;
+    if (r.mq == 0 || corr >= 0x7fffffffll || corr <= -0x7fffffffll) return f;
+    const int64_t add = (int64_t)(((uint64_t)(uint32_t)r.add_hi << 32) | (uint64_t)r.add_lo);
+    const int64_t k = corr * (int64_t)r.mq + add;
+    f.mq = r.mq;
+    f.e = r.e;
+    f.emask = r.emask;
+    f.k_hi = (int32_t)(k >> 32);
+    f.k_lo = (uint32_t)k;
+    return f;
 }
 
 // applyRescale for an operand known to fit in int32.  Scales without the shift-free form

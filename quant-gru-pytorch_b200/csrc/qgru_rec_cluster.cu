@@ -243,6 +243,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
         const int nchunks = a.NB / CH;
         int64_t corr[MT][3];
         Rescale rs[MT][3];
+        FastLin fl[MT][3];
         bool j_ok[MT];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
@@ -251,7 +252,8 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
 #pragma unroll
             for (int g = 0; g < 3; ++g) {
                 corr[mt][g] = j_ok[mt] ? a.lc.corr[g * a.H + j] : 0;
-                rs[mt][g] = j_ok[mt] ? a.lc.rs[g * a.H + j] : Rescale{1, 1, 0, 0, 0, 0};
+                rs[mt][g] = j_ok[mt] ? a.lc.rs[g * a.H + j] : Rescale{1, 1, 0, 0, 0, 0, 0, 0};
+                fl[mt][g] = j_ok[mt] ? a.lc.fl[g * a.H + j] : FastLin{0, 0, 0, 0, 0, 0};
             }
         }
         bool ok = true;
@@ -335,7 +337,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
 #pragma unroll
                         for (int i = 0; i < CH; ++i)
                             zd[mt][i] = fused_gate_fast(gc, tables, ACT_Z, ihv[mt][i][0],
-                                                        linear_epilogue_fast(acc[mt][i], (int32_t)corr[mt][0], rs[mt][0],
+                                                        linear_epilogue_fast(acc[mt][i], fl[mt][0],
                                                                              a.lc.zp_out, a.lc.lo, a.lc.hi));
                     // reset gate
                     if (!waited) {
@@ -351,7 +353,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
 #pragma unroll
                         for (int i = 0; i < CH; ++i)
                             rd[mt][i] = fused_gate_fast(gc, tables, ACT_R, ihv[mt][i][1],
-                                                        linear_epilogue_fast(acc[mt][i], (int32_t)corr[mt][1], rs[mt][1],
+                                                        linear_epilogue_fast(acc[mt][i], fl[mt][1],
                                                                              a.lc.zp_out, a.lc.lo, a.lc.hi));
                     // new gate and the state update
                     if (!waited) {
@@ -369,7 +371,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
 #pragma unroll
                         for (int i = 0; i < CH; ++i)
                             hn[mt][i] = fused_finish_fast(gc, tables, ihv[mt][i][2],
-                                                          linear_epilogue_fast(acc[mt][i], (int32_t)corr[mt][2], rs[mt][2],
+                                                          linear_epilogue_fast(acc[mt][i], fl[mt][2],
                                                                                a.lc.zp_out, a.lc.lo, a.lc.hi),
                                                           zd[mt][i], rd[mt][i], hold[mt][i]);
                 } else {

@@ -185,7 +185,7 @@ k_recurrence_mma(const __grid_constant__ CUtensorMap map_r, const __grid_constan
 #pragma unroll
             for (int g = 0; g < 3; ++g) {
                 corr[mt][g] = j_ok[mt] ? a.lc.corr[g * a.H + j] : 0;
-                rs[mt][g] = j_ok[mt] ? a.lc.rs[g * a.H + j] : Rescale{1, 1, 0, 0, 0, 0};
+                rs[mt][g] = j_ok[mt] ? a.lc.rs[g * a.H + j] : Rescale{1, 1, 0, 0, 0, 0, 0, 0};
             }
         }
         bool ok = true;
