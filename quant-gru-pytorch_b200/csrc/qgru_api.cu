@@ -356,6 +356,20 @@ int qgru_set_params(qgru_handle *h, const qgru_params *p, const float *scale_W,
             const int64_t lim = 0x7fffffffll;
             if (max_zd * max_hd + max_omz * max_nd >= lim || max_rd * max_hhd >= lim || max_pre >= lim) fused = false;
         }
+        if (fused) {
+            for (int k = 0; k < 3; ++k) {
+                g.fi_c[k] = g.ft_off[k] - g.in_lo[k];
+                g.fi_lo[k] = g.ft_off[k];
+                g.fi_hi[k] = g.ft_off[k] + (g.in_hi[k] - g.in_lo[k]);
+            }
+            for (int k = 3; k < 5; ++k) {
+                g.fi_c[k] = g.zp_hh - g.hh_lo + g.ft_off[k];
+                g.fi_lo[k] = g.ft_off[k];
+                g.fi_hi[k] = g.ft_off[k] + (g.hh_hi - g.hh_lo);
+            }
+            g.hn_clo = g.hh_lo - g.zp_hh;
+            g.hn_chi = g.hh_hi - g.zp_hh;
+        }
         g.fused_ok = fused ? 1 : 0;
         g.ih_pre_bytes = max_pre < 32768 ? 2 : 4;
         if (!fused) ft.clear();

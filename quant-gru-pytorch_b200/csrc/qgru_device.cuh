@@ -97,23 +97,44 @@ __device__ __forceinline__ int32_t gru_cell_fused(const GateConsts &gc, const in
     return clampi((int32_t)rescale32(comb, gc.uh_to_h) + gc.zp_h, gc.h_lo, gc.h_hi);
 }
 
+// 32-bit load from a shared-memory window address: table lookups stay on the shared-memory
+// path with 32-bit address arithmetic.
+__device__ __forceinline__ int32_t lds_i32(uint32_t addr) {
+    int32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+// Sign- or zero-extend a state byte held in the low bits of x: bits = 8 for int8 storage, 9 for
+// uint8 (bit 8 is zero, so the value stays non-negative).
+__device__ __forceinline__ int32_t state_byte(uint32_t x, uint32_t bits) {
+    int32_t d;
+    asm("bfe.s32 %0, %1, 0, %2;" : "=r"(d) : "r"(x), "r"(bits));
+    return d;
+}
+
 // gru_cell_fused for scales that all have the shift-free form (Rescale::mq != 0, checked on the
 // host): no branch anywhere, so the compiler can interleave the dependency chains of several
-// cells, which is what hides the table-lookup latency at four warps per scheduler.  In three
-// pieces, so that a kernel can start on the update and reset gates while the tensor core still
-// works on the rows of the new gate.
-//   which = ACT_Z / ACT_R: sigmoid LUT output minus its zero point
-__device__ __forceinline__ int32_t fused_gate_fast(const GateConsts &gc, const int32_t *ft, int which,
-                                                   int32_t a_pre, int32_t hh) {
-    const int32_t pre = a_pre + ft[gc.ft_off[3 + which] + (hh - gc.hh_lo)];
-    return ft[gc.ft_off[which] + (clampi(pre, gc.in_lo[which], gc.in_hi[which]) - gc.in_lo[which])];
+// cells, which is what hides the table-lookup latency at four warps per scheduler.  Zero
+// points, clamps and table offsets are folded into one add and one max/min pair per lookup
+// (GateConsts::fi_*).  In three pieces, so that a kernel can start on the update and reset
+// gates while the tensor core still works on the rows of the new gate.  `tab` is the
+// shared-window address of the fused table block, `q` a requantized R*h row before its zero
+// point (lin_round).
+__device__ __forceinline__ int32_t ft_lookup(const GateConsts &gc, uint32_t tab, int k, int32_t v) {
+    const int32_t idx = min(max(v + gc.fi_c[k], gc.fi_lo[k]), gc.fi_hi[k]);
+    return lds_i32(tab + 4u * (uint32_t)idx);
 }
-__device__ __forceinline__ int32_t fused_finish_fast(const GateConsts &gc, const int32_t *ft, int32_t a_n,
-                                                     int32_t hh_n, int32_t z_d, int32_t r_d, int32_t h_old) {
-    const int32_t n_pre = a_n + mul_round_hi(r_d * (hh_n - gc.zp_hh), gc.rh_to_n);
-    const int32_t n_d = ft[gc.ft_off[2] + (clampi(n_pre, gc.in_lo[ACT_N], gc.in_hi[ACT_N]) - gc.in_lo[ACT_N])];
+//   which = ACT_Z / ACT_R: sigmoid LUT output minus its zero point
+__device__ __forceinline__ int32_t fused_gate_fast(const GateConsts &gc, uint32_t tab, int which, int32_t a_pre,
+                                                   int32_t q) {
+    return ft_lookup(gc, tab, which, a_pre + ft_lookup(gc, tab, 3 + which, q));
+}
+__device__ __forceinline__ int32_t fused_finish_fast(const GateConsts &gc, uint32_t tab, int32_t a_n, int32_t q_n,
+                                                     int32_t z_d, int32_t r_d, int32_t h_old) {
+    const int32_t hh_nd = min(max(q_n, gc.hn_clo), gc.hn_chi);        // R*h row of the new gate minus zp
+    const int32_t n_d = ft_lookup(gc, tab, ACT_N, a_n + mul_round_hi(r_d * hh_nd, gc.rh_to_n));
     const int32_t comb = z_d * (h_old - gc.zp_h) + (gc.k1 - z_d) * n_d;
-    return clampi(mul_round_hi(comb, gc.uh_to_h) + gc.zp_h, gc.h_lo, gc.h_hi);
+    return min(max(mul_round_hi(comb, gc.uh_to_h) + gc.zp_h, gc.h_lo), gc.h_hi);
 }
 
 // Epilogue of a fused linear layer (src/gru_forward_cpu_quant.cc:130-138).

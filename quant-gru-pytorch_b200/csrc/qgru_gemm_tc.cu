@@ -193,10 +193,13 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                 if constexpr (Fast) {
                     // all 16 values first, stores afterwards: the chains interleave
                     if (use_tab) {
-                        const uint32_t tb = tc::smem_u32(pre_tab) + (uint32_t)((gate * ps.table_n - ps.lo) * 4);
+                        // zero point, clamp and table offset folded into one add and a max/min pair
+                        const uint32_t tb = tc::smem_u32(pre_tab);
+                        const int32_t t_c = gate * ps.table_n + lc.zp_out - ps.lo;
+                        const int32_t t_lo = gate * ps.table_n + lc.lo - ps.lo, t_hi = t_lo + (lc.hi - lc.lo);
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
-                            y[i] = tc::lds_i32(tb + 4u * (uint32_t)linear_epilogue_fast(v[i], fl, lc.zp_out, lc.lo, lc.hi));
+                            y[i] = lds_i32(tb + 4u * (uint32_t)min(max(lin_round(v[i], fl) + t_c, t_lo), t_hi));
                     } else if (ps.enabled) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i)

@@ -49,6 +49,12 @@ struct GateConsts {
     int32_t ft_off[5];                    // offsets of TZ, TR, TN, THZ, THR in the fused table block
     int32_t ih_pre_bytes;                 // storage width (2 or 4) of the pre-rescaled W*x+bw values
     int32_t ft_ih_off, ft_ih_n;           // table of the GEMM-side pre-rescale in the same block (n per gate, 0: none)
+    // Index arithmetic of the five fused-cell lookups with the zero points, the clamp and the
+    // table offset folded: entry = table[min(max(v + fi_c[k], fi_lo[k]), fi_hi[k])], k = TZ, TR,
+    // TN (v = gate input before its clamp) or THZ, THR (v = requantized R*h row before its zero
+    // point).  hn_clo/hn_chi clamp the new gate's R*h row in the same zero-point-free domain.
+    int32_t fi_c[5], fi_lo[5], fi_hi[5];
+    int32_t hn_clo, hn_chi;
     qgru_lut lut[3];
 };
 

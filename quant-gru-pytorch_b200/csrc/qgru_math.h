@@ -142,7 +142,11 @@ QG_HD int32_t qmax_of(int bits, bool uns) {
     if (bits >= 32) return 0x7FFFFFFF;
     return uns ? (int32_t)((1u << bits) - 1u) : (1 << (bits - 1)) - 1;
 }
-QG_HD int32_t clampi(int32_t v, int32_t lo, int32_t hi) { return v < lo ? lo : (v > hi ? hi : v); }
+// max then min (two instructions on the device); equal to the usual clamp for lo <= hi
+QG_HD int32_t clampi(int32_t v, int32_t lo, int32_t hi) {
+    const int32_t t = v > lo ? v : lo;
+    return t < hi ? t : hi;
+}
 
 // piecewise_linear_raw on an already clamped input (include/quantize_ops_helper.h:560-589):
 // first segment whose threshold exceeds q, else the last one.

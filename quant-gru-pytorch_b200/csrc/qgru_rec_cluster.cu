@@ -241,6 +241,8 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
         const size_t BH = (size_t)a.B * a.H;
         const IhT *ihp = reinterpret_cast<const IhT *>(a.ih);
         const int nchunks = a.NB / CH;
+        const uint32_t tab = tc::smem_u32(tables);          // fused-cell tables, shared-window address
+        const uint32_t h_bits = a.h_unsigned ? 9u : 8u;     // state bytes: zero- or sign-extended
         int64_t corr[MT][3];
         Rescale rs[MT][3];
         FastLin fl[MT][3];
@@ -310,7 +312,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         for (int g = 0; g < 3; ++g)
                             ihv[mt][i][g] = v_ok ? (int32_t)ihp[row * a.C + g * a.H + j] : 0;
                         const uint8_t hb = v_ok ? h_cur[sw128_offset(b, j, a.NB)] : (uint8_t)0;
-                        hold[mt][i] = a.h_unsigned ? (int32_t)hb : (int32_t)(int8_t)hb;
+                        hold[mt][i] = state_byte(hb, h_bits);
                     }
                 }
                 // All CH cells of a tile are computed before anything is stored: a byte store into
@@ -336,9 +338,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                         for (int i = 0; i < CH; ++i)
-                            zd[mt][i] = fused_gate_fast(gc, tables, ACT_Z, ihv[mt][i][0],
-                                                        linear_epilogue_fast(acc[mt][i], fl[mt][0],
-                                                                             a.lc.zp_out, a.lc.lo, a.lc.hi));
+                            zd[mt][i] = fused_gate_fast(gc, tab, ACT_Z, ihv[mt][i][0], lin_round(acc[mt][i], fl[mt][0]));
                     // reset gate
                     if (!waited) {
                         ok = tc::mbar_wait(&mma_done[1], par, WAIT_BUDGET);
@@ -352,9 +352,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                         for (int i = 0; i < CH; ++i)
-                            rd[mt][i] = fused_gate_fast(gc, tables, ACT_R, ihv[mt][i][1],
-                                                        linear_epilogue_fast(acc[mt][i], fl[mt][1],
-                                                                             a.lc.zp_out, a.lc.lo, a.lc.hi));
+                            rd[mt][i] = fused_gate_fast(gc, tab, ACT_R, ihv[mt][i][1], lin_round(acc[mt][i], fl[mt][1]));
                     // new gate and the state update
                     if (!waited) {
                         ok = tc::mbar_wait(&mma_done[2], par, WAIT_BUDGET);
@@ -370,9 +368,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                         for (int i = 0; i < CH; ++i)
-                            hn[mt][i] = fused_finish_fast(gc, tables, ihv[mt][i][2],
-                                                          linear_epilogue_fast(acc[mt][i], fl[mt][2],
-                                                                               a.lc.zp_out, a.lc.lo, a.lc.hi),
+                            hn[mt][i] = fused_finish_fast(gc, tab, ihv[mt][i][2], lin_round(acc[mt][i], fl[mt][2]),
                                                           zd[mt][i], rd[mt][i], hold[mt][i]);
                 } else {
                     if (!waited) {

@@ -42,13 +42,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// 32-bit load from a shared-memory address (shared window offset): keeps table lookups on the
-// shared-memory path with 32-bit address arithmetic.
-__device__ __forceinline__ int32_t lds_i32(uint32_t addr) {
-    int32_t v;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
 // Bounded wait: gives up after `budget` clock cycles and returns false.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, long long budget) {
     if (mbar_try_wait(bar, parity)) return true;
