@@ -246,11 +246,21 @@ def run_ours(args):
         hbm = peaks.get("hbm_gbs", 6650.0)
         peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
         # dominant kernel: the persistent recurrence kernel of one direction.  Algorithmic bytes
-        # per launch = T * rows * (3H*b_ih read + H*(1 + 4) written: 8-bit state + fp32 output)
+        # per launch = T * rows * (3H*b_ih read + 4H written as fp32 output); the 8-bit state adds
+        # H per token only where it is exchanged through global memory (not in the cluster kernel)
         w = wins[0]
         rec_ms = w["recurrence_ms"] / max(1, w["calls"])
         gemm_ms = w["input_gemm_ms"] / max(1, w["calls"])
-        rec_bytes = T * rows * (3 * H * ih_bytes + H * 5)
+        cluster = "exchange=cluster_dsmem" in plan
+        kernel = ("k_recurrence_cluster" if cluster else "k_recurrence_mma") if "rec=tcgen05" in plan \
+            else ("k_recurrence_dp4a" if "path=int8" in plan else "k_linear_generic+k_gates_generic")
+        rec_bytes = T * rows * (3 * H * ih_bytes + H * (4 if cluster else 5))
+        # DRAM traffic of one launch from the ncu capture of this kernel on this workload
+        # (dram__bytes_read.sum + dram__bytes_write.sum = 234.8 MB for 51200 tokens of cfg2),
+        # scaled by the tokens of a launch; other kernels / workloads were not captured
+        traffic = None
+        if args.workload == "cfg2" and kernel == "k_recurrence_cluster" and ih_bytes == 2:
+            traffic = 234.8e6 * (T * rows) / 51200.0
         achieved = rec_bytes / (rec_ms * 1e-3) / 1e9 if rec_ms > 0 else 0.0
         result = {
             "metric": "int-quant GRU fwd tokens/s (batch x seq)", "value": value, "unit": "tokens/s",
@@ -264,9 +274,9 @@ def run_ours(args):
                        "l2": "inputs larger than L2: x, W*x+bw and the fp32 outputs of one step "
                              f"total {(rows * T * bytes_per_token(I, H, ih_bytes) * len(handles)) / 1e6:.0f} MB > 126 MB",
                        "plan": plan},
-            "roofline": {"bound": "hbm", "kernel": ("k_recurrence_mma" if "rec=tcgen05" in plan else "k_recurrence_dp4a") + " (one direction)", "achieved": achieved,
+            "roofline": {"bound": "hbm", "kernel": kernel + " (one direction)", "achieved": achieved,
                          "peak": hbm, "unit": "GB/s", "frac": achieved / hbm, "peak_kind": peak_kind,
-                         "traffic": None, "us_per_timestep": rec_ms * 1e3 / T,
+                         "traffic": traffic, "us_per_timestep": rec_ms * 1e3 / T,
                          "input_gemm_ms": gemm_ms, "recurrence_ms": rec_ms,
                          "whole_forward_frac": (tokens_step / world * bytes_per_token(I, H, ih_bytes) * len(handles) /
                                                 ((ms_total / args.steps) * 1e-3) / 1e9) / hbm},
