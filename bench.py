@@ -40,6 +40,9 @@ WORKLOADS = {
     "cfg4": (1024, 1024, 64, 1000, False, "sym8_tensor", "normal", 4),
     "cfg5": (80, 256, 1, 16000, False, "cfg5", "ar1", 4),
 }
+# calibration method of each workload as BASELINE.json names it: (method, percentile)
+CALIBRATION = {"cfg1": ("minmax", 0.0), "cfg2": ("minmax", 0.0), "cfg3": ("percentile", 99.9),
+               "cfg4": ("sqnr", 0.0), "cfg5": ("minmax", 0.0)}
 
 
 def parse():
@@ -155,7 +158,9 @@ def run_ours(args):
     weights = build_problem(WORKLOADS[args.workload], 1000 + int(args.workload[3:]) * 10)
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
 
-    # --- calibration (MinMax over n_calib seeded batches of the unit shape), per direction
+    # --- calibration over n_calib seeded batches of the unit shape, per direction: MinMax ranges
+    # or 2048-bin histograms (Percentile / SQNR), as the workload's configuration says
+    method, pct = CALIBRATION[args.workload]
     handles = []
     for d in me.directions:
         hd = gru_ops.Handle(I, H, device=local)
@@ -163,11 +168,20 @@ def run_ours(args):
             hd.set_option("sm_limit", sms // 2)
         W, R, bw, br = [torch.from_numpy(a).to(dev) for a in weights[d]]
         ranges = params_mod.Ranges(H)
+        hist = params_mod.Histograms(H, device=local) if method != "minmax" else None
         for k in range(n_calib):
             xc = torch.from_numpy(gen_x(np.random.default_rng(100 * int(args.workload[3:]) + k), T,
                                         B_unit, I, xdist)).to(dev)
-            hd.calibrate_minmax(W, R, bw, br, xc.flip(0).contiguous() if d == 1 else xc, ranges)
-        qp = params_mod.GRUQuantParams.from_ranges(ranges, cfg)
+            xc = xc.flip(0).contiguous() if d == 1 else xc
+            if hist is None:
+                hd.calibrate_minmax(W, R, bw, br, xc, ranges)
+            else:
+                hd.calibrate_hist(W, R, bw, br, xc, hist, cfg.granularity_list())
+        if hist is None:
+            qp = params_mod.GRUQuantParams.from_ranges(ranges, cfg)
+        else:
+            qp = params_mod.GRUQuantParams.from_histograms(hist, cfg, method == "percentile", pct)
+            hist.close()
         hd.set_params(qp)
         hd.set_weights_f32(W, R, bw, br)
         handles.append((hd, d == 1, torch.cuda.Stream(device=dev)))
@@ -269,7 +283,8 @@ def run_ours(args):
             "vs_baseline": None, "dtype": "int8 (int32 accumulate, 64-bit requantize)",
             "data": "synthetic",
             "config": {"workload": f"{args.workload}: {'bi' if bidir else 'uni'}directional GRU I={I} H={H} "
-                                   f"global_batch={B_global} T={T}, bit widths '{cfg_name}', MinMax x{n_calib}",
+                                   f"global_batch={B_global} T={T}, bit widths '{cfg_name}', "
+                                   f"{method}{' %g' % pct if method == 'percentile' else ''} calibration x{n_calib}",
                        "per_gpu": f"directions={list(me.directions)} rows={rows}",
                        "l2": "inputs larger than L2: x, W*x+bw and the fp32 outputs of one step "
                              f"total {(rows * T * bytes_per_token(I, H, ih_bytes) * len(handles)) / 1e6:.0f} MB > 126 MB",

@@ -291,6 +291,61 @@ QGRU_API int qgru_calibrate_minmax(qgru_handle *h, int T, int B, const float *W,
                                    const float *x, const float *h0, qgru_ranges *ranges,
                                    float *h_out, void *stream);
 
+/* ---- histogram calibration (Percentile / SQNR) ----
+ * A qgru_hist holds one 2048-bin (or fewer) histogram with range growth per operator, as
+ * GRUGPUHistogramCollectors does (include/histogram_gpu.cuh; collectors of
+ * src/calibration_gpu.cu:820-1039).  Index space:
+ *   QGRU_OP_* ids           the 13 activation operators; QGRU_OP_W/R/BW/BR: per-tensor weights
+ *   QGRU_HIST_GATE0 + 3*k+g per-gate weight histograms (k: 0 W, 1 R, 2 bw, 3 br; g: z, r, n)
+ *   QGRU_HIST_CHANNEL0 + k*3H + c   per-channel weight histograms
+ * Counts live on the device; ranges and totals on the host. */
+typedef struct qgru_hist qgru_hist;
+#define QGRU_HIST_GATE0 17
+#define QGRU_HIST_CHANNEL0 29
+
+QGRU_API int qgru_hist_create(qgru_hist **out, int device, int hidden_size, int num_bins);
+QGRU_API void qgru_hist_destroy(qgru_hist *hs);
+QGRU_API int qgru_hist_reset(qgru_hist *hs);
+QGRU_API int qgru_hist_count(const qgru_hist *hs);
+QGRU_API const char *qgru_hist_last_error(const qgru_hist *hs);
+
+/* GPUHistogramCollector::collect (src/calibration_gpu.cu:820-876) for one collector: fold n
+ * device floats into histogram `index` (first call fixes the range, later calls grow it and
+ * redistribute the old counts).  Synchronous. */
+QGRU_API int qgru_hist_collect(qgru_hist *hs, int index, const float *data, long long n,
+                               void *stream);
+
+/* Copy one histogram out (counts: host array of num_bins floats, may be NULL) or in. */
+QGRU_API int qgru_hist_export(const qgru_hist *hs, int index, float *counts, float *min_val,
+                              float *max_val, int64_t *total_count);
+QGRU_API int qgru_hist_import(qgru_hist *hs, int index, const float *counts, float min_val,
+                              float max_val, int64_t total_count);
+
+/* forwardWithCalibrationGPU, histogram branch (src/gru_interface.cc:1283-1372 with
+ * collectAllHistogramsGPU, src/histogram_calibration_utils.cu:18-123): float forward of one
+ * batch, then every operator's values are folded into `hs`.  granularity[4]: QGRU_PER_* of
+ * W, R, bw, br (per-channel weight histograms are built once).  Synchronous. */
+QGRU_API int qgru_calibrate_hist(qgru_handle *h, qgru_hist *hs, int T, int B, const float *W,
+                                 const float *R, const float *bw, const float *br,
+                                 const float *x, const float *h0, const int32_t *granularity,
+                                 void *stream);
+
+/* calculateGRUQuantitativeParametersFromHistograms (src/gru_interface.cc:1079-1153):
+ * histograms + bit-width config (fields of `p` as for qgru_calc_params_from_ranges) ->
+ * scales, zero points and LUTs, by Percentile (use_percentile != 0; percentile e.g. 99.99)
+ * or by the SQNR search (calibrateSqnr, include/pot_sqnr_calibrator.h:246-381). */
+QGRU_API int qgru_calc_params_from_hist(const qgru_hist *hs, int use_percentile, float percentile,
+                                        qgru_params *p, float *scale_W, float *scale_R,
+                                        float *scale_bw, float *scale_br);
+
+/* The same derivation for one histogram given as host arrays (pure host function):
+ * calibrateContinuousScaleFromHistogram + encodeScaleResult
+ * (include/pot_sqnr_calibrator.h:526-544, 451-524).  In: op->bits / is_unsigned / symmetric;
+ * out: op->scale, op->zero_point. */
+QGRU_API int qgru_calibrate_from_histogram(const float *counts, int num_bins, float min_val,
+                                           float max_val, int64_t total_count, int use_pot2,
+                                           int use_percentile, float percentile, qgru_op *op);
+
 /* Initialise a qgru_ranges to "empty" (min=+FLT_MAX, max=-FLT_MAX), as
  * GRUQuantizationRanges::reset does (include/gru_quantization_ranges.h:75-123). */
 QGRU_API void qgru_ranges_reset(qgru_ranges *r, int hidden);

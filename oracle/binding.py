@@ -115,6 +115,22 @@ class _Checker:
             raise RuntimeError("dequantize failed")
         return out
 
+    def calibrate_from_histogram(self, counts, min_val, max_val, total, op, pot2, use_percentile,
+                                 percentile=99.99):
+        """One histogram -> (scale, zero_point) for the operator described by `op` (bits,
+        is_unsigned, symmetric); None where the checker reports a failure."""
+        counts = np.ascontiguousarray(counts, np.float32)
+        o = self.cabi.Op(0.0, 0, op.bits, op.is_unsigned, op.symmetric, 0)
+        rc = self._fn("calibrate_from_histogram")(
+            _f(counts), int(counts.size), C.c_float(min_val), C.c_float(max_val), C.c_int64(int(total)),
+            int(bool(pot2)), int(bool(use_percentile)), C.c_float(percentile), C.byref(o))
+        return None if rc else (float(np.float32(o.scale)), int(o.zero_point))
+
+    def hist_new(self, bins=2048):
+        f = self._fn("hist_new")
+        f.restype = C.c_void_p
+        return _Hist(self, C.c_void_p(f(int(bins))), bins)
+
     def forward_i32(self, T, B, I, H, wq, x_q, h0_q, params, sc, threads=1):
         x_q = np.ascontiguousarray(x_q, np.int32)
         h = np.zeros((T + 1, B, H), np.int32)
@@ -138,6 +154,34 @@ class _Checker:
         if rc:
             raise RuntimeError("forward_f32 failed")
         return h
+
+
+class _Hist:
+    """One histogram collector of a checker (oracle: the GPU collector's rules on the CPU;
+    reference: its CPU HistogramCollector)."""
+
+    def __init__(self, chk, handle, bins):
+        self.chk, self.h, self.bins = chk, handle, bins
+
+    def collect(self, data):
+        data = np.ascontiguousarray(data, np.float32).ravel()
+        rc = self.chk._fn("hist_collect")(self.h, _f(data), C.c_size_t(data.size))
+        if rc:
+            raise RuntimeError("hist_collect failed")
+
+    def get(self):
+        counts = np.zeros(self.bins, np.float32)
+        mn, mx, tot = C.c_float(), C.c_float(), C.c_int64()
+        self.chk._fn("hist_get")(self.h, _f(counts), C.byref(mn), C.byref(mx), C.byref(tot))
+        return counts, float(mn.value), float(mx.value), int(tot.value)
+
+    def __del__(self):
+        try:
+            f = self.chk._fn("hist_free")
+            f.argtypes = [C.c_void_p]
+            f(self.h)
+        except Exception:
+            pass
 
 
 class Oracle(_Checker):

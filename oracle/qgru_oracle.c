@@ -834,3 +834,294 @@ ORC_API int orc_forward_float(int T, int B, int I, int H, const float *W, const 
     free(acc);
     return 0;
 }
+
+/* ------------------------------------------------------- histogram calibration */
+
+/* Histogram::bin_width, include/histogram_collector.h:76-79. */
+static float hist_bw(float mn, float mx, int bins) {
+    if (bins <= 0 || mx <= mn) return 1.0f;
+    return (mx - mn) / bins;
+}
+
+/* Histogram::getPercentileRange, include/histogram_collector.h:105-165: cumulative sum in
+ * single precision, first bins whose cumulative count reaches total*clip and total*(1-clip),
+ * left bin edges. */
+static void percentile_range(const float *counts, int bins, float mn, float mx, int64_t total,
+                             float clip, float *pmin, float *pmax) {
+    *pmin = mn;
+    *pmax = mx;
+    if (bins <= 0 || total <= 0 || clip <= 0.0f) return;
+    float *cum = (float *)malloc(sizeof(float) * (size_t)bins);
+    cum[0] = counts[0];
+    for (int i = 1; i < bins; ++i) cum[i] = cum[i - 1] + counts[i];
+    const float sum = cum[bins - 1];
+    if (sum >= 1e-6f) {
+        const float bw = hist_bw(mn, mx, bins);
+        const float keep = 1.0f - clip;
+        const float t_lo = sum * clip, t_hi = sum * keep;
+        int i_lo = 0, i_hi = bins - 1;
+        for (int i = 0; i < bins; ++i) if (cum[i] >= t_lo) { i_lo = i; break; }
+        for (int i = 0; i < bins; ++i) if (cum[i] >= t_hi) { i_hi = i; break; }
+        float a = mn + i_lo * bw, b = mn + i_hi * bw;
+        if (b <= a) b = mx;
+        *pmin = a;
+        *pmax = b;
+    }
+    free(cum);
+}
+
+/* calibratePercentile, include/pot_sqnr_calibrator.h:99-186. */
+static void continuous_percentile(const float *counts, int bins, float mn, float mx, int64_t total,
+                                  int64_t steps, int sym, int uns, float percentile,
+                                  float *scale_out, float *min_out) {
+    const float ms = minimum_scale(steps);
+    const float clip = (100.0f - percentile) / 100.0f;
+    float pmin, pmax;
+    percentile_range(counts, bins, mn, mx, total, clip, &pmin, &pmax);
+    pmin = fminf(pmin, 0.0f);
+    pmax = fmaxf(pmax, 0.0f);
+    pmin = fmaxf(-FLT_MAX, fminf(pmin, 0.0f));
+    pmax = fminf(FLT_MAX, fmaxf(pmax, 0.0f));
+    if ((pmax - pmin) / (float)steps < ms) {
+        if (sym && !uns) {
+            pmin -= ms * (float)((steps + 1) / 2);
+            pmax += ms * (float)(steps / 2);
+        } else {
+            pmax += ms * (float)steps;
+        }
+    }
+    float scale, rmin;
+    if (sym && uns) {
+        const float dmax = fmaxf(pmax, ms);
+        scale = fmaxf(dmax / (float)steps, ms);
+        rmin = 0.0f;
+    } else if (sym) {
+        const int64_t pos = steps / 2, neg = (steps + 1) / 2;
+        const float d_max = pos > 0 ? pmax / (float)pos : FLT_MAX;
+        const float d_min = neg > 0 ? -pmin / (float)neg : FLT_MAX;
+        scale = fmaxf(d_max, d_min);
+        rmin = -(float)neg * scale;
+    } else {
+        scale = (pmax - pmin) / (float)steps;
+        rmin = pmin;
+    }
+    *scale_out = fmaxf(scale, ms);
+    *min_out = rmin;
+}
+
+/* sqnr_detail::estimateNoise, include/pot_sqnr_calibrator.h:210-238, gamma 3, p 2. */
+static float sqnr_noise(const float *counts, int bins, float hmin, float bw, float delta,
+                        float offset, int64_t steps) {
+    if (delta <= 0) return FLT_MAX;
+    float total = 0.0f;
+    for (int i = 0; i < bins; ++i) {
+        const float cnt = counts[i];
+        if (cnt < 1e-6f) continue;
+        const float x = hmin + (i + 0.5f) * bw;
+        float q = rintf(x / delta - offset);
+        const int clipped = (q < 0) || (q > (float)steps);
+        q = fmaxf(0.0f, fminf((float)steps, q));
+        const float xr = (q + offset) * delta;
+        float err = powf(fabsf(xr - x), 2.0f);
+        if (clipped) err *= 3.0f;
+        total += err * cnt;
+    }
+    return total;
+}
+
+/* calibrateSqnr / searchSymmetric / searchAsymmetric, include/pot_sqnr_calibrator.h:246-381. */
+static int continuous_sqnr(const float *counts, int bins, float hmin, float hmax, int64_t steps,
+                           int sym, int uns, float *scale_out, float *min_out) {
+    const float ms = minimum_scale(steps);
+    const float bw = hist_bw(hmin, hmax, bins);
+    const float vmin = fminf(hmin, 0.0f);
+    float vmax = fmaxf(hmax, 0.0f);
+    const float lim = vmin + ms * (float)steps;
+    vmax = (vmax > lim) ? vmax : lim;
+    float best = FLT_MAX, best_scale = 0.0f, best_min = 0.0f;
+    if (sym) {
+        float max_delta, offset;
+        if (uns) { max_delta = vmax / (float)steps; offset = 0.0f; }
+        else { max_delta = 2.0f * fmaxf(vmax, -vmin) / (float)steps; offset = -(float)((steps + 1) / 2); }
+        max_delta = fmaxf(max_delta, ms);
+        for (int d = 1; d <= 101; ++d) {
+            float delta = max_delta * d / 100;
+            delta = fmaxf(delta, ms);
+            const float noise = sqnr_noise(counts, bins, hmin, bw, delta, offset, steps);
+            if (noise < best) { best = noise; best_scale = delta; best_min = offset * delta; }
+        }
+    } else {
+        const float max_delta = (vmax - vmin) / (float)steps;
+        const float o_obs = rintf(vmin / max_delta);
+        const float obs_min = max_delta * o_obs;
+        const float obs_max = obs_min + max_delta * (float)steps;
+        int n_off = (int)(steps + 2);
+        if (n_off > 21) n_off = 21;
+        float offs[21];
+        const float step = (float)steps / (n_off - 2);
+        for (int o = 0; o < n_off - 1; ++o) offs[o] = rintf(-(float)steps + o * step);
+        offs[n_off - 1] = o_obs;
+        for (int d = 1; d <= 17; ++d) {
+            float delta = max_delta * d / 16;
+            delta = fmaxf(delta, ms);
+            for (int o = 0; o < n_off; ++o) {
+                float tmin = delta * offs[o];
+                float tmax = tmin + delta * (float)steps;
+                tmin = fmaxf(obs_min, tmin);
+                tmax = fminf(obs_max, tmax);
+                float cd = (tmax - tmin) / (float)steps;
+                cd = fmaxf(cd, ms);
+                const float co = rintf(tmin / cd);
+                const float noise = sqnr_noise(counts, bins, hmin, bw, cd, co, steps);
+                if (noise < best) { best = noise; best_scale = cd; best_min = co * cd; }
+            }
+        }
+    }
+    if (best == FLT_MAX) return 1;
+    *scale_out = best_scale;
+    *min_out = best_min;
+    return 0;
+}
+
+/* histCalibrate of calculateGRUQuantitativeParametersFromHistograms, src/gru_interface.cc:
+ * 1092-1100: continuous scale from the histogram, then encodeScaleResult(coverage_round =
+ * false) and storedScaleForMode. */
+ORC_API int orc_calibrate_from_histogram(const float *counts, int bins, float min_val, float max_val,
+                                         int64_t total, int use_pot2, int use_percentile,
+                                         float percentile, qgru_op *op) {
+    if (bins <= 0 || total <= 0) return 1;
+    const int uns = eff_unsigned(op);
+    const int64_t steps = (int64_t)qmax_of(op->bits, uns) - (int64_t)qmin_of(op->bits, uns);
+    if (steps <= 0) return 1;
+    float cs, cmin;
+    if (use_percentile)
+        continuous_percentile(counts, bins, min_val, max_val, total, steps, op->symmetric, uns, percentile, &cs, &cmin);
+    else if (continuous_sqnr(counts, bins, min_val, max_val, steps, op->symmetric, uns, &cs, &cmin))
+        return 1;
+    return encode_scale(cs, cmin, op, op->symmetric, use_pot2, 0, &op->scale, &op->zero_point);
+}
+
+/* One histogram collector with the rules of GPUHistogramCollector::collect
+ * (src/calibration_gpu.cu:820-876) and the arithmetic of its kernels (histogram_kernel_shared
+ * :66-104, redistribute_histogram_kernel :116-158, build_histogram :499-522,
+ * redistribute_histogram :524-540), evaluated one operation at a time. */
+typedef struct orc_hist {
+    int bins;
+    float *counts;
+    float min_val, max_val;
+    int64_t total;
+    int valid;
+    float limit_min, limit_max;
+} orc_hist;
+
+ORC_API orc_hist *orc_hist_new(int bins) {
+    orc_hist *h = (orc_hist *)calloc(1, sizeof(orc_hist));
+    h->bins = bins;
+    h->counts = (float *)calloc((size_t)bins, sizeof(float));
+    h->min_val = FLT_MAX;
+    h->max_val = -FLT_MAX;
+    return h;
+}
+ORC_API void orc_hist_free(orc_hist *h) {
+    if (!h) return;
+    free(h->counts);
+    free(h);
+}
+
+static void hist_add(float *counts, int bins, const float *data, size_t n, float mn, float mx) {
+    float bw = (mx - mn) / bins;
+    if (bw < 1e-9f) bw = 1e-9f;
+    const float inv = 1.0f / bw;
+    for (size_t i = 0; i < n; ++i) {
+        const float v = data[i];
+        if (!isfinite(v)) continue;
+        int b;
+        if (v < mn) b = 0;
+        else if (v > mx) b = bins - 1;
+        else {
+            b = (int)((v - mn) * inv);
+            if (b > bins - 1) b = bins - 1;
+        }
+        counts[b] += 1.0f;
+    }
+}
+
+static void hist_redistribute(const float *src, float smin, float sbw, float *dst, float dmin,
+                              float dbw, int bins) {
+    const float inv = 1.0f / dbw;
+    for (int i = 0; i < bins; ++i) {
+        const float cnt = src[i];
+        if (cnt <= 0) continue;
+        const float start = smin + (float)i * sbw;
+        int d = (int)((start - dmin) * inv);
+        if (d > bins - 1) d = bins - 1;
+        const float end = dmin + dbw * (float)(d + 1);
+        const float split = rintf(((end - start) / sbw) * cnt);
+        const float first = fminf(split, cnt);
+        dst[d] += first;
+        const float rest = cnt - first;
+        if (rest > 0) {
+            int o = (int)((start + dbw - dmin) * inv);
+            if (o > bins - 1) o = bins - 1;
+            dst[o] += rest;
+        }
+    }
+}
+
+ORC_API int orc_hist_collect(orc_hist *h, const float *data, size_t n) {
+    if (n == 0) return 0;
+    float dmin = FLT_MAX, dmax = -FLT_MAX;
+    for (size_t i = 0; i < n; ++i)
+        if (isfinite(data[i])) { dmin = fminf(dmin, data[i]); dmax = fmaxf(dmax, data[i]); }
+    if (dmin > dmax) dmin = dmax = 0.0f;
+    if (dmin == dmax) { dmin -= 0.5f; dmax += 0.5f; }
+    const float eps = 1.19209290e-07f, v = 0.01f / (float)h->bins;
+    const float tiny_range = (eps < v ? eps : v) * h->bins;
+    float range = dmax - dmin;
+    if (range < tiny_range || isnan(range) || isinf(range)) {
+        dmin = fminf(dmin, 0.0f);
+        dmax = fmaxf(dmax, 0.0f);
+        range = tiny_range;
+        dmax = dmin + tiny_range;
+    }
+    if (!h->valid) {
+        memset(h->counts, 0, sizeof(float) * (size_t)h->bins);
+        h->min_val = dmin;
+        h->max_val = dmax;
+        hist_add(h->counts, h->bins, data, n, dmin, dmax);
+        h->total = (int64_t)n;
+        h->valid = 1;
+        h->limit_min = dmin - range * INFINITY / 2.0f;
+        h->limit_max = dmax + range * INFINITY / 2.0f;
+        return 0;
+    }
+    const float nmin = fmaxf(h->limit_min, fminf(dmin, h->min_val));
+    const float nmax = fminf(h->limit_max, fmaxf(dmax, h->max_val));
+    if (nmin == h->min_val && nmax == h->max_val) {
+        hist_add(h->counts, h->bins, data, n, h->min_val, h->max_val);
+    } else {
+        float *fresh = (float *)calloc((size_t)h->bins, sizeof(float));
+        const float sbw_check = hist_bw(h->min_val, h->max_val, h->bins);
+        if (fabsf(sbw_check) >= (eps < v ? eps : v) && !isnan(sbw_check) && !isinf(sbw_check)) {
+            const float sbw = (h->max_val - h->min_val) / h->bins;
+            float dbw = (nmax - nmin) / h->bins;
+            if (dbw < 1e-9f) dbw = 1e-9f;
+            hist_redistribute(h->counts, h->min_val, sbw, fresh, nmin, dbw, h->bins);
+        }
+        hist_add(fresh, h->bins, data, n, nmin, nmax);
+        free(h->counts);
+        h->counts = fresh;
+        h->min_val = nmin;
+        h->max_val = nmax;
+    }
+    h->total += (int64_t)n;
+    return 0;
+}
+
+ORC_API int orc_hist_get(const orc_hist *h, float *counts, float *min_val, float *max_val, int64_t *total) {
+    if (counts) memcpy(counts, h->counts, sizeof(float) * (size_t)h->bins);
+    *min_val = h->min_val;
+    *max_val = h->max_val;
+    *total = h->valid ? h->total : 0;
+    return 0;
+}

@@ -347,4 +347,44 @@ int ref_forward_f32(int T, int B, int I, int H, const int32_t *W, const int32_t 
     });
 }
 
+
+// ---- histogram calibration: the reference's host code (header-only), run as it is
+
+// calibrateContinuousScaleFromHistogram + encodeScaleResult + storedScaleForMode
+// (include/pot_sqnr_calibrator.h), the body of histCalibrate in
+// calculateGRUQuantitativeParametersFromHistograms (src/gru_interface.cc:1092-1100).
+int ref_calibrate_from_histogram(const float *counts, int bins, float min_val, float max_val,
+                                 int64_t total, int use_pot2, int use_percentile, float percentile,
+                                 qgru_op *op) {
+    return guarded([&] {
+        Histogram h(bins);
+        h.counts.assign(counts, counts + bins);
+        h.min_val = min_val;
+        h.max_val = max_val;
+        h.total_count = total;
+        const QuantBitWidth bw = bwOf(*op);
+        const bool sym = op->symmetric != 0;
+        ContinuousScaleResult c = calibrateContinuousScaleFromHistogram(h, bw, sym, use_percentile != 0, percentile);
+        EncodedScaleResult e = encodeScaleResult(c.scale, c.min, bw, sym, use_pot2 != 0);
+        op->scale = storedScaleForMode(e, use_pot2 != 0);
+        op->zero_point = e.zero_point;
+    });
+}
+
+// the reference's CPU HistogramCollector (include/histogram_collector.h), one object per handle
+void *ref_hist_new(int bins) { return new HistogramCollector(bins); }
+void ref_hist_free(void *h) { delete static_cast<HistogramCollector *>(h); }
+int ref_hist_collect(void *h, const float *data, size_t n) {
+    return guarded([&] { static_cast<HistogramCollector *>(h)->collect(data, n); });
+}
+int ref_hist_get(void *h, float *counts, float *min_val, float *max_val, int64_t *total) {
+    return guarded([&] {
+        const Histogram &g = static_cast<HistogramCollector *>(h)->histogram();
+        if (counts) std::memcpy(counts, g.counts.data(), sizeof(float) * g.counts.size());
+        *min_val = g.min_val;
+        *max_val = g.max_val;
+        *total = g.total_count;
+    });
+}
+
 }  // extern "C"

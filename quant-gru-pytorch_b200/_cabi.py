@@ -83,7 +83,22 @@ SYMBOLS = {
     "qgru_calibrate_minmax": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, _P, _P, _P,
                                         C.POINTER(Ranges), _P, _P]),
     "qgru_ranges_reset": (None, [C.POINTER(Ranges), C.c_int]),
+    "qgru_hist_create": (C.c_int, [C.POINTER(_P), C.c_int, C.c_int, C.c_int]),
+    "qgru_hist_destroy": (None, [_P]),
+    "qgru_hist_reset": (C.c_int, [_P]),
+    "qgru_hist_count": (C.c_int, [_P]),
+    "qgru_hist_last_error": (C.c_char_p, [_P]),
+    "qgru_hist_collect": (C.c_int, [_P, C.c_int, _P, C.c_longlong, _P]),
+    "qgru_hist_export": (C.c_int, [_P, C.c_int, _F, _F, _F, C.POINTER(C.c_int64)]),
+    "qgru_hist_import": (C.c_int, [_P, C.c_int, _F, C.c_float, C.c_float, C.c_int64]),
+    "qgru_calibrate_hist": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, _P, _P, _P, _P,
+                                      C.POINTER(C.c_int32), _P]),
+    "qgru_calc_params_from_hist": (C.c_int, [_P, C.c_int, C.c_float, C.POINTER(Params), _F, _F, _F, _F]),
+    "qgru_calibrate_from_histogram": (C.c_int, [_F, C.c_int, C.c_float, C.c_float, C.c_int64, C.c_int,
+                                                C.c_int, C.c_float, C.POINTER(Op)]),
 }
+HIST_GATE0 = 17
+HIST_CHANNEL0 = 29
 
 _lib = None
 

@@ -101,7 +101,7 @@ template <bool Calib>
 __global__ void __launch_bounds__(256)
 k_float_step(const float *__restrict__ wx, const float *__restrict__ R, const float *__restrict__ bw,
              const float *__restrict__ br, const float *__restrict__ h_in, float *__restrict__ h_out,
-             float *__restrict__ v, int B, int H, unsigned *acc_min, unsigned *acc_max) {
+             float *__restrict__ v, int v_stride, int B, int H, unsigned *acc_min, unsigned *acc_max) {
     extern __shared__ float hs[];  // [2][H]
     const int j = blockIdx.x * 128 + threadIdx.x;
     const int b = blockIdx.y * 2 + threadIdx.y;
@@ -144,8 +144,12 @@ k_float_step(const float *__restrict__ wx, const float *__restrict__ R, const fl
         const float hn = old_c + new_c;
         h_out[(size_t)b * H + j] = hn;
         if (v) {
-            float *vb = v + (size_t)b * 4 * H + j;
-            vb[0] = z; vb[H] = r; vb[2 * H] = g; vb[3 * H] = rg;
+            // 4 slots per row: the reference's training buffer (z, r, n, Rh_n + br_n); 6 slots:
+            // all three R*h + br rows as well (z, r, n, Rh_z+br_z, Rh_r+br_r, Rh_n+br_n)
+            float *vb = v + (size_t)b * v_stride * H + j;
+            vb[0] = z; vb[H] = r; vb[2 * H] = g;
+            if (v_stride == 6) { vb[3 * H] = rz; vb[4 * H] = rr_; vb[5 * H] = rg; }
+            else vb[3 * H] = rg;
         }
         if (Calib) {
             m_h.add(hn);
@@ -210,9 +214,13 @@ __global__ void k_init_h_float(const float *__restrict__ h0, float *__restrict__
     if (i < n) h[i] = h0 ? h0[i] : 0.f;
 }
 
+}  // namespace
+
+namespace qgru {
+
 int float_forward(qgru_handle *h, int T, int B, const float *W, const float *R, const float *bw,
                   const float *br, const float *x, const float *h0, float *h_out, float *v_out,
-                  unsigned *acc_min, unsigned *acc_max, cudaStream_t st) {
+                  int v_stride, unsigned *acc_min, unsigned *acc_max, cudaStream_t st) {
     const int H = h->H, Cn = h->C, I = h->I;
     const long long N = (long long)T * B;
     int rc;
@@ -232,18 +240,18 @@ int float_forward(qgru_handle *h, int T, int B, const float *W, const float *R, 
     for (int t = 0; t < T; ++t) {
         const float *hin = h_out + (size_t)t * NH;
         float *hout = h_out + (size_t)(t + 1) * NH;
-        float *vt = v_out ? v_out + (size_t)t * B * 4 * H : nullptr;
+        float *vt = v_out ? v_out + (size_t)t * B * v_stride * H : nullptr;
         if (acc_min)
-            k_float_step<true><<<grid, blk, smem, st>>>(wx + (size_t)t * B * Cn, R, bw, br, hin, hout, vt, B, H, acc_min, acc_max);
+            k_float_step<true><<<grid, blk, smem, st>>>(wx + (size_t)t * B * Cn, R, bw, br, hin, hout, vt, v_stride, B, H, acc_min, acc_max);
         else
-            k_float_step<false><<<grid, blk, smem, st>>>(wx + (size_t)t * B * Cn, R, bw, br, hin, hout, vt, B, H, nullptr, nullptr);
+            k_float_step<false><<<grid, blk, smem, st>>>(wx + (size_t)t * B * Cn, R, bw, br, hin, hout, vt, v_stride, B, H, nullptr, nullptr);
         h->launches++;
     }
     CK(cudaGetLastError());
     return QGRU_OK;
 }
 
-}  // namespace
+}  // namespace qgru
 
 extern "C" {
 
@@ -253,7 +261,7 @@ int qgru_forward_float(qgru_handle *h, int T, int B, const float *W, const float
     if (!h || !W || !R || !bw || !br || !x || !h_out) return QGRU_ERR_BAD_ARG;
     if (T <= 0 || B <= 0) return fail(h, QGRU_ERR_BAD_ARG, "T and B must be positive");
     CK(cudaSetDevice(h->device));
-    return float_forward(h, T, B, W, R, bw, br, x, h0, h_out, v_out, nullptr, nullptr, (cudaStream_t)stream);
+    return float_forward(h, T, B, W, R, bw, br, x, h0, h_out, v_out, 4, nullptr, nullptr, (cudaStream_t)stream);
 }
 
 int qgru_calibrate_minmax(qgru_handle *h, int T, int B, const float *W, const float *R,
@@ -289,7 +297,7 @@ int qgru_calibrate_minmax(qgru_handle *h, int T, int B, const float *W, const fl
     for (int k = 0; k < 4; ++k)
         k_minmax_channels<<<(Cn + 127) / 128, 128, 0, st>>>(mats[k], rows[k], Cn, ch + (2 * k) * Cn, ch + (2 * k + 1) * Cn);
     h->launches += 7;
-    if ((rc = float_forward(h, T, B, W, R, bw, br, x, h0, hbuf, nullptr, acc_min, acc_max, st))) return rc;
+    if ((rc = float_forward(h, T, B, W, R, bw, br, x, h0, hbuf, nullptr, 4, acc_min, acc_max, st))) return rc;
     std::vector<unsigned> host(n_acc);
     CK(cudaMemcpyAsync(host.data(), acc, (size_t)n_acc * 4, cudaMemcpyDeviceToHost, st));
     CK(cudaStreamSynchronize(st));

@@ -302,12 +302,241 @@ bool calibrate_channels(qgru_op *op, int gran, bool pot2, int H, const float *mi
     return true;
 }
 
+
+// ------------------------------------------------------------------ histogram calibration
+// Histogram -> continuous scale (Percentile or SQNR) -> stored scale and zero point.  All
+// single precision, operand order as in the reference: these results are compared exactly.
+
+struct ContScale {
+    float scale, min, max;
+};
+
+float hist_bin_width(const float min_val, const float max_val, int bins) {
+    if (bins <= 0 || max_val <= min_val) return 1.0f;   // Histogram::bin_width, include/histogram_collector.h:76-79
+    return (max_val - min_val) / bins;
+}
+
+// Histogram::getPercentileRange, include/histogram_collector.h:105-165.
+void percentile_range(const float *counts, int bins, float min_val, float max_val, long long total,
+                      float clip, float *pmin, float *pmax) {
+    *pmin = min_val;
+    *pmax = max_val;
+    if (bins <= 0 || total <= 0 || clip <= 0.0f) return;
+    std::vector<float> cum(bins);
+    cum[0] = counts[0];
+    for (int i = 1; i < bins; ++i) cum[i] = cum[i - 1] + counts[i];
+    const float sum = cum[bins - 1];
+    if (sum < 1e-6f) return;
+    const float bw = hist_bin_width(min_val, max_val, bins);
+    const float keep = 1.0f - clip;
+    const float lo_thr = sum * clip, hi_thr = sum * keep;
+    int lo_i = 0, hi_i = bins - 1;
+    for (int i = 0; i < bins; ++i)
+        if (cum[i] >= lo_thr) { lo_i = i; break; }
+    for (int i = 0; i < bins; ++i)
+        if (cum[i] >= hi_thr) { hi_i = i; break; }
+    float a = min_val + lo_i * bw, b = min_val + hi_i * bw;
+    if (b <= a) b = max_val;
+    *pmin = a;
+    *pmax = b;
+}
+
+// calibratePercentile, include/pot_sqnr_calibrator.h:99-186.
+ContScale calibrate_percentile(const float *counts, int bins, float min_val, float max_val, long long total,
+                               int64_t steps, bool sym, bool uns, float percentile) {
+    const float tiny = minimum_scale(steps);
+    const float clip = (100.0f - percentile) / 100.0f;
+    float pmin, pmax;
+    percentile_range(counts, bins, min_val, max_val, total, clip, &pmin, &pmax);
+    pmin = std::min(pmin, 0.0f);
+    pmax = std::max(pmax, 0.0f);
+    pmin = std::max(-FLT_MAX, std::min(pmin, 0.0f));
+    pmax = std::min(FLT_MAX, std::max(pmax, 0.0f));
+    if ((pmax - pmin) / static_cast<float>(steps) < tiny) {
+        if (sym && !uns) {
+            pmin -= tiny * static_cast<float>((steps + 1) / 2);
+            pmax += tiny * static_cast<float>(steps / 2);
+        } else {
+            pmax += tiny * static_cast<float>(steps);
+        }
+    }
+    ContScale r;
+    if (sym && uns) {
+        const float data_max = std::max(pmax, tiny);
+        r.scale = std::max(data_max / static_cast<float>(steps), tiny);
+        r.min = 0.0f;
+        r.max = r.scale * static_cast<float>(steps);
+    } else if (sym) {
+        const int64_t pos = steps / 2, neg = (steps + 1) / 2;
+        const float from_max = pos > 0 ? pmax / static_cast<float>(pos) : FLT_MAX;
+        const float from_min = neg > 0 ? -pmin / static_cast<float>(neg) : FLT_MAX;
+        r.scale = std::max(from_max, from_min);
+        r.min = -static_cast<float>(neg) * r.scale;
+        r.max = static_cast<float>(pos) * r.scale;
+    } else {
+        r.scale = (pmax - pmin) / static_cast<float>(steps);
+        r.min = pmin;
+        r.max = pmax;
+    }
+    r.scale = std::max(r.scale, tiny);
+    return r;
+}
+
+// sqnr_detail::estimateNoise, include/pot_sqnr_calibrator.h:210-238 (gamma = 3, p = 2).
+float sqnr_noise(const float *counts, int bins, float min_val, float bw, float delta, float offset,
+                 int64_t steps) {
+    if (delta <= 0) return FLT_MAX;
+    const float gamma = 3.0f, p = 2.0f;
+    float noise = 0.0f;
+    for (int i = 0; i < bins; ++i) {
+        const float count = counts[i];
+        if (count < 1e-6f) continue;
+        const float x = min_val + (i + 0.5f) * bw;
+        float q = rintf(x / delta - offset);
+        const bool clipped = (q < 0) || (q > static_cast<float>(steps));
+        q = std::max(0.0f, std::min(static_cast<float>(steps), q));
+        const float x_recon = (q + offset) * delta;
+        float err = std::pow(std::abs(x_recon - x), p);
+        if (clipped) err *= gamma;
+        noise += err * count;
+    }
+    return noise;
+}
+
+// calibrateSqnr with searchSymmetric / searchAsymmetric, include/pot_sqnr_calibrator.h:246-381
+// (101 symmetric deltas; 17 deltas x min(steps + 2, 21) offsets otherwise).
+bool calibrate_sqnr(const float *counts, int bins, float hmin, float hmax, int64_t steps, bool sym,
+                    bool uns, ContScale *out) {
+    const float tiny = minimum_scale(steps);
+    const float bw = hist_bin_width(hmin, hmax, bins);
+    const float min_val = std::min(hmin, 0.0f);
+    float max_val = std::max(hmax, 0.0f);
+    const float floor_max = min_val + tiny * static_cast<float>(steps);
+    max_val = (max_val > floor_max) ? max_val : floor_max;
+    float best_noise = FLT_MAX;
+    ContScale best{0, 0, 0};
+    if (sym) {
+        float max_delta, offset;
+        if (uns) {
+            max_delta = max_val / static_cast<float>(steps);
+            offset = 0.0f;
+        } else {
+            max_delta = 2.0f * std::max(max_val, -min_val) / static_cast<float>(steps);
+            offset = -static_cast<float>((steps + 1) / 2);
+        }
+        max_delta = std::max(max_delta, tiny);
+        const int cand = 101, div = cand - 1;
+        for (int d = 1; d <= cand; ++d) {
+            float delta = max_delta * d / div;
+            delta = std::max(delta, tiny);
+            const float noise = sqnr_noise(counts, bins, hmin, bw, delta, offset, steps);
+            if (noise < best_noise) {
+                best_noise = noise;
+                best.scale = delta;
+                best.min = offset * delta;
+                best.max = best.min + steps * delta;
+            }
+        }
+    } else {
+        const float max_delta = (max_val - min_val) / static_cast<float>(steps);
+        const float obs_off = rintf(min_val / max_delta);
+        const float obs_min = max_delta * obs_off;
+        const float obs_max = obs_min + max_delta * static_cast<float>(steps);
+        const int n_off = std::min(static_cast<int>(steps + 2), 21);
+        std::vector<float> offs(n_off);
+        const float step = static_cast<float>(steps) / (n_off - 2);
+        for (int o = 0; o < n_off - 1; ++o) offs[o] = rintf(-static_cast<float>(steps) + o * step);
+        offs[n_off - 1] = obs_off;
+        const int cand = 17;
+        for (int d = 1; d <= cand; ++d) {
+            float delta = max_delta * d / (cand - 1);
+            delta = std::max(delta, tiny);
+            for (int o = 0; o < n_off; ++o) {
+                float t_min = delta * offs[o];
+                float t_max = t_min + delta * static_cast<float>(steps);
+                t_min = std::max(obs_min, t_min);
+                t_max = std::min(obs_max, t_max);
+                float cd = (t_max - t_min) / static_cast<float>(steps);
+                cd = std::max(cd, tiny);
+                const float co = rintf(t_min / cd);
+                const float noise = sqnr_noise(counts, bins, hmin, bw, cd, co, steps);
+                if (noise < best_noise) {
+                    best_noise = noise;
+                    best.scale = cd;
+                    best.min = co * cd;
+                    best.max = best.min + steps * cd;
+                }
+            }
+        }
+    }
+    if (best_noise == FLT_MAX) return false;
+    *out = best;
+    return true;
+}
+
+// encodeScaleResult(coverage_round = false) + storedScaleForMode, include/pot_sqnr_calibrator.h:
+// 72-74, 388-447, 451-524: POT2 rounds the scale to the nearest power of two; otherwise the
+// zero point is computed against the decoded 16-bit-mantissa scale and the continuous scale is
+// what is stored.
+bool encode_histogram_scale(const ContScale &c, bool pot2, qgru_op *op) {
+    const bool sym = op->symmetric != 0;
+    const int32_t qlo = op_qmin(*op);
+    if (!(c.scale > 0.0f)) return false;
+    if (pot2) {
+        const float nf = rintf(-std::log2(c.scale));
+        if (nf < -128.0f || nf > 127.0f) return false;
+        const int8_t n = static_cast<int8_t>(nf);
+        const float po2 = std::pow(2.0f, -static_cast<float>(n));
+        op->zero_point = sym ? 0 : static_cast<int32_t>(rintf(static_cast<float>(qlo) - c.min / po2));
+        op->scale = po2;
+        return true;
+    }
+    Rescale fs;
+    if (!encode_mshift(c.scale, &fs)) return false;
+    const float effective = decode_scale(fs);
+    op->zero_point = sym ? 0 : static_cast<int32_t>(rintf(static_cast<float>(qlo) - c.min / effective));
+    op->scale = c.scale;
+    return true;
+}
+
+// calibrateContinuousScaleFromHistogram + encodeScaleResult for one histogram.
+int calibrate_histogram(const float *counts, int bins, float min_val, float max_val, long long total,
+                        bool pot2, bool use_percentile, float percentile, qgru_op *op) {
+    if (!counts || bins <= 0 || total <= 0) return QGRU_ERR_NOT_READY;   // Histogram::is_valid
+    const bool uns = op->bits < 32 && op->is_unsigned;
+    const bool sym = op->symmetric != 0;
+    const int64_t steps = static_cast<int64_t>(op_qmax(*op)) - static_cast<int64_t>(op_qmin(*op));
+    if (steps <= 0) return QGRU_ERR_BAD_ARG;
+    ContScale c;
+    if (use_percentile) {
+        c = calibrate_percentile(counts, bins, min_val, max_val, total, steps, sym, uns, percentile);
+    } else if (!calibrate_sqnr(counts, bins, min_val, max_val, steps, sym, uns, &c)) {
+        return QGRU_ERR_RANGE;
+    }
+    return encode_histogram_scale(c, pot2, op) ? QGRU_OK : QGRU_ERR_RANGE;
+}
+
 }  // namespace
+}  // namespace qgru
+
+namespace qgru {
+int calibrate_histogram_op(const float *counts, int bins, float min_val, float max_val, long long total,
+                           bool pot2, bool use_percentile, float percentile, qgru_op *op) {
+    return calibrate_histogram(counts, bins, min_val, max_val, total, pot2, use_percentile, percentile, op);
+}
 }  // namespace qgru
 
 using namespace qgru;
 
 extern "C" {
+
+int qgru_calibrate_from_histogram(const float *counts, int num_bins, float min_val, float max_val,
+                                  int64_t total_count, int use_pot2, int use_percentile, float percentile,
+                                  qgru_op *op) {
+    if (!counts || !op || op->bits < 1 || op->bits > 32) return QGRU_ERR_BAD_ARG;
+    return calibrate_histogram(counts, num_bins, min_val, max_val, total_count, use_pot2 != 0,
+                               use_percentile != 0, percentile, op);
+}
 
 const char *qgru_status_string(int status) {
     switch (status) {

@@ -18,6 +18,9 @@ float decode_scale(Rescale r);
 bool make_rescale(float src, float dst, bool pot2, Rescale *out);
 bool make_rescale_product(float a, float b, float dst, bool pot2, Rescale *out);
 bool make_rescale_to_product(float src, float a, float b, bool pot2, Rescale *out);
+// one histogram -> op->scale / op->zero_point by Percentile or SQNR (qgru_host.cc)
+int calibrate_histogram_op(const float *counts, int bins, float min_val, float max_val, long long total,
+                           bool pot2, bool use_percentile, float percentile, qgru_op *op);
 int32_t op_qmin(const qgru_op &o);
 int32_t op_qmax(const qgru_op &o);
 int32_t lut_eval(const qgru_lut &lut, int32_t q_x, const qgru_op &in_bw, const qgru_op &out_bw);

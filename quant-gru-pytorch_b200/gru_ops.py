@@ -12,7 +12,7 @@ import ctypes as C
 import torch
 
 from . import _cabi
-from .params import GRUQuantParams, OperatorQuantConfig, Ranges, WEIGHT_OPS  # noqa: F401
+from .params import Histograms, GRUQuantParams, OperatorQuantConfig, Ranges, WEIGHT_OPS  # noqa: F401
 
 
 def _ptr(t):
@@ -215,6 +215,19 @@ class Handle:
         ranges.load(rs)
         return h
 
+    def calibrate_hist(self, W, R, bw, br, x, hist, granularity, h0=None):
+        """Float forward + fold of every operator's values of this batch into ``hist``
+        (a params.Histograms); granularity = QGRU_PER_* of W, R, bw, br."""
+        T, B = int(x.shape[0]), int(x.shape[1])
+        H = self.hidden_size
+        args = [_check_tensor(t, n, torch.float32) for t, n in
+                ((W, "W"), (R, "R"), (bw, "bw"), (br, "br"), (x, "x"))]
+        if h0 is not None:
+            h0 = _check_tensor(h0, "h0", torch.float32, (B, H))
+        gran = (C.c_int32 * 4)(*[int(g) for g in granularity])
+        self._ck(self._lib.qgru_calibrate_hist(self._h, hist._h, T, B, *[_ptr(t) for t in args], _ptr(h0),
+                                               gran, _stream(self._tdev)), "qgru_calibrate_hist")
+
     # -- introspection
     def synchronize(self):
         self._ck(self._lib.qgru_synchronize(self._h, _stream(self._tdev)), "qgru_synchronize")
@@ -270,6 +283,13 @@ def calculate_gru_quantitative_parameters(quant_ranges, bitwidth_config):
     return GRUQuantParams.from_ranges(quant_ranges, bitwidth_config)
 
 
+def calculate_gru_quantitative_parameters_from_histograms(hist_collectors, bitwidth_config,
+                                                          use_percentile=False, percentile_value=99.99):
+    """Histograms + bit-width config -> GRUQuantParams with LUTs (binding :233-262): Percentile
+    (use_percentile) or SQNR."""
+    return GRUQuantParams.from_histograms(hist_collectors, bitwidth_config, use_percentile, percentile_value)
+
+
 def forward_quant_int_storage(is_training, time_steps, batch_size, input_size, hidden_size,
                               W, R, bw, br, x, h0, quant_params, slot=0, reverse=False):
     """Integer forward with float interface (binding :436-571, inference mode).
@@ -314,10 +334,21 @@ def forward_fp(is_training, time_steps, batch_size, input_size, hidden_size, W, 
 def forward_calibrate(is_training, time_steps, batch_size, input_size, hidden_size, W, R, bw, br,
                       x, h0, calib_method_str, bitwidth_config, quant_ranges=None,
                       hist_collectors=None):
-    """Calibration forward (binding :683-790), MinMax method: float forward whose ranges are
-    folded into ``quant_ranges`` in place; returns (h, v)."""
-    if calib_method_str.lower() != "minmax":
-        raise NotImplementedError("only the 'minmax' calibration method is built")
+    """Calibration forward (binding :683-790): a float forward whose operator statistics are
+    folded in place into ``quant_ranges`` (method 'minmax') or into ``hist_collectors``
+    (methods 'sqnr' and 'percentile'); returns (h, v)."""
+    method = calib_method_str.lower()
+    if method in ("sqnr", "percentile", "histogram"):
+        if hist_collectors is None:
+            raise ValueError("hist_collectors is required for histogram calibration")
+        x = _check_tensor(x, "x", torch.float32, (time_steps, batch_size, input_size))
+        hd = _handle_for(x.device.index or 0, input_size, hidden_size, "fp")
+        h0 = h0 if (h0 is not None and h0.numel() > 0) else None
+        hd.calibrate_hist(W, R, bw, br, x, hist_collectors, bitwidth_config.granularity_list(), h0)
+        h = hd.forward_float(W, R, bw, br, x, h0)
+        return h, torch.empty(0, dtype=torch.float32, device=x.device)
+    if method != "minmax":
+        raise ValueError(f"unknown calibration method {calib_method_str!r}")
     if quant_ranges is None:
         raise ValueError("quant_ranges is required for minmax calibration")
     x = _check_tensor(x, "x", torch.float32, (time_steps, batch_size, input_size))

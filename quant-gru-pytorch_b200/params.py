@@ -107,6 +107,10 @@ class OperatorQuantConfig:
                                                   "use_pot2_scale": self.use_pot2},
                                "operator_config": ops}}
 
+    def granularity_list(self):
+        """QGRU_PER_* of W, R, bw, br."""
+        return [self.granularity[n] for n in WEIGHT_OPS]
+
     def fill(self, params):
         """Write the configuration fields of a ``_cabi.Params``."""
         params.use_pot2 = int(self.use_pot2)
@@ -165,6 +169,73 @@ class Ranges:
                               [self.ch_max[n] for n in WEIGHT_OPS])
 
 
+class Histograms:
+    """One direction's histogram collectors (GRUGPUHistogramCollectors,
+    include/histogram_gpu.cuh): 2048-bin histograms with range growth for the 13 activation
+    operators and, by granularity, per-tensor / per-gate / per-channel ones for W, R, bw, br.
+    Counts live on the GPU inside the library."""
+
+    def __init__(self, hidden, device=0, num_bins=2048):
+        self.hidden, self.device, self.num_bins = hidden, device, num_bins
+        self._lib = _cabi.lib()
+        self._h = C.c_void_p()
+        _cabi.check(self._lib.qgru_hist_create(C.byref(self._h), device, hidden, num_bins), "qgru_hist_create")
+
+    def close(self):
+        if getattr(self, "_h", None) is not None and self._h.value:
+            self._lib.qgru_hist_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _ck(self, st, where):
+        if st != 0:
+            raise RuntimeError(f"{where}: {_cabi.status_string(st)}: "
+                               f"{(self._lib.qgru_hist_last_error(self._h) or b'').decode()}")
+
+    def reset(self):
+        self._ck(self._lib.qgru_hist_reset(self._h), "qgru_hist_reset")
+
+    def count(self):
+        return int(self._lib.qgru_hist_count(self._h))
+
+    def collect(self, index, data):
+        """Fold a float32 CUDA tensor into collector ``index`` (GPUHistogramCollector::collect)."""
+        import torch
+        if not (data.is_cuda and data.dtype == torch.float32 and data.is_contiguous()):
+            raise ValueError("data must be a contiguous float32 CUDA tensor")
+        stream = C.c_void_p(torch.cuda.current_stream(data.device).cuda_stream)
+        self._ck(self._lib.qgru_hist_collect(self._h, int(index), C.c_void_p(data.data_ptr()),
+                                             int(data.numel()), stream), "qgru_hist_collect")
+
+    def get(self, index):
+        """(counts [num_bins] float32, min, max, total) of collector ``index``."""
+        counts = np.zeros(self.num_bins, np.float32)
+        mn, mx, tot = C.c_float(), C.c_float(), C.c_int64()
+        self._ck(self._lib.qgru_hist_export(self._h, int(index), counts.ctypes.data_as(C.POINTER(C.c_float)),
+                                            C.byref(mn), C.byref(mx), C.byref(tot)), "qgru_hist_export")
+        return counts, float(mn.value), float(mx.value), int(tot.value)
+
+    def put(self, index, counts, min_val, max_val, total):
+        counts = np.ascontiguousarray(counts, np.float32)
+        if counts.size != self.num_bins:
+            raise ValueError("counts must hold num_bins values")
+        self._ck(self._lib.qgru_hist_import(self._h, int(index), counts.ctypes.data_as(C.POINTER(C.c_float)),
+                                            float(min_val), float(max_val), int(total)), "qgru_hist_import")
+
+    def is_valid(self):
+        return self.get_total(OP["x"]) > 0
+
+    def get_total(self, index):
+        tot = C.c_int64()
+        self._ck(self._lib.qgru_hist_export(self._h, int(index), None, None, None, C.byref(tot)), "qgru_hist_export")
+        return int(tot.value)
+
+
 class GRUQuantParams:
     """One direction's quant params: the ``_cabi.Params`` POD plus the four per-channel scale
     arrays (GRUQuantParams, include/quantize_param_types.h:100-146)."""
@@ -187,6 +258,18 @@ class GRUQuantParams:
         st = L.qgru_calc_params_from_ranges(C.byref(rs), C.byref(self.c),
                                             *[self.scales[n].ctypes.data_as(fp) for n in WEIGHT_OPS])
         _cabi.check(st, "qgru_calc_params_from_ranges")
+        return self
+
+    @classmethod
+    def from_histograms(cls, hist, config, use_percentile=False, percentile=99.99):
+        """calculate_gru_quantitative_parameters_from_histograms: histograms + config -> params +
+        LUTs, by Percentile (use_percentile) or by the SQNR search."""
+        self = cls(hist.hidden, config)
+        fp = C.POINTER(C.c_float)
+        st = hist._lib.qgru_calc_params_from_hist(hist._h, int(bool(use_percentile)), float(percentile),
+                                                  C.byref(self.c),
+                                                  *[self.scales[n].ctypes.data_as(fp) for n in WEIGHT_OPS])
+        hist._ck(st, "qgru_calc_params_from_hist")
         return self
 
     def regenerate_luts(self):

@@ -22,7 +22,7 @@ import torch
 from torch import nn
 
 from . import gru_ops
-from .params import GRUQuantParams, OperatorQuantConfig, Ranges
+from .params import GRUQuantParams, Histograms, OperatorQuantConfig, Ranges
 
 
 def reorder_weights_pytorch_to_haste(w):
@@ -91,6 +91,7 @@ class QuantGRU(nn.Module):
         self.calibrating = False
         self.quant_ranges = self.quant_params = None
         self.quant_ranges_reverse = self.quant_params_reverse = None
+        self.hist_collectors = self.hist_collectors_reverse = None
         self._quant_params_dirty = False
         self._dirs = [_Direction() for _ in suffixes]
 
@@ -129,17 +130,34 @@ class QuantGRU(nn.Module):
     def reset_calibration(self):
         self.quant_ranges = self.quant_params = None
         self.quant_ranges_reverse = self.quant_params_reverse = None
+        self.hist_collectors = self.hist_collectors_reverse = None
         self._quant_params_dirty = False
 
+    def _check_method(self):
+        if self.calibration_method not in ("minmax", "sqnr", "percentile"):
+            raise ValueError(f"calibration_method must be 'minmax', 'sqnr' or 'percentile', "
+                             f"got {self.calibration_method!r}")
+
     def finalize_calibration(self, verbose=False):
-        if self.calibration_method != "minmax":
-            raise NotImplementedError("only calibration_method='minmax' is built")
-        if self.quant_ranges is None or (self.bidirectional and self.quant_ranges_reverse is None):
-            raise RuntimeError("no calibration data: set calibrating=True and call forward() first")
-        self.quant_params = gru_ops.calculate_gru_quantitative_parameters(self.quant_ranges, self._bitwidth_config)
-        if self.bidirectional:
-            self.quant_params_reverse = gru_ops.calculate_gru_quantitative_parameters(
-                self.quant_ranges_reverse, self._bitwidth_config)
+        """Ranges (minmax) or histograms (sqnr / percentile) -> quant params and LUTs
+        (pytorch/quant_gru.py finalize_calibration)."""
+        self._check_method()
+        if self.calibration_method == "minmax":
+            if self.quant_ranges is None or (self.bidirectional and self.quant_ranges_reverse is None):
+                raise RuntimeError("no calibration data: set calibrating=True and call forward() first")
+            self.quant_params = gru_ops.calculate_gru_quantitative_parameters(self.quant_ranges, self._bitwidth_config)
+            if self.bidirectional:
+                self.quant_params_reverse = gru_ops.calculate_gru_quantitative_parameters(
+                    self.quant_ranges_reverse, self._bitwidth_config)
+        else:
+            if self.hist_collectors is None or (self.bidirectional and self.hist_collectors_reverse is None):
+                raise RuntimeError("no calibration data: set calibrating=True and call forward() first")
+            pct = self.calibration_method == "percentile"
+            self.quant_params = gru_ops.calculate_gru_quantitative_parameters_from_histograms(
+                self.hist_collectors, self._bitwidth_config, pct, self.percentile_value)
+            if self.bidirectional:
+                self.quant_params_reverse = gru_ops.calculate_gru_quantitative_parameters_from_histograms(
+                    self.hist_collectors_reverse, self._bitwidth_config, pct, self.percentile_value)
         self._quant_params_dirty = False
 
     # ---------------------------------------------------------- quant-param JSON files
@@ -269,16 +287,23 @@ class QuantGRU(nn.Module):
         h0 = self._split_h0(hx, B, device, torch.float32)
 
         if self.calibrating:
-            if self.calibration_method != "minmax":
-                raise NotImplementedError("only calibration_method='minmax' is built")
+            self._check_method()
             outs = []
             for d in range(self.num_directions):
                 st = self._direction(d, device)
-                rng_name = "quant_ranges_reverse" if d == 1 else "quant_ranges"
-                if getattr(self, rng_name) is None:
-                    setattr(self, rng_name, Ranges(self.hidden_size))
                 xd = x.flip(0).contiguous() if d == 1 else x
-                h = st.handle.calibrate_minmax(*st.weights, xd, getattr(self, rng_name), h0[d], want_h=True)
+                if self.calibration_method == "minmax":
+                    rng_name = "quant_ranges_reverse" if d == 1 else "quant_ranges"
+                    if getattr(self, rng_name) is None:
+                        setattr(self, rng_name, Ranges(self.hidden_size))
+                    h = st.handle.calibrate_minmax(*st.weights, xd, getattr(self, rng_name), h0[d], want_h=True)
+                else:
+                    name = "hist_collectors_reverse" if d == 1 else "hist_collectors"
+                    if getattr(self, name) is None:
+                        setattr(self, name, Histograms(self.hidden_size, device.index or 0))
+                    st.handle.calibrate_hist(*st.weights, xd, getattr(self, name),
+                                             self._bitwidth_config.granularity_list(), h0[d])
+                    h = st.handle.forward_float(*st.weights, xd, h0[d])
                 outs.append(torch.cat([h[1:].flip(0), h[0:1]], 0) if d == 1 else h)
             self._quant_params_dirty = True
         elif self.use_quantization:
