@@ -569,15 +569,19 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
     const bool dp4a_ok = plan_recurrence(h, B, &pl);
     RecMmaPlan mp;
     const int n_tab_mma = std::max(h->n_table, h->gc_host.fused_ok ? h->gc_host.ft_ih_off : 0);
-    const bool mma_ok = h->opt_rec != 1 && rec_mma_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, &mp);
-    if (h->opt_rec == 2 && !mma_ok) return fail(h, QGRU_ERR_UNSUPPORTED, "tensor-core recurrence needs H <= 512");
+    // two tensor-core forms: state exchanged through distributed shared memory (one cluster per
+    // group; H <= 1024) or through global memory with a counter per group (H <= 512)
+    RecMmaPlan cp;
+    const bool cluster_ok = h->opt_rec != 1 && h->opt_exchange != 1 &&
+                            rec_cluster_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, h->opt_r_where, &cp);
+    const bool global_ok = h->opt_rec != 1 && rec_mma_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, &mp);
+    const bool mma_ok = cluster_ok || global_ok;
+    if (h->opt_rec == 2 && !mma_ok)
+        return fail(h, QGRU_ERR_UNSUPPORTED, "tensor-core recurrence needs H <= 1024 (H <= 512 with exchange=global)");
     // Tiny batches whose R fits one SM run barrier-free on one CTA per batch row: lower latency
     // than tensor-core tiles of 16 batch columns.
     bool use_mma = mma_ok && (h->opt_rec == 2 || !(dp4a_ok && pl.P == 1 && B <= 4));
-    // state exchange through distributed shared memory (one cluster per group) where it fits
-    RecMmaPlan cp;
-    const bool use_cluster = use_mma && h->opt_exchange != 1 &&
-                             rec_cluster_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, h->opt_r_where, &cp);
+    const bool use_cluster = use_mma && cluster_ok;
     if (h->opt_exchange == 2 && use_mma && !use_cluster)
         return fail(h, QGRU_ERR_UNSUPPORTED, "cluster exchange does not fit shared memory");
     if (use_cluster) mp = cp;
@@ -672,7 +676,7 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
         h->launches += h->rec.launches + h->rec_cl.launches - before;
         snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 exchange=%s cell=%s MT=%d NB=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d r_in=%s narrow=%d ih_bytes=%d shiftfree=%d%d%d%d",
                  used_tc ? "tcgen05_i8" : "simt_dp4a", use_cluster ? "cluster_dsmem" : "global", fast_cell ? "fused_shiftfree" : fused ? "fused" : "generic", mp.MT, mp.NB, mp.P, mp.G,
-                 mp.groups_per_launch, mp.smem, mp.tmem_cols, (use_cluster && mp.r_tmem_col > 0) ? "tmem" : "smem",
+                 mp.groups_per_launch, mp.smem, mp.tmem_cols, !use_cluster || mp.tmem_tiles == 0 ? "smem" : (mp.tmem_tiles == mp.MT * 3 * (h->Hpad / 128) ? "tmem" : "tmem+smem"),
                  h->gc_host.narrow, ih_bytes, (int)a.lc.fits32,
                  (int)h->rs_fast[1], h->gc_host.rh_to_n.mq != 0, h->gc_host.uh_to_h.mq != 0);
     } else {

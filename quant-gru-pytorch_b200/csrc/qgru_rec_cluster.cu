@@ -69,10 +69,12 @@ struct ClusterSmem {
     size_t r_tiles, h_tile, bars, tables, total;
 };
 
-__host__ __device__ inline ClusterSmem cluster_smem_layout(int MT, int KBn, int NB, int n_table) {
+// r_slots: 16 KB tile slots for R (staging on the way to tensor memory, then home of the tiles
+// that stay in shared memory)
+__host__ __device__ inline ClusterSmem cluster_smem_layout(int r_slots, int KBn, int NB, int n_table) {
     ClusterSmem s;
     s.r_tiles = 0;
-    s.h_tile = (size_t)MT * 3 * KBn * 16384;
+    s.h_tile = (size_t)r_slots * 16384;
     s.bars = s.h_tile + (size_t)2 * KBn * NB * 128;   // two state buffers
     s.tables = s.bars + 128;
     s.total = s.tables + (((size_t)n_table * 4 + 15) & ~size_t(15));
@@ -95,7 +97,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
     const uint32_t raw = tc::smem_u32(smem_raw);
     unsigned char *base = smem_raw + (((raw + 1023u) & ~1023u) - raw);
     const int KBn = a.Hpad >> 7;
-    const ClusterSmem L = cluster_smem_layout(MT, KBn, a.NB, a.n_table);
+    const ClusterSmem L = cluster_smem_layout(a.r_slots, KBn, a.NB, a.n_table);
     unsigned char *r_tiles = base + L.r_tiles;
     unsigned char *h_tile = base + L.h_tile;
     const uint32_t h_buf_bytes = (uint32_t)(KBn * a.NB * 128);
@@ -141,18 +143,33 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
         bool ok = true;
         uint32_t idesc = 0, r_lo0 = 0, h_lo0 = 0, desc_hi = 0, desc_lo = 0;
         if (lane == 0) {
-            tc::mbar_expect_tx(r_full, (uint32_t)(MT * 3 * KBn) * 16384u);
-            for (int mt = 0; mt < MT; ++mt)
-                for (int g = 0; g < 3; ++g)
-                    for (int kb = 0; kb < KBn; ++kb)
-                        tc::tma_load_2d(r_tiles + (size_t)((mt * 3 + g) * KBn + kb) * 16384, &map_r, r_full,
-                                        kb * 128, g * a.H + j0 + mt * 128);
+            // R slice: tiles [0, tmem_tiles) go to tensor memory through the slots, one pass of up to
+            // r_slots tiles at a time (the epilogue threads copy a pass and hand the slots back);
+            // the remaining tiles are then loaded into the slots to stay.
+            const int n_tiles = MT * 3 * KBn;
+            auto load_tiles = [&](int first, int cnt) {
+                tc::mbar_expect_tx(r_full, (uint32_t)cnt * 16384u);
+                for (int i = 0; i < cnt; ++i) {
+                    const int t = first + i, mt = t / (3 * KBn), g = (t / KBn) % 3, kb = t % KBn;
+                    tc::tma_load_2d(r_tiles + (size_t)i * 16384, &map_r, r_full, kb * 128, g * a.H + j0 + mt * 128);
+                }
+            };
+            int pass = 0;
+            for (int done = 0; done < a.tmem_tiles && ok; ++pass) {
+                const int cnt = min(a.r_slots, a.tmem_tiles - done);
+                load_tiles(done, cnt);
+                ok = tc::mbar_wait(r_ready, (uint32_t)(pass & 1), WAIT_BUDGET);   // copied: slots free again
+                done += cnt;
+            }
+            if (ok && n_tiles > a.tmem_tiles) {
+                load_tiles(a.tmem_tiles, n_tiles - a.tmem_tiles);
+                ok = tc::mbar_wait(r_full, (uint32_t)(pass & 1), WAIT_BUDGET);
+            }
             // the initial state (written by the preceding kernel) into buffer 0
             tc::mbar_expect_tx(h_full, h_buf_bytes);
             for (int kb = 0; kb < KBn; ++kb)
                 tc::tma_load_2d(h_tile + (size_t)kb * a.NB * 128, &map_h, h_full, kb * 128, b0);
-            ok = tc::mbar_wait(r_full, 0, WAIT_BUDGET) && tc::mbar_wait(h_full, 0, WAIT_BUDGET);
-            if (ok && a.r_tmem_col > 0) ok = tc::mbar_wait(r_ready, 0, WAIT_BUDGET);
+            ok = ok && tc::mbar_wait(h_full, 0, WAIT_BUDGET);
             idesc = tc::idesc_i8(128, a.NB, true, !a.h_unsigned);
             r_lo0 = (tc::smem_u32(r_tiles) & 0x3FFFFu) >> 4;
             h_lo0 = (tc::smem_u32(h_tile) & 0x3FFFFu) >> 4;
@@ -186,45 +203,76 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                 // the reset and new gates are still being multiplied.  The epilogue warps that share
                 // this warp's scheduler are busy by then, so every operand is prepared up front and
                 // the loops are fully unrolled: one independent add per MMA, no dependent chain.
-                uint32_t bdl[4][4];   // low descriptor words of the state tile: K-slab kb, 32-byte step ks
-#pragma unroll
-                for (int kb = 0; kb < 4; ++kb)
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) bdl[kb][ks] = desc_lo | (hbuf + (uint32_t)(kb * a.NB * 8 + 2 * ks));
                 const uint64_t dhi = (uint64_t)desc_hi << 32;
-                if (a.r_tmem_col > 0) {   // A operand from tensor memory
+                const uint32_t r_t0 = tmem_base + (uint32_t)a.r_tmem_col;
+                if (KBn <= 4 && (a.tmem_tiles == 0 || a.tmem_tiles == MT * 3 * KBn)) {
+                    // the common shapes (H <= 512, R in one place): every operand prepared up front,
+                    // one independent add per MMA - the issuing thread's instruction stream sets the pace
+                    uint32_t bdl[4][4];   // low descriptor words of the state tile: K-slab kb, 32-byte step ks
 #pragma unroll
-                    for (int g = 0; g < 3; ++g) {
+                    for (int kb = 0; kb < 4; ++kb)
 #pragma unroll
-                        for (int mt = 0; mt < MT; ++mt) {
-                            const uint32_t d = tmem_base + (uint32_t)((mt * 3 + g) * a.NB);
-                            const uint32_t ra = tmem_base + (uint32_t)(a.r_tmem_col + (mt * 3 + g) * KBn * 32);
+                        for (int ks = 0; ks < 4; ++ks) bdl[kb][ks] = desc_lo | (hbuf + (uint32_t)(kb * a.NB * 8 + 2 * ks));
+                    if (a.tmem_tiles > 0) {   // A operand from tensor memory
 #pragma unroll
-                            for (int kb = 0; kb < 4; ++kb)
-                                if (kb < KBn) {
+                        for (int g = 0; g < 3; ++g) {
 #pragma unroll
-                                    for (int ks = 0; ks < 4; ++ks)
-                                        tc::mma_i8_ts(d, ra + (uint32_t)(kb * 32 + ks * 8), dhi | bdl[kb][ks], idesc,
-                                                      (kb | ks) != 0);
-                                }
+                            for (int mt = 0; mt < MT; ++mt) {
+                                const uint32_t d = tmem_base + (uint32_t)((mt * 3 + g) * a.NB);
+                                const uint32_t ra = r_t0 + (uint32_t)((mt * 3 + g) * KBn * 32);
+#pragma unroll
+                                for (int kb = 0; kb < 4; ++kb)
+                                    if (kb < KBn) {
+#pragma unroll
+                                        for (int ks = 0; ks < 4; ++ks)
+                                            tc::mma_i8_ts(d, ra + (uint32_t)(kb * 32 + ks * 8), dhi | bdl[kb][ks], idesc,
+                                                          (kb | ks) != 0);
+                                    }
+                            }
+                            tc::mma_commit(&mma_done[g]);
                         }
-                        tc::mma_commit(&mma_done[g]);
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < 3; ++g) {
+#pragma unroll
+                            for (int mt = 0; mt < MT; ++mt) {
+                                const uint32_t d = tmem_base + (uint32_t)((mt * 3 + g) * a.NB);
+                                const uint32_t rb = desc_lo | (r_lo0 + (uint32_t)((mt * 3 + g) * KBn * 1024));
+#pragma unroll
+                                for (int kb = 0; kb < 4; ++kb)
+                                    if (kb < KBn) {
+#pragma unroll
+                                        for (int ks = 0; ks < 4; ++ks)
+                                            tc::mma_i8(d, dhi | (rb + (uint32_t)(kb * 1024 + 2 * ks)), dhi | bdl[kb][ks], idesc,
+                                                       (kb | ks) != 0);
+                                    }
+                            }
+                            tc::mma_commit(&mma_done[g]);
+                        }
                     }
                 } else {
-#pragma unroll
+                    // wide hidden sizes: the tiles of a gate come partly from tensor memory, partly
+                    // from their shared-memory slots
+                    // (rolled loops: the fully unrolled form of these 96 MMAs measured slower)
+                    const uint32_t hb0 = desc_lo | hbuf;
                     for (int g = 0; g < 3; ++g) {
-#pragma unroll
                         for (int mt = 0; mt < MT; ++mt) {
                             const uint32_t d = tmem_base + (uint32_t)((mt * 3 + g) * a.NB);
-                            const uint32_t rb = desc_lo | (r_lo0 + (uint32_t)((mt * 3 + g) * KBn * 1024));
-#pragma unroll
-                            for (int kb = 0; kb < 4; ++kb)
-                                if (kb < KBn) {
+                            for (int kb = 0; kb < KBn; ++kb) {
+                                const int tile = (mt * 3 + g) * KBn + kb;
+                                const uint32_t bd = hb0 + (uint32_t)(kb * a.NB * 8);
+                                if (tile < a.tmem_tiles) {
+                                    const uint32_t ra = r_t0 + (uint32_t)(tile * 32);
 #pragma unroll
                                     for (int ks = 0; ks < 4; ++ks)
-                                        tc::mma_i8(d, dhi | (rb + (uint32_t)(kb * 1024 + 2 * ks)), dhi | bdl[kb][ks], idesc,
-                                                   (kb | ks) != 0);
+                                        tc::mma_i8_ts(d, ra + (uint32_t)(ks * 8), dhi | (bd + 2 * ks), idesc, (kb | ks) != 0);
+                                } else {
+                                    const uint32_t rb = desc_lo | (r_lo0 + (uint32_t)((tile - a.tmem_tiles) * 1024));
+#pragma unroll
+                                    for (int ks = 0; ks < 4; ++ks)
+                                        tc::mma_i8(d, dhi | (rb + (uint32_t)(2 * ks)), dhi | (bd + 2 * ks), idesc, (kb | ks) != 0);
                                 }
+                            }
                         }
                         tc::mma_commit(&mma_done[g]);
                     }
@@ -259,29 +307,34 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
             }
         }
         bool ok = true;
-        if (a.r_tmem_col > 0) {
-            // Move the R slice from its TMA-written tiles into tensor memory, where the MMA reads
-            // its A operand without touching shared memory.  This thread owns row u of every
-            // 128-row tile: eight 16-byte chunks per 128-byte row, un-swizzled on the way (chunk c
-            // of row u lies at chunk c ^ (u & 7)), written to 32 columns of TMEM lane u.
-            ok = tc::mbar_wait(r_full, 0, WAIT_BUDGET);
-            const int n_tiles = MT * 3 * KBn;
-            for (int tile = rank; tile < n_tiles && ok; tile += EPW) {
-                const unsigned char *row = r_tiles + (size_t)tile * 16384 + (size_t)(u >> 3) * 1024 + (size_t)(u & 7) * 128;
-                uint32_t w[32];
+        {
+            // Move tiles [0, tmem_tiles) of the R slice from their TMA-written slots into tensor
+            // memory, where the MMA reads its A operand without touching shared memory.  This thread
+            // owns row u of every 128-row tile: eight 16-byte chunks per 128-byte row, un-swizzled
+            // on the way (chunk c of row u lies at chunk c ^ (u & 7)), written to 32 columns of TMEM
+            // lane u.  One pass per refill of the slots.
+            int pass = 0;
+            for (int done = 0; done < a.tmem_tiles && ok; ++pass) {
+                const int cnt = min(a.r_slots, a.tmem_tiles - done);
+                ok = tc::mbar_wait(r_full, (uint32_t)(pass & 1), WAIT_BUDGET);
+                for (int i = rank; i < cnt && ok; i += EPW) {
+                    const unsigned char *row = r_tiles + (size_t)i * 16384 + (size_t)(u >> 3) * 1024 + (size_t)(u & 7) * 128;
+                    uint32_t w[32];
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const uint4 v = *reinterpret_cast<const uint4 *>(row + ((c ^ (u & 7)) << 4));
-                    w[4 * c + 0] = v.x;
-                    w[4 * c + 1] = v.y;
-                    w[4 * c + 2] = v.z;
-                    w[4 * c + 3] = v.w;
+                    for (int c = 0; c < 8; ++c) {
+                        const uint4 v = *reinterpret_cast<const uint4 *>(row + ((c ^ (u & 7)) << 4));
+                        w[4 * c + 0] = v.x;
+                        w[4 * c + 1] = v.y;
+                        w[4 * c + 2] = v.z;
+                        w[4 * c + 3] = v.w;
+                    }
+                    tc::tmem_st32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a.r_tmem_col + (done + i) * 32), w);
                 }
-                tc::tmem_st32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a.r_tmem_col + tile * 32), w);
+                tc::tmem_st_wait();
+                tc::tc_fence_before_sync();
+                tc::mbar_arrive(r_ready);
+                done += cnt;
             }
-            tc::tmem_st_wait();
-            tc::tc_fence_before_sync();
-            tc::mbar_arrive(r_ready);
         }
         // the TMA-written initial state must be complete before h_{t-1} is read from the tile
         ok = tc::mbar_wait(h_full, 0, WAIT_BUDGET) && ok;
@@ -522,35 +575,43 @@ cudaError_t launch_any(bool fused, bool narrow, int ih_bytes, int MT, const CUte
 
 bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, int r_where,
                       RecMmaPlan *out) {
-    if (Hpad > 512) return false;                  // the R slice of 128 units must fit one SM
+    if (Hpad > 1024) return false;                 // K-slab loops are unrolled to 8
     const int KBn = Hpad / 128;
     const int MT = (H > 128 && H <= 256) ? 2 : 1;
-    const int P = (H + 128 * MT - 1) / (128 * MT);  // cluster size: 1..4
+    const int P = (H + 128 * MT - 1) / (128 * MT);  // cluster size: 1..8 (the portable maximum)
     if (P > 8 || P > sms) return false;
     const int groups_max = std::max(1, sms / P);
     int NB = ((B + groups_max - 1) / groups_max + 15) / 16 * 16;
     const int nb_cap = MT == 2 ? 64 : 128;         // 3*MT*NB accumulator columns <= 512
     NB = std::min(NB, nb_cap);
-    while (NB > 16 && cluster_smem_layout(MT, KBn, NB, n_table).total + 1024 > (size_t)smem_optin) NB -= 16;
-    const size_t smem = cluster_smem_layout(MT, KBn, NB, n_table).total + 1024;
-    if (smem > (size_t)smem_optin) return false;
-    // R resident in tensor memory when it fits beside the accumulators (r_where: 0 auto, 1 shared
-    // memory, 2 tensor memory): 32 columns per 128x128 tile
-    const int acc_cols = (3 * MT * NB + 31) / 32 * 32;
-    const int r_cols = MT * 3 * KBn * 32;
-    const bool r_tmem = r_where != 1 && acc_cols + r_cols <= 512;
-    if (r_where == 2 && !r_tmem) return false;
-    uint32_t cols = 32;
-    while ((int)cols < (r_tmem ? acc_cols + r_cols : 3 * MT * NB)) cols <<= 1;
-    out->r_tmem_col = r_tmem ? acc_cols : 0;
-    out->MT = MT;
-    out->P = P;
-    out->NB = NB;
-    out->G = (B + NB - 1) / NB;
-    out->smem = smem;
-    out->tmem_cols = (int)cols;
-    out->groups_per_launch = out->G;               // clusters are scheduled as SMs free up
-    return true;
+    const int n_tiles = MT * 3 * KBn;
+    // Where the R slice lives: as many 128x128 tiles as fit beside the accumulators go to tensor
+    // memory (32 columns each; r_where: 0 auto, 1 none, 2 at least one), the rest stays in
+    // shared-memory slots; the slots also stage the tensor-memory tiles, up to 12 per pass.
+    for (;; NB -= 16) {
+        const int acc_cols = (3 * MT * NB + 31) / 32 * 32;
+        const int tmem_tiles = r_where == 1 ? 0 : std::max(0, std::min(n_tiles, (512 - acc_cols) / 32));
+        const int resident = n_tiles - tmem_tiles;
+        for (int stage = std::min(std::max(tmem_tiles, 1), 12); stage >= 1; --stage) {
+            const int r_slots = std::max(resident, stage);
+            const size_t smem = cluster_smem_layout(r_slots, KBn, NB, n_table).total + 1024;
+            if (smem > (size_t)smem_optin || (r_where == 2 && tmem_tiles == 0)) continue;
+            uint32_t cols = 32;
+            while ((int)cols < acc_cols + tmem_tiles * 32) cols <<= 1;
+            out->MT = MT;
+            out->P = P;
+            out->NB = NB;
+            out->G = (B + NB - 1) / NB;
+            out->smem = smem;
+            out->tmem_cols = (int)cols;
+            out->r_tmem_col = tmem_tiles > 0 ? acc_cols : 0;
+            out->tmem_tiles = tmem_tiles;
+            out->r_slots = r_slots;
+            out->groups_per_launch = out->G;       // clusters are scheduled as SMs free up
+            return true;
+        }
+        if (NB <= 16) return false;
+    }
 }
 
 int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const GateConsts &gc_host,
@@ -578,6 +639,8 @@ int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const
     a.h_unsigned = h_unsigned ? 1 : 0;
     a.tmem_cols = (uint32_t)pl.tmem_cols;
     a.r_tmem_col = pl.r_tmem_col;
+    a.tmem_tiles = pl.tmem_tiles;
+    a.r_slots = pl.r_slots;
     a.b_off = 0;
     a.b_cnt = a.B;
     const cudaError_t e = launch_any(fused, narrow, ih_bytes, pl.MT, mr, mh, gc_host, a, pl.G * pl.P, pl.smem, stream);

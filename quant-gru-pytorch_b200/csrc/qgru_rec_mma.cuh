@@ -19,7 +19,9 @@ struct RecMmaArgs {
     int reverse;
     int h_unsigned;   // the state h is stored as uint8 (else int8)
     uint32_t tmem_cols;
-    int r_tmem_col;   // first tensor-memory column of the resident R slice, 0: R stays in shared memory
+    int r_tmem_col;   // first tensor-memory column of the R tiles kept there
+    int tmem_tiles;   // cluster kernel: R tiles [0, tmem_tiles) live in tensor memory, the rest in shared memory
+    int r_slots;      // cluster kernel: 16 KB shared-memory tile slots for R
     const void *ih;         // [T*B][3H]: raw W*x+bw (int8/int16) or pre-rescaled for the fused cell (int16/int32)
     uint8_t *h8;            // [2][B][Hpad] ping-pong state (+ slack rows)
     int32_t *hq_out;        // [(T+1)][B][H] or null
@@ -35,7 +37,7 @@ struct RecMmaArgs {
 
 struct RecMmaPlan {
     int MT = 1, P = 1, NB = 16, G = 1, tmem_cols = 32, groups_per_launch = 1;
-    int r_tmem_col = 0;
+    int r_tmem_col = 0, tmem_tiles = 0, r_slots = 0;
     size_t smem = 0;
 };
 

@@ -79,16 +79,26 @@ def test_shapes_default_config(oracle, cuda_device, shape, rec):
     assert np.array_equal(got, _want(oracle, case)), plan
 
 
-def test_simt_gemm_and_wide_hidden_fallback(oracle, cuda_device):
-    """The SIMT GEMM stays available (option), and H > 512 runs on the dp4a recurrence."""
+def test_simt_gemm_and_wide_hidden(oracle, cuda_device):
+    """The SIMT GEMM stays available (option); 512 < H <= 1024 runs on the cluster recurrence with
+    the R slice split between tensor memory and shared memory; H > 1024 on the dp4a recurrence."""
     case = make_case(12, 5, 9, 72, 136, oracle, config_named("cfg2"))
     got, plan, _ = _run(case, cuda_device, opts=(("gemm", "simt"),))
     assert "gemm=simt_dp4a" in plan and np.array_equal(got, _want(oracle, case))
-    wide = make_case(13, 3, 5, 40, 640, oracle, config_named("default"))
-    got, plan, _ = _run(wide, cuda_device)
-    assert "rec=dp4a" in plan and np.array_equal(got, _want(oracle, wide)), plan
+    for H in (640, 1024):
+        wide = make_case(13, 3, 21, 40, H, oracle, config_named("default"))
+        got, plan, _ = _run(wide, cuda_device)
+        assert "rec=tcgen05_i8" in plan and "r_in=tmem+smem" in plan, plan
+        assert np.array_equal(got, _want(oracle, wide)), plan
+        got, plan, _ = _run(wide, cuda_device, opts=(("rec", "dp4a"),))
+        assert "rec=dp4a" in plan and np.array_equal(got, _want(oracle, wide)), plan
+        with pytest.raises(Exception):
+            _run(wide, cuda_device, opts=(("rec", "mma"), ("exchange", "global")))
+    huge = make_case(15, 2, 3, 24, 1100, oracle, config_named("default"))
+    got, plan, _ = _run(huge, cuda_device)
+    assert "rec=dp4a" in plan and np.array_equal(got, _want(oracle, huge)), plan
     with pytest.raises(Exception):
-        _run(wide, cuda_device, opts=(("rec", "mma"),))
+        _run(huge, cuda_device, opts=(("rec", "mma"),))
 
 
 def test_large_batch_many_groups(oracle, cuda_device):
