@@ -155,7 +155,8 @@ int qgru_set_option(qgru_handle *h, const char *name, const char *value) {
         else if (v == "dp4a") h->opt_rec = 1;
         else if (v == "mma") h->opt_rec = 2;
         else if (v == "generic") h->opt_rec = 3;
-        else return fail(h, QGRU_ERR_BAD_ARG, "rec: auto|dp4a|mma|generic");
+        else if (v == "gemv") h->opt_rec = 4;
+        else return fail(h, QGRU_ERR_BAD_ARG, "rec: auto|dp4a|mma|gemv|generic");
     } else if (n == "exchange") {
         if (v == "auto") h->opt_exchange = 0;
         else if (v == "global") h->opt_exchange = 1;
@@ -556,6 +557,29 @@ int launch_rec(qgru_handle *h, RecArgs &a, const RecPlan &pl, cudaStream_t st) {
     return QGRU_OK;
 }
 
+// Small-batch form: one CTA per batch row, whole R in shared memory (H <= 256).
+size_t gemv_smem(const qgru_handle *h, int n_table) {
+    const size_t units = (size_t)(h->H + 31) / 32 * 32;
+    return (((size_t)n_table * 4 + 15) & ~size_t(15)) + (size_t)2 * (h->Hpad + 64) + (size_t)3 * units * h->Hpad;
+}
+bool gemv_fits(const qgru_handle *h) {
+    const int n_tab = std::max(h->n_table, h->gc_host.fused_ok ? h->gc_host.ft_ih_off : 0);
+    return h->Hpad <= 256 && gemv_smem(h, n_tab) <= (size_t)h->smem_optin;
+}
+
+template <bool HU, typename IhT>
+int launch_gemv(qgru_handle *h, RecArgs &a, bool fused, cudaStream_t st) {
+    auto kern = fused ? k_recurrence_gemv<HU, IhT, 2>
+                      : (h->gc_host.narrow ? k_recurrence_gemv<HU, IhT, 1> : k_recurrence_gemv<HU, IhT, 0>);
+    const size_t smem = gemv_smem(h, a.n_table);
+    CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int threads = 4 * ((h->H + 31) / 32 * 32);
+    kern<<<a.B, threads, smem, st>>>(h->gc_host, a);
+    CK(cudaGetLastError());
+    h->launches++;
+    return QGRU_OK;
+}
+
 // Shared tail of the two device entry points, 8-bit path: x8 and the initial state are ready.
 int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsigned flags,
              cudaStream_t st) {
@@ -581,13 +605,22 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
     // Tiny batches whose R fits one SM run barrier-free on one CTA per batch row: lower latency
     // than tensor-core tiles of 16 batch columns.
     bool use_mma = mma_ok && (h->opt_rec == 2 || !(dp4a_ok && pl.P == 1 && B <= 4));
+    // One CTA per row with the whole R on chip: no synchronisation between CTAs at all.  Taken
+    // while the rows fit one wave of SMs (beyond that the tensor-core tiles win on throughput).
+    const bool gemv_ok = gemv_fits(h) && h->opt_rec != 1 && h->opt_rec != 2;
+    if (h->opt_rec == 4 && !gemv_ok) return fail(h, QGRU_ERR_UNSUPPORTED, "rec=gemv needs H <= 256");
+    const bool use_gemv = gemv_ok && (h->opt_rec == 4 || (h->opt_rec == 0 && B <= sms));
+    if (use_gemv) use_mma = false;
     const bool use_cluster = use_mma && cluster_ok;
     if (h->opt_exchange == 2 && use_mma && !use_cluster)
         return fail(h, QGRU_ERR_UNSUPPORTED, "cluster exchange does not fit shared memory");
     if (use_cluster) mp = cp;
-    if (!use_mma && !dp4a_ok) return fail(h, QGRU_ERR_UNSUPPORTED, "no recurrence plan fits shared memory");
+    if (!use_mma && !use_gemv && !dp4a_ok) return fail(h, QGRU_ERR_UNSUPPORTED, "no recurrence plan fits shared memory");
     // the fused cell needs the GEMM epilogue to pre-rescale W*x+bw: tensor-core GEMM only
-    const bool fused = use_mma && h->gc_host.fused_ok && h->opt_gemm != 1 && h->opt_cell != 1;
+    // (the one-CTA-per-row form takes it only in its branch-free shape: every scale shift-free)
+    const bool gemv_fused = use_gemv && h->opt_cell == 0 && h->lin_fits32[1] && h->rs_fast[1] &&
+                            h->gc_host.rh_to_n.mq != 0 && h->gc_host.uh_to_h.mq != 0;
+    const bool fused = (use_mma || gemv_fused) && h->gc_host.fused_ok && h->opt_gemm != 1 && h->opt_cell != 1;
     const int ih_bytes = fused ? h->gc_host.ih_pre_bytes : h->ih_bytes;
     PreScale ps{};
     if (fused) {
@@ -696,11 +729,25 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
         a.bar = h->d_bar;
         a.abort_flag = h->d_flags + 1;
         a.spin_limit = h->spin_limit;
-        if (h->ih_bytes == 1) rc = h->h_uns ? launch_rec<true, int8_t>(h, a, pl, st) : launch_rec<false, int8_t>(h, a, pl, st);
-        else rc = h->h_uns ? launch_rec<true, int16_t>(h, a, pl, st) : launch_rec<false, int16_t>(h, a, pl, st);
-        if (rc) return rc;
-        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=dp4a Hs=%d Bt=%d P=%d G=%d smem=%zu narrow=%d ih_bytes=%d",
-                 used_tc ? "tcgen05_i8" : "simt_dp4a", pl.Hs, pl.Bt, pl.P, pl.G, pl.smem, h->gc_host.narrow, h->ih_bytes);
+        if (use_gemv) {
+            if (fused) {
+                a.tables = h->d_ftables;
+                a.n_table = h->gc_host.ft_ih_off;
+            }
+            if (ih_bytes == 1) rc = h->h_uns ? launch_gemv<true, int8_t>(h, a, fused, st) : launch_gemv<false, int8_t>(h, a, fused, st);
+            else if (ih_bytes == 2) rc = h->h_uns ? launch_gemv<true, int16_t>(h, a, fused, st) : launch_gemv<false, int16_t>(h, a, fused, st);
+            else rc = h->h_uns ? launch_gemv<true, int32_t>(h, a, fused, st) : launch_gemv<false, int32_t>(h, a, fused, st);
+            if (rc) return rc;
+            snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=gemv cell=%s rows_per_cta=1 ctas=%d smem=%zu narrow=%d ih_bytes=%d",
+                     used_tc ? "tcgen05_i8" : "simt_dp4a", fused ? "fused_shiftfree" : "generic", B,
+                     gemv_smem(h, a.n_table), h->gc_host.narrow, ih_bytes);
+        } else {
+            if (h->ih_bytes == 1) rc = h->h_uns ? launch_rec<true, int8_t>(h, a, pl, st) : launch_rec<false, int8_t>(h, a, pl, st);
+            else rc = h->h_uns ? launch_rec<true, int16_t>(h, a, pl, st) : launch_rec<false, int16_t>(h, a, pl, st);
+            if (rc) return rc;
+            snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=dp4a Hs=%d Bt=%d P=%d G=%d smem=%zu narrow=%d ih_bytes=%d",
+                     used_tc ? "tcgen05_i8" : "simt_dp4a", pl.Hs, pl.Bt, pl.P, pl.G, pl.smem, h->gc_host.narrow, h->ih_bytes);
+        }
     }
     CK(cudaEventRecord(h->ev[3], st));
     h->timing_valid = true;

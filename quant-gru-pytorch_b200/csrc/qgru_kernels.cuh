@@ -402,6 +402,137 @@ __global__ void __launch_bounds__(256, 1) k_recurrence_dp4a(RecArgs a) {
     }
 }
 
+// ------------------------------------------- persistent recurrence, small batch (GEMV form)
+
+// One CTA per batch row, the whole R (3H x Hpad int8, H <= 256) in shared memory for all T
+// steps: rows never interact, so there is no inter-CTA synchronisation at all and the step is
+// as short as one matrix-vector product plus one cell.  A quad of threads owns one hidden unit:
+// each lane takes a quarter of K for the unit's three gate rows (dp4a), two shuffles add the
+// partial sums, lane 0 of the quad requantizes and runs the cell.  R is stored in the order the
+// threads read it ([16-byte chunk][gate][thread]), so every 128-bit load is conflict-free.
+// The state h_t stays in shared memory (two buffers, one __syncthreads per step).
+// Cell: 0 generic datapath, 1 its 32-bit ("narrow") rescales, 2 the tabulated branch-free cell
+// (W*x+bw arrives pre-rescaled from the GEMM; every scale in shift-free form).
+template <bool HUnsigned, typename IhT, int Cell>
+__global__ void __launch_bounds__(1024, 1) k_recurrence_gemv(const __grid_constant__ GateConsts gc, RecArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int NT = blockDim.x;             // 4 * units (units rounded up to 32)
+    const int Kq = a.Hpad >> 2;            // K bytes per lane of a quad
+    const int nch = Kq >> 4;               // 16-byte chunks per lane and gate row (2 or 4)
+    // layout: tables | hs[2][Hs] | Rq[nch * 3][NT] uint4.  The four K-quarters of a state buffer
+    // are 16 bytes further apart than their length, so that the four 16-byte segments a warp
+    // reads at once fall into different banks.
+    const int Qs = Kq + 16, Hs = 4 * Qs;
+    int32_t *tables = reinterpret_cast<int32_t *>(smem_raw);
+    size_t off = ((size_t)a.n_table * 4 + 15) & ~size_t(15);
+    unsigned char *hs = smem_raw + off;
+    off += (size_t)2 * Hs;
+    uint4 *Rq = reinterpret_cast<uint4 *>(smem_raw + off);
+
+    const int tid = threadIdx.x, qd = tid & 3, j = tid >> 2;
+    const int b = blockIdx.x;
+    const bool j_ok = j < a.H;
+
+    for (int i = tid; i < a.n_table; i += NT) tables[i] = a.tables[i];
+    for (int i = tid; i < a.Hpad; i += NT) {
+        const int at = (i / Kq) * Qs + (i % Kq);
+        hs[at] = a.h8[(size_t)b * a.Hpad + i];      // initial state of this row (buffer 0 of h8)
+        hs[Hs + at] = 0;
+    }
+    const int j_at = (j / Kq) * Qs + (j % Kq);      // where unit j's byte sits in a state buffer
+    for (int g = 0; g < 3; ++g)
+        for (int c = 0; c < nch; ++c) {
+            uint4 w = make_uint4(0u, 0u, 0u, 0u);
+            if (j_ok) w = *reinterpret_cast<const uint4 *>(a.r8 + (size_t)(g * a.H + j) * a.Hpad + qd * Kq + 16 * c);
+            Rq[(size_t)(c * 3 + g) * NT + tid] = w;
+        }
+    // per-unit constants of the R*h + br epilogue (used by lane 0 of the quad)
+    int64_t corr[3] = {0, 0, 0};
+    Rescale rs[3];
+    FastLin fl[3];
+    bool fast = a.lc.fits32 != 0;
+#pragma unroll
+    for (int g = 0; g < 3; ++g) {
+        rs[g] = Rescale{1, 1, 0, 0, 0, 0, 0, 0};
+        fl[g] = FastLin{0, 0, 0, 0, 0, 0};
+        if (j_ok) {
+            corr[g] = a.lc.corr[g * a.H + j];
+            rs[g] = a.lc.rs[g * a.H + j];
+            fl[g] = a.lc.fl[g * a.H + j];
+        }
+        fast = fast && fl[g].mq != 0;
+    }
+    __syncthreads();
+
+    const size_t BH = (size_t)a.B * a.H;
+    const IhT *ihp = reinterpret_cast<const IhT *>(a.ih);
+    const uint32_t tab = (uint32_t)__cvta_generic_to_shared(tables);
+    const bool worker = qd == 0 && j_ok;
+    // W*x + bw of this row: loaded one step ahead, so the cell never waits for global memory
+    auto load_ih = [&](int s, int32_t (&v)[3]) {
+        const int t = a.reverse ? (a.T - 1 - s) : s;
+        const IhT *src = ihp + ((size_t)t * a.B + b) * a.C + j;
+        v[0] = (int32_t)src[0];
+        v[1] = (int32_t)src[a.H];
+        v[2] = (int32_t)src[2 * a.H];
+    };
+    int32_t ihv[3] = {0, 0, 0};
+    if (worker) load_ih(0, ihv);
+    for (int s = 0; s < a.T; ++s) {
+        const long long out_slot = a.reverse ? (a.T - 1 - s) : (s + 1);
+        const unsigned char *h_cur = hs + (size_t)(s & 1) * Hs;
+        unsigned char *h_nxt = hs + (size_t)((s + 1) & 1) * Hs;
+        int32_t ihn[3] = {0, 0, 0};
+        if (worker && s + 1 < a.T) load_ih(s + 1, ihn);
+        int acc[3] = {0, 0, 0};
+        const uint4 *hq4 = reinterpret_cast<const uint4 *>(h_cur + qd * Qs);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            if (c >= nch) break;
+            const uint4 hv = hq4[c];
+#pragma unroll
+            for (int g = 0; g < 3; ++g) {
+                const uint4 w = Rq[(size_t)(c * 3 + g) * NT + tid];
+                acc[g] = dp4a_w<HUnsigned>((int)w.x, hv.x, acc[g]);
+                acc[g] = dp4a_w<HUnsigned>((int)w.y, hv.y, acc[g]);
+                acc[g] = dp4a_w<HUnsigned>((int)w.z, hv.z, acc[g]);
+                acc[g] = dp4a_w<HUnsigned>((int)w.w, hv.w, acc[g]);
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < 3; ++g) {
+            acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 1);
+            acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 2);
+        }
+        if (worker) {
+            const unsigned char hb = h_cur[j_at];
+            const int32_t h_old = HUnsigned ? (int32_t)hb : (int32_t)(int8_t)hb;
+            int32_t hn;
+            if constexpr (Cell == 2) {
+                const int32_t z_d = fused_gate_fast(gc, tab, ACT_Z, ihv[0], lin_round(acc[0], fl[0]));
+                const int32_t r_d = fused_gate_fast(gc, tab, ACT_R, ihv[1], lin_round(acc[1], fl[1]));
+                hn = fused_finish_fast(gc, tab, ihv[2], lin_round(acc[2], fl[2]), z_d, r_d, h_old);
+            } else {
+                int32_t hh[3];
+#pragma unroll
+                for (int g = 0; g < 3; ++g) {
+                    if (fast) hh[g] = linear_epilogue_fast(acc[g], fl[g], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                    else hh[g] = linear_epilogue(acc[g], corr[g], rs[g], a.lc.zp_out, a.lc.lo, a.lc.hi);
+                }
+                hn = gru_cell<Cell == 1>(gc, tables, ihv[0], ihv[1], ihv[2], hh[0], hh[1], hh[2], h_old);
+            }
+            h_nxt[j_at] = (unsigned char)hn;
+            const size_t o = (size_t)out_slot * BH + (size_t)b * a.H + j;
+            if (a.hq_out) a.hq_out[o] = hn;
+            if (a.hf_out) a.hf_out[o] = (float)(hn - gc.zp_h) * gc.h_scale;
+        }
+        ihv[0] = ihn[0];
+        ihv[1] = ihn[1];
+        ihv[2] = ihn[2];
+        __syncthreads();
+    }
+}
+
 // --------------------------------------------- generic fallback (any bit width, int32 data)
 
 // out[n][m] = epilogue( sum_k W_q[k][m] * in[n][k] ) with 64-bit accumulation
