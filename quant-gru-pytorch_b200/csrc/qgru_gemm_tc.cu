@@ -162,15 +162,33 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
         constexpr int COLS = GN / (EPI_WARPS / 4);
         long long local = 0;
         bool ok = true;
+        // per-channel constants of a tile's rows: loaded one tile ahead, so that their global-memory
+        // latency is not paid at the start of every tile
+        struct ChanConsts {
+            int64_t corr;
+            Rescale rs;
+            FastLin fl;
+        };
+        auto load_consts = [&](long long tile) {
+            ChanConsts c;
+            const int m = (int)(tile % m_tiles) * GM + q * 32 + lane;
+            const bool m_ok = tile < total && m < C;
+            c.corr = m_ok ? lc.corr[m] : 0;
+            c.rs = m_ok ? lc.rs[m] : Rescale{1, 1, 0, 0, 0, 0, 0, 0};
+            c.fl = m_ok ? lc.fl[m] : FastLin{0, 0, 0, 0, 0, 0};
+            return c;
+        };
+        ChanConsts cur = load_consts(blockIdx.x);
         for (long long tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++local) {
             const int m0 = (int)(tile % m_tiles) * GM;
             const long long n0 = (tile / m_tiles) * GN;
             const int buf = (int)(local & 1);
             const int m = m0 + q * 32 + lane;
             const bool m_ok = m < C;
-            const int64_t corr = m_ok ? lc.corr[m] : 0;
-            const Rescale rs = m_ok ? lc.rs[m] : Rescale{1, 1, 0, 0, 0, 0, 0, 0};
-            const FastLin fl = m_ok ? lc.fl[m] : FastLin{0, 0, 0, 0, 0, 0};
+            const ChanConsts nxt = load_consts(tile + gridDim.x);
+            const int64_t corr = cur.corr;
+            const Rescale rs = cur.rs;
+            const FastLin fl = cur.fl;
             // fused-cell mode: the channel's gate decides the second rescale (to its input scale)
             const int gate = (ps.enabled && m_ok) ? m / ps.H : 0;
             const Rescale pre_rs = ps.to[gate];
@@ -180,15 +198,19 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             if (!ok) break;
             tc::tc_fence_after_sync();
             IhT *out = ih + m;
-            for (int c0 = part * COLS; c0 < (part + 1) * COLS; c0 += 16) {
-                int32_t v[16];
-                tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * GN + c0), v);
-                tc::tmem_ld_wait();
-                if (c0 + 16 >= (part + 1) * COLS) {
-                    // this warp has read its last accumulator columns: hand the buffer back
-                    tc::tc_fence_before_sync();
-                    if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
-                }
+            // this warp's COLS accumulator columns: both halves are fetched before anything is
+            // computed, and the buffer goes back to the MMA warp as soon as they have arrived
+            static_assert(COLS == 32, "two 16-column loads per warp and tile");
+            int32_t vv[2][16];
+            tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * GN + part * COLS), vv[0]);
+            tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * GN + part * COLS + 16), vv[1]);
+            tc::tmem_ld_wait();
+            tc::tc_fence_before_sync();
+            if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int c0 = part * COLS + 16 * half;
+                const int32_t (&v)[16] = vv[half];
                 int32_t y[16];
                 if constexpr (Fast) {
                     // all 16 values first, stores afterwards: the chains interleave
@@ -229,6 +251,7 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                         if (n0 + c0 + i < N) *po = (IhT)y[i];
                 }
             }
+            cur = nxt;
         }
         if (!ok && lane == 0) atomicExch(failed, 1);
     }

@@ -590,7 +590,12 @@ bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_tab
     // shared-memory slots; the slots also stage the tensor-memory tiles, up to 12 per pass.
     for (;; NB -= 16) {
         const int acc_cols = (3 * MT * NB + 31) / 32 * 32;
-        const int tmem_tiles = r_where == 1 ? 0 : std::max(0, std::min(n_tiles, (512 - acc_cols) / 32));
+        int tmem_tiles = r_where == 1 ? 0 : std::max(0, std::min(n_tiles, (512 - acc_cols) / 32));
+        // a slice that does not fit tensor memory as a whole but fits shared memory stays there as
+        // a whole: the split form needs a slower, rolled MMA issue loop
+        if (tmem_tiles < n_tiles && r_where != 2 &&
+            cluster_smem_layout(n_tiles, KBn, NB, n_table).total + 1024 <= (size_t)smem_optin)
+            tmem_tiles = 0;
         const int resident = n_tiles - tmem_tiles;
         for (int stage = std::min(std::max(tmem_tiles, 1), 12); stage >= 1; --stage) {
             const int r_slots = std::max(resident, stage);
