@@ -132,7 +132,7 @@ void qgru_destroy(qgru_handle *h) {
     if (h->h_flags) cudaFreeHost(h->h_flags);
     cudaFree(h->d_bar);
     for (DevBuf *b : {&h->x8, &h->ih, &h->h8, &h->x32, &h->ih32, &h->hh32, &h->hq32, &h->stage_in,
-                      &h->stage_h0, &h->stage_out, &h->f_wx, &h->f_h, &h->f_v, &h->f_acc})
+                      &h->stage_h0, &h->stage_out, &h->f_wx, &h->f_h, &h->f_v, &h->f_acc, &h->f_acc2})
         cudaFree(b->p);
     cudaGetLastError();
     delete h;

@@ -95,22 +95,15 @@ k_sgemm_xw(const float *__restrict__ x, const float *__restrict__ W, float *__re
     }
 }
 
-// ---- one timestep: R*h for (b, j) and the float gates of src/gru_forward_gpu.cu:23-125.
-// blockDim = (128 hidden units, 2 batch rows); h_{t-1} rows are staged in shared memory.
+// ---- one timestep after R*h has been multiplied (k_sgemm_xw on h_{t-1}): the float gates of
+// src/gru_forward_gpu.cu:23-125 for (b, j).  rh [B][3H] holds R*h without its bias.
 template <bool Calib>
 __global__ void __launch_bounds__(256)
-k_float_step(const float *__restrict__ wx, const float *__restrict__ R, const float *__restrict__ bw,
+k_float_step(const float *__restrict__ wx, const float *__restrict__ rh, const float *__restrict__ bw,
              const float *__restrict__ br, const float *__restrict__ h_in, float *__restrict__ h_out,
              float *__restrict__ v, int v_stride, int B, int H, unsigned *acc_min, unsigned *acc_max) {
-    extern __shared__ float hs[];  // [2][H]
-    const int j = blockIdx.x * 128 + threadIdx.x;
-    const int b = blockIdx.y * 2 + threadIdx.y;
-    const int tid = threadIdx.y * 128 + threadIdx.x;
-    for (int i = tid; i < 2 * H; i += 256) {
-        const int bb = blockIdx.y * 2 + i / H;
-        hs[i] = bb < B ? h_in[(size_t)bb * H + i % H] : 0.f;
-    }
-    __syncthreads();
+    const int j = blockIdx.x * 128 + (threadIdx.x & 127);
+    const int b = blockIdx.y * 2 + (threadIdx.x >> 7);
     const bool ok = j < H && b < B;
     const int Cn = 3 * H;
     MinMax m_h, m_ih, m_hh, m_zin, m_rin, m_nin, m_z, m_r, m_n, m_rh, m_new, m_old;
@@ -119,15 +112,8 @@ k_float_step(const float *__restrict__ wx, const float *__restrict__ R, const fl
         m_z.init(); m_r.init(); m_n.init(); m_rh.init(); m_new.init(); m_old.init();
     }
     if (ok) {
-        const float *hrow = hs + threadIdx.y * H;
-        float az = 0.f, ar = 0.f, an = 0.f;
-        for (int k = 0; k < H; ++k) {
-            const float hv = hrow[k];
-            const float *rr = R + (size_t)k * Cn + j;
-            az = fmaf(rr[0], hv, az);
-            ar = fmaf(rr[H], hv, ar);
-            an = fmaf(rr[2 * H], hv, an);
-        }
+        const float *rhr = rh + (size_t)b * Cn + j;
+        const float az = rhr[0], ar = rhr[H], an = rhr[2 * H];
         const float *wxr = wx + (size_t)b * Cn + j;
         const float wz = wxr[0] + bw[j], rz = az + br[j];
         const float z_pre = wz + rz;
@@ -138,7 +124,7 @@ k_float_step(const float *__restrict__ wx, const float *__restrict__ R, const fl
         const float wg = wxr[2 * H] + bw[2 * H + j], rg = an + br[2 * H + j];
         const float g_pre = wg + r * rg;
         const float g = tanhf(g_pre);
-        const float h_old = hrow[j];
+        const float h_old = h_in[(size_t)b * H + j];
         const float old_c = z * h_old;
         const float new_c = (1.0f - z) * g;
         const float hn = old_c + new_c;
@@ -231,21 +217,21 @@ int float_forward(qgru_handle *h, int T, int B, const float *W, const float *R, 
     dim3 gg((unsigned)((N + 63) / 64), (unsigned)((Cn + 63) / 64));
     k_sgemm_xw<<<gg, 256, 0, st>>>(x, W, wx, N, I, Cn);
     h->launches += 2;
-    dim3 blk(128, 2), grid((H + 127) / 128, (B + 1) / 2);
-    const size_t smem = (size_t)2 * H * 4;
-    if (smem > 48 * 1024) {
-        CK(cudaFuncSetAttribute(k_float_step<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        CK(cudaFuncSetAttribute(k_float_step<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    }
+    // per step: R*h as a tiled fp32 GEMM ([B][H] x [H][3H], the kernel of the input projection),
+    // then the pointwise gates
+    if ((rc = ensure(h, h->f_acc2, (size_t)B * Cn * 4))) return rc;
+    float *rh = (float *)h->f_acc2.p;
+    dim3 grid((H + 127) / 128, (B + 1) / 2), gr((unsigned)((B + 63) / 64), (unsigned)((Cn + 63) / 64));
     for (int t = 0; t < T; ++t) {
         const float *hin = h_out + (size_t)t * NH;
         float *hout = h_out + (size_t)(t + 1) * NH;
         float *vt = v_out ? v_out + (size_t)t * B * v_stride * H : nullptr;
+        k_sgemm_xw<<<gr, 256, 0, st>>>(hin, R, rh, B, H, Cn);
         if (acc_min)
-            k_float_step<true><<<grid, blk, smem, st>>>(wx + (size_t)t * B * Cn, R, bw, br, hin, hout, vt, v_stride, B, H, acc_min, acc_max);
+            k_float_step<true><<<grid, 256, 0, st>>>(wx + (size_t)t * B * Cn, rh, bw, br, hin, hout, vt, v_stride, B, H, acc_min, acc_max);
         else
-            k_float_step<false><<<grid, blk, smem, st>>>(wx + (size_t)t * B * Cn, R, bw, br, hin, hout, vt, v_stride, B, H, nullptr, nullptr);
-        h->launches++;
+            k_float_step<false><<<grid, 256, 0, st>>>(wx + (size_t)t * B * Cn, rh, bw, br, hin, hout, vt, v_stride, B, H, nullptr, nullptr);
+        h->launches += 2;
     }
     CK(cudaGetLastError());
     return QGRU_OK;

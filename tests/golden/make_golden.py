@@ -63,5 +63,54 @@ def main():
         print(name, "h_q", h_q.shape, "unique", len(np.unique(h_q)))
 
 
+HIST_OPS = [(8, 0, 1), (8, 0, 0), (8, 1, 0), (8, 1, 1), (16, 0, 0), (4, 0, 1), (12, 0, 1)]  # bits, unsigned, symmetric
+
+
+def hist_inputs(seed):
+    """Seeded 2048-bin histograms of five value distributions (the ones the GRU's operators show)."""
+    rng = np.random.default_rng(seed)
+    out = []
+    for kind in ("normal", "sigmoid", "outliers", "positive", "sparse"):
+        if kind == "normal":
+            data = rng.normal(0.1, 1.3, 40000)
+        elif kind == "sigmoid":
+            data = 1 / (1 + np.exp(-rng.normal(0, 3, 40000)))
+        elif kind == "outliers":
+            data = rng.normal(0, 1, 40000)
+            data[rng.integers(0, data.size, 400)] *= 8
+        elif kind == "positive":
+            data = np.abs(rng.normal(0, 0.4, 40000))
+        else:
+            data = rng.normal(0, 0.05, 256)
+        data = data.astype(np.float32)
+        mn, mx = float(data.min()), float(data.max())
+        counts, _ = np.histogram(data, bins=2048, range=(mn, mx))
+        out.append((counts.astype(np.float32), mn, mx, int(data.size)))
+    return out
+
+
+def main_hist():
+    """Percentile / SQNR parameters of the reference's host code for seeded histograms:
+    golden/hist/hist_calibration.npz (inputs are regenerated from the seed by the test)."""
+    ref = Reference()
+
+    class Op:
+        pass
+    rows = []
+    for h_idx, (counts, mn, mx, total) in enumerate(hist_inputs(77)):
+        for o_idx, (bits, uns, sym) in enumerate(HIST_OPS):
+            op = Op()
+            op.bits, op.is_unsigned, op.symmetric = bits, uns, sym
+            for pot2 in (0, 1):
+                for method, pct in ((1, 99.9), (1, 99.99), (0, 0.0)):
+                    r = ref.calibrate_from_histogram(counts, mn, mx, total, op, pot2, method, pct or 99.99)
+                    rows.append([h_idx, o_idx, pot2, method, pct, np.float32(r[0]).view(np.uint32), r[1]])
+    os.makedirs(os.path.join(HERE, "hist"), exist_ok=True)
+    np.savez_compressed(os.path.join(HERE, "hist", "hist_calibration.npz"),
+                        rows=np.array(rows, dtype=np.float64), seed=np.array(77))
+    print("hist_calibration", len(rows), "rows")
+
+
 if __name__ == "__main__":
     main()
+    main_hist()

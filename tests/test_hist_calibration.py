@@ -116,3 +116,30 @@ def test_oracle_collector_degenerate_inputs(oracle):
     h2.collect(np.array([0.0, 1.0, np.inf, np.nan, -np.inf, 0.5], np.float32))
     counts, mn, mx, total = h2.get()
     assert (mn, mx) == (0.0, 1.0) and counts.sum() == 3 and total == 6
+
+
+def test_golden_histogram_params(oracle):
+    """Known answers from the compiled reference (tests/golden/hist/hist_calibration.npz, written by
+    tests/golden/make_golden.py): the oracle and the product's host function reproduce them on
+    machines without the reference tree."""
+    import importlib.util
+    import os
+    here = os.path.dirname(os.path.abspath(__file__))
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(here, "golden", "make_golden.py"))
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    d = np.load(os.path.join(here, "golden", "hist", "hist_calibration.npz"))
+    hists = mg.hist_inputs(int(d["seed"]))
+    lib = _cabi.lib()
+    assert len(d["rows"]) >= 200
+    for h_idx, o_idx, pot2, method, pct, scale_bits, zp in d["rows"]:
+        counts, mn, mx, total = hists[int(h_idx)]
+        bits, uns, sym = mg.HIST_OPS[int(o_idx)]
+        want = (float(np.uint32(scale_bits).view(np.float32)), int(zp))
+        got = oracle.calibrate_from_histogram(counts, mn, mx, total, _Op(bits, uns, sym), int(pot2), int(method),
+                                              pct or 99.99)
+        assert got == want, (h_idx, o_idx, pot2, method, pct, got, want)
+        o = _cabi.Op(0.0, 0, bits, uns, sym, 0)
+        rc = lib.qgru_calibrate_from_histogram(counts.ctypes.data_as(C.POINTER(C.c_float)), counts.size, mn, mx,
+                                               total, int(pot2), int(method), pct or 99.99, C.byref(o))
+        assert rc == 0 and (float(np.float32(o.scale)), int(o.zero_point)) == want
