@@ -166,6 +166,8 @@ def run_ours(args):
         hd = gru_ops.Handle(I, H, device=local)
         if len(me.directions) > 1:
             hd.set_option("sm_limit", sms // 2)
+        for kv in filter(None, os.environ.get("QGRU_OPTS", "").split(",")):   # tuning experiments
+            hd.set_option(*kv.split("=", 1))
         W, R, bw, br = [torch.from_numpy(a).to(dev) for a in weights[d]]
         ranges = params_mod.Ranges(H)
         hist = params_mod.Histograms(H, device=local) if method != "minmax" else None

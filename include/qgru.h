@@ -269,6 +269,7 @@ QGRU_API const char *qgru_describe_plan(qgru_handle *h, int T, int B);
  *   "cell"     auto | fused | generic       gate datapath: tabulated (auto also allows its
  *                                           shift-free form), or the reference's step by step
  *   "r_resident" auto | smem | tmem       where the cluster recurrence keeps its slice of R
+ *   "tiles_per_cta" 1 | 2                 cluster recurrence at 128 < H <= 256: 128-unit tiles per CTA
  *   "sm_limit" n   use at most n SMs (0 = all);  "spin_limit" n   bound of the group barrier
  * Unknown names or values return QGRU_ERR_BAD_ARG. */
 QGRU_API int qgru_set_option(qgru_handle *h, const char *name, const char *value);

@@ -167,6 +167,8 @@ int qgru_set_option(qgru_handle *h, const char *name, const char *value) {
         else if (v == "smem") h->opt_r_where = 1;
         else if (v == "tmem") h->opt_r_where = 2;
         else return fail(h, QGRU_ERR_BAD_ARG, "r_resident: auto|smem|tmem");
+    } else if (n == "tiles_per_cta") {
+        h->opt_mt = std::max(0, atoi(value));
     } else if (n == "cell") {
         if (v == "auto") h->opt_cell = 0;
         else if (v == "generic") h->opt_cell = 1;
@@ -597,7 +599,7 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
     // group; H <= 1024) or through global memory with a counter per group (H <= 512)
     RecMmaPlan cp;
     const bool cluster_ok = h->opt_rec != 1 && h->opt_exchange != 1 &&
-                            rec_cluster_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, h->opt_r_where, &cp);
+                            rec_cluster_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, h->opt_r_where, h->opt_mt, &cp);
     const bool global_ok = h->opt_rec != 1 && rec_mma_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, &mp);
     const bool mma_ok = cluster_ok || global_ok;
     if (h->opt_rec == 2 && !mma_ok)

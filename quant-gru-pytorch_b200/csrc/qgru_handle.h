@@ -40,6 +40,7 @@ struct qgru_handle {
     int opt_sm_limit = 0;  // 0: all SMs
     int opt_exchange = 0;  // 0 auto (cluster where it fits), 1 global counter, 2 cluster only
     int opt_cell = 0;      // 0 auto (fused cell where valid), 1 generic cell
+    int opt_mt = 0;                          // cluster recurrence: 2 = two 128-unit tiles per CTA where 128 < H <= 256
     int opt_r_where = 0;                     // cluster recurrence: 0 auto, 1 R in shared memory, 2 in tensor memory
     unsigned spin_limit = 1u << 24;
     long long *dbg_stamps = nullptr;  // profiling aid of the tensor-core recurrence kernel

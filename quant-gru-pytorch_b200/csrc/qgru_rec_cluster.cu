@@ -84,6 +84,36 @@ __host__ __device__ inline ClusterSmem cluster_smem_layout(int r_slots, int KBn,
 
 namespace {
 
+// MMA issue for wide hidden sizes (512 < H <= 1024): the tiles of a gate come partly from tensor
+// memory, partly from their shared-memory slots.  Rolled loops (the fully unrolled form of these
+// 96 MMAs measured slower) in a function of its own, so that its registers do not weigh on the
+// kernel's common path.
+__device__ __noinline__ void issue_wide(int MT, int KBn, int NB, int tmem_tiles, uint32_t tmem_base, uint32_t r_t0,
+                                        uint32_t r_lo0, uint32_t hb0, uint32_t desc_lo, uint64_t dhi, uint32_t idesc,
+                                        uint64_t *mma_done) {
+    for (int g = 0; g < 3; ++g) {
+        for (int mt = 0; mt < MT; ++mt) {
+            const uint32_t d = tmem_base + (uint32_t)((mt * 3 + g) * NB);
+            for (int kb = 0; kb < KBn; ++kb) {
+                const int tile = (mt * 3 + g) * KBn + kb;
+                const uint32_t bd = hb0 + (uint32_t)(kb * NB * 8);
+                if (tile < tmem_tiles) {
+                    const uint32_t ra = r_t0 + (uint32_t)(tile * 32);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks)
+                        tc::mma_i8_ts(d, ra + (uint32_t)(ks * 8), dhi | (bd + 2 * ks), idesc, (kb | ks) != 0);
+                } else {
+                    const uint32_t rb = desc_lo | (r_lo0 + (uint32_t)((tile - tmem_tiles) * 1024));
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks)
+                        tc::mma_i8(d, dhi | (rb + (uint32_t)(2 * ks)), dhi | (bd + 2 * ks), idesc, (kb | ks) != 0);
+                }
+            }
+        }
+        tc::mma_commit(&mma_done[g]);
+    }
+}
+
 // Cell variants: Fused = false: the generic datapath (Narrow picks its 32-bit rescales);
 // Fused = true: the tabulated cell, where Narrow = true selects the branch-free form that needs
 // every scale of the step in shift-free form and 32-bit linear sums.
@@ -251,31 +281,8 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         }
                     }
                 } else {
-                    // wide hidden sizes: the tiles of a gate come partly from tensor memory, partly
-                    // from their shared-memory slots
-                    // (rolled loops: the fully unrolled form of these 96 MMAs measured slower)
-                    const uint32_t hb0 = desc_lo | hbuf;
-                    for (int g = 0; g < 3; ++g) {
-                        for (int mt = 0; mt < MT; ++mt) {
-                            const uint32_t d = tmem_base + (uint32_t)((mt * 3 + g) * a.NB);
-                            for (int kb = 0; kb < KBn; ++kb) {
-                                const int tile = (mt * 3 + g) * KBn + kb;
-                                const uint32_t bd = hb0 + (uint32_t)(kb * a.NB * 8);
-                                if (tile < a.tmem_tiles) {
-                                    const uint32_t ra = r_t0 + (uint32_t)(tile * 32);
-#pragma unroll
-                                    for (int ks = 0; ks < 4; ++ks)
-                                        tc::mma_i8_ts(d, ra + (uint32_t)(ks * 8), dhi | (bd + 2 * ks), idesc, (kb | ks) != 0);
-                                } else {
-                                    const uint32_t rb = desc_lo | (r_lo0 + (uint32_t)((tile - a.tmem_tiles) * 1024));
-#pragma unroll
-                                    for (int ks = 0; ks < 4; ++ks)
-                                        tc::mma_i8(d, dhi | (rb + (uint32_t)(2 * ks)), dhi | (bd + 2 * ks), idesc, (kb | ks) != 0);
-                                }
-                            }
-                        }
-                        tc::mma_commit(&mma_done[g]);
-                    }
+                    issue_wide(MT, KBn, a.NB, a.tmem_tiles, tmem_base, r_t0, r_lo0, desc_lo | hbuf, desc_lo, dhi, idesc,
+                               mma_done);
                 }
                 if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 3] = clock64();
             }
@@ -574,10 +581,13 @@ cudaError_t launch_any(bool fused, bool narrow, int ih_bytes, int MT, const CUte
 }  // namespace
 
 bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, int r_where,
-                      RecMmaPlan *out) {
+                      int mt_opt, RecMmaPlan *out) {
     if (Hpad > 1024) return false;                 // K-slab loops are unrolled to 8
     const int KBn = Hpad / 128;
-    const int MT = (H > 128 && H <= 256) ? 2 : 1;
+    // One 128-unit tile per CTA.  Two tiles per CTA for 128 < H <= 256 (one CTA per group, no
+    // exchange) exist as an option (mt_opt 2) but measured 2.4x slower per step: twice the
+    // epilogue per thread under the same register limit.
+    const int MT = (mt_opt == 2 && H > 128 && H <= 256) ? 2 : 1;
     const int P = (H + 128 * MT - 1) / (128 * MT);  // cluster size: 1..8 (the portable maximum)
     if (P > 8 || P > sms) return false;
     const int groups_max = std::max(1, sms / P);

@@ -63,7 +63,7 @@ int rec_mma_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const Gat
 // The same kernel with the P CTAs of a group as one thread-block cluster exchanging h_t through
 // distributed shared memory (qgru_rec_cluster.cu).  Same plan fields; no cooperative launch.
 bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, int r_where,
-                      RecMmaPlan *out);
+                      int mt_opt, RecMmaPlan *out);
 
 int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const GateConsts &gc_host,
                        const int8_t *r8, long long r_rows_alloc, long long h_rows_alloc, bool h_unsigned,

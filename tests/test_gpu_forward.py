@@ -104,6 +104,15 @@ def test_simt_gemm_and_wide_hidden(oracle, cuda_device):
         _run(huge, cuda_device, opts=(("rec", "mma"),))
 
 
+def test_two_tiles_per_cta_option(oracle, cuda_device):
+    """128 < H <= 256 with both 128-unit tiles in one CTA (no exchange): kept as an option."""
+    case = make_case(16, 5, 37, 24, 200, oracle, config_named("cfg2"))
+    got, plan, _ = _run(case, cuda_device, opts=(("rec", "mma"), ("tiles_per_cta", "2")))
+    assert "MT=2" in plan and "P=1" in plan and np.array_equal(got, _want(oracle, case)), plan
+    got, plan, _ = _run(case, cuda_device, opts=(("rec", "mma"),))
+    assert "MT=1" in plan and "P=2" in plan and np.array_equal(got, _want(oracle, case)), plan
+
+
 def test_large_batch_many_groups(oracle, cuda_device):
     """More batch rows than one wave of groups holds at H = 512: consecutive launches."""
     case = make_case(14, 3, 700, 32, 384, oracle, config_named("default"), calib_batches=1)
@@ -222,3 +231,33 @@ def test_argument_errors(oracle, cuda_device):
         p = importlib.import_module(PKG_NAME + ".params").GRUQuantParams(16, bad_cfg)
         with gru_ops.Handle(8, 16, device=0) as hd:
             hd.set_params(p)
+
+
+def test_forward_is_capturable_into_a_cuda_graph(oracle, cuda_device):
+    """After one warm-up call (workspace allocation, tensor maps) a forward only enqueues work on
+    the caller's stream, so it can be captured into a CUDA graph and replayed on new inputs -
+    the way a streaming caller removes the per-call launch overhead."""
+    import torch
+    case = make_case(41, 6, 5, 24, 48, oracle, config_named("cfg2"))
+    want = _want(oracle, case)
+    with gru_ops.Handle(case.I, case.H, device=0) as hd:
+        hd.set_params(case.params)
+        hd.set_weights_i32(*[_t(a, cuda_device) for a in case.wq])
+        x_static = torch.zeros((case.T, case.B, case.I), dtype=torch.int32, device=cuda_device)
+        out_static = torch.zeros((case.T + 1, case.B, case.H), dtype=torch.int32, device=cuda_device)
+        side = torch.cuda.Stream(device=cuda_device)
+        side.wait_stream(torch.cuda.current_stream(cuda_device))
+        with torch.cuda.stream(side):
+            hd.forward_i32(x_static, None, out=out_static, sync=False)      # warm-up: allocations happen here
+        torch.cuda.current_stream(cuda_device).wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            hd.forward_i32(x_static, None, out=out_static, sync=False)
+        for _ in range(2):
+            x_static.copy_(_t(case.x_q, cuda_device))
+            graph.replay()
+            torch.cuda.synchronize()
+            assert np.array_equal(out_static.cpu().numpy(), want)
+            out_static.zero_()
+            x_static.zero_()
