@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2]
 
 One "step" is one forward pass of the workload over one batch of seeded synthetic input.
-The default workload is configuration 2 of BASELINE.json: bidirectional GRU, input 256,
+The default workload is the reference's bidirectional headline configuration: input 256,
 hidden 512, batch 256 per GPU-unit, 200 timesteps; 8-bit per-channel symmetric weights, 8-bit
 asymmetric activations, 16-bit gate outputs, MinMax calibration on 16 seeded batches.
 
@@ -40,7 +40,7 @@ WORKLOADS = {
     "cfg4": (1024, 1024, 64, 1000, False, "sym8_tensor", "normal", 4),
     "cfg5": (80, 256, 1, 16000, False, "cfg5", "ar1", 4),
 }
-# calibration method of each workload as BASELINE.json names it: (method, percentile)
+# calibration method of each workload configuration: (method, percentile)
 CALIBRATION = {"cfg1": ("minmax", 0.0), "cfg2": ("minmax", 0.0), "cfg3": ("percentile", 99.9),
                "cfg4": ("sqnr", 0.0), "cfg5": ("minmax", 0.0)}
 

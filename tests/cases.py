@@ -94,7 +94,7 @@ def make_case(seed, T, B, I, H, checker, config=None, dist="normal", sigma=1.0, 
 
 
 def config_named(name):
-    """Bit-width configurations used across the tests (BASELINE configs and variations)."""
+    """Bit-width configurations used across the tests (the benchmark configurations and variations)."""
     c = params_mod.OperatorQuantConfig()
     acts = [n for n in _cabi.OPS if n not in params_mod.WEIGHT_OPS]
     if name == "default":

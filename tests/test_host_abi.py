@@ -151,7 +151,8 @@ def test_bitwidth_json_round_trip(tmp_path):
 
 
 def test_reference_shipped_bitwidth_json_loads():
-    path = "/root/reference/pytorch/config/gru_quant_bitwidth_config.json"
+    from oracle.binding import REF_ROOT
+    path = os.path.join(REF_ROOT, "pytorch", "config", "gru_quant_bitwidth_config.json")
     if not os.path.exists(path):
         pytest.skip("reference tree not present")
     cfg = params_mod.OperatorQuantConfig.from_json(path)
