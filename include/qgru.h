@@ -205,6 +205,16 @@ QGRU_API int qgru_get_weights_i32(qgru_handle *h, int32_t *W_q, int32_t *R_q, in
 QGRU_API int qgru_forward_i32(qgru_handle *h, int T, int B, const int32_t *x_q,
                               const int32_t *h0_q, int32_t *h_q, unsigned flags, void *stream);
 
+/* quantGRUForwardInt32 with is_training = true and v_q given (src/gru_interface.cc:551-603;
+ * buffer written at src/gru_forward_gpu_quant.cu:318-330, src/gru_forward_cpu_quant.cc:199-205):
+ * the same h_q plus v_q [T,B,4H] int32 device out = quantized update, reset and new gate outputs
+ * and the R*h + br row of the new gate, per timestep of x (with QGRU_FLAG_REVERSE, slot t of
+ * v_q belongs to x_q[t]).  Runs on the step-by-step int32 kernels, which keep those
+ * intermediates; the clamp masks of the reference's training mode are not produced. */
+QGRU_API int qgru_forward_i32_train(qgru_handle *h, int T, int B, const int32_t *x_q,
+                                    const int32_t *h0_q, int32_t *h_q, int32_t *v_q,
+                                    unsigned flags, void *stream);
+
 /* quantGRUForwardInt (src/gru_interface.cc:610-725), inference mode: float in, float out.
  *   x [T,B,I] f32 device, h0 [B,H] f32 device or NULL, h [(T+1),B,H] f32 device out,
  *   x_q_out [T,B,I] int32 device or NULL. */

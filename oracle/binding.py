@@ -145,6 +145,18 @@ class _Checker:
             raise RuntimeError("forward_i32 failed")
         return h
 
+    def forward_i32_v(self, T, B, I, H, wq, x_q, h0_q, params, sc):
+        """Training-mode forward: (h_q [(T+1),B,H], v_q [T,B,4H])."""
+        x_q = np.ascontiguousarray(x_q, np.int32)
+        h = np.zeros((T + 1, B, H), np.int32)
+        v = np.zeros((T, B, 4 * H), np.int32)
+        h0p = _i(np.ascontiguousarray(h0_q, np.int32)) if h0_q is not None else None
+        rc = self._fn("forward_i32_v")(T, B, I, H, *[_i(np.ascontiguousarray(w, np.int32)) for w in wq], _i(x_q),
+                                       h0p, C.byref(params), *[_f(s) for s in sc], _i(h), _i(v))
+        if rc:
+            raise RuntimeError("forward_i32_v failed")
+        return h, v
+
     def forward_f32(self, T, B, I, H, wq, x, h0, params, sc):
         x = np.ascontiguousarray(x, np.float32)
         h = np.zeros((T + 1, B, H), np.float32)

@@ -624,10 +624,34 @@ static void linear(int N, int K, int C, const int32_t *Wt, const int32_t *in, co
 
 /* ForwardPassQuantCPU::RunImpl + the h_q[0] initialisation of quantGRUForwardCPU,
  * src/gru_forward_cpu_quant.cc:302-325 and src/gru_interface.cc:815-824. */
+static int forward_i32_impl(int T, int B, int I, int H, const int32_t *W, const int32_t *R,
+                            const int32_t *bw, const int32_t *br, const int32_t *x_q,
+                            const int32_t *h0_q, const qgru_params *p, const float *sW,
+                            const float *sR, const float *sbw, const float *sbr, int32_t *h_q,
+                            int32_t *v_q);
+
 ORC_API int orc_forward_i32(int T, int B, int I, int H, const int32_t *W, const int32_t *R,
                             const int32_t *bw, const int32_t *br, const int32_t *x_q,
                             const int32_t *h0_q, const qgru_params *p, const float *sW,
                             const float *sR, const float *sbw, const float *sbr, int32_t *h_q) {
+    return forward_i32_impl(T, B, I, H, W, R, bw, br, x_q, h0_q, p, sW, sR, sbw, sbr, h_q, NULL);
+}
+
+/* Training-mode forward: also v_q [T,B,4H] = (update, reset, new gate outputs, R*h + br row of
+ * the new gate), src/gru_forward_cpu_quant.cc:199-205. */
+ORC_API int orc_forward_i32_v(int T, int B, int I, int H, const int32_t *W, const int32_t *R,
+                              const int32_t *bw, const int32_t *br, const int32_t *x_q,
+                              const int32_t *h0_q, const qgru_params *p, const float *sW,
+                              const float *sR, const float *sbw, const float *sbr, int32_t *h_q,
+                              int32_t *v_q) {
+    return forward_i32_impl(T, B, I, H, W, R, bw, br, x_q, h0_q, p, sW, sR, sbw, sbr, h_q, v_q);
+}
+
+static int forward_i32_impl(int T, int B, int I, int H, const int32_t *W, const int32_t *R,
+                            const int32_t *bw, const int32_t *br, const int32_t *x_q,
+                            const int32_t *h0_q, const qgru_params *p, const float *sW,
+                            const float *sR, const float *sbw, const float *sbr, int32_t *h_q,
+                            int32_t *v_q) {
     if (p->hidden != H) return 1;
     orc_derived d;
     if (derive(p, sW, sR, sbw, sbr, &d)) return 1;
@@ -654,6 +678,13 @@ ORC_API int orc_forward_i32(int T, int B, int I, int H, const int32_t *W, const 
                                                QGRU_OP_RESET_IN, QGRU_OP_RESET_OUT, QGRU_LUT_RESET);
                 const int32_t n = new_gate(iht[w + 2 * H], hh[w + 2 * H], r, p, &d);
                 h_out[(size_t)b * H + j] = hidden_state(u, n, h_in[(size_t)b * H + j], p, &d);
+                if (v_q) {
+                    int32_t *vb = v_q + ((size_t)t * B + b) * 4 * H + j;
+                    vb[0] = u;
+                    vb[H] = r;
+                    vb[2 * H] = n;
+                    vb[3 * H] = hh[w + 2 * H];
+                }
             }
         }
     }

@@ -293,6 +293,22 @@ int ref_forward_i32(int T, int B, int I, int H, const int32_t *W, const int32_t 
 // Same result as ref_forward_i32, computed on `nthreads` host threads by cutting the batch
 // into independent slices (rows of a batch never interact in a GRU).  Used as the
 // all-cores CPU baseline; the reference itself is single threaded.
+// Training-mode forward of the CPU path: also returns v_q [T,B,4H] = (update, reset, new gate
+// outputs, R*h + br row of the new gate), src/gru_forward_cpu_quant.cc:199-205.
+int ref_forward_i32_v(int T, int B, int I, int H, const int32_t *W, const int32_t *R,
+                      const int32_t *bw, const int32_t *br, const int32_t *x_q, const int32_t *h0_q,
+                      const qgru_params *p, const float *sW, const float *sR, const float *sbw,
+                      const float *sbr, int32_t *h_q, int32_t *v_q) {
+    return guarded([&] {
+        GRUQuantParams q = fromPod(*p, sW, sR, sbw, sbr);
+        const int NH = B * H;
+        for (int i = 0; i < NH; ++i) h_q[i] = h0_q ? h0_q[i] : q.h_.zero_point;
+        cpu::ForwardPassQuantCPU fwd(true, B, I, H);
+        fwd.setRescaleParam(q);
+        fwd.Run(T, W, R, bw, br, x_q, h_q, v_q, 0.0f, nullptr);
+    });
+}
+
 int ref_forward_i32_mt(int T, int B, int I, int H, const int32_t *W, const int32_t *R,
                        const int32_t *bw, const int32_t *br, const int32_t *x_q,
                        const int32_t *h0_q, const qgru_params *p, const float *sW,

@@ -758,7 +758,7 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
 }
 
 // Generic path: int32 operands, 64-bit accumulation, one launch pair per step.
-int run_generic(qgru_handle *h, int T, int B, const int32_t *x32, int32_t *hq, unsigned flags,
+int run_generic(qgru_handle *h, int T, int B, const int32_t *x32, int32_t *hq, int32_t *vq, unsigned flags,
                 cudaStream_t st) {
     const long long N = (long long)T * B;
     const int C = h->C, H = h->H;
@@ -784,7 +784,8 @@ int run_generic(qgru_handle *h, int T, int B, const int32_t *x32, int32_t *hq, u
         dim3 g2((H + 127) / 128, B);
         k_gates_generic<<<g2, 128, 0, st>>>((const int32_t *)h->ih32.p + (size_t)t * B * C,
                                             (const int32_t *)h->hh32.p, hq + in_slot * BH,
-                                            hq + out_slot * BH, B, H, h->d_gc, h->d_tables);
+                                            hq + out_slot * BH, vq ? vq + (size_t)t * B * 4 * H : nullptr, B, H,
+                                            h->d_gc, h->d_tables);
         h->launches += 2;
     }
     CK(cudaGetLastError());
@@ -824,7 +825,7 @@ int qgru_forward_i32(qgru_handle *h, int T, int B, const int32_t *x_q, const int
             h0_q, nullptr, nullptr, h_q, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale, ho.zero_point,
             op_qmin(ho), op_qmax(ho), h->d_flags);
         h->launches++;
-        return run_generic(h, T, B, x_q, h_q, flags, st);
+        return run_generic(h, T, B, x_q, h_q, nullptr, flags, st);
     }
     if ((rc = ensure(h, h->x8, (size_t)((N + 127) / 128 * 128) * h->Ipad))) return rc;
     if ((rc = ensure(h, h->h8, (size_t)(2 * B + 256) * h->Hpad))) return rc;
@@ -837,6 +838,27 @@ int qgru_forward_i32(qgru_handle *h, int T, int B, const int32_t *x_q, const int
     h->launches += 2;
     CK(cudaGetLastError());
     return run_fast(h, T, B, h_q, nullptr, flags, st);
+}
+
+int qgru_forward_i32_train(qgru_handle *h, int T, int B, const int32_t *x_q, const int32_t *h0_q,
+                           int32_t *h_q, int32_t *v_q, unsigned flags, void *stream) {
+    if (!h || !x_q || !h_q || !v_q) return QGRU_ERR_BAD_ARG;
+    int rc = check_forward_args(h, T, B);
+    if (rc) return rc;
+    CK(cudaSetDevice(h->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const qgru_op &ho = h->p.op[QGRU_OP_H];
+    const long long init_slot = (flags & QGRU_FLAG_REVERSE) ? T : 0;
+    h->ev = h->ring[h->calls % qgru_handle::kRing];
+    h->calls++;
+    CK(cudaEventRecord(h->ev[0], st));
+    CK(cudaMemsetAsync(h->d_flags, 0, 2 * sizeof(int), st));
+    // the step-by-step kernels keep every intermediate the training buffer wants
+    k_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
+        h0_q, nullptr, nullptr, h_q, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale, ho.zero_point,
+        op_qmin(ho), op_qmax(ho), h->d_flags);
+    h->launches++;
+    return run_generic(h, T, B, x_q, h_q, v_q, flags, st);
 }
 
 int qgru_forward_f32(qgru_handle *h, int T, int B, const float *x, const float *h0, float *h_out,
@@ -867,7 +889,7 @@ int qgru_forward_f32(qgru_handle *h, int T, int B, const float *x, const float *
             nullptr, h0, nullptr, (int32_t *)h->hq32.p, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale,
             ho.zero_point, op_qmin(ho), op_qmax(ho), h->d_flags);
         h->launches += 2;
-        if ((rc = run_generic(h, T, B, x32, (int32_t *)h->hq32.p, flags, st))) return rc;
+        if ((rc = run_generic(h, T, B, x32, (int32_t *)h->hq32.p, nullptr, flags, st))) return rc;
         k_dequantize<<<grid_for((long long)nh, 256, h->sm_count), 256, 0, st>>>(
             (const int32_t *)h->hq32.p, h_out, (long long)nh, h->h_scale, ho.zero_point);
         h->launches++;

@@ -51,11 +51,13 @@ __device__ __forceinline__ int32_t rescale_diff(int32_t v, int32_t zp, Rescale r
 // computeUpdateGate / computeResetGate / computeNewGate / computeHiddenState, inference
 // branch (include/quantize_ops_helper.h:749-1084).  ih_* and hh_* are the clamped outputs of
 // the two fused linear layers; h_old is the quantized previous state.
+// gates: optional [3] out, the quantized update, reset and new gate outputs (the reference's
+// training buffer v, src/gru_forward_gpu_quant.cu:318-330).
 template <bool Narrow>
 __device__ __forceinline__ int32_t gru_cell(const GateConsts &gc, const int32_t *tables,
                                             int32_t ih_z, int32_t ih_r, int32_t ih_n,
                                             int32_t hh_z, int32_t hh_r, int32_t hh_n,
-                                            int32_t h_old) {
+                                            int32_t h_old, int32_t *gates = nullptr) {
     const int32_t z_pre = rescale_diff<Narrow>(ih_z, gc.zp_ih, gc.ih_to[ACT_Z]) +
                           rescale_diff<Narrow>(hh_z, gc.zp_hh, gc.hh_to[ACT_Z]) + gc.zp_in[ACT_Z];
     const int32_t z = activation(gc, tables, ACT_Z, z_pre);
@@ -74,6 +76,11 @@ __device__ __forceinline__ int32_t gru_cell(const GateConsts &gc, const int32_t 
     const int64_t one_minus = ((int64_t)gc.one_q - z) - gc.zp_out[ACT_Z];
     const int64_t new_c = one_minus * ((int64_t)n_h - gc.zp_h);
     const int32_t h_new = (int32_t)rescale64(old_c + new_c, gc.uh_to_h) + gc.zp_h;
+    if (gates) {
+        gates[0] = z;
+        gates[1] = r;
+        gates[2] = n;
+    }
     return clampi(h_new, gc.h_lo, gc.h_hi);
 }
 

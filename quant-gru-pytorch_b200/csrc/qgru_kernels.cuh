@@ -548,16 +548,26 @@ __global__ void k_linear_generic(const int32_t *__restrict__ wq, const int32_t *
     out[n * C + m] = linear_epilogue(acc, lc.corr[m], lc.rs[m], lc.zp_out, lc.lo, lc.hi);
 }
 
+// v: optional [B][4H] out of this step: update, reset, new gate outputs and the R*h + br row of
+// the new gate (the training buffer of the reference).
 __global__ void k_gates_generic(const int32_t *__restrict__ ih, const int32_t *__restrict__ hh,
-                                const int32_t *__restrict__ h_in, int32_t *__restrict__ h_out, int B,
-                                int H, const GateConsts *__restrict__ gcp,
+                                const int32_t *__restrict__ h_in, int32_t *__restrict__ h_out,
+                                int32_t *__restrict__ v, int B, int H, const GateConsts *__restrict__ gcp,
                                 const int32_t *__restrict__ tables) {
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     const int b = blockIdx.y;
     if (j >= H || b >= B) return;
     const size_t w = (size_t)b * 3 * H + j;
+    int32_t gates[3];
     h_out[(size_t)b * H + j] = gru_cell<false>(*gcp, tables, ih[w], ih[w + H], ih[w + 2 * H], hh[w],
-                                               hh[w + H], hh[w + 2 * H], h_in[(size_t)b * H + j]);
+                                               hh[w + H], hh[w + 2 * H], h_in[(size_t)b * H + j], gates);
+    if (v) {
+        int32_t *vb = v + (size_t)b * 4 * H + j;
+        vb[0] = gates[0];
+        vb[H] = gates[1];
+        vb[2 * H] = gates[2];
+        vb[3 * H] = hh[w + 2 * H];
+    }
 }
 
 }  // namespace qgru

@@ -128,6 +128,22 @@ class Handle:
             self.synchronize()
         return h_q
 
+    def forward_i32_train(self, x_q, h0_q=None, reverse=False):
+        """Training-mode integer forward: (h_q [(T+1),B,H], v_q [T,B,4H]) int32; v_q holds the
+        quantized update / reset / new gate outputs and the R*h + br row of the new gate."""
+        T, B = int(x_q.shape[0]), int(x_q.shape[1])
+        H = self.hidden_size
+        x_q = _check_tensor(x_q, "x_q", torch.int32, (T, B, self.input_size))
+        if h0_q is not None:
+            h0_q = _check_tensor(h0_q, "h0_q", torch.int32, (B, H))
+        h = torch.empty((T + 1, B, H), dtype=torch.int32, device=self._tdev)
+        v = torch.empty((T, B, 4 * H), dtype=torch.int32, device=self._tdev)
+        self._ck(self._lib.qgru_forward_i32_train(self._h, T, B, _ptr(x_q), _ptr(h0_q), _ptr(h), _ptr(v),
+                                                  1 if reverse else 0, _stream(self._tdev)),
+                 "qgru_forward_i32_train")
+        self.synchronize()
+        return h, v
+
     def forward_i32_static(self, x_q, h0_q=None, reverse=False, out=None, sync=True):
         """forward_i32 for callers that may not allocate device memory at call time: the
         workspace is a fixed 8 MiB array inside the library (shared by every call on the GPU, so

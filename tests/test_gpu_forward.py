@@ -261,3 +261,21 @@ def test_forward_is_capturable_into_a_cuda_graph(oracle, cuda_device):
             assert np.array_equal(out_static.cpu().numpy(), want)
             out_static.zero_()
             x_static.zero_()
+
+
+@pytest.mark.parametrize("name", ["default", "cfg2", "wide16"])
+def test_training_buffer(oracle, cuda_device, name):
+    """qgru_forward_i32_train: h_q as in inference plus v_q equal to the oracle's training buffer;
+    in reverse mode slot t of v_q belongs to x_q[t]."""
+    case = make_case(51, 6, 5, 24, 40, oracle, config_named(name), with_h0=True)
+    args = (case.T, case.B, case.I, case.H, case.wq, case.x_q, case.h0_q, case.params.c, case.params.scale_list())
+    want_h, want_v = oracle.forward_i32_v(*args)
+    with gru_ops.Handle(case.I, case.H, device=0) as hd:
+        hd.set_params(case.params)
+        hd.set_weights_i32(*[_t(a, cuda_device) for a in case.wq])
+        h, v = hd.forward_i32_train(_t(case.x_q, cuda_device), _t(case.h0_q, cuda_device))
+        assert np.array_equal(h.cpu().numpy(), want_h) and np.array_equal(v.cpu().numpy(), want_v)
+        flipped = np.ascontiguousarray(case.x_q[::-1])
+        h2, v2 = hd.forward_i32_train(_t(flipped, cuda_device), _t(case.h0_q, cuda_device), reverse=True)
+        assert np.array_equal(v2.cpu().numpy()[::-1], want_v)
+        assert np.array_equal(h2.cpu().numpy()[:case.T][::-1], want_h[1:])

@@ -69,3 +69,14 @@ def test_lut_eval_whole_domain(oracle, reference):
         for q in range(-300, 300):
             assert oracle.lut_eval(p.lut[lut], q, p.op[i_in], p.op[i_out]) == \
                 reference.lut_eval(p.lut[lut], q, p.op[i_in], p.op[i_out])
+
+
+def test_training_buffer_matches_reference(oracle, reference):
+    """v_q (gate outputs and the new gate's R*h row) of the training-mode CPU forward."""
+    for seed, cfg in enumerate(("default", "cfg2", "pot2_asym", "wide16")):
+        case = make_case(70 + seed, 5, 3, 12, 20, reference, config_named(cfg), with_h0=bool(seed & 1))
+        args = (case.T, case.B, case.I, case.H, case.wq, case.x_q, case.h0_q, case.params.c, case.params.scale_list())
+        h_r, v_r = reference.forward_i32_v(*args)
+        h_o, v_o = oracle.forward_i32_v(*args)
+        assert np.array_equal(h_r, h_o) and np.array_equal(v_r, v_o)
+        assert np.array_equal(h_o, oracle.forward_i32(*args))
