@@ -5,12 +5,13 @@
 // group of NB batch rows and keeps its slice of R in shared memory for all T steps.  Here the P
 // CTAs of a group form one thread-block cluster and h_t never leaves the SMs.  The 128 units of
 // CTA p are exactly K-slab p of the B-operand tile (NB rows x 128 bytes, 128-byte swizzle), a
-// contiguous NB*128-byte block.  Each epilogue thread stores its 8-bit h_t value into that block
-// of its OWN tile; one thread then pushes the block into the same place of every peer's tile
-// with a bulk asynchronous copy (cp.async.bulk.shared::cluster) that signals the peer's
-// mbarrier.  A CTA starts the MMAs of a step when its own block is written and the P-1 peer
-// blocks have arrived: no cluster-wide barrier, no global-memory round trip, no gpu-scope
-// fence, no polling.  Only the outputs go to global memory.
+// contiguous NB*128-byte block.  Each epilogue warp transposes its 4 rows x 32 units of 8-bit h_t
+// through shuffles into one 32-bit word per lane, stores the word into its OWN tile and sends
+// it to the same place of every peer's tile with st.async, a store that counts its bytes on the
+// peer's mbarrier when it lands.  A CTA starts the MMAs of a step when its 16 warps have arrived
+// and the P-1 peer blocks have landed: no relay through one thread, no cluster-wide barrier,
+// no fence on the sending side, no global-memory round trip.  Only the outputs go to global
+// memory.
 //
 // The tile is double buffered: step s multiplies buffer s&1 while the blocks of h_{s+1} land in
 // buffer (s+1)&1.  A peer can never be more than one step ahead (its MMAs of step s+1 need this
@@ -45,13 +46,15 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t ran
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
     return r;
 }
-// bulk copy of `bytes` (multiple of 16) from own shared memory into a peer's; completion is
-// counted in bytes on the peer's mbarrier (both destination addresses are cluster addresses)
-__device__ __forceinline__ void bulk_push(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes,
-                                          uint32_t mbar_cluster) {
-    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst_cluster), "r"(src_cta), "r"(bytes), "r"(mbar_cluster)
+// 32-bit store into a peer CTA's shared memory that counts its 4 bytes on the peer's mbarrier when
+// it lands: no fence and no acknowledgement on the sending side
+__device__ __forceinline__ void st_async_u32(uint32_t peer_addr, uint32_t v, uint32_t peer_bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(peer_addr),
+                 "r"(v), "r"(peer_bar)
                  : "memory");
+}
+__device__ __forceinline__ void sts_u32(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async_cta() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -132,8 +135,8 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
     unsigned char *h_tile = base + L.h_tile;
     const uint32_t h_buf_bytes = (uint32_t)(KBn * a.NB * 128);
     uint64_t *bars = reinterpret_cast<uint64_t *>(base + L.bars);
-    uint64_t *r_full = bars, *h_full = bars + 1, *h_written = bars + 2, *r_ready = bars + 3;
-    uint64_t *h_ready = bars + 4;                    // [2]: peer blocks of the tile buffer have landed
+    uint64_t *r_full = bars, *h_full = bars + 1, *r_ready = bars + 3;
+    uint64_t *h_ready = bars + 4;                    // [2]: the tile buffer holds h_t of every CTA of the cluster
     uint64_t *mma_done = bars + 6;                   // [3]: the rows of gate z / r / n are accumulated
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 9);
     int32_t *tables = reinterpret_cast<int32_t *>(base + L.tables);
@@ -151,9 +154,10 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
         tc::mbar_init(r_full, 1);
         tc::mbar_init(h_full, 1);
         for (int g = 0; g < 3; ++g) tc::mbar_init(&mma_done[g], 1);
-        tc::mbar_init(h_written, EPI_THREADS);
-        tc::mbar_init(&h_ready[0], 1);
-        tc::mbar_init(&h_ready[1], 1);
+        // per phase: one arrival per epilogue warp, one by the control thread (which also announces
+        // the bytes the peers send)
+        tc::mbar_init(&h_ready[0], 4 * EPW + 1);
+        tc::mbar_init(&h_ready[1], 4 * EPW + 1);
         tc::mbar_init(r_ready, EPI_THREADS);
         tc::fence_barrier_init();
         tc::tma_prefetch_desc(&map_r);
@@ -209,22 +213,15 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
         }
         if (lane == 0) {
             const uint32_t blk_bytes = (uint32_t)(a.NB * 128);           // one K-slab of the tile
-            const uint32_t my_blk = (uint32_t)p * blk_bytes;             // MT == 1 whenever P > 1
             for (int s = 0; s < a.T && ok; ++s) {
                 const uint32_t buf_off = (uint32_t)(s & 1) * h_buf_bytes;
                 if (s > 0) {
-                    // own block of h_s: written by this CTA's epilogue threads in step s-1
-                    if (!tc::mbar_wait(h_written, (uint32_t)((s - 1) & 1), WAIT_BUDGET)) { ok = false; break; }
+                    // h_s in buffer s & 1: the 16 warps of this CTA have stored their words and the
+                    // (P-1) * NB * 128 bytes of the peers have landed
+                    tc::mbar_expect_tx(&h_ready[s & 1], (uint32_t)(a.P - 1) * blk_bytes);
                     if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 0] = clock64();
-                    if (a.P > 1) {
-                        const uint32_t src = tc::smem_u32(h_tile) + buf_off + my_blk;
-                        const uint32_t bar_local = tc::smem_u32(&h_ready[s & 1]);
-                        for (int r = 0; r < a.P; ++r)
-                            if (r != p) bulk_push(map_to_rank(src, (uint32_t)r), src, blk_bytes, map_to_rank(bar_local, (uint32_t)r));
-                        // the P-1 peer blocks of h_s
-                        tc::mbar_expect_tx(&h_ready[s & 1], (uint32_t)(a.P - 1) * blk_bytes);
-                        if (!tc::mbar_wait(&h_ready[s & 1], (uint32_t)(((s - 1) >> 1) & 1), WAIT_BUDGET)) { ok = false; break; }
-                    }
+                    if (!tc::mbar_wait(&h_ready[s & 1], (uint32_t)(((s - 1) >> 1) & 1), WAIT_BUDGET)) { ok = false; break; }
+                    fence_proxy_async_cta();   // the MMAs read these stores through the async proxy
                 }
                 if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 1] = clock64();
                 tc::tc_fence_after_sync();
@@ -298,6 +295,14 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
         const int nchunks = a.NB / CH;
         const uint32_t tab = tc::smem_u32(tables);          // fused-cell tables, shared-window address
         const uint32_t h_bits = a.h_unsigned ? 9u : 8u;     // state bytes: zero- or sign-extended
+        // Exchange: after the shuffle transposition lane t holds the word (row t >> 3 of the chunk,
+        // units 4 * (t & 7) .. + 3 of this warp's 32); source lanes, byte selector and the peers'
+        // tile / barrier addresses are fixed for the whole launch.
+        static_assert(CH == 4, "the exchange packs four row bytes per lane");
+        const int x_row = lane >> 3, x_word = lane & 7;
+        const uint32_t x_sel = (uint32_t)x_row | ((uint32_t)(4 + x_row) << 4);
+        const uint32_t tile_u32 = tc::smem_u32(h_tile);
+        const uint32_t bar0_u32 = tc::smem_u32(&h_ready[0]), bar1_u32 = tc::smem_u32(&h_ready[1]);
         int64_t corr[MT][3];
         Rescale rs[MT][3];
         FastLin fl[MT][3];
@@ -349,7 +354,6 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
             const int t = a.reverse ? (a.T - 1 - s) : s;
             const long long out_slot = a.reverse ? (a.T - 1 - s) : (s + 1);
             const unsigned char *h_cur = h_tile + (size_t)(s & 1) * h_buf_bytes;
-            unsigned char *h_nxt = h_tile + (size_t)((s + 1) & 1) * h_buf_bytes;
             const uint32_t par = (uint32_t)(s & 1);
             const bool stamp = a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0;
             bool waited = false;
@@ -473,21 +477,41 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     asm volatile("mov.u64 %0, %%clock64;" : "=l"(tck) : "r"(hn[0][0]), "r"(hn[MT - 1][CH - 1]), "r"(hn[0][1]), "r"(hn[0][2]) : "memory");
                     a.dbg[s * 8 + 6] = tck;
                 }
-                // h_t[b][j] = element (row b, K index j) of the next B tile: this CTA's own K-slab
+                // h_t[b][j] = element (row b, K index j) of the next B tile.  Pack the CH row bytes of
+                // this lane's unit, gather byte x_row of the four lanes 4 * x_word .. + 3, store the
+                // word into this CTA's tile and send it to every peer's.  Absent rows and units send
+                // their (clamped) values too: they land in padding rows, or multiply zero columns of
+                // R, and the peers count on the full number of bytes.
                 const bool last = c + EPW >= nchunks;
+                const int nx = (s + 1) & 1;
+                const uint32_t bar_nx = nx ? bar1_u32 : bar0_u32;
+                // (nothing reads the state after the last step, and no store may be on its way to a
+                // peer when the kernel ends)
+#pragma unroll
+                for (int mt = 0; mt < MT && s + 1 < a.T; ++mt) {
+                    const uint32_t packed = ((uint32_t)hn[mt][0] & 0xffu) | (((uint32_t)hn[mt][1] & 0xffu) << 8) |
+                                            (((uint32_t)hn[mt][2] & 0xffu) << 16) | ((uint32_t)hn[mt][3] << 24);
+                    const uint32_t v0 = __shfl_sync(0xffffffffu, packed, 4 * x_word + 0);
+                    const uint32_t v1 = __shfl_sync(0xffffffffu, packed, 4 * x_word + 1);
+                    const uint32_t v2 = __shfl_sync(0xffffffffu, packed, 4 * x_word + 2);
+                    const uint32_t v3 = __shfl_sync(0xffffffffu, packed, 4 * x_word + 3);
+                    const uint32_t word = __byte_perm(__byte_perm(v0, v1, x_sel), __byte_perm(v2, v3, x_sel), 0x5410);
+                    const uint32_t at = tile_u32 + (uint32_t)nx * h_buf_bytes +
+                                        sw128_offset(c0 + x_row, j0 + mt * 128 + q * 32 + 4 * x_word, a.NB);
+                    sts_u32(at, word);
+                    for (int r = 0; r < a.P; ++r)
+                        if (r != p) st_async_u32(map_to_rank(at, (uint32_t)r), word, map_to_rank(bar_nx, (uint32_t)r));
+                }
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
                     const int j = j0 + mt * 128 + u;
 #pragma unroll
                     for (int i = 0; i < CH; ++i) {
                         const int b = c0 + i;
-                        if (b < nb && j_ok[mt]) {
-                            h_nxt[sw128_offset(b, j, a.NB)] = (unsigned char)hn[mt][i];
-                            if (!last) {
-                                const size_t o = (size_t)out_slot * BH + (size_t)(b0 + b) * a.H + j;
-                                if (a.hq_out) a.hq_out[o] = hn[mt][i];
-                                if (a.hf_out) a.hf_out[o] = (float)(hn[mt][i] - gc.zp_h) * gc.h_scale;
-                            }
+                        if (!last && b < nb && j_ok[mt]) {
+                            const size_t o = (size_t)out_slot * BH + (size_t)(b0 + b) * a.H + j;
+                            if (a.hq_out) a.hq_out[o] = hn[mt][i];
+                            if (a.hf_out) a.hf_out[o] = (float)(hn[mt][i] - gc.zp_h) * gc.h_scale;
                         }
                         hn_last[mt][i] = hn[mt][i];
                     }
@@ -495,16 +519,18 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                 if (last) c_last = c;
             }
             if (ok && !waited) {
-                // A warp without a chunk still waits for this step's MMAs: it must not arrive on
-                // h_written twice within one phase.
+                // A warp without a chunk still waits for this step's MMAs: it must not arrive twice
+                // within one phase of the tile barrier.
                 ok = tc::mbar_wait(&mma_done[2], par, WAIT_BUDGET);
                 tc::tc_fence_after_sync();
             }
             if (stamp) a.dbg[s * 8 + 7] = clock64();
-            // the bulk copy and the next MMA read these generic-proxy stores through the async proxy
+            // this warp's own words are ordered for the async proxy (the MMAs read them), then one
+            // lane arrives for the warp on this CTA's barrier of the buffer just written
             fence_proxy_async_cta();
             tc::tc_fence_before_sync();
-            tc::mbar_arrive(h_written);
+            __syncwarp();
+            if (lane == 0 && s + 1 < a.T) tc::mbar_arrive(&h_ready[(s + 1) & 1]);
             if (stamp) a.dbg[s * 8 + 5] = clock64();
             // Outputs of the last chunk leave for global memory after the arrive: nothing in the next
             // step waits for them, so they overlap the exchange and the next MMAs.
