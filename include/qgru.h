@@ -210,10 +210,21 @@ QGRU_API int qgru_forward_i32(qgru_handle *h, int T, int B, const int32_t *x_q,
  * the same h_q plus v_q [T,B,4H] int32 device out = quantized update, reset and new gate outputs
  * and the R*h + br row of the new gate, per timestep of x (with QGRU_FLAG_REVERSE, slot t of
  * v_q belongs to x_q[t]).  Runs on the step-by-step int32 kernels, which keep those
- * intermediates; the clamp masks of the reference's training mode are not produced. */
+ * intermediates.
+ * masks (may be NULL, and so may each member): the five clamp masks of the reference's training
+ * mode (include/gru_interface.h:380-402; src/gru_forward_gpu_quant.cu:168-178, :318-348), uint8
+ * device out, 1 = the value was inside its range before the clamp (the backward pass keeps the
+ * gradient), 0 = it was clamped; rows are indexed like v_q (row t*B + b belongs to x_q[t]). */
+typedef struct qgru_masks {
+    uint8_t *ih_linear;   /* [T*B, 3H] W*x + bw */
+    uint8_t *hh_linear;   /* [T*B, 3H] R*h + br */
+    uint8_t *gate_input;  /* [T*B, 3H] gate inputs (z, r, n) */
+    uint8_t *gate_output; /* [T*B, 3H] gate outputs (z, r, n) */
+    uint8_t *h;           /* [T*B, H]  new state */
+} qgru_masks;
 QGRU_API int qgru_forward_i32_train(qgru_handle *h, int T, int B, const int32_t *x_q,
                                     const int32_t *h0_q, int32_t *h_q, int32_t *v_q,
-                                    unsigned flags, void *stream);
+                                    const qgru_masks *masks, unsigned flags, void *stream);
 
 /* quantGRUForwardInt (src/gru_interface.cc:610-725), inference mode: float in, float out.
  *   x [T,B,I] f32 device, h0 [B,H] f32 device or NULL, h [(T+1),B,H] f32 device out,

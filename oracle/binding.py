@@ -157,6 +157,22 @@ class _Checker:
             raise RuntimeError("forward_i32_v failed")
         return h, v
 
+    def forward_i32_train(self, T, B, I, H, wq, x_q, h0_q, params, sc):
+        """Training-mode forward with the five clamp masks (oracle only: the reference's CPU path
+        has none): (h_q, v_q, [ih, hh, gate_in, gate_out (each [T*B,3H]), h [T*B,H]] uint8)."""
+        x_q = np.ascontiguousarray(x_q, np.int32)
+        h = np.zeros((T + 1, B, H), np.int32)
+        v = np.zeros((T, B, 4 * H), np.int32)
+        ms = [np.zeros((T * B, 3 * H), np.uint8) for _ in range(4)] + [np.zeros((T * B, H), np.uint8)]
+        mptr = (C.c_void_p * 5)(*[m.ctypes.data for m in ms])
+        h0p = _i(np.ascontiguousarray(h0_q, np.int32)) if h0_q is not None else None
+        rc = self._fn("forward_i32_train")(T, B, I, H, *[_i(np.ascontiguousarray(w, np.int32)) for w in wq],
+                                           _i(x_q), h0p, C.byref(params), *[_f(s) for s in sc], _i(h), _i(v),
+                                           mptr)
+        if rc:
+            raise RuntimeError("forward_i32_train failed")
+        return h, v, ms
+
     def forward_f32(self, T, B, I, H, wq, x, h0, params, sc):
         x = np.ascontiguousarray(x, np.float32)
         h = np.zeros((T + 1, B, H), np.float32)
@@ -228,6 +244,122 @@ class Reference(_Checker):
         if so is None:
             raise FileNotFoundError("oracle/_ref/libqgru_ref.so has not been built")
         super().__init__(so)
+
+
+class ReferenceGpu:
+    """The reference's own GPU paths (ref_gpu_* of oracle/ref_shim.cc): host arrays in and out,
+    run on the current CUDA device.  Only meaningful on a machine with a GPU."""
+    prefix = "ref_gpu_"
+    kind = "reference-gpu"
+
+    def __init__(self, ref):
+        self.lib, self.cabi, self.ref = ref.lib, ref.cabi, ref
+        self.lib.ref_last_error.restype = C.c_char_p
+
+    def _fn(self, name):
+        return getattr(self.lib, self.prefix + name)
+
+    def _check(self, rc, what):
+        if rc:
+            raise RuntimeError(f"{what}: {self.lib.ref_last_error().decode(errors='replace')}")
+
+    def device_count(self):
+        return int(self._fn("device_count")())
+
+    def forward_i32(self, T, B, I, H, wq, x_q, h0_q, params, sc, training=False, masks=False):
+        """quantGRUForwardInt32 on the GPU: h_q, and in training mode (v_q, the 5 clamp masks)."""
+        x_q = np.ascontiguousarray(x_q, np.int32)
+        h = np.zeros((T + 1, B, H), np.int32)
+        v = np.zeros((T, B, 4 * H), np.int32) if training else None
+        ms = None
+        mptr = None
+        if masks:
+            ms = [np.zeros((T * B, 3 * H), np.uint8) for _ in range(4)] + [np.zeros((T * B, H), np.uint8)]
+            mptr = (C.c_void_p * 5)(*[m.ctypes.data for m in ms])
+        h0p = _i(np.ascontiguousarray(h0_q, np.int32)) if h0_q is not None else None
+        rc = self._fn("forward_i32")(int(training), T, B, I, H,
+                                     *[_i(np.ascontiguousarray(w, np.int32)) for w in wq], _i(x_q), h0p,
+                                     C.byref(params), *[_f(s) for s in sc], _i(h),
+                                     _i(v) if v is not None else None, mptr)
+        self._check(rc, "ref_gpu_forward_i32")
+        return (h, v, ms) if training else h
+
+    def forward_float(self, T, B, I, H, W, R, bw, br, x, h0=None, want_v=False):
+        h = np.zeros((T + 1, B, H), np.float32)
+        v = np.zeros((T, B, 4 * H), np.float32) if want_v else None
+        rc = self._fn("forward_float")(T, B, I, H, _f(W), _f(R), _f(bw), _f(br),
+                                       _f(np.ascontiguousarray(x, np.float32)),
+                                       _f(np.ascontiguousarray(h0, np.float32)) if h0 is not None else None,
+                                       _f(h), _f(v) if v is not None else None)
+        self._check(rc, "ref_gpu_forward_float")
+        return (h, v) if want_v else h
+
+    def calibrate_minmax(self, T, B, I, H, W, R, bw, br, x, ranges):
+        """forwardWithCalibrationGPU(MINMAX): folds one batch into `ranges`; returns h."""
+        h = np.zeros((T + 1, B, H), np.float32)
+        rs = ranges.struct()
+        rc = self._fn("calibrate_minmax")(T, B, I, H, _f(W), _f(R), _f(bw), _f(br),
+                                          _f(np.ascontiguousarray(x, np.float32)), C.byref(rs), _f(h))
+        self._check(rc, "ref_gpu_calibrate_minmax")
+        ranges.load(rs)
+        return h
+
+    def hist_new(self, bins=2048):
+        f = self._fn("hist_new")
+        f.restype = C.c_void_p
+        return _Hist(self, C.c_void_p(f(int(bins))), bins)
+
+    def histset_new(self, hidden, bins=2048):
+        return _GpuHistSet(self, hidden, bins)
+
+
+class _GpuHistSet:
+    """GRUGPUHistogramCollectors of the reference, filled by its calibration forward."""
+
+    def __init__(self, gpu, hidden, bins):
+        f = gpu._fn("histset_new")
+        f.restype = C.c_void_p
+        self.gpu, self.hidden, self.bins = gpu, hidden, bins
+        self.h = C.c_void_p(f(int(hidden), int(bins)))
+        if not self.h:
+            raise RuntimeError("ref_gpu_histset_new failed")
+
+    def calibrate(self, T, B, I, H, W, R, bw, br, x, params, use_percentile):
+        rc = self.gpu._fn("histset_calibrate")(self.h, T, B, I, H, _f(W), _f(R), _f(bw), _f(br),
+                                               _f(np.ascontiguousarray(x, np.float32)), C.byref(params),
+                                               int(use_percentile))
+        self.gpu._check(rc, "ref_gpu_histset_calibrate")
+
+    def sync(self):
+        self.gpu._check(self.gpu._fn("histset_sync")(self.h), "ref_gpu_histset_sync")
+
+    def get(self, index):
+        """(counts, min, max, total) of histogram `index` (qgru_hist layout), or None if empty."""
+        counts = np.zeros(self.bins, np.float32)
+        mn, mx, tot, valid = C.c_float(), C.c_float(), C.c_int64(), C.c_int()
+        rc = self.gpu._fn("histset_get")(self.h, int(index), _f(counts), C.byref(mn), C.byref(mx),
+                                         C.byref(tot), C.byref(valid))
+        self.gpu._check(rc, "ref_gpu_histset_get")
+        if not valid.value:
+            return None
+        return counts, float(mn.value), float(mx.value), int(tot.value)
+
+    def params(self, params, use_percentile, percentile=99.99):
+        """calculateGRUQuantitativeParametersFromHistograms on the collected set; fills `params`
+        in place and returns the four per-channel scale arrays."""
+        sc = [np.zeros(3 * self.hidden, np.float32) for _ in range(4)]
+        rc = self.gpu._fn("histset_params")(self.h, C.byref(params), int(use_percentile),
+                                            C.c_float(percentile), *[_f(a) for a in sc])
+        self.gpu._check(rc, "ref_gpu_histset_params")
+        return sc
+
+    def __del__(self):
+        try:
+            f = self.gpu._fn("histset_free")
+            f.argtypes = [C.c_void_p]
+            f(self.h)
+        except Exception:
+            pass
 
 
 def reference_or_none():

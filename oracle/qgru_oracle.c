@@ -129,6 +129,14 @@ static int32_t clamp_bw(int32_t v, const qgru_op *o) {
     return v < lo ? lo : (v > hi ? hi : v);
 }
 
+/* clamp_by_bitwidth<Training>: *keep = 1 iff v was inside the range (the flag the backward pass
+ * multiplies gradients with), include/quantize_ops_helper.h:365-376.  keep may be NULL. */
+static int32_t clamp_keep(int32_t v, const qgru_op *o, uint8_t *keep) {
+    const int32_t c = clamp_bw(v, o);
+    if (keep) *keep = (uint8_t)(c == v);
+    return c;
+}
+
 /* quantize(float, FixedPointScale, zp, bw), include/quantize_ops_helper.h:528-533. */
 static int32_t quantize_fs(float x, uint16_t m, int8_t s, int32_t zp, const qgru_op *o) {
     float q = rintf(x / decode_scale(m, s)) + (float)zp;
@@ -143,9 +151,17 @@ static float dequantize_fs(int32_t q, uint16_t m, int8_t s, int32_t zp) {
 /* ------------------------------------------------------------------------- LUT */
 
 /* piecewise_linear, include/quantize_ops_helper.h:560-606. */
+static int32_t lut_eval_keep(const qgru_lut *lut, int32_t q_x, const qgru_op *in_bw,
+                             const qgru_op *out_bw, uint8_t *keep_in, uint8_t *keep_out);
 ORC_API int32_t orc_lut_eval(const qgru_lut *lut, int32_t q_x, const qgru_op *in_bw,
                              const qgru_op *out_bw) {
-    const int32_t q = clamp_bw(q_x, in_bw);
+    return lut_eval_keep(lut, q_x, in_bw, out_bw, NULL, NULL);
+}
+/* The training branch keeps the two clamp flags (gate input, gate output),
+ * include/quantize_ops_helper.h:760-783. */
+static int32_t lut_eval_keep(const qgru_lut *lut, int32_t q_x, const qgru_op *in_bw,
+                             const qgru_op *out_bw, uint8_t *keep_in, uint8_t *keep_out) {
+    const int32_t q = clamp_keep(q_x, in_bw, keep_in);
     int seg = QGRU_LUT_SEGMENTS - 1;
     for (int i = 0; i < QGRU_LUT_SEGMENTS; ++i)
         if (q < lut->seg[i].threshold) { seg = i; break; }
@@ -155,7 +171,7 @@ ORC_API int32_t orc_lut_eval(const qgru_lut *lut, int32_t q_x, const qgru_op *in
     const int n = (int8_t)s->n_bx;
     const int32_t term = (n >= 0) ? (int32_t)orc_rshift_round(bx, n)
                                   : (int32_t)((uint64_t)bx << (-n));
-    return clamp_bw((int32_t)((uint32_t)term + (uint32_t)s->term_c), out_bw);
+    return clamp_keep((int32_t)((uint32_t)term + (uint32_t)s->term_c), out_bw, keep_out);
 }
 
 /* linear_fit, src/quantize_ops.cu:996-1017. */
@@ -553,29 +569,30 @@ static int derive(const qgru_params *p, const float *sW, const float *sR, const 
 /* computeUpdateGate / computeResetGate (inference branch),
  * include/quantize_ops_helper.h:749-821 and 832-901. */
 static int32_t sigmoid_gate(int32_t ih, int32_t hh, const qgru_params *p, orc_rescale r_ih,
-                            orc_rescale r_hh, int op_in, int op_out, int lut) {
+                            orc_rescale r_hh, int op_in, int op_out, int lut, uint8_t *keep) {
     const int64_t ih_d = (int64_t)ih - p->op[QGRU_OP_IH_LINEAR].zero_point;
     const int64_t hh_d = (int64_t)hh - p->op[QGRU_OP_HH_LINEAR].zero_point;
     const int32_t a = (int32_t)apply_rescale(ih_d, r_ih);
     const int32_t b = (int32_t)apply_rescale(hh_d, r_hh);
     const int32_t in = (int32_t)((uint32_t)a + (uint32_t)b + (uint32_t)p->op[op_in].zero_point);
-    return orc_lut_eval(&p->lut[lut], in, &p->op[op_in], &p->op[op_out]);
+    return lut_eval_keep(&p->lut[lut], in, &p->op[op_in], &p->op[op_out], keep, keep ? keep + 1 : NULL);
 }
 
 /* computeNewGate, include/quantize_ops_helper.h:917-997. */
 static int32_t new_gate(int32_t ih, int32_t hh, int32_t r, const qgru_params *p,
-                        const orc_derived *d) {
+                        const orc_derived *d, uint8_t *keep) {
     const int64_t r_d = (int64_t)r - p->op[QGRU_OP_RESET_OUT].zero_point;
     const int64_t hh_d = (int64_t)hh - p->op[QGRU_OP_HH_LINEAR].zero_point;
     const int32_t rh = (int32_t)apply_rescale(r_d * hh_d, d->rh_to_n);
     const int32_t a = (int32_t)apply_rescale((int64_t)ih - p->op[QGRU_OP_IH_LINEAR].zero_point, d->ih_to_n);
     const int32_t in = (int32_t)((uint32_t)a + (uint32_t)rh + (uint32_t)p->op[QGRU_OP_NEW_IN].zero_point);
-    return orc_lut_eval(&p->lut[QGRU_LUT_NEW], in, &p->op[QGRU_OP_NEW_IN], &p->op[QGRU_OP_NEW_OUT]);
+    return lut_eval_keep(&p->lut[QGRU_LUT_NEW], in, &p->op[QGRU_OP_NEW_IN], &p->op[QGRU_OP_NEW_OUT], keep,
+                         keep ? keep + 1 : NULL);
 }
 
 /* computeHiddenState, include/quantize_ops_helper.h:1008-1084. */
 static int32_t hidden_state(int32_t u, int32_t n, int32_t h_old, const qgru_params *p,
-                            const orc_derived *d) {
+                            const orc_derived *d, uint8_t *keep) {
     const int32_t zp_h = p->op[QGRU_OP_H].zero_point;
     const int32_t zp_u = p->op[QGRU_OP_UPDATE_OUT].zero_point;
     const int64_t n_d = (int64_t)n - p->op[QGRU_OP_NEW_OUT].zero_point;
@@ -588,14 +605,14 @@ static int32_t hidden_state(int32_t u, int32_t n, int32_t h_old, const qgru_para
     const int64_t n_ald = (int64_t)n_al - zp_h;
     const int64_t new_c = omu_d * n_ald;
     const int32_t h_new = (int32_t)((uint32_t)(int32_t)apply_rescale(old_c + new_c, d->uh_to_h) + (uint32_t)zp_h);
-    return clamp_bw(h_new, &p->op[QGRU_OP_H]);
+    return clamp_keep(h_new, &p->op[QGRU_OP_H], keep);
 }
 
 /* ComputeLinearX / ComputeLinearH with PrecomputeWeightSums,
  * src/gru_forward_cpu_quant.cc:76-168.  Wt is [K][C] (haste layout), in is [N][K]. */
 static void linear(int N, int K, int C, const int32_t *Wt, const int32_t *in, const int32_t *bias,
                    int32_t zp_in, const orc_rescale *r_gemm, const orc_rescale *r_bias,
-                   const qgru_op *out_op, int32_t *out) {
+                   const qgru_op *out_op, int32_t *out, uint8_t *keep) {
     int64_t *wsum = (int64_t *)malloc(sizeof(int64_t) * (size_t)C);
     int64_t *acc = (int64_t *)malloc(sizeof(int64_t) * (size_t)C);
     for (int m = 0; m < C; ++m) {
@@ -615,7 +632,7 @@ static void linear(int N, int K, int C, const int32_t *Wt, const int32_t *in, co
             const int64_t b = apply_rescale((int64_t)bias[m], r_bias[m]);
             const int64_t v = apply_rescale(g + b, r_gemm[m]);
             const int32_t res = (int32_t)((uint32_t)(int32_t)v + (uint32_t)out_op->zero_point);
-            out[(size_t)n * C + m] = clamp_bw(res, out_op);
+            out[(size_t)n * C + m] = clamp_keep(res, out_op, keep ? keep + (size_t)n * C + m : NULL);
         }
     }
     free(wsum);
@@ -628,13 +645,13 @@ static int forward_i32_impl(int T, int B, int I, int H, const int32_t *W, const 
                             const int32_t *bw, const int32_t *br, const int32_t *x_q,
                             const int32_t *h0_q, const qgru_params *p, const float *sW,
                             const float *sR, const float *sbw, const float *sbr, int32_t *h_q,
-                            int32_t *v_q);
+                            int32_t *v_q, uint8_t *const *masks);
 
 ORC_API int orc_forward_i32(int T, int B, int I, int H, const int32_t *W, const int32_t *R,
                             const int32_t *bw, const int32_t *br, const int32_t *x_q,
                             const int32_t *h0_q, const qgru_params *p, const float *sW,
                             const float *sR, const float *sbw, const float *sbr, int32_t *h_q) {
-    return forward_i32_impl(T, B, I, H, W, R, bw, br, x_q, h0_q, p, sW, sR, sbw, sbr, h_q, NULL);
+    return forward_i32_impl(T, B, I, H, W, R, bw, br, x_q, h0_q, p, sW, sR, sbw, sbr, h_q, NULL, NULL);
 }
 
 /* Training-mode forward: also v_q [T,B,4H] = (update, reset, new gate outputs, R*h + br row of
@@ -644,15 +661,31 @@ ORC_API int orc_forward_i32_v(int T, int B, int I, int H, const int32_t *W, cons
                               const int32_t *h0_q, const qgru_params *p, const float *sW,
                               const float *sR, const float *sbw, const float *sbr, int32_t *h_q,
                               int32_t *v_q) {
-    return forward_i32_impl(T, B, I, H, W, R, bw, br, x_q, h0_q, p, sW, sR, sbw, sbr, h_q, v_q);
+    return forward_i32_impl(T, B, I, H, W, R, bw, br, x_q, h0_q, p, sW, sR, sbw, sbr, h_q, v_q, NULL);
+}
+
+/* Training-mode forward with the five clamp masks of quantGRUForwardInt32
+ * (include/gru_interface.h:380-402; written by src/gru_forward_gpu_quant.cu:168-178 and
+ * :318-348): masks[0] W*x+bw [T*B,3H], masks[1] R*h+br [T*B,3H], masks[2] gate inputs
+ * [T*B,3H], masks[3] gate outputs [T*B,3H], masks[4] h [T*B,H]; 1 = the value was not clamped.
+ * Any of the five may be NULL. */
+ORC_API int orc_forward_i32_train(int T, int B, int I, int H, const int32_t *W, const int32_t *R,
+                                  const int32_t *bw, const int32_t *br, const int32_t *x_q,
+                                  const int32_t *h0_q, const qgru_params *p, const float *sW,
+                                  const float *sR, const float *sbw, const float *sbr, int32_t *h_q,
+                                  int32_t *v_q, uint8_t *const *masks) {
+    return forward_i32_impl(T, B, I, H, W, R, bw, br, x_q, h0_q, p, sW, sR, sbw, sbr, h_q, v_q, masks);
 }
 
 static int forward_i32_impl(int T, int B, int I, int H, const int32_t *W, const int32_t *R,
                             const int32_t *bw, const int32_t *br, const int32_t *x_q,
                             const int32_t *h0_q, const qgru_params *p, const float *sW,
                             const float *sR, const float *sbw, const float *sbr, int32_t *h_q,
-                            int32_t *v_q) {
+                            int32_t *v_q, uint8_t *const *masks) {
     if (p->hidden != H) return 1;
+    uint8_t *m_ih = masks ? masks[0] : NULL, *m_hh = masks ? masks[1] : NULL;
+    uint8_t *m_gi = masks ? masks[2] : NULL, *m_go = masks ? masks[3] : NULL;
+    uint8_t *m_h = masks ? masks[4] : NULL;
     orc_derived d;
     if (derive(p, sW, sR, sbw, sbr, &d)) return 1;
     const int C = 3 * H;
@@ -662,22 +695,27 @@ static int forward_i32_impl(int T, int B, int I, int H, const int32_t *W, const 
     if (!ih || !hh) { free(ih); free(hh); free(d.gemm_x); return 1; }
     for (size_t i = 0; i < NH; ++i) h_q[i] = h0_q ? h0_q[i] : p->op[QGRU_OP_H].zero_point;
     linear(T * B, I, C, W, x_q, bw, p->op[QGRU_OP_X].zero_point, d.gemm_x, d.bias_w,
-           &p->op[QGRU_OP_IH_LINEAR], ih);
+           &p->op[QGRU_OP_IH_LINEAR], ih, m_ih);
     for (int t = 0; t < T; ++t) {
         const int32_t *h_in = h_q + (size_t)t * NH;
         int32_t *h_out = h_q + (size_t)(t + 1) * NH;
         const int32_t *iht = ih + (size_t)t * B * C;
         linear(B, H, C, R, h_in, br, p->op[QGRU_OP_H].zero_point, d.gemm_h, d.bias_r,
-               &p->op[QGRU_OP_HH_LINEAR], hh);
+               &p->op[QGRU_OP_HH_LINEAR], hh, m_hh ? m_hh + (size_t)t * B * C : NULL);
         for (int b = 0; b < B; ++b) {
             for (int j = 0; j < H; ++j) {
                 const size_t w = (size_t)b * C + j;
+                uint8_t ku[2], kr[2], kn[2], kh;
                 const int32_t u = sigmoid_gate(iht[w], hh[w], p, d.ih_to_z, d.hh_to_z,
-                                               QGRU_OP_UPDATE_IN, QGRU_OP_UPDATE_OUT, QGRU_LUT_UPDATE);
+                                               QGRU_OP_UPDATE_IN, QGRU_OP_UPDATE_OUT, QGRU_LUT_UPDATE, ku);
                 const int32_t r = sigmoid_gate(iht[w + H], hh[w + H], p, d.ih_to_r, d.hh_to_r,
-                                               QGRU_OP_RESET_IN, QGRU_OP_RESET_OUT, QGRU_LUT_RESET);
-                const int32_t n = new_gate(iht[w + 2 * H], hh[w + 2 * H], r, p, &d);
-                h_out[(size_t)b * H + j] = hidden_state(u, n, h_in[(size_t)b * H + j], p, &d);
+                                               QGRU_OP_RESET_IN, QGRU_OP_RESET_OUT, QGRU_LUT_RESET, kr);
+                const int32_t n = new_gate(iht[w + 2 * H], hh[w + 2 * H], r, p, &d, kn);
+                h_out[(size_t)b * H + j] = hidden_state(u, n, h_in[(size_t)b * H + j], p, &d, &kh);
+                const size_t mw = (size_t)t * B * C + w;
+                if (m_gi) { m_gi[mw] = ku[0]; m_gi[mw + H] = kr[0]; m_gi[mw + 2 * H] = kn[0]; }
+                if (m_go) { m_go[mw] = ku[1]; m_go[mw + H] = kr[1]; m_go[mw + 2 * H] = kn[1]; }
+                if (m_h) m_h[((size_t)t * B + b) * H + j] = kh;
                 if (v_q) {
                     int32_t *vb = v_q + ((size_t)t * B + b) * 4 * H + j;
                     vb[0] = u;

@@ -7,13 +7,23 @@
 // format.  Only host functions of the reference are reached: the CPU forward
 // (src/gru_forward_cpu_quant.cc), quantitativeWeightCPU / quantGRUForwardCPU /
 // calculateGRUQuantitativeParameters (src/gru_interface.cc) and the LUT generator
-// (src/quantize_ops.cu:21-52).  No CUDA call is made by anything reached from here.
+// (src/quantize_ops.cu:21-52).  No CUDA call is made by anything reached from the ref_*
+// functions.  The ref_gpu_* functions at the end of the file are the exception: they run the
+// reference's own GPU paths (integer forward, float forward, float-storage forward, MinMax and
+// histogram calibration) on the current CUDA device, with host buffers in and out, so that
+// the GPU tests can hold the product against the reference itself on the same machine.
+#include <array>
 #include <cstring>
+#include <memory>
 #include <stdexcept>
 #include <string>
 #include <thread>
 #include <vector>
 
+#include <cublas_v2.h>
+#include <cuda_runtime.h>
+
+#include "calibration_gpu.cuh"
 #include "gru_interface.h"
 #include "gru_quant_cpu.h"
 #include "pot_sqnr_calibrator.h"
@@ -400,6 +410,297 @@ int ref_hist_get(void *h, float *counts, float *min_val, float *max_val, int64_t
         *min_val = g.min_val;
         *max_val = g.max_val;
         *total = g.total_count;
+    });
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// The reference's GPU paths, host buffers in and out.  Test infrastructure for machines with a
+// CUDA device; every function returns 1 (message in ref_last_error) when a CUDA call fails.
+namespace {
+
+void cudaOk(cudaError_t e, const char *what) {
+    if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+template <class T>
+struct DevBuf {
+    T *p = nullptr;
+    size_t n = 0;
+    DevBuf() = default;
+    explicit DevBuf(size_t count) : n(count) {
+        if (n) cudaOk(cudaMalloc(&p, n * sizeof(T)), "cudaMalloc");
+    }
+    DevBuf(const T *host, size_t count) : DevBuf(host ? count : 0) {
+        if (n) cudaOk(cudaMemcpy(p, host, n * sizeof(T), cudaMemcpyHostToDevice), "copy in");
+    }
+    DevBuf(const DevBuf &) = delete;
+    DevBuf &operator=(const DevBuf &) = delete;
+    ~DevBuf() {
+        if (p) cudaFree(p);
+    }
+    void zero() {
+        if (n) cudaOk(cudaMemset(p, 0, n * sizeof(T)), "cudaMemset");
+    }
+    void toHost(T *host) const {
+        if (host && n) cudaOk(cudaMemcpy(host, p, n * sizeof(T), cudaMemcpyDeviceToHost), "copy out");
+    }
+};
+
+cublasHandle_t &blasHandle() {
+    static cublasHandle_t h = nullptr;
+    if (!h) init_gru_cublas(h);
+    return h;
+}
+
+void rangesFromPod(const qgru_ranges &r, GRUQuantizationRanges &g) {
+    const int C = r.hidden * 3;
+    g.min_x_ = r.min_v[QGRU_OP_X]; g.max_x_ = r.max_v[QGRU_OP_X];
+    g.min_h_ = r.min_v[QGRU_OP_H]; g.max_h_ = r.max_v[QGRU_OP_H];
+    g.min_Wx_ = r.min_v[QGRU_OP_IH_LINEAR]; g.max_Wx_ = r.max_v[QGRU_OP_IH_LINEAR];
+    g.min_Rh_ = r.min_v[QGRU_OP_HH_LINEAR]; g.max_Rh_ = r.max_v[QGRU_OP_HH_LINEAR];
+    g.min_update_gate_input_ = r.min_v[QGRU_OP_UPDATE_IN]; g.max_update_gate_input_ = r.max_v[QGRU_OP_UPDATE_IN];
+    g.min_update_gate_output_ = r.min_v[QGRU_OP_UPDATE_OUT]; g.max_update_gate_output_ = r.max_v[QGRU_OP_UPDATE_OUT];
+    g.min_reset_gate_input_ = r.min_v[QGRU_OP_RESET_IN]; g.max_reset_gate_input_ = r.max_v[QGRU_OP_RESET_IN];
+    g.min_reset_gate_output_ = r.min_v[QGRU_OP_RESET_OUT]; g.max_reset_gate_output_ = r.max_v[QGRU_OP_RESET_OUT];
+    g.min_new_gate_input_ = r.min_v[QGRU_OP_NEW_IN]; g.max_new_gate_input_ = r.max_v[QGRU_OP_NEW_IN];
+    g.min_new_gate_output_ = r.min_v[QGRU_OP_NEW_OUT]; g.max_new_gate_output_ = r.max_v[QGRU_OP_NEW_OUT];
+    g.min_mul_reset_hidden_ = r.min_v[QGRU_OP_MUL_RESET_HIDDEN]; g.max_mul_reset_hidden_ = r.max_v[QGRU_OP_MUL_RESET_HIDDEN];
+    g.min_mul_new_contribution_ = r.min_v[QGRU_OP_MUL_NEW_CONTRIB]; g.max_mul_new_contribution_ = r.max_v[QGRU_OP_MUL_NEW_CONTRIB];
+    g.min_mul_old_contribution_ = r.min_v[QGRU_OP_MUL_OLD_CONTRIB]; g.max_mul_old_contribution_ = r.max_v[QGRU_OP_MUL_OLD_CONTRIB];
+    g.min_W_.assign(r.min_W, r.min_W + C); g.max_W_.assign(r.max_W, r.max_W + C);
+    g.min_R_.assign(r.min_R, r.min_R + C); g.max_R_.assign(r.max_R, r.max_R + C);
+    g.min_bw_.assign(r.min_bw, r.min_bw + C); g.max_bw_.assign(r.max_bw, r.max_bw + C);
+    g.min_br_.assign(r.min_br, r.min_br + C); g.max_br_.assign(r.max_br, r.max_br + C);
+}
+
+void rangesToPod(const GRUQuantizationRanges &g, qgru_ranges &r) {
+    const size_t C = size_t(r.hidden) * 3;
+    r.min_v[QGRU_OP_X] = g.min_x_; r.max_v[QGRU_OP_X] = g.max_x_;
+    r.min_v[QGRU_OP_H] = g.min_h_; r.max_v[QGRU_OP_H] = g.max_h_;
+    r.min_v[QGRU_OP_IH_LINEAR] = g.min_Wx_; r.max_v[QGRU_OP_IH_LINEAR] = g.max_Wx_;
+    r.min_v[QGRU_OP_HH_LINEAR] = g.min_Rh_; r.max_v[QGRU_OP_HH_LINEAR] = g.max_Rh_;
+    r.min_v[QGRU_OP_UPDATE_IN] = g.min_update_gate_input_; r.max_v[QGRU_OP_UPDATE_IN] = g.max_update_gate_input_;
+    r.min_v[QGRU_OP_UPDATE_OUT] = g.min_update_gate_output_; r.max_v[QGRU_OP_UPDATE_OUT] = g.max_update_gate_output_;
+    r.min_v[QGRU_OP_RESET_IN] = g.min_reset_gate_input_; r.max_v[QGRU_OP_RESET_IN] = g.max_reset_gate_input_;
+    r.min_v[QGRU_OP_RESET_OUT] = g.min_reset_gate_output_; r.max_v[QGRU_OP_RESET_OUT] = g.max_reset_gate_output_;
+    r.min_v[QGRU_OP_NEW_IN] = g.min_new_gate_input_; r.max_v[QGRU_OP_NEW_IN] = g.max_new_gate_input_;
+    r.min_v[QGRU_OP_NEW_OUT] = g.min_new_gate_output_; r.max_v[QGRU_OP_NEW_OUT] = g.max_new_gate_output_;
+    r.min_v[QGRU_OP_MUL_RESET_HIDDEN] = g.min_mul_reset_hidden_; r.max_v[QGRU_OP_MUL_RESET_HIDDEN] = g.max_mul_reset_hidden_;
+    r.min_v[QGRU_OP_MUL_NEW_CONTRIB] = g.min_mul_new_contribution_; r.max_v[QGRU_OP_MUL_NEW_CONTRIB] = g.max_mul_new_contribution_;
+    r.min_v[QGRU_OP_MUL_OLD_CONTRIB] = g.min_mul_old_contribution_; r.max_v[QGRU_OP_MUL_OLD_CONTRIB] = g.max_mul_old_contribution_;
+    auto put = [&](float *dst, const std::vector<float> &src) {
+        if (dst && src.size() == C) std::memcpy(dst, src.data(), C * sizeof(float));
+    };
+    put(r.min_W, g.min_W_); put(r.max_W, g.max_W_);
+    put(r.min_R, g.min_R_); put(r.max_R, g.max_R_);
+    put(r.min_bw, g.min_bw_); put(r.max_bw, g.max_bw_);
+    put(r.min_br, g.min_br_); put(r.max_br, g.max_br_);
+}
+
+// the collector that include/qgru.h's histogram index names, in the CPU copy of a collector set
+const HistogramCollector *histByIndex(const GRUHistogramCollectors &c, int index) {
+    const int C3 = c.hidden_ * 3;
+    switch (index) {
+        case QGRU_OP_X: return &c.x_hist;
+        case QGRU_OP_H: return &c.h_hist;
+        case QGRU_OP_W: return &c.W_tensor_hist;
+        case QGRU_OP_R: return &c.R_tensor_hist;
+        case QGRU_OP_BW: return &c.bw_tensor_hist;
+        case QGRU_OP_BR: return &c.br_tensor_hist;
+        case QGRU_OP_IH_LINEAR: return &c.Wx_hist;
+        case QGRU_OP_HH_LINEAR: return &c.Rh_hist;
+        case QGRU_OP_UPDATE_IN: return &c.update_gate_input_hist;
+        case QGRU_OP_UPDATE_OUT: return &c.update_gate_output_hist;
+        case QGRU_OP_RESET_IN: return &c.reset_gate_input_hist;
+        case QGRU_OP_RESET_OUT: return &c.reset_gate_output_hist;
+        case QGRU_OP_NEW_IN: return &c.new_gate_input_hist;
+        case QGRU_OP_NEW_OUT: return &c.new_gate_output_hist;
+        case QGRU_OP_MUL_RESET_HIDDEN: return &c.mul_reset_hidden_hist;
+        case QGRU_OP_MUL_NEW_CONTRIB: return &c.mul_new_contribution_hist;
+        case QGRU_OP_MUL_OLD_CONTRIB: return &c.mul_old_contribution_hist;
+        default: break;
+    }
+    if (index >= QGRU_HIST_GATE0 && index < QGRU_HIST_CHANNEL0) {
+        const int k = (index - QGRU_HIST_GATE0) / 3, g = (index - QGRU_HIST_GATE0) % 3;
+        const std::array<HistogramCollector, 3> *a[4] = {&c.W_gate_hist, &c.R_gate_hist, &c.bw_gate_hist,
+                                                         &c.br_gate_hist};
+        return &(*a[k])[g];
+    }
+    if (index >= QGRU_HIST_CHANNEL0 && index < QGRU_HIST_CHANNEL0 + 4 * C3) {
+        const int k = (index - QGRU_HIST_CHANNEL0) / C3, ch = (index - QGRU_HIST_CHANNEL0) % C3;
+        const std::vector<HistogramCollector> *a[4] = {&c.W_hist, &c.R_hist, &c.bw_hist, &c.br_hist};
+        return &(*a[k])[ch];
+    }
+    throw std::invalid_argument("histogram index out of range");
+}
+
+struct GpuHistSet {
+    GRUGPUHistogramCollectors gpu;
+    GRUHistogramCollectors cpu;   // refreshed by ref_gpu_histset_sync
+    explicit GpuHistSet(int hidden, int bins) : gpu(hidden, bins) {}
+};
+
+}  // namespace
+
+extern "C" {
+
+int ref_gpu_device_count() {
+    int n = 0;
+    return cudaGetDeviceCount(&n) == cudaSuccess ? n : 0;
+}
+
+// quantGRUForwardInt32 (src/gru_interface.cc:551): the reference's GPU integer core.
+// masks[5] = weight_ih_linear, weight_hh_linear, gate_input, gate_output, h (each may be null
+// HERE; in training mode the reference's own kernels write the two linear masks without a null
+// check, src/gru_forward_gpu_quant.cu:168-178, so all five device buffers are always handed
+// to it in that mode and only the requested ones are copied back).
+int ref_gpu_forward_i32(int training, int T, int B, int I, int H, const int32_t *W, const int32_t *R,
+                        const int32_t *bw, const int32_t *br, const int32_t *x_q, const int32_t *h0_q,
+                        const qgru_params *p, const float *sW, const float *sR, const float *sbw,
+                        const float *sbr, int32_t *h_q, int32_t *v_q, uint8_t *const *masks) {
+    return guarded([&] {
+        GRUQuantParams q = fromPod(*p, sW, sR, sbw, sbr);
+        const size_t C3 = size_t(H) * 3, TB = size_t(T) * B;
+        DevBuf<int32_t> dW(W, size_t(I) * C3), dR(R, size_t(H) * C3), dbw(bw, C3), dbr(br, C3),
+            dx(x_q, TB * I), dh0(h0_q, size_t(B) * H), dh((TB + B) * H), dv((v_q || training) ? TB * H * 4 : 0);
+        const size_t msz[5] = {TB * C3, TB * C3, TB * C3, TB * C3, TB * H};
+        std::unique_ptr<DevBuf<uint8_t>> dm[5];
+        uint8_t *mp[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+        for (int k = 0; k < 5; ++k)
+            if (training) {
+                dm[k].reset(new DevBuf<uint8_t>(msz[k]));
+                dm[k]->zero();
+                mp[k] = dm[k]->p;
+            }
+        dh.zero();
+        quantGRUForwardInt32(training != 0, T, B, I, H, dW.p, dR.p, dbw.p, dbr.p, dx.p, dh0.p, q,
+                             blasHandle(), dh.p, dv.p, mp[0], mp[1], mp[2], mp[3], mp[4]);
+        cudaOk(cudaDeviceSynchronize(), "quantGRUForwardInt32");
+        dh.toHost(h_q);
+        dv.toHost(v_q);
+        for (int k = 0; k < 5; ++k)
+            if (dm[k] && masks && masks[k]) dm[k]->toHost(masks[k]);
+    });
+}
+
+// hasteGRUForward (src/gru_interface.cc:173): the reference's fp32 GRU on the GPU.
+int ref_gpu_forward_float(int T, int B, int I, int H, const float *W, const float *R, const float *bw,
+                          const float *br, const float *x, const float *h0, float *h, float *v) {
+    return guarded([&] {
+        const size_t C3 = size_t(H) * 3, TB = size_t(T) * B;
+        DevBuf<float> dW(W, size_t(I) * C3), dR(R, size_t(H) * C3), dbw(bw, C3), dbr(br, C3),
+            dx(x, TB * I), dh0(h0, size_t(B) * H), dh((TB + B) * H), dv(TB * H * 4);
+        dh.zero();
+        hasteGRUForward(v != nullptr, T, B, I, H, dW.p, dR.p, dbw.p, dbr.p, dx.p, dh0.p, blasHandle(),
+                        dh.p, dv.p);
+        cudaOk(cudaDeviceSynchronize(), "hasteGRUForward");
+        dh.toHost(h);
+        dv.toHost(v);
+    });
+}
+
+// forwardWithCalibrationGPU (src/gru_interface.cc:1283), MinMax: folds one batch into `r`.
+int ref_gpu_calibrate_minmax(int T, int B, int I, int H, const float *W, const float *R,
+                             const float *bw, const float *br, const float *x, qgru_ranges *r,
+                             float *h) {
+    return guarded([&] {
+        const size_t C3 = size_t(H) * 3, TB = size_t(T) * B;
+        GRUQuantizationRanges g(H);
+        rangesFromPod(*r, g);
+        DevBuf<float> dW(W, size_t(I) * C3), dR(R, size_t(H) * C3), dbw(bw, C3), dbr(br, C3),
+            dx(x, TB * I), dh((TB + B) * H), dv(TB * H * 4);
+        dh.zero();
+        forwardWithCalibrationGPU(false, T, B, I, H, dW.p, dR.p, dbw.p, dbr.p, dx.p, nullptr,
+                                  blasHandle(), CalibrationMethod::MINMAX, &g, nullptr,
+                                  OperatorQuantConfig(), dh.p, dv.p);
+        cudaOk(cudaDeviceSynchronize(), "forwardWithCalibrationGPU");
+        rangesToPod(g, *r);
+        dh.toHost(h);
+    });
+}
+
+// One GPUHistogramCollector (src/calibration_gpu.cu:820-1039) fed from host arrays.
+void *ref_gpu_hist_new(int bins) {
+    void *out = nullptr;
+    guarded([&] { out = new GPUHistogramCollector(bins); });
+    return out;
+}
+void ref_gpu_hist_free(void *h) { delete static_cast<GPUHistogramCollector *>(h); }
+int ref_gpu_hist_collect(void *h, const float *data, size_t n) {
+    return guarded([&] {
+        DevBuf<float> d(data, n);
+        static_cast<GPUHistogramCollector *>(h)->collect(d.p, n);
+        cudaOk(cudaDeviceSynchronize(), "GPUHistogramCollector::collect");
+    });
+}
+int ref_gpu_hist_get(void *h, float *counts, float *min_val, float *max_val, int64_t *total) {
+    return guarded([&] {
+        const GPUHistogram &g = static_cast<GPUHistogramCollector *>(h)->histogram();
+        if (counts && g.num_bins > 0) {
+            std::vector<float> c = g.to_host();
+            std::memcpy(counts, c.data(), sizeof(float) * c.size());
+        }
+        *min_val = g.min_val;
+        *max_val = g.max_val;
+        *total = g.total_count;
+    });
+}
+
+// The whole collector set of one GRU (GRUGPUHistogramCollectors) through the calibration forward
+// (collectAllHistogramsGPU, src/histogram_calibration_utils.cu:18-123).
+void *ref_gpu_histset_new(int hidden, int bins) {
+    void *out = nullptr;
+    guarded([&] { out = new GpuHistSet(hidden, bins); });
+    return out;
+}
+void ref_gpu_histset_free(void *s) { delete static_cast<GpuHistSet *>(s); }
+int ref_gpu_histset_calibrate(void *s, int T, int B, int I, int H, const float *W, const float *R,
+                              const float *bw, const float *br, const float *x,
+                              const qgru_params *p, int use_percentile) {
+    return guarded([&] {
+        const size_t C3 = size_t(H) * 3, TB = size_t(T) * B;
+        OperatorQuantConfig cfg;
+        fillConfig(*p, cfg);
+        DevBuf<float> dW(W, size_t(I) * C3), dR(R, size_t(H) * C3), dbw(bw, C3), dbr(br, C3),
+            dx(x, TB * I), dh((TB + B) * H), dv(TB * H * 4);
+        dh.zero();
+        forwardWithCalibrationGPU(false, T, B, I, H, dW.p, dR.p, dbw.p, dbr.p, dx.p, nullptr,
+                                  blasHandle(),
+                                  use_percentile ? CalibrationMethod::PERCENTILE : CalibrationMethod::SQNR,
+                                  nullptr, &static_cast<GpuHistSet *>(s)->gpu, cfg, dh.p, dv.p);
+        cudaOk(cudaDeviceSynchronize(), "forwardWithCalibrationGPU");
+    });
+}
+int ref_gpu_histset_sync(void *s) {
+    return guarded([&] {
+        auto *hs = static_cast<GpuHistSet *>(s);
+        hs->cpu = convertGPUHistogramsToCPU(hs->gpu);
+    });
+}
+// valid = 0 when that collector never received data (counts untouched)
+int ref_gpu_histset_get(void *s, int index, float *counts, float *min_val, float *max_val,
+                        int64_t *total, int *valid) {
+    return guarded([&] {
+        const HistogramCollector *c = histByIndex(static_cast<GpuHistSet *>(s)->cpu, index);
+        *valid = c->is_valid() ? 1 : 0;
+        const Histogram &g = c->histogram();
+        if (counts && *valid) std::memcpy(counts, g.counts.data(), sizeof(float) * g.counts.size());
+        *min_val = g.min_val;
+        *max_val = g.max_val;
+        *total = g.total_count;
+    });
+}
+// calculateGRUQuantitativeParametersFromHistograms on the synced CPU copy
+int ref_gpu_histset_params(void *s, qgru_params *p, int use_percentile, float percentile, float *sW,
+                           float *sR, float *sbw, float *sbr) {
+    return guarded([&] {
+        OperatorQuantConfig cfg;
+        fillConfig(*p, cfg);
+        GRUQuantParams q = calculateGRUQuantitativeParametersFromHistograms(
+            static_cast<GpuHistSet *>(s)->cpu, cfg, use_percentile != 0, percentile);
+        toPod(q, *p, sW, sR, sbw, sbr);
     });
 }
 

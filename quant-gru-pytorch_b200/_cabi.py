@@ -40,6 +40,12 @@ class Params(C.Structure):
                 ("granularity", C.c_int32 * 4), ("lut", Lut * 3)]
 
 
+class Masks(C.Structure):
+    """qgru_masks: the five clamp masks of the training-mode integer forward (device pointers)."""
+    _fields_ = [("ih_linear", C.c_void_p), ("hh_linear", C.c_void_p), ("gate_input", C.c_void_p),
+                ("gate_output", C.c_void_p), ("h", C.c_void_p)]
+
+
 class Ranges(C.Structure):
     _fields_ = [("hidden", C.c_int32), ("reserved", C.c_int32),
                 ("min_v", C.c_float * NUM_OPS), ("max_v", C.c_float * NUM_OPS),
@@ -69,7 +75,7 @@ SYMBOLS = {
     "qgru_set_weights_i32": (C.c_int, [_P, _P, _P, _P, _P, _P]),
     "qgru_get_weights_i32": (C.c_int, [_P, _P, _P, _P, _P, _P]),
     "qgru_forward_i32": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, C.c_uint, _P]),
-    "qgru_forward_i32_train": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, _P, C.c_uint, _P]),
+    "qgru_forward_i32_train": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, _P, _P, C.c_uint, _P]),
     "qgru_forward_i32_static": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, C.c_uint, _P]),
     "qgru_forward_f32": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, _P, C.c_uint, _P]),
     "qgru_forward_i32_host": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, C.c_uint, _P]),

@@ -759,7 +759,7 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
 
 // Generic path: int32 operands, 64-bit accumulation, one launch pair per step.
 int run_generic(qgru_handle *h, int T, int B, const int32_t *x32, int32_t *hq, int32_t *vq, unsigned flags,
-                cudaStream_t st) {
+                cudaStream_t st, const qgru_masks *mk = nullptr) {
     const long long N = (long long)T * B;
     const int C = h->C, H = h->H;
     int rc;
@@ -769,7 +769,8 @@ int run_generic(qgru_handle *h, int T, int B, const int32_t *x32, int32_t *hq, i
     const LinearConsts lcx = linear_consts(h, 0), lch = linear_consts(h, 1);
     {
         dim3 grid((C + 127) / 128, (unsigned)N);
-        k_linear_generic<<<grid, 128, 0, st>>>(h->d_wq[0], x32, (int32_t *)h->ih32.p, N, h->I, C, lcx);
+        k_linear_generic<<<grid, 128, 0, st>>>(h->d_wq[0], x32, (int32_t *)h->ih32.p, N, h->I, C, lcx,
+                                               mk ? mk->ih_linear : nullptr);
         h->launches++;
     }
     CK(cudaEventRecord(h->ev[2], st));
@@ -780,8 +781,17 @@ int run_generic(qgru_handle *h, int T, int B, const int32_t *x32, int32_t *hq, i
         const size_t in_slot = rev ? (size_t)(T - s) : (size_t)s;
         const size_t out_slot = rev ? (size_t)(T - 1 - s) : (size_t)(s + 1);
         dim3 g1((C + 127) / 128, B);
-        k_linear_generic<<<g1, 128, 0, st>>>(h->d_wq[1], hq + in_slot * BH, (int32_t *)h->hh32.p, B, H, C, lch);
+        const size_t row = (size_t)t * B;
+        k_linear_generic<<<g1, 128, 0, st>>>(h->d_wq[1], hq + in_slot * BH, (int32_t *)h->hh32.p, B, H, C, lch,
+                                             mk && mk->hh_linear ? mk->hh_linear + row * C : nullptr);
         dim3 g2((H + 127) / 128, B);
+        if (mk)
+            k_gates_train<<<g2, 128, 0, st>>>((const int32_t *)h->ih32.p + row * C, (const int32_t *)h->hh32.p,
+                                              hq + in_slot * BH, hq + out_slot * BH, vq + row * 4 * H,
+                                              mk->gate_input ? mk->gate_input + row * C : nullptr,
+                                              mk->gate_output ? mk->gate_output + row * C : nullptr,
+                                              mk->h ? mk->h + row * H : nullptr, B, H, h->d_gc);
+        else
         k_gates_generic<<<g2, 128, 0, st>>>((const int32_t *)h->ih32.p + (size_t)t * B * C,
                                             (const int32_t *)h->hh32.p, hq + in_slot * BH,
                                             hq + out_slot * BH, vq ? vq + (size_t)t * B * 4 * H : nullptr, B, H,
@@ -841,7 +851,8 @@ int qgru_forward_i32(qgru_handle *h, int T, int B, const int32_t *x_q, const int
 }
 
 int qgru_forward_i32_train(qgru_handle *h, int T, int B, const int32_t *x_q, const int32_t *h0_q,
-                           int32_t *h_q, int32_t *v_q, unsigned flags, void *stream) {
+                           int32_t *h_q, int32_t *v_q, const qgru_masks *masks, unsigned flags,
+                           void *stream) {
     if (!h || !x_q || !h_q || !v_q) return QGRU_ERR_BAD_ARG;
     int rc = check_forward_args(h, T, B);
     if (rc) return rc;
@@ -858,7 +869,7 @@ int qgru_forward_i32_train(qgru_handle *h, int T, int B, const int32_t *x_q, con
         h0_q, nullptr, nullptr, h_q, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale, ho.zero_point,
         op_qmin(ho), op_qmax(ho), h->d_flags);
     h->launches++;
-    return run_generic(h, T, B, x_q, h_q, v_q, flags, st);
+    return run_generic(h, T, B, x_q, h_q, v_q, flags, st, masks);
 }
 
 int qgru_forward_f32(qgru_handle *h, int T, int B, const float *x, const float *h0, float *h_out,

@@ -84,6 +84,48 @@ __device__ __forceinline__ int32_t gru_cell(const GateConsts &gc, const int32_t 
     return clampi(h_new, gc.h_lo, gc.h_hi);
 }
 
+// piecewise_linear in the training branch (include/quantize_ops_helper.h:760-783): always the
+// segment evaluation, and the two clamp flags (1 = inside the range) are kept.
+__device__ __forceinline__ int32_t activation_keep(const GateConsts &gc, int which, int32_t pre,
+                                                   uint8_t &keep_in, uint8_t &keep_out) {
+    const int32_t q = clampi(pre, gc.in_lo[which], gc.in_hi[which]);
+    keep_in = q == pre;
+    const int32_t raw = lut_raw(gc.lut[which], q);
+    const int32_t out = clampi(raw, gc.out_lo[which], gc.out_hi[which]);
+    keep_out = out == raw;
+    return out;
+}
+
+// gru_cell in training mode: the gate outputs and the seven clamp flags of one cell
+// (src/gru_forward_gpu_quant.cu:296-348).  keep[0..2] gate inputs z, r, n; keep[3..5] gate
+// outputs; keep[6] the new state.
+__device__ __forceinline__ int32_t gru_cell_train(const GateConsts &gc, int32_t ih_z, int32_t ih_r,
+                                                  int32_t ih_n, int32_t hh_z, int32_t hh_r, int32_t hh_n,
+                                                  int32_t h_old, int32_t *gates, uint8_t *keep) {
+    const int32_t z_pre = rescale_diff<false>(ih_z, gc.zp_ih, gc.ih_to[ACT_Z]) +
+                          rescale_diff<false>(hh_z, gc.zp_hh, gc.hh_to[ACT_Z]) + gc.zp_in[ACT_Z];
+    const int32_t z = activation_keep(gc, ACT_Z, z_pre, keep[0], keep[3]);
+    const int32_t r_pre = rescale_diff<false>(ih_r, gc.zp_ih, gc.ih_to[ACT_R]) +
+                          rescale_diff<false>(hh_r, gc.zp_hh, gc.hh_to[ACT_R]) + gc.zp_in[ACT_R];
+    const int32_t r = activation_keep(gc, ACT_R, r_pre, keep[1], keep[4]);
+    const int64_t r_hh = ((int64_t)r - gc.zp_out[ACT_R]) * ((int64_t)hh_n - gc.zp_hh);
+    const int32_t n_pre = rescale_diff<false>(ih_n, gc.zp_ih, gc.ih_to[ACT_N]) +
+                          (int32_t)rescale64(r_hh, gc.rh_to_n) + gc.zp_in[ACT_N];
+    const int32_t n = activation_keep(gc, ACT_N, n_pre, keep[2], keep[5]);
+    const int32_t n_h = rescale_diff<false>(n, gc.zp_out[ACT_N], gc.n_to_h) + gc.zp_h;
+    const int64_t z_d = (int64_t)z - gc.zp_out[ACT_Z];
+    const int64_t old_c = z_d * ((int64_t)h_old - gc.zp_h);
+    const int64_t one_minus = ((int64_t)gc.one_q - z) - gc.zp_out[ACT_Z];
+    const int64_t new_c = one_minus * ((int64_t)n_h - gc.zp_h);
+    const int32_t h_new = (int32_t)rescale64(old_c + new_c, gc.uh_to_h) + gc.zp_h;
+    gates[0] = z;
+    gates[1] = r;
+    gates[2] = n;
+    const int32_t h_c = clampi(h_new, gc.h_lo, gc.h_hi);
+    keep[6] = h_c == h_new;
+    return h_c;
+}
+
 // The same cell with everything that depends on one narrow operand tabulated on the host:
 //   a_*   W*x+bw already rescaled to the gate's input scale, zp_in included (GEMM epilogue)
 //   THZ/THR[hh - hh_lo]      = rescale(hh - zp_hh -> z / r input scale)
@@ -146,9 +188,12 @@ __device__ __forceinline__ int32_t fused_finish_fast(const GateConsts &gc, uint3
 
 // Epilogue of a fused linear layer (src/gru_forward_cpu_quant.cc:130-138).
 __device__ __forceinline__ int32_t linear_epilogue(int64_t acc, int64_t corr, Rescale rs,
-                                                   int32_t zp_out, int32_t lo, int32_t hi) {
+                                                   int32_t zp_out, int32_t lo, int32_t hi,
+                                                   uint8_t *keep = nullptr) {
     const int32_t v = (int32_t)rescale64(acc + corr, rs) + zp_out;
-    return clampi(v, lo, hi);
+    const int32_t c = clampi(v, lo, hi);
+    if (keep) *keep = c == v;
+    return c;
 }
 // The same when acc + corr is known to fit int32 (LinearConsts::fits32).
 __device__ __forceinline__ int32_t linear_epilogue32(int32_t acc, int32_t corr, Rescale rs,

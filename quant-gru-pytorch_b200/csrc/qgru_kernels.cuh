@@ -539,13 +539,14 @@ __global__ void __launch_bounds__(1024, 1) k_recurrence_gemv(const __grid_consta
 // (quantizedGemmBiasFused's arithmetic, src/gru_forward_gpu_quant.cu:110-180).
 __global__ void k_linear_generic(const int32_t *__restrict__ wq, const int32_t *__restrict__ in,
                                  int32_t *__restrict__ out, long long N, int K, int C,
-                                 LinearConsts lc) {
+                                 LinearConsts lc, uint8_t *__restrict__ keep = nullptr) {
     const int m = blockIdx.x * blockDim.x + threadIdx.x;
     const long long n = blockIdx.y;
     if (m >= C || n >= N) return;
     int64_t acc = 0;
     for (int k = 0; k < K; ++k) acc += (int64_t)wq[(size_t)k * C + m] * (int64_t)in[n * K + k];
-    out[n * C + m] = linear_epilogue(acc, lc.corr[m], lc.rs[m], lc.zp_out, lc.lo, lc.hi);
+    out[n * C + m] = linear_epilogue(acc, lc.corr[m], lc.rs[m], lc.zp_out, lc.lo, lc.hi,
+                                     keep ? keep + n * C + m : nullptr);
 }
 
 // v: optional [B][4H] out of this step: update, reset, new gate outputs and the R*h + br row of
@@ -568,6 +569,31 @@ __global__ void k_gates_generic(const int32_t *__restrict__ ih, const int32_t *_
         vb[2 * H] = gates[2];
         vb[3 * H] = hh[w + 2 * H];
     }
+}
+
+// The training form of k_gates_generic: v as above plus the clamp masks of this step (each may be
+// null): gate inputs and gate outputs [B][3H], new state [B][H]; 1 = not clamped.
+__global__ void k_gates_train(const int32_t *__restrict__ ih, const int32_t *__restrict__ hh,
+                              const int32_t *__restrict__ h_in, int32_t *__restrict__ h_out,
+                              int32_t *__restrict__ v, uint8_t *__restrict__ m_in,
+                              uint8_t *__restrict__ m_out, uint8_t *__restrict__ m_h, int B, int H,
+                              const GateConsts *__restrict__ gcp) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = blockIdx.y;
+    if (j >= H || b >= B) return;
+    const size_t w = (size_t)b * 3 * H + j;
+    int32_t gates[3];
+    uint8_t keep[7];
+    h_out[(size_t)b * H + j] = gru_cell_train(*gcp, ih[w], ih[w + H], ih[w + 2 * H], hh[w], hh[w + H],
+                                              hh[w + 2 * H], h_in[(size_t)b * H + j], gates, keep);
+    int32_t *vb = v + (size_t)b * 4 * H + j;
+    vb[0] = gates[0];
+    vb[H] = gates[1];
+    vb[2 * H] = gates[2];
+    vb[3 * H] = hh[w + 2 * H];
+    if (m_in) { m_in[w] = keep[0]; m_in[w + H] = keep[1]; m_in[w + 2 * H] = keep[2]; }
+    if (m_out) { m_out[w] = keep[3]; m_out[w + H] = keep[4]; m_out[w + 2 * H] = keep[5]; }
+    if (m_h) m_h[(size_t)b * H + j] = keep[6];
 }
 
 }  // namespace qgru

@@ -128,9 +128,12 @@ class Handle:
             self.synchronize()
         return h_q
 
-    def forward_i32_train(self, x_q, h0_q=None, reverse=False):
+    def forward_i32_train(self, x_q, h0_q=None, reverse=False, want_masks=False):
         """Training-mode integer forward: (h_q [(T+1),B,H], v_q [T,B,4H]) int32; v_q holds the
-        quantized update / reset / new gate outputs and the R*h + br row of the new gate."""
+        quantized update / reset / new gate outputs and the R*h + br row of the new gate.
+        With want_masks also the five uint8 clamp masks (1 = not clamped) as a third result:
+        [W*x+bw [T*B,3H], R*h+br [T*B,3H], gate inputs [T*B,3H], gate outputs [T*B,3H],
+        h [T*B,H]]."""
         T, B = int(x_q.shape[0]), int(x_q.shape[1])
         H = self.hidden_size
         x_q = _check_tensor(x_q, "x_q", torch.int32, (T, B, self.input_size))
@@ -138,11 +141,17 @@ class Handle:
             h0_q = _check_tensor(h0_q, "h0_q", torch.int32, (B, H))
         h = torch.empty((T + 1, B, H), dtype=torch.int32, device=self._tdev)
         v = torch.empty((T, B, 4 * H), dtype=torch.int32, device=self._tdev)
+        masks, mk = None, None
+        if want_masks:
+            masks = [torch.empty((T * B, 3 * H), dtype=torch.uint8, device=self._tdev) for _ in range(4)]
+            masks.append(torch.empty((T * B, H), dtype=torch.uint8, device=self._tdev))
+            mk = _cabi.Masks(*[m.data_ptr() for m in masks])
         self._ck(self._lib.qgru_forward_i32_train(self._h, T, B, _ptr(x_q), _ptr(h0_q), _ptr(h), _ptr(v),
-                                                  1 if reverse else 0, _stream(self._tdev)),
+                                                  C.byref(mk) if mk is not None else None,
+                                                  _cabi.FLAG_REVERSE if reverse else 0, _stream(self._tdev)),
                  "qgru_forward_i32_train")
         self.synchronize()
-        return h, v
+        return (h, v, masks) if want_masks else (h, v)
 
     def forward_i32_static(self, x_q, h0_q=None, reverse=False, out=None, sync=True):
         """forward_i32 for callers that may not allocate device memory at call time: the

@@ -1,0 +1,199 @@
+"""GPU tests against the reference's own GPU code (the unmodified sources compiled into the
+checker library, driven through the ref_gpu_* functions of oracle/ref_shim.cc): the integer
+forward, its training buffer and clamp masks bit for bit, the histogram collectors bit for bit
+on identical arrays, and the float forward, MinMax ranges and calibration histograms to the
+precision the reference's float forward has on this GPU.  That forward switches cuBLAS to
+tensor-op math (src/gru_forward_gpu.cu:359), i.e. TF32 products with a 10-bit mantissa, so its
+outputs sit about 3e-4 from an fp32 GRU; the 1e-5 bound of the float mode is held against the
+fp32 restatement and torch.nn.GRU in test_gpu_module.py, and here the bound is TF32_RTOL.
+Skipped where the checker library has not been built."""
+import importlib
+
+import numpy as np
+import pytest
+
+from __graft_entry__ import PKG_NAME
+from tests.cases import OP, config_named, gen_weights, gen_x, make_case, params_mod
+
+gru_ops = importlib.import_module(PKG_NAME + ".gru_ops")
+_cabi = importlib.import_module(PKG_NAME + "._cabi")
+pytestmark = pytest.mark.gpu
+
+TF32_RTOL = 2e-3     # relative to the largest magnitude of the compared tensor
+
+
+@pytest.fixture(scope="module")
+def refgpu(reference, cuda_device):
+    from oracle.binding import ReferenceGpu
+    g = ReferenceGpu(reference)
+    if g.device_count() < 1:
+        pytest.skip("the reference library sees no CUDA device")
+    return g
+
+
+def _t(a, dev):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+def _rel_err(got, want):
+    return np.abs(got - want).max() / max(np.abs(want).max(), 1e-30)
+
+
+@pytest.mark.parametrize("cfg_name", ["default", "cfg2", "cfg3", "cfg5", "pot2_asym"])
+@pytest.mark.parametrize("shape", [(5, 6, 20, 40), (4, 20, 48, 512), (6, 3, 80, 256)])
+def test_integer_forward_equals_reference_gpu(reference, refgpu, cuda_device, cfg_name, shape):
+    """h_q of every timestep: product == the reference's GPU integer path == its CPU path."""
+    T, B, I, H = shape
+    case = make_case(seed=31, T=T, B=B, I=I, H=H, checker=reference, config=config_named(cfg_name),
+                     with_h0=(cfg_name == "cfg2"))
+    sc = case.params.scale_list()
+    want = refgpu.forward_i32(T, B, I, H, case.wq, case.x_q, case.h0_q, case.params.c, sc)
+    cpu = reference.forward_i32(T, B, I, H, case.wq, case.x_q, case.h0_q, case.params.c, sc)
+    assert np.array_equal(want, cpu), "the reference's GPU and CPU integer paths differ"
+    with gru_ops.Handle(I, H, device=0) as hd:
+        hd.set_params(case.params)
+        hd.set_weights_i32(*[_t(a, cuda_device) for a in case.wq])
+        got = hd.forward_i32(_t(case.x_q, cuda_device),
+                             _t(case.h0_q, cuda_device) if case.h0_q is not None else None)
+        got = got.cpu().numpy()
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("cfg_name,sigma", [("cfg2", 1.0), ("default", 4.0), ("pot2_asym", 4.0)])
+def test_training_outputs_equal_reference_gpu(oracle, reference, refgpu, cuda_device, cfg_name, sigma):
+    """Training mode: h_q, v_q and the five clamp masks: product == the reference's GPU path ==
+    the oracle.  sigma = 4 feeds inputs four times wider than the calibration saw, so that a
+    good share of the values is clamped and the masks hold both zeros and ones."""
+    T, B, I, H = 5, 4, 24, 72
+    case = make_case(seed=32, T=T, B=B, I=I, H=H, checker=reference, config=config_named(cfg_name))
+    rng = np.random.default_rng(77)
+    x_q = reference.quantize(gen_x(rng, T, B, I, sigma=sigma), case.params.c, OP["x"])
+    sc = case.params.scale_list()
+    want_h, want_v, want_m = refgpu.forward_i32(T, B, I, H, case.wq, x_q, None, case.params.c, sc,
+                                                training=True, masks=True)
+    orc_h, orc_v, orc_m = oracle.forward_i32_train(T, B, I, H, case.wq, x_q, None, case.params.c, sc)
+    assert np.array_equal(orc_h, want_h) and np.array_equal(orc_v, want_v)
+    for k in range(5):
+        assert np.array_equal(orc_m[k], want_m[k]), k
+    with gru_ops.Handle(I, H, device=0) as hd:
+        hd.set_params(case.params)
+        hd.set_weights_i32(*[_t(a, cuda_device) for a in case.wq])
+        got_h, got_v, got_m = hd.forward_i32_train(_t(x_q, cuda_device), want_masks=True)
+    assert np.array_equal(got_h.cpu().numpy(), want_h)
+    assert np.array_equal(got_v.cpu().numpy(), want_v)
+    for k in range(5):
+        assert np.array_equal(got_m[k].cpu().numpy(), want_m[k]), k
+    if sigma > 1.0:
+        assert any(0 < m.mean() < 1 for m in want_m), "no clamp was exercised"
+
+
+@pytest.mark.parametrize("shape", [(6, 5, 20, 40), (12, 33, 64, 128), (3, 2, 300, 520)])
+def test_float_mode_matches_reference_gpu(refgpu, cuda_device, shape):
+    """fp32 GRU against hasteGRUForward (TF32 products) on the same device."""
+    T, B, I, H = shape
+    rng = np.random.default_rng(5)
+    W, R, bw, br = gen_weights(rng, I, H)
+    x = gen_x(rng, T, B, I)
+    h0 = (rng.standard_normal((B, H)) * 0.3).astype(np.float32)
+    want_h, want_v = refgpu.forward_float(T, B, I, H, W, R, bw, br, x, h0, want_v=True)
+    with gru_ops.Handle(I, H, device=0) as hd:
+        h, v = hd.forward_float(*[_t(a, cuda_device) for a in (W, R, bw, br, x)], _t(h0, cuda_device),
+                                want_v=True)
+    assert _rel_err(h.cpu().numpy(), want_h) <= TF32_RTOL
+    assert _rel_err(v.cpu().numpy(), want_v) <= TF32_RTOL
+
+
+def test_minmax_ranges_match_reference_gpu(refgpu, cuda_device):
+    """forwardWithCalibrationGPU(MINMAX) over three batches: computed ranges to TF32 precision,
+    the ranges of x and of the weights exactly."""
+    T, B, I, H = 9, 7, 20, 48
+    rng = np.random.default_rng(9)
+    W, R, bw, br = gen_weights(rng, I, H)
+    batches = [gen_x(rng, T, B, I, "outliers") for _ in range(3)]
+    want, got = params_mod.Ranges(H), params_mod.Ranges(H)
+    with gru_ops.Handle(I, H, device=0) as hd:
+        dW = [_t(a, cuda_device) for a in (W, R, bw, br)]
+        for xb in batches:
+            refgpu.calibrate_minmax(T, B, I, H, W, R, bw, br, xb, want)
+            hd.calibrate_minmax(*dW, _t(xb, cuda_device), got)
+    idx = [0, 1] + list(range(6, 17))
+    span = np.maximum(np.abs(want.max_v[idx]), np.abs(want.min_v[idx]))
+    assert np.all(np.abs(got.min_v[idx] - want.min_v[idx]) <= TF32_RTOL * span + 1e-6)
+    assert np.all(np.abs(got.max_v[idx] - want.max_v[idx]) <= TF32_RTOL * span + 1e-6)
+    for n in params_mod.WEIGHT_OPS:
+        assert np.array_equal(got.ch_min[n], want.ch_min[n]) and np.array_equal(got.ch_max[n], want.ch_max[n])
+    assert got.min_v[OP["x"]] == want.min_v[OP["x"]] and got.max_v[OP["x"]] == want.max_v[OP["x"]]
+
+
+def _same(a, b):
+    c1, mn1, mx1, t1 = a
+    c2, mn2, mx2, t2 = b
+    assert (mn1, mx1, t1) == (mn2, mx2, t2), ((mn1, mx1, t1), (mn2, mx2, t2))
+    assert np.array_equal(c1, c2), np.abs(c1 - c2).sum()
+
+
+def test_collector_equals_reference_gpu_collector(oracle, refgpu, cuda_device):
+    """One collector over batches with growing and shrinking spread: product == the reference's
+    GPUHistogramCollector == the oracle's restatement of it, counts and range, bit for bit."""
+    rng = np.random.default_rng(3)
+    hs = params_mod.Histograms(8, device=0)
+    for idx, scales in enumerate(([1.0, 1.0, 1.7, 0.5, 3.0], [0.01, 5.0, 5.0], [2.0, 1.0, 1.0, 1.0])):
+        want = refgpu.hist_new(2048)
+        orc = oracle.hist_new(2048)
+        for s in scales:
+            data = (rng.normal(0.3, s, 50000)).astype(np.float32)
+            hs.collect(idx, _t(data, cuda_device))
+            want.collect(data)
+            orc.collect(data)
+            _same(orc.get(), want.get())
+            _same(hs.get(idx), want.get())
+    hs.close()
+
+
+@pytest.mark.parametrize("gran", ["PER_CHANNEL", "PER_GATE", "PER_TENSOR"])
+def test_calibration_histograms_match_reference_gpu(refgpu, cuda_device, gran):
+    """Two batches through the calibration forward of both libraries.  Histograms of tensors that
+    are read (x, the weights) are equal bit for bit; histograms of computed tensors agree in
+    total, in range to TF32 precision, and in shape (cumulative counts within 1 % of the total:
+    a range that differs by 1e-3 of its span shifts every bin edge by up to two bins)."""
+    T, B, I, H = 7, 6, 20, 40
+    rng = np.random.default_rng(9)
+    W, R, bw, br = gen_weights(rng, I, H)
+    g = {"PER_CHANNEL": _cabi.PER_CHANNEL, "PER_GATE": _cabi.PER_GATE, "PER_TENSOR": _cabi.PER_TENSOR}[gran]
+    cfg = params_mod.OperatorQuantConfig()
+    for n in params_mod.WEIGHT_OPS:
+        cfg.granularity[n] = g
+    p = params_mod.GRUQuantParams(H, cfg)
+    hs = params_mod.Histograms(H, device=0)
+    ref_set = refgpu.histset_new(H, 2048)
+    with gru_ops.Handle(I, H, device=0) as hd:
+        dev = [_t(a, cuda_device) for a in (W, R, bw, br)]
+        for batch in range(2):
+            x = gen_x(rng, T, B, I, sigma=1.0 + batch)
+            hd.calibrate_hist(*dev, _t(x, cuda_device), hs, [g] * 4)
+            ref_set.calibrate(T, B, I, H, W, R, bw, br, x, p.c, use_percentile=True)
+    ref_set.sync()
+    _same(hs.get(OP["x"]), ref_set.get(OP["x"]))
+    for name in ("h", "weight_ih_linear", "weight_hh_linear", "update_gate_input", "update_gate_output",
+                 "reset_gate_input", "reset_gate_output", "new_gate_input", "new_gate_output",
+                 "mul_reset_hidden", "mul_new_contribution", "mul_old_contribution"):
+        c1, mn1, mx1, t1 = hs.get(OP[name])
+        c2, mn2, mx2, t2 = ref_set.get(OP[name])
+        assert t1 == t2, name
+        span = max(abs(mx2 - mn2), 1e-30)
+        assert abs(mn1 - mn2) <= TF32_RTOL * span + 1e-7 and abs(mx1 - mx2) <= TF32_RTOL * span + 1e-7, name
+        moved = np.abs(np.cumsum(c1.astype(np.float64)) - np.cumsum(c2.astype(np.float64))).max()
+        assert moved <= max(3.0, 1e-2 * t1), (name, moved)
+    C3 = 3 * H
+    for k, name in enumerate(("W", "R", "bw", "br")):
+        if gran == "PER_TENSOR":
+            _same(hs.get(OP[name]), ref_set.get(OP[name]))
+        elif gran == "PER_GATE":
+            for gi in range(3):
+                _same(hs.get(_cabi.HIST_GATE0 + 3 * k + gi), ref_set.get(_cabi.HIST_GATE0 + 3 * k + gi))
+        else:
+            for c_idx in (0, 1, H + 3, C3 - 1):
+                _same(hs.get(_cabi.HIST_CHANNEL0 + k * C3 + c_idx),
+                      ref_set.get(_cabi.HIST_CHANNEL0 + k * C3 + c_idx))
+    hs.close()

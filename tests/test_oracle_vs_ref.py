@@ -80,3 +80,35 @@ def test_training_buffer_matches_reference(oracle, reference):
         h_o, v_o = oracle.forward_i32_v(*args)
         assert np.array_equal(h_r, h_o) and np.array_equal(v_r, v_o)
         assert np.array_equal(h_o, oracle.forward_i32(*args))
+
+
+def test_training_masks_of_the_oracle(oracle, reference):
+    """The reference's CPU path writes no clamp masks, so on the CPU the oracle's masks are held
+    against what they must imply: same h_q and v_q as the plain training forward, and wherever a
+    mask is 0 the clamped value sits on a bound of its range (the GPU tests compare the masks
+    themselves with the reference's GPU path)."""
+    from tests.cases import gen_x
+    case = make_case(91, 6, 4, 12, 20, reference, config_named("default"))
+    p = case.params.c
+    x_q = reference.quantize(gen_x(np.random.default_rng(4), 6, 4, 12, sigma=5.0), p, OP["x"])
+    args = (case.T, case.B, case.I, case.H, case.wq, x_q, None, p, case.params.scale_list())
+    h, v, m = oracle.forward_i32_train(*args)
+    h_r, v_r = reference.forward_i32_v(*args)
+    assert np.array_equal(h, h_r) and np.array_equal(v, v_r)
+    H = case.H
+
+    def bounds(name):
+        o = p.op[OP[name]]
+        lo = 0 if o.is_unsigned else -(1 << (o.bits - 1))
+        return lo, lo + (1 << o.bits) - 1
+
+    lo, hi = bounds("h")
+    clamped = m[4].reshape(case.T, case.B, H) == 0
+    assert np.all((h[1:][clamped] == lo) | (h[1:][clamped] == hi))
+    gate_out = m[3].reshape(case.T, case.B, 3 * H)
+    for g, name in enumerate(("update_gate_output", "reset_gate_output", "new_gate_output")):
+        lo, hi = bounds(name)
+        vals = v[:, :, g * H:(g + 1) * H][gate_out[:, :, g * H:(g + 1) * H] == 0]
+        assert np.all((vals == lo) | (vals == hi))
+    assert all(set(np.unique(a)) <= {0, 1} for a in m)
+    assert m[0].mean() < 1.0, "inputs five times wider than calibrated must clamp W*x somewhere"
