@@ -226,6 +226,19 @@ QGRU_API int qgru_forward_i32_train(qgru_handle *h, int T, int B, const int32_t 
                                     const int32_t *h0_q, int32_t *h_q, int32_t *v_q,
                                     const qgru_masks *masks, unsigned flags, void *stream);
 
+/* quantGRUForwardFP (src/gru_interface.cc:894-995, src/gru_forward_gpu_quant_fp.cu), inference
+ * mode: the float-storage quantized forward that QuantGRU.forward runs by default and that QAT
+ * trains against.  Tensors hold quantized values, the requantization between operators is
+ * float arithmetic (round(x * scale_ratio)) and the gates are the real sigmoid / tanh of the
+ * dequantized gate inputs, not the piecewise-linear tables.  x [T,B,I], h0 [B,H] or NULL,
+ * h_out [(T+1),B,H] (dequantized, slot layout as qgru_forward_i32), x_q_out [T,B,I] or NULL
+ * (the quantized input as floats): device fp32.  Needs 8-bit W, R, x and h (else
+ * QGRU_ERR_UNSUPPORTED); weights as set by qgru_set_weights_f32 / _i32.  The matrix products
+ * are exact integer sums; the reference's are fp32 sums of the same integers, exact below
+ * 2^24, and every float operation after them is the reference's, in its order. */
+QGRU_API int qgru_forward_fstorage(qgru_handle *h, int T, int B, const float *x, const float *h0,
+                                   float *h_out, float *x_q_out, unsigned flags, void *stream);
+
 /* quantGRUForwardInt (src/gru_interface.cc:610-725), inference mode: float in, float out.
  *   x [T,B,I] f32 device, h0 [B,H] f32 device or NULL, h [(T+1),B,H] f32 device out,
  *   x_q_out [T,B,I] int32 device or NULL. */

@@ -235,6 +235,19 @@ class Oracle(_Checker):
         return (h, v) if want_v else h
 
 
+    def forward_fstorage(self, T, B, I, H, wq, x, h0, params, sc):
+        """Float-storage quantized forward (orc_forward_fstorage): (h dequantized, x_q floats)."""
+        x = np.ascontiguousarray(x, np.float32)
+        h = np.zeros((T + 1, B, H), np.float32)
+        xq = np.zeros((T, B, I), np.float32)
+        h0p = _f(np.ascontiguousarray(h0, np.float32)) if h0 is not None else None
+        rc = self.lib.orc_forward_fstorage(T, B, I, H, *[_i(np.ascontiguousarray(a, np.int32)) for a in wq],
+                                           _f(x), h0p, C.byref(params), *[_f(a) for a in sc], _f(h), _f(xq))
+        if rc:
+            raise RuntimeError("forward_fstorage failed")
+        return h, xq
+
+
 class Reference(_Checker):
     prefix = "ref_"
     kind = "reference"
@@ -293,6 +306,21 @@ class ReferenceGpu:
                                        _f(h), _f(v) if v is not None else None)
         self._check(rc, "ref_gpu_forward_float")
         return (h, v) if want_v else h
+
+    def forward_fstorage(self, T, B, I, H, W, R, bw, br, x, h0, params, sc):
+        """quantGRUForwardFP, inference: (h dequantized, x_q as floats, [W_q, R_q, bw_q, br_q] as
+        floats)."""
+        h = np.zeros((T + 1, B, H), np.float32)
+        xq = np.zeros((T, B, I), np.float32)
+        wq = [np.zeros((I, 3 * H), np.float32), np.zeros((H, 3 * H), np.float32),
+              np.zeros(3 * H, np.float32), np.zeros(3 * H, np.float32)]
+        rc = self._fn("forward_fstorage")(T, B, I, H, _f(W), _f(R), _f(bw), _f(br),
+                                          _f(np.ascontiguousarray(x, np.float32)),
+                                          _f(np.ascontiguousarray(h0, np.float32)) if h0 is not None else None,
+                                          C.byref(params), *[_f(a) for a in sc], _f(h), _f(xq),
+                                          *[_f(a) for a in wq])
+        self._check(rc, "ref_gpu_forward_fstorage")
+        return h, xq, wq
 
     def calibrate_minmax(self, T, B, I, H, W, R, bw, br, x, ranges):
         """forwardWithCalibrationGPU(MINMAX): folds one batch into `ranges`; returns h."""

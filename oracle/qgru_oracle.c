@@ -1073,7 +1073,8 @@ ORC_API int orc_calibrate_from_histogram(const float *counts, int bins, float mi
 /* One histogram collector with the rules of GPUHistogramCollector::collect
  * (src/calibration_gpu.cu:820-876) and the arithmetic of its kernels (histogram_kernel_shared
  * :66-104, redistribute_histogram_kernel :116-158, build_histogram :499-522,
- * redistribute_histogram :524-540), evaluated one operation at a time. */
+ * redistribute_histogram :524-540), evaluated one operation at a time except for the two
+ * multiply-adds of the redistribution kernel, which nvcc fuses when it compiles the reference. */
 typedef struct orc_hist {
     int bins;
     float *counts;
@@ -1121,10 +1122,10 @@ static void hist_redistribute(const float *src, float smin, float sbw, float *ds
     for (int i = 0; i < bins; ++i) {
         const float cnt = src[i];
         if (cnt <= 0) continue;
-        const float start = smin + (float)i * sbw;
+        const float start = fmaf((float)i, sbw, smin);      /* as nvcc contracts the kernel's a + i * w */
         int d = (int)((start - dmin) * inv);
         if (d > bins - 1) d = bins - 1;
-        const float end = dmin + dbw * (float)(d + 1);
+        const float end = fmaf(dbw, (float)(d + 1), dmin);
         const float split = rintf(((end - start) / sbw) * cnt);
         const float first = fminf(split, cnt);
         dst[d] += first;
@@ -1192,5 +1193,145 @@ ORC_API int orc_hist_get(const orc_hist *h, float *counts, float *min_val, float
     *min_val = h->min_val;
     *max_val = h->max_val;
     *total = h->valid ? h->total : 0;
+    return 0;
+}
+
+/* ------------------------------------------- float-storage quantized forward (inference) */
+
+static float fs_clampf(float v, const qgru_op *o) {
+    const float lo = (float)qmin_of(o->bits, eff_unsigned(o)), hi = (float)qmax_of(o->bits, eff_unsigned(o));
+    return fmaxf(lo, fminf(v, hi));   /* clamp_f, include/quantize_ops_helper.h:416-431 */
+}
+/* quantize_f(src, FixedPointScale, zp, bw), include/quantize_ops_helper.h:514-519: the zero
+ * point is added BEFORE the rounding, unlike quantize() of the integer path. */
+static float fs_quantize(float x, float scale, int32_t zp, const qgru_op *o) {
+    return fs_clampf(rintf(x / scale + (float)zp), o);
+}
+/* biasRescaleInline, src/gru_forward_gpu_quant_fp.cu:117-142. */
+static float fs_linear(float gemm, float wsum_zp, float bias, float inv_bias, float inv_gemm,
+                       const qgru_op *out) {
+    const float val = gemm - wsum_zp;
+    const float bias_term = rintf(bias * inv_bias);
+    const float combined = val + bias_term;
+    return fs_clampf(rintf(combined * inv_gemm) + (float)out->zero_point, out);
+}
+/* real_sigmoid_f / real_tanh_f, include/quantize_ops_helper.h:687-720. */
+static float fs_act(float q_x, const qgru_op *in, const qgru_op *out, int is_tanh) {
+    const float x = (q_x - (float)in->zero_point) * in->scale;
+    const float y = is_tanh ? tanhf(x) : 1.0f / (1.0f + expf(-x));
+    return fs_clampf(rintf(y / out->scale + (float)out->zero_point), out);
+}
+
+/* quantGRUForwardFP, inference mode (src/gru_interface.cc:894-995; ForwardPassQuantFP and
+ * PointwiseOperationsFP, src/gru_forward_gpu_quant_fp.cu:572-770, 821-1003, 1177-1232): quantized
+ * values held as floats, float requantization, real sigmoid / tanh.  W..br are the quantized
+ * weights (the values quantizeGRUWeights produces are those of the integer path).  The
+ * reference's two products are fp32 SGEMMs over integer-valued operands; they are evaluated here
+ * as exact integer sums converted to float, which is what an fp32 sum gives below 2^24.  expf
+ * and tanhf are the host's, the reference's are CUDA's: a gate output can differ by one step
+ * where the two libraries round a value across a .5 boundary.
+ * h [(T+1),B,H] dequantized; x_q_out [T,B,I] (quantized x as floats) may be NULL. */
+ORC_API int orc_forward_fstorage(int T, int B, int I, int H, const int32_t *W, const int32_t *R,
+                                 const int32_t *bw, const int32_t *br, const float *x, const float *h0,
+                                 const qgru_params *p, const float *sW, const float *sR,
+                                 const float *sbw, const float *sbr, float *h, float *x_q_out) {
+    if (p->hidden != H) return 1;
+    const int C = 3 * H, pot2 = p->use_pot2 != 0;
+    const size_t NH = (size_t)B * H;
+    const qgru_op *ox = &p->op[QGRU_OP_X], *oh = &p->op[QGRU_OP_H];
+    const qgru_op *oih = &p->op[QGRU_OP_IH_LINEAR], *ohh = &p->op[QGRU_OP_HH_LINEAR];
+    const qgru_op *ozi = &p->op[QGRU_OP_UPDATE_IN], *ozo = &p->op[QGRU_OP_UPDATE_OUT];
+    const qgru_op *ori = &p->op[QGRU_OP_RESET_IN], *oro = &p->op[QGRU_OP_RESET_OUT];
+    const qgru_op *oni = &p->op[QGRU_OP_NEW_IN], *ono = &p->op[QGRU_OP_NEW_OUT];
+    uint16_t m;
+    int8_t s;
+    if (to_fixed_scale(ox->scale, pot2, &m, &s)) return 1;
+    const float x_scale = decode_scale(m, s);
+    if (to_fixed_scale(oh->scale, pot2, &m, &s)) return 1;
+    const float h_scale = decode_scale(m, s);
+    /* setRescaleParam, src/gru_forward_gpu_quant_fp.cu:821-1003: ratios of the stored scales */
+    const float ih_to_z = oih->scale / ozi->scale, hh_to_z = ohh->scale / ozi->scale;
+    const float ih_to_r = oih->scale / ori->scale, hh_to_r = ohh->scale / ori->scale;
+    const float ih_to_n = oih->scale / oni->scale;
+    const float rh_to_n = (oro->scale * ohh->scale) / oni->scale;
+    const float one_q = rintf(1.0f / ozo->scale) + (float)ozo->zero_point;
+    const float uh_to_h = (ozo->scale * oh->scale) / oh->scale;
+    const float n_to_h = ono->scale / oh->scale;
+    const float zp_x = (float)ox->zero_point, zp_h = (float)oh->zero_point;
+    const float zp_ih = (float)oih->zero_point, zp_hh = (float)ohh->zero_point;
+
+    float *cst = (float *)malloc(sizeof(float) * 6 * (size_t)C);
+    float *xq = (float *)malloc(sizeof(float) * (size_t)T * B * I);
+    float *hq = (float *)malloc(sizeof(float) * 2 * NH);
+    float *ih = (float *)malloc(sizeof(float) * (size_t)C), *hh = (float *)malloc(sizeof(float) * (size_t)C);
+    int64_t *acc = (int64_t *)malloc(sizeof(int64_t) * (size_t)C);
+    if (!cst || !xq || !hq || !ih || !hh || !acc) { free(cst); free(xq); free(hq); free(ih); free(hh); free(acc); return 1; }
+    float *inv_gx = cst, *inv_bw = cst + C, *inv_gh = cst + 2 * C, *inv_br = cst + 3 * C;
+    float *wsx = cst + 4 * C, *wsh = cst + 5 * C;
+    for (int c = 0; c < C; ++c) {
+        const float s_wx = sW[c] * ox->scale, s_rh = sR[c] * oh->scale;
+        inv_gx[c] = s_wx / oih->scale;
+        inv_bw[c] = sbw[c] / s_wx;
+        inv_gh[c] = s_rh / ohh->scale;
+        inv_br[c] = sbr[c] / s_rh;
+        /* computeWeightSumKernel, :442-458: float sum of the column, times the zero point */
+        float sum = 0.0f;
+        for (int k = 0; k < I; ++k) sum += (float)W[(size_t)k * C + c];
+        wsx[c] = ox->zero_point != 0 ? sum * zp_x : 0.0f;
+        sum = 0.0f;
+        for (int k = 0; k < H; ++k) sum += (float)R[(size_t)k * C + c];
+        wsh[c] = oh->zero_point != 0 ? sum * zp_h : 0.0f;
+    }
+    for (size_t i = 0; i < (size_t)T * B * I; ++i) {
+        xq[i] = fs_quantize(x[i], x_scale, ox->zero_point, ox);
+        if (x_q_out) x_q_out[i] = xq[i];
+    }
+    float *cur = hq, *nxt = hq + NH;
+    for (size_t i = 0; i < NH; ++i) {
+        cur[i] = h0 ? fs_quantize(h0[i], h_scale, oh->zero_point, oh) : zp_h;
+        h[i] = (cur[i] - zp_h) * h_scale;
+    }
+    for (int t = 0; t < T; ++t) {
+        for (int b = 0; b < B; ++b) {
+            const float *xr = xq + ((size_t)t * B + b) * I, *hr = cur + (size_t)b * H;
+            for (int c = 0; c < C; ++c) acc[c] = 0;
+            for (int k = 0; k < I; ++k) {
+                const int64_t xv = (int64_t)xr[k];
+                const int32_t *wr = W + (size_t)k * C;
+                for (int c = 0; c < C; ++c) acc[c] += (int64_t)wr[c] * xv;
+            }
+            for (int c = 0; c < C; ++c)
+                ih[c] = fs_linear((float)acc[c], wsx[c], (float)bw[c], inv_bw[c], inv_gx[c], oih);
+            for (int c = 0; c < C; ++c) acc[c] = 0;
+            for (int k = 0; k < H; ++k) {
+                const int64_t hv = (int64_t)hr[k];
+                const int32_t *rr = R + (size_t)k * C;
+                for (int c = 0; c < C; ++c) acc[c] += (int64_t)rr[c] * hv;
+            }
+            for (int c = 0; c < C; ++c)
+                hh[c] = fs_linear((float)acc[c], wsh[c], (float)br[c], inv_br[c], inv_gh[c], ohh);
+            for (int j = 0; j < H; ++j) {
+                /* computeUpdateGateFP / computeResetGateFP, :153-239 */
+                float a = rintf((ih[j] - zp_ih) * ih_to_z), c2 = rintf((hh[j] - zp_hh) * hh_to_z);
+                const float u = fs_act(fs_clampf(a + c2 + (float)ozi->zero_point, ozi), ozi, ozo, 0);
+                a = rintf((ih[j + H] - zp_ih) * ih_to_r);
+                c2 = rintf((hh[j + H] - zp_hh) * hh_to_r);
+                const float r = fs_act(fs_clampf(a + c2 + (float)ori->zero_point, ori), ori, oro, 0);
+                /* computeNewGateFP, :241-290 */
+                const float rh = rintf(((r - (float)oro->zero_point) * (hh[j + 2 * H] - zp_hh)) * rh_to_n);
+                a = rintf((ih[j + 2 * H] - zp_ih) * ih_to_n);
+                const float n = fs_act(fs_clampf(a + rh + (float)oni->zero_point, oni), oni, ono, 1);
+                /* computeHiddenStateFP, :302-372 */
+                const float n_h = rintf((n - (float)ono->zero_point) * n_to_h) + zp_h;
+                const float old_c = (u - (float)ozo->zero_point) * (hr[j] - zp_h);
+                const float new_c = ((one_q - u) - (float)ozo->zero_point) * (n_h - zp_h);
+                const float hn = fs_clampf(rintf((old_c + new_c) * uh_to_h) + zp_h, oh);
+                nxt[(size_t)b * H + j] = hn;
+                h[(size_t)(t + 1) * NH + (size_t)b * H + j] = (hn - zp_h) * h_scale;
+            }
+        }
+        float *tmp = cur; cur = nxt; nxt = tmp;
+    }
+    free(cst); free(xq); free(hq); free(ih); free(hh); free(acc);
     return 0;
 }

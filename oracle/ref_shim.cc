@@ -601,6 +601,33 @@ int ref_gpu_forward_float(int T, int B, int I, int H, const float *W, const floa
     });
 }
 
+// quantGRUForwardFP (src/gru_interface.cc:894), inference mode: the float-storage quantized
+// forward.  Returns h (dequantized) and, where asked, the quantized x and weights as floats.
+int ref_gpu_forward_fstorage(int T, int B, int I, int H, const float *W, const float *R,
+                             const float *bw, const float *br, const float *x, const float *h0,
+                             const qgru_params *p, const float *sW, const float *sR, const float *sbw,
+                             const float *sbr, float *h, float *x_q_out, float *W_q_out,
+                             float *R_q_out, float *bw_q_out, float *br_q_out) {
+    return guarded([&] {
+        GRUQuantParams q = fromPod(*p, sW, sR, sbw, sbr);
+        const size_t C3 = size_t(H) * 3, TB = size_t(T) * B;
+        DevBuf<float> dW(W, size_t(I) * C3), dR(R, size_t(H) * C3), dbw(bw, C3), dbr(br, C3),
+            dx(x, TB * I), dh0(h0, size_t(B) * H), dh((TB + B) * H);
+        DevBuf<float> qW(size_t(I) * C3), qR(size_t(H) * C3), qbw(C3), qbr(C3), qx(TB * I);
+        dh.zero();
+        quantGRUForwardFP(false, T, B, I, H, dW.p, dR.p, dbw.p, dbr.p, dx.p, dh0.p, q, blasHandle(),
+                          dh.p, nullptr, qW.p, qR.p, qbw.p, qbr.p, qx.p, nullptr, nullptr, nullptr,
+                          nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr);
+        cudaOk(cudaDeviceSynchronize(), "quantGRUForwardFP");
+        dh.toHost(h);
+        qx.toHost(x_q_out);
+        qW.toHost(W_q_out);
+        qR.toHost(R_q_out);
+        qbw.toHost(bw_q_out);
+        qbr.toHost(br_q_out);
+    });
+}
+
 // forwardWithCalibrationGPU (src/gru_interface.cc:1283), MinMax: folds one batch into `r`.
 int ref_gpu_calibrate_minmax(int T, int B, int I, int H, const float *W, const float *R,
                              const float *bw, const float *br, const float *x, qgru_ranges *r,

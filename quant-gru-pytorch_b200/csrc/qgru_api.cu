@@ -415,6 +415,7 @@ int qgru_set_params(qgru_handle *h, const qgru_params *p, const float *scale_W,
     for (int k = 0; k < 4; ++k)
         CK(cudaMemcpy(h->d_wscale[k], wscale[k].data(), C * sizeof(float), cudaMemcpyHostToDevice));
     h->params_set = true;
+    h->fs_ready = false;
     return QGRU_OK;
 }
 
@@ -1150,3 +1151,5 @@ extern "C" int qgru_forward_i32_static(qgru_handle *h, int T, int B, const int32
     h->plan_text = "path=int8 gemm=simt_dp4a rec=dp4a workspace=static";
     return QGRU_OK;
 }
+
+#include "qgru_fstorage.cuh"

@@ -1,0 +1,295 @@
+// Float-storage quantized forward: the reference's quantGRUForwardFP (src/gru_interface.cc:894-995,
+// src/gru_forward_gpu_quant_fp.cu), inference mode.  Every tensor holds quantized values, but the
+// requantization between operators is float arithmetic (round(x * scale_ratio)) and the gates
+// are the real sigmoid / tanh on dequantized inputs - the arithmetic QAT trains against.
+//
+// The reference stores the quantized values in fp32 and multiplies with cuBLAS SGEMM.  Here the
+// operands stay 8 bit: the two matrix products run as exact int32 dp4a GEMMs on the packed
+// weights the integer path already holds (an fp32 sum of integer products below 2^24 is exact
+// too, so both give the same number), and one kernel per step then does what
+// PointwiseOperationsFP does, in the same float operations and in the same order, so that results
+// agree with the reference bit for bit wherever its fp32 sums were exact.
+//
+// Included at the end of qgru_api.cu (it shares that file's kernels).
+#pragma once
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+#include "qgru_handle.h"
+#include "qgru_internal.h"
+#include "qgru_kernels.cuh"
+
+namespace qgru {
+
+// GateQuantParamsFP + the scalar part of LinearRescaleParamsFP
+// (ForwardPassQuantFP::setRescaleParam, src/gru_forward_gpu_quant_fp.cu:821-1003).
+struct FsConsts {
+    float zp_x, zp_h, zp_ih, zp_hh;
+    float zp_in[3], zp_out[3];      // gate inputs / outputs: z, r, n
+    float s_in[3], s_out[3];
+    float ih_to[3];                 // weight_ih_linear -> gate input
+    float hh_to[2];                 // weight_hh_linear -> z, r input
+    float rh_to_n;                  // (r * hh_n) -> new gate input
+    float n_to_h, uh_to_h, one_q;
+    float ih_lo, ih_hi, hh_lo, hh_hi, h_lo, h_hi;
+    float in_lo[3], in_hi[3], out_lo[3], out_hi[3];
+    float h_scale;                  // decoded scale of h, for the dequantized output
+    int h_bits;                     // 8: signed state bytes, 9: unsigned
+};
+
+// per-channel float arrays, one block of 4 * C floats on the device
+struct FsChannels {
+    const float *inv_gemm_x, *inv_bw, *inv_gemm_h, *inv_br;
+};
+
+__device__ __forceinline__ float fs_clamp(float v, float lo, float hi) { return fmaxf(lo, fminf(v, hi)); }
+
+// quantize_f (include/quantize_ops_helper.h:514-519): the zero point is added before rounding.
+__device__ __forceinline__ float fs_quantize(float x, float scale, float zp, float lo, float hi) {
+    return fs_clamp(rintf(x / scale + zp), lo, hi);
+}
+
+// fp32 activations -> 8-bit rows padded to Kpad; optionally the quantized values as floats.
+__global__ void k_fs_quantize_rows(const float *__restrict__ x, uint8_t *__restrict__ out8,
+                                   float *__restrict__ xq_out, long long rows, int K, int Kpad,
+                                   float scale, float zp, float lo, float hi) {
+    const int kw = Kpad >> 2;
+    const long long total = rows * kw;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long row = i / kw;
+        const int k0 = (int)(i - row * kw) * 4;
+        unsigned packed = 0;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int k = k0 + u;
+            int q = 0;
+            if (k < K) {
+                const float qf = fs_quantize(x[row * K + k], scale, zp, lo, hi);
+                if (xq_out) xq_out[row * K + k] = qf;
+                q = (int)qf;
+            }
+            packed |= ((unsigned)q & 0xffu) << (8 * u);
+        }
+        reinterpret_cast<unsigned *>(out8)[i] = packed;
+    }
+}
+
+// Initial state: quantize_f(h0) or the zero point (src/gru_interface.cc:949-961), into the
+// 8-bit state rows and, dequantized, into slot `slot` of the output.
+__global__ void k_fs_init_state(const float *__restrict__ h0, uint8_t *__restrict__ h8,
+                                float *__restrict__ h_out, int B, int H, int Hpad, long long slot,
+                                FsConsts fc) {
+    const long long total = (long long)B * Hpad;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int b = (int)(i / Hpad), j = (int)(i % Hpad);
+        float q = 0.f;
+        if (j < H) {
+            q = h0 ? fs_quantize(h0[(size_t)b * H + j], fc.h_scale, fc.zp_h, fc.h_lo, fc.h_hi) : fc.zp_h;
+            h_out[slot * B * H + (long long)b * H + j] = (q - fc.zp_h) * fc.h_scale;
+        }
+        h8[i] = (uint8_t)(int)q;
+    }
+}
+
+// biasRescaleInline (src/gru_forward_gpu_quant_fp.cu:117-142): acc is the exact integer
+// sum_k W*x, wsum the integer column sum of the quantized weights.
+__device__ __forceinline__ float fs_linear(int acc, int wsum, float zp_in, float bias, float inv_bias,
+                                           float inv_gemm, float zp_out, float lo, float hi) {
+    const float val = (float)acc - (float)wsum * zp_in;
+    const float bias_term = rintf(bias * inv_bias);
+    const float combined = val + bias_term;
+    return fs_clamp(rintf(combined * inv_gemm) + zp_out, lo, hi);
+}
+
+__device__ __forceinline__ float fs_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// PointwiseOperationsFP<false, false> (src/gru_forward_gpu_quant_fp.cu:572-770): one thread per
+// (hidden unit, batch row).
+__global__ void k_fs_cell(const int32_t *__restrict__ ih_acc, const int32_t *__restrict__ hh_acc,
+                          const int32_t *__restrict__ wsum_x, const int32_t *__restrict__ wsum_h,
+                          const int32_t *__restrict__ bw_q, const int32_t *__restrict__ br_q,
+                          FsChannels ch, const uint8_t *__restrict__ h8_in, uint8_t *__restrict__ h8_out,
+                          float *__restrict__ h_out, int B, int H, int Hpad, FsConsts fc) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = blockIdx.y;
+    if (j >= H || b >= B) return;
+    const size_t w = (size_t)b * 3 * H + j;
+    float ih[3], hh[3];
+#pragma unroll
+    for (int g = 0; g < 3; ++g) {
+        const int m = j + g * H;
+        ih[g] = fs_linear(ih_acc[w + g * H], wsum_x[m], fc.zp_x, (float)bw_q[m], ch.inv_bw[m],
+                          ch.inv_gemm_x[m], fc.zp_ih, fc.ih_lo, fc.ih_hi);
+        hh[g] = fs_linear(hh_acc[w + g * H], wsum_h[m], fc.zp_h, (float)br_q[m], ch.inv_br[m],
+                          ch.inv_gemm_h[m], fc.zp_hh, fc.hh_lo, fc.hh_hi);
+    }
+    // update and reset gates (computeUpdateGateFP / computeResetGateFP, :153-239)
+    float gate[2];
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        const float a = rintf((ih[g] - fc.zp_ih) * fc.ih_to[g]);
+        const float c = rintf((hh[g] - fc.zp_hh) * fc.hh_to[g]);
+        const float in = fs_clamp(a + c + fc.zp_in[g], fc.in_lo[g], fc.in_hi[g]);
+        const float y = fs_sigmoid((in - fc.zp_in[g]) * fc.s_in[g]);
+        gate[g] = fs_clamp(rintf(y / fc.s_out[g] + fc.zp_out[g]), fc.out_lo[g], fc.out_hi[g]);
+    }
+    const float u = gate[0], r = gate[1];
+    // new gate (computeNewGateFP, :241-290)
+    const float rh = rintf(((r - fc.zp_out[1]) * (hh[2] - fc.zp_hh)) * fc.rh_to_n);
+    const float a_n = rintf((ih[2] - fc.zp_ih) * fc.ih_to[2]);
+    const float in_n = fs_clamp(a_n + rh + fc.zp_in[2], fc.in_lo[2], fc.in_hi[2]);
+    const float y_n = tanhf((in_n - fc.zp_in[2]) * fc.s_in[2]);
+    const float n = fs_clamp(rintf(y_n / fc.s_out[2] + fc.zp_out[2]), fc.out_lo[2], fc.out_hi[2]);
+    // state update (computeHiddenStateFP, :302-372)
+    const float h_old = (float)state_byte(h8_in[(size_t)b * Hpad + j], fc.h_bits);
+    const float n_h = rintf((n - fc.zp_out[2]) * fc.n_to_h) + fc.zp_h;
+    const float old_c = (u - fc.zp_out[0]) * (h_old - fc.zp_h);
+    const float new_c = ((fc.one_q - u) - fc.zp_out[0]) * (n_h - fc.zp_h);
+    const float h_new = fs_clamp(rintf((old_c + new_c) * fc.uh_to_h) + fc.zp_h, fc.h_lo, fc.h_hi);
+    h8_out[(size_t)b * Hpad + j] = (uint8_t)(int)h_new;
+    h_out[(size_t)b * H + j] = (h_new - fc.zp_h) * fc.h_scale;
+}
+
+namespace {
+
+float op_lo(const qgru_op &o) { return (float)op_qmin(o); }
+float op_hi(const qgru_op &o) { return (float)op_qmax(o); }
+
+}  // namespace
+
+// Host side of quantGRUForwardFP, inference mode.  x, h0, h_out, xq_out are device pointers.
+int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *h0, float *h_out,
+                     float *xq_out, unsigned flags, cudaStream_t st) {
+    if (!h->fast)
+        return fail(h, QGRU_ERR_UNSUPPORTED,
+                    "float-storage forward needs 8-bit W, R, x and h (the operands of the two products)");
+    const qgru_params &p = h->p;
+    const int H = h->H, C = h->C;
+    const long long N = (long long)T * B;
+    // ---- constants (setRescaleParam, src/gru_forward_gpu_quant_fp.cu:821-1003): float ratios
+    // of the stored scales, computed in the same float operations
+    FsConsts fc{};
+    const qgru_op &ox = p.op[QGRU_OP_X], &oh = p.op[QGRU_OP_H], &oih = p.op[QGRU_OP_IH_LINEAR],
+                  &ohh = p.op[QGRU_OP_HH_LINEAR];
+    const int op_in[3] = {QGRU_OP_UPDATE_IN, QGRU_OP_RESET_IN, QGRU_OP_NEW_IN};
+    const int op_out[3] = {QGRU_OP_UPDATE_OUT, QGRU_OP_RESET_OUT, QGRU_OP_NEW_OUT};
+    fc.zp_x = (float)ox.zero_point;
+    fc.zp_h = (float)oh.zero_point;
+    fc.zp_ih = (float)oih.zero_point;
+    fc.zp_hh = (float)ohh.zero_point;
+    for (int g = 0; g < 3; ++g) {
+        const qgru_op &i_ = p.op[op_in[g]], &o_ = p.op[op_out[g]];
+        fc.zp_in[g] = (float)i_.zero_point;
+        fc.zp_out[g] = (float)o_.zero_point;
+        fc.s_in[g] = i_.scale;
+        fc.s_out[g] = o_.scale;
+        fc.ih_to[g] = oih.scale / i_.scale;
+        if (g < 2) fc.hh_to[g] = ohh.scale / i_.scale;
+        fc.in_lo[g] = op_lo(i_);
+        fc.in_hi[g] = op_hi(i_);
+        fc.out_lo[g] = op_lo(o_);
+        fc.out_hi[g] = op_hi(o_);
+    }
+    const qgru_op &ou = p.op[QGRU_OP_UPDATE_OUT], &orr = p.op[QGRU_OP_RESET_OUT], &on = p.op[QGRU_OP_NEW_OUT];
+    fc.rh_to_n = (orr.scale * ohh.scale) / p.op[QGRU_OP_NEW_IN].scale;
+    fc.one_q = rintf(1.0f / ou.scale) + (float)ou.zero_point;
+    fc.uh_to_h = (ou.scale * oh.scale) / oh.scale;
+    fc.n_to_h = on.scale / oh.scale;
+    fc.ih_lo = op_lo(oih); fc.ih_hi = op_hi(oih);
+    fc.hh_lo = op_lo(ohh); fc.hh_hi = op_hi(ohh);
+    fc.h_lo = op_lo(oh); fc.h_hi = op_hi(oh);
+    fc.h_scale = h->h_scale;
+    fc.h_bits = h->h_uns ? 9 : 8;
+
+    int rc;
+    if ((rc = ensure(h, h->fs_ch, (size_t)4 * C * sizeof(float)))) return rc;
+    if (!h->fs_ready) {
+        std::vector<float> hostc((size_t)4 * C);
+        for (int m = 0; m < C; ++m) {
+            const float s_wx = h->sc[0][m] * ox.scale;
+            hostc[m] = s_wx / oih.scale;                 // inv_div_gemm_x_to_weight_ih_linear
+            hostc[C + m] = h->sc[2][m] / s_wx;           // inv_div_bw_to_gemm_x
+            const float s_rh = h->sc[1][m] * oh.scale;
+            hostc[2 * C + m] = s_rh / ohh.scale;
+            hostc[3 * C + m] = h->sc[3][m] / s_rh;
+        }
+        CK(cudaMemcpyAsync(h->fs_ch.p, hostc.data(), hostc.size() * sizeof(float), cudaMemcpyHostToDevice, st));
+        CK(cudaStreamSynchronize(st));   // hostc leaves scope
+        h->fs_ready = true;
+    }
+    const float *chp = (const float *)h->fs_ch.p;
+    const FsChannels ch{chp, chp + C, chp + 2 * C, chp + 3 * C};
+
+    if ((rc = ensure(h, h->x8, (size_t)((N + 127) / 128 * 128) * h->Ipad))) return rc;
+    if ((rc = ensure(h, h->h8, (size_t)(2 * B + 256) * h->Hpad))) return rc;
+    if ((rc = ensure(h, h->ih32, (size_t)N * C * 4))) return rc;
+    if ((rc = ensure(h, h->hh32, (size_t)B * C * 4))) return rc;
+    const bool rev = flags & QGRU_FLAG_REVERSE;
+    const long long init_slot = rev ? T : 0;
+    uint8_t *h8 = (uint8_t *)h->h8.p;
+    const size_t h8_half = (size_t)B * h->Hpad;
+
+    h->ev = h->ring[h->calls % qgru_handle::kRing];
+    h->calls++;
+    CK(cudaEventRecord(h->ev[0], st));
+    k_fs_quantize_rows<<<grid_for(N * (h->Ipad / 4), 256, h->sm_count), 256, 0, st>>>(
+        x, (uint8_t *)h->x8.p, xq_out, N, h->I, h->Ipad, h->x_scale, fc.zp_x, op_lo(ox), op_hi(ox));
+    CK(cudaMemsetAsync(h8, 0, (size_t)(2 * B + 256) * h->Hpad, st));
+    k_fs_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
+        h0, h8, h_out, B, H, h->Hpad, init_slot, fc);
+    CK(cudaEventRecord(h->ev[1], st));
+    {
+        dim3 grid((unsigned)((N + 63) / 64), (unsigned)((C + 63) / 64));
+        if (h->x_uns)
+            k_gemm_wx_simt<true, int32_t, true><<<grid, 256, 0, st>>>((const uint8_t *)h->x8.p, h->d_w8[0],
+                                                                    (int32_t *)h->ih32.p, N, C, h->Ipad, LinearConsts{});
+        else
+            k_gemm_wx_simt<false, int32_t, true><<<grid, 256, 0, st>>>((const uint8_t *)h->x8.p, h->d_w8[0],
+                                                                     (int32_t *)h->ih32.p, N, C, h->Ipad, LinearConsts{});
+    }
+    CK(cudaEventRecord(h->ev[2], st));
+    h->launches += 3;
+    const size_t BH = (size_t)B * H;
+    for (int s = 0; s < T; ++s) {
+        const int t = rev ? T - 1 - s : s;
+        const size_t out_slot = rev ? (size_t)(T - 1 - s) : (size_t)(s + 1);
+        const uint8_t *hin = h8 + (size_t)(s & 1) * h8_half;
+        uint8_t *hout = h8 + (size_t)((s + 1) & 1) * h8_half;
+        dim3 g1((unsigned)((B + 63) / 64), (unsigned)((C + 63) / 64));
+        if (h->h_uns)
+            k_gemm_wx_simt<true, int32_t, true><<<g1, 256, 0, st>>>(hin, h->d_w8[1], (int32_t *)h->hh32.p, B, C,
+                                                                  h->Hpad, LinearConsts{});
+        else
+            k_gemm_wx_simt<false, int32_t, true><<<g1, 256, 0, st>>>(hin, h->d_w8[1], (int32_t *)h->hh32.p, B, C,
+                                                                   h->Hpad, LinearConsts{});
+        dim3 g2((H + 127) / 128, B);
+        k_fs_cell<<<g2, 128, 0, st>>>((const int32_t *)h->ih32.p + (size_t)t * B * C, (const int32_t *)h->hh32.p,
+                                      h->d_wsum[0], h->d_wsum[1], h->d_wq[2], h->d_wq[3], ch, hin, hout,
+                                      h_out + out_slot * BH, B, H, h->Hpad, fc);
+        h->launches += 2;
+    }
+    CK(cudaGetLastError());
+    CK(cudaEventRecord(h->ev[3], st));
+    h->timing_valid = true;
+    h->plan_text = "path=float_storage gemm=simt_dp4a_raw rec=per_step_float_cell";
+    return QGRU_OK;
+}
+
+}  // namespace qgru
+
+extern "C" {
+
+int qgru_forward_fstorage(qgru_handle *h, int T, int B, const float *x, const float *h0, float *h_out,
+                          float *x_q_out, unsigned flags, void *stream) {
+    if (!h || !x || !h_out) return QGRU_ERR_BAD_ARG;
+    if (T <= 0 || B <= 0) return fail(h, QGRU_ERR_BAD_ARG, "T and B must be positive");
+    if (!h->params_set || !h->weights_set)
+        return fail(h, QGRU_ERR_NOT_READY, "set_params and set_weights first");
+    CK(cudaSetDevice(h->device));
+    return qgru::fstorage_forward(h, T, B, x, h0, h_out, x_q_out, flags, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -68,6 +68,8 @@ struct qgru_handle {
     // workspace
     DevBuf x8, ih, h8, x32, ih32, hh32, hq32, stage_in, stage_h0, stage_out;
     DevBuf f_wx, f_h, f_v, f_acc, f_acc2;  // float mode / calibration (f_acc2: R*h of one step)
+    DevBuf fs_ch;                          // float-storage forward: 4 x 3H per-channel scale ratios
+    bool fs_ready = false;                 // fs_ch matches the current parameters
     static constexpr int kRing = 64;
     cudaEvent_t ring[kRing][4] = {};   // per forward: start, gemm start, gemm end, recurrence end
     cudaEvent_t *ev = ring[0];          // the slot the current forward records into

@@ -194,10 +194,10 @@ __global__ void k_hist_redistribute(const float *__restrict__ src, float src_min
     const float count = src[i];
     if (count <= 0) return;
     const float inv = 1.0f / dst_bw;
-    const float start = __fadd_rn(src_min, __fmul_rn((float)i, src_bw));
+    const float start = __fmaf_rn((float)i, src_bw, src_min);   // fused, as the reference's kernel compiles
     int d = (int)__fmul_rn(start - dst_min, inv);
     d = min(d, bins - 1);
-    const float end = __fadd_rn(dst_min, __fmul_rn(dst_bw, (float)(d + 1)));
+    const float end = __fmaf_rn(dst_bw, (float)(d + 1), dst_min);
     const float split = rintf(__fmul_rn((end - start) / src_bw, count));
     const float first = fminf(split, count);
     atomicAdd(&dst[d], first);

@@ -147,7 +147,8 @@ __global__ void k_channel_consts(const int32_t *__restrict__ bias_q,
 
 // ih[n][m] = epilogue( sum_k W8[m][k] * x8[n][k] ), n < N tokens, m < C channels.
 // 64x64 output tile per CTA, 256 threads, 4x4 outputs per thread, K staged in 64-byte slabs.
-template <bool XUnsigned, typename IhT>
+// Raw: store the int32 sums themselves (no zero-point compensation, bias or requantization).
+template <bool XUnsigned, typename IhT, bool Raw = false>
 __global__ void __launch_bounds__(256)
 k_gemm_wx_simt(const uint8_t *__restrict__ x8, const int8_t *__restrict__ w8, IhT *__restrict__ ih,
                long long N, int C, int Kpad, LinearConsts lc) {
@@ -193,7 +194,8 @@ k_gemm_wx_simt(const uint8_t *__restrict__ x8, const int8_t *__restrict__ w8, Ih
         for (int j = 0; j < 4; ++j) {
             const int m = m0 + tx + 16 * j;
             if (m >= C) continue;
-            ih[n * C + m] = (IhT)linear_epilogue(acc[i][j], lc.corr[m], lc.rs[m], lc.zp_out, lc.lo, lc.hi);
+            if constexpr (Raw) ih[n * C + m] = (IhT)acc[i][j];
+            else ih[n * C + m] = (IhT)linear_epilogue(acc[i][j], lc.corr[m], lc.rs[m], lc.zp_out, lc.lo, lc.hi);
         }
     }
 }

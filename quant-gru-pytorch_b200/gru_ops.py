@@ -190,6 +190,25 @@ class Handle:
             self.synchronize()
         return (h, x_q) if want_x_q else h
 
+    def forward_fstorage(self, x, h0=None, reverse=False, want_x_q=False, sync=True):
+        """Float-storage quantized forward (the reference's forward_quant_float_storage, inference):
+        float requantization and real sigmoid / tanh on quantized tensors.  x [T,B,I] fp32 ->
+        h [(T+1),B,H] fp32 dequantized; with want_x_q also the quantized x as floats."""
+        x = _check_tensor(x, "x", torch.float32)
+        if x.dim() != 3 or x.shape[2] != self.input_size:
+            raise ValueError("x must have shape [time_steps, batch_size, input_size]")
+        T, B = int(x.shape[0]), int(x.shape[1])
+        if h0 is not None:
+            h0 = _check_tensor(h0, "h0", torch.float32, (B, self.hidden_size))
+        h = torch.empty((T + 1, B, self.hidden_size), dtype=torch.float32, device=self._tdev)
+        x_q = torch.empty((T, B, self.input_size), dtype=torch.float32, device=self._tdev) if want_x_q else None
+        self._ck(self._lib.qgru_forward_fstorage(self._h, T, B, _ptr(x), _ptr(h0), _ptr(h), _ptr(x_q),
+                                                 _cabi.FLAG_REVERSE if reverse else 0, _stream(self._tdev)),
+                 "qgru_forward_fstorage")
+        if sync:
+            self.synchronize()
+        return (h, x_q) if want_x_q else h
+
     # -- forward (host tensors; copies are part of the call)
     def forward_i32_host(self, x_q, h0_q=None, reverse=False, out=None):
         x_q = _check_tensor(x_q, "x_q", torch.int32, cuda=False)

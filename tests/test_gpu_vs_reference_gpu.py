@@ -155,8 +155,9 @@ def test_collector_equals_reference_gpu_collector(oracle, refgpu, cuda_device):
 def test_calibration_histograms_match_reference_gpu(refgpu, cuda_device, gran):
     """Two batches through the calibration forward of both libraries.  Histograms of tensors that
     are read (x, the weights) are equal bit for bit; histograms of computed tensors agree in
-    total, in range to TF32 precision, and in shape (cumulative counts within 1 % of the total:
-    a range that differs by 1e-3 of its span shifts every bin edge by up to two bins)."""
+    total, in range to TF32 precision, and in shape: a TF32 error of 3e-4 of the span is more than
+    half a bin of 2048, so single values change bins freely; the cumulative distributions must
+    stay within 5 % of the total of each other (Kolmogorov-Smirnov distance)."""
     T, B, I, H = 7, 6, 20, 40
     rng = np.random.default_rng(9)
     W, R, bw, br = gen_weights(rng, I, H)
@@ -184,7 +185,7 @@ def test_calibration_histograms_match_reference_gpu(refgpu, cuda_device, gran):
         span = max(abs(mx2 - mn2), 1e-30)
         assert abs(mn1 - mn2) <= TF32_RTOL * span + 1e-7 and abs(mx1 - mx2) <= TF32_RTOL * span + 1e-7, name
         moved = np.abs(np.cumsum(c1.astype(np.float64)) - np.cumsum(c2.astype(np.float64))).max()
-        assert moved <= max(3.0, 1e-2 * t1), (name, moved)
+        assert moved <= max(3.0, 5e-2 * t1), (name, moved)
     C3 = 3 * H
     for k, name in enumerate(("W", "R", "bw", "br")):
         if gran == "PER_TENSOR":
@@ -197,3 +198,42 @@ def test_calibration_histograms_match_reference_gpu(refgpu, cuda_device, gran):
                 _same(hs.get(_cabi.HIST_CHANNEL0 + k * C3 + c_idx),
                       ref_set.get(_cabi.HIST_CHANNEL0 + k * C3 + c_idx))
     hs.close()
+
+
+def _quanta(h, case):
+    """Dequantized h back to integer steps of the h scale."""
+    hs = np.float32(case.params.c.op[OP["h"]].scale)
+    return np.rint(h.astype(np.float64) / float(hs)).astype(np.int64)
+
+
+@pytest.mark.parametrize("cfg_name", ["default", "sym8_tensor", "cfg2", "cfg3", "cfg5", "pot2_asym"])
+@pytest.mark.parametrize("shape", [(6, 5, 20, 40), (5, 9, 64, 256)])
+def test_float_storage_forward_equals_reference_gpu(oracle, reference, refgpu, cuda_device, cfg_name, shape):
+    """quantGRUForwardFP (inference) on the same device: quantized x and every timestep of h are
+    equal bit for bit (the products are exact integer sums on both sides and the float
+    operations after them are the same in the same order).  The CPU oracle evaluates expf / tanhf
+    with the host's libm, so a gate output may round across a .5 boundary differently: at most
+    one step of the h scale on at most 1 % of the elements."""
+    T, B, I, H = shape
+    case = make_case(seed=41, T=T, B=B, I=I, H=H, checker=reference, config=config_named(cfg_name),
+                     with_h0=True)
+    sc = case.params.scale_list()
+    want_h, want_xq, want_wq = refgpu.forward_fstorage(T, B, I, H, case.W, case.R, case.bw, case.br, case.x,
+                                                       case.h0, case.params.c, sc)
+    for a, b in zip(want_wq, case.wq):   # quantizeGRUWeights == the integer path's weight quantize
+        assert np.array_equal(a.astype(np.int32).reshape(b.shape), b)
+    with gru_ops.Handle(I, H, device=0) as hd:
+        hd.set_params(case.params)
+        hd.set_weights_f32(*[_t(a, cuda_device) for a in (case.W, case.R, case.bw, case.br)])
+        got_h, got_xq = hd.forward_fstorage(_t(case.x, cuda_device), _t(case.h0, cuda_device), want_x_q=True)
+        got_h, got_xq = got_h.cpu().numpy(), got_xq.cpu().numpy()
+        flipped = np.ascontiguousarray(case.x[::-1])
+        rev = hd.forward_fstorage(_t(flipped, cuda_device), _t(case.h0, cuda_device), reverse=True).cpu().numpy()
+    assert np.array_equal(got_xq, want_xq)
+    assert np.array_equal(got_h, want_h), np.abs(_quanta(got_h, case) - _quanta(want_h, case)).max()
+    # reverse flag: slot T holds the initial state, slots T-1..0 the outputs
+    assert np.array_equal(rev[::-1], want_h)
+    orc_h, orc_xq = oracle.forward_fstorage(T, B, I, H, case.wq, case.x, case.h0, case.params.c, sc)
+    assert np.array_equal(orc_xq, want_xq)
+    d = np.abs(_quanta(orc_h, case) - _quanta(want_h, case))
+    assert d.max() <= 1 and (d > 0).mean() <= 0.01, (d.max(), (d > 0).mean())
