@@ -297,6 +297,15 @@ class ReferenceGpu:
         self._check(rc, "ref_gpu_forward_i32")
         return (h, v, ms) if training else h
 
+    def time_forward_i32(self, T, B, I, H, wq, x_q, params, sc, warmup=2, iters=5):
+        """Milliseconds per call of quantGRUForwardInt32 (inference) with resident inputs."""
+        ms = C.c_float()
+        rc = self._fn("time_forward_i32")(T, B, I, H, *[_i(np.ascontiguousarray(w, np.int32)) for w in wq],
+                                          _i(np.ascontiguousarray(x_q, np.int32)), C.byref(params),
+                                          *[_f(s) for s in sc], int(warmup), int(iters), C.byref(ms))
+        self._check(rc, "ref_gpu_time_forward_i32")
+        return float(ms.value)
+
     def forward_float(self, T, B, I, H, W, R, bw, br, x, h0=None, want_v=False):
         h = np.zeros((T + 1, B, H), np.float32)
         v = np.zeros((T, B, 4 * H), np.float32) if want_v else None
