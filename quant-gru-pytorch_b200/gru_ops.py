@@ -353,6 +353,28 @@ def forward_quant_int_storage(is_training, time_steps, batch_size, input_size, h
     return h, v, W_q, R_q, bw_q, br_q, x_q
 
 
+def forward_quant_float_storage(is_training, time_steps, batch_size, input_size, hidden_size,
+                                W, R, bw, br, x, h0, quant_params, slot=0, reverse=False):
+    """Float-storage quantized forward (binding :283-423, inference mode): quantized values kept
+    as floats, float requantization, real sigmoid / tanh.
+
+    Returns (h [(T+1),B,H] f32, v (empty), W_q, R_q, bw_q, br_q, x_q) with the quantized tensors
+    as float32 like the reference; the masks of its training mode are not produced
+    (is_training must be False)."""
+    if is_training:
+        raise NotImplementedError("the training mode of the float-storage forward serves the backward pass, "
+                                  "which is not built")
+    x = _check_tensor(x, "x", torch.float32, (time_steps, batch_size, input_size))
+    hd = _handle_for(x.device.index or 0, input_size, hidden_size, slot)
+    hd.set_params(quant_params)
+    hd.set_weights_f32(W, R, bw, br)
+    h0 = h0 if (h0 is not None and h0.numel() > 0) else None
+    h, x_q = hd.forward_fstorage(x, h0, reverse=reverse, want_x_q=True)
+    W_q, R_q, bw_q, br_q = [t.to(torch.float32) for t in hd.get_weights_i32()]
+    v = torch.empty(0, dtype=torch.float32, device=x.device)
+    return h, v, W_q, R_q, bw_q, br_q, x_q
+
+
 def forward_quantized_int_io(time_steps, batch_size, input_size, hidden_size, W, R, bw, br, x_q,
                              h0_q, quant_params, slot=0, reverse=False):
     """int32 in / int32 out inference (binding :573-618): returns (output_q [T,B,H], h_n_q [1,B,H])."""

@@ -5,15 +5,16 @@ What is kept, with the reference's names and meaning: the constructor signature 
 names (``weight_ih_l0`` ... in PyTorch's (r, z, n) gate order), ``batch_first``,
 ``bidirectional``, ``use_quantization``, ``calibrating`` + ``finalize_calibration`` (MinMax),
 ``load_bitwidth_config`` / ``set_all_bitwidth``, ``forward`` (float mode, calibration mode,
-quantized mode with ``quant_storage_dtype="int32"``), ``forward_quantized`` (int32 in / out),
+quantized mode with ``quant_storage_dtype="int32"``: the integer path, or ``"float32"``: the
+float-storage path with real sigmoid / tanh, both in eval mode), ``forward_quantized`` (int32 in / out),
 ``export_quant_params`` / ``load_quant_params``.
 
 What differs by design: each direction owns a ``gru_ops.Handle`` whose packed weights are
 re-quantized only when a parameter tensor or the quant params change (the reference
 re-quantizes weights and regenerates LUTs on every call); the reverse direction runs on the
 same input with reversed time indexing instead of two ``flip`` copies; the two directions
-are queued on two CUDA streams.  Training-mode outputs, backward, the float-storage path
-(``quant_storage_dtype="float32"`` with quantization on), ONNX and AIMET hooks are not built.
+are queued on two CUDA streams.  Training (autograd, backward), ONNX and AIMET hooks are not
+built.
 """
 import json
 import math
@@ -236,10 +237,6 @@ class QuantGRU(nn.Module):
         return [hx[d].contiguous() for d in range(self.num_directions)]
 
     def _ensure_quant_ready(self):
-        if self.quant_storage_dtype != "int32":
-            raise NotImplementedError(
-                "quantized forward is built for quant_storage_dtype='int32' (the bit-exact integer "
-                "path); the float-storage path is not part of this library")
         if self.training:
             raise NotImplementedError("training-mode (QAT) outputs are not built; call .eval()")
         if self._quant_params_dirty and self.quant_ranges is not None:
@@ -310,8 +307,11 @@ class QuantGRU(nn.Module):
             self._ensure_quant_ready()
             for d in range(self.num_directions):
                 self._ready_quant(d, device)
-            outs = self._run_directions(
-                lambda d, st: st.handle.forward_f32(x, h0[d], reverse=(d == 1), sync=False), device)
+            if self.quant_storage_dtype == "int32":
+                run = lambda d, st: st.handle.forward_f32(x, h0[d], reverse=(d == 1), sync=False)  # noqa: E731
+            else:
+                run = lambda d, st: st.handle.forward_fstorage(x, h0[d], reverse=(d == 1), sync=False)  # noqa: E731
+            outs = self._run_directions(run, device)
         else:
             outs = []
             for d in range(self.num_directions):

@@ -94,7 +94,7 @@ def test_nan_and_inf_are_skipped_by_calibration(cuda_device):
     assert np.isfinite(r.max_v[OP["x"]]) and r.max_v[OP["x"]] == np.max(x[np.isfinite(x)])
 
 
-def _oracle_module_forward(oracle, mod, x, hx, T, B):
+def _oracle_module_forward(oracle, mod, x, hx, T, B, float_storage=False):
     """Compose the oracle the way the reference module composes its kernels."""
     I, H = mod.input_size, mod.hidden_size
     outs, hns = [], []
@@ -106,7 +106,11 @@ def _oracle_module_forward(oracle, mod, x, hx, T, B):
             getattr(mod, "bias_ih_l0" + sfx), getattr(mod, "bias_hh_l0" + sfx), H, "cpu")]
         wq = oracle.quantize_weights(I, H, W, R, bw, br, qp.c, qp.scale_list())
         xd = x[::-1].copy() if d else x
-        h = oracle.forward_f32(T, B, I, H, wq, xd, hx[d] if hx is not None else None, qp.c, qp.scale_list())
+        h0 = hx[d] if hx is not None else None
+        if float_storage:
+            h, _ = oracle.forward_fstorage(T, B, I, H, wq, xd, h0, qp.c, qp.scale_list())
+        else:
+            h = oracle.forward_f32(T, B, I, H, wq, xd, h0, qp.c, qp.scale_list())
         outs.append(h[1:][::-1] if d else h[1:])
         hns.append(h[-1:])
     return np.concatenate(outs, -1), np.concatenate(hns, 0)
@@ -180,6 +184,39 @@ def test_quantgru_param_file_round_trip(oracle, cuda_device, tmp_path):
     assert torch.equal(got, want)
 
 
+@pytest.mark.parametrize("bidir,bf", [(False, False), (True, True)])
+def test_quantgru_module_float_storage(oracle, cuda_device, bidir, bf):
+    """The module's default quantized mode (quant_storage_dtype="float32": float requantization,
+    real sigmoid / tanh) against the oracle's restatement of that path: at most one step of the
+    h scale on at most 1 % of the elements (host libm against CUDA's expf / tanhf); the same
+    path is bit-exact against the reference's GPU code in test_gpu_vs_reference_gpu.py."""
+    import torch
+    torch.manual_seed(5)
+    T, B, I, H = 8, 6, 20, 40
+    mod = quant_gru.QuantGRU(I, H, batch_first=bf, bidirectional=bidir).cuda().eval()
+    assert mod.quant_storage_dtype == "float32"
+    rng = np.random.default_rng(6)
+    mod.calibrating = True
+    for _ in range(3):
+        xc = gen_x(rng, T, B, I)
+        mod(_t(xc.transpose(1, 0, 2) if bf else xc, cuda_device))
+    mod.calibrating = False
+    mod.use_quantization = True
+    x = gen_x(rng, T, B, I)
+    hx = (rng.standard_normal((2 if bidir else 1, B, H)) * 0.2).astype(np.float32)
+    out, hn = mod(_t(x.transpose(1, 0, 2) if bf else x, cuda_device), _t(hx, cuda_device))
+    want_o, want_h = _oracle_module_forward(oracle, mod, x, hx, T, B, float_storage=True)
+    got_o = out.cpu().numpy().transpose(1, 0, 2) if bf else out.cpu().numpy()
+    for d in range(mod.num_directions):
+        qp = mod.quant_params_reverse if d else mod.quant_params
+        hs = float(np.float32(qp.c.op[OP["h"]].scale))
+        diff = np.abs(np.rint(got_o[..., d * H:(d + 1) * H].astype(np.float64) / hs) -
+                      np.rint(want_o[..., d * H:(d + 1) * H].astype(np.float64) / hs))
+        assert diff.max() <= 1 and (diff > 0).mean() <= 0.01
+    assert hn.shape == (mod.num_directions, B, H)
+    assert np.abs(hn.cpu().numpy() - want_h).max() <= 1.01 * hs
+
+
 def test_quantgru_errors(cuda_device):
     import torch
     m = quant_gru.QuantGRU(8, 16, quant_storage_dtype="int32").cuda().eval()
@@ -198,10 +235,11 @@ def test_quantgru_errors(cuda_device):
     m.finalize_calibration()
     with pytest.raises(TypeError):             # float input to the int-in/int-out entry
         m.forward_quantized(torch.randn(3, 2, 8, device=cuda_device))
-    f = quant_gru.QuantGRU(8, 16).cuda().eval()  # float-storage path is not built
+    f = quant_gru.QuantGRU(8, 16).cuda()         # training mode (QAT) is not built
     f.calibrating = True
     f(torch.randn(3, 2, 8, device=cuda_device))
     f.calibrating = False
     f.use_quantization = True
+    f.train()
     with pytest.raises(NotImplementedError):
         f(torch.randn(3, 2, 8, device=cuda_device))
