@@ -306,6 +306,15 @@ class ReferenceGpu:
         self._check(rc, "ref_gpu_time_forward_i32")
         return float(ms.value)
 
+    def time_forward_fstorage(self, T, B, I, H, W, R, bw, br, x, params, sc, warmup=1, iters=3):
+        """Milliseconds per call of quantGRUForwardFP (inference) with resident inputs."""
+        ms = C.c_float()
+        rc = self._fn("time_forward_fstorage")(T, B, I, H, _f(W), _f(R), _f(bw), _f(br),
+                                               _f(np.ascontiguousarray(x, np.float32)), C.byref(params),
+                                               *[_f(s) for s in sc], int(warmup), int(iters), C.byref(ms))
+        self._check(rc, "ref_gpu_time_forward_fstorage")
+        return float(ms.value)
+
     def forward_float(self, T, B, I, H, W, R, bw, br, x, h0=None, want_v=False):
         h = np.zeros((T + 1, B, H), np.float32)
         v = np.zeros((T, B, 4 * H), np.float32) if want_v else None

@@ -615,6 +615,37 @@ int ref_gpu_time_forward_i32(int T, int B, int I, int H, const int32_t *W, const
     });
 }
 
+// The same for quantGRUForwardFP (inference): float inputs resident, ms per call.
+int ref_gpu_time_forward_fstorage(int T, int B, int I, int H, const float *W, const float *R,
+                                  const float *bw, const float *br, const float *x,
+                                  const qgru_params *p, const float *sW, const float *sR,
+                                  const float *sbw, const float *sbr, int warmup, int iters,
+                                  float *ms_per_call) {
+    return guarded([&] {
+        GRUQuantParams q = fromPod(*p, sW, sR, sbw, sbr);
+        const size_t C3 = size_t(H) * 3, TB = size_t(T) * B;
+        DevBuf<float> dW(W, size_t(I) * C3), dR(R, size_t(H) * C3), dbw(bw, C3), dbr(br, C3),
+            dx(x, TB * I), dh((TB + B) * H);
+        DevBuf<float> qW(size_t(I) * C3), qR(size_t(H) * C3), qbw(C3), qbr(C3), qx(TB * I);
+        cudaEvent_t e0, e1;
+        cudaOk(cudaEventCreate(&e0), "cudaEventCreate");
+        cudaOk(cudaEventCreate(&e1), "cudaEventCreate");
+        for (int i = 0; i < warmup + iters; ++i) {
+            if (i == warmup) cudaOk(cudaEventRecord(e0, 0), "cudaEventRecord");
+            quantGRUForwardFP(false, T, B, I, H, dW.p, dR.p, dbw.p, dbr.p, dx.p, nullptr, q, blasHandle(),
+                              dh.p, nullptr, qW.p, qR.p, qbw.p, qbr.p, qx.p, nullptr, nullptr, nullptr,
+                              nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr);
+        }
+        cudaOk(cudaEventRecord(e1, 0), "cudaEventRecord");
+        cudaOk(cudaEventSynchronize(e1), "cudaEventSynchronize");
+        float ms = 0.f;
+        cudaOk(cudaEventElapsedTime(&ms, e0, e1), "cudaEventElapsedTime");
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        *ms_per_call = ms / (float)iters;
+    });
+}
+
 // hasteGRUForward (src/gru_interface.cc:173): the reference's fp32 GRU on the GPU.
 int ref_gpu_forward_float(int T, int B, int I, int H, const float *W, const float *R, const float *bw,
                           const float *br, const float *x, const float *h0, float *h, float *v) {

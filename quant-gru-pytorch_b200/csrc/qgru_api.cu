@@ -460,6 +460,7 @@ int finish_weights(qgru_handle *h, cudaStream_t st) {
     h->rec.valid = false;
     h->rec_cl.valid = false;
     h->weights_set = true;
+    h->fs_ready = false;
     return QGRU_OK;
 }
 

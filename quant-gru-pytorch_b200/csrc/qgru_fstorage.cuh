@@ -94,38 +94,28 @@ __global__ void k_fs_init_state(const float *__restrict__ h0, uint8_t *__restric
     }
 }
 
-// biasRescaleInline (src/gru_forward_gpu_quant_fp.cu:117-142): acc is the exact integer
-// sum_k W*x, wsum the integer column sum of the quantized weights.
-__device__ __forceinline__ float fs_linear(int acc, int wsum, float zp_in, float bias, float inv_bias,
-                                           float inv_gemm, float zp_out, float lo, float hi) {
-    const float val = (float)acc - (float)wsum * zp_in;
-    const float bias_term = rintf(bias * inv_bias);
-    const float combined = val + bias_term;
-    return fs_clamp(rintf(combined * inv_gemm) + zp_out, lo, hi);
+// biasRescaleInline (src/gru_forward_gpu_quant_fp.cu:117-142).  acc is the exact integer
+// sum_k W*x; off = float(sum_k W) * zp_in as computeWeightSumKernel leaves it (:442-458, one
+// rounded product); bias_term = round(bias * inv_bias).  Sub, add and multiply are kept as
+// separate roundings, as in the reference's compiled kernel (none of them is an a*b+c there).
+__device__ __forceinline__ float fs_linear(int acc, float off, float bias_term, float inv_gemm,
+                                           float zp_out, float lo, float hi) {
+    const float val = __fsub_rn((float)acc, off);
+    const float combined = __fadd_rn(val, bias_term);
+    return fs_clamp(rintf(__fmul_rn(combined, inv_gemm)) + zp_out, lo, hi);
+}
+__device__ __forceinline__ float fs_offset(int wsum, float zp_in) { return __fmul_rn((float)wsum, zp_in); }
+__device__ __forceinline__ float fs_bias_term(int bias_q, float inv_bias) {
+    return rintf(__fmul_rn((float)bias_q, inv_bias));
 }
 
 __device__ __forceinline__ float fs_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
 
-// PointwiseOperationsFP<false, false> (src/gru_forward_gpu_quant_fp.cu:572-770): one thread per
-// (hidden unit, batch row).
-__global__ void k_fs_cell(const int32_t *__restrict__ ih_acc, const int32_t *__restrict__ hh_acc,
-                          const int32_t *__restrict__ wsum_x, const int32_t *__restrict__ wsum_h,
-                          const int32_t *__restrict__ bw_q, const int32_t *__restrict__ br_q,
-                          FsChannels ch, const uint8_t *__restrict__ h8_in, uint8_t *__restrict__ h8_out,
-                          float *__restrict__ h_out, int B, int H, int Hpad, FsConsts fc) {
-    const int j = blockIdx.x * blockDim.x + threadIdx.x;
-    const int b = blockIdx.y;
-    if (j >= H || b >= B) return;
-    const size_t w = (size_t)b * 3 * H + j;
-    float ih[3], hh[3];
-#pragma unroll
-    for (int g = 0; g < 3; ++g) {
-        const int m = j + g * H;
-        ih[g] = fs_linear(ih_acc[w + g * H], wsum_x[m], fc.zp_x, (float)bw_q[m], ch.inv_bw[m],
-                          ch.inv_gemm_x[m], fc.zp_ih, fc.ih_lo, fc.ih_hi);
-        hh[g] = fs_linear(hh_acc[w + g * H], wsum_h[m], fc.zp_h, (float)br_q[m], ch.inv_br[m],
-                          ch.inv_gemm_h[m], fc.zp_hh, fc.hh_lo, fc.hh_hi);
-    }
+// The gate and state arithmetic of PointwiseOperationsFP (src/gru_forward_gpu_quant_fp.cu:714-770)
+// for one cell: ih / hh are the requantized, clamped linear outputs (z, r, n), h_old the
+// quantized previous state; returns the new quantized state.
+__device__ __forceinline__ float fs_cell(const FsConsts &fc, const float ih[3], const float hh[3],
+                                         float h_old) {
     // update and reset gates (computeUpdateGateFP / computeResetGateFP, :153-239)
     float gate[2];
 #pragma unroll
@@ -144,13 +134,192 @@ __global__ void k_fs_cell(const int32_t *__restrict__ ih_acc, const int32_t *__r
     const float y_n = tanhf((in_n - fc.zp_in[2]) * fc.s_in[2]);
     const float n = fs_clamp(rintf(y_n / fc.s_out[2] + fc.zp_out[2]), fc.out_lo[2], fc.out_hi[2]);
     // state update (computeHiddenStateFP, :302-372)
-    const float h_old = (float)state_byte(h8_in[(size_t)b * Hpad + j], fc.h_bits);
     const float n_h = rintf((n - fc.zp_out[2]) * fc.n_to_h) + fc.zp_h;
     const float old_c = (u - fc.zp_out[0]) * (h_old - fc.zp_h);
     const float new_c = ((fc.one_q - u) - fc.zp_out[0]) * (n_h - fc.zp_h);
-    const float h_new = fs_clamp(rintf((old_c + new_c) * fc.uh_to_h) + fc.zp_h, fc.h_lo, fc.h_hi);
+    return fs_clamp(rintf((old_c + new_c) * fc.uh_to_h) + fc.zp_h, fc.h_lo, fc.h_hi);
+}
+
+// Per-channel constants of the two linear layers, prepared once per parameter set:
+// chan[0..2] = offset, bias term, GEMM ratio of W*x; chan[3..5] the same for R*h; each [3H].
+__global__ void k_fs_channel_consts(const int32_t *__restrict__ wsum_x, const int32_t *__restrict__ wsum_h,
+                                    const int32_t *__restrict__ bw_q, const int32_t *__restrict__ br_q,
+                                    FsChannels ch, float zp_x, float zp_h, float *__restrict__ chan, int C) {
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= C) return;
+    chan[m] = fs_offset(wsum_x[m], zp_x);
+    chan[C + m] = fs_bias_term(bw_q[m], ch.inv_bw[m]);
+    chan[2 * C + m] = ch.inv_gemm_x[m];
+    chan[3 * C + m] = fs_offset(wsum_h[m], zp_h);
+    chan[4 * C + m] = fs_bias_term(br_q[m], ch.inv_br[m]);
+    chan[5 * C + m] = ch.inv_gemm_h[m];
+}
+
+// PointwiseOperationsFP<false, false> (src/gru_forward_gpu_quant_fp.cu:572-770) as its own launch:
+// one thread per (hidden unit, batch row).  Used where the persistent kernel below has no plan.
+__global__ void k_fs_cell(const int32_t *__restrict__ ih_acc, const int32_t *__restrict__ hh_acc,
+                          const float *__restrict__ chan, const uint8_t *__restrict__ h8_in,
+                          uint8_t *__restrict__ h8_out, float *__restrict__ h_out, int B, int H, int Hpad,
+                          FsConsts fc) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = blockIdx.y;
+    if (j >= H || b >= B) return;
+    const int C = 3 * H;
+    const size_t w = (size_t)b * C + j;
+    float ih[3], hh[3];
+#pragma unroll
+    for (int g = 0; g < 3; ++g) {
+        const int m = j + g * H;
+        ih[g] = fs_linear(ih_acc[w + g * H], chan[m], chan[C + m], chan[2 * C + m], fc.zp_ih, fc.ih_lo, fc.ih_hi);
+        hh[g] = fs_linear(hh_acc[w + g * H], chan[3 * C + m], chan[4 * C + m], chan[5 * C + m], fc.zp_hh,
+                          fc.hh_lo, fc.hh_hi);
+    }
+    const float h_old = (float)state_byte(h8_in[(size_t)b * Hpad + j], fc.h_bits);
+    const float h_new = fs_cell(fc, ih, hh, h_old);
     h8_out[(size_t)b * Hpad + j] = (uint8_t)(int)h_new;
     h_out[(size_t)b * H + j] = (h_new - fc.zp_h) * fc.h_scale;
+}
+
+// The whole recurrence in one launch: k_recurrence_dp4a's organisation (a CTA keeps its slice of
+// R in shared memory for all T steps, the P CTAs of a group of batch rows meet once per step at
+// a counter in global memory, bounded spin) with the float-storage epilogue.  Shared memory:
+// chan[6][3*Hs] floats | Rs[3][kw][Hs] words | hs[Bt][kw] words.
+struct FsRecArgs {
+    FsConsts fc;
+    const int32_t *ih_acc;   // [T*B][3H] raw sums of W*x
+    const float *chan;       // [6][3H]
+};
+
+template <bool HUnsigned>
+__global__ void __launch_bounds__(256, 1) k_fs_recurrence(RecArgs a, FsRecArgs f) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int kw = a.Hpad >> 2;
+    float *chan = reinterpret_cast<float *>(smem_raw);
+    size_t off = ((size_t)18 * a.Hs * 4 + 15) & ~size_t(15);
+    unsigned *Rs = reinterpret_cast<unsigned *>(smem_raw + off);
+    off += (size_t)3 * kw * a.Hs * 4;
+    unsigned *hs = reinterpret_cast<unsigned *>(smem_raw + off);
+
+    const int grp = blockIdx.x / a.P, p = blockIdx.x % a.P;
+    const int j0 = p * a.Hs, b0 = grp * a.Bt;
+    const int nb = min(a.Bt, a.B - b0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const FsConsts &fc = f.fc;
+
+    for (int i = tid; i < 18 * a.Hs; i += 256) {
+        const int q = i / (3 * a.Hs), r = i % (3 * a.Hs);
+        const int g = r / a.Hs, j = j0 + r % a.Hs;
+        chan[i] = (j < a.H) ? f.chan[(size_t)q * a.C + g * a.H + j] : 0.f;
+    }
+    {
+        const unsigned *r8w = reinterpret_cast<const unsigned *>(a.r8);
+        const int total = 3 * a.Hs * kw;
+        for (int i = tid; i < total; i += 256) {
+            const int k4 = i % kw, gj = i / kw;
+            const int g = gj / a.Hs, jl = gj % a.Hs, j = j0 + jl;
+            Rs[(g * kw + k4) * a.Hs + jl] = (j < a.H) ? r8w[(size_t)(g * a.H + j) * kw + k4] : 0u;
+        }
+    }
+    __syncthreads();
+
+    const int JW = a.Hs >> 5;
+    const int BW = 8 / JW;
+    const int wj = warp % JW, wb = warp / JW;
+    const int jl = wj * 32 + lane, j = j0 + jl;
+    const bool j_ok = j < a.H;
+    constexpr int NB = 4;
+    const size_t BH = (size_t)a.B * a.H;
+    unsigned *bar = a.bar + grp * 32;
+    bool dead = false;
+
+    for (int s = 0; s < a.T; ++s) {
+        const int t = a.reverse ? (a.T - 1 - s) : s;
+        const long long out_slot = a.reverse ? (a.T - 1 - s) : (s + 1);
+        const uint8_t *h_cur = a.h8 + (size_t)(s & 1) * a.B * a.Hpad;
+        uint8_t *h_nxt = a.h8 + (size_t)((s + 1) & 1) * a.B * a.Hpad;
+
+        if (a.P > 1 && s > 0) {
+            if (tid == 0) {
+                const unsigned want = (unsigned)a.P * (unsigned)s;
+                unsigned it = 0;
+                while (ld_acquire(bar) < want) {
+                    if (++it > a.spin_limit || (it % 1024 == 0 && *(volatile int *)a.abort_flag)) {
+                        atomicOr(a.abort_flag, 1);
+                        break;
+                    }
+                }
+            }
+            __syncthreads();
+            if (tid == 0 && *(volatile int *)a.abort_flag) dead = true;
+            if (__syncthreads_or(dead)) break;
+        }
+        {
+            const uint4 *src = reinterpret_cast<const uint4 *>(h_cur + (size_t)b0 * a.Hpad);
+            uint4 *dst = reinterpret_cast<uint4 *>(hs);
+            const int total = nb * (a.Hpad >> 4);
+            for (int i = tid; i < total; i += 256) dst[i] = __ldcg(src + i);
+        }
+        __syncthreads();
+
+        for (int bb = wb * NB; bb < nb; bb += BW * NB) {
+            int acc[NB][3];
+#pragma unroll
+            for (int u = 0; u < NB; ++u) acc[u][0] = acc[u][1] = acc[u][2] = 0;
+            int32_t ihv[NB][3];
+#pragma unroll
+            for (int u = 0; u < NB; ++u) {
+                const int b = bb + u;
+#pragma unroll
+                for (int g = 0; g < 3; ++g)
+                    ihv[u][g] = (b < nb && j_ok) ? f.ih_acc[((size_t)t * a.B + b0 + b) * a.C + g * a.H + j] : 0;
+            }
+            for (int k4 = 0; k4 < kw; k4 += 4) {
+                uint4 hv[NB];
+#pragma unroll
+                for (int u = 0; u < NB; ++u) {
+                    const int b = min(bb + u, nb - 1);
+                    hv[u] = *reinterpret_cast<const uint4 *>(hs + (size_t)b * kw + k4);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int wz = (int)Rs[(0 * kw + k4 + q) * a.Hs + jl];
+                    const int wr = (int)Rs[(1 * kw + k4 + q) * a.Hs + jl];
+                    const int wn = (int)Rs[(2 * kw + k4 + q) * a.Hs + jl];
+#pragma unroll
+                    for (int u = 0; u < NB; ++u) {
+                        const unsigned h4 = q == 0 ? hv[u].x : q == 1 ? hv[u].y : q == 2 ? hv[u].z : hv[u].w;
+                        acc[u][0] = dp4a_w<HUnsigned>(wz, h4, acc[u][0]);
+                        acc[u][1] = dp4a_w<HUnsigned>(wr, h4, acc[u][1]);
+                        acc[u][2] = dp4a_w<HUnsigned>(wn, h4, acc[u][2]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < NB; ++u) {
+                const int b = bb + u;
+                if (b >= nb || !j_ok) continue;
+                float ih[3], hh[3];
+#pragma unroll
+                for (int g = 0; g < 3; ++g) {
+                    const int c = g * a.Hs + jl;
+                    ih[g] = fs_linear(ihv[u][g], chan[c], chan[3 * a.Hs + c], chan[6 * a.Hs + c], fc.zp_ih,
+                                      fc.ih_lo, fc.ih_hi);
+                    hh[g] = fs_linear(acc[u][g], chan[9 * a.Hs + c], chan[12 * a.Hs + c], chan[15 * a.Hs + c],
+                                      fc.zp_hh, fc.hh_lo, fc.hh_hi);
+                }
+                const uint8_t hb = reinterpret_cast<const uint8_t *>(hs)[(size_t)b * a.Hpad + j];
+                const float h_old = HUnsigned ? (float)hb : (float)(int8_t)hb;
+                const float hn = fs_cell(fc, ih, hh, h_old);
+                h_nxt[(size_t)(b0 + b) * a.Hpad + j] = (uint8_t)(int)hn;
+                a.hf_out[(size_t)out_slot * BH + (size_t)(b0 + b) * a.H + j] = (hn - fc.zp_h) * fc.h_scale;
+            }
+        }
+        __syncthreads();
+        if (a.P > 1 && tid == 0) {
+            __threadfence();
+            atomicAdd(bar, 1u);
+        }
+    }
 }
 
 namespace {
@@ -205,7 +374,11 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
     fc.h_bits = h->h_uns ? 9 : 8;
 
     int rc;
-    if ((rc = ensure(h, h->fs_ch, (size_t)4 * C * sizeof(float)))) return rc;
+    // per-channel constants: 4 x C scale ratios from the host, then 6 x C derived on the device
+    // from the packed weights (column sums, quantized biases)
+    if ((rc = ensure(h, h->fs_ch, (size_t)10 * C * sizeof(float)))) return rc;
+    float *chp = (float *)h->fs_ch.p;
+    float *chan = chp + (size_t)4 * C;
     if (!h->fs_ready) {
         std::vector<float> hostc((size_t)4 * C);
         for (int m = 0; m < C; ++m) {
@@ -216,17 +389,19 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
             hostc[2 * C + m] = s_rh / ohh.scale;
             hostc[3 * C + m] = h->sc[3][m] / s_rh;
         }
-        CK(cudaMemcpyAsync(h->fs_ch.p, hostc.data(), hostc.size() * sizeof(float), cudaMemcpyHostToDevice, st));
+        CK(cudaMemcpyAsync(chp, hostc.data(), hostc.size() * sizeof(float), cudaMemcpyHostToDevice, st));
         CK(cudaStreamSynchronize(st));   // hostc leaves scope
+        const FsChannels ch{chp, chp + C, chp + 2 * C, chp + 3 * C};
+        k_fs_channel_consts<<<(C + 127) / 128, 128, 0, st>>>(h->d_wsum[0], h->d_wsum[1], h->d_wq[2], h->d_wq[3], ch,
+                                                            fc.zp_x, fc.zp_h, chan, C);
+        CK(cudaGetLastError());
+        h->launches++;
         h->fs_ready = true;
     }
-    const float *chp = (const float *)h->fs_ch.p;
-    const FsChannels ch{chp, chp + C, chp + 2 * C, chp + 3 * C};
 
     if ((rc = ensure(h, h->x8, (size_t)((N + 127) / 128 * 128) * h->Ipad))) return rc;
     if ((rc = ensure(h, h->h8, (size_t)(2 * B + 256) * h->Hpad))) return rc;
     if ((rc = ensure(h, h->ih32, (size_t)N * C * 4))) return rc;
-    if ((rc = ensure(h, h->hh32, (size_t)B * C * 4))) return rc;
     const bool rev = flags & QGRU_FLAG_REVERSE;
     const long long init_slot = rev ? T : 0;
     uint8_t *h8 = (uint8_t *)h->h8.p;
@@ -235,6 +410,7 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
     h->ev = h->ring[h->calls % qgru_handle::kRing];
     h->calls++;
     CK(cudaEventRecord(h->ev[0], st));
+    CK(cudaMemsetAsync(h->d_flags, 0, 2 * sizeof(int), st));
     k_fs_quantize_rows<<<grid_for(N * (h->Ipad / 4), 256, h->sm_count), 256, 0, st>>>(
         x, (uint8_t *)h->x8.p, xq_out, N, h->I, h->Ipad, h->x_scale, fc.zp_x, op_lo(ox), op_hi(ox));
     CK(cudaMemsetAsync(h8, 0, (size_t)(2 * B + 256) * h->Hpad, st));
@@ -252,29 +428,71 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
     }
     CK(cudaEventRecord(h->ev[2], st));
     h->launches += 3;
-    const size_t BH = (size_t)B * H;
-    for (int s = 0; s < T; ++s) {
-        const int t = rev ? T - 1 - s : s;
-        const size_t out_slot = rev ? (size_t)(T - 1 - s) : (size_t)(s + 1);
-        const uint8_t *hin = h8 + (size_t)(s & 1) * h8_half;
-        uint8_t *hout = h8 + (size_t)((s + 1) & 1) * h8_half;
-        dim3 g1((unsigned)((B + 63) / 64), (unsigned)((C + 63) / 64));
-        if (h->h_uns)
-            k_gemm_wx_simt<true, int32_t, true><<<g1, 256, 0, st>>>(hin, h->d_w8[1], (int32_t *)h->hh32.p, B, C,
-                                                                  h->Hpad, LinearConsts{});
-        else
-            k_gemm_wx_simt<false, int32_t, true><<<g1, 256, 0, st>>>(hin, h->d_w8[1], (int32_t *)h->hh32.p, B, C,
-                                                                   h->Hpad, LinearConsts{});
-        dim3 g2((H + 127) / 128, B);
-        k_fs_cell<<<g2, 128, 0, st>>>((const int32_t *)h->ih32.p + (size_t)t * B * C, (const int32_t *)h->hh32.p,
-                                      h->d_wsum[0], h->d_wsum[1], h->d_wq[2], h->d_wq[3], ch, hin, hout,
-                                      h_out + out_slot * BH, B, H, h->Hpad, fc);
-        h->launches += 2;
+    char buf[200];
+    RecPlan pl;
+    if (h->opt_rec != 3 && plan_recurrence(h, B, &pl)) {
+        // the whole recurrence in one launch
+        if (pl.G > h->bar_groups) {
+            if ((rc = alloc_dev(h, &h->d_bar, (size_t)pl.G * 32))) return rc;
+            h->bar_groups = pl.G;
+        }
+        CK(cudaMemsetAsync(h->d_bar, 0, (size_t)pl.G * 32 * sizeof(unsigned), st));
+        RecArgs a{};
+        a.T = T; a.B = B; a.H = H; a.Hpad = h->Hpad; a.C = C;
+        a.Hs = pl.Hs; a.Bt = pl.Bt; a.P = pl.P;
+        a.reverse = rev ? 1 : 0;
+        a.r8 = h->d_w8[1];
+        a.h8 = h8;
+        a.hf_out = h_out;
+        a.bar = h->d_bar;
+        a.abort_flag = h->d_flags + 1;
+        a.spin_limit = h->spin_limit;
+        FsRecArgs f{fc, (const int32_t *)h->ih32.p, chan};
+        auto kern = h->h_uns ? k_fs_recurrence<true> : k_fs_recurrence<false>;
+        CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+        const int grid = pl.G * pl.P;
+        if (pl.P > 1) {
+            if (!h->coop) return fail(h, QGRU_ERR_UNSUPPORTED, "device lacks cooperative launch");
+            int per_sm = 0;
+            CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, 256, pl.smem));
+            if ((long long)per_sm * h->sm_count < grid)
+                return fail(h, QGRU_ERR_UNSUPPORTED, "recurrence grid cannot be co-resident");
+            void *args[] = {&a, &f};
+            CK(cudaLaunchCooperativeKernel((void *)kern, dim3(grid), dim3(256), args, pl.smem, st));
+        } else {
+            kern<<<grid, 256, pl.smem, st>>>(a, f);
+            CK(cudaGetLastError());
+        }
+        h->launches++;
+        snprintf(buf, sizeof(buf), "path=float_storage gemm=simt_dp4a_raw rec=dp4a_float_cell Hs=%d Bt=%d P=%d G=%d smem=%zu",
+                 pl.Hs, pl.Bt, pl.P, pl.G, pl.smem);
+    } else {
+        // two launches per step, as the reference
+        if ((rc = ensure(h, h->hh32, (size_t)B * C * 4))) return rc;
+        const size_t BH = (size_t)B * H;
+        for (int s = 0; s < T; ++s) {
+            const int t = rev ? T - 1 - s : s;
+            const size_t out_slot = rev ? (size_t)(T - 1 - s) : (size_t)(s + 1);
+            const uint8_t *hin = h8 + (size_t)(s & 1) * h8_half;
+            uint8_t *hout = h8 + (size_t)((s + 1) & 1) * h8_half;
+            dim3 g1((unsigned)((B + 63) / 64), (unsigned)((C + 63) / 64));
+            if (h->h_uns)
+                k_gemm_wx_simt<true, int32_t, true><<<g1, 256, 0, st>>>(hin, h->d_w8[1], (int32_t *)h->hh32.p, B, C,
+                                                                      h->Hpad, LinearConsts{});
+            else
+                k_gemm_wx_simt<false, int32_t, true><<<g1, 256, 0, st>>>(hin, h->d_w8[1], (int32_t *)h->hh32.p, B, C,
+                                                                       h->Hpad, LinearConsts{});
+            dim3 g2((H + 127) / 128, B);
+            k_fs_cell<<<g2, 128, 0, st>>>((const int32_t *)h->ih32.p + (size_t)t * B * C, (const int32_t *)h->hh32.p,
+                                          chan, hin, hout, h_out + out_slot * BH, B, H, h->Hpad, fc);
+            h->launches += 2;
+        }
+        snprintf(buf, sizeof(buf), "path=float_storage gemm=simt_dp4a_raw rec=per_step_float_cell");
     }
     CK(cudaGetLastError());
     CK(cudaEventRecord(h->ev[3], st));
     h->timing_valid = true;
-    h->plan_text = "path=float_storage gemm=simt_dp4a_raw rec=per_step_float_cell";
+    h->plan_text = buf;
     return QGRU_OK;
 }
 
