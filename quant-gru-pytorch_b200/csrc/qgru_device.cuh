@@ -202,6 +202,24 @@ __device__ __forceinline__ int32_t linear_epilogue32(int32_t acc, int32_t corr, 
     return clampi(v, lo, hi);
 }
 
+// ---- float-storage forward (the reference's quantGRUForwardFP): float requantization
+__device__ __forceinline__ float fs_clamp(float v, float lo, float hi) { return fmaxf(lo, fminf(v, hi)); }
+
+// biasRescaleInline (src/gru_forward_gpu_quant_fp.cu:117-142).  acc is the exact integer
+// sum_k W*x; off = float(sum_k W) * zp_in as computeWeightSumKernel leaves it (:442-458, one
+// rounded product); bias_term = round(bias * inv_bias).  Sub, add and multiply are kept as
+// separate roundings, as in the reference's compiled kernel (none of them is an a*b+c there).
+__device__ __forceinline__ float fs_linear(int acc, float off, float bias_term, float inv_gemm,
+                                           float zp_out, float lo, float hi) {
+    const float val = __fsub_rn((float)acc, off);
+    const float combined = __fadd_rn(val, bias_term);
+    return fs_clamp(rintf(__fmul_rn(combined, inv_gemm)) + zp_out, lo, hi);
+}
+__device__ __forceinline__ float fs_offset(int wsum, float zp_in) { return __fmul_rn((float)wsum, zp_in); }
+__device__ __forceinline__ float fs_bias_term(int bias_q, float inv_bias) {
+    return rintf(__fmul_rn((float)bias_q, inv_bias));
+}
+
 // linear_epilogue32 for a scale with the shift-free form.
 __device__ __forceinline__ int32_t linear_epilogue_fast(int32_t acc, const FastLin &f, int32_t zp_out,
                                                         int32_t lo, int32_t hi) {

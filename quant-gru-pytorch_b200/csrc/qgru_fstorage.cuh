@@ -4,11 +4,13 @@
 // are the real sigmoid / tanh on dequantized inputs - the arithmetic QAT trains against.
 //
 // The reference stores the quantized values in fp32 and multiplies with cuBLAS SGEMM.  Here the
-// operands stay 8 bit: the two matrix products run as exact int32 dp4a GEMMs on the packed
-// weights the integer path already holds (an fp32 sum of integer products below 2^24 is exact
-// too, so both give the same number), and one kernel per step then does what
-// PointwiseOperationsFP does, in the same float operations and in the same order, so that results
-// agree with the reference bit for bit wherever its fp32 sums were exact.
+// operands stay 8 bit: W*x runs on the tcgen05 int8 GEMM of the integer path with the float
+// requantization (biasRescaleInline) as its epilogue, so W*x + bw is stored once, clamped, in one
+// or two bytes; R*h runs as exact dp4a sums inside one persistent kernel that keeps its slice
+// of R in shared memory for all T steps and applies the float cell.  An fp32 sum of integer
+// products below 2^24 is exact too, so both sides see the same sums, and every float operation
+// after them is PointwiseOperationsFP's, in its order: results agree with the reference bit for
+// bit wherever its fp32 sums were exact.
 //
 // Included at the end of qgru_api.cu (it shares that file's kernels).
 #pragma once
@@ -42,8 +44,6 @@ struct FsConsts {
 struct FsChannels {
     const float *inv_gemm_x, *inv_bw, *inv_gemm_h, *inv_br;
 };
-
-__device__ __forceinline__ float fs_clamp(float v, float lo, float hi) { return fmaxf(lo, fminf(v, hi)); }
 
 // quantize_f (include/quantize_ops_helper.h:514-519): the zero point is added before rounding.
 __device__ __forceinline__ float fs_quantize(float x, float scale, float zp, float lo, float hi) {
@@ -94,21 +94,6 @@ __global__ void k_fs_init_state(const float *__restrict__ h0, uint8_t *__restric
     }
 }
 
-// biasRescaleInline (src/gru_forward_gpu_quant_fp.cu:117-142).  acc is the exact integer
-// sum_k W*x; off = float(sum_k W) * zp_in as computeWeightSumKernel leaves it (:442-458, one
-// rounded product); bias_term = round(bias * inv_bias).  Sub, add and multiply are kept as
-// separate roundings, as in the reference's compiled kernel (none of them is an a*b+c there).
-__device__ __forceinline__ float fs_linear(int acc, float off, float bias_term, float inv_gemm,
-                                           float zp_out, float lo, float hi) {
-    const float val = __fsub_rn((float)acc, off);
-    const float combined = __fadd_rn(val, bias_term);
-    return fs_clamp(rintf(__fmul_rn(combined, inv_gemm)) + zp_out, lo, hi);
-}
-__device__ __forceinline__ float fs_offset(int wsum, float zp_in) { return __fmul_rn((float)wsum, zp_in); }
-__device__ __forceinline__ float fs_bias_term(int bias_q, float inv_bias) {
-    return rintf(__fmul_rn((float)bias_q, inv_bias));
-}
-
 __device__ __forceinline__ float fs_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 // The gate and state arithmetic of PointwiseOperationsFP (src/gru_forward_gpu_quant_fp.cu:714-770)
@@ -157,7 +142,8 @@ __global__ void k_fs_channel_consts(const int32_t *__restrict__ wsum_x, const in
 
 // PointwiseOperationsFP<false, false> (src/gru_forward_gpu_quant_fp.cu:572-770) as its own launch:
 // one thread per (hidden unit, batch row).  Used where the persistent kernel below has no plan.
-__global__ void k_fs_cell(const int32_t *__restrict__ ih_acc, const int32_t *__restrict__ hh_acc,
+template <typename IhT>
+__global__ void k_fs_cell(const IhT *__restrict__ ih_q, const int32_t *__restrict__ hh_acc,
                           const float *__restrict__ chan, const uint8_t *__restrict__ h8_in,
                           uint8_t *__restrict__ h8_out, float *__restrict__ h_out, int B, int H, int Hpad,
                           FsConsts fc) {
@@ -170,7 +156,7 @@ __global__ void k_fs_cell(const int32_t *__restrict__ ih_acc, const int32_t *__r
 #pragma unroll
     for (int g = 0; g < 3; ++g) {
         const int m = j + g * H;
-        ih[g] = fs_linear(ih_acc[w + g * H], chan[m], chan[C + m], chan[2 * C + m], fc.zp_ih, fc.ih_lo, fc.ih_hi);
+        ih[g] = (float)ih_q[w + g * H];     // requantized and clamped by the GEMM's epilogue
         hh[g] = fs_linear(hh_acc[w + g * H], chan[3 * C + m], chan[4 * C + m], chan[5 * C + m], fc.zp_hh,
                           fc.hh_lo, fc.hh_hi);
     }
@@ -183,19 +169,19 @@ __global__ void k_fs_cell(const int32_t *__restrict__ ih_acc, const int32_t *__r
 // The whole recurrence in one launch: k_recurrence_dp4a's organisation (a CTA keeps its slice of
 // R in shared memory for all T steps, the P CTAs of a group of batch rows meet once per step at
 // a counter in global memory, bounded spin) with the float-storage epilogue.  Shared memory:
-// chan[6][3*Hs] floats | Rs[3][kw][Hs] words | hs[Bt][kw] words.
+// chan[3][3*Hs] floats (R*h side) | Rs[3][kw][Hs] words | hs[Bt][kw] words.
 struct FsRecArgs {
     FsConsts fc;
-    const int32_t *ih_acc;   // [T*B][3H] raw sums of W*x
+    const void *ih_q;        // [T*B][3H] W*x + bw, requantized and clamped (int8 or int16)
     const float *chan;       // [6][3H]
 };
 
-template <bool HUnsigned>
+template <bool HUnsigned, typename IhT>
 __global__ void __launch_bounds__(256, 1) k_fs_recurrence(RecArgs a, FsRecArgs f) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int kw = a.Hpad >> 2;
     float *chan = reinterpret_cast<float *>(smem_raw);
-    size_t off = ((size_t)18 * a.Hs * 4 + 15) & ~size_t(15);
+    size_t off = ((size_t)9 * a.Hs * 4 + 15) & ~size_t(15);
     unsigned *Rs = reinterpret_cast<unsigned *>(smem_raw + off);
     off += (size_t)3 * kw * a.Hs * 4;
     unsigned *hs = reinterpret_cast<unsigned *>(smem_raw + off);
@@ -206,10 +192,10 @@ __global__ void __launch_bounds__(256, 1) k_fs_recurrence(RecArgs a, FsRecArgs f
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const FsConsts &fc = f.fc;
 
-    for (int i = tid; i < 18 * a.Hs; i += 256) {
+    for (int i = tid; i < 9 * a.Hs; i += 256) {          // the three arrays of the R*h side
         const int q = i / (3 * a.Hs), r = i % (3 * a.Hs);
         const int g = r / a.Hs, j = j0 + r % a.Hs;
-        chan[i] = (j < a.H) ? f.chan[(size_t)q * a.C + g * a.H + j] : 0.f;
+        chan[i] = (j < a.H) ? f.chan[(size_t)(3 + q) * a.C + g * a.H + j] : 0.f;
     }
     {
         const unsigned *r8w = reinterpret_cast<const unsigned *>(a.r8);
@@ -230,6 +216,7 @@ __global__ void __launch_bounds__(256, 1) k_fs_recurrence(RecArgs a, FsRecArgs f
     constexpr int NB = 4;
     const size_t BH = (size_t)a.B * a.H;
     unsigned *bar = a.bar + grp * 32;
+    const IhT *ihp = reinterpret_cast<const IhT *>(f.ih_q);
     bool dead = false;
 
     for (int s = 0; s < a.T; ++s) {
@@ -271,7 +258,7 @@ __global__ void __launch_bounds__(256, 1) k_fs_recurrence(RecArgs a, FsRecArgs f
                 const int b = bb + u;
 #pragma unroll
                 for (int g = 0; g < 3; ++g)
-                    ihv[u][g] = (b < nb && j_ok) ? f.ih_acc[((size_t)t * a.B + b0 + b) * a.C + g * a.H + j] : 0;
+                    ihv[u][g] = (b < nb && j_ok) ? (int32_t)ihp[((size_t)t * a.B + b0 + b) * a.C + g * a.H + j] : 0;
             }
             for (int k4 = 0; k4 < kw; k4 += 4) {
                 uint4 hv[NB];
@@ -302,10 +289,9 @@ __global__ void __launch_bounds__(256, 1) k_fs_recurrence(RecArgs a, FsRecArgs f
 #pragma unroll
                 for (int g = 0; g < 3; ++g) {
                     const int c = g * a.Hs + jl;
-                    ih[g] = fs_linear(ihv[u][g], chan[c], chan[3 * a.Hs + c], chan[6 * a.Hs + c], fc.zp_ih,
-                                      fc.ih_lo, fc.ih_hi);
-                    hh[g] = fs_linear(acc[u][g], chan[9 * a.Hs + c], chan[12 * a.Hs + c], chan[15 * a.Hs + c],
-                                      fc.zp_hh, fc.hh_lo, fc.hh_hi);
+                    ih[g] = (float)ihv[u][g];
+                    hh[g] = fs_linear(acc[u][g], chan[c], chan[3 * a.Hs + c], chan[6 * a.Hs + c], fc.zp_hh,
+                                      fc.hh_lo, fc.hh_hi);
                 }
                 const uint8_t hb = reinterpret_cast<const uint8_t *>(hs)[(size_t)b * a.Hpad + j];
                 const float h_old = HUnsigned ? (float)hb : (float)(int8_t)hb;
@@ -401,11 +387,16 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
 
     if ((rc = ensure(h, h->x8, (size_t)((N + 127) / 128 * 128) * h->Ipad))) return rc;
     if ((rc = ensure(h, h->h8, (size_t)(2 * B + 256) * h->Hpad))) return rc;
-    if ((rc = ensure(h, h->ih32, (size_t)N * C * 4))) return rc;
+    // W*x + bw requantized and clamped to the width of weight_ih_linear: one or two bytes
+    const int ih_bytes = (oih.bits <= 8 && !oih.is_unsigned) ? 1 : 2;
+    if (oih.bits > 16 || (oih.bits == 16 && oih.is_unsigned))
+        return fail(h, QGRU_ERR_UNSUPPORTED, "float-storage forward stores W*x + bw in at most 16 signed bits");
+    if ((rc = ensure(h, h->ih, (size_t)N * C * ih_bytes))) return rc;
     const bool rev = flags & QGRU_FLAG_REVERSE;
     const long long init_slot = rev ? T : 0;
     uint8_t *h8 = (uint8_t *)h->h8.p;
     const size_t h8_half = (size_t)B * h->Hpad;
+    const int sms = h->opt_sm_limit > 0 ? std::min(h->opt_sm_limit, h->sm_count) : h->sm_count;
 
     h->ev = h->ring[h->calls % qgru_handle::kRing];
     h->calls++;
@@ -417,14 +408,31 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
     k_fs_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
         h0, h8, h_out, B, H, h->Hpad, init_slot, fc);
     CK(cudaEventRecord(h->ev[1], st));
-    {
+    // the input projection: exact int32 sums on the tensor cores (dp4a form as fallback), float
+    // requantization in the epilogue
+    LinearConsts lcx = linear_consts(h, 0);
+    lcx.fs = chan;
+    lcx.fs_C = C;
+    bool used_tc = false;
+    if (h->opt_gemm != 1) {
+        PreScale ps{};
+        rc = tc_gemm_launch(h->tc, (const uint8_t *)h->x8.p, (N + 127) / 128 * 128, h->d_w8[0], h->w8_rows[0],
+                            h->ih.p, N, C, h->Ipad, h->x_uns, ih_bytes, lcx, ps, false, h->d_flags + 1, sms, st,
+                            &h->err);
+        if (rc == QGRU_OK) used_tc = true;
+        else if (rc != QGRU_ERR_UNSUPPORTED || h->opt_gemm == 2) return rc;
+    }
+    if (!used_tc) {
         dim3 grid((unsigned)((N + 63) / 64), (unsigned)((C + 63) / 64));
-        if (h->x_uns)
-            k_gemm_wx_simt<true, int32_t, true><<<grid, 256, 0, st>>>((const uint8_t *)h->x8.p, h->d_w8[0],
-                                                                    (int32_t *)h->ih32.p, N, C, h->Ipad, LinearConsts{});
-        else
-            k_gemm_wx_simt<false, int32_t, true><<<grid, 256, 0, st>>>((const uint8_t *)h->x8.p, h->d_w8[0],
-                                                                     (int32_t *)h->ih32.p, N, C, h->Ipad, LinearConsts{});
+        const uint8_t *x8 = (const uint8_t *)h->x8.p;
+        if (ih_bytes == 1) {
+            if (h->x_uns) k_gemm_wx_simt<true, int8_t><<<grid, 256, 0, st>>>(x8, h->d_w8[0], (int8_t *)h->ih.p, N, C, h->Ipad, lcx);
+            else k_gemm_wx_simt<false, int8_t><<<grid, 256, 0, st>>>(x8, h->d_w8[0], (int8_t *)h->ih.p, N, C, h->Ipad, lcx);
+        } else {
+            if (h->x_uns) k_gemm_wx_simt<true, int16_t><<<grid, 256, 0, st>>>(x8, h->d_w8[0], (int16_t *)h->ih.p, N, C, h->Ipad, lcx);
+            else k_gemm_wx_simt<false, int16_t><<<grid, 256, 0, st>>>(x8, h->d_w8[0], (int16_t *)h->ih.p, N, C, h->Ipad, lcx);
+        }
+        CK(cudaGetLastError());
     }
     CK(cudaEventRecord(h->ev[2], st));
     h->launches += 3;
@@ -447,8 +455,9 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
         a.bar = h->d_bar;
         a.abort_flag = h->d_flags + 1;
         a.spin_limit = h->spin_limit;
-        FsRecArgs f{fc, (const int32_t *)h->ih32.p, chan};
-        auto kern = h->h_uns ? k_fs_recurrence<true> : k_fs_recurrence<false>;
+        FsRecArgs f{fc, h->ih.p, chan};
+        auto kern = ih_bytes == 1 ? (h->h_uns ? k_fs_recurrence<true, int8_t> : k_fs_recurrence<false, int8_t>)
+                                  : (h->h_uns ? k_fs_recurrence<true, int16_t> : k_fs_recurrence<false, int16_t>);
         CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
         const int grid = pl.G * pl.P;
         if (pl.P > 1) {
@@ -464,8 +473,8 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
             CK(cudaGetLastError());
         }
         h->launches++;
-        snprintf(buf, sizeof(buf), "path=float_storage gemm=simt_dp4a_raw rec=dp4a_float_cell Hs=%d Bt=%d P=%d G=%d smem=%zu",
-                 pl.Hs, pl.Bt, pl.P, pl.G, pl.smem);
+        snprintf(buf, sizeof(buf), "path=float_storage gemm=%s rec=dp4a_float_cell Hs=%d Bt=%d P=%d G=%d smem=%zu ih_bytes=%d",
+                 used_tc ? "tcgen05_i8" : "simt_dp4a", pl.Hs, pl.Bt, pl.P, pl.G, pl.smem, ih_bytes);
     } else {
         // two launches per step, as the reference
         if ((rc = ensure(h, h->hh32, (size_t)B * C * 4))) return rc;
@@ -483,11 +492,16 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
                 k_gemm_wx_simt<false, int32_t, true><<<g1, 256, 0, st>>>(hin, h->d_w8[1], (int32_t *)h->hh32.p, B, C,
                                                                        h->Hpad, LinearConsts{});
             dim3 g2((H + 127) / 128, B);
-            k_fs_cell<<<g2, 128, 0, st>>>((const int32_t *)h->ih32.p + (size_t)t * B * C, (const int32_t *)h->hh32.p,
-                                          chan, hin, hout, h_out + out_slot * BH, B, H, h->Hpad, fc);
+            if (ih_bytes == 1)
+                k_fs_cell<int8_t><<<g2, 128, 0, st>>>((const int8_t *)h->ih.p + (size_t)t * B * C, (const int32_t *)h->hh32.p,
+                                                      chan, hin, hout, h_out + out_slot * BH, B, H, h->Hpad, fc);
+            else
+                k_fs_cell<int16_t><<<g2, 128, 0, st>>>((const int16_t *)h->ih.p + (size_t)t * B * C, (const int32_t *)h->hh32.p,
+                                                       chan, hin, hout, h_out + out_slot * BH, B, H, h->Hpad, fc);
             h->launches += 2;
         }
-        snprintf(buf, sizeof(buf), "path=float_storage gemm=simt_dp4a_raw rec=per_step_float_cell");
+        snprintf(buf, sizeof(buf), "path=float_storage gemm=%s rec=per_step_float_cell ih_bytes=%d",
+                 used_tc ? "tcgen05_i8" : "simt_dp4a", ih_bytes);
     }
     CK(cudaGetLastError());
     CK(cudaEventRecord(h->ev[3], st));

@@ -168,6 +168,7 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             int64_t corr;
             Rescale rs;
             FastLin fl;
+            float fs_off, fs_bias, fs_ratio;   // float-storage forward (lc.fs set)
         };
         auto load_consts = [&](long long tile) {
             ChanConsts c;
@@ -176,6 +177,10 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             c.corr = m_ok ? lc.corr[m] : 0;
             c.rs = m_ok ? lc.rs[m] : Rescale{1, 1, 0, 0, 0, 0, 0, 0};
             c.fl = m_ok ? lc.fl[m] : FastLin{0, 0, 0, 0, 0, 0};
+            const bool fs_ok = m_ok && lc.fs != nullptr;
+            c.fs_off = fs_ok ? lc.fs[m] : 0.f;
+            c.fs_bias = fs_ok ? lc.fs[lc.fs_C + m] : 0.f;
+            c.fs_ratio = fs_ok ? lc.fs[2 * lc.fs_C + m] : 0.f;
             return c;
         };
         ChanConsts cur = load_consts(blockIdx.x);
@@ -230,6 +235,12 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
 #pragma unroll
                         for (int i = 0; i < 16; ++i) y[i] = linear_epilogue_fast(v[i], fl, lc.zp_out, lc.lo, lc.hi);
                     }
+                } else if (lc.fs != nullptr) {
+                    // float-storage forward: the reference's float requantization of the exact sum
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        y[i] = (int32_t)fs_linear(v[i], cur.fs_off, cur.fs_bias, cur.fs_ratio, (float)lc.zp_out,
+                                                  (float)lc.lo, (float)lc.hi);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {

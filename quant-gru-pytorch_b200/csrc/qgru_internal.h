@@ -83,6 +83,10 @@ struct LinearConsts {
     const FastLin *fl;    // [3H] device: rs and corr in the folded shift-free form (mq == 0: none)
     int32_t zp_out, lo, hi;
     int32_t fits32;       // 1: acc + corr fits int32 for every channel (one widening multiply)
+    // float-storage forward: [3][fs_C] floats (offset, bias term, scale ratio per channel); when
+    // set, the epilogue is the reference's float requantization instead of the integer one
+    const float *fs = nullptr;
+    int32_t fs_C = 0;
 };
 
 }  // namespace qgru

@@ -195,6 +195,9 @@ k_gemm_wx_simt(const uint8_t *__restrict__ x8, const int8_t *__restrict__ w8, Ih
             const int m = m0 + tx + 16 * j;
             if (m >= C) continue;
             if constexpr (Raw) ih[n * C + m] = (IhT)acc[i][j];
+            else if (lc.fs != nullptr)
+                ih[n * C + m] = (IhT)(int32_t)fs_linear(acc[i][j], lc.fs[m], lc.fs[lc.fs_C + m], lc.fs[2 * lc.fs_C + m],
+                                                        (float)lc.zp_out, (float)lc.lo, (float)lc.hi);
             else ih[n * C + m] = (IhT)linear_epilogue(acc[i][j], lc.corr[m], lc.rs[m], lc.zp_out, lc.lo, lc.hi);
         }
     }
