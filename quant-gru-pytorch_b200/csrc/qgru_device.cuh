@@ -220,6 +220,37 @@ __device__ __forceinline__ float fs_bias_term(int bias_q, float inv_bias) {
     return rintf(__fmul_rn((float)bias_q, inv_bias));
 }
 
+__device__ __forceinline__ float fs_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// The gate and state arithmetic of PointwiseOperationsFP (src/gru_forward_gpu_quant_fp.cu:714-770)
+// for one cell: ih / hh are the requantized, clamped linear outputs (z, r, n), h_old the
+// quantized previous state; returns the new quantized state.
+__device__ __forceinline__ float fs_cell(const FsConsts &fc, const float ih[3], const float hh[3],
+                                         float h_old) {
+    // update and reset gates (computeUpdateGateFP / computeResetGateFP, :153-239)
+    float gate[2];
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        const float a = rintf((ih[g] - fc.zp_ih) * fc.ih_to[g]);
+        const float c = rintf((hh[g] - fc.zp_hh) * fc.hh_to[g]);
+        const float in = fs_clamp(a + c + fc.zp_in[g], fc.in_lo[g], fc.in_hi[g]);
+        const float y = fs_sigmoid((in - fc.zp_in[g]) * fc.s_in[g]);
+        gate[g] = fs_clamp(rintf(y / fc.s_out[g] + fc.zp_out[g]), fc.out_lo[g], fc.out_hi[g]);
+    }
+    const float u = gate[0], r = gate[1];
+    // new gate (computeNewGateFP, :241-290)
+    const float rh = rintf(((r - fc.zp_out[1]) * (hh[2] - fc.zp_hh)) * fc.rh_to_n);
+    const float a_n = rintf((ih[2] - fc.zp_ih) * fc.ih_to[2]);
+    const float in_n = fs_clamp(a_n + rh + fc.zp_in[2], fc.in_lo[2], fc.in_hi[2]);
+    const float y_n = tanhf((in_n - fc.zp_in[2]) * fc.s_in[2]);
+    const float n = fs_clamp(rintf(y_n / fc.s_out[2] + fc.zp_out[2]), fc.out_lo[2], fc.out_hi[2]);
+    // state update (computeHiddenStateFP, :302-372)
+    const float n_h = rintf((n - fc.zp_out[2]) * fc.n_to_h) + fc.zp_h;
+    const float old_c = (u - fc.zp_out[0]) * (h_old - fc.zp_h);
+    const float new_c = ((fc.one_q - u) - fc.zp_out[0]) * (n_h - fc.zp_h);
+    return fs_clamp(rintf((old_c + new_c) * fc.uh_to_h) + fc.zp_h, fc.h_lo, fc.h_hi);
+}
+
 // linear_epilogue32 for a scale with the shift-free form.
 __device__ __forceinline__ int32_t linear_epilogue_fast(int32_t acc, const FastLin &f, int32_t zp_out,
                                                         int32_t lo, int32_t hi) {

@@ -73,6 +73,22 @@ struct PreScale {
     int32_t table_n, lo;
 };
 
+// GateQuantParamsFP + the scalar part of LinearRescaleParamsFP
+// (ForwardPassQuantFP::setRescaleParam, src/gru_forward_gpu_quant_fp.cu:821-1003).
+struct FsConsts {
+    float zp_x, zp_h, zp_ih, zp_hh;
+    float zp_in[3], zp_out[3];      // gate inputs / outputs: z, r, n
+    float s_in[3], s_out[3];
+    float ih_to[3];                 // weight_ih_linear -> gate input
+    float hh_to[2];                 // weight_hh_linear -> z, r input
+    float rh_to_n;                  // (r * hh_n) -> new gate input
+    float n_to_h, uh_to_h, one_q;
+    float ih_lo, ih_hi, hh_lo, hh_hi, h_lo, h_hi;
+    float in_lo[3], in_hi[3], out_lo[3], out_hi[3];
+    float h_scale;                  // decoded scale of h, for the dequantized output
+    int h_bits;                     // 8: signed state bytes, 9: unsigned
+};
+
 // Per output channel constants of one fused linear layer:
 //   out = clamp( int32( rescale( acc + corr[m], rs[m] ) ) + zp_out )
 // with corr[m] = rescale(bias_q[m], bias_rs[m]) - zp_in * sum_k W_q[k][m]

@@ -318,6 +318,15 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                 fl[mt][g] = j_ok[mt] ? a.lc.fl[g * a.H + j] : FastLin{0, 0, 0, 0, 0, 0};
             }
         }
+        // float-storage forward: offset, bias term and scale ratio of this thread's three R*h rows
+        float fsk[MT][3][3];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int g = 0; g < 3; ++g)
+#pragma unroll
+                for (int k = 0; k < 3; ++k)
+                    fsk[mt][g][k] = (a.fs_on && j_ok[mt]) ? a.fs_chan[(size_t)k * a.C + g * a.H + j0 + mt * 128 + u] : 0.f;
         bool ok = true;
         {
             // Move tiles [0, tmem_tiles) of the R slice from their TMA-written slots into tensor
@@ -451,6 +460,20 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         tc::tmem_ld4(ta + a.NB, ar);
                         tc::tmem_ld4(ta + 2 * a.NB, an);
                         tc::tmem_ld_wait();
+                        if (!Fused && !Narrow && a.fs_on) {
+                            // float-storage forward: float requantization of the exact sums, real
+                            // sigmoid / tanh (PointwiseOperationsFP of the reference)
+#pragma unroll
+                            for (int i = 0; i < CH; ++i) {
+                                const float fih[3] = {(float)ihv[mt][i][0], (float)ihv[mt][i][1], (float)ihv[mt][i][2]};
+                                const float fhh[3] = {
+                                    fs_linear(az[i], fsk[mt][0][0], fsk[mt][0][1], fsk[mt][0][2], a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi),
+                                    fs_linear(ar[i], fsk[mt][1][0], fsk[mt][1][1], fsk[mt][1][2], a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi),
+                                    fs_linear(an[i], fsk[mt][2][0], fsk[mt][2][1], fsk[mt][2][2], a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi)};
+                                hn[mt][i] = (int32_t)fs_cell(a.fs, fih, fhh, (float)hold[mt][i]);
+                            }
+                            continue;
+                        }
 #pragma unroll
                         for (int i = 0; i < CH; ++i) {
                             int32_t hh_z, hh_r, hh_n;

@@ -33,6 +33,11 @@ struct RecMmaArgs {
     int *abort_flag;
     unsigned spin_limit;
     long long *dbg;         // optional [T][8] clock stamps of CTA 0 (profiling aid), else null
+    // float-storage forward (cluster kernel, generic-cell instantiation only): the float cell of
+    // the reference's quantGRUForwardFP instead of the integer one
+    int fs_on = 0;
+    const float *fs_chan = nullptr;   // [3][C]: offset, bias term, scale ratio of R*h + br per channel
+    FsConsts fs{};
 };
 
 struct RecMmaPlan {

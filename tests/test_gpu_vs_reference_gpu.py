@@ -227,11 +227,13 @@ def test_float_storage_forward_equals_reference_gpu(oracle, reference, refgpu, c
         hd.set_weights_f32(*[_t(a, cuda_device) for a in (case.W, case.R, case.bw, case.br)])
         got_h, got_xq = hd.forward_fstorage(_t(case.x, cuda_device), _t(case.h0, cuda_device), want_x_q=True)
         got_h, got_xq = got_h.cpu().numpy(), got_xq.cpu().numpy()
-        assert "rec=dp4a_float_cell" in hd.describe_plan()          # the one-launch recurrence
-        hd.set_option("rec", "generic")                             # two launches per step
-        step_h = hd.forward_fstorage(_t(case.x, cuda_device), _t(case.h0, cuda_device)).cpu().numpy()
-        assert "rec=per_step_float_cell" in hd.describe_plan()
-        assert np.array_equal(step_h, got_h)
+        for opt, form in (("mma", "rec=tcgen05_i8_float_cell"),     # tensor-core cluster recurrence
+                          ("dp4a", "rec=dp4a_float_cell"),          # one launch, dp4a products
+                          ("generic", "rec=per_step_float_cell")):  # two launches per step
+            hd.set_option("rec", opt)
+            other = hd.forward_fstorage(_t(case.x, cuda_device), _t(case.h0, cuda_device)).cpu().numpy()
+            assert form in hd.describe_plan()
+            assert np.array_equal(other, got_h), form
         hd.set_option("rec", "auto")
         flipped = np.ascontiguousarray(case.x[::-1])
         rev = hd.forward_fstorage(_t(flipped, cuda_device), _t(case.h0, cuda_device), reverse=True).cpu().numpy()
