@@ -223,32 +223,34 @@ __device__ __forceinline__ float fs_bias_term(int bias_q, float inv_bias) {
 __device__ __forceinline__ float fs_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 // The gate and state arithmetic of PointwiseOperationsFP (src/gru_forward_gpu_quant_fp.cu:714-770)
-// for one cell: ih / hh are the requantized, clamped linear outputs (z, r, n), h_old the
-// quantized previous state; returns the new quantized state.
-__device__ __forceinline__ float fs_cell(const FsConsts &fc, const float ih[3], const float hh[3],
-                                         float h_old) {
-    // update and reset gates (computeUpdateGateFP / computeResetGateFP, :153-239)
-    float gate[2];
-#pragma unroll
-    for (int g = 0; g < 2; ++g) {
-        const float a = rintf((ih[g] - fc.zp_ih) * fc.ih_to[g]);
-        const float c = rintf((hh[g] - fc.zp_hh) * fc.hh_to[g]);
-        const float in = fs_clamp(a + c + fc.zp_in[g], fc.in_lo[g], fc.in_hi[g]);
-        const float y = fs_sigmoid((in - fc.zp_in[g]) * fc.s_in[g]);
-        gate[g] = fs_clamp(rintf(y / fc.s_out[g] + fc.zp_out[g]), fc.out_lo[g], fc.out_hi[g]);
-    }
-    const float u = gate[0], r = gate[1];
-    // new gate (computeNewGateFP, :241-290)
-    const float rh = rintf(((r - fc.zp_out[1]) * (hh[2] - fc.zp_hh)) * fc.rh_to_n);
-    const float a_n = rintf((ih[2] - fc.zp_ih) * fc.ih_to[2]);
+// in two pieces, so that a kernel may compute the update and the reset gate on different threads.
+// ih / hh are the requantized, clamped linear outputs, h_old the quantized previous state.
+// computeUpdateGateFP / computeResetGateFP (:153-239); g = 0 update, 1 reset
+__device__ __forceinline__ float fs_sigmoid_gate(const FsConsts &fc, int g, float ih, float hh) {
+    const float a = rintf((ih - fc.zp_ih) * fc.ih_to[g]);
+    const float c = rintf((hh - fc.zp_hh) * fc.hh_to[g]);
+    const float in = fs_clamp(a + c + fc.zp_in[g], fc.in_lo[g], fc.in_hi[g]);
+    const float y = fs_sigmoid((in - fc.zp_in[g]) * fc.s_in[g]);
+    return fs_clamp(rintf(y / fc.s_out[g] + fc.zp_out[g]), fc.out_lo[g], fc.out_hi[g]);
+}
+// computeNewGateFP (:241-290) and computeHiddenStateFP (:302-372): returns the new quantized state
+__device__ __forceinline__ float fs_finish(const FsConsts &fc, float u, float r, float ih_n, float hh_n,
+                                           float h_old) {
+    const float rh = rintf(((r - fc.zp_out[1]) * (hh_n - fc.zp_hh)) * fc.rh_to_n);
+    const float a_n = rintf((ih_n - fc.zp_ih) * fc.ih_to[2]);
     const float in_n = fs_clamp(a_n + rh + fc.zp_in[2], fc.in_lo[2], fc.in_hi[2]);
     const float y_n = tanhf((in_n - fc.zp_in[2]) * fc.s_in[2]);
     const float n = fs_clamp(rintf(y_n / fc.s_out[2] + fc.zp_out[2]), fc.out_lo[2], fc.out_hi[2]);
-    // state update (computeHiddenStateFP, :302-372)
     const float n_h = rintf((n - fc.zp_out[2]) * fc.n_to_h) + fc.zp_h;
     const float old_c = (u - fc.zp_out[0]) * (h_old - fc.zp_h);
     const float new_c = ((fc.one_q - u) - fc.zp_out[0]) * (n_h - fc.zp_h);
     return fs_clamp(rintf((old_c + new_c) * fc.uh_to_h) + fc.zp_h, fc.h_lo, fc.h_hi);
+}
+__device__ __forceinline__ float fs_cell(const FsConsts &fc, const float ih[3], const float hh[3],
+                                         float h_old) {
+    const float u = fs_sigmoid_gate(fc, 0, ih[0], hh[0]);
+    const float r = fs_sigmoid_gate(fc, 1, ih[1], hh[1]);
+    return fs_finish(fc, u, r, ih[2], hh[2], h_old);
 }
 
 // linear_epilogue32 for a scale with the shift-free form.

@@ -394,9 +394,9 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
     RecMmaPlan cp;
     // the tensor-core recurrence of the integer path (one cluster per group of batch rows, h_t
     // exchanged through distributed shared memory) with the float cell as its epilogue
-    // (small batches of a narrow layer run faster on the dp4a form below: measured 0.17 ms against
+    // (small batches of a narrow layer run faster on the SIMT forms below: measured 0.17 ms against
     // 0.28 ms at H = 128, B = 32 and 4.1 against 4.6 us per step at H = 256, B = 1)
-    const bool small = h->opt_rec == 0 && h->Hpad <= 256 && B <= sms;
+    const bool small = (h->opt_rec == 0 || h->opt_rec == 4) && h->Hpad <= 256 && B <= sms;
     const bool cluster_ok = !small && h->opt_rec != 1 && h->opt_rec != 3 && h->opt_exchange != 1 &&
                             rec_cluster_plan(H, h->Hpad, B, sms, h->smem_optin, h->n_table, h->opt_r_where, h->opt_mt, &cp);
     if (cluster_ok) {
@@ -431,6 +431,33 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
         h->launches += h->rec_cl.launches - before;
         snprintf(buf, sizeof(buf), "path=float_storage gemm=%s rec=tcgen05_i8_float_cell exchange=cluster_dsmem NB=%d P=%d G=%d smem=%zu tmem_cols=%d ih_bytes=%d",
                  used_tc ? "tcgen05_i8" : "simt_dp4a", cp.NB, cp.P, cp.G, cp.smem, cp.tmem_cols, ih_bytes);
+    } else if ((h->opt_rec == 0 || h->opt_rec == 4) && gemv_fits(h) && B <= sms) {
+        // one CTA per batch row, the whole R in shared memory, no synchronisation between CTAs
+        RecArgs a{};
+        a.T = T; a.B = B; a.H = H; a.Hpad = h->Hpad; a.C = C;
+        a.reverse = rev ? 1 : 0;
+        a.r8 = h->d_w8[1];
+        a.ih = h->ih.p;
+        a.h8 = h8;
+        a.hf_out = h_out;
+        a.lc = linear_consts(h, 1);
+        a.gc = h->d_gc;
+        a.tables = h->d_tables;
+        a.n_table = 0;
+        a.abort_flag = h->d_flags + 1;
+        a.spin_limit = h->spin_limit;
+        a.fs_chan = chan + (size_t)3 * C;
+        a.fs = fc;
+        auto kern = ih_bytes == 1 ? (h->h_uns ? k_recurrence_gemv<true, int8_t, 3> : k_recurrence_gemv<false, int8_t, 3>)
+                                  : (h->h_uns ? k_recurrence_gemv<true, int16_t, 3> : k_recurrence_gemv<false, int16_t, 3>);
+        const size_t smem = gemv_smem(h, 0);
+        CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        const int threads = 4 * ((H + 31) / 32 * 32);
+        kern<<<B, threads, smem, st>>>(h->gc_host, a);
+        CK(cudaGetLastError());
+        h->launches++;
+        snprintf(buf, sizeof(buf), "path=float_storage gemm=%s rec=gemv_float_cell rows_per_cta=1 ctas=%d smem=%zu ih_bytes=%d",
+                 used_tc ? "tcgen05_i8" : "simt_dp4a", B, smem, ih_bytes);
     } else if (h->opt_rec != 3 && plan_recurrence(h, B, &pl)) {
         // the whole recurrence in one launch
         if (pl.G > h->bar_groups) {

@@ -254,6 +254,10 @@ struct RecArgs {
     unsigned *bar;         // one counter per group, 32 words apart
     int *abort_flag;       // set when a barrier wait ran out; every CTA then leaves
     unsigned spin_limit;
+    // float-storage forward (k_recurrence_gemv with Cell 3): the float cell of the reference's
+    // quantGRUForwardFP; fs_chan = [3][C] offset, bias term, scale ratio of R*h + br per channel
+    const float *fs_chan = nullptr;
+    FsConsts fs{};
 };
 
 // One CTA owns Hs hidden units (all three gates) of one group of Bt batch rows and keeps its
@@ -417,7 +421,8 @@ __global__ void __launch_bounds__(256, 1) k_recurrence_dp4a(RecArgs a) {
 // threads read it ([16-byte chunk][gate][thread]), so every 128-bit load is conflict-free.
 // The state h_t stays in shared memory (two buffers, one __syncthreads per step).
 // Cell: 0 generic datapath, 1 its 32-bit ("narrow") rescales, 2 the tabulated branch-free cell
-// (W*x+bw arrives pre-rescaled from the GEMM; every scale in shift-free form).
+// (W*x+bw arrives pre-rescaled from the GEMM; every scale in shift-free form), 3 the float cell
+// of the float-storage forward (W*x+bw arrives requantized by the GEMM's float epilogue).
 template <bool HUnsigned, typename IhT, int Cell>
 __global__ void __launch_bounds__(1024, 1) k_recurrence_gemv(const __grid_constant__ GateConsts gc, RecArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -466,6 +471,13 @@ __global__ void __launch_bounds__(1024, 1) k_recurrence_gemv(const __grid_consta
             fl[g] = a.lc.fl[g * a.H + j];
         }
         fast = fast && fl[g].mq != 0;
+    }
+    float fsk[3][3] = {};
+    if constexpr (Cell == 3) {
+#pragma unroll
+        for (int g = 0; g < 3; ++g)
+#pragma unroll
+            for (int k = 0; k < 3; ++k) fsk[g][k] = j_ok ? a.fs_chan[(size_t)k * a.C + g * a.H + j] : 0.f;
     }
     __syncthreads();
 
@@ -517,6 +529,14 @@ __global__ void __launch_bounds__(1024, 1) k_recurrence_gemv(const __grid_consta
                 const int32_t z_d = fused_gate_fast(gc, tab, ACT_Z, ihv[0], lin_round(acc[0], fl[0]));
                 const int32_t r_d = fused_gate_fast(gc, tab, ACT_R, ihv[1], lin_round(acc[1], fl[1]));
                 hn = fused_finish_fast(gc, tab, ihv[2], lin_round(acc[2], fl[2]), z_d, r_d, h_old);
+            } else if constexpr (Cell == 3) {
+                // (computing the update and the reset gate on two lanes of the quad measured no faster)
+                const float fih[3] = {(float)ihv[0], (float)ihv[1], (float)ihv[2]};
+                float fhh[3];
+#pragma unroll
+                for (int g = 0; g < 3; ++g)
+                    fhh[g] = fs_linear(acc[g], fsk[g][0], fsk[g][1], fsk[g][2], a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi);
+                hn = (int32_t)fs_cell(a.fs, fih, fhh, (float)h_old);
             } else {
                 int32_t hh[3];
 #pragma unroll

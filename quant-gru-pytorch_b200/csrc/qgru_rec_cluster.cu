@@ -443,6 +443,61 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         for (int i = 0; i < CH; ++i)
                             hn[mt][i] = fused_finish_fast(gc, tab, ihv[mt][i][2], lin_round(acc[mt][i], fl[mt][2]),
                                                           zd[mt][i], rd[mt][i], hold[mt][i]);
+                } else if (!Fused && !Narrow && a.fs_on) {
+                    // float-storage forward: float requantization of the exact sums, real sigmoid /
+                    // tanh (PointwiseOperationsFP of the reference), gate by gate as the MMAs of
+                    // each gate's rows complete
+                    int32_t acc[MT][CH];
+                    float ug[MT][CH], rg[MT][CH];
+                    if (!waited) {
+                        ok = tc::mbar_wait(&mma_done[0], par, WAIT_BUDGET);
+                        if (!ok) break;
+                        tc::tc_fence_after_sync();
+                        if (stamp) a.dbg[s * 8 + 4] = clock64();
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 0) * a.NB), acc[mt]);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                        for (int i = 0; i < CH; ++i)
+                            ug[mt][i] = fs_sigmoid_gate(a.fs, 0, (float)ihv[mt][i][0],
+                                                        fs_linear(acc[mt][i], fsk[mt][0][0], fsk[mt][0][1], fsk[mt][0][2],
+                                                                  a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi));
+                    if (!waited) {
+                        ok = tc::mbar_wait(&mma_done[1], par, WAIT_BUDGET);
+                        if (!ok) break;
+                        tc::tc_fence_after_sync();
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 1) * a.NB), acc[mt]);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                        for (int i = 0; i < CH; ++i)
+                            rg[mt][i] = fs_sigmoid_gate(a.fs, 1, (float)ihv[mt][i][1],
+                                                        fs_linear(acc[mt][i], fsk[mt][1][0], fsk[mt][1][1], fsk[mt][1][2],
+                                                                  a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi));
+                    if (!waited) {
+                        ok = tc::mbar_wait(&mma_done[2], par, WAIT_BUDGET);
+                        if (!ok) break;
+                        tc::tc_fence_after_sync();
+                        waited = true;
+                        if (stamp) a.dbg[s * 8 + 2] = clock64();
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 2) * a.NB), acc[mt]);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                        for (int i = 0; i < CH; ++i)
+                            hn[mt][i] = (int32_t)fs_finish(a.fs, ug[mt][i], rg[mt][i], (float)ihv[mt][i][2],
+                                                           fs_linear(acc[mt][i], fsk[mt][2][0], fsk[mt][2][1], fsk[mt][2][2],
+                                                                     a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi),
+                                                           (float)hold[mt][i]);
                 } else {
                     if (!waited) {
                         ok = tc::mbar_wait(&mma_done[0], par, WAIT_BUDGET) && tc::mbar_wait(&mma_done[1], par, WAIT_BUDGET) &&
@@ -460,20 +515,6 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         tc::tmem_ld4(ta + a.NB, ar);
                         tc::tmem_ld4(ta + 2 * a.NB, an);
                         tc::tmem_ld_wait();
-                        if (!Fused && !Narrow && a.fs_on) {
-                            // float-storage forward: float requantization of the exact sums, real
-                            // sigmoid / tanh (PointwiseOperationsFP of the reference)
-#pragma unroll
-                            for (int i = 0; i < CH; ++i) {
-                                const float fih[3] = {(float)ihv[mt][i][0], (float)ihv[mt][i][1], (float)ihv[mt][i][2]};
-                                const float fhh[3] = {
-                                    fs_linear(az[i], fsk[mt][0][0], fsk[mt][0][1], fsk[mt][0][2], a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi),
-                                    fs_linear(ar[i], fsk[mt][1][0], fsk[mt][1][1], fsk[mt][1][2], a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi),
-                                    fs_linear(an[i], fsk[mt][2][0], fsk[mt][2][1], fsk[mt][2][2], a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi)};
-                                hn[mt][i] = (int32_t)fs_cell(a.fs, fih, fhh, (float)hold[mt][i]);
-                            }
-                            continue;
-                        }
 #pragma unroll
                         for (int i = 0; i < CH; ++i) {
                             int32_t hh_z, hh_r, hh_n;

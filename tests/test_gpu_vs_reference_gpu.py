@@ -227,6 +227,7 @@ def test_float_storage_forward_equals_reference_gpu(oracle, reference, refgpu, c
         hd.set_weights_f32(*[_t(a, cuda_device) for a in (case.W, case.R, case.bw, case.br)])
         got_h, got_xq = hd.forward_fstorage(_t(case.x, cuda_device), _t(case.h0, cuda_device), want_x_q=True)
         got_h, got_xq = got_h.cpu().numpy(), got_xq.cpu().numpy()
+        assert "rec=gemv_float_cell" in hd.describe_plan()          # small batch: one CTA per row
         for opt, form in (("mma", "rec=tcgen05_i8_float_cell"),     # tensor-core cluster recurrence
                           ("dp4a", "rec=dp4a_float_cell"),          # one launch, dp4a products
                           ("generic", "rec=per_step_float_cell")):  # two launches per step
