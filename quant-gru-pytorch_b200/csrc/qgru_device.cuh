@@ -225,26 +225,50 @@ __device__ __forceinline__ float fs_sigmoid(float x) { return 1.0f / (1.0f + exp
 // The gate and state arithmetic of PointwiseOperationsFP (src/gru_forward_gpu_quant_fp.cu:714-770)
 // in two pieces, so that a kernel may compute the update and the reset gate on different threads.
 // ih / hh are the requantized, clamped linear outputs, h_old the quantized previous state.
-// computeUpdateGateFP / computeResetGateFP (:153-239); g = 0 update, 1 reset
-__device__ __forceinline__ float fs_sigmoid_gate(const FsConsts &fc, int g, float ih, float hh) {
-    const float a = rintf((ih - fc.zp_ih) * fc.ih_to[g]);
-    const float c = rintf((hh - fc.zp_hh) * fc.hh_to[g]);
-    const float in = fs_clamp(a + c + fc.zp_in[g], fc.in_lo[g], fc.in_hi[g]);
-    const float y = fs_sigmoid((in - fc.zp_in[g]) * fc.s_in[g]);
+// The activation half of a gate: real_sigmoid_f / real_tanh_f (include/quantize_ops_helper.h:
+// 687-720) on a clamped gate input; g = 0 update, 1 reset (sigmoid), 2 new (tanh).
+__device__ __forceinline__ float fs_activation(const FsConsts &fc, int g, float in) {
+    const float x = (in - fc.zp_in[g]) * fc.s_in[g];
+    const float y = g == 2 ? tanhf(x) : fs_sigmoid(x);
     return fs_clamp(rintf(y / fc.s_out[g] + fc.zp_out[g]), fc.out_lo[g], fc.out_hi[g]);
 }
+// The same through the table (tab: shared-window address of the float table), or directly.
+__device__ __forceinline__ float fs_activation_tab(const FsConsts &fc, uint32_t tab, int g, float in) {
+    if (fc.tab_on) return __int_as_float(lds_i32(tab + 4u * (uint32_t)(fc.tab_off[g] + (int)(in - fc.in_lo[g]))));
+    return fs_activation(fc, g, in);
+}
+// computeUpdateGateFP / computeResetGateFP (:153-239); g = 0 update, 1 reset
+__device__ __forceinline__ float fs_gate_input(const FsConsts &fc, int g, float ih, float hh) {
+    const float a = rintf((ih - fc.zp_ih) * fc.ih_to[g]);
+    const float c = rintf((hh - fc.zp_hh) * fc.hh_to[g]);
+    return fs_clamp(a + c + fc.zp_in[g], fc.in_lo[g], fc.in_hi[g]);
+}
+__device__ __forceinline__ float fs_sigmoid_gate(const FsConsts &fc, int g, float ih, float hh) {
+    return fs_activation(fc, g, fs_gate_input(fc, g, ih, hh));
+}
 // computeNewGateFP (:241-290) and computeHiddenStateFP (:302-372): returns the new quantized state
-__device__ __forceinline__ float fs_finish(const FsConsts &fc, float u, float r, float ih_n, float hh_n,
-                                           float h_old) {
+__device__ __forceinline__ float fs_new_gate_input(const FsConsts &fc, float r, float ih_n, float hh_n) {
     const float rh = rintf(((r - fc.zp_out[1]) * (hh_n - fc.zp_hh)) * fc.rh_to_n);
     const float a_n = rintf((ih_n - fc.zp_ih) * fc.ih_to[2]);
-    const float in_n = fs_clamp(a_n + rh + fc.zp_in[2], fc.in_lo[2], fc.in_hi[2]);
-    const float y_n = tanhf((in_n - fc.zp_in[2]) * fc.s_in[2]);
-    const float n = fs_clamp(rintf(y_n / fc.s_out[2] + fc.zp_out[2]), fc.out_lo[2], fc.out_hi[2]);
+    return fs_clamp(a_n + rh + fc.zp_in[2], fc.in_lo[2], fc.in_hi[2]);
+}
+__device__ __forceinline__ float fs_state(const FsConsts &fc, float u, float n, float h_old) {
     const float n_h = rintf((n - fc.zp_out[2]) * fc.n_to_h) + fc.zp_h;
     const float old_c = (u - fc.zp_out[0]) * (h_old - fc.zp_h);
     const float new_c = ((fc.one_q - u) - fc.zp_out[0]) * (n_h - fc.zp_h);
     return fs_clamp(rintf((old_c + new_c) * fc.uh_to_h) + fc.zp_h, fc.h_lo, fc.h_hi);
+}
+__device__ __forceinline__ float fs_finish(const FsConsts &fc, float u, float r, float ih_n, float hh_n,
+                                           float h_old) {
+    return fs_state(fc, u, fs_activation(fc, 2, fs_new_gate_input(fc, r, ih_n, hh_n)), h_old);
+}
+// The gates through the table where it exists (tab_on), else evaluated.
+__device__ __forceinline__ float fs_sigmoid_gate_tab(const FsConsts &fc, uint32_t tab, int g, float ih, float hh) {
+    return fs_activation_tab(fc, tab, g, fs_gate_input(fc, g, ih, hh));
+}
+__device__ __forceinline__ float fs_finish_tab(const FsConsts &fc, uint32_t tab, float u, float r, float ih_n,
+                                               float hh_n, float h_old) {
+    return fs_state(fc, u, fs_activation_tab(fc, tab, 2, fs_new_gate_input(fc, r, ih_n, hh_n)), h_old);
 }
 __device__ __forceinline__ float fs_cell(const FsConsts &fc, const float ih[3], const float hh[3],
                                          float h_old) {

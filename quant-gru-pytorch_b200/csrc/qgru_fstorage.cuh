@@ -93,6 +93,15 @@ __global__ void k_fs_channel_consts(const int32_t *__restrict__ wsum_x, const in
     chan[5 * C + m] = ch.inv_gemm_h[m];
 }
 
+// Gate outputs over the whole clamped gate-input range, evaluated by the code that evaluates a
+// gate directly (fs_activation), so a lookup returns exactly what the evaluation would.
+__global__ void k_fs_tables(FsConsts fc, float *__restrict__ tab) {
+    const int g = blockIdx.x;
+    const int n = (int)(fc.in_hi[g] - fc.in_lo[g]) + 1;
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+        tab[fc.tab_off[g] + i] = fs_activation(fc, g, fc.in_lo[g] + (float)i);
+}
+
 // PointwiseOperationsFP<false, false> (src/gru_forward_gpu_quant_fp.cu:572-770) as its own launch:
 // one thread per (hidden unit, batch row).  Used where the persistent kernel below has no plan.
 template <typename IhT>
@@ -312,12 +321,26 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
     fc.h_scale = h->h_scale;
     fc.h_bits = h->h_uns ? 9 : 8;
 
+    // gate tables where every gate input has at most 10 bits (3 x 1024 floats of shared memory);
+    // option cell=generic keeps the tables out of the kernels (every gate is evaluated)
+    bool tab_possible = true;
+    int tab_total = 0;
+    for (int g = 0; g < 3; ++g) {
+        const int n = (int)(fc.in_hi[g] - fc.in_lo[g]) + 1;
+        if (n > 1024) tab_possible = false;
+        fc.tab_off[g] = tab_total;
+        tab_total += n;
+    }
+    fc.tab_on = (tab_possible && h->opt_cell != 1) ? 1 : 0;
+    const int n_tab = fc.tab_on ? tab_total : 0;
+
     int rc;
     // per-channel constants: 4 x C scale ratios from the host, then 6 x C derived on the device
-    // from the packed weights (column sums, quantized biases)
-    if ((rc = ensure(h, h->fs_ch, (size_t)10 * C * sizeof(float)))) return rc;
+    // from the packed weights (column sums, quantized biases); then the gate tables
+    if ((rc = ensure(h, h->fs_ch, ((size_t)10 * C + 3 * 1024) * sizeof(float)))) return rc;
     float *chp = (float *)h->fs_ch.p;
     float *chan = chp + (size_t)4 * C;
+    float *gate_tab = chp + (size_t)10 * C;
     if (!h->fs_ready) {
         std::vector<float> hostc((size_t)4 * C);
         for (int m = 0; m < C; ++m) {
@@ -333,8 +356,9 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
         const FsChannels ch{chp, chp + C, chp + 2 * C, chp + 3 * C};
         k_fs_channel_consts<<<(C + 127) / 128, 128, 0, st>>>(h->d_wsum[0], h->d_wsum[1], h->d_wq[2], h->d_wq[3], ch,
                                                             fc.zp_x, fc.zp_h, chan, C);
+        if (tab_possible) k_fs_tables<<<3, 256, 0, st>>>(fc, gate_tab);
         CK(cudaGetLastError());
-        h->launches++;
+        h->launches += 2;
         h->fs_ready = true;
     }
 
@@ -398,7 +422,7 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
     // 0.28 ms at H = 128, B = 32 and 4.1 against 4.6 us per step at H = 256, B = 1)
     const bool small = (h->opt_rec == 0 || h->opt_rec == 4) && h->Hpad <= 256 && B <= sms;
     const bool cluster_ok = !small && h->opt_rec != 1 && h->opt_rec != 3 && h->opt_exchange != 1 &&
-                            rec_cluster_plan(H, h->Hpad, B, sms, h->smem_optin, h->n_table, h->opt_r_where, h->opt_mt, &cp);
+                            rec_cluster_plan(H, h->Hpad, B, sms, h->smem_optin, n_tab, h->opt_r_where, h->opt_mt, &cp);
     if (cluster_ok) {
         if (cp.G > h->bar_groups) {
             if ((rc = alloc_dev(h, &h->d_bar, (size_t)cp.G * 32))) return rc;
@@ -415,8 +439,8 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
         a.hq_out = nullptr;
         a.hf_out = h_out;
         a.lc = linear_consts(h, 1);
-        a.tables = h->d_tables;
-        a.n_table = h->n_table;
+        a.tables = (const int32_t *)gate_tab;   // float bit patterns
+        a.n_table = n_tab;
         a.bar = h->d_bar;
         a.abort_flag = h->d_flags + 1;
         a.spin_limit = h->spin_limit;
@@ -429,9 +453,11 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
                                 h->h_uns, ih_bytes, false, false, st, &h->err);
         if (rc) return rc;
         h->launches += h->rec_cl.launches - before;
-        snprintf(buf, sizeof(buf), "path=float_storage gemm=%s rec=tcgen05_i8_float_cell exchange=cluster_dsmem NB=%d P=%d G=%d smem=%zu tmem_cols=%d ih_bytes=%d",
-                 used_tc ? "tcgen05_i8" : "simt_dp4a", cp.NB, cp.P, cp.G, cp.smem, cp.tmem_cols, ih_bytes);
-    } else if ((h->opt_rec == 0 || h->opt_rec == 4) && gemv_fits(h) && B <= sms) {
+        snprintf(buf, sizeof(buf), "path=float_storage gemm=%s rec=tcgen05_i8_float_cell exchange=cluster_dsmem NB=%d P=%d G=%d smem=%zu tmem_cols=%d ih_bytes=%d gates=%s",
+                 used_tc ? "tcgen05_i8" : "simt_dp4a", cp.NB, cp.P, cp.G, cp.smem, cp.tmem_cols, ih_bytes,
+                 fc.tab_on ? "tabulated" : "evaluated");
+    } else if ((h->opt_rec == 0 || h->opt_rec == 4) && h->Hpad <= 256 && B <= sms &&
+               gemv_smem(h, n_tab) <= (size_t)h->smem_optin) {
         // one CTA per batch row, the whole R in shared memory, no synchronisation between CTAs
         RecArgs a{};
         a.T = T; a.B = B; a.H = H; a.Hpad = h->Hpad; a.C = C;
@@ -442,22 +468,22 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
         a.hf_out = h_out;
         a.lc = linear_consts(h, 1);
         a.gc = h->d_gc;
-        a.tables = h->d_tables;
-        a.n_table = 0;
+        a.tables = (const int32_t *)gate_tab;   // float bit patterns
+        a.n_table = n_tab;
         a.abort_flag = h->d_flags + 1;
         a.spin_limit = h->spin_limit;
         a.fs_chan = chan + (size_t)3 * C;
         a.fs = fc;
         auto kern = ih_bytes == 1 ? (h->h_uns ? k_recurrence_gemv<true, int8_t, 3> : k_recurrence_gemv<false, int8_t, 3>)
                                   : (h->h_uns ? k_recurrence_gemv<true, int16_t, 3> : k_recurrence_gemv<false, int16_t, 3>);
-        const size_t smem = gemv_smem(h, 0);
+        const size_t smem = gemv_smem(h, n_tab);
         CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         const int threads = 4 * ((H + 31) / 32 * 32);
         kern<<<B, threads, smem, st>>>(h->gc_host, a);
         CK(cudaGetLastError());
         h->launches++;
-        snprintf(buf, sizeof(buf), "path=float_storage gemm=%s rec=gemv_float_cell rows_per_cta=1 ctas=%d smem=%zu ih_bytes=%d",
-                 used_tc ? "tcgen05_i8" : "simt_dp4a", B, smem, ih_bytes);
+        snprintf(buf, sizeof(buf), "path=float_storage gemm=%s rec=gemv_float_cell rows_per_cta=1 ctas=%d smem=%zu ih_bytes=%d gates=%s",
+                 used_tc ? "tcgen05_i8" : "simt_dp4a", B, smem, ih_bytes, fc.tab_on ? "tabulated" : "evaluated");
     } else if (h->opt_rec != 3 && plan_recurrence(h, B, &pl)) {
         // the whole recurrence in one launch
         if (pl.G > h->bar_groups) {

@@ -87,6 +87,11 @@ struct FsConsts {
     float in_lo[3], in_hi[3], out_lo[3], out_hi[3];
     float h_scale;                  // decoded scale of h, for the dequantized output
     int h_bits;                     // 8: signed state bytes, 9: unsigned
+    // Gate outputs tabulated over the clamped gate input (built on the device by the very code
+    // that evaluates a gate directly): entry tab_off[g] + (input - in_lo[g]) of a float table the
+    // kernel holds in shared memory.  tab_on = 0: evaluate sigmoid / tanh per cell.
+    int tab_on;
+    int tab_off[3];
 };
 
 // Per output channel constants of one fused linear layer:

@@ -536,7 +536,9 @@ __global__ void __launch_bounds__(1024, 1) k_recurrence_gemv(const __grid_consta
 #pragma unroll
                 for (int g = 0; g < 3; ++g)
                     fhh[g] = fs_linear(acc[g], fsk[g][0], fsk[g][1], fsk[g][2], a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi);
-                hn = (int32_t)fs_cell(a.fs, fih, fhh, (float)h_old);
+                const float u_g = fs_sigmoid_gate_tab(a.fs, tab, 0, fih[0], fhh[0]);
+                const float r_g = fs_sigmoid_gate_tab(a.fs, tab, 1, fih[1], fhh[1]);
+                hn = (int32_t)fs_finish_tab(a.fs, tab, u_g, r_g, fih[2], fhh[2], (float)h_old);
             } else {
                 int32_t hh[3];
 #pragma unroll

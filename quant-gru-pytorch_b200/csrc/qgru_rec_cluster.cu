@@ -462,9 +462,9 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                         for (int i = 0; i < CH; ++i)
-                            ug[mt][i] = fs_sigmoid_gate(a.fs, 0, (float)ihv[mt][i][0],
-                                                        fs_linear(acc[mt][i], fsk[mt][0][0], fsk[mt][0][1], fsk[mt][0][2],
-                                                                  a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi));
+                            ug[mt][i] = fs_sigmoid_gate_tab(a.fs, tab, 0, (float)ihv[mt][i][0],
+                                                            fs_linear(acc[mt][i], fsk[mt][0][0], fsk[mt][0][1], fsk[mt][0][2],
+                                                                      a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi));
                     if (!waited) {
                         ok = tc::mbar_wait(&mma_done[1], par, WAIT_BUDGET);
                         if (!ok) break;
@@ -477,9 +477,9 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                         for (int i = 0; i < CH; ++i)
-                            rg[mt][i] = fs_sigmoid_gate(a.fs, 1, (float)ihv[mt][i][1],
-                                                        fs_linear(acc[mt][i], fsk[mt][1][0], fsk[mt][1][1], fsk[mt][1][2],
-                                                                  a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi));
+                            rg[mt][i] = fs_sigmoid_gate_tab(a.fs, tab, 1, (float)ihv[mt][i][1],
+                                                            fs_linear(acc[mt][i], fsk[mt][1][0], fsk[mt][1][1], fsk[mt][1][2],
+                                                                      a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi));
                     if (!waited) {
                         ok = tc::mbar_wait(&mma_done[2], par, WAIT_BUDGET);
                         if (!ok) break;
@@ -494,7 +494,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                         for (int i = 0; i < CH; ++i)
-                            hn[mt][i] = (int32_t)fs_finish(a.fs, ug[mt][i], rg[mt][i], (float)ihv[mt][i][2],
+                            hn[mt][i] = (int32_t)fs_finish_tab(a.fs, tab, ug[mt][i], rg[mt][i], (float)ihv[mt][i][2],
                                                            fs_linear(acc[mt][i], fsk[mt][2][0], fsk[mt][2][1], fsk[mt][2][2],
                                                                      a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi),
                                                            (float)hold[mt][i]);

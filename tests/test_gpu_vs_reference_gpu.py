@@ -228,6 +228,7 @@ def test_float_storage_forward_equals_reference_gpu(oracle, reference, refgpu, c
         got_h, got_xq = hd.forward_fstorage(_t(case.x, cuda_device), _t(case.h0, cuda_device), want_x_q=True)
         got_h, got_xq = got_h.cpu().numpy(), got_xq.cpu().numpy()
         assert "rec=gemv_float_cell" in hd.describe_plan()          # small batch: one CTA per row
+        assert "gates=tabulated" in hd.describe_plan()
         for opt, form in (("mma", "rec=tcgen05_i8_float_cell"),     # tensor-core cluster recurrence
                           ("dp4a", "rec=dp4a_float_cell"),          # one launch, dp4a products
                           ("generic", "rec=per_step_float_cell")):  # two launches per step
@@ -235,6 +236,12 @@ def test_float_storage_forward_equals_reference_gpu(oracle, reference, refgpu, c
             other = hd.forward_fstorage(_t(case.x, cuda_device), _t(case.h0, cuda_device)).cpu().numpy()
             assert form in hd.describe_plan()
             assert np.array_equal(other, got_h), form
+        hd.set_option("rec", "mma")
+        hd.set_option("cell", "generic")                            # gates evaluated, not tabulated
+        direct = hd.forward_fstorage(_t(case.x, cuda_device), _t(case.h0, cuda_device)).cpu().numpy()
+        assert "gates=evaluated" in hd.describe_plan()
+        assert np.array_equal(direct, got_h)
+        hd.set_option("cell", "auto")
         hd.set_option("rec", "auto")
         flipped = np.ascontiguousarray(case.x[::-1])
         rev = hd.forward_fstorage(_t(flipped, cuda_device), _t(case.h0, cuda_device), reverse=True).cpu().numpy()
