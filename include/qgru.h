@@ -239,6 +239,26 @@ QGRU_API int qgru_forward_i32_train(qgru_handle *h, int T, int B, const int32_t 
 QGRU_API int qgru_forward_fstorage(qgru_handle *h, int T, int B, const float *x, const float *h0,
                                    float *h_out, float *x_q_out, unsigned flags, void *stream);
 
+/* hasteGRUBackward (src/gru_interface.cc:215-240) and quantGRUBackward (:246-290): backward pass
+ * through T steps from the forward's saved h [(T+1),B,H] and v [T,B,4H] (float mode:
+ * qgru_forward_float's v; quantized training: the dequantized training buffer).  All device fp32.
+ * In: W_t [3H,I], R_t [3H,H], x_t [I,T*B] (the transposes, as the reference takes them),
+ * dh_new [(T+1),B,H] (gradient of every output state; slot 0 unused).  In/out, accumulated like
+ * the reference does: dW [I,3H], dR [H,3H], dbw [3H], dbr [3H] (+=), dh [B,H] (in: gradient
+ * arriving at the last state from outside the sequence, normally zeros; out: gradient of h0).
+ * Out: dx [T*B,I].  masks: NULL for the float backward; else the straight-through masks of
+ * the quantized training forward (1 = gradient kept, 0 = the forward clamped there), each
+ * member may be NULL: x [T*B,I], h0 [B,H], W [I,3H], R [H,3H], bw [3H], br [3H], and the five
+ * masks of qgru_masks. */
+typedef struct qgru_bwd_masks {
+    const uint8_t *x, *h0, *W, *R, *bw, *br;
+    const uint8_t *ih_linear, *hh_linear, *gate_input, *gate_output, *h;
+} qgru_bwd_masks;
+QGRU_API int qgru_backward(qgru_handle *h, int T, int B, const float *W_t, const float *R_t,
+                           const float *x_t, const float *dh_new, const float *h_all, const float *v,
+                           float *dx, float *dW, float *dR, float *dbw, float *dbr, float *dh,
+                           const qgru_bwd_masks *masks, void *stream);
+
 /* quantGRUForwardInt (src/gru_interface.cc:610-725), inference mode: float in, float out.
  *   x [T,B,I] f32 device, h0 [B,H] f32 device or NULL, h [(T+1),B,H] f32 device out,
  *   x_q_out [T,B,I] int32 device or NULL. */

@@ -340,6 +340,24 @@ class ReferenceGpu:
         self._check(rc, "ref_gpu_forward_fstorage")
         return h, xq, wq
 
+    def backward(self, T, B, I, H, W, R, bw, br, x, dh_new, h, v, masks=None):
+        """hasteGRUBackward, or quantGRUBackward when `masks` (dict of all eleven uint8 arrays,
+        names as oracle/backward_np.MASK_NAMES) is given: (dx, dW, dR, dbw, dbr, dh)."""
+        from oracle.backward_np import MASK_NAMES
+        f32 = lambda a: np.ascontiguousarray(a, np.float32)  # noqa: E731
+        W_t, R_t = f32(np.asarray(W).T), f32(np.asarray(R).T)
+        x_t = f32(np.asarray(x).transpose(2, 0, 1))
+        outs = [np.zeros((T, B, I), np.float32), np.zeros((I, 3 * H), np.float32), np.zeros((H, 3 * H), np.float32),
+                np.zeros(3 * H, np.float32), np.zeros(3 * H, np.float32), np.zeros((B, H), np.float32)]
+        mptr, keep = None, []
+        if masks is not None:
+            keep = [np.ascontiguousarray(masks[n], np.uint8) for n in MASK_NAMES]
+            mptr = (C.c_void_p * 11)(*[m.ctypes.data for m in keep])
+        rc = self._fn("backward")(T, B, I, H, _f(W_t), _f(R_t), _f(f32(bw)), _f(f32(br)), _f(x_t), _f(f32(dh_new)),
+                                  _f(f32(h)), _f(f32(v)), int(masks is not None), mptr, *[_f(o) for o in outs])
+        self._check(rc, "ref_gpu_backward")
+        return tuple(outs)
+
     def calibrate_minmax(self, T, B, I, H, W, R, bw, br, x, ranges):
         """forwardWithCalibrationGPU(MINMAX): folds one batch into `ranges`; returns h."""
         h = np.zeros((T + 1, B, H), np.float32)

@@ -646,6 +646,41 @@ int ref_gpu_time_forward_fstorage(int T, int B, int I, int H, const float *W, co
     });
 }
 
+// hasteGRUBackward (src/gru_interface.cc:215) or, with use_masks, quantGRUBackward (:246) with
+// all eleven masks (masks[11] in the order of qgru_bwd_masks; each must then be non-null).
+// W_t [3H,I], R_t [3H,H], x_t [I,T*B]; dW..dbr are returned from zero, dh from zero.
+int ref_gpu_backward(int T, int B, int I, int H, const float *W_t, const float *R_t, const float *bw,
+                     const float *br, const float *x_t, const float *dh_new, const float *h,
+                     const float *v, int use_masks, const uint8_t *const *masks, float *dx, float *dW,
+                     float *dR, float *dbw, float *dbr, float *dh) {
+    return guarded([&] {
+        const size_t C3 = size_t(H) * 3, TB = size_t(T) * B;
+        DevBuf<float> dWt(W_t, C3 * I), dRt(R_t, C3 * H), dbw_in(bw, C3), dbr_in(br, C3), dxt(x_t, TB * I),
+            ddh_new(dh_new, (TB + B) * H), dh_all(h, (TB + B) * H), dv(v, TB * H * 4);
+        DevBuf<float> o_dx(TB * I), o_dW(size_t(I) * C3), o_dR(size_t(H) * C3), o_dbw(C3), o_dbr(C3),
+            o_dh(size_t(B) * H);
+        o_dx.zero(); o_dW.zero(); o_dR.zero(); o_dbw.zero(); o_dbr.zero(); o_dh.zero();
+        if (!use_masks) {
+            hasteGRUBackward(T, B, I, H, dWt.p, dRt.p, dbw_in.p, dbr_in.p, dxt.p, ddh_new.p, dh_all.p, dv.p,
+                             blasHandle(), o_dx.p, o_dW.p, o_dR.p, o_dbw.p, o_dbr.p, o_dh.p);
+        } else {
+            const size_t msz[11] = {TB * I, size_t(B) * H, size_t(I) * C3, size_t(H) * C3, C3, C3,
+                                    TB * C3, TB * C3, TB * C3, TB * C3, TB * H};
+            std::unique_ptr<DevBuf<uint8_t>> dm[11];
+            for (int k = 0; k < 11; ++k) {
+                if (!masks || !masks[k]) throw std::invalid_argument("ref_gpu_backward: all masks are required");
+                dm[k].reset(new DevBuf<uint8_t>(masks[k], msz[k]));
+            }
+            quantGRUBackward(T, B, I, H, dWt.p, dRt.p, dbw_in.p, dbr_in.p, dxt.p, ddh_new.p, dh_all.p, dv.p,
+                             blasHandle(), o_dx.p, o_dW.p, o_dR.p, o_dbw.p, o_dbr.p, o_dh.p, nullptr,
+                             dm[0]->p, dm[1]->p, dm[2]->p, dm[3]->p, dm[4]->p, dm[5]->p, dm[6]->p, dm[7]->p,
+                             dm[8]->p, dm[9]->p, dm[10]->p);
+        }
+        cudaOk(cudaDeviceSynchronize(), "backward");
+        o_dx.toHost(dx); o_dW.toHost(dW); o_dR.toHost(dR); o_dbw.toHost(dbw); o_dbr.toHost(dbr); o_dh.toHost(dh);
+    });
+}
+
 // hasteGRUForward (src/gru_interface.cc:173): the reference's fp32 GRU on the GPU.
 int ref_gpu_forward_float(int T, int B, int I, int H, const float *W, const float *R, const float *bw,
                           const float *br, const float *x, const float *h0, float *h, float *v) {

@@ -46,6 +46,12 @@ class Masks(C.Structure):
                 ("gate_output", C.c_void_p), ("h", C.c_void_p)]
 
 
+class BwdMasks(C.Structure):
+    """qgru_bwd_masks: straight-through masks of the quantized backward (device pointers, 0 = absent)."""
+    _fields_ = [(n, C.c_void_p) for n in ("x", "h0", "W", "R", "bw", "br", "ih_linear", "hh_linear",
+                                          "gate_input", "gate_output", "h")]
+
+
 class Ranges(C.Structure):
     _fields_ = [("hidden", C.c_int32), ("reserved", C.c_int32),
                 ("min_v", C.c_float * NUM_OPS), ("max_v", C.c_float * NUM_OPS),
@@ -75,6 +81,7 @@ SYMBOLS = {
     "qgru_set_weights_i32": (C.c_int, [_P, _P, _P, _P, _P, _P]),
     "qgru_get_weights_i32": (C.c_int, [_P, _P, _P, _P, _P, _P]),
     "qgru_forward_i32": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, C.c_uint, _P]),
+    "qgru_backward": (C.c_int, [_P, C.c_int, C.c_int] + [_P] * 14),
     "qgru_forward_fstorage": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, _P, C.c_uint, _P]),
     "qgru_forward_i32_train": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, _P, _P, C.c_uint, _P]),
     "qgru_forward_i32_static": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, C.c_uint, _P]),

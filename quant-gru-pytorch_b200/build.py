@@ -4,7 +4,7 @@ import subprocess
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
-SOURCES = ["qgru_api.cu", "qgru_gemm_tc.cu", "qgru_rec_mma.cu", "qgru_rec_cluster.cu", "qgru_float.cu", "qgru_hist.cu", "qgru_host.cc"]
+SOURCES = ["qgru_api.cu", "qgru_gemm_tc.cu", "qgru_rec_mma.cu", "qgru_rec_cluster.cu", "qgru_float.cu", "qgru_hist.cu", "qgru_backward.cu", "qgru_host.cc"]
 OUT = os.path.join(_HERE, "libqgru_b200.so")
 
 

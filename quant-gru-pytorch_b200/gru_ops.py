@@ -209,6 +209,42 @@ class Handle:
             self.synchronize()
         return (h, x_q) if want_x_q else h
 
+    def backward(self, W, R, x, dh_new, h, v, masks=None, dh_last=None):
+        """Backward pass through the saved forward (hasteGRUBackward; with `masks`, a dict of
+        uint8 tensors named as in qgru_bwd_masks, quantGRUBackward).  W [I,3H], R [H,3H],
+        x [T,B,I], dh_new / h [(T+1),B,H], v [T,B,4H]: CUDA fp32.  Returns
+        (dx [T,B,I], dW, dR, dbw, dbr, dh [B,H])."""
+        T, B = int(x.shape[0]), int(x.shape[1])
+        I, H = self.input_size, self.hidden_size
+        x = _check_tensor(x, "x", torch.float32, (T, B, I))
+        W = _check_tensor(W, "W", torch.float32, (I, 3 * H))
+        R = _check_tensor(R, "R", torch.float32, (H, 3 * H))
+        dh_new = _check_tensor(dh_new, "dh_new", torch.float32, (T + 1, B, H))
+        h = _check_tensor(h, "h", torch.float32, (T + 1, B, H))
+        v = _check_tensor(v, "v", torch.float32, (T, B, 4 * H))
+        x_t = x.permute(2, 0, 1).contiguous()        # [I, T*B]
+        W_t, R_t = W.t().contiguous(), R.t().contiguous()
+        dev = self._tdev
+        dx = torch.empty((T, B, I), dtype=torch.float32, device=dev)
+        dW = torch.zeros((I, 3 * H), dtype=torch.float32, device=dev)
+        dR = torch.zeros((H, 3 * H), dtype=torch.float32, device=dev)
+        dbw = torch.zeros(3 * H, dtype=torch.float32, device=dev)
+        dbr = torch.zeros(3 * H, dtype=torch.float32, device=dev)
+        dh = torch.zeros((B, H), dtype=torch.float32, device=dev) if dh_last is None else \
+            _check_tensor(dh_last, "dh_last", torch.float32, (B, H)).clone()
+        mk, keep = None, []
+        if masks:
+            mk = _cabi.BwdMasks()
+            for name, t in masks.items():
+                if t is not None:
+                    keep.append(_check_tensor(t, name, torch.uint8))   # alive until the call has run
+                    setattr(mk, name, keep[-1].data_ptr())
+        self._ck(self._lib.qgru_backward(self._h, T, B, _ptr(W_t), _ptr(R_t), _ptr(x_t), _ptr(dh_new), _ptr(h),
+                                         _ptr(v), _ptr(dx), _ptr(dW), _ptr(dR), _ptr(dbw), _ptr(dbr), _ptr(dh),
+                                         C.byref(mk) if mk is not None else None, _stream(dev)), "qgru_backward")
+        self.synchronize()
+        return dx, dW, dR, dbw, dbr, dh
+
     # -- forward (host tensors; copies are part of the call)
     def forward_i32_host(self, x_q, h0_q=None, reverse=False, out=None):
         x_q = _check_tensor(x_q, "x_q", torch.int32, cuda=False)
@@ -373,6 +409,27 @@ def forward_quant_float_storage(is_training, time_steps, batch_size, input_size,
     W_q, R_q, bw_q, br_q = [t.to(torch.float32) for t in hd.get_weights_i32()]
     v = torch.empty(0, dtype=torch.float32, device=x.device)
     return h, v, W_q, R_q, bw_q, br_q, x_q
+
+
+def backward_fp(time_steps, batch_size, input_size, hidden_size, W, R, bw, br, x, dh_new, h, v):
+    """Float backward (binding :945-1020): returns (dx, dW, dR, dbw, dbr, dh)."""
+    hd = _handle_for(x.device.index or 0, input_size, hidden_size, "fp")
+    return hd.backward(W, R, x, dh_new, h, v)
+
+
+def backward_quant_float_storage(time_steps, batch_size, input_size, hidden_size, W, R, bw, br, x, dh_new, h, v,
+                                 x_mask=None, h0_mask=None, W_mask=None, R_mask=None, bw_mask=None, br_mask=None,
+                                 weight_ih_linear_mask=None, weight_hh_linear_mask=None, gate_input_mask=None,
+                                 gate_output_mask=None, h_mask=None):
+    """Backward of the quantized training forward with its straight-through masks (binding
+    :1022-1160; W..x are the dequantized quantized tensors the forward returned): returns
+    (dx, dW, dR, dbw, dbr, dh)."""
+    hd = _handle_for(x.device.index or 0, input_size, hidden_size, "fp")
+    masks = {"x": x_mask, "h0": h0_mask, "W": W_mask, "R": R_mask, "bw": bw_mask, "br": br_mask,
+             "ih_linear": weight_ih_linear_mask, "hh_linear": weight_hh_linear_mask,
+             "gate_input": gate_input_mask, "gate_output": gate_output_mask, "h": h_mask}
+    masks = {k: (m if (m is not None and m.numel() > 0) else None) for k, m in masks.items()}
+    return hd.backward(W, R, x, dh_new, h, v, masks=masks)
 
 
 def forward_quantized_int_io(time_steps, batch_size, input_size, hidden_size, W, R, bw, br, x_q,
