@@ -13,8 +13,9 @@ What differs by design: each direction owns a ``gru_ops.Handle`` whose packed we
 re-quantized only when a parameter tensor or the quant params change (the reference
 re-quantizes weights and regenerates LUTs on every call); the reverse direction runs on the
 same input with reversed time indexing instead of two ``flip`` copies; the two directions
-are queued on two CUDA streams.  Training (autograd, backward), ONNX and AIMET hooks are not
-built.
+are queued on two CUDA streams.  Float mode trains: in train() mode with gradients enabled,
+forward runs through an autograd function whose backward is qgru_backward.  Quantization-aware
+training (the quantized forward with autograd), ONNX and AIMET hooks are not built.
 """
 import json
 import math
@@ -44,6 +45,28 @@ def convert_weights_to_haste_format(weight_ih, weight_hh, bias_ih, bias_hh, hidd
         bw = torch.zeros(3 * hidden_size, device=device, dtype=torch.float32)
         br = torch.zeros(3 * hidden_size, device=device, dtype=torch.float32)
     return W, R, bw, br
+
+
+class _FloatGRUFunction(torch.autograd.Function):
+    """One direction of the fp32 GRU with its backward pass (the reference's GRUFunction,
+    pytorch/quant_gru.py:760-1058, float mode): forward keeps h and the gate buffer v, backward
+    is qgru_backward.  Inputs in haste layout: x [T,B,I], W [I,3H], R [H,3H], bw, br [3H],
+    h0 [B,H]; returns h [(T+1),B,H] (slot 0 = h0)."""
+
+    @staticmethod
+    def forward(ctx, handle, x, W, R, bw, br, h0):
+        h, v = handle.forward_float(W, R, bw, br, x, h0, want_v=True)
+        ctx.handle = handle
+        ctx.save_for_backward(x, W, R, h, v)
+        return h
+
+    @staticmethod
+    def backward(ctx, dh_all):
+        x, W, R, h, v = ctx.saved_tensors
+        dh_all = dh_all.contiguous()
+        # the gradient of slot 0 (h0 passed through as an output) is added to what flows back to h0
+        dx, dW, dR, dbw, dbr, dh0 = ctx.handle.backward(W, R, x, dh_all, h, v)
+        return None, dx, dW, dR, dbw, dbr, dh0 + dh_all[0]
 
 
 class _Direction:
@@ -273,9 +296,52 @@ class QuantGRU(nn.Module):
             self._dirs[d].handle.synchronize()
         return outs
 
+    def _forward_float_train(self, input, hx):
+        """Float mode with autograd: every tensor operation outside the two library calls is a
+        torch operation, so gradients reach the module's parameters in their PyTorch layout."""
+        x = input.transpose(0, 1) if self.batch_first else input
+        device = x.device
+        x = x.to(torch.float32).contiguous()
+        T, B, _ = x.shape
+        H = self.hidden_size
+        outs, hns = [], []
+        for d in range(self.num_directions):
+            st = self._direction(d, device)
+            w_ih, w_hh, b_ih, b_hh = self._params_of(d)
+            W = reorder_weights_pytorch_to_haste(w_ih.to(torch.float32)).t().contiguous()
+            R = reorder_weights_pytorch_to_haste(w_hh.to(torch.float32)).t().contiguous()
+            if b_ih is not None and b_hh is not None:
+                bw = reorder_weights_pytorch_to_haste(b_ih.to(torch.float32))
+                br = reorder_weights_pytorch_to_haste(b_hh.to(torch.float32))
+            else:
+                bw = torch.zeros(3 * H, device=device)
+                br = torch.zeros(3 * H, device=device)
+            h0 = hx[d].to(torch.float32).contiguous() if hx is not None else torch.zeros(B, H, device=device)
+            xd = x.flip(0).contiguous() if d == 1 else x
+            h = _FloatGRUFunction.apply(st.handle, xd, W, R, bw, br, h0)
+            outs.append(h[1:].flip(0) if d == 1 else h[1:])
+            hns.append(h[T:T + 1])
+        output = torch.cat(outs, dim=-1) if self.bidirectional else outs[0]
+        h_n = torch.cat(hns, dim=0)
+        if self.batch_first:
+            output = output.transpose(0, 1).contiguous()
+        return output, h_n
+
     # --------------------------------------------------------------------------- forward
-    @torch.no_grad()
     def forward(self, input, hx=None):
+        needs_grad = torch.is_grad_enabled() and (input.requires_grad or (hx is not None and hx.requires_grad) or
+                                                  any(p.requires_grad for p in self.parameters()))
+        if needs_grad and self.training and not self.calibrating and not self.use_quantization:
+            if not input.is_cuda:
+                raise ValueError("input must be a CUDA tensor")
+            want = (self.num_directions, input.shape[0 if self.batch_first else 1], self.hidden_size)
+            if hx is not None and tuple(hx.shape) != want:
+                raise ValueError(f"hx must have shape {list(want)}, got {list(hx.shape)}")
+            return self._forward_float_train(input, hx)
+        with torch.no_grad():
+            return self._forward_impl(input, hx)
+
+    def _forward_impl(self, input, hx=None):
         if self.batch_first:
             input = input.transpose(0, 1)
         device = input.device if input.is_cuda else torch.device("cuda", torch.cuda.current_device())

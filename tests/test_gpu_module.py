@@ -50,8 +50,36 @@ def test_float_mode_matches_torch_gru(cuda_device):
         hx = torch.randn(2 if bidir else 1, 7 if bf else 9, 40) * 0.2
         want_o, want_h = ref(x, hx)
         got_o, got_h = mine.cuda()(x.cuda(), hx.cuda())
-        assert _rel_err(got_o.cpu().numpy(), want_o.detach().numpy()) <= 2e-5
-        assert _rel_err(got_h.cpu().numpy(), want_h.detach().numpy()) <= 2e-5
+        assert _rel_err(got_o.detach().cpu().numpy(), want_o.detach().numpy()) <= 2e-5
+        assert _rel_err(got_h.detach().cpu().numpy(), want_h.detach().numpy()) <= 2e-5
+
+
+@pytest.mark.parametrize("bidir,bf", [(False, False), (True, True)])
+def test_float_mode_trains_like_torch_gru(cuda_device, bidir, bf):
+    """Gradients of a loss over output and h_n through QuantGRU (float mode, train()) against
+    torch.nn.GRU on the CPU in fp32 with the same weights: parameters, input and hx."""
+    import torch
+    torch.manual_seed(1)
+    I, H = 24, 40
+    ref = torch.nn.GRU(I, H, batch_first=bf, bidirectional=bidir)
+    mine = quant_gru.QuantGRU(I, H, batch_first=bf, bidirectional=bidir)
+    mine.load_state_dict(ref.state_dict())
+    mine = mine.cuda().train()
+    x = torch.rand(7, 9, I) * 1.5 - 0.7
+    hx = torch.randn(2 if bidir else 1, 7 if bf else 9, H) * 0.2
+    g_o = torch.randn(7, 9, H * (2 if bidir else 1))
+    g_h = torch.randn_like(hx)
+    xr, hr = x.clone().requires_grad_(), hx.clone().requires_grad_()
+    o, hn = ref(xr, hr)
+    ((o * g_o).sum() + (hn * g_h).sum()).backward()
+    xm, hm = x.cuda().requires_grad_(), hx.cuda().requires_grad_()
+    o2, hn2 = mine(xm, hm)
+    ((o2 * g_o.cuda()).sum() + (hn2 * g_h.cuda()).sum()).backward()
+    assert _rel_err(o2.detach().cpu().numpy(), o.detach().numpy()) <= 2e-5
+    assert _rel_err(xm.grad.cpu().numpy(), xr.grad.numpy()) <= 5e-5
+    assert _rel_err(hm.grad.cpu().numpy(), hr.grad.numpy()) <= 5e-5
+    for (name, p_ref), (_, p_mine) in zip(ref.named_parameters(), mine.named_parameters()):
+        assert _rel_err(p_mine.grad.cpu().numpy(), p_ref.grad.numpy()) <= 5e-5, name
 
 
 def test_minmax_calibration_matches_oracle(oracle, cuda_device):
