@@ -239,6 +239,22 @@ QGRU_API int qgru_forward_i32_train(qgru_handle *h, int T, int B, const int32_t 
 QGRU_API int qgru_forward_fstorage(qgru_handle *h, int T, int B, const float *x, const float *h0,
                                    float *h_out, float *x_q_out, unsigned flags, void *stream);
 
+/* quantGRUForwardFP with is_training = true: the float-storage forward that also returns what
+ * the masked backward needs.  v_out [T,B,4H]: dequantized update, reset and new gate outputs and
+ * R*h + br row of the new gate.  masks (may be NULL, and so may each member): uint8 device out,
+ * 1 = not clamped; the six input masks x [T*B,I], h0 [B,H], W [I,3H], R [H,3H], bw, br [3H]
+ * (W..br: the float master weights, device, needed only for these four) and the five
+ * computation masks of qgru_masks.  Runs on exact int32 sums and a per-step kernel (two launches
+ * per step); h_out equals qgru_forward_fstorage's. */
+typedef struct qgru_train_masks {
+    uint8_t *x, *h0, *W, *R, *bw, *br;
+    uint8_t *ih_linear, *hh_linear, *gate_input, *gate_output, *h;
+} qgru_train_masks;
+QGRU_API int qgru_forward_fstorage_train(qgru_handle *h, int T, int B, const float *W, const float *R,
+                                         const float *bw, const float *br, const float *x, const float *h0,
+                                         float *h_out, float *v_out, float *x_q_out,
+                                         const qgru_train_masks *masks, unsigned flags, void *stream);
+
 /* hasteGRUBackward (src/gru_interface.cc:215-240) and quantGRUBackward (:246-290): backward pass
  * through T steps from the forward's saved h [(T+1),B,H] and v [T,B,4H] (float mode:
  * qgru_forward_float's v; quantized training: the dequantized training buffer).  All device fp32.

@@ -340,6 +340,23 @@ class ReferenceGpu:
         self._check(rc, "ref_gpu_forward_fstorage")
         return h, xq, wq
 
+    def forward_fstorage_train(self, T, B, I, H, W, R, bw, br, x, h0, params, sc):
+        """quantGRUForwardFP, training mode: (h, v dequantized, dict of the eleven masks)."""
+        from oracle.backward_np import MASK_NAMES
+        h = np.zeros((T + 1, B, H), np.float32)
+        v = np.zeros((T, B, 4 * H), np.float32)
+        shapes = {"x": (T * B, I), "h0": (B, H), "W": (I, 3 * H), "R": (H, 3 * H), "bw": (3 * H,), "br": (3 * H,),
+                  "ih_linear": (T * B, 3 * H), "hh_linear": (T * B, 3 * H), "gate_input": (T * B, 3 * H),
+                  "gate_output": (T * B, 3 * H), "h": (T * B, H)}
+        ms = {n: np.zeros(shapes[n], np.uint8) for n in MASK_NAMES}
+        mptr = (C.c_void_p * 11)(*[ms[n].ctypes.data for n in MASK_NAMES])
+        rc = self._fn("forward_fstorage_train")(T, B, I, H, _f(W), _f(R), _f(bw), _f(br),
+                                                _f(np.ascontiguousarray(x, np.float32)),
+                                                _f(np.ascontiguousarray(h0, np.float32)), C.byref(params),
+                                                *[_f(a) for a in sc], _f(h), _f(v), mptr)
+        self._check(rc, "ref_gpu_forward_fstorage_train")
+        return h, v, ms
+
     def backward(self, T, B, I, H, W, R, bw, br, x, dh_new, h, v, masks=None):
         """hasteGRUBackward, or quantGRUBackward when `masks` (dict of all eleven uint8 arrays,
         names as oracle/backward_np.MASK_NAMES) is given: (dx, dW, dR, dbw, dbr, dh)."""

@@ -37,7 +37,8 @@ __device__ __forceinline__ float fs_quantize(float x, float scale, float zp, flo
 // fp32 activations -> 8-bit rows padded to Kpad; optionally the quantized values as floats.
 __global__ void k_fs_quantize_rows(const float *__restrict__ x, uint8_t *__restrict__ out8,
                                    float *__restrict__ xq_out, long long rows, int K, int Kpad,
-                                   float scale, float zp, float lo, float hi) {
+                                   float scale, float zp, float lo, float hi,
+                                   uint8_t *__restrict__ keep = nullptr) {
     const int kw = Kpad >> 2;
     const long long total = rows * kw;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -50,8 +51,10 @@ __global__ void k_fs_quantize_rows(const float *__restrict__ x, uint8_t *__restr
             const int k = k0 + u;
             int q = 0;
             if (k < K) {
-                const float qf = fs_quantize(x[row * K + k], scale, zp, lo, hi);
+                const float raw = rintf(x[row * K + k] / scale + zp);
+                const float qf = fs_clamp(raw, lo, hi);
                 if (xq_out) xq_out[row * K + k] = qf;
+                if (keep) keep[row * K + k] = (raw < lo || raw > hi) ? 0 : 1;
                 q = (int)qf;
             }
             packed |= ((unsigned)q & 0xffu) << (8 * u);
@@ -64,15 +67,17 @@ __global__ void k_fs_quantize_rows(const float *__restrict__ x, uint8_t *__restr
 // 8-bit state rows and, dequantized, into slot `slot` of the output.
 __global__ void k_fs_init_state(const float *__restrict__ h0, uint8_t *__restrict__ h8,
                                 float *__restrict__ h_out, int B, int H, int Hpad, long long slot,
-                                FsConsts fc) {
+                                FsConsts fc, uint8_t *__restrict__ keep = nullptr) {
     const long long total = (long long)B * Hpad;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const int b = (int)(i / Hpad), j = (int)(i % Hpad);
         float q = 0.f;
         if (j < H) {
-            q = h0 ? fs_quantize(h0[(size_t)b * H + j], fc.h_scale, fc.zp_h, fc.h_lo, fc.h_hi) : fc.zp_h;
+            const float raw = h0 ? rintf(h0[(size_t)b * H + j] / fc.h_scale + fc.zp_h) : fc.zp_h;
+            q = fs_clamp(raw, fc.h_lo, fc.h_hi);
             h_out[slot * B * H + (long long)b * H + j] = (q - fc.zp_h) * fc.h_scale;
+            if (keep) keep[(size_t)b * H + j] = (raw < fc.h_lo || raw > fc.h_hi) ? 0 : 1;
         }
         h8[i] = (uint8_t)(int)q;
     }
@@ -126,6 +131,103 @@ __global__ void k_fs_cell(const IhT *__restrict__ ih_q, const int32_t *__restric
     const float h_new = fs_cell(fc, ih, hh, h_old);
     h8_out[(size_t)b * Hpad + j] = (uint8_t)(int)h_new;
     h_out[(size_t)b * H + j] = (h_new - fc.zp_h) * fc.h_scale;
+}
+
+// ---- training mode (quantGRUForwardFP with is_training): the per-step kernel also keeps the gate
+// buffer v and the clamp masks, 1 = the value was inside its range before the clamp
+// (clamp_f<true>, include/quantize_ops_helper.h:416-431).
+
+// Dequantization constants of the four slots of v (dequantificationVFPInplace,
+// src/quantize_ops.cu:368-397): update, reset, new gate outputs, R*h + br row of the new gate.
+struct FsTrainConsts {
+    float scale[4], zp[4];
+};
+
+__device__ __forceinline__ float fs_clamp_keep(float v, float lo, float hi, uint8_t &keep) {
+    keep = (v < lo || v > hi) ? 0 : 1;
+    return fs_clamp(v, lo, hi);
+}
+// biasRescaleInline<true>
+__device__ __forceinline__ float fs_linear_keep(int acc, float off, float bias_term, float inv_gemm,
+                                                float zp_out, float lo, float hi, uint8_t &keep) {
+    const float val = __fsub_rn((float)acc, off);
+    const float combined = __fadd_rn(val, bias_term);
+    return fs_clamp_keep(rintf(__fmul_rn(combined, inv_gemm)) + zp_out, lo, hi, keep);
+}
+// real_sigmoid_f<true> / real_tanh_f<true> on an already clamped gate input
+__device__ __forceinline__ float fs_activation_keep(const FsConsts &fc, int g, float in, uint8_t &keep) {
+    const float x = (in - fc.zp_in[g]) * fc.s_in[g];
+    const float y = g == 2 ? tanhf(x) : fs_sigmoid(x);
+    return fs_clamp_keep(rintf(y / fc.s_out[g] + fc.zp_out[g]), fc.out_lo[g], fc.out_hi[g], keep);
+}
+
+// PointwiseOperationsFP<true, false> (src/gru_forward_gpu_quant_fp.cu:572-770) for one timestep.
+// ih_acc / hh_acc: exact sums of W*x and R*h; masks point at this step's rows, any may be null.
+__global__ void k_fs_cell_train(const int32_t *__restrict__ ih_acc, const int32_t *__restrict__ hh_acc,
+                                const float *__restrict__ chan, const uint8_t *__restrict__ h8_in,
+                                uint8_t *__restrict__ h8_out, float *__restrict__ h_out, float *__restrict__ v,
+                                uint8_t *__restrict__ m_ih, uint8_t *__restrict__ m_hh, uint8_t *__restrict__ m_gin,
+                                uint8_t *__restrict__ m_gout, uint8_t *__restrict__ m_h, int B, int H, int Hpad,
+                                FsConsts fc, FsTrainConsts tc) {
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = blockIdx.y;
+    if (j >= H || b >= B) return;
+    const int C = 3 * H;
+    const size_t w = (size_t)b * C + j;
+    float ih[3], hh[3];
+    uint8_t k_ih[3], k_hh[3], k_in[3], k_out[3], k_h;
+#pragma unroll
+    for (int g = 0; g < 3; ++g) {
+        const int m = j + g * H;
+        ih[g] = fs_linear_keep(ih_acc[w + g * H], chan[m], chan[C + m], chan[2 * C + m], fc.zp_ih, fc.ih_lo,
+                               fc.ih_hi, k_ih[g]);
+        hh[g] = fs_linear_keep(hh_acc[w + g * H], chan[3 * C + m], chan[4 * C + m], chan[5 * C + m], fc.zp_hh,
+                               fc.hh_lo, fc.hh_hi, k_hh[g]);
+    }
+    float gate[2];
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+        const float a = rintf((ih[g] - fc.zp_ih) * fc.ih_to[g]);
+        const float c = rintf((hh[g] - fc.zp_hh) * fc.hh_to[g]);
+        const float in = fs_clamp_keep(a + c + fc.zp_in[g], fc.in_lo[g], fc.in_hi[g], k_in[g]);
+        gate[g] = fs_activation_keep(fc, g, in, k_out[g]);
+    }
+    const float u = gate[0], r = gate[1];
+    const float rh = rintf(((r - fc.zp_out[1]) * (hh[2] - fc.zp_hh)) * fc.rh_to_n);
+    const float a_n = rintf((ih[2] - fc.zp_ih) * fc.ih_to[2]);
+    const float in_n = fs_clamp_keep(a_n + rh + fc.zp_in[2], fc.in_lo[2], fc.in_hi[2], k_in[2]);
+    const float n = fs_activation_keep(fc, 2, in_n, k_out[2]);
+    const float h_old = (float)state_byte(h8_in[(size_t)b * Hpad + j], fc.h_bits);
+    const float n_h = rintf((n - fc.zp_out[2]) * fc.n_to_h) + fc.zp_h;
+    const float old_c = (u - fc.zp_out[0]) * (h_old - fc.zp_h);
+    const float new_c = ((fc.one_q - u) - fc.zp_out[0]) * (n_h - fc.zp_h);
+    const float h_new = fs_clamp_keep(rintf((old_c + new_c) * fc.uh_to_h) + fc.zp_h, fc.h_lo, fc.h_hi, k_h);
+    h8_out[(size_t)b * Hpad + j] = (uint8_t)(int)h_new;
+    h_out[(size_t)b * H + j] = (h_new - fc.zp_h) * fc.h_scale;
+    float *vb = v + (size_t)b * 4 * H + j;
+    vb[0] = (u - tc.zp[0]) * tc.scale[0];
+    vb[H] = (r - tc.zp[1]) * tc.scale[1];
+    vb[2 * H] = (n - tc.zp[2]) * tc.scale[2];
+    vb[3 * H] = (hh[2] - tc.zp[3]) * tc.scale[3];
+#pragma unroll
+    for (int g = 0; g < 3; ++g) {
+        if (m_ih) m_ih[w + g * H] = k_ih[g];
+        if (m_hh) m_hh[w + g * H] = k_hh[g];
+        if (m_gin) m_gin[w + g * H] = k_in[g];
+        if (m_gout) m_gout[w + g * H] = k_out[g];
+    }
+    if (m_h) m_h[(size_t)b * H + j] = k_h;
+}
+
+// Clamp masks of the weight quantization (quantificationPerChannelFP<true>, src/quantize_ops.cu:
+// 155-175): w [K][C] or [C], per-channel scales.
+__global__ void k_fs_weight_mask(const float *__restrict__ w, long long n, int C, const float *__restrict__ scales,
+                                 float lo, float hi, uint8_t *__restrict__ keep) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x) {
+        const float q = rintf(w[i] / scales[i % C]);
+        keep[i] = (q < lo || q > hi) ? 0 : 1;
+    }
 }
 
 // The whole recurrence in one launch: k_recurrence_dp4a's organisation (a CTA keeps its slice of
@@ -277,9 +379,103 @@ float op_hi(const qgru_op &o) { return (float)op_qmax(o); }
 
 }  // namespace
 
+// Training mode: what fstorage_forward does after its constants are ready when the caller wants
+// the gate buffer v and the clamp masks.  Exact int32 sums of both products (dp4a GEMMs), then
+// per step k_fs_cell_train; two launches per step, like the reference.
+struct FsTrainArgs {
+    const float *W, *R, *bw, *br;   // float master weights (device), for the weight masks; may be null
+    float *v;                       // [T,B,4H] dequantized gate buffer
+    qgru_train_masks m;
+};
+
+int fstorage_train_tail(qgru_handle *h, int T, int B, const float *x, const float *h0, float *h_out,
+                        float *xq_out, unsigned flags, cudaStream_t st, const FsConsts &fc, const float *chan,
+                        const FsTrainArgs &tr) {
+    const qgru_params &p = h->p;
+    const int H = h->H, C = h->C, I = h->I;
+    const long long N = (long long)T * B;
+    const bool pot2 = p.use_pot2 != 0;
+    FsTrainConsts tc{};
+    const int v_ops[4] = {QGRU_OP_UPDATE_OUT, QGRU_OP_RESET_OUT, QGRU_OP_NEW_OUT, QGRU_OP_HH_LINEAR};
+    for (int k = 0; k < 4; ++k) {
+        Rescale f;
+        if (!to_fixed_scale(p.op[v_ops[k]].scale, pot2, &f)) return fail(h, QGRU_ERR_RANGE, "scale cannot be encoded");
+        tc.scale[k] = decode_scale(f);
+        tc.zp[k] = (float)p.op[v_ops[k]].zero_point;
+    }
+    int rc;
+    if ((rc = ensure(h, h->x8, (size_t)((N + 127) / 128 * 128) * h->Ipad))) return rc;
+    if ((rc = ensure(h, h->h8, (size_t)(2 * B + 256) * h->Hpad))) return rc;
+    if ((rc = ensure(h, h->ih32, (size_t)N * C * 4))) return rc;
+    if ((rc = ensure(h, h->hh32, (size_t)B * C * 4))) return rc;
+    const qgru_op &ox = p.op[QGRU_OP_X];
+    const bool rev = flags & QGRU_FLAG_REVERSE;
+    const long long init_slot = rev ? T : 0;
+    uint8_t *h8 = (uint8_t *)h->h8.p;
+    const size_t h8_half = (size_t)B * h->Hpad;
+    h->ev = h->ring[h->calls % qgru_handle::kRing];
+    h->calls++;
+    CK(cudaEventRecord(h->ev[0], st));
+    CK(cudaMemsetAsync(h->d_flags, 0, 2 * sizeof(int), st));
+    k_fs_quantize_rows<<<grid_for(N * (h->Ipad / 4), 256, h->sm_count), 256, 0, st>>>(
+        x, (uint8_t *)h->x8.p, xq_out, N, I, h->Ipad, h->x_scale, fc.zp_x, op_lo(ox), op_hi(ox), tr.m.x);
+    CK(cudaMemsetAsync(h8, 0, (size_t)(2 * B + 256) * h->Hpad, st));
+    k_fs_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
+        h0, h8, h_out, B, H, h->Hpad, init_slot, fc, tr.m.h0);
+    // weight masks: W [I][3H], R [H][3H], bw, br [3H] against their per-channel scales
+    const float *wsrc[4] = {tr.W, tr.R, tr.bw, tr.br};
+    uint8_t *wmask[4] = {tr.m.W, tr.m.R, tr.m.bw, tr.m.br};
+    const long long wn[4] = {(long long)I * C, (long long)H * C, C, C};
+    const int wop[4] = {QGRU_OP_W, QGRU_OP_R, QGRU_OP_BW, QGRU_OP_BR};
+    for (int k = 0; k < 4; ++k)
+        if (wsrc[k] && wmask[k])
+            k_fs_weight_mask<<<grid_for(wn[k], 256, h->sm_count), 256, 0, st>>>(
+                wsrc[k], wn[k], C, h->d_wscale[k], op_lo(p.op[wop[k]]), op_hi(p.op[wop[k]]), wmask[k]);
+    CK(cudaEventRecord(h->ev[1], st));
+    {
+        dim3 grid((unsigned)((N + 63) / 64), (unsigned)((C + 63) / 64));
+        if (h->x_uns)
+            k_gemm_wx_simt<true, int32_t, true><<<grid, 256, 0, st>>>((const uint8_t *)h->x8.p, h->d_w8[0],
+                                                                    (int32_t *)h->ih32.p, N, C, h->Ipad, LinearConsts{});
+        else
+            k_gemm_wx_simt<false, int32_t, true><<<grid, 256, 0, st>>>((const uint8_t *)h->x8.p, h->d_w8[0],
+                                                                     (int32_t *)h->ih32.p, N, C, h->Ipad, LinearConsts{});
+    }
+    CK(cudaEventRecord(h->ev[2], st));
+    const size_t BH = (size_t)B * H, BC = (size_t)B * C;
+    for (int s = 0; s < T; ++s) {
+        const int t = rev ? T - 1 - s : s;
+        const size_t out_slot = rev ? (size_t)(T - 1 - s) : (size_t)(s + 1);
+        const uint8_t *hin = h8 + (size_t)(s & 1) * h8_half;
+        uint8_t *hout = h8 + (size_t)((s + 1) & 1) * h8_half;
+        dim3 g1((unsigned)((B + 63) / 64), (unsigned)((C + 63) / 64));
+        if (h->h_uns)
+            k_gemm_wx_simt<true, int32_t, true><<<g1, 256, 0, st>>>(hin, h->d_w8[1], (int32_t *)h->hh32.p, B, C,
+                                                                  h->Hpad, LinearConsts{});
+        else
+            k_gemm_wx_simt<false, int32_t, true><<<g1, 256, 0, st>>>(hin, h->d_w8[1], (int32_t *)h->hh32.p, B, C,
+                                                                   h->Hpad, LinearConsts{});
+        dim3 g2((H + 127) / 128, B);
+        k_fs_cell_train<<<g2, 128, 0, st>>>(
+            (const int32_t *)h->ih32.p + (size_t)t * BC, (const int32_t *)h->hh32.p, chan, hin, hout,
+            h_out + out_slot * BH, tr.v + (size_t)t * B * 4 * H,
+            tr.m.ih_linear ? tr.m.ih_linear + (size_t)t * BC : nullptr,
+            tr.m.hh_linear ? tr.m.hh_linear + (size_t)t * BC : nullptr,
+            tr.m.gate_input ? tr.m.gate_input + (size_t)t * BC : nullptr,
+            tr.m.gate_output ? tr.m.gate_output + (size_t)t * BC : nullptr, tr.m.h ? tr.m.h + (size_t)t * BH : nullptr,
+            B, H, h->Hpad, fc, tc);
+    }
+    h->launches += 4 + 2ull * T;
+    CK(cudaGetLastError());
+    CK(cudaEventRecord(h->ev[3], st));
+    h->timing_valid = true;
+    h->plan_text = "path=float_storage_training gemm=simt_dp4a_raw rec=per_step_float_cell_train";
+    return QGRU_OK;
+}
+
 // Host side of quantGRUForwardFP, inference mode.  x, h0, h_out, xq_out are device pointers.
 int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *h0, float *h_out,
-                     float *xq_out, unsigned flags, cudaStream_t st) {
+                     float *xq_out, unsigned flags, cudaStream_t st, const FsTrainArgs *train = nullptr) {
     if (!h->fast)
         return fail(h, QGRU_ERR_UNSUPPORTED,
                     "float-storage forward needs 8-bit W, R, x and h (the operands of the two products)");
@@ -361,6 +557,7 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
         h->launches += 2;
         h->fs_ready = true;
     }
+    if (train) return fstorage_train_tail(h, T, B, x, h0, h_out, xq_out, flags, st, fc, chan, *train);
 
     if ((rc = ensure(h, h->x8, (size_t)((N + 127) / 128 * 128) * h->Ipad))) return rc;
     if ((rc = ensure(h, h->h8, (size_t)(2 * B + 256) * h->Hpad))) return rc;
@@ -568,6 +765,18 @@ int qgru_forward_fstorage(qgru_handle *h, int T, int B, const float *x, const fl
         return fail(h, QGRU_ERR_NOT_READY, "set_params and set_weights first");
     CK(cudaSetDevice(h->device));
     return qgru::fstorage_forward(h, T, B, x, h0, h_out, x_q_out, flags, (cudaStream_t)stream);
+}
+
+int qgru_forward_fstorage_train(qgru_handle *h, int T, int B, const float *W, const float *R, const float *bw,
+                                const float *br, const float *x, const float *h0, float *h_out, float *v_out,
+                                float *x_q_out, const qgru_train_masks *masks, unsigned flags, void *stream) {
+    if (!h || !x || !h_out || !v_out) return QGRU_ERR_BAD_ARG;
+    if (T <= 0 || B <= 0) return fail(h, QGRU_ERR_BAD_ARG, "T and B must be positive");
+    if (!h->params_set || !h->weights_set)
+        return fail(h, QGRU_ERR_NOT_READY, "set_params and set_weights first");
+    CK(cudaSetDevice(h->device));
+    qgru::FsTrainArgs tr{W, R, bw, br, v_out, masks ? *masks : qgru_train_masks{}};
+    return qgru::fstorage_forward(h, T, B, x, h0, h_out, x_q_out, flags, (cudaStream_t)stream, &tr);
 }
 
 }  // extern "C"

@@ -209,6 +209,33 @@ class Handle:
             self.synchronize()
         return (h, x_q) if want_x_q else h
 
+    MASK_NAMES = ("x", "h0", "W", "R", "bw", "br", "ih_linear", "hh_linear", "gate_input", "gate_output", "h")
+
+    def forward_fstorage_train(self, W, R, bw, br, x, h0=None, reverse=False):
+        """Training mode of the float-storage forward: (h [(T+1),B,H], v [T,B,4H] dequantized,
+        x_q [T,B,I] as floats, masks: dict of the eleven uint8 clamp masks, 1 = not clamped).
+        W..br are the float master weights the handle was loaded with (set_weights_f32)."""
+        x = _check_tensor(x, "x", torch.float32)
+        T, B = int(x.shape[0]), int(x.shape[1])
+        I, H = self.input_size, self.hidden_size
+        ws = [_check_tensor(t, n, torch.float32) for t, n in ((W, "W"), (R, "R"), (bw, "bw"), (br, "br"))]
+        if h0 is not None:
+            h0 = _check_tensor(h0, "h0", torch.float32, (B, H))
+        dev = self._tdev
+        h = torch.empty((T + 1, B, H), dtype=torch.float32, device=dev)
+        v = torch.empty((T, B, 4 * H), dtype=torch.float32, device=dev)
+        x_q = torch.empty((T, B, I), dtype=torch.float32, device=dev)
+        shapes = {"x": (T * B, I), "h0": (B, H), "W": (I, 3 * H), "R": (H, 3 * H), "bw": (3 * H,), "br": (3 * H,),
+                  "ih_linear": (T * B, 3 * H), "hh_linear": (T * B, 3 * H), "gate_input": (T * B, 3 * H),
+                  "gate_output": (T * B, 3 * H), "h": (T * B, H)}
+        masks = {n: torch.ones(shapes[n], dtype=torch.uint8, device=dev) for n in self.MASK_NAMES}
+        mk = _cabi.BwdMasks(*[masks[n].data_ptr() for n in self.MASK_NAMES])
+        self._ck(self._lib.qgru_forward_fstorage_train(
+            self._h, T, B, *[_ptr(t) for t in ws], _ptr(x), _ptr(h0), _ptr(h), _ptr(v), _ptr(x_q), C.byref(mk),
+            _cabi.FLAG_REVERSE if reverse else 0, _stream(dev)), "qgru_forward_fstorage_train")
+        self.synchronize()
+        return h, v, x_q, masks
+
     def backward(self, W, R, x, dh_new, h, v, masks=None, dh_last=None):
         """Backward pass through the saved forward (hasteGRUBackward; with `masks`, a dict of
         uint8 tensors named as in qgru_bwd_masks, quantGRUBackward).  W [I,3H], R [H,3H],
@@ -391,24 +418,26 @@ def forward_quant_int_storage(is_training, time_steps, batch_size, input_size, h
 
 def forward_quant_float_storage(is_training, time_steps, batch_size, input_size, hidden_size,
                                 W, R, bw, br, x, h0, quant_params, slot=0, reverse=False):
-    """Float-storage quantized forward (binding :283-423, inference mode): quantized values kept
-    as floats, float requantization, real sigmoid / tanh.
+    """Float-storage quantized forward (binding :283-423): quantized values kept as floats, float
+    requantization, real sigmoid / tanh.
 
-    Returns (h [(T+1),B,H] f32, v (empty), W_q, R_q, bw_q, br_q, x_q) with the quantized tensors
-    as float32 like the reference; the masks of its training mode are not produced
-    (is_training must be False)."""
-    if is_training:
-        raise NotImplementedError("the training mode of the float-storage forward serves the backward pass, "
-                                  "which is not built")
+    Returns the reference's 18-tuple (h [(T+1),B,H] f32, v, W_q, R_q, bw_q, br_q, x_q, x_mask,
+    h0_mask, W_mask, R_mask, bw_mask, br_mask, weight_ih_linear_mask, weight_hh_linear_mask,
+    gate_input_mask, gate_output_mask, h_mask) with the quantized tensors as float32; in
+    inference mode v and the masks are empty tensors."""
     x = _check_tensor(x, "x", torch.float32, (time_steps, batch_size, input_size))
     hd = _handle_for(x.device.index or 0, input_size, hidden_size, slot)
     hd.set_params(quant_params)
     hd.set_weights_f32(W, R, bw, br)
     h0 = h0 if (h0 is not None and h0.numel() > 0) else None
-    h, x_q = hd.forward_fstorage(x, h0, reverse=reverse, want_x_q=True)
     W_q, R_q, bw_q, br_q = [t.to(torch.float32) for t in hd.get_weights_i32()]
+    if is_training:
+        h, v, x_q, m = hd.forward_fstorage_train(W, R, bw, br, x, h0, reverse=reverse)
+        return (h, v, W_q, R_q, bw_q, br_q, x_q) + tuple(m[n] for n in Handle.MASK_NAMES)
+    h, x_q = hd.forward_fstorage(x, h0, reverse=reverse, want_x_q=True)
+    e = torch.empty(0, dtype=torch.uint8, device=x.device)
     v = torch.empty(0, dtype=torch.float32, device=x.device)
-    return h, v, W_q, R_q, bw_q, br_q, x_q
+    return (h, v, W_q, R_q, bw_q, br_q, x_q) + (e,) * 11
 
 
 def backward_fp(time_steps, batch_size, input_size, hidden_size, W, R, bw, br, x, dh_new, h, v):
