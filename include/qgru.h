@@ -255,6 +255,16 @@ QGRU_API int qgru_forward_fstorage_train(qgru_handle *h, int T, int B, const flo
                                          float *h_out, float *v_out, float *x_q_out,
                                          const qgru_train_masks *masks, unsigned flags, void *stream);
 
+/* dequantizeGRUWeights (include/gru_interface.h:141): the quantized weights the handle holds,
+ * times their per-channel scales, as device fp32 (W [I,3H], R [H,3H], bw, br [3H]; NULL = skip).
+ * These are the weights the masked backward differentiates through. */
+QGRU_API int qgru_get_weights_dequantized(qgru_handle *h, float *W, float *R, float *bw, float *br,
+                                          void *stream);
+/* dequantize_f (include/quantize_ops_helper.h:510-512) for operator `op` (QGRU_OP_*) of the
+ * handle's parameters on n float-stored quantized values: out = (q - zero_point) * scale. */
+QGRU_API int qgru_dequantize_f32(qgru_handle *h, int op, const float *q, float *out, long long n,
+                                 void *stream);
+
 /* hasteGRUBackward (src/gru_interface.cc:215-240) and quantGRUBackward (:246-290): backward pass
  * through T steps from the forward's saved h [(T+1),B,H] and v [T,B,4H] (float mode:
  * qgru_forward_float's v; quantized training: the dequantized training buffer).  All device fp32.

@@ -767,6 +767,50 @@ int qgru_forward_fstorage(qgru_handle *h, int T, int B, const float *x, const fl
     return qgru::fstorage_forward(h, T, B, x, h0, h_out, x_q_out, flags, (cudaStream_t)stream);
 }
 
+// out[i] = q[i] * scale[i % C]  (dequantizeGRUWeights: weights have zero point 0)
+__global__ void k_dequantize_weights(const int32_t *__restrict__ q, float *__restrict__ out, long long n, int C,
+                                     const float *__restrict__ scales) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x)
+        out[i] = (float)q[i] * scales[i % C];
+}
+// out[i] = (q[i] - zp) * scale on float-stored quantized values (dequantize_f)
+__global__ void k_dequantize_fq(const float *__restrict__ q, float *__restrict__ out, long long n, float scale,
+                                float zp) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x)
+        out[i] = (q[i] - zp) * scale;
+}
+
+int qgru_get_weights_dequantized(qgru_handle *h, float *W, float *R, float *bw, float *br, void *stream) {
+    if (!h) return QGRU_ERR_BAD_ARG;
+    if (!h->weights_set) return fail(h, QGRU_ERR_NOT_READY, "set_weights first");
+    CK(cudaSetDevice(h->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const int C = h->C;
+    const long long n[4] = {(long long)h->I * C, (long long)h->H * C, C, C};
+    float *dst[4] = {W, R, bw, br};
+    for (int k = 0; k < 4; ++k)
+        if (dst[k])
+            k_dequantize_weights<<<grid_for(n[k], 256, h->sm_count), 256, 0, st>>>(h->d_wq[k], dst[k], n[k], C,
+                                                                                h->d_wscale[k]);
+    CK(cudaGetLastError());
+    return QGRU_OK;
+}
+
+int qgru_dequantize_f32(qgru_handle *h, int op, const float *q, float *out, long long n, void *stream) {
+    if (!h || !q || !out || op < 0 || op >= QGRU_NUM_OPS || n < 0) return QGRU_ERR_BAD_ARG;
+    if (!h->params_set) return fail(h, QGRU_ERR_NOT_READY, "set_params first");
+    CK(cudaSetDevice(h->device));
+    Rescale f;
+    if (!to_fixed_scale(h->p.op[op].scale, h->p.use_pot2 != 0, &f)) return fail(h, QGRU_ERR_RANGE, "scale cannot be encoded");
+    if (n)
+        k_dequantize_fq<<<grid_for(n, 256, h->sm_count), 256, 0, (cudaStream_t)stream>>>(
+            q, out, n, decode_scale(f), (float)h->p.op[op].zero_point);
+    CK(cudaGetLastError());
+    return QGRU_OK;
+}
+
 int qgru_forward_fstorage_train(qgru_handle *h, int T, int B, const float *W, const float *R, const float *bw,
                                 const float *br, const float *x, const float *h0, float *h_out, float *v_out,
                                 float *x_q_out, const qgru_train_masks *masks, unsigned flags, void *stream) {

@@ -209,6 +209,22 @@ class Handle:
             self.synchronize()
         return (h, x_q) if want_x_q else h
 
+    def get_weights_dequantized(self):
+        """The handle's quantized weights times their scales: (W [I,3H], R [H,3H], bw, br) fp32."""
+        I, H = self.input_size, self.hidden_size
+        outs = [torch.empty(s, dtype=torch.float32, device=self._tdev) for s in ((I, 3 * H), (H, 3 * H), (3 * H,), (3 * H,))]
+        self._ck(self._lib.qgru_get_weights_dequantized(self._h, *[_ptr(o) for o in outs], _stream(self._tdev)),
+                 "qgru_get_weights_dequantized")
+        return outs
+
+    def dequantize_f32(self, q, op_name):
+        """Float-stored quantized values of operator `op_name` -> real values."""
+        q = _check_tensor(q, "q", torch.float32)
+        out = torch.empty_like(q)
+        self._ck(self._lib.qgru_dequantize_f32(self._h, _cabi.OP_INDEX[op_name], _ptr(q), _ptr(out), q.numel(),
+                                               _stream(self._tdev)), "qgru_dequantize_f32")
+        return out
+
     MASK_NAMES = ("x", "h0", "W", "R", "bw", "br", "ih_linear", "hh_linear", "gate_input", "gate_output", "h")
 
     def forward_fstorage_train(self, W, R, bw, br, x, h0=None, reverse=False):

@@ -13,9 +13,11 @@ What differs by design: each direction owns a ``gru_ops.Handle`` whose packed we
 re-quantized only when a parameter tensor or the quant params change (the reference
 re-quantizes weights and regenerates LUTs on every call); the reverse direction runs on the
 same input with reversed time indexing instead of two ``flip`` copies; the two directions
-are queued on two CUDA streams.  Float mode trains: in train() mode with gradients enabled,
-forward runs through an autograd function whose backward is qgru_backward.  Quantization-aware
-training (the quantized forward with autograd), ONNX and AIMET hooks are not built.
+are queued on two CUDA streams.  Training: in train() mode with gradients enabled, forward
+runs through an autograd function whose backward is qgru_backward - the fp32 GRU in float mode,
+and with use_quantization (float32 storage) the float-storage quantized forward in training
+mode with its clamp masks as straight-through estimators (QAT).  ONNX and AIMET hooks are not
+built.
 """
 import json
 import math
@@ -67,6 +69,32 @@ class _FloatGRUFunction(torch.autograd.Function):
         # the gradient of slot 0 (h0 passed through as an output) is added to what flows back to h0
         dx, dW, dR, dbw, dbr, dh0 = ctx.handle.backward(W, R, x, dh_all, h, v)
         return None, dx, dW, dR, dbw, dbr, dh0 + dh_all[0]
+
+
+class _QuantGRUFunction(torch.autograd.Function):
+    """One direction of quantization-aware training (the reference's GRUFunction with
+    use_quantization and float32 storage, pytorch/quant_gru.py:826-1050): forward is the
+    float-storage quantized forward in training mode (gate buffer and clamp masks kept),
+    backward differentiates through the dequantized quantized tensors with the masks as
+    straight-through estimators (qgru_backward)."""
+
+    @staticmethod
+    def forward(ctx, handle, qp, x, W, R, bw, br, h0):
+        handle.set_params(qp)
+        handle.set_weights_f32(W, R, bw, br)
+        h, v, x_q, masks = handle.forward_fstorage_train(W, R, bw, br, x, h0)
+        Wd, Rd, _, _ = handle.get_weights_dequantized()
+        xd = handle.dequantize_f32(x_q, "x")
+        ctx.handle, ctx.masks = handle, masks
+        ctx.save_for_backward(xd, Wd, Rd, h, v)
+        return h
+
+    @staticmethod
+    def backward(ctx, dh_all):
+        xd, Wd, Rd, h, v = ctx.saved_tensors
+        dh_all = dh_all.contiguous()
+        dx, dW, dR, dbw, dbr, dh0 = ctx.handle.backward(Wd, Rd, xd, dh_all, h, v, masks=ctx.masks)
+        return None, None, dx, dW, dR, dbw, dbr, dh0 + dh_all[0]
 
 
 class _Direction:
@@ -259,9 +287,10 @@ class QuantGRU(nn.Module):
         hx = hx.to(device=device, dtype=dtype)
         return [hx[d].contiguous() for d in range(self.num_directions)]
 
-    def _ensure_quant_ready(self):
-        if self.training:
-            raise NotImplementedError("training-mode (QAT) outputs are not built; call .eval()")
+    def _ensure_quant_ready(self, training_ok=False):
+        if self.training and not training_ok:
+            raise NotImplementedError("the quantized forward in train() mode needs gradients enabled and "
+                                      "quant_storage_dtype='float32'; call .eval() for inference")
         if self._quant_params_dirty and self.quant_ranges is not None:
             self.finalize_calibration()
         elif not self.is_calibrated():
@@ -297,7 +326,7 @@ class QuantGRU(nn.Module):
         return outs
 
     def _forward_float_train(self, input, hx):
-        """Float mode with autograd: every tensor operation outside the two library calls is a
+        """Float mode and QAT with autograd: every tensor operation outside the two library calls is a
         torch operation, so gradients reach the module's parameters in their PyTorch layout."""
         x = input.transpose(0, 1) if self.batch_first else input
         device = x.device
@@ -318,7 +347,12 @@ class QuantGRU(nn.Module):
                 br = torch.zeros(3 * H, device=device)
             h0 = hx[d].to(torch.float32).contiguous() if hx is not None else torch.zeros(B, H, device=device)
             xd = x.flip(0).contiguous() if d == 1 else x
-            h = _FloatGRUFunction.apply(st.handle, xd, W, R, bw, br, h0)
+            if self.use_quantization:
+                qp = self.quant_params_reverse if d == 1 else self.quant_params
+                h = _QuantGRUFunction.apply(st.handle, qp, xd, W, R, bw, br, h0)
+                st.loaded_key = None        # the handle was reloaded outside the module's cache
+            else:
+                h = _FloatGRUFunction.apply(st.handle, xd, W, R, bw, br, h0)
             outs.append(h[1:].flip(0) if d == 1 else h[1:])
             hns.append(h[T:T + 1])
         output = torch.cat(outs, dim=-1) if self.bidirectional else outs[0]
@@ -331,7 +365,12 @@ class QuantGRU(nn.Module):
     def forward(self, input, hx=None):
         needs_grad = torch.is_grad_enabled() and (input.requires_grad or (hx is not None and hx.requires_grad) or
                                                   any(p.requires_grad for p in self.parameters()))
-        if needs_grad and self.training and not self.calibrating and not self.use_quantization:
+        if needs_grad and self.training and not self.calibrating:
+            if self.use_quantization:
+                if self.quant_storage_dtype != "float32":
+                    raise NotImplementedError("quantization-aware training runs on the float-storage path "
+                                              "(quant_storage_dtype='float32')")
+                self._ensure_quant_ready(training_ok=True)
             if not input.is_cuda:
                 raise ValueError("input must be a CUDA tensor")
             want = (self.num_directions, input.shape[0 if self.batch_first else 1], self.hidden_size)

@@ -245,6 +245,60 @@ def test_quantgru_module_float_storage(oracle, cuda_device, bidir, bf):
     assert np.abs(hn.cpu().numpy() - want_h).max() <= 1.01 * hs
 
 
+def test_quantgru_qat_gradients(oracle, cuda_device):
+    """Quantization-aware training through the module: the training forward returns what the
+    eval-mode float-storage forward returns, and the gradients are those of the masked backward
+    (numpy oracle) applied to the dequantized quantized tensors, gate buffer and clamp masks of
+    that forward, mapped back to PyTorch's parameter layout."""
+    import torch
+    from oracle.backward_np import gru_backward
+    torch.manual_seed(7)
+    T, B, I, H = 6, 5, 16, 24
+    mod = quant_gru.QuantGRU(I, H).cuda()
+    rng = np.random.default_rng(8)
+    mod.eval()
+    mod.calibrating = True
+    for _ in range(2):
+        mod(_t(gen_x(rng, T, B, I), cuda_device))
+    mod.calibrating = False
+    mod.use_quantization = True
+    x = gen_x(rng, T, B, I, sigma=2.5)            # wider than calibrated: some clamps
+    hx = (rng.standard_normal((1, B, H)) * 0.2).astype(np.float32)
+    with torch.no_grad():
+        want_o, want_hn = mod(_t(x, cuda_device), _t(hx, cuda_device))
+    mod.train()
+    xm, hm = _t(x, cuda_device).requires_grad_(), _t(hx, cuda_device).requires_grad_()
+    out, hn = mod(xm, hm)
+    assert torch.equal(out.detach(), want_o) and torch.equal(hn.detach(), want_hn)
+    g_o = torch.randn(T, B, H, device=cuda_device)
+    g_h = torch.randn(1, B, H, device=cuda_device)
+    ((out * g_o).sum() + (hn * g_h).sum()).backward()
+
+    # the same through the library's pieces and the numpy oracle
+    W, R, bw, br = quant_gru.convert_weights_to_haste_format(mod.weight_ih_l0, mod.weight_hh_l0, mod.bias_ih_l0,
+                                                             mod.bias_hh_l0, H, cuda_device)
+    with gru_ops.Handle(I, H, device=0) as hd:
+        hd.set_params(mod.quant_params)
+        hd.set_weights_f32(W, R, bw, br)
+        h, v, x_q, masks = hd.forward_fstorage_train(W, R, bw, br, _t(x, cuda_device), _t(hx[0], cuda_device))
+        Wd, Rd, _, _ = hd.get_weights_dequantized()
+        xd = hd.dequantize_f32(x_q, "x")
+    dh_new = np.zeros((T + 1, B, H), np.float32)
+    dh_new[1:] = g_o.cpu().numpy()
+    dh_new[T] += g_h.cpu().numpy()[0]
+    dx, dW, dR, dbw, dbr, dh0 = gru_backward(Wd.cpu().numpy(), Rd.cpu().numpy(), xd.cpu().numpy(), dh_new,
+                                             h.cpu().numpy(), v.cpu().numpy(),
+                                             masks={n: m.cpu().numpy() for n, m in masks.items()})
+    re = quant_gru.reorder_weights_pytorch_to_haste
+    pairs = [(xm.grad, dx), (hm.grad[0], dh0), (mod.weight_ih_l0.grad, re(torch.from_numpy(dW).t()).numpy()),
+             (mod.weight_hh_l0.grad, re(torch.from_numpy(dR).t()).numpy()),
+             (mod.bias_ih_l0.grad, re(torch.from_numpy(dbw)).numpy()),
+             (mod.bias_hh_l0.grad, re(torch.from_numpy(dbr)).numpy())]
+    for k, (got, want) in enumerate(pairs):
+        assert _rel_err(got.cpu().numpy(), np.asarray(want)) <= 5e-5, k
+    assert any(0 < float(m.float().mean()) < 1 for m in masks.values()), "no clamp was exercised"
+
+
 def test_quantgru_errors(cuda_device):
     import torch
     m = quant_gru.QuantGRU(8, 16, quant_storage_dtype="int32").cuda().eval()
@@ -263,7 +317,7 @@ def test_quantgru_errors(cuda_device):
     m.finalize_calibration()
     with pytest.raises(TypeError):             # float input to the int-in/int-out entry
         m.forward_quantized(torch.randn(3, 2, 8, device=cuda_device))
-    f = quant_gru.QuantGRU(8, 16).cuda()         # training mode (QAT) is not built
+    f = quant_gru.QuantGRU(8, 16, quant_storage_dtype="int32").cuda()   # QAT runs on float32 storage only
     f.calibrating = True
     f(torch.randn(3, 2, 8, device=cuda_device))
     f.calibrating = False
