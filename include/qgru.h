@@ -134,6 +134,11 @@ QGRU_API const char *qgru_version(void);
  * [32768, 65535].  Returns QGRU_ERR_RANGE where the reference throws. */
 QGRU_API int qgru_encode_mshift(float scale, uint16_t *multiplier, int8_t *shift);
 
+/* decode_effective_scale of the reference's binding (pytorch/lib/gru_interface_binding.cc:
+ * 1285-1296): the scale the kernels really apply for a stored scale - multiplier * 2^-shift of
+ * its 16-bit fixed-point encoding, or 2^-shift in POT2 mode.  QGRU_ERR_BAD_ARG for scale <= 0. */
+QGRU_API int qgru_decode_effective_scale(float scale, int use_pot2, float *effective);
+
 /* rshift_round(int64) (include/quantize_ops_helper.h:183-206). */
 QGRU_API int64_t qgru_rshift_round(int64_t x, int n);
 

@@ -67,6 +67,7 @@ _F = C.POINTER(C.c_float)
 SYMBOLS = {
     "qgru_status_string": (C.c_char_p, [C.c_int]),
     "qgru_version": (C.c_char_p, []),
+    "qgru_decode_effective_scale": (C.c_int, [C.c_float, C.c_int, C.POINTER(C.c_float)]),
     "qgru_encode_mshift": (C.c_int, [C.c_float, C.POINTER(C.c_uint16), C.POINTER(C.c_int8)]),
     "qgru_rshift_round": (C.c_int64, [C.c_int64, C.c_int]),
     "qgru_apply_rescale": (C.c_int32, [C.c_int32, C.c_uint16, C.c_int]),

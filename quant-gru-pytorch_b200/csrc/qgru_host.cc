@@ -563,6 +563,15 @@ int qgru_encode_mshift(float scale, uint16_t *multiplier, int8_t *shift) {
     return QGRU_OK;
 }
 
+int qgru_decode_effective_scale(float scale, int use_pot2, float *effective) {
+    if (!effective) return QGRU_ERR_BAD_ARG;
+    if (!(scale > 0.0f)) return QGRU_ERR_BAD_ARG;
+    Rescale r;
+    if (!to_fixed_scale(scale, use_pot2 != 0, &r)) return QGRU_ERR_RANGE;
+    *effective = decode_scale(r);
+    return QGRU_OK;
+}
+
 int64_t qgru_rshift_round(int64_t x, int n) { return rshift_round64(x, n); }
 
 int32_t qgru_apply_rescale(int32_t x, uint16_t multiplier, int shift) {

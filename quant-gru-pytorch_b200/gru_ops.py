@@ -462,14 +462,36 @@ def backward_fp(time_steps, batch_size, input_size, hidden_size, W, R, bw, br, x
     return hd.backward(W, R, x, dh_new, h, v)
 
 
-def backward_quant_float_storage(time_steps, batch_size, input_size, hidden_size, W, R, bw, br, x, dh_new, h, v,
-                                 x_mask=None, h0_mask=None, W_mask=None, R_mask=None, bw_mask=None, br_mask=None,
-                                 weight_ih_linear_mask=None, weight_hh_linear_mask=None, gate_input_mask=None,
-                                 gate_output_mask=None, h_mask=None):
+def decode_effective_scale(scale, use_pot2):
+    """The scale the kernels really apply for a stored scale (binding :1285-1296)."""
+    out = C.c_float()
+    _cabi.check(_cabi.lib().qgru_decode_effective_scale(float(scale), int(bool(use_pot2)), C.byref(out)),
+                "qgru_decode_effective_scale")
+    return float(out.value)
+
+
+def backward_quant_float_storage(time_steps, batch_size, input_size, hidden_size, W_q, R_q, bw_q, br_q, x_q,
+                                 dh_new, h, v, quant_params, x_mask=None, h0_mask=None, W_mask=None, R_mask=None,
+                                 bw_mask=None, br_mask=None, weight_ih_linear_mask=None,
+                                 weight_hh_linear_mask=None, gate_input_mask=None, gate_output_mask=None,
+                                 h_mask=None):
     """Backward of the quantized training forward with its straight-through masks (binding
-    :1022-1160; W..x are the dequantized quantized tensors the forward returned): returns
-    (dx, dW, dR, dbw, dbr, dh)."""
-    hd = _handle_for(x.device.index or 0, input_size, hidden_size, "fp")
+    :763-900): W_q .. x_q are the float-stored quantized tensors the forward returned; they are
+    dequantized here (per-channel weight scales, the scale and zero point of x), then
+    quantGRUBackward's arithmetic runs.  Returns (dx, dW, dR, dbw, dbr, dh)."""
+    c = quant_params.c
+    pot2 = bool(c.use_pot2)
+    dev = x_q.device
+
+    def chan(name):
+        return torch.tensor([decode_effective_scale(s, pot2) for s in quant_params.scales[name]],
+                            dtype=torch.float32, device=dev)
+
+    W = W_q.to(torch.float32) * chan("W")
+    R = R_q.to(torch.float32) * chan("R")
+    xo = c.op[_cabi.OP_INDEX["x"]]
+    x = (x_q.to(torch.float32) - float(xo.zero_point)) * decode_effective_scale(xo.scale, pot2)
+    hd = _handle_for(dev.index or 0, input_size, hidden_size, "fp")
     masks = {"x": x_mask, "h0": h0_mask, "W": W_mask, "R": R_mask, "bw": bw_mask, "br": br_mask,
              "ih_linear": weight_ih_linear_mask, "hh_linear": weight_hh_linear_mask,
              "gate_input": gate_input_mask, "gate_output": gate_output_mask, "h": h_mask}

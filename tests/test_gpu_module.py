@@ -298,6 +298,15 @@ def test_quantgru_qat_gradients(oracle, cuda_device):
         assert _rel_err(got.cpu().numpy(), np.asarray(want)) <= 5e-5, k
     assert any(0 < float(m.float().mean()) < 1 for m in masks.values()), "no clamp was exercised"
 
+    # the reference-named pair of entry points gives the same gradients
+    fwd = gru_ops.forward_quant_float_storage(True, T, B, I, H, W, R, bw, br, _t(x, cuda_device),
+                                              _t(hx[0], cuda_device), mod.quant_params)
+    assert len(fwd) == 18 and torch.equal(fwd[0], h) and torch.equal(fwd[1], v)
+    got = gru_ops.backward_quant_float_storage(T, B, I, H, *fwd[2:7], _t(dh_new, cuda_device), fwd[0], fwd[1],
+                                               mod.quant_params, *fwd[7:])
+    for g, w in zip(got, (dx, dW, dR, dbw, dbr, dh0)):
+        assert _rel_err(g.cpu().numpy().reshape(w.shape), w) <= 5e-5
+
 
 def test_quantgru_errors(cuda_device):
     import torch

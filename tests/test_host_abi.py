@@ -172,3 +172,17 @@ def test_quant_param_export_round_trip(oracle):
     blob = case.params.to_bytes()
     again = params_mod.GRUQuantParams.from_bytes(blob, 12)
     assert bytes(again.c) == bytes(case.params.c)
+
+
+def test_decode_effective_scale_matches_encoding(oracle):
+    """qgru_decode_effective_scale == multiplier * 2^-shift of encodeMShift (POT2: 2^-round(-log2 s))."""
+    import importlib
+    from __graft_entry__ import PKG_NAME
+    gru_ops = importlib.import_module(PKG_NAME + ".gru_ops")
+    rng = np.random.default_rng(0)
+    for s in list(10.0 ** rng.uniform(-6, 1, 200)) + [1.0, 0.5, 0.0078125]:
+        m, sh = oracle.encode_mshift(float(np.float32(s)))
+        assert gru_ops.decode_effective_scale(s, False) == float(np.float32(m) * np.float32(2.0) ** np.float32(-sh))
+        assert gru_ops.decode_effective_scale(s, True) == 2.0 ** -round(-np.log2(float(np.float32(s))))
+    with pytest.raises(ValueError):
+        gru_ops.decode_effective_scale(0.0, False)
