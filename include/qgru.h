@@ -349,6 +349,9 @@ QGRU_API const char *qgru_describe_plan(qgru_handle *h, int T, int B);
 
 /* Restrict or force kernel choices (testing).  Names and values:
  *   "gemm"     auto | simt | tcgen05        W*x kernel
+ *   "gemm_order" auto | stream | w_stationary  tile order of the tcgen05 W*x kernel: W and x slabs
+ *                                           stream per tile (auto), or a CTA keeps one slice of W
+ *                                           in shared memory for the whole launch
  *   "rec"      auto | dp4a | mma | generic  recurrence kernel (generic = int32 storage path)
  *   "exchange" auto | global | cluster      how the CTAs of a batch group exchange h_t
  *   "cell"     auto | fused | generic       gate datapath: tabulated (auto also allows its

@@ -169,6 +169,11 @@ int qgru_set_option(qgru_handle *h, const char *name, const char *value) {
         else return fail(h, QGRU_ERR_BAD_ARG, "r_resident: auto|smem|tmem");
     } else if (n == "tiles_per_cta") {
         h->opt_mt = std::max(0, atoi(value));
+    } else if (n == "gemm_order") {
+        if (v == "auto") h->tc.order = 0;
+        else if (v == "stream") h->tc.order = 1;
+        else if (v == "w_stationary") h->tc.order = 2;
+        else return fail(h, QGRU_ERR_BAD_ARG, "gemm_order: auto|stream|w_stationary");
     } else if (n == "cell") {
         if (v == "auto") h->opt_cell = 0;
         else if (v == "generic") h->opt_cell = 1;

@@ -67,7 +67,12 @@ constexpr size_t GEMM_SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256 + PRE_TAB
 
 // Fast: every scale of the epilogue has the shift-free form and the sums fit 32 bits, so the
 // epilogue is branch-free (Rescale::mq, checked by the caller).
-template <bool XUnsigned, typename IhT, bool Fast>
+// AStat ("A stationary"): a CTA works on one tile of 128 channels for the whole launch and keeps
+// that slice of W (all K slabs) in shared memory; only token tiles stream through the ring.  The
+// CTAs that share a token-tile sequence (one per channel tile) run side by side, so each x tile
+// is read from L2 by all of them at about the same time.  Halves the operand traffic from L2,
+// which is what bounds the kernel at K = 1024.  Grid = m_tiles * groups CTAs.
+template <bool XUnsigned, typename IhT, bool Fast, bool AStat>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
              IhT *__restrict__ ih, long long N, int C, int Kpad, LinearConsts lc, PreScale ps,
@@ -75,12 +80,18 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     extern __shared__ unsigned char smem_raw[];
     unsigned char *tiles = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t *bars = reinterpret_cast<uint64_t *>(tiles + (size_t)STAGES * STAGE_BYTES);
+    // AStat: [Kpad/KB resident W slabs of GM*KB bytes][STAGES x tiles of GN*KB bytes]; else the
+    // ring holds a W slab and an x slab per stage
+    const size_t tile_bytes = AStat ? (size_t)(Kpad / KB) * GM * KB + (size_t)STAGES * GN * KB
+                                    : (size_t)STAGES * STAGE_BYTES;
+    unsigned char *ring = AStat ? tiles + (size_t)(Kpad / KB) * GM * KB : tiles;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tiles + tile_bytes);
     uint64_t *full = bars, *empty = bars + STAGES;
     uint64_t *acc_full = bars + 2 * STAGES, *acc_empty = bars + 2 * STAGES + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+    uint64_t *a_full = bars + 2 * STAGES + 4;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 5);
     int *failed = reinterpret_cast<int *>(tmem_slot + 1);
-    int32_t *pre_tab = reinterpret_cast<int32_t *>(tiles + (size_t)STAGES * STAGE_BYTES + 256);
+    int32_t *pre_tab = reinterpret_cast<int32_t *>(tiles + tile_bytes + 256);
     const bool use_tab = ps.enabled && ps.table != nullptr && 3 * ps.table_n <= PRE_TAB_MAX;
     if (use_tab)
         for (int i = threadIdx.x; i < 3 * ps.table_n; i += blockDim.x) pre_tab[i] = ps.table[i];
@@ -90,6 +101,22 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     const int m_tiles = (C + GM - 1) / GM;
     const long long n_tiles = (N + GN - 1) / GN;
     const long long total = (long long)m_tiles * n_tiles;   // consecutive tiles share the token tile
+    const int groups = AStat ? (int)gridDim.x / m_tiles : 1;
+    // the `local`-th tile of this CTA: false when there is none
+    auto tile_of = [&](long long local, int &m0, long long &n0) -> bool {
+        if (AStat) {
+            const long long n = (long long)(blockIdx.x / m_tiles) + local * groups;
+            if (n >= n_tiles || (int)blockIdx.x >= m_tiles * groups) return false;
+            m0 = (int)(blockIdx.x % m_tiles) * GM;
+            n0 = n * GN;
+        } else {
+            const long long tile = blockIdx.x + local * gridDim.x;
+            if (tile >= total) return false;
+            m0 = (int)(tile % m_tiles) * GM;
+            n0 = (tile / m_tiles) * GN;
+        }
+        return true;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -100,6 +127,7 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             tc::mbar_init(&acc_full[b], 1);
             tc::mbar_init(&acc_empty[b], EPI_WARPS);
         }
+        tc::mbar_init(a_full, 1);
         *failed = 0;
         tc::fence_barrier_init();
         tc::tma_prefetch_desc(&map_w);
@@ -115,17 +143,28 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
         if (lane == 0) {
             long long it = 0;   // k-slab counter across tiles: ring position and phase
             bool ok = true;
-            for (long long tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-                const int m0 = (int)(tile % m_tiles) * GM;
-                const long long n0 = (tile / m_tiles) * GN;
+            int m0;
+            long long n0;
+            if (AStat && tile_of(0, m0, n0)) {
+                // this CTA's slice of W, once
+                tc::mbar_expect_tx(a_full, (uint32_t)(num_kb * GM * KB));
+                for (int kb = 0; kb < num_kb; ++kb)
+                    tc::tma_load_2d(tiles + (size_t)kb * GM * KB, &map_w, a_full, kb * KB, m0);
+            }
+            for (long long local = 0; ok && tile_of(local, m0, n0); ++local) {
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = (int)(it % STAGES);
                     const uint32_t ph = (uint32_t)((it / STAGES) & 1);
                     if (!tc::mbar_wait(&empty[s], ph ^ 1, WAIT_BUDGET)) { ok = false; break; }
-                    unsigned char *a = tiles + (size_t)s * STAGE_BYTES;
-                    tc::mbar_expect_tx(&full[s], STAGE_BYTES);
-                    tc::tma_load_2d(a, &map_w, &full[s], kb * KB, m0);
-                    tc::tma_load_2d(a + GM * KB, &map_x, &full[s], kb * KB, (int)n0);
+                    if (AStat) {
+                        tc::mbar_expect_tx(&full[s], GN * KB);
+                        tc::tma_load_2d(ring + (size_t)s * GN * KB, &map_x, &full[s], kb * KB, (int)n0);
+                    } else {
+                        unsigned char *a = tiles + (size_t)s * STAGE_BYTES;
+                        tc::mbar_expect_tx(&full[s], STAGE_BYTES);
+                        tc::tma_load_2d(a, &map_w, &full[s], kb * KB, m0);
+                        tc::tma_load_2d(a + GM * KB, &map_x, &full[s], kb * KB, (int)n0);
+                    }
                 }
             }
             if (!ok) atomicExch(failed, 1);
@@ -133,9 +172,15 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = tc::idesc_i8(GM, GN, true, !XUnsigned);
-            long long it = 0, local = 0;
+            long long it = 0;
             bool ok = true;
-            for (long long tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++local) {
+            int m0;
+            long long n0;
+            if (AStat && tile_of(0, m0, n0)) {
+                ok = tc::mbar_wait(a_full, 0, WAIT_BUDGET);
+                tc::tc_fence_after_sync();
+            }
+            for (long long local = 0; ok && tile_of(local, m0, n0); ++local) {
                 const int buf = (int)(local & 1);
                 if (!tc::mbar_wait(&acc_empty[buf], (uint32_t)(((local >> 1) & 1) ^ 1), WAIT_BUDGET)) { ok = false; break; }
                 tc::tc_fence_after_sync();
@@ -144,9 +189,11 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                     const uint32_t ph = (uint32_t)((it / STAGES) & 1);
                     if (!tc::mbar_wait(&full[s], ph, WAIT_BUDGET)) { ok = false; break; }
                     tc::tc_fence_after_sync();
-                    const uint32_t a_addr = tc::smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                    const uint32_t a_addr = AStat ? tc::smem_u32(tiles + (size_t)kb * GM * KB)
+                                                  : tc::smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                    const uint32_t b_addr = AStat ? tc::smem_u32(ring + (size_t)s * GN * KB) : a_addr + GM * KB;
                     const uint64_t a_desc = tc::smem_desc_sw128(a_addr);
-                    const uint64_t b_desc = tc::smem_desc_sw128(a_addr + GM * KB);
+                    const uint64_t b_desc = tc::smem_desc_sw128(b_addr);
 #pragma unroll
                     for (int ks = 0; ks < KB / 32; ++ks)
                         tc::mma_i8(tmem_base + buf * GN, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (kb | ks) != 0);
@@ -170,10 +217,13 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             FastLin fl;
             float fs_off, fs_bias, fs_ratio;   // float-storage forward (lc.fs set)
         };
-        auto load_consts = [&](long long tile) {
+        auto load_consts = [&](long long lcl) {
             ChanConsts c;
-            const int m = (int)(tile % m_tiles) * GM + q * 32 + lane;
-            const bool m_ok = tile < total && m < C;
+            int tm0 = 0;
+            long long tn0 = 0;
+            const bool have = tile_of(lcl, tm0, tn0);
+            const int m = tm0 + q * 32 + lane;
+            const bool m_ok = have && m < C;
             c.corr = m_ok ? lc.corr[m] : 0;
             c.rs = m_ok ? lc.rs[m] : Rescale{1, 1, 0, 0, 0, 0, 0, 0};
             c.fl = m_ok ? lc.fl[m] : FastLin{0, 0, 0, 0, 0, 0};
@@ -183,14 +233,14 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             c.fs_ratio = fs_ok ? lc.fs[2 * lc.fs_C + m] : 0.f;
             return c;
         };
-        ChanConsts cur = load_consts(blockIdx.x);
-        for (long long tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++local) {
-            const int m0 = (int)(tile % m_tiles) * GM;
-            const long long n0 = (tile / m_tiles) * GN;
+        ChanConsts cur = load_consts(0);
+        int m0;
+        long long n0;
+        for (; ok && tile_of(local, m0, n0); ++local) {
             const int buf = (int)(local & 1);
             const int m = m0 + q * 32 + lane;
             const bool m_ok = m < C;
-            const ChanConsts nxt = load_consts(tile + gridDim.x);
+            const ChanConsts nxt = AStat ? cur : load_consts(local + 1);
             const int64_t corr = cur.corr;
             const Rescale rs = cur.rs;
             const FastLin fl = cur.fl;
@@ -272,13 +322,36 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     if (warp == 1) tc::tmem_dealloc(tmem_base, 2 * GN);
 }
 
+constexpr size_t SMEM_LIMIT = 227 * 1024;   // opt-in shared memory per CTA on sm_100
+
+size_t astat_smem(int Kpad) {
+    return (size_t)(Kpad / KB) * GM * KB + (size_t)STAGES * GN * KB + 1024 + 256 + PRE_TAB_MAX * 4;
+}
+
 template <bool XU, typename IhT, bool Fast>
 cudaError_t launch_f(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long long N, int C, int Kpad,
-                     LinearConsts lc, PreScale ps, int *abort_flag, int sms, cudaStream_t st) {
-    auto kern = k_gemm_wx_tc<XU, IhT, Fast>;
+                     LinearConsts lc, PreScale ps, int *abort_flag, int sms, int order, cudaStream_t st) {
+    const int m_tiles = (C + GM - 1) / GM;
+    const long long n_tiles = (N + GN - 1) / GN;
+    // W-stationary order: only on request (option gemm_order), where the slice of W fits beside
+    // the ring and every CTA can get a channel tile.  It halves the operand traffic from L2 and
+    // measured the same time as the streaming order at K = 1024 (0.293 ms for 64000 x 3072 x 1024):
+    // the kernel is bound by its epilogue there too, not by operand delivery.
+    const bool fits = astat_smem(Kpad) <= SMEM_LIMIT && m_tiles <= sms;
+    const bool astat = fits && order == 2;
+    if (astat) {
+        auto kern = k_gemm_wx_tc<XU, IhT, Fast, true>;
+        const size_t smem = astat_smem(Kpad);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        const long long groups = std::max<long long>(1, std::min<long long>(sms / m_tiles, n_tiles));
+        kern<<<(unsigned)(m_tiles * groups), GEMM_THREADS, smem, st>>>(mw, mx, (IhT *)ih, N, C, Kpad, lc, ps, abort_flag);
+        return cudaGetLastError();
+    }
+    auto kern = k_gemm_wx_tc<XU, IhT, Fast, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
     if (e != cudaSuccess) return e;
-    const long long tiles = (long long)((C + GM - 1) / GM) * ((N + GN - 1) / GN);
+    const long long tiles = (long long)m_tiles * n_tiles;
     const unsigned grid = (unsigned)std::min<long long>(tiles, sms);   // persistent: one CTA per SM
     kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(mw, mx, (IhT *)ih, N, C, Kpad, lc, ps, abort_flag);
     return cudaGetLastError();
@@ -286,9 +359,9 @@ cudaError_t launch_f(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, lon
 
 template <bool XU, typename IhT>
 cudaError_t launch(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long long N, int C, int Kpad,
-                   LinearConsts lc, PreScale ps, bool fast, int *abort_flag, int sms, cudaStream_t st) {
-    return fast ? launch_f<XU, IhT, true>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, st)
-                : launch_f<XU, IhT, false>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, st);
+                   LinearConsts lc, PreScale ps, bool fast, int *abort_flag, int sms, int order, cudaStream_t st) {
+    return fast ? launch_f<XU, IhT, true>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, order, st)
+                : launch_f<XU, IhT, false>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, order, st);
 }
 
 }  // namespace
@@ -323,14 +396,14 @@ int tc_gemm_launch(TcGemmState &s, const uint8_t *x8, long long x_rows_alloc, co
     fast = fast && (!ps.enabled || tab || (ps.to[0].mq != 0 && ps.to[1].mq != 0 && ps.to[2].mq != 0));
     cudaError_t e;
     if (ih_bytes == 1)
-        e = x_unsigned ? launch<true, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, stream)
-                       : launch<false, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, stream);
+        e = x_unsigned ? launch<true, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, s.order, stream)
+                       : launch<false, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, s.order, stream);
     else if (ih_bytes == 2)
-        e = x_unsigned ? launch<true, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, stream)
-                       : launch<false, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, stream);
+        e = x_unsigned ? launch<true, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, s.order, stream)
+                       : launch<false, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, s.order, stream);
     else
-        e = x_unsigned ? launch<true, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, stream)
-                       : launch<false, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, stream);
+        e = x_unsigned ? launch<true, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, s.order, stream)
+                       : launch<false, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, s.order, stream);
     if (e != cudaSuccess) {
         if (err) *err = std::string("tcgen05 GEMM launch: ") + cudaGetErrorString(e);
         return QGRU_ERR_CUDA;

@@ -15,6 +15,7 @@ struct TcGemmState {
     const void *x8 = nullptr, *w8 = nullptr;
     long long x_rows = 0, w_rows = 0;
     int Kpad = 0;
+    int order = 0;   // tile order: 0 auto, 1 token-tile-major (W and x slabs stream), 2 W-stationary
     alignas(64) unsigned char map_w[128];
     alignas(64) unsigned char map_x[128];
 };

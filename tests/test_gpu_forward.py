@@ -279,3 +279,17 @@ def test_training_buffer(oracle, cuda_device, name):
         h2, v2 = hd.forward_i32_train(_t(flipped, cuda_device), _t(case.h0_q, cuda_device), reverse=True)
         assert np.array_equal(v2.cpu().numpy()[::-1], want_v)
         assert np.array_equal(h2.cpu().numpy()[:case.T][::-1], want_h[1:])
+
+
+@pytest.mark.parametrize("order", ["stream", "w_stationary"])
+@pytest.mark.parametrize("shape,name", [((3, 50, 20, 40), "default"), ((5, 70, 300, 200), "cfg2"),
+                                        ((2, 300, 1024, 520), "default"), ((4, 33, 640, 136), "cfg3")])
+def test_input_gemm_tile_orders(oracle, cuda_device, shape, name, order):
+    """Both tile orders of the tcgen05 input GEMM (W and x slabs streaming per tile; the slice
+    of W resident in shared memory for the whole launch), K from 128 to 1024 padded bytes, more
+    and fewer token tiles than CTAs per channel tile: bit-exact."""
+    T, B, I, H = shape
+    case = make_case(seed=51, T=T, B=B, I=I, H=H, checker=oracle, config=config_named(name))
+    got, plan, _ = _run(case, cuda_device, opts=(("gemm", "tcgen05"), ("gemm_order", order)))
+    assert "gemm=tcgen05_i8" in plan
+    assert np.array_equal(got, _want(oracle, case))
