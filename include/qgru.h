@@ -260,6 +260,16 @@ QGRU_API int qgru_forward_fstorage_train(qgru_handle *h, int T, int B, const flo
                                          float *h_out, float *v_out, float *x_q_out,
                                          const qgru_train_masks *masks, unsigned flags, void *stream);
 
+/* quantGRUForwardInt with is_training = true (src/gru_interface.cc:610-725): the integer forward
+ * with float interface that also returns what the masked backward needs.  Same arguments as
+ * qgru_forward_fstorage_train, except x_q_out [T,B,I] int32 (may be NULL); v_out holds the
+ * dequantized gate buffer of the integer path (piecewise-linear gates).  Runs on the
+ * step-by-step int32 kernels. */
+QGRU_API int qgru_forward_f32_train(qgru_handle *h, int T, int B, const float *W, const float *R,
+                                    const float *bw, const float *br, const float *x, const float *h0,
+                                    float *h_out, float *v_out, int32_t *x_q_out,
+                                    const qgru_train_masks *masks, unsigned flags, void *stream);
+
 /* dequantizeGRUWeights (include/gru_interface.h:141): the quantized weights the handle holds,
  * times their per-channel scales, as device fp32 (W [I,3H], R [H,3H], bw, br [3H]; NULL = skip).
  * These are the weights the masked backward differentiates through. */

@@ -340,8 +340,9 @@ class ReferenceGpu:
         self._check(rc, "ref_gpu_forward_fstorage")
         return h, xq, wq
 
-    def forward_fstorage_train(self, T, B, I, H, W, R, bw, br, x, h0, params, sc):
-        """quantGRUForwardFP, training mode: (h, v dequantized, dict of the eleven masks)."""
+    def forward_fstorage_train(self, T, B, I, H, W, R, bw, br, x, h0, params, sc, int_storage=False):
+        """quantGRUForwardFP (or, with int_storage, quantGRUForwardInt) in training mode:
+        (h, v dequantized, dict of the eleven masks)."""
         from oracle.backward_np import MASK_NAMES
         h = np.zeros((T + 1, B, H), np.float32)
         v = np.zeros((T, B, 4 * H), np.float32)
@@ -350,7 +351,7 @@ class ReferenceGpu:
                   "gate_output": (T * B, 3 * H), "h": (T * B, H)}
         ms = {n: np.zeros(shapes[n], np.uint8) for n in MASK_NAMES}
         mptr = (C.c_void_p * 11)(*[ms[n].ctypes.data for n in MASK_NAMES])
-        rc = self._fn("forward_fstorage_train")(T, B, I, H, _f(W), _f(R), _f(bw), _f(br),
+        rc = self._fn("forward_int_train" if int_storage else "forward_fstorage_train")(T, B, I, H, _f(W), _f(R), _f(bw), _f(br),
                                                 _f(np.ascontiguousarray(x, np.float32)),
                                                 _f(np.ascontiguousarray(h0, np.float32)), C.byref(params),
                                                 *[_f(a) for a in sc], _f(h), _f(v), mptr)

@@ -758,6 +758,37 @@ int ref_gpu_forward_fstorage_train(int T, int B, int I, int H, const float *W, c
     });
 }
 
+// quantGRUForwardInt with is_training = true (src/gru_interface.cc:610): h, v (dequantized) and
+// the eleven masks; same conventions as ref_gpu_forward_fstorage_train.
+int ref_gpu_forward_int_train(int T, int B, int I, int H, const float *W, const float *R, const float *bw,
+                              const float *br, const float *x, const float *h0, const qgru_params *p,
+                              const float *sW, const float *sR, const float *sbw, const float *sbr,
+                              float *h, float *v, uint8_t *const *masks) {
+    return guarded([&] {
+        if (!h0 || !masks) throw std::invalid_argument("ref_gpu_forward_int_train: h0 and masks are required");
+        GRUQuantParams q = fromPod(*p, sW, sR, sbw, sbr);
+        const size_t C3 = size_t(H) * 3, TB = size_t(T) * B;
+        DevBuf<float> dW(W, size_t(I) * C3), dR(R, size_t(H) * C3), dbw(bw, C3), dbr(br, C3),
+            dx(x, TB * I), dh0(h0, size_t(B) * H), dh((TB + B) * H), dv(TB * H * 4);
+        const size_t msz[11] = {TB * I, size_t(B) * H, size_t(I) * C3, size_t(H) * C3, C3, C3,
+                                TB * C3, TB * C3, TB * C3, TB * C3, TB * H};
+        std::unique_ptr<DevBuf<uint8_t>> dm[11];
+        for (int k = 0; k < 11; ++k) {
+            if (!masks[k]) throw std::invalid_argument("ref_gpu_forward_int_train: all masks are required");
+            dm[k].reset(new DevBuf<uint8_t>(msz[k]));
+            dm[k]->zero();
+        }
+        dh.zero();
+        quantGRUForwardInt(true, T, B, I, H, dW.p, dR.p, dbw.p, dbr.p, dx.p, dh0.p, q, blasHandle(), dh.p, dv.p,
+                           dm[0]->p, dm[1]->p, dm[2]->p, dm[3]->p, dm[4]->p, dm[5]->p, dm[6]->p, dm[7]->p,
+                           dm[8]->p, dm[9]->p, dm[10]->p, nullptr, nullptr, nullptr, nullptr, nullptr);
+        cudaOk(cudaDeviceSynchronize(), "quantGRUForwardInt");
+        dh.toHost(h);
+        dv.toHost(v);
+        for (int k = 0; k < 11; ++k) dm[k]->toHost(masks[k]);
+    });
+}
+
 // forwardWithCalibrationGPU (src/gru_interface.cc:1283), MinMax: folds one batch into `r`.
 int ref_gpu_calibrate_minmax(int T, int B, int I, int H, const float *W, const float *R,
                              const float *bw, const float *br, const float *x, qgru_ranges *r,

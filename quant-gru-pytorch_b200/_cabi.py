@@ -82,6 +82,7 @@ SYMBOLS = {
     "qgru_set_weights_i32": (C.c_int, [_P, _P, _P, _P, _P, _P]),
     "qgru_get_weights_i32": (C.c_int, [_P, _P, _P, _P, _P, _P]),
     "qgru_forward_i32": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, C.c_uint, _P]),
+    "qgru_forward_f32_train": (C.c_int, [_P, C.c_int, C.c_int] + [_P] * 10 + [C.c_uint, _P]),
     "qgru_forward_fstorage_train": (C.c_int, [_P, C.c_int, C.c_int] + [_P] * 10 + [C.c_uint, _P]),
     "qgru_get_weights_dequantized": (C.c_int, [_P] * 6),
     "qgru_dequantize_f32": (C.c_int, [_P, C.c_int, _P, _P, C.c_longlong, _P]),

@@ -1159,3 +1159,4 @@ extern "C" int qgru_forward_i32_static(qgru_handle *h, int T, int B, const int32
 }
 
 #include "qgru_fstorage.cuh"
+#include "qgru_train.cuh"

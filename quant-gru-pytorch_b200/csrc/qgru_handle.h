@@ -68,6 +68,7 @@ struct qgru_handle {
     // workspace
     DevBuf x8, ih, h8, x32, ih32, hh32, hq32, stage_in, stage_h0, stage_out;
     DevBuf f_wx, f_h, f_v, f_acc, f_acc2;  // float mode / calibration (f_acc2: R*h of one step)
+    DevBuf vq32;                           // integer training forward: gate buffer before dequantization
     DevBuf bwd_dp, bwd_dq;                 // backward pass: gradients of W*x + bw and R*h + br, [T*B][3H] each
     DevBuf fs_ch;                          // float-storage forward: 4 x 3H per-channel scale ratios
     bool fs_ready = false;                 // fs_ch matches the current parameters

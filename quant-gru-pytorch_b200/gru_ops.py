@@ -227,10 +227,12 @@ class Handle:
 
     MASK_NAMES = ("x", "h0", "W", "R", "bw", "br", "ih_linear", "hh_linear", "gate_input", "gate_output", "h")
 
-    def forward_fstorage_train(self, W, R, bw, br, x, h0=None, reverse=False):
+    def forward_fstorage_train(self, W, R, bw, br, x, h0=None, reverse=False, int_storage=False):
         """Training mode of the float-storage forward: (h [(T+1),B,H], v [T,B,4H] dequantized,
         x_q [T,B,I] as floats, masks: dict of the eleven uint8 clamp masks, 1 = not clamped).
-        W..br are the float master weights the handle was loaded with (set_weights_f32)."""
+        W..br are the float master weights the handle was loaded with (set_weights_f32).
+        int_storage: the integer forward in training mode instead (quantGRUForwardInt:
+        piecewise-linear gates, x_q as int32)."""
         x = _check_tensor(x, "x", torch.float32)
         T, B = int(x.shape[0]), int(x.shape[1])
         I, H = self.input_size, self.hidden_size
@@ -240,15 +242,16 @@ class Handle:
         dev = self._tdev
         h = torch.empty((T + 1, B, H), dtype=torch.float32, device=dev)
         v = torch.empty((T, B, 4 * H), dtype=torch.float32, device=dev)
-        x_q = torch.empty((T, B, I), dtype=torch.float32, device=dev)
+        x_q = torch.empty((T, B, I), dtype=torch.int32 if int_storage else torch.float32, device=dev)
         shapes = {"x": (T * B, I), "h0": (B, H), "W": (I, 3 * H), "R": (H, 3 * H), "bw": (3 * H,), "br": (3 * H,),
                   "ih_linear": (T * B, 3 * H), "hh_linear": (T * B, 3 * H), "gate_input": (T * B, 3 * H),
                   "gate_output": (T * B, 3 * H), "h": (T * B, H)}
         masks = {n: torch.ones(shapes[n], dtype=torch.uint8, device=dev) for n in self.MASK_NAMES}
         mk = _cabi.BwdMasks(*[masks[n].data_ptr() for n in self.MASK_NAMES])
-        self._ck(self._lib.qgru_forward_fstorage_train(
-            self._h, T, B, *[_ptr(t) for t in ws], _ptr(x), _ptr(h0), _ptr(h), _ptr(v), _ptr(x_q), C.byref(mk),
-            _cabi.FLAG_REVERSE if reverse else 0, _stream(dev)), "qgru_forward_fstorage_train")
+        fn = self._lib.qgru_forward_f32_train if int_storage else self._lib.qgru_forward_fstorage_train
+        self._ck(fn(self._h, T, B, *[_ptr(t) for t in ws], _ptr(x), _ptr(h0), _ptr(h), _ptr(v), _ptr(x_q),
+                    C.byref(mk), _cabi.FLAG_REVERSE if reverse else 0, _stream(dev)),
+                 "qgru_forward_f32_train" if int_storage else "qgru_forward_fstorage_train")
         self.synchronize()
         return h, v, x_q, masks
 
@@ -415,21 +418,24 @@ def calculate_gru_quantitative_parameters_from_histograms(hist_collectors, bitwi
 
 def forward_quant_int_storage(is_training, time_steps, batch_size, input_size, hidden_size,
                               W, R, bw, br, x, h0, quant_params, slot=0, reverse=False):
-    """Integer forward with float interface (binding :436-571, inference mode).
+    """Integer forward with float interface (binding :436-571).
 
-    Returns (h [(T+1),B,H] f32, v (empty), W_q, R_q, bw_q, br_q, x_q) like the reference;
-    training-mode masks are not produced (is_training must be False)."""
-    if is_training:
-        raise NotImplementedError("training-mode outputs (v, clamp masks) are outside the inference hot path")
+    Returns the reference's 18-tuple (h [(T+1),B,H] f32, v, W_q, R_q, bw_q, br_q, x_q (int32), then
+    the eleven clamp masks in the order of Handle.MASK_NAMES); in inference mode v and the
+    masks are empty tensors."""
     x = _check_tensor(x, "x", torch.float32, (time_steps, batch_size, input_size))
     hd = _handle_for(x.device.index or 0, input_size, hidden_size, slot)
     hd.set_params(quant_params)
     hd.set_weights_f32(W, R, bw, br)
     h0 = h0 if (h0 is not None and h0.numel() > 0) else None
-    h, x_q = hd.forward_f32(x, h0, reverse=reverse, want_x_q=True)
     W_q, R_q, bw_q, br_q = hd.get_weights_i32()
+    if is_training:
+        h, v, x_q, m = hd.forward_fstorage_train(W, R, bw, br, x, h0, reverse=reverse, int_storage=True)
+        return (h, v, W_q, R_q, bw_q, br_q, x_q) + tuple(m[n] for n in Handle.MASK_NAMES)
+    h, x_q = hd.forward_f32(x, h0, reverse=reverse, want_x_q=True)
+    e = torch.empty(0, dtype=torch.uint8, device=x.device)
     v = torch.empty(0, dtype=torch.float32, device=x.device)
-    return h, v, W_q, R_q, bw_q, br_q, x_q
+    return (h, v, W_q, R_q, bw_q, br_q, x_q) + (e,) * 11
 
 
 def forward_quant_float_storage(is_training, time_steps, batch_size, input_size, hidden_size,

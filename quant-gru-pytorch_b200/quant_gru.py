@@ -15,8 +15,9 @@ re-quantizes weights and regenerates LUTs on every call); the reverse direction 
 same input with reversed time indexing instead of two ``flip`` copies; the two directions
 are queued on two CUDA streams.  Training: in train() mode with gradients enabled, forward
 runs through an autograd function whose backward is qgru_backward - the fp32 GRU in float mode,
-and with use_quantization (float32 storage) the float-storage quantized forward in training
-mode with its clamp masks as straight-through estimators (QAT).  ONNX and AIMET hooks are not
+and with use_quantization the quantized forward in training mode (float-storage path, or the
+integer path with quant_storage_dtype="int32") with its clamp masks as straight-through
+estimators (QAT).  ONNX and AIMET hooks are not
 built.
 """
 import json
@@ -79,12 +80,14 @@ class _QuantGRUFunction(torch.autograd.Function):
     straight-through estimators (qgru_backward)."""
 
     @staticmethod
-    def forward(ctx, handle, qp, x, W, R, bw, br, h0):
+    def forward(ctx, handle, qp, int_storage, x, W, R, bw, br, h0):
         handle.set_params(qp)
         handle.set_weights_f32(W, R, bw, br)
-        h, v, x_q, masks = handle.forward_fstorage_train(W, R, bw, br, x, h0)
+        # float32 storage: float requantization, real sigmoid / tanh; int32 storage: the integer
+        # path (piecewise-linear gates) in training mode
+        h, v, x_q, masks = handle.forward_fstorage_train(W, R, bw, br, x, h0, int_storage=int_storage)
         Wd, Rd, _, _ = handle.get_weights_dequantized()
-        xd = handle.dequantize_f32(x_q, "x")
+        xd = handle.dequantize_f32(x_q.to(torch.float32), "x")
         ctx.handle, ctx.masks = handle, masks
         ctx.save_for_backward(xd, Wd, Rd, h, v)
         return h
@@ -94,7 +97,7 @@ class _QuantGRUFunction(torch.autograd.Function):
         xd, Wd, Rd, h, v = ctx.saved_tensors
         dh_all = dh_all.contiguous()
         dx, dW, dR, dbw, dbr, dh0 = ctx.handle.backward(Wd, Rd, xd, dh_all, h, v, masks=ctx.masks)
-        return None, None, dx, dW, dR, dbw, dbr, dh0 + dh_all[0]
+        return None, None, None, dx, dW, dR, dbw, dbr, dh0 + dh_all[0]
 
 
 class _Direction:
@@ -289,8 +292,8 @@ class QuantGRU(nn.Module):
 
     def _ensure_quant_ready(self, training_ok=False):
         if self.training and not training_ok:
-            raise NotImplementedError("the quantized forward in train() mode needs gradients enabled and "
-                                      "quant_storage_dtype='float32'; call .eval() for inference")
+            raise NotImplementedError("the quantized forward in train() mode needs gradients enabled "
+                                      "(quantization-aware training); call .eval() for inference")
         if self._quant_params_dirty and self.quant_ranges is not None:
             self.finalize_calibration()
         elif not self.is_calibrated():
@@ -349,7 +352,7 @@ class QuantGRU(nn.Module):
             xd = x.flip(0).contiguous() if d == 1 else x
             if self.use_quantization:
                 qp = self.quant_params_reverse if d == 1 else self.quant_params
-                h = _QuantGRUFunction.apply(st.handle, qp, xd, W, R, bw, br, h0)
+                h = _QuantGRUFunction.apply(st.handle, qp, self.quant_storage_dtype == "int32", xd, W, R, bw, br, h0)
                 st.loaded_key = None        # the handle was reloaded outside the module's cache
             else:
                 h = _FloatGRUFunction.apply(st.handle, xd, W, R, bw, br, h0)
@@ -367,9 +370,6 @@ class QuantGRU(nn.Module):
                                                   any(p.requires_grad for p in self.parameters()))
         if needs_grad and self.training and not self.calibrating:
             if self.use_quantization:
-                if self.quant_storage_dtype != "float32":
-                    raise NotImplementedError("quantization-aware training runs on the float-storage path "
-                                              "(quant_storage_dtype='float32')")
                 self._ensure_quant_ready(training_ok=True)
             if not input.is_cuda:
                 raise ValueError("input must be a CUDA tensor")

@@ -245,7 +245,8 @@ def test_quantgru_module_float_storage(oracle, cuda_device, bidir, bf):
     assert np.abs(hn.cpu().numpy() - want_h).max() <= 1.01 * hs
 
 
-def test_quantgru_qat_gradients(oracle, cuda_device):
+@pytest.mark.parametrize("storage", ["float32", "int32"])
+def test_quantgru_qat_gradients(oracle, cuda_device, storage):
     """Quantization-aware training through the module: the training forward returns what the
     eval-mode float-storage forward returns, and the gradients are those of the masked backward
     (numpy oracle) applied to the dequantized quantized tensors, gate buffer and clamp masks of
@@ -254,7 +255,8 @@ def test_quantgru_qat_gradients(oracle, cuda_device):
     from oracle.backward_np import gru_backward
     torch.manual_seed(7)
     T, B, I, H = 6, 5, 16, 24
-    mod = quant_gru.QuantGRU(I, H).cuda()
+    mod = quant_gru.QuantGRU(I, H, quant_storage_dtype=storage).cuda()
+    ints = storage == "int32"
     rng = np.random.default_rng(8)
     mod.eval()
     mod.calibrating = True
@@ -280,9 +282,10 @@ def test_quantgru_qat_gradients(oracle, cuda_device):
     with gru_ops.Handle(I, H, device=0) as hd:
         hd.set_params(mod.quant_params)
         hd.set_weights_f32(W, R, bw, br)
-        h, v, x_q, masks = hd.forward_fstorage_train(W, R, bw, br, _t(x, cuda_device), _t(hx[0], cuda_device))
+        h, v, x_q, masks = hd.forward_fstorage_train(W, R, bw, br, _t(x, cuda_device), _t(hx[0], cuda_device),
+                                                     int_storage=ints)
         Wd, Rd, _, _ = hd.get_weights_dequantized()
-        xd = hd.dequantize_f32(x_q, "x")
+        xd = hd.dequantize_f32(x_q.to(torch.float32), "x")
     dh_new = np.zeros((T + 1, B, H), np.float32)
     dh_new[1:] = g_o.cpu().numpy()
     dh_new[T] += g_h.cpu().numpy()[0]
@@ -298,6 +301,8 @@ def test_quantgru_qat_gradients(oracle, cuda_device):
         assert _rel_err(got.cpu().numpy(), np.asarray(want)) <= 5e-5, k
     assert any(0 < float(m.float().mean()) < 1 for m in masks.values()), "no clamp was exercised"
 
+    if ints:
+        return
     # the reference-named pair of entry points gives the same gradients
     fwd = gru_ops.forward_quant_float_storage(True, T, B, I, H, W, R, bw, br, _t(x, cuda_device),
                                               _t(hx[0], cuda_device), mod.quant_params)
@@ -332,5 +337,5 @@ def test_quantgru_errors(cuda_device):
     f.calibrating = False
     f.use_quantization = True
     f.train()
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(NotImplementedError), torch.no_grad():   # train() mode without gradients
         f(torch.randn(3, 2, 8, device=cuda_device))

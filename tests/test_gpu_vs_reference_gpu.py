@@ -280,3 +280,28 @@ def test_float_storage_training_forward_equals_reference_gpu(reference, refgpu, 
         assert np.array_equal(m.cpu().numpy(), want_m[n]), n
     if sigma > 1.0:
         assert sum(0 < want_m[n].mean() < 1 for n in want_m) >= 3, "too few clamps were exercised"
+
+
+@pytest.mark.parametrize("cfg_name,sigma", [("default", 1.0), ("cfg2", 3.0), ("pot2_asym", 3.0)])
+def test_integer_training_forward_float_interface_equals_reference_gpu(reference, refgpu, cuda_device, cfg_name, sigma):
+    """quantGRUForwardInt(is_training): dequantized h and v and the eleven clamp masks of the
+    integer path, bit for bit."""
+    T, B, I, H = 6, 5, 20, 72
+    case = make_case(seed=44, T=T, B=B, I=I, H=H, checker=reference, config=config_named(cfg_name), with_h0=True)
+    x = (case.x * np.float32(sigma)).astype(np.float32)
+    h0 = (case.h0 * np.float32(sigma)).astype(np.float32)
+    sc = case.params.scale_list()
+    want_h, want_v, want_m = refgpu.forward_fstorage_train(T, B, I, H, case.W, case.R, case.bw, case.br, x, h0,
+                                                           case.params.c, sc, int_storage=True)
+    with gru_ops.Handle(I, H, device=0) as hd:
+        hd.set_params(case.params)
+        dw = [_t(a, cuda_device) for a in (case.W, case.R, case.bw, case.br)]
+        hd.set_weights_f32(*dw)
+        h, v, x_q, masks = hd.forward_fstorage_train(*dw, _t(x, cuda_device), _t(h0, cuda_device), int_storage=True)
+        h_inf = hd.forward_f32(_t(x, cuda_device), _t(h0, cuda_device))
+    assert np.array_equal(h.cpu().numpy(), want_h)
+    assert np.array_equal(h_inf.cpu().numpy(), want_h)
+    assert np.array_equal(v.cpu().numpy(), want_v)
+    assert np.array_equal(x_q.cpu().numpy(), reference.quantize(x, case.params.c, OP["x"]))
+    for n, m in masks.items():
+        assert np.array_equal(m.cpu().numpy(), want_m[n]), n
