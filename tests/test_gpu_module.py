@@ -313,6 +313,26 @@ def test_quantgru_qat_gradients(oracle, cuda_device, storage):
         assert _rel_err(g.cpu().numpy().reshape(w.shape), w) <= 5e-5
 
 
+def test_reference_named_quantized_forwards_return_the_reference_tuple(oracle, cuda_device):
+    """forward_quant_int_storage / forward_quant_float_storage: 18 results like the binding's;
+    inference and training mode give the same h; training fills v and the masks."""
+    import torch
+    T, B, I, H = 5, 4, 12, 24
+    case = make_case(seed=61, T=T, B=B, I=I, H=H, checker=oracle, config=config_named("cfg2"), with_h0=True)
+    dev = [_t(a, cuda_device) for a in (case.W, case.R, case.bw, case.br, case.x, case.h0)]
+    for fn, xq_dtype in ((gru_ops.forward_quant_int_storage, torch.int32),
+                         (gru_ops.forward_quant_float_storage, torch.float32)):
+        inf = fn(False, T, B, I, H, *dev, case.params)
+        trn = fn(True, T, B, I, H, *dev, case.params)
+        assert len(inf) == len(trn) == 18
+        assert torch.equal(inf[0], trn[0]) and inf[1].numel() == 0 and trn[1].shape == (T, B, 4 * H)
+        assert inf[6].dtype == trn[6].dtype == xq_dtype and torch.equal(inf[6], trn[6])
+        assert all(m.numel() == 0 for m in inf[7:]) and all(m.dtype == torch.uint8 and m.numel() > 0 for m in trn[7:])
+    want = oracle.forward_f32(T, B, I, H, case.wq, case.x, case.h0, case.params.c, case.params.scale_list())
+    got = gru_ops.forward_quant_int_storage(False, T, B, I, H, *dev, case.params)[0]
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+
+
 def test_quantgru_errors(cuda_device):
     import torch
     m = quant_gru.QuantGRU(8, 16, quant_storage_dtype="int32").cuda().eval()
