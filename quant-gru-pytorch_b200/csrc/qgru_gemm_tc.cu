@@ -58,6 +58,7 @@ constexpr int GM = 128;      // channels per tile
 constexpr int GN = 128;      // tokens per tile
 constexpr int KB = 128;      // K bytes per stage
 constexpr int STAGES = 4;
+constexpr int NACC = 4;        // accumulator buffers in tensor memory (NACC * GN = 512 columns: all of it)
 constexpr int EPI_WARPS = 16;                      // four warps per TMEM lane quadrant
 constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int STAGE_BYTES = (GM + GN) * KB;
@@ -87,9 +88,9 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     unsigned char *ring = AStat ? tiles + (size_t)(Kpad / KB) * GM * KB : tiles;
     uint64_t *bars = reinterpret_cast<uint64_t *>(tiles + tile_bytes);
     uint64_t *full = bars, *empty = bars + STAGES;
-    uint64_t *acc_full = bars + 2 * STAGES, *acc_empty = bars + 2 * STAGES + 2;
-    uint64_t *a_full = bars + 2 * STAGES + 4;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 5);
+    uint64_t *acc_full = bars + 2 * STAGES, *acc_empty = bars + 2 * STAGES + NACC;
+    uint64_t *a_full = bars + 2 * STAGES + 2 * NACC;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 2 * NACC + 1);
     int *failed = reinterpret_cast<int *>(tmem_slot + 1);
     int32_t *pre_tab = reinterpret_cast<int32_t *>(tiles + tile_bytes + 256);
     const bool use_tab = ps.enabled && ps.table != nullptr && 3 * ps.table_n <= PRE_TAB_MAX;
@@ -123,7 +124,7 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             tc::mbar_init(&full[s], 1);
             tc::mbar_init(&empty[s], 1);
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < NACC; ++b) {
             tc::mbar_init(&acc_full[b], 1);
             tc::mbar_init(&acc_empty[b], EPI_WARPS);
         }
@@ -133,7 +134,7 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
         tc::tma_prefetch_desc(&map_w);
         tc::tma_prefetch_desc(&map_x);
     }
-    if (warp == 1) tc::tmem_alloc(tmem_slot, 2 * GN);   // two accumulators: MMA of tile i+1 overlaps epilogue of tile i
+    if (warp == 1) tc::tmem_alloc(tmem_slot, NACC * GN);   // several accumulators: the MMAs run ahead of the epilogue
     tc::tc_fence_before_sync();
     __syncthreads();
     tc::tc_fence_after_sync();
@@ -181,8 +182,8 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                 tc::tc_fence_after_sync();
             }
             for (long long local = 0; ok && tile_of(local, m0, n0); ++local) {
-                const int buf = (int)(local & 1);
-                if (!tc::mbar_wait(&acc_empty[buf], (uint32_t)(((local >> 1) & 1) ^ 1), WAIT_BUDGET)) { ok = false; break; }
+                const int buf = (int)(local % NACC);
+                if (!tc::mbar_wait(&acc_empty[buf], (uint32_t)(((local / NACC) & 1) ^ 1), WAIT_BUDGET)) { ok = false; break; }
                 tc::tc_fence_after_sync();
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = (int)(it % STAGES);
@@ -237,7 +238,7 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
         int m0;
         long long n0;
         for (; ok && tile_of(local, m0, n0); ++local) {
-            const int buf = (int)(local & 1);
+            const int buf = (int)(local % NACC);
             const int m = m0 + q * 32 + lane;
             const bool m_ok = m < C;
             const ChanConsts nxt = AStat ? cur : load_consts(local + 1);
@@ -249,7 +250,7 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             const Rescale pre_rs = ps.to[gate];
             const int32_t pre_zp = ps.zp_in[gate];
             const int32_t c32 = (int32_t)corr;
-            ok = tc::mbar_wait(&acc_full[buf], (uint32_t)((local >> 1) & 1), WAIT_BUDGET);
+            ok = tc::mbar_wait(&acc_full[buf], (uint32_t)((local / NACC) & 1), WAIT_BUDGET);
             if (!ok) break;
             tc::tc_fence_after_sync();
             IhT *out = ih + m;
@@ -319,7 +320,7 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     tc::tc_fence_before_sync();
     __syncthreads();
     if (threadIdx.x == 0 && *failed) atomicOr(abort_flag, 2);
-    if (warp == 1) tc::tmem_dealloc(tmem_base, 2 * GN);
+    if (warp == 1) tc::tmem_dealloc(tmem_base, NACC * GN);
 }
 
 constexpr size_t SMEM_LIMIT = 227 * 1024;   // opt-in shared memory per CTA on sm_100
