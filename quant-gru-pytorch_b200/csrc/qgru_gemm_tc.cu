@@ -7,8 +7,8 @@
 //
 // Persistent kernel, one CTA per SM looping over tiles of 128 output channels (TMEM lanes) x 128
 // tokens (TMEM columns); K streamed in 128-byte slabs through a 4-stage shared-memory ring that
-// runs ahead across tiles; two accumulators in tensor memory so that the MMAs of tile i+1
-// overlap the epilogue of tile i.  Warp roles: warp 0 issues the TMA loads, warp 1
+// runs ahead across tiles; four accumulators in tensor memory (all 512 columns) so that the MMAs
+// run up to three tiles ahead of the epilogue.  Warp roles: warp 0 issues the TMA loads, warp 1
 // owns tensor memory and issues the MMAs, warps 2-17 run the epilogue (one TMEM lane = one
 // output channel per thread, so each thread keeps its channel's constants in registers and a
 // warp's stores cover 32 consecutive channels of a token).
