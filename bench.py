@@ -14,13 +14,18 @@ same work per GPU at every N.  Ranks never exchange data on the timed path.
 
 Rank 0 prints one JSON line.  `value` is measured with inputs resident in HBM, `e2e` through
 the same calls with pinned host buffers (host->device copy of x and device->host copy of
-every output inside the timed region).  `--impl reference` times the reference's own CPU
-integer path (oracle/_ref, else the C port) on the box's host cores instead.
+every output inside the timed region).  After the timed regions every rank compares rows of
+its GPU result, every timestep, bit for bit with the reference's CPU integer path (`check`);
+with N > 1 the per-rank outputs are all-gathered once over NCCL and compared with the local
+shards (`gather`), and the throughput configuration (batch 4096 split evenly over the N
+GPUs, fixed total work) is timed as the `strong` block.  `--impl reference` times the
+reference's own CPU integer path (oracle/_ref, else the C port) on the box's host cores.
 """
 import argparse
 import importlib
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -32,17 +37,14 @@ sys.path.insert(0, ROOT)
 
 import numpy as np  # noqa: E402
 
-WORKLOADS = {
-    # name: (I, H, B per unit, T, bidirectional, config name, x distribution, calib batches)
-    "cfg1": (64, 128, 32, 50, False, "sym8_tensor", "normal", 8),
-    "cfg2": (256, 512, 256, 200, True, "cfg2", "normal", 16),
-    "cfg3": (128, 256, 4096, 100, False, "cfg3", "outliers", 16),
-    "cfg4": (1024, 1024, 64, 1000, False, "sym8_tensor", "normal", 4),
-    "cfg5": (80, 256, 1, 16000, False, "cfg5", "ar1", 4),
-}
-# calibration method of each workload configuration: (method, percentile)
-CALIBRATION = {"cfg1": ("minmax", 0.0), "cfg2": ("minmax", 0.0), "cfg3": ("percentile", 99.9),
-               "cfg4": ("sqnr", 0.0), "cfg5": ("minmax", 0.0)}
+from __graft_entry__ import PKG_NAME, load_package  # noqa: E402
+
+load_package()
+workloads = importlib.import_module(PKG_NAME + ".workloads")
+WORKLOADS, CALIBRATION = workloads.WORKLOADS, workloads.CALIBRATION
+
+METRIC = "int-quant GRU fwd tokens/s (batch x seq)"
+STRONG_WORKLOAD = "cfg3"      # batch 4096 sharded evenly over the GPUs: fixed total work
 
 
 def parse():
@@ -53,10 +55,16 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-check", action="store_true", help="skip the bit-exact comparison with the CPU path")
+    ap.add_argument("--check-rows", type=int, default=0,
+                    help="batch rows per direction compared with the CPU path (0: as many as ~10 s of CPU buy)")
+    ap.add_argument("--no-strong", action="store_true", help="skip the fixed-total-work block at N > 1")
     ap.add_argument("--calib-batches", type=int, default=0,
                     help="override the number of calibration batches (profiling runs only)")
     ap.add_argument("--rows", type=int, default=0,
                     help="override the batch rows per GPU-unit (small profiling cases only)")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="library option set on every handle (see qgru_set_option)")
     return ap.parse_args()
 
 
@@ -112,29 +120,135 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def build_problem(wl, seed_base):
-    """Seeded weights for each direction, in the reference's haste layout."""
-    from tests.cases import gen_weights
-    I, H = wl[0], wl[1]
-    dirs = 2 if wl[4] else 1
-    return [gen_weights(np.random.default_rng(seed_base + d), I, H) for d in range(dirs)]
-
-
 def bytes_per_token(I, H, ih_bytes):
     # fp32 x read + W*x+bw written once and read once + fp32 h written
     return 4 * I + 2 * 3 * H * ih_bytes + 4 * H
 
 
+def profiled_traffic_per_token(kernel, workload):
+    """DRAM bytes per token of `kernel` on `workload` from the committed ncu summary
+    profiles/<kernel>_<workload>.md (its line `dram_bytes_per_token: <number>`); None where no
+    capture of that pair exists."""
+    try:
+        text = open(os.path.join(ROOT, "profiles", f"{kernel}_{workload}.md")).read()
+    except OSError:
+        return None
+    m = re.search(r"dram_bytes_per_token:\s*([0-9.]+)", text)
+    return float(m.group(1)) if m else None
+
+
 # ----------------------------------------------------------------------------- our arm
+class Job:
+    """One rank's share of a workload: calibrated handles, resident input, output buffers."""
+
+    def __init__(self, args, name, torch, dev, local, rank, world, global_batch, n_calib=0, options=()):
+        gru_ops = importlib.import_module(PKG_NAME + ".gru_ops")
+        sharding = importlib.import_module(PKG_NAME + ".sharding")
+        self.torch, self.dev, self.name, self.rank, self.world = torch, dev, name, rank, world
+        I, H, _, T, bidir = WORKLOADS[name][:5]
+        self.I, self.H, self.T, self.bidir = I, H, T, bidir
+        self.global_batch = global_batch
+        self.shards = sharding.plan_shards(world, global_batch, bidir)
+        self.me = self.shards[rank]
+        self.rows = self.me.rows
+        self.n_calib = n_calib or WORKLOADS[name][7]
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        weights = workloads.workload_weights(name)
+        self.handles = []   # (handle, reverse, stream, quant params)
+        for d in self.me.directions:
+            hd = gru_ops.Handle(I, H, device=local)
+            if len(self.me.directions) > 1:
+                hd.set_option("sm_limit", sms // 2)
+            for kv in options:
+                hd.set_option(*kv.split("=", 1))
+            wdev = [torch.from_numpy(a).to(dev) for a in weights[d]]
+            qp = workloads.calibrate_workload(hd, name, d, wdev, lambda a: torch.from_numpy(a).to(dev),
+                                              n_calib=self.n_calib)
+            hd.set_params(qp)
+            hd.set_weights_f32(*wdev)
+            self.handles.append((hd, d == 1, torch.cuda.Stream(device=dev), qp))
+        self.x_np = workloads.workload_input(name, rank, self.rows)
+        self.x_host = torch.from_numpy(self.x_np).pin_memory()
+        self.x_dev = self.x_host.to(dev)
+        self.outs = [torch.empty((T + 1, self.rows, H), dtype=torch.float32, device=dev) for _ in self.handles]
+
+    def step(self, x=None, into=None):
+        torch, dev = self.torch, self.dev
+        cur = torch.cuda.current_stream(dev)
+        x = self.x_dev if x is None else x
+        for (hd, rev, st, _), o in zip(self.handles, into or self.outs):
+            st.wait_stream(cur)
+            with torch.cuda.stream(st):
+                hd.forward_f32(x, None, reverse=rev, out=o, sync=False)
+        for _, _, st, _ in self.handles:
+            cur.wait_stream(st)
+
+    def launch_count(self):
+        return sum(h[0].launch_count() for h in self.handles)
+
+    def synchronize(self):
+        for h in self.handles:
+            h[0].synchronize()
+
+    def plan(self):
+        return self.handles[0][0].describe_plan()
+
+    def tokens_per_step(self):
+        return self.global_batch * self.T
+
+    def close(self):
+        for h in self.handles:
+            h[0].close()
+
+    # -- bit-exact comparison of this rank's result with the CPU integer path
+    def check(self, want_rows, threads):
+        from oracle import check as ocheck
+        chk = ocheck.checker()
+        self.step()
+        self.synchronize()
+        self.torch.cuda.synchronize(self.dev)
+        rows = ocheck.spread_rows(self.rows, want_rows)
+        res = {"rows": 0, "steps": self.T, "mismatches": 0, "kind": chk.kind, "directions": len(self.handles)}
+        for (hd, rev, _, qp), o in zip(self.handles, self.outs):
+            r = ocheck.check_forward_rows(chk, hd, qp, self.x_np, o, rows, reverse=rev, threads=threads)
+            res["rows"] += r["rows"]
+            res["mismatches"] += r["mismatches"]
+        return res
+
+    def auto_check_rows(self, threads, budget_s=10.0):
+        # the reference's CPU path runs about 0.5 G multiply-adds per second and thread
+        macs_row = self.T * 3 * self.H * (self.I + self.H) * len(self.handles)
+        n = int(budget_s * 0.5e9 * max(1, threads) / max(1, macs_row))
+        return max(min(self.rows, 48), min(self.rows, n))
+
+    # -- NCCL all-gather of every rank's output, compared with the local shard
+    def gather_check(self):
+        import torch.distributed as dist
+        torch = self.torch
+        sharding = importlib.import_module(PKG_NAME + ".sharding")
+        self.step()
+        self.synchronize()
+        outs = []
+        for (_, rev, _, _), o in zip(self.handles, self.outs):
+            outs.append(o[:-1] if rev else o[1:])   # per-timestep outputs (the reverse result keeps its start in slot T)
+        hns = [o[0:1] if rev else o[-1:] for (_, rev, _, _), o in zip(self.handles, self.outs)]
+        local_out = torch.cat(outs, dim=-1) if len(outs) > 1 else outs[0].contiguous()
+        local_hn = torch.cat(hns, dim=0) if len(hns) > 1 else hns[0].contiguous()
+        full, full_hn = sharding.gather_outputs(local_out, local_hn, self.shards, self.rank, self.H,
+                                                self.global_batch, self.T, self.bidir)
+        ok = True
+        for k, d in enumerate(self.me.directions):
+            ok = ok and torch.equal(full[:, self.me.b0:self.me.b1, d * self.H:(d + 1) * self.H],
+                                    local_out[:, :, k * self.H:(k + 1) * self.H])
+            ok = ok and torch.equal(full_hn[d, self.me.b0:self.me.b1], local_hn[k])
+        flag = torch.tensor([0 if ok else 1], device=self.dev)
+        dist.all_reduce(flag)
+        return int(flag.item()) == 0, list(full.shape)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    from __graft_entry__ import PKG_NAME, load_package
-    load_package()
-    gru_ops = importlib.import_module(PKG_NAME + ".gru_ops")
-    params_mod = importlib.import_module(PKG_NAME + ".params")
-    sharding = importlib.import_module(PKG_NAME + ".sharding")
-    from tests.cases import config_named, gen_x
 
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -146,64 +260,12 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    I, H, B_unit, T, bidir, cfg_name, xdist, n_calib = WORKLOADS[args.workload]
-    if args.calib_batches > 0:
-        n_calib = args.calib_batches
+    I, H, B_unit, T, bidir, cfg_name, xdist, _ = WORKLOADS[args.workload]
     if args.rows > 0:
         B_unit = args.rows
-    B_global = B_unit * world
-    shards = sharding.plan_shards(world, B_global, bidir)
-    me = shards[rank]
-    cfg = config_named(cfg_name)
-    weights = build_problem(WORKLOADS[args.workload], 1000 + int(args.workload[3:]) * 10)
-    sms = torch.cuda.get_device_properties(dev).multi_processor_count
-
-    # --- calibration over n_calib seeded batches of the unit shape, per direction: MinMax ranges
-    # or 2048-bin histograms (Percentile / SQNR), as the workload's configuration says
+    job = Job(args, args.workload, torch, dev, local, rank, world, B_unit * world, args.calib_batches, args.option)
+    rows = job.rows
     method, pct = CALIBRATION[args.workload]
-    handles = []
-    for d in me.directions:
-        hd = gru_ops.Handle(I, H, device=local)
-        if len(me.directions) > 1:
-            hd.set_option("sm_limit", sms // 2)
-        for kv in filter(None, os.environ.get("QGRU_OPTS", "").split(",")):   # tuning experiments
-            hd.set_option(*kv.split("=", 1))
-        W, R, bw, br = [torch.from_numpy(a).to(dev) for a in weights[d]]
-        ranges = params_mod.Ranges(H)
-        hist = params_mod.Histograms(H, device=local) if method != "minmax" else None
-        for k in range(n_calib):
-            xc = torch.from_numpy(gen_x(np.random.default_rng(100 * int(args.workload[3:]) + k), T,
-                                        B_unit, I, xdist)).to(dev)
-            xc = xc.flip(0).contiguous() if d == 1 else xc
-            if hist is None:
-                hd.calibrate_minmax(W, R, bw, br, xc, ranges)
-            else:
-                hd.calibrate_hist(W, R, bw, br, xc, hist, cfg.granularity_list())
-        if hist is None:
-            qp = params_mod.GRUQuantParams.from_ranges(ranges, cfg)
-        else:
-            qp = params_mod.GRUQuantParams.from_histograms(hist, cfg, method == "percentile", pct)
-            hist.close()
-        hd.set_params(qp)
-        hd.set_weights_f32(W, R, bw, br)
-        handles.append((hd, d == 1, torch.cuda.Stream(device=dev)))
-
-    # --- this rank's input shard, resident on the device and pinned on the host
-    rows = me.rows
-    x_host = torch.from_numpy(gen_x(np.random.default_rng(int(args.workload[3:]) + 7919 * rank), T, rows, I,
-                                    xdist)).pin_memory()
-    x_dev = x_host.to(dev)
-    outs = [torch.empty((T + 1, rows, H), dtype=torch.float32, device=dev) for _ in handles]
-    outs_host = [torch.empty((T + 1, rows, H), dtype=torch.float32).pin_memory() for _ in handles]
-
-    def step(x, into=None):
-        cur = torch.cuda.current_stream(dev)
-        for (hd, rev, st), o in zip(handles, into or outs):
-            st.wait_stream(cur)
-            with torch.cuda.stream(st):
-                hd.forward_f32(x, None, reverse=rev, out=o, sync=False)
-        for hd, rev, st in handles:
-            cur.wait_stream(st)
 
     # End to end: every step copies its input from pinned host memory and its outputs back to
     # pinned host memory.  The three phases run on three streams over two sets of device buffers,
@@ -211,10 +273,11 @@ def run_ours(args):
     # is full duplex); each step's copies are still inside the timed region.
     # Two copy-out streams: one device-to-host copy alone reaches about 41 GB/s on this box, two
     # concurrent ones about 57 GB/s.
+    outs_host = [torch.empty((T + 1, rows, H), dtype=torch.float32).pin_memory() for _ in job.handles]
     copy_in = torch.cuda.Stream(device=dev)
     copy_outs = [torch.cuda.Stream(device=dev) for _ in range(2)]
-    x_stage = [torch.empty_like(x_dev) for _ in range(2)]
-    outs2 = [outs, [torch.empty_like(o) for o in outs]]
+    x_stage = [torch.empty_like(job.x_dev) for _ in range(2)]
+    outs2 = [job.outs, [torch.empty_like(o) for o in job.outs]]
     ev_in = [torch.cuda.Event() for _ in range(2)]
     ev_done = [torch.cuda.Event() for _ in range(2)]
     ev_out = [[torch.cuda.Event() for _ in range(2)] for _ in range(2)]
@@ -240,13 +303,13 @@ def run_ours(args):
         if i >= 2:
             copy_in.wait_event(ev_done[k])             # step i-2 has consumed this input buffer
         with torch.cuda.stream(copy_in):
-            x_stage[k].copy_(x_host, non_blocking=True)
+            x_stage[k].copy_(job.x_host, non_blocking=True)
             ev_in[k].record(copy_in)
         cur.wait_event(ev_in[k])
         if i >= 2:
             for e in ev_out[k]:
                 cur.wait_event(e)                      # step i-2's outputs have left these buffers
-        step(x_stage[k], outs2[k])
+        job.step(x_stage[k], outs2[k])
         ev_done[k].record(cur)
         for n, (o, oh) in enumerate(out_pieces(k)):
             st = copy_outs[n % 2]
@@ -284,25 +347,65 @@ def run_ours(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    launches0 = sum(hd.launch_count() for hd, _, _ in handles)
+    launches0 = job.launch_count()
     with ClockSampler(local) as clk:
-        ms_total = timed(lambda: step(x_dev), args.steps, args.warmup)
-    launches = sum(hd.launch_count() for hd, _, _ in handles) - launches0
-    for hd, _, _ in handles:
-        hd.synchronize()
+        ms_total = timed(job.step, args.steps, args.warmup)
+    launches = job.launch_count() - launches0
+    job.synchronize()
     # per-kernel time of the timed steps, from events the library records on its launch stream
     nwin = min(args.steps, 64)
-    wins = [hd.timing_window(nwin) for hd, _, _ in handles]
-    ms_e2e = timed(step_e2e, max(3, args.steps // 2), 2, drain=e2e_drain)
+    wins = [h[0].timing_window(nwin) for h in job.handles]
     e2e_steps = max(3, args.steps // 2)
-    for hd, _, _ in handles:
-        hd.synchronize()
+    ms_e2e = timed(step_e2e, e2e_steps, 2, drain=e2e_drain)
+    job.synchronize()
+    del x_stage, outs2, outs_host
 
-    tokens_step = B_global * T
+    tokens_step = job.tokens_per_step()
     value = tokens_step * args.steps / (ms_total * 1e-3)
     e2e = tokens_step * e2e_steps / (ms_e2e * 1e-3)
-    plan = handles[0][0].describe_plan()
-    ih_bytes = 2 if "ih_bytes=2" in plan else 1
+    plan = job.plan()
+    ih_bytes = 2 if "ih_bytes=2" in plan else (4 if "ih_bytes=4" in plan else 1)
+
+    # ---- outside the timed regions: bit-exact check of this rank's rows, gather check, strong block
+    cores = os.cpu_count() or 1
+    threads = max(1, cores // world)
+    check = None
+    if not args.no_check:
+        res = job.check(args.check_rows or job.auto_check_rows(threads), threads)
+        tot = torch.tensor([res["rows"], res["mismatches"]], device=dev, dtype=torch.int64)
+        if world > 1:
+            dist.all_reduce(tot)
+        check = {"status": "ok" if int(tot[1]) == 0 else "MISMATCH", "bit_exact": int(tot[1]) == 0,
+                 "checked_rows": int(tot[0]), "timesteps": T, "ranks": world, "against": res["kind"],
+                 "mismatching_values": int(tot[1])}
+    gather = None
+    if world > 1:
+        ok, shape = job.gather_check()
+        gather = {"status": "ok" if ok else "MISMATCH", "backend": "nccl", "gathered_shape": shape}
+    job_rows, job_handles = job.rows, len(job.handles)
+    job.close()
+    del job
+    torch.cuda.empty_cache()
+
+    strong = None
+    if world > 1 and not args.no_strong and args.workload == "cfg2":
+        sI, sH, sB, sT = WORKLOADS[STRONG_WORKLOAD][:4]
+        sj = Job(args, STRONG_WORKLOAD, torch, dev, local, rank, world, sB, 0, args.option)
+        ms_s = timed(sj.step, args.steps, args.warmup)
+        sj.synchronize()
+        sw = sj.handles[0][0].timing_window(min(args.steps, 64))
+        strong = {"workload": f"{STRONG_WORKLOAD}: unidirectional GRU I={sI} H={sH} global_batch={sB} T={sT}, "
+                              f"batch split evenly over {world} GPUs ({sj.rows} rows each)",
+                  "scaling": "strong", "value": sB * sT * args.steps / (ms_s * 1e-3), "unit": "tokens/s",
+                  "ms_per_step": ms_s / args.steps, "n_gpus": world,
+                  "us_per_timestep": sw["recurrence_ms"] / max(1, sw["calls"]) * 1e3 / sT, "plan": sj.plan()}
+        if not args.no_check:
+            res = sj.check(args.check_rows or sj.auto_check_rows(threads, 5.0), threads)
+            tot = torch.tensor([res["rows"], res["mismatches"]], device=dev, dtype=torch.int64)
+            dist.all_reduce(tot)
+            strong["check"] = {"status": "ok" if int(tot[1]) == 0 else "MISMATCH", "checked_rows": int(tot[0]),
+                               "timesteps": sT, "against": res["kind"]}
+        sj.close()
 
     result = None
     if rank == 0:
@@ -321,56 +424,63 @@ def run_ours(args):
         gemm_ms = w["input_gemm_ms"] / max(1, w["calls"])
         cluster = "exchange=cluster_dsmem" in plan
         kernel = ("k_recurrence_cluster" if cluster else "k_recurrence_mma") if "rec=tcgen05" in plan \
-            else ("k_recurrence_dp4a" if "path=int8" in plan else "k_linear_generic+k_gates_generic")
-        rec_bytes = T * rows * (3 * H * ih_bytes + H * (4 if cluster else 5))
-        # DRAM traffic of one launch from the ncu capture of this kernel on this workload
-        # (dram__bytes_read.sum + dram__bytes_write.sum = 234.8 MB for 51200 tokens of cfg2),
-        # scaled by the tokens of a launch; other kernels / workloads were not captured
-        traffic = None
-        if args.workload == "cfg2" and kernel == "k_recurrence_cluster" and ih_bytes == 2:
-            traffic = 234.8e6 * (T * rows) / 51200.0
+            else ("k_recurrence_gemv" if "rec=gemv" in plan else
+                  ("k_recurrence_dp4a" if "path=int8" in plan else "k_linear_generic+k_gates_generic"))
+        rec_bytes = T * job_rows * (3 * H * ih_bytes + H * (4 if cluster or "rec=gemv" in plan else 5))
+        per_token = profiled_traffic_per_token(kernel, args.workload)
+        traffic = per_token * T * job_rows if per_token else None
         achieved = rec_bytes / (rec_ms * 1e-3) / 1e9 if rec_ms > 0 else 0.0
         result = {
-            "metric": "int-quant GRU fwd tokens/s (batch x seq)", "value": value, "unit": "tokens/s",
+            "metric": METRIC, "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8 (int32 accumulate, 64-bit requantize)",
             "data": "synthetic",
             "config": {"workload": f"{args.workload}: {'bi' if bidir else 'uni'}directional GRU I={I} H={H} "
-                                   f"global_batch={B_global} T={T}, bit widths '{cfg_name}', "
-                                   f"{method}{' %g' % pct if method == 'percentile' else ''} calibration x{n_calib}",
-                       "per_gpu": f"directions={list(me.directions)} rows={rows}",
+                                   f"global_batch={B_unit * world} T={T}, bit widths '{cfg_name}', "
+                                   f"{method}{' %g' % pct if method == 'percentile' else ''} calibration "
+                                   f"x{args.calib_batches or WORKLOADS[args.workload][7]}",
+                       "per_gpu": f"directions={list(range(2)) if job_handles > 1 else 'one'} rows={job_rows}",
                        "l2": "inputs larger than L2: x, W*x+bw and the fp32 outputs of one step "
-                             f"total {(rows * T * bytes_per_token(I, H, ih_bytes) * len(handles)) / 1e6:.0f} MB > 126 MB",
+                             f"total {(job_rows * T * bytes_per_token(I, H, ih_bytes) * job_handles) / 1e6:.0f} MB > 126 MB"
+                             if job_rows * T * bytes_per_token(I, H, ih_bytes) * job_handles > 126e6 else
+                             "working set below L2 (126 MB): this workload is latency-bound by its T dependent steps, "
+                             "not by memory; timed as is",
                        "plan": plan},
             "roofline": {"bound": "hbm", "kernel": kernel + " (one direction)", "achieved": achieved,
                          "peak": hbm, "unit": "GB/s", "frac": achieved / hbm, "peak_kind": peak_kind,
                          "traffic": traffic, "us_per_timestep": rec_ms * 1e3 / T,
                          "input_gemm_ms": gemm_ms, "recurrence_ms": rec_ms,
-                         "whole_forward_frac": (tokens_step / world * bytes_per_token(I, H, ih_bytes) * len(handles) /
+                         "whole_forward_frac": (tokens_step / world * bytes_per_token(I, H, ih_bytes) * job_handles /
                                                 ((ms_total / args.steps) * 1e-3) / 1e9) / hbm},
             "e2e": {"value": e2e, "unit": "tokens/s",
-                    "h2d_bytes_per_step": int(x_host.numel() * 4),
-                    "d2h_bytes_per_step": int(sum(o.numel() * 4 for o in outs_host))},
+                    "h2d_bytes_per_step": int(T * job_rows * I * 4),
+                    "d2h_bytes_per_step": int((T + 1) * job_rows * H * 4 * job_handles)},
             "gpu_launches": int(launches),
             "clocks": clk.summary(),
         }
+        if check is not None:
+            result["check"] = check
+        if gather is not None:
+            result["gather"] = gather
+        if strong is not None:
+            result["strong"] = strong
         if world == 1 and not args.no_cpu_baseline:
             result["cpu_baseline"] = cpu_baseline(args.workload, budget_s=15.0)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-    for hd, _, _ in handles:
-        hd.close()
     if result is not None:
         print(json.dumps(result))
+    if check is not None and not check["bit_exact"]:
+        raise SystemExit("bench: the GPU result differs from the CPU integer path")
 
 
 # ------------------------------------------------------------------ CPU baseline / reference arm
 def cpu_problem(workload):
     """Quantized operands of one small batch for the CPU integer path (both directions)."""
     from oracle.binding import Oracle, reference_or_none
-    from tests.cases import config_named, make_case
+    from oracle.cases import make_case
     I, H, B_unit, T, bidir, cfg_name, xdist, _ = WORKLOADS[workload]
     ref = reference_or_none()
     chk = ref or Oracle()
@@ -379,9 +489,9 @@ def cpu_problem(workload):
     cases = []
     for d in range(2 if bidir else 1):
         # calibration on a short, narrow batch: it fixes the values, not the running time
-        cal = make_case(1000 + d, min(T, 20), 4, I, H, chk, config_named(cfg_name), dist=xdist,
+        cal = make_case(1000 + d, min(T, 20), 4, I, H, chk, workloads.config_named(cfg_name), dist=xdist,
                         calib_batches=1, oracle=Oracle())
-        x = np.random.default_rng(77 + d).standard_normal((T, rows, I)).astype(np.float32)
+        x = workloads.gen_x(np.random.default_rng(77 + d), T, rows, I, xdist)
         x_q = chk.quantize(x, cal.params.c, 0)
         cases.append((cal, x_q))
     return chk, cases, rows, T, I, H, cores
@@ -421,7 +531,7 @@ def run_reference(args):
     value = rows * T * args.steps / dt
     wl = WORKLOADS[args.workload]
     print(json.dumps({
-        "impl": "reference", "metric": "int-quant GRU fwd tokens/s (batch x seq)", "value": value,
+        "impl": "reference", "metric": METRIC, "value": value,
         "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int32 containers, int64 accumulate (CPU)", "data": "synthetic",

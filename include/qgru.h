@@ -357,6 +357,17 @@ QGRU_API uint64_t qgru_launch_count(const qgru_handle *h);
  * ("gemm=tcgen05_i8 rec=mma ..."), for benchmarks and tests. */
 QGRU_API const char *qgru_describe_plan(qgru_handle *h, int T, int B);
 
+/* No counterpart in the reference (it has no tensor-core code).  Measurement aid: runs `mmas`
+ * back-to-back tcgen05.mma kind::i8 instructions of shape M x N x 32 (M 128 with N a multiple of
+ * 16, or M 64 with N a multiple of 8; N <= 256) on `ctas` CTAs, one per SM, operands resident in
+ * shared memory (or A in tensor memory), rotating over `accumulators` accumulators; no loads, no
+ * epilogue.  Returns the SM clock cycles one MMA takes in that chain (slowest CTA) and the
+ * aggregate rate in 1e12 int8 operations per second (2*M*N*32 per MMA, CUDA-event time).  The
+ * large-N figure is the measured peak of the int8 tensor pipe that benchmark lines quote the
+ * W*x GEMM against; the small-N figures are the cost model of the recurrence kernels. */
+QGRU_API int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int accumulators, int mmas,
+                               int ctas, double *cycles_per_mma, double *tera_ops);
+
 /* Restrict or force kernel choices (testing).  Names and values:
  *   "gemm"     auto | simt | tcgen05        W*x kernel
  *   "gemm_order" auto | stream | w_stationary  tile order of the tcgen05 W*x kernel: W and x slabs

@@ -15,7 +15,8 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
-REF_ROOT = os.environ.get("QGRU_REF_ROOT", "/root/reference")
+# the reference project's tree: QGRU_REF_ROOT, else a checkout named "reference" beside this repository
+REF_ROOT = os.environ.get("QGRU_REF_ROOT") or os.path.join(os.path.dirname(_ROOT), "reference")
 
 
 def _pkg():

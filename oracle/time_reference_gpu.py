@@ -20,9 +20,9 @@ sys.path.insert(0, ROOT)
 def main(names):
     fstorage = "--fstorage" in names
     names = [n for n in names if not n.startswith("--")] or ["cfg2"]
-    from bench import WORKLOADS
     from oracle.binding import Oracle, Reference, ReferenceGpu
-    from tests.cases import config_named, make_case
+    from oracle.cases import config_named, make_case, _workloads
+    WORKLOADS = _workloads.WORKLOADS
     ref = Reference()
     gpu = ReferenceGpu(ref)
     if gpu.device_count() < 1:
@@ -31,7 +31,7 @@ def main(names):
         I, H, B, T, bidir, cfg_name, xdist, _ = WORKLOADS[name]
         cal = make_case(1000, min(T, 20), 4, I, H, ref, config_named(cfg_name), dist=xdist, calib_batches=1,
                         oracle=Oracle())
-        x = np.random.default_rng(77).standard_normal((T, B, I)).astype(np.float32)
+        x = _workloads.gen_x(np.random.default_rng(77), T, B, I, xdist)
         if fstorage:
             time_fstorage(name, gpu, cal, x, T, B, I, H)
             continue

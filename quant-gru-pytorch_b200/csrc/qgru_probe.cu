@@ -1,0 +1,122 @@
+// qgru_probe.cu - measurement aids of the library: the issue rate of tcgen05.mma kind::i8.
+//
+// qgru_probe_mma_i8 runs, on a given number of CTAs (one per SM), a chain of back-to-back
+// tcgen05.mma.cta_group::1.kind::i8 instructions of one shape (M x N x 32) on operands that
+// already sit in shared / tensor memory: no loads, no epilogue.  What it returns is the rate the
+// tensor pipe itself sustains for that shape - the denominator the W*x GEMM's "tensor pipe
+// busy" figure is quoted against (large N), and the cost model of the recurrence kernels, whose
+// MMAs have few batch columns (small N).  The reference has no tensor-core code and no
+// counterpart of this file.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <vector>
+
+#include "qgru.h"
+#include "qgru_tc.cuh"
+
+namespace qgru {
+namespace {
+
+constexpr long long PROBE_WAIT = 2000000000ll;
+
+// One control thread issues `mmas` MMAs; accumulator i % n_acc, K-step i % 4 of a 128-byte slab.
+// A: 128 rows x 128 bytes (shared memory, 128-byte swizzle, or 32 columns of tensor memory);
+// B: N rows x 128 bytes in shared memory.  The operands are zeros: an integer pipe does not
+// care.  cycles[cta] = clock ticks from the first issue to the completion of the last MMA.
+__global__ void __launch_bounds__(128, 1)
+k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, long long *cycles, int *timeouts) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = tc::smem_u32(smem_raw);
+    unsigned char *base = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+    unsigned char *a_tile = base;                    // 16 KB
+    unsigned char *b_tile = base + 16384;            // up to 32 KB
+    uint64_t *bar = reinterpret_cast<uint64_t *>(base + 16384 + 32768);
+    uint32_t *slot = reinterpret_cast<uint32_t *>(bar + 1);
+    for (int i = threadIdx.x; i < (16384 + 32768) / 4; i += blockDim.x) reinterpret_cast<uint32_t *>(base)[i] = 0u;
+    if (threadIdx.x == 0) {
+        tc::mbar_init(bar, 1);
+        tc::fence_barrier_init();
+    }
+    if (threadIdx.x < 32) tc::tmem_alloc(slot, 512);
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem = *slot;
+    if (threadIdx.x == 0) {
+        const uint32_t idesc = tc::idesc_i8(M, N, true, true);
+        const uint64_t adesc = tc::smem_desc_sw128(tc::smem_u32(a_tile));
+        const uint64_t bdesc = tc::smem_desc_sw128(tc::smem_u32(b_tile));
+        const uint32_t a_col = tmem + (uint32_t)(n_acc * N);   // 32 columns after the accumulators
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        const long long t0 = clock64();
+        for (int i = 0; i < mmas; ++i) {
+            const uint32_t d = tmem + (uint32_t)((i % n_acc) * N);
+            const uint32_t ks = (uint32_t)(i & 3);
+            if (a_in_tmem) tc::mma_i8_ts(d, a_col + ks * 8, bdesc + 2 * ks, idesc, 1u);
+            else tc::mma_i8(d, adesc + 2 * ks, bdesc + 2 * ks, idesc, 1u);
+        }
+        tc::mma_commit(bar);
+        const bool ok = tc::mbar_wait(bar, 0, PROBE_WAIT);
+        const long long t1 = clock64();
+        cycles[blockIdx.x] = t1 - t0;
+        if (!ok) atomicAdd(timeouts, 1);
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x < 32) tc::tmem_dealloc(tmem, 512);
+}
+
+}  // namespace
+}  // namespace qgru
+
+extern "C" int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int accumulators, int mmas, int ctas,
+                                 double *cycles_per_mma, double *tera_ops) {
+    using namespace qgru;
+    if (!cycles_per_mma || !tera_ops) return QGRU_ERR_BAD_ARG;
+    if (!((M == 128 && N % 16 == 0) || (M == 64 && N % 8 == 0)) || N < 8 || N > 256) return QGRU_ERR_BAD_ARG;
+    if (accumulators < 1 || accumulators * N + (a_in_tmem ? 32 : 0) > 512 || mmas < 1 || mmas > (1 << 22) || ctas < 1)
+        return QGRU_ERR_BAD_ARG;
+    if (cudaSetDevice(device) != cudaSuccess) return QGRU_ERR_CUDA;
+    int sms = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    ctas = std::min(ctas, sms);
+    long long *d_cycles = nullptr;
+    int *d_to = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    int rc = QGRU_ERR_CUDA;
+    const size_t smem = 16384 + 32768 + 64 + 1024;
+    do {
+        if (cudaMalloc(&d_cycles, sizeof(long long) * ctas) != cudaSuccess) break;
+        if (cudaMalloc(&d_to, sizeof(int)) != cudaSuccess) break;
+        if (cudaMemset(d_to, 0, sizeof(int)) != cudaSuccess) break;
+        if (cudaFuncSetAttribute(k_probe_mma_i8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) break;
+        if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) break;
+        k_probe_mma_i8<<<ctas, 128, smem>>>(M, N, a_in_tmem, accumulators, std::min(mmas, 256), d_cycles, d_to);   // warm-up
+        cudaEventRecord(e0);
+        k_probe_mma_i8<<<ctas, 128, smem>>>(M, N, a_in_tmem, accumulators, mmas, d_cycles, d_to);
+        cudaEventRecord(e1);
+        if (cudaEventSynchronize(e1) != cudaSuccess || cudaGetLastError() != cudaSuccess) break;
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        std::vector<long long> cyc(ctas);
+        int to = 0;
+        if (cudaMemcpy(cyc.data(), d_cycles, sizeof(long long) * ctas, cudaMemcpyDeviceToHost) != cudaSuccess) break;
+        if (cudaMemcpy(&to, d_to, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) break;
+        if (to) {
+            rc = QGRU_ERR_TIMEOUT;
+            break;
+        }
+        long long worst = 0;
+        for (long long c : cyc) worst = std::max(worst, c);
+        *cycles_per_mma = (double)worst / mmas;
+        *tera_ops = 2.0 * M * N * 32.0 * (double)mmas * ctas / (ms * 1e-3) / 1e12;
+        rc = QGRU_OK;
+    } while (false);
+    cudaGetLastError();
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    cudaFree(d_cycles);
+    cudaFree(d_to);
+    return rc;
+}

@@ -110,6 +110,17 @@ class Handle:
                  "qgru_get_weights_i32")
         return out
 
+    def _out_buffer(self, out, name, dtype, shape):
+        """A caller-supplied result tensor is written through its raw pointer: it must be a
+        contiguous tensor of exactly this shape and type on this handle's device."""
+        if out is None:
+            return torch.empty(shape, dtype=dtype, device=self._tdev)
+        if not isinstance(out, torch.Tensor) or not out.is_cuda or out.device != self._tdev:
+            raise ValueError(f"{name} must be a CUDA tensor on {self._tdev}")
+        if out.dtype != dtype or tuple(out.shape) != tuple(shape) or not out.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous {dtype} tensor of shape {list(shape)}")
+        return out
+
     # -- forward (device tensors)
     def forward_i32(self, x_q, h0_q=None, reverse=False, out=None, sync=True):
         """x_q [T,B,I] int32 -> h_q [(T+1),B,H] int32 (slot layout as in include/qgru.h)."""
@@ -119,8 +130,7 @@ class Handle:
         T, B = int(x_q.shape[0]), int(x_q.shape[1])
         if h0_q is not None:
             h0_q = _check_tensor(h0_q, "h0_q", torch.int32, (B, self.hidden_size))
-        h_q = out if out is not None else torch.empty((T + 1, B, self.hidden_size), dtype=torch.int32,
-                                                      device=self._tdev)
+        h_q = self._out_buffer(out, "out", torch.int32, (T + 1, B, self.hidden_size))
         self._ck(self._lib.qgru_forward_i32(self._h, T, B, _ptr(x_q), _ptr(h0_q), _ptr(h_q),
                                             _cabi.FLAG_REVERSE if reverse else 0, _stream(self._tdev)),
                  "qgru_forward_i32")
@@ -164,8 +174,7 @@ class Handle:
         T, B = int(x_q.shape[0]), int(x_q.shape[1])
         if h0_q is not None:
             h0_q = _check_tensor(h0_q, "h0_q", torch.int32, (B, self.hidden_size))
-        h_q = out if out is not None else torch.empty((T + 1, B, self.hidden_size), dtype=torch.int32,
-                                                      device=self._tdev)
+        h_q = self._out_buffer(out, "out", torch.int32, (T + 1, B, self.hidden_size))
         self._ck(self._lib.qgru_forward_i32_static(self._h, T, B, _ptr(x_q), _ptr(h0_q), _ptr(h_q),
                                                    _cabi.FLAG_REVERSE if reverse else 0,
                                                    _stream(self._tdev)), "qgru_forward_i32_static")
@@ -180,8 +189,7 @@ class Handle:
         T, B = int(x.shape[0]), int(x.shape[1])
         if h0 is not None:
             h0 = _check_tensor(h0, "h0", torch.float32, (B, self.hidden_size))
-        h = out if out is not None else torch.empty((T + 1, B, self.hidden_size), dtype=torch.float32,
-                                                    device=self._tdev)
+        h = self._out_buffer(out, "out", torch.float32, (T + 1, B, self.hidden_size))
         x_q = torch.empty((T, B, self.input_size), dtype=torch.int32, device=self._tdev) if want_x_q else None
         self._ck(self._lib.qgru_forward_f32(self._h, T, B, _ptr(x), _ptr(h0), _ptr(h), _ptr(x_q),
                                             _cabi.FLAG_REVERSE if reverse else 0, _stream(self._tdev)),
@@ -553,3 +561,13 @@ def forward_calibrate(is_training, time_steps, batch_size, input_size, hidden_si
     h = hd.calibrate_minmax(W, R, bw, br, x, quant_ranges, h0, want_h=True)
     v = torch.empty(0, dtype=torch.float32, device=x.device)
     return h, v
+
+
+def probe_mma_i8(M=128, N=256, a_in_tmem=False, accumulators=1, mmas=16384, ctas=148, device=0):
+    """Issue rate of tcgen05.mma kind::i8 for one shape (qgru_probe_mma_i8): returns
+    (SM cycles per MMA in a back-to-back chain, aggregate 1e12 int8 ops/s over `ctas` SMs)."""
+    cyc, tops = C.c_double(), C.c_double()
+    st = _cabi.lib().qgru_probe_mma_i8(int(device), int(M), int(N), int(bool(a_in_tmem)), int(accumulators),
+                                       int(mmas), int(ctas), C.byref(cyc), C.byref(tops))
+    _cabi.check(st, "qgru_probe_mma_i8")
+    return cyc.value, tops.value
