@@ -312,7 +312,9 @@ QGRU_API int qgru_forward_f32(qgru_handle *h, int T, int B, const float *x, cons
  * implicit synchronisation of cudaMalloc).  The whole workspace is a fixed array of 8 MiB inside
  * the library image - every GPU that loads the library holds it until the process exits - so the
  * call makes no cudaMalloc / cudaFree and grows nothing.  Problems whose workspace
- * (T*B*(Kpad(I) + 3H*b) + 2*B*Kpad(H) bytes, Kpad = round up to 128, b = 1 or 2) does not fit
+ * (a256(T*B*Kpad(I)) + a256(T*B*3H*b) + a256(2*B*Kpad(H)) + 128*G bytes; Kpad rounds up to 128,
+ * a256 to 256, b = 1 or 2 bytes per W*x+bw value, G = batch groups of the recurrence, at most the
+ * SM count) does not fit
  * are rejected with QGRU_ERR_BAD_ARG and a message naming both sizes.  It needs the 8-bit
  * storage plan (x, h, W, R at most 8 bits) and runs the SIMT GEMM and the dp4a recurrence.
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make
@@ -357,7 +359,7 @@ QGRU_API uint64_t qgru_launch_count(const qgru_handle *h);
  * ("gemm=tcgen05_i8 rec=mma ..."), for benchmarks and tests. */
 QGRU_API const char *qgru_describe_plan(qgru_handle *h, int T, int B);
 
-/* No counterpart in the reference (it has no tensor-core code).  Measurement aid: runs `mmas`
+/* No counterpart in the reference (it has no tensor-core code).  Measurement aid: runs `mmas` (a multiple of 8)
  * back-to-back tcgen05.mma kind::i8 instructions of shape M x N x 32 (M 128 with N a multiple of
  * 16, or M 64 with N a multiple of 8; N <= 256) on `ctas` CTAs, one per SM, operands resident in
  * shared memory (or A in tensor memory), rotating over `accumulators` accumulators; no loads, no

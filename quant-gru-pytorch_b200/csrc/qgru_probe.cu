@@ -49,12 +49,29 @@ k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, long long *cycl
         const uint64_t bdesc = tc::smem_desc_sw128(tc::smem_u32(b_tile));
         const uint32_t a_col = tmem + (uint32_t)(n_acc * N);   // 32 columns after the accumulators
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // Every operand of the 8 MMAs of a loop pass is prepared before the clock starts, so that the
+        // issuing thread's own arithmetic does not set the pace: the body is 8 MMA instructions.
+        uint32_t dcol[8], acol[8];
+        uint64_t ad[8], bd[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            dcol[j] = tmem + (uint32_t)((j % n_acc) * N);
+            acol[j] = a_col + (uint32_t)(j & 3) * 8;
+            ad[j] = adesc + 2 * (uint64_t)(j & 3);
+            bd[j] = bdesc + 2 * (uint64_t)(j & 3);
+        }
+        const int passes = mmas / 8;
         const long long t0 = clock64();
-        for (int i = 0; i < mmas; ++i) {
-            const uint32_t d = tmem + (uint32_t)((i % n_acc) * N);
-            const uint32_t ks = (uint32_t)(i & 3);
-            if (a_in_tmem) tc::mma_i8_ts(d, a_col + ks * 8, bdesc + 2 * ks, idesc, 1u);
-            else tc::mma_i8(d, adesc + 2 * ks, bdesc + 2 * ks, idesc, 1u);
+        if (a_in_tmem) {
+            for (int i = 0; i < passes; ++i) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) tc::mma_i8_ts(dcol[j], acol[j], bd[j], idesc, 1u);
+            }
+        } else {
+            for (int i = 0; i < passes; ++i) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) tc::mma_i8(dcol[j], ad[j], bd[j], idesc, 1u);
+            }
         }
         tc::mma_commit(bar);
         const bool ok = tc::mbar_wait(bar, 0, PROBE_WAIT);
@@ -75,7 +92,7 @@ extern "C" int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int ac
     using namespace qgru;
     if (!cycles_per_mma || !tera_ops) return QGRU_ERR_BAD_ARG;
     if (!((M == 128 && N % 16 == 0) || (M == 64 && N % 8 == 0)) || N < 8 || N > 256) return QGRU_ERR_BAD_ARG;
-    if (accumulators < 1 || accumulators * N + (a_in_tmem ? 32 : 0) > 512 || mmas < 1 || mmas > (1 << 22) || ctas < 1)
+    if (accumulators < 1 || accumulators * N + (a_in_tmem ? 32 : 0) > 512 || mmas < 8 || mmas % 8 != 0 || mmas > (1 << 22) || ctas < 1)
         return QGRU_ERR_BAD_ARG;
     if (cudaSetDevice(device) != cudaSuccess) return QGRU_ERR_CUDA;
     int sms = 0;
@@ -92,7 +109,7 @@ extern "C" int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int ac
         if (cudaMemset(d_to, 0, sizeof(int)) != cudaSuccess) break;
         if (cudaFuncSetAttribute(k_probe_mma_i8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) break;
         if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) break;
-        k_probe_mma_i8<<<ctas, 128, smem>>>(M, N, a_in_tmem, accumulators, std::min(mmas, 256), d_cycles, d_to);   // warm-up
+        k_probe_mma_i8<<<ctas, 128, smem>>>(M, N, a_in_tmem, accumulators, std::min(mmas, 256) / 8 * 8, d_cycles, d_to);   // warm-up
         cudaEventRecord(e0);
         k_probe_mma_i8<<<ctas, 128, smem>>>(M, N, a_in_tmem, accumulators, mmas, d_cycles, d_to);
         cudaEventRecord(e1);

@@ -290,15 +290,21 @@ class QuantGRU(nn.Module):
         hx = hx.to(device=device, dtype=dtype)
         return [hx[d].contiguous() for d in range(self.num_directions)]
 
-    def _ensure_quant_ready(self, training_ok=False):
-        if self.training and not training_ok:
-            raise NotImplementedError("the quantized forward in train() mode needs gradients enabled "
-                                      "(quantization-aware training); call .eval() for inference")
-        if self._quant_params_dirty and self.quant_ranges is not None:
+    def _has_calibration_data(self):
+        have = self.quant_ranges if self.calibration_method == "minmax" else self.hist_collectors
+        have_r = self.quant_ranges_reverse if self.calibration_method == "minmax" else self.hist_collectors_reverse
+        return have is not None and (not self.bidirectional or have_r is not None)
+
+    def _ensure_quant_ready(self):
+        """Quant params are (re)derived whenever calibration data or the bit-width configuration
+        changed since they were last computed, as the reference's forward does
+        (pytorch/quant_gru.py:2106-2125): the documented flow `calibrating=True; forward();
+        calibrating=False; forward()` needs no explicit finalize_calibration() for any method."""
+        if self._quant_params_dirty and self._has_calibration_data():
             self.finalize_calibration()
         elif not self.is_calibrated():
-            if self.quant_ranges is not None:
-                self.finalize_calibration()
+            if self.quant_ranges is not None or self.hist_collectors is not None:
+                self.finalize_calibration()   # raises if the data of the chosen method is missing
             else:
                 raise RuntimeError("quantization is enabled but the module is not calibrated: set "
                                    "calibrating=True, run forward() on calibration data, then "
@@ -370,7 +376,7 @@ class QuantGRU(nn.Module):
                                                   any(p.requires_grad for p in self.parameters()))
         if needs_grad and self.training and not self.calibrating:
             if self.use_quantization:
-                self._ensure_quant_ready(training_ok=True)
+                self._ensure_quant_ready()
             if not input.is_cuda:
                 raise ValueError("input must be a CUDA tensor")
             want = (self.num_directions, input.shape[0 if self.batch_first else 1], self.hidden_size)

@@ -356,6 +356,45 @@ def test_quantgru_errors(cuda_device):
     f(torch.randn(3, 2, 8, device=cuda_device))
     f.calibrating = False
     f.use_quantization = True
+    xt = torch.randn(3, 2, 8, device=cuda_device)
+    f.eval()
+    want = f(xt)
     f.train()
-    with pytest.raises(NotImplementedError), torch.no_grad():   # train() mode without gradients
-        f(torch.randn(3, 2, 8, device=cuda_device))
+    with torch.no_grad():                      # train() mode without gradients: the inference kernels
+        got = f(xt)
+    assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+
+
+@pytest.mark.parametrize("method", ["sqnr", "percentile"])
+def test_quantgru_histogram_flow_needs_no_explicit_finalize(cuda_device, method):
+    """calibrating=True; forward(); calibrating=False; forward() - the reference's documented flow
+    (pytorch/quant_gru.py:2106-2125) - derives the params on the first quantized forward for the
+    histogram methods too, and a second calibration pass replaces them."""
+    import torch
+    torch.manual_seed(3)
+    m = quant_gru.QuantGRU(12, 24, bidirectional=True, quant_storage_dtype="int32").cuda().eval()
+    m.calibration_method = method
+    m.percentile_value = 99.9
+    x = torch.randn(6, 5, 12, device=cuda_device)
+    m.calibrating = True
+    m(x)
+    m.calibrating = False
+    m.use_quantization = True
+    out1, _ = m(x)                              # no finalize_calibration() call
+    assert m.is_calibrated() and torch.isfinite(out1).all()
+    ref = quant_gru.QuantGRU(12, 24, bidirectional=True, quant_storage_dtype="int32").cuda().eval()
+    ref.load_state_dict(m.state_dict())
+    ref.calibration_method, ref.percentile_value = method, 99.9
+    ref.calibrating = True
+    ref(x)
+    ref.calibrating = False
+    ref.finalize_calibration()
+    ref.use_quantization = True
+    out_ref, _ = ref(x)
+    assert torch.equal(out1, out_ref)
+    scale1 = float(m.quant_params.c.op[OP["x"]].scale)
+    m.calibrating = True                        # second pass with wider data: params must follow
+    m(x * 4.0)
+    m.calibrating = False
+    m(x)
+    assert float(m.quant_params.c.op[OP["x"]].scale) > scale1
