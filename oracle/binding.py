@@ -47,6 +47,9 @@ def build_ref():
     if os.path.isdir(os.path.join(REF_ROOT, "src")):
         subprocess.run(["make", "-C", _HERE, "-j8", "ref", "REF_ROOT=" + REF_ROOT], check=True,
                        capture_output=True)
+        # the reference-signature binding of the product library and its test driver
+        subprocess.run(["make", "-C", _HERE, "shimtest", "REF_ROOT=" + REF_ROOT], check=True,
+                       capture_output=True)
     return so if os.path.exists(so) else None
 
 
@@ -443,6 +446,52 @@ class _GpuHistSet:
             f(self.h)
         except Exception:
             pass
+
+
+class ShimTest:
+    """The reference-signature entry points of quant-gru-pytorch_b200/shim/gru_interface_b200.cc
+    (quantGRUForwardInt32 / Int / IntIO), called with host arrays through oracle/shim_driver.cc.
+    Needs oracle/_ref/libqgru_shimtest.so (built where the reference's headers are) and a GPU."""
+
+    def __init__(self):
+        self.lib = C.CDLL(os.path.join(_HERE, "_ref", "libqgru_shimtest.so"))
+        self.lib.shimtest_last_error.restype = C.c_char_p
+
+    def _check(self, rc, what):
+        if rc:
+            raise (ValueError if rc == 2 else RuntimeError)(f"{what}: {self.lib.shimtest_last_error().decode()}")
+
+    def forward_i32(self, T, B, I, H, wq, x_q, h0_q, params, sc, training=False):
+        h = np.zeros((T + 1, B, H), np.int32)
+        v = np.zeros((T, B, 4 * H), np.int32) if training else None
+        masks = [np.zeros((T * B, 3 * H), np.uint8) for _ in range(4)] + [np.zeros((T * B, H), np.uint8)] \
+            if training else None
+        mp = (C.c_void_p * 5)(*[m.ctypes.data for m in masks]) if training else None
+        h0p = _i(np.ascontiguousarray(h0_q, np.int32)) if h0_q is not None else None
+        rc = self.lib.shimtest_forward_i32(int(training), T, B, I, H, *[_i(np.ascontiguousarray(a, np.int32)) for a in wq],
+                                           _i(np.ascontiguousarray(x_q, np.int32)), h0p, C.byref(params),
+                                           *[_f(a) for a in sc], _i(h), _i(v) if training else None, mp)
+        self._check(rc, "quantGRUForwardInt32 (shim)")
+        return (h, v, masks) if training else h
+
+    def forward_f32(self, T, B, I, H, W, R, bw, br, x, h0, params, sc):
+        h = np.zeros((T + 1, B, H), np.float32)
+        q = [np.zeros((I, 3 * H), np.int32), np.zeros((H, 3 * H), np.int32), np.zeros(3 * H, np.int32),
+             np.zeros(3 * H, np.int32), np.zeros((T, B, I), np.int32)]
+        h0p = _f(np.ascontiguousarray(h0, np.float32)) if h0 is not None else None
+        rc = self.lib.shimtest_forward_f32(T, B, I, H, *[_f(np.ascontiguousarray(a, np.float32)) for a in (W, R, bw, br, x)],
+                                           h0p, C.byref(params), *[_f(a) for a in sc], _f(h), *[_i(a) for a in q])
+        self._check(rc, "quantGRUForwardInt (shim)")
+        return h, q[:4], q[4]
+
+    def forward_intio(self, T, B, I, H, W, R, bw, br, x_q, h0_q, params, sc):
+        h = np.zeros((T + 1, B, H), np.int32)
+        h0p = _i(np.ascontiguousarray(h0_q, np.int32)) if h0_q is not None else None
+        rc = self.lib.shimtest_forward_intio(T, B, I, H, *[_f(np.ascontiguousarray(a, np.float32)) for a in (W, R, bw, br)],
+                                             _i(np.ascontiguousarray(x_q, np.int32)), h0p, C.byref(params),
+                                             *[_f(a) for a in sc], _i(h))
+        self._check(rc, "quantGRUForwardIntIO (shim)")
+        return h
 
 
 def reference_or_none():

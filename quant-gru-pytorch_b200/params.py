@@ -308,7 +308,11 @@ class GRUQuantParams:
     def to_export_dict(self):
         """The ``operators`` object of export_quant_params (pytorch/quant_gru.py:3934-3944):
         scalar operators export scale / zero_point / real_min / real_max; weight operators
-        always export full 3H scale lists tagged PER_CHANNEL, as the reference does."""
+        always export full 3H scale lists tagged PER_CHANNEL.  That is what the reference's
+        exporter writes whatever the configured granularity: it looks the granularity up under
+        ``weight_ih_granularity_`` (:3788), a name the binding's configuration object does not
+        have (its attribute is ``W_granularity_``), and falls back to PER_CHANNEL (:3811-3814);
+        tests/golden/ref_export_*.json are files that exporter produced."""
         out = {}
         for i, n in enumerate(OPS):
             o = self.c.op[i]
@@ -321,18 +325,47 @@ class GRUQuantParams:
                 sc = self.scales[n]
                 entry.update(scale=[float(s) for s in sc], zero_point=[0] * len(sc),
                              enc_type="PER_CHANNEL",
-                             real_min=[float(s * qmin) for s in sc],
-                             real_max=[float(s * qmax) for s in sc])
+                             real_min=[float(s) * qmin for s in sc],
+                             real_max=[float(s) * qmax for s in sc])
             else:
                 entry.update(scale=float(o.scale), zero_point=int(o.zero_point),
                              enc_type="PER_TENSOR",
-                             real_min=float(o.scale * (qmin - o.zero_point)),
-                             real_max=float(o.scale * (qmax - o.zero_point)))
+                             real_min=float(o.scale) * (qmin - o.zero_point),
+                             real_max=float(o.scale) * (qmax - o.zero_point))
             out[OP_TO_JSON[n]] = entry
         return out
 
+    @staticmethod
+    def _scale_list(key, entry):
+        """The scale values of one exported operator as a list, in the reference's order of
+        preference (_parse_runtime_scale_lists, pytorch/quant_gru.py:4008-4045): `scale`
+        (scalar or list); else `multiplier` + `shift` (M * 2^-shift each); else the old
+        power-of-two fields `n` / `exp2_inv` / `shift` (2^-n each)."""
+        def as_list(v):
+            return list(v) if isinstance(v, (list, tuple)) else [v]
+        if "scale" in entry:
+            sc = [float(v) for v in as_list(entry["scale"])]
+            if not sc:
+                raise ValueError(f"{key}: empty scale")
+            if any(v <= 0 for v in sc):
+                raise ValueError(f"{key}: every scale must be > 0")
+            return sc
+        if "multiplier" in entry and "shift" in entry:
+            m, sh = as_list(entry["multiplier"]), as_list(entry["shift"])
+            if len(m) != len(sh):
+                raise ValueError(f"{key}: multiplier and shift differ in length")
+            return [float(int(a)) * 2.0 ** (-int(b)) for a, b in zip(m, sh)]
+        for old in ("n", "exp2_inv", "shift"):
+            if old in entry:
+                return [2.0 ** (-int(v)) for v in as_list(entry[old])]
+        raise ValueError(f"{key}: no scale / multiplier+shift / power-of-two field")
+
     @classmethod
     def from_export_dict(cls, ops, hidden, use_pot2=False):
+        """Read the ``operators`` object of a quant-param file (_parse_operators_dict,
+        pytorch/quant_gru.py:4051-4127).  Weight operators carry 1 (PER_TENSOR), 3 (PER_GATE) or
+        3H (PER_CHANNEL, the default) scales; every other operator one scale, given as a scalar
+        or a one-element list."""
         self = cls(hidden)
         self.c.use_pot2 = int(use_pot2)
         for key, entry in ops.items():
@@ -342,21 +375,24 @@ class GRUQuantParams:
             o.is_unsigned = int(dt.startswith("UINT"))
             o.bits = int(dt.replace("UINT", "").replace("INT", ""))
             o.symmetric = int(bool(entry.get("symmetric", True)))
+            sc = np.asarray(cls._scale_list(key, entry), np.float32)
             if n in WEIGHT_OPS:
-                sc = np.asarray(entry["scale"], np.float32).reshape(-1)
-                enc = entry.get("enc_type", "PER_CHANNEL")
-                if sc.size == 1:
+                enc = entry.get("enc_type") or "PER_CHANNEL"
+                if enc == "PER_TENSOR":
                     sc = np.full(3 * hidden, sc[0], np.float32)
-                elif sc.size == 3:
+                elif enc == "PER_GATE":
+                    if sc.size != 3:
+                        raise ValueError(f"{key}: PER_GATE needs 3 scales, got {sc.size}")
                     sc = np.repeat(sc, hidden)
                 if sc.size != 3 * hidden:
-                    raise ValueError(f"{key}: expected 1, 3 or {3 * hidden} scales, got {sc.size}")
+                    raise ValueError(f"{key}: expected {3 * hidden} scales, got {sc.size}")
                 self.scales[n] = np.ascontiguousarray(sc)
                 self.c.granularity[WEIGHT_OPS.index(n)] = GRANULARITY.get(enc, PER_CHANNEL)
                 o.scale = float(sc[0])
                 o.zero_point = 0
             else:
-                o.scale = float(entry["scale"])
-                o.zero_point = int(entry["zero_point"])
+                zp = entry.get("zero_point", 0)
+                o.scale = float(sc[0])
+                o.zero_point = int(zp[0] if isinstance(zp, (list, tuple)) else zp)
         self.regenerate_luts()
         return self

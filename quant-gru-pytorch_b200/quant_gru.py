@@ -237,6 +237,10 @@ class QuantGRU(nn.Module):
         if info.get("hidden_size", self.hidden_size) != self.hidden_size or \
                 info.get("input_size", self.input_size) != self.input_size:
             raise ValueError("quant-param file was exported for a different input/hidden size")
+        if bool(info.get("bidirectional", False)) != self.bidirectional:   # pytorch/quant_gru.py:4379-4383
+            raise ValueError(f"bidirectional mismatch: file {info.get('bidirectional')}, module {self.bidirectional}")
+        if "operators" not in doc:
+            raise ValueError(f"unsupported quant-param file: no 'operators' (has {list(doc)})")
         pot2 = bool(info.get("use_pot2_scale", False))
         self.quant_params = GRUQuantParams.from_export_dict(doc["operators"], self.hidden_size, pot2)
         if self.bidirectional:
@@ -244,6 +248,11 @@ class QuantGRU(nn.Module):
                 raise ValueError("bidirectional module needs 'operators_reverse' in the file")
             self.quant_params_reverse = GRUQuantParams.from_export_dict(doc["operators_reverse"],
                                                                         self.hidden_size, pot2)
+            # both directions quantize the same input (pytorch/quant_gru.py:4428-4433)
+            fi, ri = doc["operators"].get("input", {}), doc["operators_reverse"].get("input", {})
+            for field in ("multiplier", "shift", "zero_point"):
+                if (field in fi or field in ri) and fi.get(field) != ri.get(field):
+                    raise ValueError(f"operators.input and operators_reverse.input differ in {field}")
         self._bitwidth_config = self.quant_params.config()
         self.use_quantization = True
         self._quant_params_dirty = False

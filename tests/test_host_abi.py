@@ -174,6 +174,62 @@ def test_quant_param_export_round_trip(oracle):
     assert bytes(again.c) == bytes(case.params.c)
 
 
+@pytest.mark.parametrize("name,hidden", [("cfg2_h8", 8), ("cfg3_h4", 4)])
+def test_quant_param_file_written_by_the_reference_exporter(name, hidden):
+    """tests/golden/ref_export_*.json were formatted by the reference's own exporter
+    (_build_operators_dict, run by tests/golden/make_export_fixture.py) from the parameters
+    stored beside them: this library's reader gives those parameters back, and its writer
+    produces the same document, key order and number formatting included."""
+    import json
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    with open(os.path.join(here, f"ref_export_{name}.json"), encoding="utf-8") as f:
+        text = f.read()
+    doc = json.loads(text)
+    with open(os.path.join(here, f"ref_export_{name}.params.bin"), "rb") as f:
+        want = params_mod.GRUQuantParams.from_bytes(f.read(), hidden)
+    got = params_mod.GRUQuantParams.from_export_dict(doc["operators"], hidden,
+                                                     bool(doc["model_info"]["use_pot2_scale"]))
+    for i in range(len(want.c.op)):
+        a, b = got.c.op[i], want.c.op[i]
+        assert (a.scale, a.zero_point, a.bits, a.is_unsigned, a.symmetric) == \
+               (b.scale, b.zero_point, b.bits, b.is_unsigned, b.symmetric), i
+    for a, b in zip(got.scale_list(), want.scale_list()):
+        assert np.array_equal(a, b)
+    assert bytes(got.c.lut[0]) == bytes(want.c.lut[0])      # LUTs are regenerated from the loaded scales
+    ours = want.to_export_dict()
+    ref_ops = doc["operators"]
+    assert set(ours) == set(ref_ops)
+    for k in ref_ops:
+        assert ours[k] == ref_ops[k], k
+        assert list(ours[k]) == list(ref_ops[k]), k          # field order inside an operator
+
+
+def test_quant_param_import_accepts_the_reference_parsers_other_encodings():
+    """_parse_runtime_scale_lists (pytorch/quant_gru.py:4008-4045): one-element lists for scalar
+    operators, multiplier + shift, the old power-of-two fields; enc_type PER_TENSOR / PER_GATE."""
+    import json
+    H = 4
+    base = {"dtype": "INT8", "symmetric": True}
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_export_cfg3_h4.json"),
+              encoding="utf-8") as f:
+        ops = json.load(f)["operators"]        # a complete file; some operators re-encoded below
+    ops.update({"input": dict(base, scale=[0.5], zero_point=[3]),
+           "output": dict(base, multiplier=40000, shift=20, zero_point=-2),
+           "weight_ih_linear": dict(base, n=5, zero_point=0),
+           "weight_ih": dict(base, scale=0.25, enc_type="PER_TENSOR"),
+           "weight_hh": dict(base, scale=[0.5, 0.25, 0.125], enc_type="PER_GATE"),
+           "bias_ih": dict(base, multiplier=[32768] * 12, shift=[20] * 12)})
+    p = params_mod.GRUQuantParams.from_export_dict(ops, H)
+    assert p.c.op[OP["x"]].scale == 0.5 and p.c.op[OP["x"]].zero_point == 3
+    assert p.c.op[OP["h"]].scale == np.float32(40000 * 2.0 ** -20) and p.c.op[OP["h"]].zero_point == -2
+    assert p.c.op[OP["weight_ih_linear"]].scale == 2.0 ** -5
+    assert np.all(p.scales["W"] == 0.25) and list(p.scales["R"]) == [0.5] * 4 + [0.25] * 4 + [0.125] * 4
+    assert np.all(p.scales["bw"] == np.float32(2.0 ** -5))
+    for bad in (dict(base, scale=[0.5, 0.25], enc_type="PER_GATE"), dict(base, scale=-1.0), dict(base)):
+        with pytest.raises(ValueError):
+            params_mod.GRUQuantParams.from_export_dict({"weight_ih": bad}, H)
+
+
 def test_decode_effective_scale_matches_encoding(oracle):
     """qgru_decode_effective_scale == multiplier * 2^-shift of encodeMShift (POT2: 2^-round(-log2 s))."""
     import importlib
