@@ -381,6 +381,11 @@ QGRU_API int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int accu
  *                                           shift-free form), or the reference's step by step
  *   "r_resident" auto | smem | tmem       where the cluster recurrence keeps its slice of R
  *   "tiles_per_cta" 1 | 2                 cluster recurrence at 128 < H <= 256: 128-unit tiles per CTA
+ *   "subgroups" auto | 1 | 2              cluster recurrence: independent batch sub-groups per CTA (with 2,
+ *                                         the MMAs of one overlap the cells of the other)
+ *   "probe_floor" 0 | 1                   measurement aid: the cluster recurrence runs with its MMAs and
+ *                                         cells left out (results are meaningless); the recurrence time of
+ *                                         qgru_last_timing is then the per-step synchronisation floor
  *   "sm_limit" n   use at most n SMs (0 = all);  "spin_limit" n   bound of the group barrier
  * Unknown names or values return QGRU_ERR_BAD_ARG. */
 QGRU_API int qgru_set_option(qgru_handle *h, const char *name, const char *value);

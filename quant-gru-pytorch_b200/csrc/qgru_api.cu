@@ -179,9 +179,13 @@ int qgru_set_option(qgru_handle *h, const char *name, const char *value) {
         else if (v == "generic") h->opt_cell = 1;
         else if (v == "fused") h->opt_cell = 2;   // tabulated cell, but never its shift-free form
         else return fail(h, QGRU_ERR_BAD_ARG, "cell: auto|generic|fused");
-    } else if (n == "debug_stamps") {
-        // address (decimal) of a device buffer of T*8 int64 clock stamps, 0 to switch off
-        h->dbg_stamps = reinterpret_cast<long long *>(strtoull(value, nullptr, 10));
+    } else if (n == "subgroups") {
+        if (v == "auto") h->opt_ng = 0;
+        else if (v == "1") h->opt_ng = 1;
+        else if (v == "2") h->opt_ng = 2;
+        else return fail(h, QGRU_ERR_BAD_ARG, "subgroups: auto|1|2");
+    } else if (n == "probe_floor") {
+        h->opt_floor = atoi(value) != 0;
     } else if (n == "sm_limit") {
         h->opt_sm_limit = std::max(0, atoi(value));
     } else if (n == "spin_limit") {
@@ -606,7 +610,7 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
     // group; H <= 1024) or through global memory with a counter per group (H <= 512)
     RecMmaPlan cp;
     const bool cluster_ok = h->opt_rec != 1 && h->opt_exchange != 1 &&
-                            rec_cluster_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, h->opt_r_where, h->opt_mt, &cp);
+                            rec_cluster_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, h->opt_r_where, h->opt_mt, h->opt_ng, &cp);
     const bool global_ok = h->opt_rec != 1 && rec_mma_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, &mp);
     const bool mma_ok = cluster_ok || global_ok;
     if (h->opt_rec == 2 && !mma_ok)
@@ -703,21 +707,21 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
         a.bar = h->d_bar;
         a.abort_flag = h->d_flags + 1;
         a.spin_limit = h->spin_limit;
-        a.dbg = h->dbg_stamps;
         const unsigned long long before = h->rec.launches + h->rec_cl.launches;
         // the branch-free fused cell: every scale of the step in shift-free form, 32-bit sums
         const bool fast_cell = fused && use_cluster && h->opt_cell != 2 && a.lc.fits32 && h->rs_fast[1] &&
                                h->gc_host.rh_to_n.mq != 0 && h->gc_host.uh_to_h.mq != 0;
         if (use_cluster)
             rc = rec_cluster_launch(h->rec_cl, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256,
-                                    h->h_uns, ih_bytes, fused ? fast_cell : h->gc_host.narrow != 0, fused, st, &h->err);
+                                    h->h_uns, ih_bytes, fused ? fast_cell : h->gc_host.narrow != 0, fused, h->opt_floor, st,
+                                    &h->err);
         else
             rc = rec_mma_launch(h->rec, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256,
                                 h->h_uns, ih_bytes, h->gc_host.narrow != 0, fused, h->coop != 0, st, &h->err);
         if (rc) return rc;
         h->launches += h->rec.launches + h->rec_cl.launches - before;
-        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 exchange=%s cell=%s MT=%d NB=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d r_in=%s narrow=%d ih_bytes=%d shiftfree=%d%d%d%d",
-                 used_tc ? "tcgen05_i8" : "simt_dp4a", use_cluster ? "cluster_dsmem" : "global", fast_cell ? "fused_shiftfree" : fused ? "fused" : "generic", mp.MT, mp.NB, mp.P, mp.G,
+        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 exchange=%s cell=%s%s MT=%d NB=%d NG=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d r_in=%s narrow=%d ih_bytes=%d shiftfree=%d%d%d%d",
+                 used_tc ? "tcgen05_i8" : "simt_dp4a", use_cluster ? "cluster_dsmem" : "global", fast_cell ? "fused_shiftfree" : fused ? "fused" : "generic", (use_cluster && h->opt_floor) ? "(FLOOR PROBE: no MMAs, no cell)" : "", mp.MT, mp.NB, mp.NG, mp.P, mp.G,
                  mp.groups_per_launch, mp.smem, mp.tmem_cols, !use_cluster || mp.tmem_tiles == 0 ? "smem" : (mp.tmem_tiles == mp.MT * 3 * (h->Hpad / 128) ? "tmem" : "tmem+smem"),
                  h->gc_host.narrow, ih_bytes, (int)a.lc.fits32,
                  (int)h->rs_fast[1], h->gc_host.rh_to_n.mq != 0, h->gc_host.uh_to_h.mq != 0);

@@ -619,7 +619,7 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
     // 0.28 ms at H = 128, B = 32 and 4.1 against 4.6 us per step at H = 256, B = 1)
     const bool small = (h->opt_rec == 0 || h->opt_rec == 4) && h->Hpad <= 256 && B <= sms;
     const bool cluster_ok = !small && h->opt_rec != 1 && h->opt_rec != 3 && h->opt_exchange != 1 &&
-                            rec_cluster_plan(H, h->Hpad, B, sms, h->smem_optin, n_tab, h->opt_r_where, h->opt_mt, &cp);
+                            rec_cluster_plan(H, h->Hpad, B, sms, h->smem_optin, n_tab, h->opt_r_where, h->opt_mt, h->opt_ng, &cp);
     if (cluster_ok) {
         if (cp.G > h->bar_groups) {
             if ((rc = alloc_dev(h, &h->d_bar, (size_t)cp.G * 32))) return rc;
@@ -641,17 +641,16 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
         a.bar = h->d_bar;
         a.abort_flag = h->d_flags + 1;
         a.spin_limit = h->spin_limit;
-        a.dbg = nullptr;
         a.fs_on = 1;
         a.fs_chan = chan + (size_t)3 * C;
         a.fs = fc;
         const unsigned long long before = h->rec_cl.launches;
         rc = rec_cluster_launch(h->rec_cl, cp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256,
-                                h->h_uns, ih_bytes, false, false, st, &h->err);
+                                h->h_uns, ih_bytes, false, false, false, st, &h->err);
         if (rc) return rc;
         h->launches += h->rec_cl.launches - before;
-        snprintf(buf, sizeof(buf), "path=float_storage gemm=%s rec=tcgen05_i8_float_cell exchange=cluster_dsmem NB=%d P=%d G=%d smem=%zu tmem_cols=%d ih_bytes=%d gates=%s",
-                 used_tc ? "tcgen05_i8" : "simt_dp4a", cp.NB, cp.P, cp.G, cp.smem, cp.tmem_cols, ih_bytes,
+        snprintf(buf, sizeof(buf), "path=float_storage gemm=%s rec=tcgen05_i8_float_cell exchange=cluster_dsmem NB=%d NG=%d P=%d G=%d smem=%zu tmem_cols=%d ih_bytes=%d gates=%s",
+                 used_tc ? "tcgen05_i8" : "simt_dp4a", cp.NB, cp.NG, cp.P, cp.G, cp.smem, cp.tmem_cols, ih_bytes,
                  fc.tab_on ? "tabulated" : "evaluated");
     } else if ((h->opt_rec == 0 || h->opt_rec == 4) && h->Hpad <= 256 && B <= sms &&
                gemv_smem(h, n_tab) <= (size_t)h->smem_optin) {

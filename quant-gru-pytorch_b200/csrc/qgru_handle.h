@@ -43,7 +43,8 @@ struct qgru_handle {
     int opt_mt = 0;                          // cluster recurrence: 2 = two 128-unit tiles per CTA where 128 < H <= 256
     int opt_r_where = 0;                     // cluster recurrence: 0 auto, 1 R in shared memory, 2 in tensor memory
     unsigned spin_limit = 1u << 24;
-    long long *dbg_stamps = nullptr;  // profiling aid of the tensor-core recurrence kernel
+    int opt_ng = 0;                          // cluster recurrence: sub-groups per CTA (0 auto, 1, 2)
+    bool opt_floor = false;                  // cluster recurrence: run the synchronisation-floor probe instead
     // device state that lives with the handle
     GateConsts *d_gc = nullptr;
     int32_t *d_tables = nullptr;

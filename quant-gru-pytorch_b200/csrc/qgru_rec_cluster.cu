@@ -17,6 +17,12 @@
 // buffer (s+1)&1.  A peer can never be more than one step ahead (its MMAs of step s+1 need this
 // CTA's block of h_{s+1}), which is what makes two buffers enough.  Step 0's state is loaded
 // from global memory by TMA.
+//
+// A CTA may own NG independent sub-groups of NB batch rows each (NG = 2: "A" and "B").  Each has
+// its own accumulators, state tiles and barriers; the control thread issues the MMAs of A then
+// B, the epilogue warps work on A then B, so that B's MMAs run on the tensor pipe while the
+// warps are busy with A's cells and A's next MMAs while they are busy with B's: the two halves
+// of a step, which are serial for one group (exchange -> MMAs -> cells), overlap.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -74,12 +80,12 @@ struct ClusterSmem {
 
 // r_slots: 16 KB tile slots for R (staging on the way to tensor memory, then home of the tiles
 // that stay in shared memory)
-__host__ __device__ inline ClusterSmem cluster_smem_layout(int r_slots, int KBn, int NB, int n_table) {
+__host__ __device__ inline ClusterSmem cluster_smem_layout(int r_slots, int KBn, int NB, int NG, int n_table) {
     ClusterSmem s;
     s.r_tiles = 0;
     s.h_tile = (size_t)r_slots * 16384;
-    s.bars = s.h_tile + (size_t)2 * KBn * NB * 128;   // two state buffers
-    s.tables = s.bars + 128;
+    s.bars = s.h_tile + (size_t)NG * 2 * KBn * NB * 128;   // two state buffers per sub-group
+    s.tables = s.bars + 256;
     s.total = s.tables + (((size_t)n_table * 4 + 15) & ~size_t(15));
     return s;
 }
@@ -117,10 +123,15 @@ __device__ __noinline__ void issue_wide(int MT, int KBn, int NB, int tmem_tiles,
     }
 }
 
+constexpr int MAX_NG = 2;                        // sub-groups of batch rows per CTA
+
 // Cell variants: Fused = false: the generic datapath (Narrow picks its 32-bit rescales);
 // Fused = true: the tabulated cell, where Narrow = true selects the branch-free form that needs
 // every scale of the step in shift-free form and 32-bit linear sums.
-template <typename IhT, bool Narrow, bool Fused, int MT>
+// Floor = true is a measurement aid: the same launch, barriers, state exchange and output stores
+// with the MMAs and the cell left out (h_t = h_{t-1}); its duration is the synchronisation floor
+// the real kernel's time per step is quoted against.
+template <typename IhT, bool Narrow, bool Fused, int MT, bool Floor>
 __global__ void __launch_bounds__(REC_THREADS, 1)
 k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_h,
                      const __grid_constant__ GateConsts gc, RecMmaArgs a) {
@@ -130,34 +141,34 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
     const uint32_t raw = tc::smem_u32(smem_raw);
     unsigned char *base = smem_raw + (((raw + 1023u) & ~1023u) - raw);
     const int KBn = a.Hpad >> 7;
-    const ClusterSmem L = cluster_smem_layout(a.r_slots, KBn, a.NB, a.n_table);
+    const int NG = a.NG;
+    const ClusterSmem L = cluster_smem_layout(a.r_slots, KBn, a.NB, NG, a.n_table);
     unsigned char *r_tiles = base + L.r_tiles;
-    unsigned char *h_tile = base + L.h_tile;
+    unsigned char *h_tile = base + L.h_tile;                  // [NG][2 buffers][KBn slabs][NB rows][128 bytes]
     const uint32_t h_buf_bytes = (uint32_t)(KBn * a.NB * 128);
     uint64_t *bars = reinterpret_cast<uint64_t *>(base + L.bars);
-    uint64_t *r_full = bars, *h_full = bars + 1, *r_ready = bars + 3;
-    uint64_t *h_ready = bars + 4;                    // [2]: the tile buffer holds h_t of every CTA of the cluster
-    uint64_t *mma_done = bars + 6;                   // [3]: the rows of gate z / r / n are accumulated
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 9);
+    uint64_t *r_full = bars, *h_full = bars + 1, *r_ready = bars + 2;
+    uint64_t *h_ready = bars + 3;                    // [NG][2]: the tile buffer holds h_t of every CTA of the cluster
+    uint64_t *mma_done = bars + 3 + 2 * MAX_NG;      // [NG][3]: the rows of gate z / r / n are accumulated
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 + 5 * MAX_NG);
     int32_t *tables = reinterpret_cast<int32_t *>(base + L.tables);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int grp = blockIdx.x / a.P;
     const int p = (int)cluster_rank();               // == blockIdx.x % P: clusters are P consecutive CTAs
     const int j0 = p * 128 * MT;
-    const int b0 = a.b_off + grp * a.NB;
-    const int nb = min(a.NB, a.b_off + a.b_cnt - b0);
+    const int b0 = a.b_off + grp * NG * a.NB;        // first batch row of the cluster; sub-group g starts NB * g later
     const uint32_t tmem_cols = a.tmem_cols;
+    const uint32_t acc_cols_g = (uint32_t)(MT * 3 * a.NB);   // accumulator columns of one sub-group
 
     for (int i = tid; i < a.n_table; i += blockDim.x) tables[i] = a.tables[i];
     if (tid == 0) {
         tc::mbar_init(r_full, 1);
         tc::mbar_init(h_full, 1);
-        for (int g = 0; g < 3; ++g) tc::mbar_init(&mma_done[g], 1);
+        for (int g = 0; g < 3 * NG; ++g) tc::mbar_init(&mma_done[g], 1);
         // per phase: one arrival per epilogue warp, one by the control thread (which also announces
         // the bytes the peers send)
-        tc::mbar_init(&h_ready[0], 4 * EPW + 1);
-        tc::mbar_init(&h_ready[1], 4 * EPW + 1);
+        for (int g = 0; g < 2 * NG; ++g) tc::mbar_init(&h_ready[g], 4 * EPW + 1);
         tc::mbar_init(r_ready, EPI_THREADS);
         tc::fence_barrier_init();
         tc::tma_prefetch_desc(&map_r);
@@ -199,10 +210,12 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                 load_tiles(a.tmem_tiles, n_tiles - a.tmem_tiles);
                 ok = tc::mbar_wait(r_full, (uint32_t)(pass & 1), WAIT_BUDGET);
             }
-            // the initial state (written by the preceding kernel) into buffer 0
-            tc::mbar_expect_tx(h_full, h_buf_bytes);
-            for (int kb = 0; kb < KBn; ++kb)
-                tc::tma_load_2d(h_tile + (size_t)kb * a.NB * 128, &map_h, h_full, kb * 128, b0);
+            // the initial state (written by the preceding kernel) into buffer 0 of every sub-group
+            tc::mbar_expect_tx(h_full, (uint32_t)NG * h_buf_bytes);
+            for (int g = 0; g < NG; ++g)
+                for (int kb = 0; kb < KBn; ++kb)
+                    tc::tma_load_2d(h_tile + (size_t)(2 * g) * h_buf_bytes + (size_t)kb * a.NB * 128, &map_h, h_full,
+                                    kb * 128, b0 + g * a.NB);
             ok = ok && tc::mbar_wait(h_full, 0, WAIT_BUDGET);
             idesc = tc::idesc_i8(128, a.NB, true, !a.h_unsigned);
             r_lo0 = (tc::smem_u32(r_tiles) & 0x3FFFFu) >> 4;
@@ -214,74 +227,78 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
         if (lane == 0) {
             const uint32_t blk_bytes = (uint32_t)(a.NB * 128);           // one K-slab of the tile
             for (int s = 0; s < a.T && ok; ++s) {
-                const uint32_t buf_off = (uint32_t)(s & 1) * h_buf_bytes;
-                if (s > 0) {
-                    // h_s in buffer s & 1: the 16 warps of this CTA have stored their words and the
-                    // (P-1) * NB * 128 bytes of the peers have landed
-                    tc::mbar_expect_tx(&h_ready[s & 1], (uint32_t)(a.P - 1) * blk_bytes);
-                    if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 0] = clock64();
-                    if (!tc::mbar_wait(&h_ready[s & 1], (uint32_t)(((s - 1) >> 1) & 1), WAIT_BUDGET)) { ok = false; break; }
-                    fence_proxy_async_cta();   // the MMAs read these stores through the async proxy
-                }
-                if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 1] = clock64();
-                tc::tc_fence_after_sync();
-                const uint32_t hbuf = h_lo0 + (buf_off >> 4);
-                // Gate by gate, with a commit after each: the epilogue starts on the update gate while
-                // the reset and new gates are still being multiplied.  The epilogue warps that share
-                // this warp's scheduler are busy by then, so every operand is prepared up front and
-                // the loops are fully unrolled: one independent add per MMA, no dependent chain.
-                const uint64_t dhi = (uint64_t)desc_hi << 32;
-                const uint32_t r_t0 = tmem_base + (uint32_t)a.r_tmem_col;
-                if (KBn <= 4 && (a.tmem_tiles == 0 || a.tmem_tiles == MT * 3 * KBn)) {
-                    // the common shapes (H <= 512, R in one place): every operand prepared up front,
-                    // one independent add per MMA - the issuing thread's instruction stream sets the pace
-                    uint32_t bdl[4][4];   // low descriptor words of the state tile: K-slab kb, 32-byte step ks
+                for (int g = 0; g < NG; ++g) {
+                    const uint32_t buf = (uint32_t)(2 * g + (s & 1));
+                    if (s > 0) {
+                        // h_s in buffer s & 1: the 16 warps of this CTA have stored their words and the
+                        // (P-1) * NB * 128 bytes of the peers have landed
+                        tc::mbar_expect_tx(&h_ready[buf], (uint32_t)(a.P - 1) * blk_bytes);
+                        if (!tc::mbar_wait(&h_ready[buf], (uint32_t)(((s - 1) >> 1) & 1), WAIT_BUDGET)) { ok = false; break; }
+                        fence_proxy_async_cta();   // the MMAs read these stores through the async proxy
+                    }
+                    tc::tc_fence_after_sync();
+                    uint64_t *md = &mma_done[3 * g];
+                    if constexpr (Floor) {
+                        for (int k = 0; k < 3; ++k) tc::mma_commit(&md[k]);
+                        continue;
+                    }
+                    const uint32_t hbuf = h_lo0 + ((buf * h_buf_bytes) >> 4);
+                    const uint32_t acc0 = tmem_base + (uint32_t)g * acc_cols_g;
+                    // Gate by gate, with a commit after each: the epilogue starts on the update gate while
+                    // the reset and new gates are still being multiplied.  The epilogue warps that share
+                    // this warp's scheduler are busy by then, so every operand is prepared up front and
+                    // the loops are fully unrolled: one independent add per MMA, no dependent chain.
+                    const uint64_t dhi = (uint64_t)desc_hi << 32;
+                    const uint32_t r_t0 = tmem_base + (uint32_t)a.r_tmem_col;
+                    if (KBn <= 4 && (a.tmem_tiles == 0 || a.tmem_tiles == MT * 3 * KBn)) {
+                        // the common shapes (H <= 512, R in one place): every operand prepared up front,
+                        // one independent add per MMA - the issuing thread's instruction stream sets the pace
+                        uint32_t bdl[4][4];   // low descriptor words of the state tile: K-slab kb, 32-byte step ks
 #pragma unroll
-                    for (int kb = 0; kb < 4; ++kb)
+                        for (int kb = 0; kb < 4; ++kb)
 #pragma unroll
-                        for (int ks = 0; ks < 4; ++ks) bdl[kb][ks] = desc_lo | (hbuf + (uint32_t)(kb * a.NB * 8 + 2 * ks));
-                    if (a.tmem_tiles > 0) {   // A operand from tensor memory
+                            for (int ks = 0; ks < 4; ++ks) bdl[kb][ks] = desc_lo | (hbuf + (uint32_t)(kb * a.NB * 8 + 2 * ks));
+                        if (a.tmem_tiles > 0) {   // A operand from tensor memory
 #pragma unroll
-                        for (int g = 0; g < 3; ++g) {
+                            for (int gate = 0; gate < 3; ++gate) {
 #pragma unroll
-                            for (int mt = 0; mt < MT; ++mt) {
-                                const uint32_t d = tmem_base + (uint32_t)((mt * 3 + g) * a.NB);
-                                const uint32_t ra = r_t0 + (uint32_t)((mt * 3 + g) * KBn * 32);
+                                for (int mt = 0; mt < MT; ++mt) {
+                                    const uint32_t d = acc0 + (uint32_t)((mt * 3 + gate) * a.NB);
+                                    const uint32_t ra = r_t0 + (uint32_t)((mt * 3 + gate) * KBn * 32);
 #pragma unroll
-                                for (int kb = 0; kb < 4; ++kb)
-                                    if (kb < KBn) {
+                                    for (int kb = 0; kb < 4; ++kb)
+                                        if (kb < KBn) {
 #pragma unroll
-                                        for (int ks = 0; ks < 4; ++ks)
-                                            tc::mma_i8_ts(d, ra + (uint32_t)(kb * 32 + ks * 8), dhi | bdl[kb][ks], idesc,
-                                                          (kb | ks) != 0);
-                                    }
+                                            for (int ks = 0; ks < 4; ++ks)
+                                                tc::mma_i8_ts(d, ra + (uint32_t)(kb * 32 + ks * 8), dhi | bdl[kb][ks], idesc,
+                                                              (kb | ks) != 0);
+                                        }
+                                }
+                                tc::mma_commit(&md[gate]);
                             }
-                            tc::mma_commit(&mma_done[g]);
+                        } else {
+#pragma unroll
+                            for (int gate = 0; gate < 3; ++gate) {
+#pragma unroll
+                                for (int mt = 0; mt < MT; ++mt) {
+                                    const uint32_t d = acc0 + (uint32_t)((mt * 3 + gate) * a.NB);
+                                    const uint32_t rb = desc_lo | (r_lo0 + (uint32_t)((mt * 3 + gate) * KBn * 1024));
+#pragma unroll
+                                    for (int kb = 0; kb < 4; ++kb)
+                                        if (kb < KBn) {
+#pragma unroll
+                                            for (int ks = 0; ks < 4; ++ks)
+                                                tc::mma_i8(d, dhi | (rb + (uint32_t)(kb * 1024 + 2 * ks)), dhi | bdl[kb][ks], idesc,
+                                                           (kb | ks) != 0);
+                                        }
+                                }
+                                tc::mma_commit(&md[gate]);
+                            }
                         }
                     } else {
-#pragma unroll
-                        for (int g = 0; g < 3; ++g) {
-#pragma unroll
-                            for (int mt = 0; mt < MT; ++mt) {
-                                const uint32_t d = tmem_base + (uint32_t)((mt * 3 + g) * a.NB);
-                                const uint32_t rb = desc_lo | (r_lo0 + (uint32_t)((mt * 3 + g) * KBn * 1024));
-#pragma unroll
-                                for (int kb = 0; kb < 4; ++kb)
-                                    if (kb < KBn) {
-#pragma unroll
-                                        for (int ks = 0; ks < 4; ++ks)
-                                            tc::mma_i8(d, dhi | (rb + (uint32_t)(kb * 1024 + 2 * ks)), dhi | bdl[kb][ks], idesc,
-                                                       (kb | ks) != 0);
-                                    }
-                            }
-                            tc::mma_commit(&mma_done[g]);
-                        }
+                        issue_wide(MT, KBn, a.NB, a.tmem_tiles, acc0, r_t0, r_lo0, desc_lo | hbuf, desc_lo, dhi, idesc, md);
                     }
-                } else {
-                    issue_wide(MT, KBn, a.NB, a.tmem_tiles, tmem_base, r_t0, r_lo0, desc_lo | hbuf, desc_lo, dhi, idesc,
-                               mma_done);
                 }
-                if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 3] = clock64();
             }
             if (!ok) atomicOr(a.abort_flag, 1);
         }
@@ -302,7 +319,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
         const int x_row = lane >> 3, x_word = lane & 7;
         const uint32_t x_sel = (uint32_t)x_row | ((uint32_t)(4 + x_row) << 4);
         const uint32_t tile_u32 = tc::smem_u32(h_tile);
-        const uint32_t bar0_u32 = tc::smem_u32(&h_ready[0]), bar1_u32 = tc::smem_u32(&h_ready[1]);
+        const uint32_t bar_u32 = tc::smem_u32(h_ready);
         int64_t corr[MT][3];
         Rescale rs[MT][3];
         FastLin fl[MT][3];
@@ -362,9 +379,12 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
         for (int s = 0; s < a.T; ++s) {
             const int t = a.reverse ? (a.T - 1 - s) : s;
             const long long out_slot = a.reverse ? (a.T - 1 - s) : (s + 1);
-            const unsigned char *h_cur = h_tile + (size_t)(s & 1) * h_buf_bytes;
             const uint32_t par = (uint32_t)(s & 1);
-            const bool stamp = a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0;
+            for (int g = 0; g < NG; ++g) {
+            const int bg0 = b0 + g * a.NB;                                   // first batch row of this sub-group
+            const int nb = max(0, min(a.NB, a.b_off + a.b_cnt - bg0));     // its rows that exist
+            const unsigned char *h_cur = h_tile + (size_t)(2 * g + (s & 1)) * h_buf_bytes;
+            uint64_t *md = &mma_done[3 * g];
             bool waited = false;
             int32_t hn_last[MT][CH];   // the warp's last chunk: its outputs go to global memory after the arrive
             int c_last = -1;
@@ -380,10 +400,10 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     for (int i = 0; i < CH; ++i) {
                         const int b = c0 + i;
                         const bool v_ok = b < nb && j_ok[mt];
-                        const size_t row = (size_t)t * a.B + b0 + b;
+                        const size_t row = (size_t)t * a.B + bg0 + b;
 #pragma unroll
-                        for (int g = 0; g < 3; ++g)
-                            ihv[mt][i][g] = v_ok ? (int32_t)ihp[row * a.C + g * a.H + j] : 0;
+                        for (int k = 0; k < 3; ++k)
+                            ihv[mt][i][k] = (v_ok && !Floor) ? (int32_t)ihp[row * a.C + k * a.H + j] : 0;
                         const uint8_t hb = v_ok ? h_cur[sw128_offset(b, j, a.NB)] : (uint8_t)0;
                         hold[mt][i] = state_byte(hb, h_bits);
                     }
@@ -394,15 +414,25 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                 // the dependency chains.  Inputs of absent rows/units are zeros and every table index
                 // is clamped, so every lane computes; only the stores are guarded.
                 int32_t hn[MT][CH];
-                const uint32_t ta0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
-                if constexpr (Fused && Narrow) {
+                const uint32_t ta0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)g * acc_cols_g + (uint32_t)c0;
+                if constexpr (Floor) {
+                    if (!waited) {
+                        ok = tc::mbar_wait(&md[2], par, WAIT_BUDGET);
+                        if (!ok) break;
+                        tc::tc_fence_after_sync();
+                        waited = true;
+                    }
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                        for (int i = 0; i < CH; ++i) hn[mt][i] = hold[mt][i];
+                } else if constexpr (Fused && Narrow) {
                     int32_t acc[MT][CH], zd[MT][CH], rd[MT][CH];
                     // update gate
                     if (!waited) {
-                        ok = tc::mbar_wait(&mma_done[0], par, WAIT_BUDGET);
+                        ok = tc::mbar_wait(&md[0], par, WAIT_BUDGET);
                         if (!ok) break;
                         tc::tc_fence_after_sync();
-                        if (stamp) a.dbg[s * 8 + 4] = clock64();
                     }
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 0) * a.NB), acc[mt]);
@@ -414,7 +444,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                             zd[mt][i] = fused_gate_fast(gc, tab, ACT_Z, ihv[mt][i][0], lin_round(acc[mt][i], fl[mt][0]));
                     // reset gate
                     if (!waited) {
-                        ok = tc::mbar_wait(&mma_done[1], par, WAIT_BUDGET);
+                        ok = tc::mbar_wait(&md[1], par, WAIT_BUDGET);
                         if (!ok) break;
                         tc::tc_fence_after_sync();
                     }
@@ -428,11 +458,10 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                             rd[mt][i] = fused_gate_fast(gc, tab, ACT_R, ihv[mt][i][1], lin_round(acc[mt][i], fl[mt][1]));
                     // new gate and the state update
                     if (!waited) {
-                        ok = tc::mbar_wait(&mma_done[2], par, WAIT_BUDGET);
+                        ok = tc::mbar_wait(&md[2], par, WAIT_BUDGET);
                         if (!ok) break;
                         tc::tc_fence_after_sync();
                         waited = true;
-                        if (stamp) a.dbg[s * 8 + 2] = clock64();
                     }
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 2) * a.NB), acc[mt]);
@@ -450,10 +479,9 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     int32_t acc[MT][CH];
                     float ug[MT][CH], rg[MT][CH];
                     if (!waited) {
-                        ok = tc::mbar_wait(&mma_done[0], par, WAIT_BUDGET);
+                        ok = tc::mbar_wait(&md[0], par, WAIT_BUDGET);
                         if (!ok) break;
                         tc::tc_fence_after_sync();
-                        if (stamp) a.dbg[s * 8 + 4] = clock64();
                     }
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 0) * a.NB), acc[mt]);
@@ -466,7 +494,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                                                             fs_linear(acc[mt][i], fsk[mt][0][0], fsk[mt][0][1], fsk[mt][0][2],
                                                                       a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi));
                     if (!waited) {
-                        ok = tc::mbar_wait(&mma_done[1], par, WAIT_BUDGET);
+                        ok = tc::mbar_wait(&md[1], par, WAIT_BUDGET);
                         if (!ok) break;
                         tc::tc_fence_after_sync();
                     }
@@ -481,11 +509,10 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                                                             fs_linear(acc[mt][i], fsk[mt][1][0], fsk[mt][1][1], fsk[mt][1][2],
                                                                       a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi));
                     if (!waited) {
-                        ok = tc::mbar_wait(&mma_done[2], par, WAIT_BUDGET);
+                        ok = tc::mbar_wait(&md[2], par, WAIT_BUDGET);
                         if (!ok) break;
                         tc::tc_fence_after_sync();
                         waited = true;
-                        if (stamp) a.dbg[s * 8 + 2] = clock64();
                     }
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 2) * a.NB), acc[mt]);
@@ -500,12 +527,11 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                                                            (float)hold[mt][i]);
                 } else {
                     if (!waited) {
-                        ok = tc::mbar_wait(&mma_done[0], par, WAIT_BUDGET) && tc::mbar_wait(&mma_done[1], par, WAIT_BUDGET) &&
-                             tc::mbar_wait(&mma_done[2], par, WAIT_BUDGET);
+                        ok = tc::mbar_wait(&md[0], par, WAIT_BUDGET) && tc::mbar_wait(&md[1], par, WAIT_BUDGET) &&
+                             tc::mbar_wait(&md[2], par, WAIT_BUDGET);
                         if (!ok) break;
                         tc::tc_fence_after_sync();
                         waited = true;
-                        if (stamp) a.dbg[s * 8 + 4] = a.dbg[s * 8 + 2] = clock64();
                     }
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
@@ -536,19 +562,14 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         }
                     }
                 }
-                if (stamp) {
-                    long long tck;   // reads the clock only once the cell values exist
-                    asm volatile("mov.u64 %0, %%clock64;" : "=l"(tck) : "r"(hn[0][0]), "r"(hn[MT - 1][CH - 1]), "r"(hn[0][1]), "r"(hn[0][2]) : "memory");
-                    a.dbg[s * 8 + 6] = tck;
-                }
                 // h_t[b][j] = element (row b, K index j) of the next B tile.  Pack the CH row bytes of
                 // this lane's unit, gather byte x_row of the four lanes 4 * x_word .. + 3, store the
                 // word into this CTA's tile and send it to every peer's.  Absent rows and units send
                 // their (clamped) values too: they land in padding rows, or multiply zero columns of
                 // R, and the peers count on the full number of bytes.
                 const bool last = c + EPW >= nchunks;
-                const int nx = (s + 1) & 1;
-                const uint32_t bar_nx = nx ? bar1_u32 : bar0_u32;
+                const uint32_t nbuf = (uint32_t)(2 * g + ((s + 1) & 1));
+                const uint32_t bar_nx = bar_u32 + 8u * nbuf;
                 // (nothing reads the state after the last step, and no store may be on its way to a
                 // peer when the kernel ends)
 #pragma unroll
@@ -560,7 +581,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     const uint32_t v2 = __shfl_sync(0xffffffffu, packed, 4 * x_word + 2);
                     const uint32_t v3 = __shfl_sync(0xffffffffu, packed, 4 * x_word + 3);
                     const uint32_t word = __byte_perm(__byte_perm(v0, v1, x_sel), __byte_perm(v2, v3, x_sel), 0x5410);
-                    const uint32_t at = tile_u32 + (uint32_t)nx * h_buf_bytes +
+                    const uint32_t at = tile_u32 + nbuf * h_buf_bytes +
                                         sw128_offset(c0 + x_row, j0 + mt * 128 + q * 32 + 4 * x_word, a.NB);
                     sts_u32(at, word);
                     for (int r = 0; r < a.P; ++r)
@@ -573,7 +594,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     for (int i = 0; i < CH; ++i) {
                         const int b = c0 + i;
                         if (!last && b < nb && j_ok[mt]) {
-                            const size_t o = (size_t)out_slot * BH + (size_t)(b0 + b) * a.H + j;
+                            const size_t o = (size_t)out_slot * BH + (size_t)(bg0 + b) * a.H + j;
                             if (a.hq_out) a.hq_out[o] = hn[mt][i];
                             if (a.hf_out) a.hf_out[o] = (float)(hn[mt][i] - gc.zp_h) * gc.h_scale;
                         }
@@ -585,17 +606,15 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
             if (ok && !waited) {
                 // A warp without a chunk still waits for this step's MMAs: it must not arrive twice
                 // within one phase of the tile barrier.
-                ok = tc::mbar_wait(&mma_done[2], par, WAIT_BUDGET);
+                ok = tc::mbar_wait(&md[2], par, WAIT_BUDGET);
                 tc::tc_fence_after_sync();
             }
-            if (stamp) a.dbg[s * 8 + 7] = clock64();
             // this warp's own words are ordered for the async proxy (the MMAs read them), then one
             // lane arrives for the warp on this CTA's barrier of the buffer just written
             fence_proxy_async_cta();
             tc::tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0 && s + 1 < a.T) tc::mbar_arrive(&h_ready[(s + 1) & 1]);
-            if (stamp) a.dbg[s * 8 + 5] = clock64();
+            if (lane == 0 && s + 1 < a.T) tc::mbar_arrive(&h_ready[2 * g + ((s + 1) & 1)]);
             // Outputs of the last chunk leave for global memory after the arrive: nothing in the next
             // step waits for them, so they overlap the exchange and the next MMAs.
             if (c_last >= 0) {
@@ -606,13 +625,14 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     for (int i = 0; i < CH; ++i) {
                         const int b = c_last * CH + i;
                         if (b < nb && j_ok[mt]) {
-                            const size_t o = (size_t)out_slot * BH + (size_t)(b0 + b) * a.H + j;
+                            const size_t o = (size_t)out_slot * BH + (size_t)(bg0 + b) * a.H + j;
                             if (a.hq_out) a.hq_out[o] = hn_last[mt][i];
                             if (a.hf_out) a.hf_out[o] = (float)(hn_last[mt][i] - gc.zp_h) * gc.h_scale;
                         }
                     }
                 }
             }
+            }   // sub-groups
         }
         if (!ok && lane == 0) atomicOr(a.abort_flag, 1);
     }
@@ -624,10 +644,10 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
     if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
 }
 
-template <typename IhT, bool Narrow, bool Fused, int MT>
+template <typename IhT, bool Narrow, bool Fused, int MT, bool Floor>
 cudaError_t launch_one(const CUtensorMap &mr, const CUtensorMap &mh, const GateConsts &gc, RecMmaArgs &a,
                        int grid, size_t smem, cudaStream_t st) {
-    auto kern = k_recurrence_cluster<IhT, Narrow, Fused, MT>;
+    auto kern = k_recurrence_cluster<IhT, Narrow, Fused, MT, Floor>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
@@ -648,13 +668,17 @@ cudaError_t launch_one(const CUtensorMap &mr, const CUtensorMap &mh, const GateC
 template <typename IhT, bool Narrow, bool Fused>
 cudaError_t launch_mt(int MT, const CUtensorMap &mr, const CUtensorMap &mh, const GateConsts &gc,
                       RecMmaArgs &a, int grid, size_t smem, cudaStream_t st) {
-    return MT == 2 ? launch_one<IhT, Narrow, Fused, 2>(mr, mh, gc, a, grid, smem, st)
-                   : launch_one<IhT, Narrow, Fused, 1>(mr, mh, gc, a, grid, smem, st);
+    return MT == 2 ? launch_one<IhT, Narrow, Fused, 2, false>(mr, mh, gc, a, grid, smem, st)
+                   : launch_one<IhT, Narrow, Fused, 1, false>(mr, mh, gc, a, grid, smem, st);
 }
 
-cudaError_t launch_any(bool fused, bool narrow, int ih_bytes, int MT, const CUtensorMap &mr,
+cudaError_t launch_any(bool fused, bool narrow, int ih_bytes, int MT, bool floor, const CUtensorMap &mr,
                        const CUtensorMap &mh, const GateConsts &gc, RecMmaArgs &a, int grid, size_t smem,
                        cudaStream_t st) {
+    if (floor)   // the synchronisation-floor measurement exists for the one form the benchmark's headline runs
+        return (fused && narrow && ih_bytes == 2 && MT == 1)
+                   ? launch_one<int16_t, true, true, 1, true>(mr, mh, gc, a, grid, smem, st)
+                   : cudaErrorNotSupported;
     if (fused && narrow)   // for the fused cell `narrow` carries "every scale is shift-free"
         return ih_bytes == 2 ? launch_mt<int16_t, true, true>(MT, mr, mh, gc, a, grid, smem, st)
                              : launch_mt<int32_t, true, true>(MT, mr, mh, gc, a, grid, smem, st);
@@ -671,7 +695,7 @@ cudaError_t launch_any(bool fused, bool narrow, int ih_bytes, int MT, const CUte
 }  // namespace
 
 bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, int r_where,
-                      int mt_opt, RecMmaPlan *out) {
+                      int mt_opt, int ng_opt, RecMmaPlan *out) {
     if (Hpad > 1024) return false;                 // K-slab loops are unrolled to 8
     const int KBn = Hpad / 128;
     // One 128-unit tile per CTA.  Two tiles per CTA for 128 < H <= 256 (one CTA per group, no
@@ -681,32 +705,39 @@ bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_tab
     const int P = (H + 128 * MT - 1) / (128 * MT);  // cluster size: 1..8 (the portable maximum)
     if (P > 8 || P > sms) return false;
     const int groups_max = std::max(1, sms / P);
-    int NB = ((B + groups_max - 1) / groups_max + 15) / 16 * 16;
-    const int nb_cap = MT == 2 ? 64 : 128;         // 3*MT*NB accumulator columns <= 512
+    // Rows per cluster, then sub-groups per CTA (ng_opt: 0 auto, 1, 2).  Two sub-groups let the MMAs
+    // of one overlap the cells of the other; taken where a cluster has at least 32 rows anyway.
+    int RC = ((B + groups_max - 1) / groups_max + 15) / 16 * 16;
+    int NG = ng_opt == 2 ? 2 : 1;
+    if (ng_opt == 0 && RC >= 32) NG = 2;
+    if (NG == 2) RC = std::max(RC, 32);
+    int NB = (RC / NG + 15) / 16 * 16;
+    const int nb_cap = (MT == 2 ? 64 : 128) / NG;  // 3 * MT * NB * NG accumulator columns <= 512
     NB = std::min(NB, nb_cap);
     const int n_tiles = MT * 3 * KBn;
     // Where the R slice lives: as many 128x128 tiles as fit beside the accumulators go to tensor
     // memory (32 columns each; r_where: 0 auto, 1 none, 2 at least one), the rest stays in
     // shared-memory slots; the slots also stage the tensor-memory tiles, up to 12 per pass.
     for (;; NB -= 16) {
-        const int acc_cols = (3 * MT * NB + 31) / 32 * 32;
+        const int acc_cols = (3 * MT * NB * NG + 31) / 32 * 32;
         int tmem_tiles = r_where == 1 ? 0 : std::max(0, std::min(n_tiles, (512 - acc_cols) / 32));
         // a slice that does not fit tensor memory as a whole but fits shared memory stays there as
         // a whole: the split form needs a slower, rolled MMA issue loop
         if (tmem_tiles < n_tiles && r_where != 2 &&
-            cluster_smem_layout(n_tiles, KBn, NB, n_table).total + 1024 <= (size_t)smem_optin)
+            cluster_smem_layout(n_tiles, KBn, NB, NG, n_table).total + 1024 <= (size_t)smem_optin)
             tmem_tiles = 0;
         const int resident = n_tiles - tmem_tiles;
         for (int stage = std::min(std::max(tmem_tiles, 1), 12); stage >= 1; --stage) {
             const int r_slots = std::max(resident, stage);
-            const size_t smem = cluster_smem_layout(r_slots, KBn, NB, n_table).total + 1024;
+            const size_t smem = cluster_smem_layout(r_slots, KBn, NB, NG, n_table).total + 1024;
             if (smem > (size_t)smem_optin || (r_where == 2 && tmem_tiles == 0)) continue;
             uint32_t cols = 32;
             while ((int)cols < acc_cols + tmem_tiles * 32) cols <<= 1;
             out->MT = MT;
             out->P = P;
             out->NB = NB;
-            out->G = (B + NB - 1) / NB;
+            out->NG = NG;
+            out->G = (B + NB * NG - 1) / (NB * NG);
             out->smem = smem;
             out->tmem_cols = (int)cols;
             out->r_tmem_col = tmem_tiles > 0 ? acc_cols : 0;
@@ -721,7 +752,7 @@ bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_tab
 
 int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const GateConsts &gc_host,
                        const int8_t *r8, long long r_rows_alloc, long long h_rows_alloc, bool h_unsigned,
-                       int ih_bytes, bool narrow, bool fused, cudaStream_t stream, std::string *err) {
+                       int ih_bytes, bool narrow, bool fused, bool floor, cudaStream_t stream, std::string *err) {
     if (!s.valid || s.r8 != r8 || s.h8 != a.h8 || s.r_rows != r_rows_alloc || s.h_rows != h_rows_alloc ||
         s.Hpad != a.Hpad || s.NB != pl.NB) {
         if (!make_map_u8_sw128(reinterpret_cast<CUtensorMap *>(s.map_r), r8, (uint64_t)r_rows_alloc, (uint64_t)a.Hpad, 128) ||
@@ -741,6 +772,7 @@ int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const
     const CUtensorMap &mh = *reinterpret_cast<const CUtensorMap *>(s.map_h);
     a.P = pl.P;
     a.NB = pl.NB;
+    a.NG = pl.NG;
     a.h_unsigned = h_unsigned ? 1 : 0;
     a.tmem_cols = (uint32_t)pl.tmem_cols;
     a.r_tmem_col = pl.r_tmem_col;
@@ -748,7 +780,11 @@ int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const
     a.r_slots = pl.r_slots;
     a.b_off = 0;
     a.b_cnt = a.B;
-    const cudaError_t e = launch_any(fused, narrow, ih_bytes, pl.MT, mr, mh, gc_host, a, pl.G * pl.P, pl.smem, stream);
+    const cudaError_t e = launch_any(fused, narrow, ih_bytes, pl.MT, floor, mr, mh, gc_host, a, pl.G * pl.P, pl.smem, stream);
+    if (e == cudaErrorNotSupported && floor) {
+        if (err) *err = "the synchronisation-floor probe exists for the fused shift-free cell with 16-bit W*x+bw only";
+        return QGRU_ERR_UNSUPPORTED;
+    }
     if (e != cudaSuccess) {
         if (err) *err = std::string("recurrence (cluster) launch: ") + cudaGetErrorString(e);
         cudaGetLastError();

@@ -118,7 +118,6 @@ k_recurrence_mma(const __grid_constant__ CUtensorMap map_r, const __grid_constan
                     // every epilogue thread of this CTA has stored its h_s values and fenced them
                     if (!tc::mbar_wait(h_written, (uint32_t)((s - 1) & 1), WAIT_BUDGET)) { ok = false; break; }
                     tc::tc_fence_after_sync();
-                    if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 0] = clock64();
                     if (a.P > 1) {
                         __threadfence();
                         atomicAdd(bar, 1u);
@@ -133,7 +132,6 @@ k_recurrence_mma(const __grid_constant__ CUtensorMap map_r, const __grid_constan
                         if (!ok) break;
                     }
                     fence_proxy_async_all();
-                    if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 1] = clock64();
                 }
                 // h_s rows of this group: KBn boxes of [NB rows x 128 bytes]
                 tc::mbar_expect_tx(h_full, h_bytes);
@@ -142,7 +140,6 @@ k_recurrence_mma(const __grid_constant__ CUtensorMap map_r, const __grid_constan
                     tc::tma_load_2d(h_tile + (size_t)kb * a.NB * 128, &map_h, h_full, kb * 128, row);
                 if (!tc::mbar_wait(h_full, (uint32_t)(s & 1), WAIT_BUDGET)) { ok = false; break; }
                 tc::tc_fence_after_sync();
-                if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 2] = clock64();
                 // Descriptors differ only in their 14-bit start-address field (bytes >> 4): the
                 // high word and the LBO field are constants, so each MMA costs two adds.
                 for (int mt = 0; mt < MT; ++mt)
@@ -160,7 +157,6 @@ k_recurrence_mma(const __grid_constant__ CUtensorMap map_r, const __grid_constan
                         }
                     }
                 tc::mma_commit(mma_done);
-                if (a.dbg && blockIdx.x == 0) a.dbg[s * 8 + 3] = clock64();
             }
             if (!ok) {
                 atomicExch(failed, 1);
@@ -220,7 +216,6 @@ k_recurrence_mma(const __grid_constant__ CUtensorMap map_r, const __grid_constan
                     if (!ok) break;
                     tc::tc_fence_after_sync();
                     waited = true;
-                    if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0) a.dbg[s * 8 + 4] = clock64();
                 }
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
@@ -231,7 +226,6 @@ k_recurrence_mma(const __grid_constant__ CUtensorMap map_r, const __grid_constan
                     tc::tmem_ld4(ta + a.NB, ar);
                     tc::tmem_ld4(ta + 2 * a.NB, an);
                     tc::tmem_ld_wait();
-                    if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0 && mt == 0) a.dbg[s * 8 + 6] = clock64();
 #pragma unroll
                     for (int i = 0; i < CH; ++i) {
                         const int b = c0 + i;
@@ -269,11 +263,9 @@ k_recurrence_mma(const __grid_constant__ CUtensorMap map_r, const __grid_constan
             // publish h_{s+1}: order the generic-proxy stores before the async-proxy (TMA) reads.
             // The gpu-scope fence that makes them visible to the other CTAs of the group is
             // executed once, by the control thread, after it has observed every arrival below.
-            if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0) a.dbg[s * 8 + 7] = clock64();
             fence_proxy_async_all();
             tc::tc_fence_before_sync();
             tc::mbar_arrive(h_written);
-            if (a.dbg && blockIdx.x == 0 && warp == 1 && lane == 0) a.dbg[s * 8 + 5] = clock64();
         }
         if (!ok && lane == 0) {
             atomicExch(failed, 1);

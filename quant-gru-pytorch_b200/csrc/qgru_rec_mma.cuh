@@ -15,6 +15,7 @@ struct RecMmaArgs {
     int T, B, H, Hpad, C;
     int P;            // CTAs per group (slices of the hidden dimension); set by the launcher
     int NB;           // batch rows per group (multiple of 16); set by the launcher
+    int NG = 1;       // cluster kernel: independent sub-groups of NB rows per CTA
     int b_off, b_cnt; // batch rows [b_off, b_off + b_cnt) are handled by this launch
     int reverse;
     int h_unsigned;   // the state h is stored as uint8 (else int8)
@@ -32,7 +33,6 @@ struct RecMmaArgs {
     unsigned *bar;          // one counter per group, 32 words apart, zeroed before the launch
     int *abort_flag;
     unsigned spin_limit;
-    long long *dbg;         // optional [T][8] clock stamps of CTA 0 (profiling aid), else null
     // float-storage forward (cluster kernel, generic-cell instantiation only): the float cell of
     // the reference's quantGRUForwardFP instead of the integer one
     int fs_on = 0;
@@ -41,7 +41,7 @@ struct RecMmaArgs {
 };
 
 struct RecMmaPlan {
-    int MT = 1, P = 1, NB = 16, G = 1, tmem_cols = 32, groups_per_launch = 1;
+    int MT = 1, P = 1, NB = 16, NG = 1, G = 1, tmem_cols = 32, groups_per_launch = 1;
     int r_tmem_col = 0, tmem_tiles = 0, r_slots = 0;
     size_t smem = 0;
 };
@@ -68,10 +68,10 @@ int rec_mma_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const Gat
 // The same kernel with the P CTAs of a group as one thread-block cluster exchanging h_t through
 // distributed shared memory (qgru_rec_cluster.cu).  Same plan fields; no cooperative launch.
 bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, int r_where,
-                      int mt_opt, RecMmaPlan *out);
+                      int mt_opt, int ng_opt, RecMmaPlan *out);
 
 int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const GateConsts &gc_host,
                        const int8_t *r8, long long r_rows_alloc, long long h_rows_alloc, bool h_unsigned,
-                       int ih_bytes, bool narrow, bool fused, cudaStream_t stream, std::string *err);
+                       int ih_bytes, bool narrow, bool fused, bool floor, cudaStream_t stream, std::string *err);
 
 }  // namespace qgru

@@ -113,6 +113,54 @@ def test_two_tiles_per_cta_option(oracle, cuda_device):
     assert "MT=1" in plan and "P=2" in plan and np.array_equal(got, _want(oracle, case)), plan
 
 
+@pytest.mark.parametrize("shape", [(9, 40, 64, 512), (7, 33, 40, 300), (6, 70, 24, 128), (5, 100, 32, 640),
+                                   (12, 5, 16, 256), (4, 200, 48, 384)])
+@pytest.mark.parametrize("cfg", ["default", "cfg2", "gate_in16"])
+def test_two_subgroups_per_cta(oracle, cuda_device, shape, cfg):
+    """Two independent batch sub-groups per CTA (their MMAs and cells overlap): same bits as one,
+    with ragged last sub-groups, one or several CTAs per cluster, R in tensor or shared memory,
+    the fused, the generic and the segment-search cell, both directions."""
+    T, B, I, H = shape
+    case = make_case(17, T, B, I, H, oracle, config_named(cfg), with_h0=True)
+    want = _want(oracle, case)
+    for extra in ((), (("r_resident", "smem"),), (("cell", "generic"),)):
+        if extra == (("r_resident", "smem"),) and H > 512:
+            continue
+        got, plan, _ = _run(case, cuda_device, opts=(("rec", "mma"), ("exchange", "cluster"), ("subgroups", "2")) + extra)
+        assert "NG=2" in plan and "exchange=cluster_dsmem" in plan, plan
+        assert np.array_equal(got, want), plan
+    got, plan, _ = _run(case, cuda_device, opts=(("rec", "mma"), ("exchange", "cluster"), ("subgroups", "1")))
+    assert "NG=1" in plan and np.array_equal(got, want), plan
+    rev, plan, _ = _run(case, cuda_device, reverse=True, opts=(("rec", "mma"), ("subgroups", "2")))
+    import copy
+    flipped = copy.copy(case)
+    flipped.x_q = np.ascontiguousarray(case.x_q[::-1])
+    assert np.array_equal(rev, _want(oracle, flipped)[::-1]), plan
+
+
+def test_sync_floor_probe_runs(oracle, cuda_device):
+    """The synchronisation-floor probe (cluster recurrence without MMAs and cells) launches, ends
+    and leaves the handle usable: the next forward is bit-exact again."""
+    import torch
+    case = make_case(18, 20, 40, 64, 512, oracle, config_named("cfg2"))
+    dev = cuda_device
+    with gru_ops.Handle(case.I, case.H, device=dev.index or 0) as hd:
+        hd.set_params(case.params)
+        hd.set_weights_i32(*[_t(a, dev) for a in case.wq])
+        x = _t(case.x_q, dev)
+        want = _want(oracle, case)
+        assert np.array_equal(hd.forward_i32(x).cpu().numpy(), want)
+        hd.set_option("probe_floor", 1)
+        hd.forward_i32(x)
+        assert "FLOOR PROBE" in hd.describe_plan()
+        t_floor = hd.last_timing()
+        hd.set_option("probe_floor", 0)
+        assert np.array_equal(hd.forward_i32(x).cpu().numpy(), want)
+        t_real = hd.last_timing()
+        assert 0 < t_floor["recurrence_ms"] < t_real["recurrence_ms"] * 1.5
+    torch.cuda.synchronize()
+
+
 def test_large_batch_many_groups(oracle, cuda_device):
     """More batch rows than one wave of groups holds at H = 512: consecutive launches."""
     case = make_case(14, 3, 700, 32, 384, oracle, config_named("default"), calib_batches=1)
