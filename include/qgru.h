@@ -383,6 +383,8 @@ QGRU_API int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int accu
  *   "tiles_per_cta" 1 | 2                 cluster recurrence at 128 < H <= 256: 128-unit tiles per CTA
  *   "subgroups" auto | 1 | 2              cluster recurrence: independent batch sub-groups per CTA (with 2,
  *                                         the MMAs of one overlap the cells of the other)
+ *   "unit_tile" auto | 64 | 128           cluster recurrence: hidden units per CTA (64: the low-latency form,
+ *                                         taken by auto where a cluster is left with at most 64 batch rows)
  *   "probe_floor" 0 | 1                   measurement aid: the cluster recurrence runs with its MMAs and
  *                                         cells left out (results are meaningless); the recurrence time of
  *                                         qgru_last_timing is then the per-step synchronisation floor

@@ -10,7 +10,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
 _CSRC = os.path.join(_HERE, "csrc")
 _OBJ = os.path.join(_HERE, "build")
-SOURCES = ["qgru_api.cu", "qgru_gemm_tc.cu", "qgru_rec_mma.cu", "qgru_rec_cluster.cu", "qgru_float.cu",
+SOURCES = ["qgru_api.cu", "qgru_gemm_tc.cu", "qgru_rec_mma.cu", "qgru_rec_cluster.cu", "qgru_rec_c64.cu", "qgru_float.cu",
            "qgru_hist.cu", "qgru_backward.cu", "qgru_probe.cu", "qgru_host.cc"]
 OUT = os.path.join(_HERE, "libqgru_b200.so")
 

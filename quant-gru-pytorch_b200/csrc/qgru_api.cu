@@ -184,6 +184,15 @@ int qgru_set_option(qgru_handle *h, const char *name, const char *value) {
         else if (v == "1") h->opt_ng = 1;
         else if (v == "2") h->opt_ng = 2;
         else return fail(h, QGRU_ERR_BAD_ARG, "subgroups: auto|1|2");
+    } else if (n == "unit_tile") {
+        if (v == "auto") h->opt_ut = 0;
+        else if (v == "64") h->opt_ut = 64;
+        else if (v == "128") h->opt_ut = 128;
+        else return fail(h, QGRU_ERR_BAD_ARG, "unit_tile: auto|64|128");
+#ifdef QGRU_STAMPS
+    } else if (n == "debug_stamps") {
+        h->dbg_stamps = reinterpret_cast<long long *>(strtoull(value, nullptr, 10));
+#endif
     } else if (n == "probe_floor") {
         h->opt_floor = atoi(value) != 0;
     } else if (n == "sm_limit") {
@@ -468,6 +477,7 @@ int finish_weights(qgru_handle *h, cudaStream_t st) {
     h->tc.valid = false;
     h->rec.valid = false;
     h->rec_cl.valid = false;
+    h->rec_c64.valid = false;
     h->weights_set = true;
     h->fs_ready = false;
     return QGRU_OK;
@@ -635,6 +645,16 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
                             h->gc_host.rh_to_n.mq != 0 && h->gc_host.uh_to_h.mq != 0;
     const bool fused = (use_mma || gemv_fused) && h->gc_host.fused_ok && h->opt_gemm != 1 && h->opt_cell != 1;
     const int ih_bytes = fused ? h->gc_host.ih_pre_bytes : h->ih_bytes;
+    // The 64-units-per-CTA form of the cluster recurrence: only the branch-free tabulated cell, and
+    // (unless asked for) only where a cluster is left with few batch rows - the latency-bound regime.
+    const bool fast_cell_ok = fused && use_cluster && h->opt_cell != 2 && h->lin_fits32[1] && h->rs_fast[1] &&
+                              h->gc_host.rh_to_n.mq != 0 && h->gc_host.uh_to_h.mq != 0;
+    RecMmaPlan c64;
+    const bool use_c64 = fast_cell_ok && h->opt_ut != 128 && h->opt_ng != 1 && !h->opt_floor && h->opt_r_where != 1 &&
+                         rec_c64_plan(h->H, h->Hpad, B, sms, h->smem_optin, h->gc_host.ft_ih_off, h->opt_ut == 64, &c64);
+    if (h->opt_ut == 64 && use_mma && !use_c64)
+        return fail(h, QGRU_ERR_UNSUPPORTED, "unit_tile=64 needs the fused shift-free cell, H <= 512 and at most 96 rows per cluster");
+    if (use_c64) mp = c64;
     PreScale ps{};
     if (fused) {
         ps.enabled = 1;
@@ -707,11 +727,17 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
         a.bar = h->d_bar;
         a.abort_flag = h->d_flags + 1;
         a.spin_limit = h->spin_limit;
-        const unsigned long long before = h->rec.launches + h->rec_cl.launches;
+#ifdef QGRU_STAMPS
+        a.dbg = h->dbg_stamps;
+#endif
+        const unsigned long long before = h->rec.launches + h->rec_cl.launches + h->rec_c64.launches;
         // the branch-free fused cell: every scale of the step in shift-free form, 32-bit sums
         const bool fast_cell = fused && use_cluster && h->opt_cell != 2 && a.lc.fits32 && h->rs_fast[1] &&
                                h->gc_host.rh_to_n.mq != 0 && h->gc_host.uh_to_h.mq != 0;
-        if (use_cluster)
+        if (use_c64)
+            rc = rec_c64_launch(h->rec_c64, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256, h->h_uns,
+                                ih_bytes, st, &h->err);
+        else if (use_cluster)
             rc = rec_cluster_launch(h->rec_cl, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256,
                                     h->h_uns, ih_bytes, fused ? fast_cell : h->gc_host.narrow != 0, fused, h->opt_floor, st,
                                     &h->err);
@@ -719,10 +745,10 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
             rc = rec_mma_launch(h->rec, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256,
                                 h->h_uns, ih_bytes, h->gc_host.narrow != 0, fused, h->coop != 0, st, &h->err);
         if (rc) return rc;
-        h->launches += h->rec.launches + h->rec_cl.launches - before;
-        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 exchange=%s cell=%s%s MT=%d NB=%d NG=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d r_in=%s narrow=%d ih_bytes=%d shiftfree=%d%d%d%d",
-                 used_tc ? "tcgen05_i8" : "simt_dp4a", use_cluster ? "cluster_dsmem" : "global", fast_cell ? "fused_shiftfree" : fused ? "fused" : "generic", (use_cluster && h->opt_floor) ? "(FLOOR PROBE: no MMAs, no cell)" : "", mp.MT, mp.NB, mp.NG, mp.P, mp.G,
-                 mp.groups_per_launch, mp.smem, mp.tmem_cols, !use_cluster || mp.tmem_tiles == 0 ? "smem" : (mp.tmem_tiles == mp.MT * 3 * (h->Hpad / 128) ? "tmem" : "tmem+smem"),
+        h->launches += h->rec.launches + h->rec_cl.launches + h->rec_c64.launches - before;
+        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 exchange=%s cell=%s%s UT=%d MT=%d NB=%d NG=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d r_in=%s narrow=%d ih_bytes=%d shiftfree=%d%d%d%d",
+                 used_tc ? "tcgen05_i8" : "simt_dp4a", use_cluster ? "cluster_dsmem" : "global", fast_cell ? "fused_shiftfree" : fused ? "fused" : "generic", (use_cluster && h->opt_floor) ? "(FLOOR PROBE: no MMAs, no cell)" : "", use_c64 ? 64 : 128, mp.MT, mp.NB, mp.NG, mp.P, mp.G,
+                 mp.groups_per_launch, mp.smem, mp.tmem_cols, !use_cluster || mp.tmem_tiles == 0 ? "smem" : ((use_c64 || mp.tmem_tiles == mp.MT * 3 * (h->Hpad / 128)) ? "tmem" : "tmem+smem"),
                  h->gc_host.narrow, ih_bytes, (int)a.lc.fits32,
                  (int)h->rs_fast[1], h->gc_host.rh_to_n.mq != 0, h->gc_host.uh_to_h.mq != 0);
     } else {

@@ -44,6 +44,10 @@ struct qgru_handle {
     int opt_r_where = 0;                     // cluster recurrence: 0 auto, 1 R in shared memory, 2 in tensor memory
     unsigned spin_limit = 1u << 24;
     int opt_ng = 0;                          // cluster recurrence: sub-groups per CTA (0 auto, 1, 2)
+    int opt_ut = 0;                          // cluster recurrence: hidden units per CTA (0 auto, 64, 128)
+#ifdef QGRU_STAMPS
+    long long *dbg_stamps = nullptr;
+#endif
     bool opt_floor = false;                  // cluster recurrence: run the synchronisation-floor probe instead
     // device state that lives with the handle
     GateConsts *d_gc = nullptr;
@@ -82,6 +86,7 @@ struct qgru_handle {
     TcGemmState tc;
     qgru::RecMmaState rec;       // tensor maps of the global-exchange recurrence
     qgru::RecMmaState rec_cl;    // tensor maps of the cluster-exchange recurrence
+    qgru::RecMmaState rec_c64;   // tensor maps of its 64-units-per-CTA form
 };
 
 #define CK(call)                                                                          \

@@ -26,11 +26,19 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include "qgru_cluster.cuh"
 #include "qgru_device.cuh"
 #include "qgru_rec_mma.cuh"
 #include "qgru_tc.cuh"
 
+#ifdef QGRU_STAMPS
+#define STAMP(cond, slot) do { if (a.dbg && blockIdx.x == 0 && (cond)) a.dbg[((size_t)s * 2 + g) * 8 + (slot)] = clock64(); } while (0)
+#else
+#define STAMP(cond, slot) do { } while (0)
+#endif
+
 namespace qgru {
+using namespace clu;
 namespace {
 
 constexpr long long WAIT_BUDGET = 2000000000ll;  // ~1 s of SM clocks
@@ -38,39 +46,6 @@ constexpr int EPW = 4;                           // epilogue warps per TMEM lane
 constexpr int EPI_THREADS = 32 * 4 * EPW;
 constexpr int REC_THREADS = 32 + EPI_THREADS;
 constexpr int CH = 4;                            // batch columns per chunk
-
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// address of the same shared-memory location in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-    return r;
-}
-// 32-bit store into a peer CTA's shared memory that counts its 4 bytes on the peer's mbarrier when
-// it lands: no fence and no acknowledgement on the sending side
-__device__ __forceinline__ void st_async_u32(uint32_t peer_addr, uint32_t v, uint32_t peer_bar) {
-    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(peer_addr),
-                 "r"(v), "r"(peer_bar)
-                 : "memory");
-}
-__device__ __forceinline__ void sts_u32(uint32_t addr, uint32_t v) {
-    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async_cta() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-// Byte offset of element (row b, byte k) inside a K-major tile of `rows` rows stored as 128-byte
-// rows with the 128-byte swizzle: slabs of 128 K-bytes follow each other; inside a slab, groups
-// of 8 rows take 1024 bytes and the 16-byte chunk index is XORed with the row index modulo 8.
-__device__ __forceinline__ uint32_t sw128_offset(int b, int k, int rows) {
-    return (uint32_t)((k >> 7) * rows * 128 + (b >> 3) * 1024 + (b & 7) * 128 +
-                      ((((k & 127) >> 4) ^ (b & 7)) << 4) + (k & 15));
-}
 
 }  // namespace
 
@@ -237,6 +212,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         fence_proxy_async_cta();   // the MMAs read these stores through the async proxy
                     }
                     tc::tc_fence_after_sync();
+                    STAMP(true, 0);
                     uint64_t *md = &mma_done[3 * g];
                     if constexpr (Floor) {
                         for (int k = 0; k < 3; ++k) tc::mma_commit(&md[k]);
@@ -298,6 +274,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     } else {
                         issue_wide(MT, KBn, a.NB, a.tmem_tiles, acc0, r_t0, r_lo0, desc_lo | hbuf, desc_lo, dhi, idesc, md);
                     }
+                    STAMP(true, 1);
                 }
             }
             if (!ok) atomicOr(a.abort_flag, 1);
@@ -433,6 +410,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         ok = tc::mbar_wait(&md[0], par, WAIT_BUDGET);
                         if (!ok) break;
                         tc::tc_fence_after_sync();
+                        STAMP(warp == 1 && lane == 0, 2);
                     }
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 0) * a.NB), acc[mt]);
@@ -614,6 +592,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
             fence_proxy_async_cta();
             tc::tc_fence_before_sync();
             __syncwarp();
+            STAMP(warp == 1 && lane == 0, 4);
             if (lane == 0 && s + 1 < a.T) tc::mbar_arrive(&h_ready[2 * g + ((s + 1) & 1)]);
             // Outputs of the last chunk leave for global memory after the arrive: nothing in the next
             // step waits for them, so they overlap the exchange and the next MMAs.

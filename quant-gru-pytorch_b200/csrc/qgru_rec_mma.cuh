@@ -33,6 +33,9 @@ struct RecMmaArgs {
     unsigned *bar;          // one counter per group, 32 words apart, zeroed before the launch
     int *abort_flag;
     unsigned spin_limit;
+#ifdef QGRU_STAMPS
+    long long *dbg = nullptr;   // development builds only: [T][2 sub-groups][8] clock stamps of CTA 0
+#endif
     // float-storage forward (cluster kernel, generic-cell instantiation only): the float cell of
     // the reference's quantGRUForwardFP instead of the integer one
     int fs_on = 0;
@@ -73,5 +76,14 @@ bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_tab
 int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const GateConsts &gc_host,
                        const int8_t *r8, long long r_rows_alloc, long long h_rows_alloc, bool h_unsigned,
                        int ih_bytes, bool narrow, bool fused, bool floor, cudaStream_t stream, std::string *err);
+
+// The cluster kernel's low-latency form: 64 hidden units per CTA, two sub-groups, the branch-free
+// tabulated cell only (qgru_rec_c64.cu).  The plan fails where it does not apply (H > 512, or - unless
+// `force` - where a cluster would hold more than 64 rows or fewer than 3 CTAs).
+bool rec_c64_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, bool force, RecMmaPlan *out);
+
+int rec_c64_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const GateConsts &gc_host, const int8_t *r8,
+                   long long r_rows_alloc, long long h_rows_alloc, bool h_unsigned, int ih_bytes, cudaStream_t stream,
+                   std::string *err);
 
 }  // namespace qgru

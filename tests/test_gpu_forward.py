@@ -126,12 +126,44 @@ def test_two_subgroups_per_cta(oracle, cuda_device, shape, cfg):
     for extra in ((), (("r_resident", "smem"),), (("cell", "generic"),)):
         if extra == (("r_resident", "smem"),) and H > 512:
             continue
-        got, plan, _ = _run(case, cuda_device, opts=(("rec", "mma"), ("exchange", "cluster"), ("subgroups", "2")) + extra)
+        got, plan, _ = _run(case, cuda_device, opts=(("rec", "mma"), ("exchange", "cluster"), ("subgroups", "2"), ("unit_tile", "128")) + extra)
         assert "NG=2" in plan and "exchange=cluster_dsmem" in plan, plan
         assert np.array_equal(got, want), plan
     got, plan, _ = _run(case, cuda_device, opts=(("rec", "mma"), ("exchange", "cluster"), ("subgroups", "1")))
     assert "NG=1" in plan and np.array_equal(got, want), plan
-    rev, plan, _ = _run(case, cuda_device, reverse=True, opts=(("rec", "mma"), ("subgroups", "2")))
+    rev, plan, _ = _run(case, cuda_device, reverse=True, opts=(("rec", "mma"), ("subgroups", "2"), ("unit_tile", "128")))
+    import copy
+    flipped = copy.copy(case)
+    flipped.x_q = np.ascontiguousarray(case.x_q[::-1])
+    assert np.array_equal(rev, _want(oracle, flipped)[::-1]), plan
+
+
+@pytest.mark.parametrize("shape,sm_limit", [((9, 40, 64, 512), 0), ((7, 33, 40, 300), 0), ((6, 70, 24, 128), 0),
+                                            ((12, 5, 16, 256), 0), ((4, 200, 48, 384), 0), ((5, 200, 48, 384), 24),
+                                            ((5, 200, 32, 448), 21), ((3, 1, 8, 64), 0), ((30, 64, 32, 512), 0)])
+@pytest.mark.parametrize("cfg", ["default", "cfg2", "sym8_tensor"])
+def test_64_units_per_cta(oracle, cuda_device, shape, sm_limit, cfg):
+    """The low-latency form of the cluster recurrence (64 hidden units per CTA, update and reset rows
+    sharing one MMA tile, lane pairs splitting a unit's cells): same bits as the oracle for ragged
+    H and B, clusters of 1 to 8 CTAs, 16, 32 and 48 rows per sub-group, both directions."""
+    T, B, I, H = shape
+    case = make_case(19, T, B, I, H, oracle, config_named(cfg), with_h0=True)
+    want = _want(oracle, case)
+    _, plan, _ = _run(case, cuda_device, opts=(("rec", "mma"), ("unit_tile", "128")))
+    if "cell=fused_shiftfree" not in plan:
+        pytest.skip("this configuration does not get the branch-free tabulated cell: " + plan)
+    opts = (("rec", "mma"), ("unit_tile", "64")) + ((("sm_limit", str(sm_limit)),) if sm_limit else ())
+    got, plan, _ = _run(case, cuda_device, opts=opts)
+    assert "UT=64" in plan and "NG=2" in plan and "cell=fused_shiftfree" in plan, plan
+    if sm_limit == 24:
+        assert "NB=32" in plan, plan
+    if sm_limit == 21:
+        assert "NB=48" in plan, plan
+    assert np.array_equal(got, want), plan
+    got, plan, _ = _run(case, cuda_device, opts=opts, f32=True)
+    assert "UT=64" in plan
+    assert np.array_equal(got.view(np.uint32), oracle.dequantize(want, case.params.c, 1).view(np.uint32)), plan
+    rev, plan, _ = _run(case, cuda_device, reverse=True, opts=opts)
     import copy
     flipped = copy.copy(case)
     flipped.x_q = np.ascontiguousarray(case.x_q[::-1])
