@@ -369,6 +369,14 @@ QGRU_API const char *qgru_describe_plan(qgru_handle *h, int T, int B);
  * W*x GEMM against; the small-N figures are the cost model of the recurrence kernels. */
 QGRU_API int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int accumulators, int mmas,
                                int ctas, double *cycles_per_mma, double *tera_ops);
+/* The same with `issuers` (1..4) warps issuing `mmas` MMAs each into accumulators of their own, and
+ * `spinners` further warps beside them that (neighbour_mode 0) poll an mbarrier as a kernel's waiting
+ * warps do, (1) run integer arithmetic back to back or (2) run dependent shared-memory loads, as its
+ * busy warps do: cycles_per_mma is the slowest issuer's chain time divided by `mmas`, tera_ops counts
+ * all issuers. */
+QGRU_API int qgru_probe_mma_i8_ex(int device, int M, int N, int a_in_tmem, int accumulators, int mmas,
+                                  int ctas, int issuers, int spinners, int neighbour_mode,
+                                  double *cycles_per_mma, double *tera_ops);
 
 /* Restrict or force kernel choices (testing).  Names and values:
  *   "gemm"     auto | simt | tcgen05        W*x kernel
@@ -383,8 +391,11 @@ QGRU_API int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int accu
  *   "tiles_per_cta" 1 | 2                 cluster recurrence at 128 < H <= 256: 128-unit tiles per CTA
  *   "subgroups" auto | 1 | 2              cluster recurrence: independent batch sub-groups per CTA (with 2,
  *                                         the MMAs of one overlap the cells of the other)
- *   "unit_tile" auto | 64 | 128           cluster recurrence: hidden units per CTA (64: the low-latency form,
- *                                         taken by auto where a cluster is left with at most 64 batch rows)
+ *   "k_parts" 1 | 2                       cluster recurrence: 1 = one MMA-issuing warp per gate, 2 = one per K half
+ *   "issue_delay" n                       cluster recurrence: SM cycles by which the reset gate's MMAs start after
+ *                                         the update gate's, and the new gate's after the reset gate's
+ *   "unit_tile" auto | 64 | 128           cluster recurrence: hidden units per CTA (auto = 128; 64: update and
+ *                                         reset rows share one MMA tile, H <= 512, tabulated cell only)
  *   "probe_floor" 0 | 1                   measurement aid: the cluster recurrence runs with its MMAs and
  *                                         cells left out (results are meaningless); the recurrence time of
  *                                         qgru_last_timing is then the per-step synchronisation floor

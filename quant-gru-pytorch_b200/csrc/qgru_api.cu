@@ -184,6 +184,10 @@ int qgru_set_option(qgru_handle *h, const char *name, const char *value) {
         else if (v == "1") h->opt_ng = 1;
         else if (v == "2") h->opt_ng = 2;
         else return fail(h, QGRU_ERR_BAD_ARG, "subgroups: auto|1|2");
+    } else if (n == "k_parts") {
+        h->opt_kp = atoi(value) == 2 ? 2 : 1;
+    } else if (n == "issue_delay") {
+        h->opt_issue_delay = std::max(0, atoi(value));
     } else if (n == "unit_tile") {
         if (v == "auto") h->opt_ut = 0;
         else if (v == "64") h->opt_ut = 64;
@@ -620,7 +624,7 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
     // group; H <= 1024) or through global memory with a counter per group (H <= 512)
     RecMmaPlan cp;
     const bool cluster_ok = h->opt_rec != 1 && h->opt_exchange != 1 &&
-                            rec_cluster_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, h->opt_r_where, h->opt_mt, h->opt_ng, &cp);
+                            rec_cluster_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, h->opt_r_where, h->opt_mt, h->opt_ng, h->opt_kp, &cp);
     const bool global_ok = h->opt_rec != 1 && rec_mma_plan(h->H, h->Hpad, B, sms, h->smem_optin, n_tab_mma, &mp);
     const bool mma_ok = cluster_ok || global_ok;
     if (h->opt_rec == 2 && !mma_ok)
@@ -645,12 +649,12 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
                             h->gc_host.rh_to_n.mq != 0 && h->gc_host.uh_to_h.mq != 0;
     const bool fused = (use_mma || gemv_fused) && h->gc_host.fused_ok && h->opt_gemm != 1 && h->opt_cell != 1;
     const int ih_bytes = fused ? h->gc_host.ih_pre_bytes : h->ih_bytes;
-    // The 64-units-per-CTA form of the cluster recurrence: only the branch-free tabulated cell, and
-    // (unless asked for) only where a cluster is left with few batch rows - the latency-bound regime.
+    // The 64-units-per-CTA form of the cluster recurrence: only the branch-free tabulated cell, and only
+    // on request (option unit_tile=64): measured slower than the 128-unit form so far.
     const bool fast_cell_ok = fused && use_cluster && h->opt_cell != 2 && h->lin_fits32[1] && h->rs_fast[1] &&
                               h->gc_host.rh_to_n.mq != 0 && h->gc_host.uh_to_h.mq != 0;
     RecMmaPlan c64;
-    const bool use_c64 = fast_cell_ok && h->opt_ut != 128 && h->opt_ng != 1 && !h->opt_floor && h->opt_r_where != 1 &&
+    const bool use_c64 = fast_cell_ok && h->opt_ut == 64 && h->opt_ng != 1 && h->opt_mt != 2 && !h->opt_floor && h->opt_r_where != 1 &&
                          rec_c64_plan(h->H, h->Hpad, B, sms, h->smem_optin, h->gc_host.ft_ih_off, h->opt_ut == 64, &c64);
     if (h->opt_ut == 64 && use_mma && !use_c64)
         return fail(h, QGRU_ERR_UNSUPPORTED, "unit_tile=64 needs the fused shift-free cell, H <= 512 and at most 96 rows per cluster");
@@ -727,6 +731,7 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
         a.bar = h->d_bar;
         a.abort_flag = h->d_flags + 1;
         a.spin_limit = h->spin_limit;
+        a.issue_delay = h->opt_issue_delay;
 #ifdef QGRU_STAMPS
         a.dbg = h->dbg_stamps;
 #endif

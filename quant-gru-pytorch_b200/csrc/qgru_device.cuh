@@ -30,6 +30,28 @@ __device__ __forceinline__ unsigned ld_acquire(const unsigned *p) {
     return v;
 }
 
+// Predicated global load of one W*x+bw value, widened to 32 bits by the load itself; 0 where `ok`
+// is false.  One instruction with no dependent select behind it, so a warp that prefetches its
+// operands keeps issuing while they are in flight.
+__device__ __forceinline__ int32_t ld_ih_pred(const int8_t *p, bool ok) {
+    int32_t v;
+    asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %2, 0;\nmov.b32 %0, 0;\n@q ld.global.s8 %0, [%1];\n}"
+                 : "=r"(v) : "l"(p), "r"((int)ok));
+    return v;
+}
+__device__ __forceinline__ int32_t ld_ih_pred(const int16_t *p, bool ok) {
+    int32_t v;
+    asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %2, 0;\nmov.b32 %0, 0;\n@q ld.global.s16 %0, [%1];\n}"
+                 : "=r"(v) : "l"(p), "r"((int)ok));
+    return v;
+}
+__device__ __forceinline__ int32_t ld_ih_pred(const int32_t *p, bool ok) {
+    int32_t v;
+    asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %2, 0;\nmov.b32 %0, 0;\n@q ld.global.s32 %0, [%1];\n}"
+                 : "=r"(v) : "l"(p), "r"((int)ok));
+    return v;
+}
+
 // ------------------------------------------------------------ gate datapath (a4-a8)
 
 // piecewise_linear with its two clamps (include/quantize_ops_helper.h:600-606).  Where the

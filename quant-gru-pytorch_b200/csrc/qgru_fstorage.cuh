@@ -619,7 +619,7 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
     // 0.28 ms at H = 128, B = 32 and 4.1 against 4.6 us per step at H = 256, B = 1)
     const bool small = (h->opt_rec == 0 || h->opt_rec == 4) && h->Hpad <= 256 && B <= sms;
     const bool cluster_ok = !small && h->opt_rec != 1 && h->opt_rec != 3 && h->opt_exchange != 1 &&
-                            rec_cluster_plan(H, h->Hpad, B, sms, h->smem_optin, n_tab, h->opt_r_where, h->opt_mt, h->opt_ng, &cp);
+                            rec_cluster_plan(H, h->Hpad, B, sms, h->smem_optin, n_tab, h->opt_r_where, h->opt_mt, h->opt_ng, h->opt_kp, &cp);
     if (cluster_ok) {
         if (cp.G > h->bar_groups) {
             if ((rc = alloc_dev(h, &h->d_bar, (size_t)cp.G * 32))) return rc;

@@ -44,6 +44,8 @@ struct qgru_handle {
     int opt_r_where = 0;                     // cluster recurrence: 0 auto, 1 R in shared memory, 2 in tensor memory
     unsigned spin_limit = 1u << 24;
     int opt_ng = 0;                          // cluster recurrence: sub-groups per CTA (0 auto, 1, 2)
+    int opt_kp = 1;                          // cluster recurrence: K halves with issuers of their own (1, 2)
+    int opt_issue_delay = 0;                 // cluster recurrence: head start of a gate's MMAs over the next gate's, cycles
     int opt_ut = 0;                          // cluster recurrence: hidden units per CTA (0 auto, 64, 128)
 #ifdef QGRU_STAMPS
     long long *dbg_stamps = nullptr;

@@ -20,79 +20,121 @@ namespace {
 
 constexpr long long PROBE_WAIT = 2000000000ll;
 
-// One control thread issues `mmas` MMAs; accumulator i % n_acc, K-step i % 4 of a 128-byte slab.
-// A: 128 rows x 128 bytes (shared memory, 128-byte swizzle, or 32 columns of tensor memory);
-// B: N rows x 128 bytes in shared memory.  The operands are zeros: an integer pipe does not
-// care.  cycles[cta] = clock ticks from the first issue to the completion of the last MMA.
-__global__ void __launch_bounds__(128, 1)
-k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, long long *cycles, int *timeouts) {
+// `issuers` warps (lane 0 of each) issue `mmas` MMAs each, every warp into accumulators of its own
+// (n_acc per warp), K-step i % 4 of a 128-byte slab.  A: 128 rows x 128 bytes (shared memory,
+// 128-byte swizzle, or 32 columns of tensor memory); B: N rows x 128 bytes in shared memory.  The
+// operands are zeros: an integer pipe does not care.  `spinners` further warps poll an mbarrier
+// the way the recurrence kernels' waiting warps do, until the issuers are done: they show what
+// waiting neighbours cost the issuing threads.  cycles[cta] = clock ticks from the first issue to
+// the completion of the last MMA of the slowest issuer.
+__global__ void __launch_bounds__(1024, 1)
+k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, int issuers, int neighbour_mode, long long *cycles,
+               int *timeouts) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = tc::smem_u32(smem_raw);
     unsigned char *base = smem_raw + (((raw + 1023u) & ~1023u) - raw);
     unsigned char *a_tile = base;                    // 16 KB
     unsigned char *b_tile = base + 16384;            // up to 32 KB
-    uint64_t *bar = reinterpret_cast<uint64_t *>(base + 16384 + 32768);
-    uint32_t *slot = reinterpret_cast<uint32_t *>(bar + 1);
+    uint64_t *bar = reinterpret_cast<uint64_t *>(base + 16384 + 32768);   // [issuers] + one nobody completes
+    uint32_t *slot = reinterpret_cast<uint32_t *>(bar + 8);
+    volatile int *done = reinterpret_cast<volatile int *>(slot + 1);
+    long long *cyc_w = reinterpret_cast<long long *>(bar + 10);           // [issuers]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int i = threadIdx.x; i < (16384 + 32768) / 4; i += blockDim.x) reinterpret_cast<uint32_t *>(base)[i] = 0u;
     if (threadIdx.x == 0) {
-        tc::mbar_init(bar, 1);
+        for (int i = 0; i < 5; ++i) tc::mbar_init(&bar[i], 1);
+        *done = 0;
         tc::fence_barrier_init();
     }
-    if (threadIdx.x < 32) tc::tmem_alloc(slot, 512);
+    if (warp == 0) tc::tmem_alloc(slot, 512);
     tc::tc_fence_before_sync();
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem = *slot;
-    if (threadIdx.x == 0) {
-        const uint32_t idesc = tc::idesc_i8(M, N, true, true);
-        const uint64_t adesc = tc::smem_desc_sw128(tc::smem_u32(a_tile));
-        const uint64_t bdesc = tc::smem_desc_sw128(tc::smem_u32(b_tile));
-        const uint32_t a_col = tmem + (uint32_t)(n_acc * N);   // 32 columns after the accumulators
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        // Every operand of the 8 MMAs of a loop pass is prepared before the clock starts, so that the
-        // issuing thread's own arithmetic does not set the pace: the body is 8 MMA instructions.
-        uint32_t dcol[8], acol[8];
-        uint64_t ad[8], bd[8];
+    if (warp < issuers) {
+        if (lane == 0) {
+            const uint32_t idesc = tc::idesc_i8(M, N, true, true);
+            const uint64_t adesc = tc::smem_desc_sw128(tc::smem_u32(a_tile));
+            const uint64_t bdesc = tc::smem_desc_sw128(tc::smem_u32(b_tile));
+            const uint32_t a_col = tmem + (uint32_t)(issuers * n_acc * N);   // 32 columns after the accumulators
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // Every operand of the 8 MMAs of a loop pass is prepared before the clock starts, so that the
+            // issuing thread's own arithmetic does not set the pace: the body is 8 MMA instructions.
+            uint32_t dcol[8], acol[8];
+            uint64_t ad[8], bd[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            dcol[j] = tmem + (uint32_t)((j % n_acc) * N);
-            acol[j] = a_col + (uint32_t)(j & 3) * 8;
-            ad[j] = adesc + 2 * (uint64_t)(j & 3);
-            bd[j] = bdesc + 2 * (uint64_t)(j & 3);
+            for (int j = 0; j < 8; ++j) {
+                dcol[j] = tmem + (uint32_t)((warp * n_acc + j % n_acc) * N);
+                acol[j] = a_col + (uint32_t)(j & 3) * 8;
+                ad[j] = adesc + 2 * (uint64_t)(j & 3);
+                bd[j] = bdesc + 2 * (uint64_t)(j & 3);
+            }
+            const int passes = mmas / 8;
+            const long long t0 = clock64();
+            if (a_in_tmem) {
+                for (int i = 0; i < passes; ++i) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) tc::mma_i8_ts(dcol[j], acol[j], bd[j], idesc, 1u);
+                }
+            } else {
+                for (int i = 0; i < passes; ++i) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) tc::mma_i8(dcol[j], ad[j], bd[j], idesc, 1u);
+                }
+            }
+            tc::mma_commit(&bar[warp]);
+            const bool ok = tc::mbar_wait(&bar[warp], 0, PROBE_WAIT);
+            const long long t1 = clock64();
+            cyc_w[warp] = t1 - t0;
+            if (!ok) atomicAdd(timeouts, 1);
+            __threadfence_block();
+            atomicAdd(const_cast<int *>(done), 1);
         }
-        const int passes = mmas / 8;
+    } else {
+        // a neighbour warp, until the issuers are done (bounded): mode 0 polls a barrier that stays incomplete
+        // (a waiting warp), mode 1 runs dependent integer arithmetic back to back (a busy warp), mode 2
+        // runs dependent shared-memory loads (a warp doing table lookups)
         const long long t0 = clock64();
-        if (a_in_tmem) {
-            for (int i = 0; i < passes; ++i) {
+        uint32_t x = threadIdx.x;
+        const uint32_t tb = tc::smem_u32(base);
+        while (*done < issuers && clock64() - t0 < PROBE_WAIT) {
+            if (neighbour_mode == 0) {
+                tc::mbar_try_wait(&bar[4], 0);
+            } else if (neighbour_mode == 1) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) tc::mma_i8_ts(dcol[j], acol[j], bd[j], idesc, 1u);
-            }
-        } else {
-            for (int i = 0; i < passes; ++i) {
+                for (int i = 0; i < 64; ++i) x = x * 1664525u + 1013904223u;
+            } else {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) tc::mma_i8(dcol[j], ad[j], bd[j], idesc, 1u);
+                for (int i = 0; i < 16; ++i) {
+                    uint32_t v;
+                    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(tb + ((x & 4095u) << 2)));
+                    x = x * 1664525u + 1013904223u + v;
+                }
             }
         }
-        tc::mma_commit(bar);
-        const bool ok = tc::mbar_wait(bar, 0, PROBE_WAIT);
-        const long long t1 = clock64();
-        cycles[blockIdx.x] = t1 - t0;
-        if (!ok) atomicAdd(timeouts, 1);
+        if (x == 0xdeadbeefu) atomicAdd(timeouts, 0);   // keeps the arithmetic alive
     }
     tc::tc_fence_before_sync();
     __syncthreads();
-    if (threadIdx.x < 32) tc::tmem_dealloc(tmem, 512);
+    if (threadIdx.x == 0) {
+        long long worst = 0;
+        for (int i = 0; i < issuers; ++i) worst = worst > cyc_w[i] ? worst : cyc_w[i];
+        cycles[blockIdx.x] = worst;
+    }
+    if (warp == 0) tc::tmem_dealloc(tmem, 512);
 }
 
 }  // namespace
 }  // namespace qgru
 
-extern "C" int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int accumulators, int mmas, int ctas,
-                                 double *cycles_per_mma, double *tera_ops) {
+extern "C" int qgru_probe_mma_i8_ex(int device, int M, int N, int a_in_tmem, int accumulators, int mmas, int ctas,
+                                    int issuers, int spinners, int neighbour_mode, double *cycles_per_mma,
+                                    double *tera_ops) {
     using namespace qgru;
     if (!cycles_per_mma || !tera_ops) return QGRU_ERR_BAD_ARG;
     if (!((M == 128 && N % 16 == 0) || (M == 64 && N % 8 == 0)) || N < 8 || N > 256) return QGRU_ERR_BAD_ARG;
-    if (accumulators < 1 || accumulators * N + (a_in_tmem ? 32 : 0) > 512 || mmas < 8 || mmas % 8 != 0 || mmas > (1 << 22) || ctas < 1)
+    if (issuers < 1 || issuers > 4 || spinners < 0 || issuers + spinners > 32) return QGRU_ERR_BAD_ARG;
+    if (accumulators < 1 || issuers * accumulators * N + (a_in_tmem ? 32 : 0) > 512 || mmas < 8 || mmas % 8 != 0 || mmas > (1 << 22) || ctas < 1)
         return QGRU_ERR_BAD_ARG;
     if (cudaSetDevice(device) != cudaSuccess) return QGRU_ERR_CUDA;
     int sms = 0;
@@ -102,16 +144,17 @@ extern "C" int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int ac
     int *d_to = nullptr;
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     int rc = QGRU_ERR_CUDA;
-    const size_t smem = 16384 + 32768 + 64 + 1024;
+    const size_t smem = 16384 + 32768 + 256 + 1024;
+    const int threads = 32 * (issuers + spinners);
     do {
         if (cudaMalloc(&d_cycles, sizeof(long long) * ctas) != cudaSuccess) break;
         if (cudaMalloc(&d_to, sizeof(int)) != cudaSuccess) break;
         if (cudaMemset(d_to, 0, sizeof(int)) != cudaSuccess) break;
         if (cudaFuncSetAttribute(k_probe_mma_i8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) break;
         if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) break;
-        k_probe_mma_i8<<<ctas, 128, smem>>>(M, N, a_in_tmem, accumulators, std::min(mmas, 256) / 8 * 8, d_cycles, d_to);   // warm-up
+        k_probe_mma_i8<<<ctas, threads, smem>>>(M, N, a_in_tmem, accumulators, std::min(mmas, 256) / 8 * 8, issuers, neighbour_mode, d_cycles, d_to);   // warm-up
         cudaEventRecord(e0);
-        k_probe_mma_i8<<<ctas, 128, smem>>>(M, N, a_in_tmem, accumulators, mmas, d_cycles, d_to);
+        k_probe_mma_i8<<<ctas, threads, smem>>>(M, N, a_in_tmem, accumulators, mmas, issuers, neighbour_mode, d_cycles, d_to);
         cudaEventRecord(e1);
         if (cudaEventSynchronize(e1) != cudaSuccess || cudaGetLastError() != cudaSuccess) break;
         float ms = 0.f;
@@ -127,7 +170,7 @@ extern "C" int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int ac
         long long worst = 0;
         for (long long c : cyc) worst = std::max(worst, c);
         *cycles_per_mma = (double)worst / mmas;
-        *tera_ops = 2.0 * M * N * 32.0 * (double)mmas * ctas / (ms * 1e-3) / 1e12;
+        *tera_ops = 2.0 * M * N * 32.0 * (double)mmas * issuers * ctas / (ms * 1e-3) / 1e12;
         rc = QGRU_OK;
     } while (false);
     cudaGetLastError();
@@ -136,4 +179,9 @@ extern "C" int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int ac
     cudaFree(d_cycles);
     cudaFree(d_to);
     return rc;
+}
+
+extern "C" int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int accumulators, int mmas, int ctas,
+                                 double *cycles_per_mma, double *tera_ops) {
+    return qgru_probe_mma_i8_ex(device, M, N, a_in_tmem, accumulators, mmas, ctas, 1, 3, 0, cycles_per_mma, tera_ops);
 }

@@ -20,6 +20,11 @@
 // on the reset gate, each with its own table offsets - then swap what the partner needs with
 // three shuffle pairs and each finishes two of the four cells (new gate and state update).
 //
+// MMA issue.  One thread issues a dependent chain of these MMAs at one per 53-80 cycles, but the
+// tensor pipe takes MMAs from several threads side by side (four issuing warps reach its full
+// rate: qgru_probe_mma_i8_ex).  So the step's MMAs are dealt to four issuing warps, one per
+// (tile, K half), each accumulating into columns of its own; the cells add the two K halves.
+//
 // Everything else is the cluster kernel's scheme: R resident in tensor memory for all T steps,
 // h_t exchanged between the P (<= 8) CTAs of a cluster through distributed shared memory with
 // st.async counted on the receivers' mbarriers, double-buffered state tiles, bounded waits.
@@ -35,7 +40,7 @@
 #include "qgru_tc.cuh"
 
 #ifdef QGRU_STAMPS
-#define STAMP(cond, slot) do { if (a.dbg && blockIdx.x == 0 && (cond)) a.dbg[((size_t)s * 2 + g) * 8 + (slot)] = clock64(); } while (0)
+#define STAMP(cond, slot) do { if (a.dbg && blockIdx.x < 2 && (cond)) a.dbg[(((size_t)blockIdx.x * a.T + s) * 2 + g) * 32 + (slot)] = clock64(); } while (0)
 #else
 #define STAMP(cond, slot) do { } while (0)
 #endif
@@ -47,7 +52,8 @@ namespace {
 constexpr long long WAIT_BUDGET = 2000000000ll;  // ~1 s of SM clocks
 constexpr int EPW = 4;                           // epilogue warps per TMEM lane quadrant
 constexpr int EPI_THREADS = 32 * 4 * EPW;
-constexpr int REC_THREADS = 32 + EPI_THREADS;
+constexpr int ISSUERS = 4;                       // warp 0 and the three warps after the epilogue warps
+constexpr int REC_THREADS = 32 * ISSUERS + EPI_THREADS;
 constexpr int UT = 64;                           // hidden units per CTA
 constexpr int MAX_NG = 2;
 
@@ -102,7 +108,7 @@ k_recurrence_c64(const __grid_constant__ CUtensorMap map_r, const __grid_constan
     if (tid == 0) {
         tc::mbar_init(r_full, 1);
         tc::mbar_init(h_full, 1);
-        for (int g = 0; g < 2 * NG; ++g) tc::mbar_init(&mma_done[g], 1);
+        for (int g = 0; g < 2 * NG; ++g) tc::mbar_init(&mma_done[g], (uint32_t)a.k_parts);   // one commit per K part
         for (int g = 0; g < 2 * NG; ++g) tc::mbar_init(&h_ready[g], 4 * EPW + 1);
         tc::mbar_init(r_ready, EPI_THREADS);
         tc::fence_barrier_init();
@@ -117,75 +123,77 @@ k_recurrence_c64(const __grid_constant__ CUtensorMap map_r, const __grid_constan
     cluster_arrive();   // no CTA may receive a peer's block before its barriers are initialised
     cluster_wait();
 
-    if (warp == 0) {
-        // ------------------------------------------------------------------ control warp
-        if (lane == 0) {
+    if (warp == 0 || warp > 4 * EPW) {
+        // ------------------------------------------------------------------ issuing warps
+        // issuer cw multiplies tile (cw & 1: ZR / N) over K part (cw >> 1); issuer 0 also loads R and the
+        // initial state and announces the peers' bytes on the state barriers
+        const int cw = warp == 0 ? 0 : warp - 4 * EPW;
+        const int ts = cw & 1, part = cw >> 1;
+        if (lane == 0 && part < a.k_parts) {
             bool ok = true;
-            // The two tile sets of this CTA's R slice, K-slab by K-slab, in boxes of 16 rows (one run of
-            // consecutive units of one gate); rows past 3H of the packed R are zeros and fill the unused
-            // halves of tile N.
-            const int zero_row = a.C + 128;
-            tc::mbar_expect_tx(r_full, (uint32_t)n_tiles * 16384u);
-            for (int kb = 0; kb < KBn; ++kb) {
-                unsigned char *zr = r_tiles + (size_t)kb * 16384, *nn = r_tiles + (size_t)(KBn + kb) * 16384;
-                for (int q = 0; q < 4; ++q) {
-                    tc::tma_load_2d(zr + (size_t)(2 * q) * 2048, &map_r, r_full, kb * 128, 0 * a.H + j0 + 16 * q);
-                    tc::tma_load_2d(zr + (size_t)(2 * q + 1) * 2048, &map_r, r_full, kb * 128, 1 * a.H + j0 + 16 * q);
-                    tc::tma_load_2d(nn + (size_t)(2 * q) * 2048, &map_r, r_full, kb * 128, 2 * a.H + j0 + 16 * q);
-                    tc::tma_load_2d(nn + (size_t)(2 * q + 1) * 2048, &map_r, r_full, kb * 128, zero_row);
+            if (cw == 0) {
+                // The two tile sets of this CTA's R slice, K-slab by K-slab, in boxes of 16 rows (one run of
+                // consecutive units of one gate); rows past 3H of the packed R are zeros and fill the unused
+                // halves of tile N.
+                const int zero_row = a.C + 128;
+                tc::mbar_expect_tx(r_full, (uint32_t)n_tiles * 16384u);
+                for (int kb = 0; kb < KBn; ++kb) {
+                    unsigned char *zr = r_tiles + (size_t)kb * 16384, *nn = r_tiles + (size_t)(KBn + kb) * 16384;
+                    for (int q = 0; q < 4; ++q) {
+                        tc::tma_load_2d(zr + (size_t)(2 * q) * 2048, &map_r, r_full, kb * 128, 0 * a.H + j0 + 16 * q);
+                        tc::tma_load_2d(zr + (size_t)(2 * q + 1) * 2048, &map_r, r_full, kb * 128, 1 * a.H + j0 + 16 * q);
+                        tc::tma_load_2d(nn + (size_t)(2 * q) * 2048, &map_r, r_full, kb * 128, 2 * a.H + j0 + 16 * q);
+                        tc::tma_load_2d(nn + (size_t)(2 * q + 1) * 2048, &map_r, r_full, kb * 128, zero_row);
+                    }
                 }
+                // the initial state (written by the preceding kernel) into buffer 0 of every sub-group
+                tc::mbar_expect_tx(h_full, (uint32_t)NG * h_buf_bytes);
+                for (int g = 0; g < NG; ++g)
+                    for (int kb = 0; kb < KBn; ++kb)
+                        tc::tma_load_2d(h_tile + (size_t)(2 * g) * h_buf_bytes + (size_t)kb * a.NB * 128, &map_h, h_full,
+                                        kb * 128, b0 + g * a.NB);
             }
             ok = tc::mbar_wait(r_ready, 0, WAIT_BUDGET);   // the epilogue threads have moved the tiles to tensor memory
-            // the initial state (written by the preceding kernel) into buffer 0 of every sub-group
-            tc::mbar_expect_tx(h_full, (uint32_t)NG * h_buf_bytes);
-            for (int g = 0; g < NG; ++g)
-                for (int kb = 0; kb < KBn; ++kb)
-                    tc::tma_load_2d(h_tile + (size_t)(2 * g) * h_buf_bytes + (size_t)kb * a.NB * 128, &map_h, h_full,
-                                    kb * 128, b0 + g * a.NB);
             ok = ok && tc::mbar_wait(h_full, 0, WAIT_BUDGET);
+            tc::tc_fence_after_sync();
             const uint32_t idesc = tc::idesc_i8(128, a.NB, true, !a.h_unsigned);
             const uint32_t h_lo0 = (tc::smem_u32(h_tile) & 0x3FFFFu) >> 4;
             const uint32_t desc_hi = (uint32_t)(tc::smem_desc_sw128(0) >> 32);
             const uint32_t desc_lo = (uint32_t)tc::smem_desc_sw128(0);
             const uint64_t dhi = (uint64_t)desc_hi << 32;
-            const uint32_t r_t0 = tmem_base + (uint32_t)a.r_tmem_col;
+            const uint32_t ra = tmem_base + (uint32_t)(a.r_tmem_col + ts * KBn * 32);
             const uint32_t blk_bytes = (uint32_t)(a.NB * UT);            // what one peer sends per sub-group and step
+            const int kb0 = part == 0 ? 0 : (KBn + 1) / 2;               // this issuer's K-slabs: [kb0, kb1)
+            const int kb1 = (a.k_parts == 1 || part == 1) ? KBn : (KBn + 1) / 2;
             for (int s = 0; s < a.T && ok; ++s) {
                 for (int g = 0; g < NG; ++g) {
                     const uint32_t buf = (uint32_t)(2 * g + (s & 1));
                     if (s > 0) {
-                        tc::mbar_expect_tx(&h_ready[buf], (uint32_t)(a.P - 1) * blk_bytes);
+                        if (cw == 0) tc::mbar_expect_tx(&h_ready[buf], (uint32_t)(a.P - 1) * blk_bytes);
                         if (!tc::mbar_wait(&h_ready[buf], (uint32_t)(((s - 1) >> 1) & 1), WAIT_BUDGET)) { ok = false; break; }
                         fence_proxy_async_cta();   // the MMAs read these stores through the async proxy
                     }
                     tc::tc_fence_after_sync();
-                    STAMP(true, 0);
+                    STAMP(true, 2 * cw);
                     const uint32_t hbuf = h_lo0 + ((buf * h_buf_bytes) >> 4);
-                    uint32_t bdl[4][4];   // low descriptor words of the state tile: K-slab kb, 32-byte step ks
+                    const uint32_t d = tmem_base + (uint32_t)(((2 * g + ts) * a.k_parts + part) * a.NB);
 #pragma unroll
                     for (int kb = 0; kb < 4; ++kb)
+                        if (kb >= kb0 && kb < kb1) {
 #pragma unroll
-                        for (int ks = 0; ks < 4; ++ks) bdl[kb][ks] = desc_lo | (hbuf + (uint32_t)(kb * a.NB * 8 + 2 * ks));
-#pragma unroll
-                    for (int ts = 0; ts < 2; ++ts) {   // tile ZR, then tile N: the update / reset gates start while N multiplies
-                        const uint32_t d = tmem_base + (uint32_t)((2 * g + ts) * a.NB);
-                        const uint32_t ra = r_t0 + (uint32_t)(ts * KBn * 32);
-#pragma unroll
-                        for (int kb = 0; kb < 4; ++kb)
-                            if (kb < KBn) {
-#pragma unroll
-                                for (int ks = 0; ks < 4; ++ks)
-                                    tc::mma_i8_ts(d, ra + (uint32_t)(kb * 32 + ks * 8), dhi | bdl[kb][ks], idesc, (kb | ks) != 0);
-                            }
-                        tc::mma_commit(&mma_done[2 * g + ts]);
-                    }
-                    STAMP(true, 1);
+                            for (int ks = 0; ks < 4; ++ks)
+                                tc::mma_i8_ts(d, ra + (uint32_t)(kb * 32 + ks * 8),
+                                              dhi | (desc_lo | (hbuf + (uint32_t)(kb * a.NB * 8 + 2 * ks))), idesc,
+                                              (kb != kb0 || ks != 0) ? 1u : 0u);
+                        }
+                    tc::mma_commit(&mma_done[2 * g + ts]);
+                    STAMP(true, 2 * cw + 1);
                 }
             }
             if (!ok) atomicOr(a.abort_flag, 1);
         }
     } else {
-        // ---------------------------------------------------------------- epilogue warps
+        // ---------------------------------------------------------------- epilogue warps (1 .. 16)
         const int q = warp & 3;                      // TMEM lane quadrant this warp may read
         const int rank = (warp - 1) >> 2;            // 0..EPW-1 among the warps of that quadrant
         const int half = lane >> 4;                  // 0: this lane holds update-gate rows, 1: reset-gate rows
@@ -233,8 +241,26 @@ k_recurrence_c64(const __grid_constant__ CUtensorMap map_r, const __grid_constan
             tc::mbar_arrive(r_ready);
         }
         ok = tc::mbar_wait(h_full, 0, WAIT_BUDGET) && ok;
+        // The W*x+bw values of a chunk come from HBM (a microsecond away under load) and a warp issues in
+        // order, so they are fetched one chunk AHEAD: while the warp works on a chunk, the six values of
+        // its next chunk (next sub-group or next step) are already in flight into registers.
+        struct Pre { int32_t g[4], n[2]; };
+        auto fetch = [&](int s_, int g_, int c_, Pre &pr) {
+            const int t_ = a.reverse ? (a.T - 1 - s_) : s_;
+            const int bg = b0 + g_ * a.NB;
+            const int nb_ = max(0, min(a.NB, a.b_off + a.b_cnt - bg));
+            const int c0_ = 4 * c_, f0_ = c0_ + 2 * half;
+            const IhT *rowp = ihp + ((size_t)t_ * a.B + bg) * a.C + j;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                pr.g[i] = ld_ih_pred(rowp + (size_t)(c0_ + i) * a.C + half * a.H, c0_ + i < nb_ && j_ok);
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+                pr.n[k] = ld_ih_pred(rowp + (size_t)(f0_ + k) * a.C + 2 * a.H, f0_ + k < nb_ && j_ok);
+        };
+        Pre cur, nxt;
+        fetch(0, 0, rank, cur);
         for (int s = 0; s < a.T; ++s) {
-            const int t = a.reverse ? (a.T - 1 - s) : s;
             const long long out_slot = a.reverse ? (a.T - 1 - s) : (s + 1);
             const uint32_t par = (uint32_t)(s & 1);
             for (int g = 0; g < NG; ++g) {
@@ -250,32 +276,46 @@ k_recurrence_c64(const __grid_constant__ CUtensorMap map_r, const __grid_constan
                 for (int c = rank; c < nchunks && ok; c += EPW) {
                     const int c0 = 4 * c;
                     const int f0 = c0 + 2 * half;      // the two batch columns this lane finishes
-                    // operands that do not depend on this step's MMAs: issued first
-                    int32_t ihg[4], ihn[2], hold[2];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const bool v_ok = c0 + i < nb && j_ok;
-                        const size_t row = (size_t)t * a.B + bg0 + c0 + i;
-                        ihg[i] = v_ok ? (int32_t)ihp[row * a.C + half * a.H + j] : 0;
+                    // the next chunk's W*x+bw values start their way now
+                    {
+                        int s2 = s, g2 = g, c2 = c + EPW;
+                        if (c2 >= nchunks) {
+                            c2 = rank;
+                            if (++g2 == NG) {
+                                g2 = 0;
+                                ++s2;
+                            }
+                        }
+                        if (s2 < a.T) fetch(s2, g2, c2, nxt);
                     }
+                    STAMP((warp % 15) == 1 && lane == 0, 13 + 8 * (warp / 15));
+                    int32_t hold[2];
 #pragma unroll
                     for (int k = 0; k < 2; ++k) {
                         const bool v_ok = f0 + k < nb && j_ok;
-                        const size_t row = (size_t)t * a.B + bg0 + f0 + k;
-                        ihn[k] = v_ok ? (int32_t)ihp[row * a.C + 2 * a.H + j] : 0;
                         const uint8_t hb = v_ok ? h_cur[sw128_offset(f0 + k, j, a.NB)] : (uint8_t)0;
                         hold[k] = state_byte(hb, h_bits);
                     }
-                    const uint32_t ta0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(2 * g * a.NB + c0);
+                    STAMP((warp % 15) == 1 && lane == 0, 14 + 8 * (warp / 15));
+                    const int32_t(&ihg)[4] = cur.g;
+                    const int32_t(&ihn)[2] = cur.n;
+                    const uint32_t ta0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(2 * g * a.k_parts * a.NB + c0);
                     // update gate (lanes 0-15) and reset gate (lanes 16-31) of four batch columns
                     if (!waited) {
                         ok = tc::mbar_wait(&md[0], par, WAIT_BUDGET);
                         if (!ok) break;
                         tc::tc_fence_after_sync();
                     }
-                    STAMP(warp == 1 && lane == 0 && !waited, 2);
+                    STAMP((warp % 15) == 1 && lane == 0 && !waited, 8 + 8 * (warp / 15));
                     int32_t acc[4], gd[4];
                     tc::tmem_ld4(ta0, acc);
+                    if (a.k_parts == 2) {   // the other K half
+                        int32_t hi[4];
+                        tc::tmem_ld4(ta0 + (uint32_t)a.NB, hi);
+                        tc::tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) acc[i] += hi[i];
+                    }
                     tc::tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
@@ -292,8 +332,15 @@ k_recurrence_c64(const __grid_constant__ CUtensorMap map_r, const __grid_constan
                         tc::tc_fence_after_sync();
                         waited = true;
                     }
-                    STAMP(warp == 1 && lane == 0, 3);
-                    tc::tmem_ld4(ta0 + (uint32_t)a.NB, acc);
+                    STAMP((warp % 15) == 1 && lane == 0, 9 + 8 * (warp / 15));
+                    tc::tmem_ld4(ta0 + (uint32_t)(a.k_parts * a.NB), acc);
+                    if (a.k_parts == 2) {
+                        int32_t hi[4];
+                        tc::tmem_ld4(ta0 + (uint32_t)(3 * a.NB), hi);
+                        tc::tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) acc[i] += hi[i];
+                    }
                     tc::tmem_ld_wait();
                     const int32_t s2 = __shfl_xor_sync(0xffffffffu, acc[2], 16);
                     const int32_t s3 = __shfl_xor_sync(0xffffffffu, acc[3], 16);
@@ -330,6 +377,7 @@ k_recurrence_c64(const __grid_constant__ CUtensorMap map_r, const __grid_constan
                         hn_last[1] = hn[1];
                         f_last = f0;
                     }
+                    cur = nxt;
                 }
                 if (ok && !waited) {
                     // a warp without a chunk still waits for this step's MMAs: it must not arrive twice
@@ -340,8 +388,9 @@ k_recurrence_c64(const __grid_constant__ CUtensorMap map_r, const __grid_constan
                 fence_proxy_async_cta();   // this warp's own words, for the MMAs' async-proxy reads
                 tc::tc_fence_before_sync();
                 __syncwarp();
-                STAMP(warp == 1 && lane == 0, 4);
+                STAMP((warp % 15) == 1 && lane == 0, 10 + 8 * (warp / 15));
                 if (lane == 0 && s + 1 < a.T) tc::mbar_arrive(&h_ready[nbuf]);
+                STAMP((warp % 15) == 1 && lane == 0, 11 + 8 * (warp / 15));
                 // outputs of the warp's last chunk leave after the arrive: nothing in the next step waits for them
                 if (f_last >= 0) {
 #pragma unroll
@@ -352,6 +401,7 @@ k_recurrence_c64(const __grid_constant__ CUtensorMap map_r, const __grid_constan
                             if (a.hf_out) a.hf_out[o] = (float)(hn_last[k] - gc.zp_h) * gc.h_scale;
                         }
                 }
+                STAMP((warp % 15) == 1 && lane == 0, 12 + 8 * (warp / 15));
             }
         }
         if (!ok && lane == 0) atomicOr(a.abort_flag, 1);
@@ -404,7 +454,11 @@ bool rec_c64_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, 
     if (NB > 48) return false;                                      // beyond 48 columns an MMA gets slower: no point
     const size_t smem = smem64_layout(KBn, NB, NG, n_table).total + 1024;
     if (smem > (size_t)smem_optin) return false;
-    const int acc_cols = (NG * 2 * NB + 31) / 32 * 32;
+    // two K halves per tile, each with an issuing warp and accumulator columns of its own, where K has
+    // two slabs and tensor memory has the room
+    int k_parts = KBn >= 2 ? 2 : 1;
+    if ((NG * 2 * k_parts * NB + 31) / 32 * 32 + 2 * KBn * 32 > 512) k_parts = 1;
+    const int acc_cols = (NG * 2 * k_parts * NB + 31) / 32 * 32;
     uint32_t cols = 32;
     while ((int)cols < acc_cols + 2 * KBn * 32) cols <<= 1;
     if (cols > 512) return false;
@@ -418,6 +472,7 @@ bool rec_c64_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, 
     out->r_tmem_col = acc_cols;
     out->tmem_tiles = 2 * KBn;
     out->r_slots = 2 * KBn;
+    out->k_parts = k_parts;
     out->groups_per_launch = out->G;
     return true;
 }
@@ -454,6 +509,7 @@ int rec_c64_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const Gat
     a.r_tmem_col = pl.r_tmem_col;
     a.tmem_tiles = pl.tmem_tiles;
     a.r_slots = pl.r_slots;
+    a.k_parts = pl.k_parts;
     a.b_off = 0;
     a.b_cnt = a.B;
     const cudaError_t e = ih_bytes == 2 ? launch64<int16_t>(mr, mh, gc_host, a, pl.G * pl.P, pl.smem, stream)

@@ -23,6 +23,16 @@
 // B, the epilogue warps work on A then B, so that B's MMAs run on the tensor pipe while the
 // warps are busy with A's cells and A's next MMAs while they are busy with B's: the two halves
 // of a step, which are serial for one group (exchange -> MMAs -> cells), overlap.
+//
+// Three warps issue the MMAs, one per gate.  A single thread issues a chain of these small MMAs at
+// one per 53-80 cycles, while the tensor pipe takes MMAs from several threads side by side
+// (qgru_probe_mma_i8_ex) and is bound by streaming the A operand (the R slice, about 115 bytes per
+// cycle): the 48 MMAs of a step at H = 512 take 1700 cycles instead of 3900.  Each issuer commits
+// once per step: a commit holds its thread until the MMAs before it are done, so a thread that
+// commits gate by gate serialises the gates (measured; the form with one issuer per K half and
+// accumulator columns of its own, k_parts = 2, is kept for experiments).  The reset and new
+// gates' issuers start a little after the update gate's, so that the update gate, which the cells
+// need first, gets the head of the stream.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -44,7 +54,8 @@ namespace {
 constexpr long long WAIT_BUDGET = 2000000000ll;  // ~1 s of SM clocks
 constexpr int EPW = 4;                           // epilogue warps per TMEM lane quadrant
 constexpr int EPI_THREADS = 32 * 4 * EPW;
-constexpr int REC_THREADS = 32 + EPI_THREADS;
+constexpr int ISSUERS = 3;                       // warp 0 and the two warps after the epilogue warps
+constexpr int REC_THREADS = 32 * ISSUERS + EPI_THREADS;
 constexpr int CH = 4;                            // batch columns per chunk
 
 }  // namespace
@@ -74,23 +85,23 @@ namespace {
 // kernel's common path.
 __device__ __noinline__ void issue_wide(int MT, int KBn, int NB, int tmem_tiles, uint32_t tmem_base, uint32_t r_t0,
                                         uint32_t r_lo0, uint32_t hb0, uint32_t desc_lo, uint64_t dhi, uint32_t idesc,
-                                        uint64_t *mma_done) {
-    for (int g = 0; g < 3; ++g) {
+                                        uint64_t *mma_done, int KP, int part, int kb0, int kb1, int gate_lo, int gate_hi) {
+    for (int g = gate_lo; g < gate_hi; ++g) {
         for (int mt = 0; mt < MT; ++mt) {
-            const uint32_t d = tmem_base + (uint32_t)((mt * 3 + g) * NB);
-            for (int kb = 0; kb < KBn; ++kb) {
+            const uint32_t d = tmem_base + (uint32_t)(((mt * 3 + g) * KP + part) * NB);
+            for (int kb = kb0; kb < kb1; ++kb) {
                 const int tile = (mt * 3 + g) * KBn + kb;
                 const uint32_t bd = hb0 + (uint32_t)(kb * NB * 8);
                 if (tile < tmem_tiles) {
                     const uint32_t ra = r_t0 + (uint32_t)(tile * 32);
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks)
-                        tc::mma_i8_ts(d, ra + (uint32_t)(ks * 8), dhi | (bd + 2 * ks), idesc, (kb | ks) != 0);
+                        tc::mma_i8_ts(d, ra + (uint32_t)(ks * 8), dhi | (bd + 2 * ks), idesc, (kb != kb0 || ks != 0) ? 1u : 0u);
                 } else {
                     const uint32_t rb = desc_lo | (r_lo0 + (uint32_t)((tile - tmem_tiles) * 1024));
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks)
-                        tc::mma_i8(d, dhi | (rb + (uint32_t)(2 * ks)), dhi | (bd + 2 * ks), idesc, (kb | ks) != 0);
+                        tc::mma_i8(d, dhi | (rb + (uint32_t)(2 * ks)), dhi | (bd + 2 * ks), idesc, (kb != kb0 || ks != 0) ? 1u : 0u);
                 }
             }
         }
@@ -134,13 +145,14 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
     const int j0 = p * 128 * MT;
     const int b0 = a.b_off + grp * NG * a.NB;        // first batch row of the cluster; sub-group g starts NB * g later
     const uint32_t tmem_cols = a.tmem_cols;
-    const uint32_t acc_cols_g = (uint32_t)(MT * 3 * a.NB);   // accumulator columns of one sub-group
+    const int KP = a.k_parts;                                      // K halves with accumulators of their own
+    const uint32_t acc_cols_g = (uint32_t)(MT * 3 * KP * a.NB);   // accumulator columns of one sub-group
 
     for (int i = tid; i < a.n_table; i += blockDim.x) tables[i] = a.tables[i];
     if (tid == 0) {
         tc::mbar_init(r_full, 1);
         tc::mbar_init(h_full, 1);
-        for (int g = 0; g < 3 * NG; ++g) tc::mbar_init(&mma_done[g], 1);
+        for (int g = 0; g < 3 * NG; ++g) tc::mbar_init(&mma_done[g], (uint32_t)KP);   // one commit per K half
         // per phase: one arrival per epilogue warp, one by the control thread (which also announces
         // the bytes the peers send)
         for (int g = 0; g < 2 * NG; ++g) tc::mbar_init(&h_ready[g], 4 * EPW + 1);
@@ -158,129 +170,138 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
     cluster_arrive();
     cluster_wait();
 
-    if (warp == 0) {
-        // ------------------------------------------------------------------ control warp
+    if (warp == 0 || warp > 4 * EPW) {
+        // ------------------------------------------------------------------ issuing warps
+        // k_parts == 1: issuer w multiplies the rows of gate w.  k_parts == 2: issuers 0 and 1 multiply one
+        // half of K each, for every gate.  Issuer 0 also loads R and the initial state and announces the
+        // peers' bytes on the state barriers.
+        const int iw = warp == 0 ? 0 : warp - 4 * EPW;
+        const int part = KP == 2 ? iw : 0;
+        const int gate_lo = KP == 2 ? 0 : iw, gate_hi = KP == 2 ? 3 : iw + 1;
         bool ok = true;
         uint32_t idesc = 0, r_lo0 = 0, h_lo0 = 0, desc_hi = 0, desc_lo = 0;
-        if (lane == 0) {
-            // R slice: tiles [0, tmem_tiles) go to tensor memory through the slots, one pass of up to
-            // r_slots tiles at a time (the epilogue threads copy a pass and hand the slots back);
-            // the remaining tiles are then loaded into the slots to stay.
-            const int n_tiles = MT * 3 * KBn;
-            auto load_tiles = [&](int first, int cnt) {
-                tc::mbar_expect_tx(r_full, (uint32_t)cnt * 16384u);
-                for (int i = 0; i < cnt; ++i) {
-                    const int t = first + i, mt = t / (3 * KBn), g = (t / KBn) % 3, kb = t % KBn;
-                    tc::tma_load_2d(r_tiles + (size_t)i * 16384, &map_r, r_full, kb * 128, g * a.H + j0 + mt * 128);
+        if (lane == 0 && (KP == 1 || iw < 2)) {
+            if (iw == 0) {
+                // R slice: tiles [0, tmem_tiles) go to tensor memory through the slots, one pass of up to
+                // r_slots tiles at a time (the epilogue threads copy a pass and hand the slots back);
+                // the remaining tiles are then loaded into the slots to stay.
+                const int n_tiles = MT * 3 * KBn;
+                auto load_tiles = [&](int first, int cnt) {
+                    tc::mbar_expect_tx(r_full, (uint32_t)cnt * 16384u);
+                    for (int i = 0; i < cnt; ++i) {
+                        const int t = first + i, mt = t / (3 * KBn), g = (t / KBn) % 3, kb = t % KBn;
+                        tc::tma_load_2d(r_tiles + (size_t)i * 16384, &map_r, r_full, kb * 128, g * a.H + j0 + mt * 128);
+                    }
+                };
+                int pass = 0;
+                for (int done = 0; done < a.tmem_tiles && ok; ++pass) {
+                    const int cnt = min(a.r_slots, a.tmem_tiles - done);
+                    load_tiles(done, cnt);
+                    ok = tc::mbar_wait(r_ready, (uint32_t)(pass & 1), WAIT_BUDGET);   // copied: slots free again
+                    done += cnt;
                 }
-            };
-            int pass = 0;
-            for (int done = 0; done < a.tmem_tiles && ok; ++pass) {
-                const int cnt = min(a.r_slots, a.tmem_tiles - done);
-                load_tiles(done, cnt);
-                ok = tc::mbar_wait(r_ready, (uint32_t)(pass & 1), WAIT_BUDGET);   // copied: slots free again
-                done += cnt;
+                if (ok && n_tiles > a.tmem_tiles) {
+                    load_tiles(a.tmem_tiles, n_tiles - a.tmem_tiles);
+                    ok = tc::mbar_wait(r_full, (uint32_t)(pass & 1), WAIT_BUDGET);
+                }
+                // the initial state (written by the preceding kernel) into buffer 0 of every sub-group; it
+                // is requested after R is in place, so its arrival tells the other issuer that too
+                tc::mbar_expect_tx(h_full, (uint32_t)NG * h_buf_bytes);
+                for (int g = 0; g < NG; ++g)
+                    for (int kb = 0; kb < KBn; ++kb)
+                        tc::tma_load_2d(h_tile + (size_t)(2 * g) * h_buf_bytes + (size_t)kb * a.NB * 128, &map_h, h_full,
+                                        kb * 128, b0 + g * a.NB);
             }
-            if (ok && n_tiles > a.tmem_tiles) {
-                load_tiles(a.tmem_tiles, n_tiles - a.tmem_tiles);
-                ok = tc::mbar_wait(r_full, (uint32_t)(pass & 1), WAIT_BUDGET);
-            }
-            // the initial state (written by the preceding kernel) into buffer 0 of every sub-group
-            tc::mbar_expect_tx(h_full, (uint32_t)NG * h_buf_bytes);
-            for (int g = 0; g < NG; ++g)
-                for (int kb = 0; kb < KBn; ++kb)
-                    tc::tma_load_2d(h_tile + (size_t)(2 * g) * h_buf_bytes + (size_t)kb * a.NB * 128, &map_h, h_full,
-                                    kb * 128, b0 + g * a.NB);
             ok = ok && tc::mbar_wait(h_full, 0, WAIT_BUDGET);
+            tc::tc_fence_after_sync();
             idesc = tc::idesc_i8(128, a.NB, true, !a.h_unsigned);
             r_lo0 = (tc::smem_u32(r_tiles) & 0x3FFFFu) >> 4;
             h_lo0 = (tc::smem_u32(h_tile) & 0x3FFFFu) >> 4;
             desc_hi = (uint32_t)(tc::smem_desc_sw128(0) >> 32);
             desc_lo = (uint32_t)tc::smem_desc_sw128(0);
             if (!ok) atomicOr(a.abort_flag, 1);
-        }
-        if (lane == 0) {
             const uint32_t blk_bytes = (uint32_t)(a.NB * 128);           // one K-slab of the tile
+            const int kb0 = part == 0 ? 0 : (KBn + 1) / 2;               // this issuer's K-slabs: [kb0, kb1)
+            const int kb1 = (KP == 1 || part == 1) ? KBn : (KBn + 1) / 2;
             for (int s = 0; s < a.T && ok; ++s) {
                 for (int g = 0; g < NG; ++g) {
                     const uint32_t buf = (uint32_t)(2 * g + (s & 1));
                     if (s > 0) {
                         // h_s in buffer s & 1: the 16 warps of this CTA have stored their words and the
                         // (P-1) * NB * 128 bytes of the peers have landed
-                        tc::mbar_expect_tx(&h_ready[buf], (uint32_t)(a.P - 1) * blk_bytes);
+                        if (iw == 0) tc::mbar_expect_tx(&h_ready[buf], (uint32_t)(a.P - 1) * blk_bytes);
                         if (!tc::mbar_wait(&h_ready[buf], (uint32_t)(((s - 1) >> 1) & 1), WAIT_BUDGET)) { ok = false; break; }
                         fence_proxy_async_cta();   // the MMAs read these stores through the async proxy
                     }
                     tc::tc_fence_after_sync();
-                    STAMP(true, 0);
+                    STAMP(iw == 0, 0);
                     uint64_t *md = &mma_done[3 * g];
                     if constexpr (Floor) {
-                        for (int k = 0; k < 3; ++k) tc::mma_commit(&md[k]);
+                        for (int k = gate_lo; k < gate_hi; ++k) tc::mma_commit(&md[k]);
                         continue;
+                    }
+                    if (KP == 1 && iw > 0 && a.issue_delay > 0) {
+                        // the update gate's MMAs get a head start on the tensor pipe (bounded: a fixed number of cycles)
+                        const long long until = clock64() + (long long)iw * a.issue_delay;
+                        while (clock64() < until) {
+                        }
                     }
                     const uint32_t hbuf = h_lo0 + ((buf * h_buf_bytes) >> 4);
                     const uint32_t acc0 = tmem_base + (uint32_t)g * acc_cols_g;
-                    // Gate by gate, with a commit after each: the epilogue starts on the update gate while
-                    // the reset and new gates are still being multiplied.  The epilogue warps that share
-                    // this warp's scheduler are busy by then, so every operand is prepared up front and
-                    // the loops are fully unrolled: one independent add per MMA, no dependent chain.
                     const uint64_t dhi = (uint64_t)desc_hi << 32;
                     const uint32_t r_t0 = tmem_base + (uint32_t)a.r_tmem_col;
                     if (KBn <= 4 && (a.tmem_tiles == 0 || a.tmem_tiles == MT * 3 * KBn)) {
-                        // the common shapes (H <= 512, R in one place): every operand prepared up front,
-                        // one independent add per MMA - the issuing thread's instruction stream sets the pace
+                        // the common shapes (H <= 512, R in one place): fully unrolled, one independent add per MMA
                         uint32_t bdl[4][4];   // low descriptor words of the state tile: K-slab kb, 32-byte step ks
 #pragma unroll
                         for (int kb = 0; kb < 4; ++kb)
 #pragma unroll
                             for (int ks = 0; ks < 4; ++ks) bdl[kb][ks] = desc_lo | (hbuf + (uint32_t)(kb * a.NB * 8 + 2 * ks));
-                        if (a.tmem_tiles > 0) {   // A operand from tensor memory
 #pragma unroll
-                            for (int gate = 0; gate < 3; ++gate) {
+                        for (int gate = 0; gate < 3; ++gate) {
+                            if (gate < gate_lo || gate >= gate_hi) continue;
+                            if (a.tmem_tiles > 0) {   // A operand from tensor memory
 #pragma unroll
                                 for (int mt = 0; mt < MT; ++mt) {
-                                    const uint32_t d = acc0 + (uint32_t)((mt * 3 + gate) * a.NB);
+                                    const uint32_t d = acc0 + (uint32_t)(((mt * 3 + gate) * KP + part) * a.NB);
                                     const uint32_t ra = r_t0 + (uint32_t)((mt * 3 + gate) * KBn * 32);
 #pragma unroll
                                     for (int kb = 0; kb < 4; ++kb)
-                                        if (kb < KBn) {
+                                        if (kb >= kb0 && kb < kb1) {
 #pragma unroll
                                             for (int ks = 0; ks < 4; ++ks)
                                                 tc::mma_i8_ts(d, ra + (uint32_t)(kb * 32 + ks * 8), dhi | bdl[kb][ks], idesc,
-                                                              (kb | ks) != 0);
+                                                              (kb != kb0 || ks != 0) ? 1u : 0u);
                                         }
                                 }
-                                tc::mma_commit(&md[gate]);
-                            }
-                        } else {
-#pragma unroll
-                            for (int gate = 0; gate < 3; ++gate) {
+                            } else {
 #pragma unroll
                                 for (int mt = 0; mt < MT; ++mt) {
-                                    const uint32_t d = acc0 + (uint32_t)((mt * 3 + gate) * a.NB);
+                                    const uint32_t d = acc0 + (uint32_t)(((mt * 3 + gate) * KP + part) * a.NB);
                                     const uint32_t rb = desc_lo | (r_lo0 + (uint32_t)((mt * 3 + gate) * KBn * 1024));
 #pragma unroll
                                     for (int kb = 0; kb < 4; ++kb)
-                                        if (kb < KBn) {
+                                        if (kb >= kb0 && kb < kb1) {
 #pragma unroll
                                             for (int ks = 0; ks < 4; ++ks)
                                                 tc::mma_i8(d, dhi | (rb + (uint32_t)(kb * 1024 + 2 * ks)), dhi | bdl[kb][ks], idesc,
-                                                           (kb | ks) != 0);
+                                                           (kb != kb0 || ks != 0) ? 1u : 0u);
                                         }
                                 }
-                                tc::mma_commit(&md[gate]);
                             }
+                            tc::mma_commit(&md[gate]);
                         }
                     } else {
-                        issue_wide(MT, KBn, a.NB, a.tmem_tiles, acc0, r_t0, r_lo0, desc_lo | hbuf, desc_lo, dhi, idesc, md);
+                        issue_wide(MT, KBn, a.NB, a.tmem_tiles, acc0, r_t0, r_lo0, desc_lo | hbuf, desc_lo, dhi, idesc, md, KP,
+                                   part, kb0, kb1, gate_lo, gate_hi);
                     }
-                    STAMP(true, 1);
+                    STAMP(iw == 0, 1);
                 }
             }
             if (!ok) atomicOr(a.abort_flag, 1);
         }
     } else {
-        // ---------------------------------------------------------------- epilogue warps
+        // ---------------------------------------------------------------- epilogue warps (1 .. 16)
         const int q = warp & 3;                      // TMEM lane quadrant this warp may read
         const int rank = (warp - 1) >> 2;            // 0..EPW-1 among the warps of that quadrant
         const int u = q * 32 + lane;                 // unit within a 128-unit tile = TMEM lane
@@ -392,12 +413,30 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                 // is clamped, so every lane computes; only the stores are guarded.
                 int32_t hn[MT][CH];
                 const uint32_t ta0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)g * acc_cols_g + (uint32_t)c0;
+                // the sums of one gate for this thread's CH cells: the K halves are added here
+                auto ld_gate = [&](int gate, int32_t(&acc)[MT][CH]) {
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)(((mt * 3 + gate) * KP) * a.NB), acc[mt]);
+                    if (KP == 2) {
+                        int32_t hi[MT][CH];
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)(((mt * 3 + gate) * KP + 1) * a.NB), hi[mt]);
+                        tc::tmem_ld_wait();
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                            for (int i = 0; i < CH; ++i) acc[mt][i] += hi[mt][i];
+                    } else {
+                        tc::tmem_ld_wait();
+                    }
+                };
                 if constexpr (Floor) {
                     if (!waited) {
                         ok = tc::mbar_wait(&md[2], par, WAIT_BUDGET);
                         if (!ok) break;
                         tc::tc_fence_after_sync();
                         waited = true;
+                        STAMP(warp == 1 && lane == 0, 2);
                     }
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt)
@@ -412,9 +451,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         tc::tc_fence_after_sync();
                         STAMP(warp == 1 && lane == 0, 2);
                     }
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 0) * a.NB), acc[mt]);
-                    tc::tmem_ld_wait();
+                    ld_gate(0, acc);
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -426,9 +463,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         if (!ok) break;
                         tc::tc_fence_after_sync();
                     }
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 1) * a.NB), acc[mt]);
-                    tc::tmem_ld_wait();
+                    ld_gate(1, acc);
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -441,9 +476,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         tc::tc_fence_after_sync();
                         waited = true;
                     }
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 2) * a.NB), acc[mt]);
-                    tc::tmem_ld_wait();
+                    ld_gate(2, acc);
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -461,9 +494,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         if (!ok) break;
                         tc::tc_fence_after_sync();
                     }
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 0) * a.NB), acc[mt]);
-                    tc::tmem_ld_wait();
+                    ld_gate(0, acc);
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -476,9 +507,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         if (!ok) break;
                         tc::tc_fence_after_sync();
                     }
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 1) * a.NB), acc[mt]);
-                    tc::tmem_ld_wait();
+                    ld_gate(1, acc);
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -492,9 +521,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         tc::tc_fence_after_sync();
                         waited = true;
                     }
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) tc::tmem_ld4(ta0 + (uint32_t)((mt * 3 + 2) * a.NB), acc[mt]);
-                    tc::tmem_ld_wait();
+                    ld_gate(2, acc);
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -514,10 +541,23 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
                         int32_t az[CH], ar[CH], an[CH];
-                        const uint32_t ta = ta0 + (uint32_t)(mt * 3 * a.NB);
+                        const uint32_t ta = ta0 + (uint32_t)(mt * 3 * KP * a.NB);
                         tc::tmem_ld4(ta, az);
-                        tc::tmem_ld4(ta + a.NB, ar);
-                        tc::tmem_ld4(ta + 2 * a.NB, an);
+                        tc::tmem_ld4(ta + KP * a.NB, ar);
+                        tc::tmem_ld4(ta + 2 * KP * a.NB, an);
+                        if (KP == 2) {
+                            int32_t bz[CH], br_[CH], bn[CH];
+                            tc::tmem_ld4(ta + a.NB, bz);
+                            tc::tmem_ld4(ta + 3 * a.NB, br_);
+                            tc::tmem_ld4(ta + 5 * a.NB, bn);
+                            tc::tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < CH; ++i) {
+                                az[i] += bz[i];
+                                ar[i] += br_[i];
+                                an[i] += bn[i];
+                            }
+                        }
                         tc::tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < CH; ++i) {
@@ -674,7 +714,7 @@ cudaError_t launch_any(bool fused, bool narrow, int ih_bytes, int MT, bool floor
 }  // namespace
 
 bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, int r_where,
-                      int mt_opt, int ng_opt, RecMmaPlan *out) {
+                      int mt_opt, int ng_opt, int kp_opt, RecMmaPlan *out) {
     if (Hpad > 1024) return false;                 // K-slab loops are unrolled to 8
     const int KBn = Hpad / 128;
     // One 128-unit tile per CTA.  Two tiles per CTA for 128 < H <= 256 (one CTA per group, no
@@ -684,11 +724,11 @@ bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_tab
     const int P = (H + 128 * MT - 1) / (128 * MT);  // cluster size: 1..8 (the portable maximum)
     if (P > 8 || P > sms) return false;
     const int groups_max = std::max(1, sms / P);
-    // Rows per cluster, then sub-groups per CTA (ng_opt: 0 auto, 1, 2).  Two sub-groups let the MMAs
-    // of one overlap the cells of the other; taken where a cluster has at least 32 rows anyway.
+    // Rows per cluster, then sub-groups per CTA (ng_opt: 0 auto = 1, 1, 2).  Two sub-groups let the
+    // MMAs of one overlap the cells of the other; measured no faster so far (the warps' own
+    // instruction latencies between two chunks fill the time), so only on request.
     int RC = ((B + groups_max - 1) / groups_max + 15) / 16 * 16;
     int NG = ng_opt == 2 ? 2 : 1;
-    if (ng_opt == 0 && RC >= 32) NG = 2;
     if (NG == 2) RC = std::max(RC, 32);
     int NB = (RC / NG + 15) / 16 * 16;
     const int nb_cap = (MT == 2 ? 64 : 128) / NG;  // 3 * MT * NB * NG accumulator columns <= 512
@@ -698,7 +738,13 @@ bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_tab
     // memory (32 columns each; r_where: 0 auto, 1 none, 2 at least one), the rest stays in
     // shared-memory slots; the slots also stage the tensor-memory tiles, up to 12 per pass.
     for (;; NB -= 16) {
-        const int acc_cols = (3 * MT * NB * NG + 31) / 32 * 32;
+        // two K halves with accumulators of their own where K has two slabs and the whole slice of R still
+        // fits tensor memory beside them
+        int KP = (kp_opt == 2 && KBn >= 2) ? 2 : 1;
+        if ((3 * MT * NB * NG * KP + 31) / 32 * 32 + n_tiles * 32 > 512 && (3 * MT * NB * NG + 31) / 32 * 32 + n_tiles * 32 <= 512)
+            KP = 1;
+        if (3 * MT * NB * NG * KP > 384) KP = 1;
+        const int acc_cols = (3 * MT * NB * NG * KP + 31) / 32 * 32;
         int tmem_tiles = r_where == 1 ? 0 : std::max(0, std::min(n_tiles, (512 - acc_cols) / 32));
         // a slice that does not fit tensor memory as a whole but fits shared memory stays there as
         // a whole: the split form needs a slower, rolled MMA issue loop
@@ -722,6 +768,7 @@ bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_tab
             out->r_tmem_col = tmem_tiles > 0 ? acc_cols : 0;
             out->tmem_tiles = tmem_tiles;
             out->r_slots = r_slots;
+            out->k_parts = KP;
             out->groups_per_launch = out->G;       // clusters are scheduled as SMs free up
             return true;
         }
@@ -757,6 +804,7 @@ int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const
     a.r_tmem_col = pl.r_tmem_col;
     a.tmem_tiles = pl.tmem_tiles;
     a.r_slots = pl.r_slots;
+    a.k_parts = pl.k_parts;
     a.b_off = 0;
     a.b_cnt = a.B;
     const cudaError_t e = launch_any(fused, narrow, ih_bytes, pl.MT, floor, mr, mh, gc_host, a, pl.G * pl.P, pl.smem, stream);

@@ -16,6 +16,8 @@ struct RecMmaArgs {
     int P;            // CTAs per group (slices of the hidden dimension); set by the launcher
     int NB;           // batch rows per group (multiple of 16); set by the launcher
     int NG = 1;       // cluster kernel: independent sub-groups of NB rows per CTA
+    int k_parts = 1;  // cluster kernels: K halves with an issuing warp and accumulators of their own
+    int issue_delay = 0;   // cluster kernel: head start (cycles) of the update gate's MMAs over the reset gate's, and of those over the new gate's
     int b_off, b_cnt; // batch rows [b_off, b_off + b_cnt) are handled by this launch
     int reverse;
     int h_unsigned;   // the state h is stored as uint8 (else int8)
@@ -45,7 +47,7 @@ struct RecMmaArgs {
 
 struct RecMmaPlan {
     int MT = 1, P = 1, NB = 16, NG = 1, G = 1, tmem_cols = 32, groups_per_launch = 1;
-    int r_tmem_col = 0, tmem_tiles = 0, r_slots = 0;
+    int r_tmem_col = 0, tmem_tiles = 0, r_slots = 0, k_parts = 1;
     size_t smem = 0;
 };
 
@@ -71,7 +73,7 @@ int rec_mma_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const Gat
 // The same kernel with the P CTAs of a group as one thread-block cluster exchanging h_t through
 // distributed shared memory (qgru_rec_cluster.cu).  Same plan fields; no cooperative launch.
 bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, int r_where,
-                      int mt_opt, int ng_opt, RecMmaPlan *out);
+                      int mt_opt, int ng_opt, int kp_opt, RecMmaPlan *out);
 
 int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const GateConsts &gc_host,
                        const int8_t *r8, long long r_rows_alloc, long long h_rows_alloc, bool h_unsigned,

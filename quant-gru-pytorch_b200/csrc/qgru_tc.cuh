@@ -42,14 +42,37 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking test of a phase: returns at once, never suspends the thread.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after `budget` clock cycles and returns false.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, long long budget) {
+#ifdef QGRU_POLL
+    if (mbar_test_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_test_wait(bar, parity)) {
+        if (clock64() - t0 > budget) return false;
+    }
+    return true;
+#else
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
         if (clock64() - t0 > budget) return false;
     }
     return true;
+#endif
 }
 
 // ----------------------------------------------------------------------------- TMA

@@ -563,11 +563,15 @@ def forward_calibrate(is_training, time_steps, batch_size, input_size, hidden_si
     return h, v
 
 
-def probe_mma_i8(M=128, N=256, a_in_tmem=False, accumulators=1, mmas=16384, ctas=148, device=0):
-    """Issue rate of tcgen05.mma kind::i8 for one shape (qgru_probe_mma_i8): returns
-    (SM cycles per MMA in a back-to-back chain, aggregate 1e12 int8 ops/s over `ctas` SMs)."""
+def probe_mma_i8(M=128, N=256, a_in_tmem=False, accumulators=1, mmas=16384, ctas=148, device=0, issuers=1,
+                 spinners=3, neighbour_mode=0):
+    """Issue rate of tcgen05.mma kind::i8 for one shape (qgru_probe_mma_i8_ex): returns
+    (SM cycles per MMA in a back-to-back chain of one issuing thread, aggregate 1e12 int8 ops/s
+    over `ctas` SMs and `issuers` issuing warps); `spinners` neighbour warps wait (mode 0), compute (1) or
+    load from shared memory (2) beside them."""
     cyc, tops = C.c_double(), C.c_double()
-    st = _cabi.lib().qgru_probe_mma_i8(int(device), int(M), int(N), int(bool(a_in_tmem)), int(accumulators),
-                                       int(mmas), int(ctas), C.byref(cyc), C.byref(tops))
-    _cabi.check(st, "qgru_probe_mma_i8")
+    st = _cabi.lib().qgru_probe_mma_i8_ex(int(device), int(M), int(N), int(bool(a_in_tmem)), int(accumulators),
+                                          int(mmas), int(ctas), int(issuers), int(spinners), int(neighbour_mode), C.byref(cyc),
+                                          C.byref(tops))
+    _cabi.check(st, "qgru_probe_mma_i8_ex")
     return cyc.value, tops.value

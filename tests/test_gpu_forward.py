@@ -109,7 +109,7 @@ def test_two_tiles_per_cta_option(oracle, cuda_device):
     case = make_case(16, 5, 37, 24, 200, oracle, config_named("cfg2"))
     got, plan, _ = _run(case, cuda_device, opts=(("rec", "mma"), ("tiles_per_cta", "2")))
     assert "MT=2" in plan and "P=1" in plan and np.array_equal(got, _want(oracle, case)), plan
-    got, plan, _ = _run(case, cuda_device, opts=(("rec", "mma"),))
+    got, plan, _ = _run(case, cuda_device, opts=(("rec", "mma"), ("unit_tile", "128")))
     assert "MT=1" in plan and "P=2" in plan and np.array_equal(got, _want(oracle, case)), plan
 
 
@@ -124,8 +124,8 @@ def test_two_subgroups_per_cta(oracle, cuda_device, shape, cfg):
     case = make_case(17, T, B, I, H, oracle, config_named(cfg), with_h0=True)
     want = _want(oracle, case)
     for extra in ((), (("r_resident", "smem"),), (("cell", "generic"),)):
-        if extra == (("r_resident", "smem"),) and H > 512:
-            continue
+        if extra == (("r_resident", "smem"),) and H > 384:
+            continue                      # the slice of R and four state tiles do not fit shared memory together
         got, plan, _ = _run(case, cuda_device, opts=(("rec", "mma"), ("exchange", "cluster"), ("subgroups", "2"), ("unit_tile", "128")) + extra)
         assert "NG=2" in plan and "exchange=cluster_dsmem" in plan, plan
         assert np.array_equal(got, want), plan
@@ -140,7 +140,7 @@ def test_two_subgroups_per_cta(oracle, cuda_device, shape, cfg):
 
 @pytest.mark.parametrize("shape,sm_limit", [((9, 40, 64, 512), 0), ((7, 33, 40, 300), 0), ((6, 70, 24, 128), 0),
                                             ((12, 5, 16, 256), 0), ((4, 200, 48, 384), 0), ((5, 200, 48, 384), 24),
-                                            ((5, 200, 32, 448), 21), ((3, 1, 8, 64), 0), ((30, 64, 32, 512), 0)])
+                                            ((5, 200, 32, 192), 9), ((3, 1, 8, 64), 0), ((30, 64, 32, 512), 0)])
 @pytest.mark.parametrize("cfg", ["default", "cfg2", "sym8_tensor"])
 def test_64_units_per_cta(oracle, cuda_device, shape, sm_limit, cfg):
     """The low-latency form of the cluster recurrence (64 hidden units per CTA, update and reset rows
@@ -157,7 +157,7 @@ def test_64_units_per_cta(oracle, cuda_device, shape, sm_limit, cfg):
     assert "UT=64" in plan and "NG=2" in plan and "cell=fused_shiftfree" in plan, plan
     if sm_limit == 24:
         assert "NB=32" in plan, plan
-    if sm_limit == 21:
+    if sm_limit == 9:
         assert "NB=48" in plan, plan
     assert np.array_equal(got, want), plan
     got, plan, _ = _run(case, cuda_device, opts=opts, f32=True)
