@@ -147,6 +147,12 @@ QGRU_API int64_t qgru_rshift_round(int64_t x, int n);
  * form (one 32x32->64 multiply by the left-aligned multiplier, rounding on the high word) for
  * shifts 17..48 (2..33 when multiplier is 1), else through 64-bit shifts. */
 QGRU_API int32_t qgru_apply_rescale(int32_t x, uint16_t multiplier, int shift);
+/* No counterpart in the reference.  Can x * multiplier / 2^shift be an exact tie (remainder
+ * exactly one half) for some integer x in [lo, hi]?  Where it cannot, rounding half up gives what
+ * the reference's round-half-even gives, and the kernels drop the tie rule (option "tie_rule").
+ * qgru_apply_rescale_half_up is that cheaper rounding, through the kernels' shift-free form. */
+QGRU_API int qgru_rescale_can_tie(uint16_t multiplier, int shift, int64_t lo, int64_t hi);
+QGRU_API int32_t qgru_apply_rescale_half_up(int32_t x, uint16_t multiplier, int shift);
 
 /* Evaluate one LUT the way piecewise_linear does (include/quantize_ops_helper.h:600-606). */
 QGRU_API int32_t qgru_lut_eval(const qgru_lut *lut, int32_t q_x, const qgru_op *in_bw,
@@ -391,6 +397,9 @@ QGRU_API int qgru_probe_mma_i8_ex(int device, int M, int N, int a_in_tmem, int a
  *   "tiles_per_cta" 1 | 2                 cluster recurrence at 128 < H <= 256: 128-unit tiles per CTA
  *   "subgroups" auto | 1 | 2              cluster recurrence: independent batch sub-groups per CTA (with 2,
  *                                         the MMAs of one overlap the cells of the other)
+ *   "tie_rule" auto | always              auto: kernels round half up where the library has proved that no value
+ *                                         in range is an exact tie (same result as round-half-even, fewer
+ *                                         instructions); always: every rescale applies the tie rule
  *   "k_parts" 1 | 2                       cluster recurrence: 1 = one MMA-issuing warp per gate, 2 = one per K half
  *   "issue_delay" n                       cluster recurrence: SM cycles by which the reset gate's MMAs start after
  *                                         the update gate's, and the new gate's after the reset gate's

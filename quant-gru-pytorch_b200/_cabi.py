@@ -71,6 +71,8 @@ SYMBOLS = {
     "qgru_encode_mshift": (C.c_int, [C.c_float, C.POINTER(C.c_uint16), C.POINTER(C.c_int8)]),
     "qgru_rshift_round": (C.c_int64, [C.c_int64, C.c_int]),
     "qgru_apply_rescale": (C.c_int32, [C.c_int32, C.c_uint16, C.c_int]),
+    "qgru_rescale_can_tie": (C.c_int, [C.c_uint16, C.c_int, C.c_int64, C.c_int64]),
+    "qgru_apply_rescale_half_up": (C.c_int32, [C.c_int32, C.c_uint16, C.c_int]),
     "qgru_lut_eval": (C.c_int32, [C.POINTER(Lut), C.c_int32, C.POINTER(Op), C.POINTER(Op)]),
     "qgru_generate_luts": (C.c_int, [C.POINTER(Params)]),
     "qgru_calc_params_from_ranges": (C.c_int, [C.POINTER(Ranges), C.POINTER(Params), _F, _F, _F, _F]),

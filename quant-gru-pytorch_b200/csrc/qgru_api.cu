@@ -184,6 +184,10 @@ int qgru_set_option(qgru_handle *h, const char *name, const char *value) {
         else if (v == "1") h->opt_ng = 1;
         else if (v == "2") h->opt_ng = 2;
         else return fail(h, QGRU_ERR_BAD_ARG, "subgroups: auto|1|2");
+    } else if (n == "tie_rule") {
+        if (v == "auto") h->opt_tie = 0;
+        else if (v == "always") h->opt_tie = 1;
+        else return fail(h, QGRU_ERR_BAD_ARG, "tie_rule: auto|always");
     } else if (n == "k_parts") {
         h->opt_kp = atoi(value) == 2 ? 2 : 1;
     } else if (n == "issue_delay") {
@@ -380,6 +384,10 @@ int qgru_set_params(qgru_handle *h, const qgru_params *p, const float *scale_W,
             const int64_t max_hd = max_abs_diff(op[QGRU_OP_H]), max_hhd = max_abs_diff(op[QGRU_OP_HH_LINEAR]);
             const int64_t lim = 0x7fffffffll;
             if (max_zd * max_hd + max_omz * max_nd >= lim || max_rd * max_hhd >= lim || max_pre >= lim) fused = false;
+            // round-half-up is enough for the cell's two rescales where no operand in range is an exact tie
+            const int64_t rh = max_rd * max_hhd, cb = max_zd * max_hd + max_omz * max_nd;
+            g.cell_notie = (!rescale_can_tie(g.rh_to_n.mult, g.rh_to_n.shift, -rh, rh) &&
+                            !rescale_can_tie(g.uh_to_h.mult, g.uh_to_h.shift, -cb, cb)) ? 1 : 0;
         }
         if (fused) {
             for (int k = 0; k < 3; ++k) {
@@ -478,6 +486,8 @@ int finish_weights(qgru_handle *h, cudaStream_t st) {
         return fail(h, QGRU_ERR_BAD_ARG, "quantized weight outside the 8-bit range its operator declares");
     h->lin_fits32[0] = !(h->h_flags[0] & 8);
     h->lin_fits32[1] = !(h->h_flags[0] & 16);
+    h->lin_notie[0] = !(h->h_flags[0] & 32);
+    h->lin_notie[1] = !(h->h_flags[0] & 64);
     h->tc.valid = false;
     h->rec.valid = false;
     h->rec_cl.valid = false;
@@ -684,7 +694,8 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
         // (the launcher also looks at how the second rescale is applied: table or shift-free scale)
         const bool gemm_fast = lcx.fits32 && h->rs_fast[0] && h->opt_cell != 2;
         rc = tc_gemm_launch(h->tc, (const uint8_t *)h->x8.p, (N + 127) / 128 * 128, h->d_w8[0], h->w8_rows[0],
-                            h->ih.p, N, C, h->Ipad, h->x_uns, ih_bytes, lcx, ps, gemm_fast, h->d_flags + 1, sms, st,
+                            h->ih.p, N, C, h->Ipad, h->x_uns, ih_bytes, lcx, ps, gemm_fast, h->lin_notie[0] && h->opt_tie != 1,
+                            h->d_flags + 1, sms, st,
                             &h->err);
         if (rc == QGRU_OK) {
             used_tc = true;
@@ -739,23 +750,27 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
         // the branch-free fused cell: every scale of the step in shift-free form, 32-bit sums
         const bool fast_cell = fused && use_cluster && h->opt_cell != 2 && a.lc.fits32 && h->rs_fast[1] &&
                                h->gc_host.rh_to_n.mq != 0 && h->gc_host.uh_to_h.mq != 0;
+        // round-half-up suffices where no operand in range can be an exact tie (R*h requantization and the
+        // cell's two rescales): checked when the weights / parameters were set
+        const bool cell_notie = fast_cell && h->lin_notie[1] && h->gc_host.cell_notie != 0 && h->opt_tie != 1;
         if (use_c64)
             rc = rec_c64_launch(h->rec_c64, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256, h->h_uns,
-                                ih_bytes, st, &h->err);
+                                ih_bytes, cell_notie, st, &h->err);
         else if (use_cluster)
             rc = rec_cluster_launch(h->rec_cl, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256,
-                                    h->h_uns, ih_bytes, fused ? fast_cell : h->gc_host.narrow != 0, fused, h->opt_floor, st,
-                                    &h->err);
+                                    h->h_uns, ih_bytes, fused ? fast_cell : h->gc_host.narrow != 0, fused, h->opt_floor,
+                                    cell_notie, st, &h->err);
         else
             rc = rec_mma_launch(h->rec, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256,
                                 h->h_uns, ih_bytes, h->gc_host.narrow != 0, fused, h->coop != 0, st, &h->err);
         if (rc) return rc;
         h->launches += h->rec.launches + h->rec_cl.launches + h->rec_c64.launches - before;
-        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 exchange=%s cell=%s%s UT=%d MT=%d NB=%d NG=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d r_in=%s narrow=%d ih_bytes=%d shiftfree=%d%d%d%d",
+        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 exchange=%s cell=%s%s UT=%d MT=%d NB=%d NG=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d r_in=%s narrow=%d ih_bytes=%d shiftfree=%d%d%d%d tie_free=%d%d",
                  used_tc ? "tcgen05_i8" : "simt_dp4a", use_cluster ? "cluster_dsmem" : "global", fast_cell ? "fused_shiftfree" : fused ? "fused" : "generic", (use_cluster && h->opt_floor) ? "(FLOOR PROBE: no MMAs, no cell)" : "", use_c64 ? 64 : 128, mp.MT, mp.NB, mp.NG, mp.P, mp.G,
                  mp.groups_per_launch, mp.smem, mp.tmem_cols, !use_cluster || mp.tmem_tiles == 0 ? "smem" : ((use_c64 || mp.tmem_tiles == mp.MT * 3 * (h->Hpad / 128)) ? "tmem" : "tmem+smem"),
                  h->gc_host.narrow, ih_bytes, (int)a.lc.fits32,
-                 (int)h->rs_fast[1], h->gc_host.rh_to_n.mq != 0, h->gc_host.uh_to_h.mq != 0);
+                 (int)h->rs_fast[1], h->gc_host.rh_to_n.mq != 0, h->gc_host.uh_to_h.mq != 0,
+                 (int)(used_tc && h->lin_notie[0] && h->opt_tie != 1), (int)cell_notie);
     } else {
         RecArgs a;
         a.T = T; a.B = B; a.H = h->H; a.Hpad = h->Hpad; a.C = C;

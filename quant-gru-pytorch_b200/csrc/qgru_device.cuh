@@ -200,12 +200,13 @@ __device__ __forceinline__ int32_t fused_gate_fast(const GateConsts &gc, uint32_
                                                    int32_t q) {
     return ft_lookup(gc, tab, which, a_pre + ft_lookup(gc, tab, 3 + which, q));
 }
+template <bool Tie = true>
 __device__ __forceinline__ int32_t fused_finish_fast(const GateConsts &gc, uint32_t tab, int32_t a_n, int32_t q_n,
                                                      int32_t z_d, int32_t r_d, int32_t h_old) {
     const int32_t hh_nd = min(max(q_n, gc.hn_clo), gc.hn_chi);        // R*h row of the new gate minus zp
-    const int32_t n_d = ft_lookup(gc, tab, ACT_N, a_n + mul_round_hi(r_d * hh_nd, gc.rh_to_n));
+    const int32_t n_d = ft_lookup(gc, tab, ACT_N, a_n + mul_round_hi<Tie>(r_d * hh_nd, gc.rh_to_n));
     const int32_t comb = z_d * (h_old - gc.zp_h) + (gc.k1 - z_d) * n_d;
-    return min(max(mul_round_hi(comb, gc.uh_to_h) + gc.zp_h, gc.h_lo), gc.h_hi);
+    return min(max(mul_round_hi<Tie>(comb, gc.uh_to_h) + gc.zp_h, gc.h_lo), gc.h_hi);
 }
 
 // Epilogue of a fused linear layer (src/gru_forward_cpu_quant.cc:130-138).
@@ -300,9 +301,10 @@ __device__ __forceinline__ float fs_cell(const FsConsts &fc, const float ih[3], 
 }
 
 // linear_epilogue32 for a scale with the shift-free form.
+template <bool Tie = true>
 __device__ __forceinline__ int32_t linear_epilogue_fast(int32_t acc, const FastLin &f, int32_t zp_out,
                                                         int32_t lo, int32_t hi) {
-    return clampi(lin_round(acc, f) + zp_out, lo, hi);
+    return clampi(lin_round<Tie>(acc, f) + zp_out, lo, hi);
 }
 
 }  // namespace qgru

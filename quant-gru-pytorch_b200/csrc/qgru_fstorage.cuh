@@ -591,7 +591,7 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
     if (h->opt_gemm != 1) {
         PreScale ps{};
         rc = tc_gemm_launch(h->tc, (const uint8_t *)h->x8.p, (N + 127) / 128 * 128, h->d_w8[0], h->w8_rows[0],
-                            h->ih.p, N, C, h->Ipad, h->x_uns, ih_bytes, lcx, ps, false, h->d_flags + 1, sms, st,
+                            h->ih.p, N, C, h->Ipad, h->x_uns, ih_bytes, lcx, ps, false, false, h->d_flags + 1, sms, st,
                             &h->err);
         if (rc == QGRU_OK) used_tc = true;
         else if (rc != QGRU_ERR_UNSUPPORTED || h->opt_gemm == 2) return rc;
@@ -646,7 +646,7 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
         a.fs = fc;
         const unsigned long long before = h->rec_cl.launches;
         rc = rec_cluster_launch(h->rec_cl, cp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256,
-                                h->h_uns, ih_bytes, false, false, false, st, &h->err);
+                                h->h_uns, ih_bytes, false, false, false, false, st, &h->err);
         if (rc) return rc;
         h->launches += h->rec_cl.launches - before;
         snprintf(buf, sizeof(buf), "path=float_storage gemm=%s rec=tcgen05_i8_float_cell exchange=cluster_dsmem NB=%d NG=%d P=%d G=%d smem=%zu tmem_cols=%d ih_bytes=%d gates=%s",

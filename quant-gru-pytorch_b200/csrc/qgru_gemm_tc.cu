@@ -73,7 +73,10 @@ constexpr size_t GEMM_SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256 + PRE_TAB
 // CTAs that share a token-tile sequence (one per channel tile) run side by side, so each x tile
 // is read from L2 by all of them at about the same time.  Halves the operand traffic from L2,
 // which is what bounds the kernel at K = 1024.  Grid = m_tiles * groups CTAs.
-template <bool XUnsigned, typename IhT, bool Fast, bool AStat>
+// Tie = false (with Fast): the requantization rounds half up, which equals the reference's
+// round-half-even because no channel can meet an exact tie in its accumulator range (checked
+// when the weights are set: rescale_can_tie).
+template <bool XUnsigned, typename IhT, bool Fast, bool AStat, bool Tie>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
              IhT *__restrict__ ih, long long N, int C, int Kpad, LinearConsts lc, PreScale ps,
@@ -277,14 +280,14 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                         const int32_t t_lo = gate * ps.table_n + lc.lo - ps.lo, t_hi = t_lo + (lc.hi - lc.lo);
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
-                            y[i] = lds_i32(tb + 4u * (uint32_t)min(max(lin_round(v[i], fl) + t_c, t_lo), t_hi));
+                            y[i] = lds_i32(tb + 4u * (uint32_t)min(max(lin_round<Tie>(v[i], fl) + t_c, t_lo), t_hi));
                     } else if (ps.enabled) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
-                            y[i] = mul_round_hi(linear_epilogue_fast(v[i], fl, lc.zp_out, lc.lo, lc.hi) - ps.zp_ih, pre_rs) + pre_zp;
+                            y[i] = mul_round_hi(linear_epilogue_fast<Tie>(v[i], fl, lc.zp_out, lc.lo, lc.hi) - ps.zp_ih, pre_rs) + pre_zp;
                     } else {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) y[i] = linear_epilogue_fast(v[i], fl, lc.zp_out, lc.lo, lc.hi);
+                        for (int i = 0; i < 16; ++i) y[i] = linear_epilogue_fast<Tie>(v[i], fl, lc.zp_out, lc.lo, lc.hi);
                     }
                 } else if (lc.fs != nullptr) {
                     // float-storage forward: the reference's float requantization of the exact sum
@@ -329,7 +332,7 @@ size_t astat_smem(int Kpad) {
     return (size_t)(Kpad / KB) * GM * KB + (size_t)STAGES * GN * KB + 1024 + 256 + PRE_TAB_MAX * 4;
 }
 
-template <bool XU, typename IhT, bool Fast>
+template <bool XU, typename IhT, bool Fast, bool Tie>
 cudaError_t launch_f(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long long N, int C, int Kpad,
                      LinearConsts lc, PreScale ps, int *abort_flag, int sms, int order, cudaStream_t st) {
     const int m_tiles = (C + GM - 1) / GM;
@@ -341,7 +344,7 @@ cudaError_t launch_f(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, lon
     const bool fits = astat_smem(Kpad) <= SMEM_LIMIT && m_tiles <= sms;
     const bool astat = fits && order == 2;
     if (astat) {
-        auto kern = k_gemm_wx_tc<XU, IhT, Fast, true>;
+        auto kern = k_gemm_wx_tc<XU, IhT, Fast, true, Tie>;
         const size_t smem = astat_smem(Kpad);
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
@@ -349,7 +352,7 @@ cudaError_t launch_f(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, lon
         kern<<<(unsigned)(m_tiles * groups), GEMM_THREADS, smem, st>>>(mw, mx, (IhT *)ih, N, C, Kpad, lc, ps, abort_flag);
         return cudaGetLastError();
     }
-    auto kern = k_gemm_wx_tc<XU, IhT, Fast, false>;
+    auto kern = k_gemm_wx_tc<XU, IhT, Fast, false, Tie>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM);
     if (e != cudaSuccess) return e;
     const long long tiles = (long long)m_tiles * n_tiles;
@@ -360,16 +363,18 @@ cudaError_t launch_f(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, lon
 
 template <bool XU, typename IhT>
 cudaError_t launch(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long long N, int C, int Kpad,
-                   LinearConsts lc, PreScale ps, bool fast, int *abort_flag, int sms, int order, cudaStream_t st) {
-    return fast ? launch_f<XU, IhT, true>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, order, st)
-                : launch_f<XU, IhT, false>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, order, st);
+                   LinearConsts lc, PreScale ps, bool fast, bool notie, int *abort_flag, int sms, int order,
+                   cudaStream_t st) {
+    if (fast && notie) return launch_f<XU, IhT, true, false>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, order, st);
+    return fast ? launch_f<XU, IhT, true, true>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, order, st)
+                : launch_f<XU, IhT, false, true>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, order, st);
 }
 
 }  // namespace
 
 int tc_gemm_launch(TcGemmState &s, const uint8_t *x8, long long x_rows_alloc, const int8_t *w8,
                    long long w_rows_alloc, void *ih, long long N, int C, int Kpad, bool x_unsigned,
-                   int ih_bytes, LinearConsts lc, PreScale ps, bool fast, int *abort_flag, int sms,
+                   int ih_bytes, LinearConsts lc, PreScale ps, bool fast, bool notie, int *abort_flag, int sms,
                    cudaStream_t stream, std::string *err) {
     if (Kpad % KB != 0 || x_rows_alloc < (N + GN - 1) / GN * GN || w_rows_alloc < (C + GM - 1) / GM * GM) {
         if (err) *err = "tcgen05 GEMM needs K padded to 128 and operand rows padded to the tile";
@@ -397,14 +402,14 @@ int tc_gemm_launch(TcGemmState &s, const uint8_t *x8, long long x_rows_alloc, co
     fast = fast && (!ps.enabled || tab || (ps.to[0].mq != 0 && ps.to[1].mq != 0 && ps.to[2].mq != 0));
     cudaError_t e;
     if (ih_bytes == 1)
-        e = x_unsigned ? launch<true, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, s.order, stream)
-                       : launch<false, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, s.order, stream);
+        e = x_unsigned ? launch<true, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, stream)
+                       : launch<false, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, stream);
     else if (ih_bytes == 2)
-        e = x_unsigned ? launch<true, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, s.order, stream)
-                       : launch<false, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, s.order, stream);
+        e = x_unsigned ? launch<true, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, stream)
+                       : launch<false, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, stream);
     else
-        e = x_unsigned ? launch<true, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, s.order, stream)
-                       : launch<false, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, abort_flag, sms, s.order, stream);
+        e = x_unsigned ? launch<true, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, stream)
+                       : launch<false, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, stream);
     if (e != cudaSuccess) {
         if (err) *err = std::string("tcgen05 GEMM launch: ") + cudaGetErrorString(e);
         return QGRU_ERR_CUDA;

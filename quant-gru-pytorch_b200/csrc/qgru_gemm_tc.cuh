@@ -28,7 +28,7 @@ struct TcGemmState {
 // Returns QGRU_ERR_UNSUPPORTED when the shapes do not meet that, QGRU_ERR_CUDA on failure.
 int tc_gemm_launch(TcGemmState &st, const uint8_t *x8, long long x_rows_alloc, const int8_t *w8,
                    long long w_rows_alloc, void *ih, long long N, int C, int Kpad, bool x_unsigned,
-                   int ih_bytes, LinearConsts lc, PreScale ps, bool fast, int *abort_flag, int sms,
+                   int ih_bytes, LinearConsts lc, PreScale ps, bool fast, bool notie, int *abort_flag, int sms,
                    cudaStream_t stream, std::string *err);
 
 }  // namespace qgru

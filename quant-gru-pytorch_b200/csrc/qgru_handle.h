@@ -46,6 +46,7 @@ struct qgru_handle {
     int opt_ng = 0;                          // cluster recurrence: sub-groups per CTA (0 auto, 1, 2)
     int opt_kp = 1;                          // cluster recurrence: K halves with issuers of their own (1, 2)
     int opt_issue_delay = 0;                 // cluster recurrence: head start of a gate's MMAs over the next gate's, cycles
+    int opt_tie = 0;                         // 0: drop the tie rule where it provably cannot matter, 1: always apply it
     int opt_ut = 0;                          // cluster recurrence: hidden units per CTA (0 auto, 64, 128)
 #ifdef QGRU_STAMPS
     long long *dbg_stamps = nullptr;
@@ -67,6 +68,7 @@ struct qgru_handle {
     int8_t *d_w8[2] = {nullptr, nullptr};     // W8 [3H][Ipad], R8 [3H][Hpad] (rows over-allocated)
     long long w8_rows[2] = {0, 0};
     bool lin_fits32[2] = {false, false};      // acc + corr fits int32 (x side, h side)
+    bool lin_notie[2] = {false, false};       // no channel of that layer's requantization can meet an exact tie
     bool rs_fast[2] = {false, false};   // every per-channel GEMM rescale has the shift-free form
     int *d_flags = nullptr;                   // [0] data errors, [1] barrier abort
     int *h_flags = nullptr;                   // pinned mirror

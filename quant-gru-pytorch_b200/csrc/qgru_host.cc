@@ -580,6 +580,17 @@ int32_t qgru_apply_rescale(int32_t x, uint16_t multiplier, int shift) {
     return rescale32(x, r);
 }
 
+int qgru_rescale_can_tie(uint16_t multiplier, int shift, int64_t lo, int64_t hi) {
+    return rescale_can_tie((int32_t)multiplier, shift, lo, hi) ? 1 : 0;
+}
+
+int32_t qgru_apply_rescale_half_up(int32_t x, uint16_t multiplier, int shift) {
+    Rescale r{(int32_t)multiplier, shift, 0, 0, 0, 0, 0, 0};
+    set_fast_form(&r);
+    if (r.mq == 0) return rescale32(x, r);
+    return mul_round_hi<false>(x, r);
+}
+
 int32_t qgru_lut_eval(const qgru_lut *lut, int32_t q_x, const qgru_op *in_bw,
                       const qgru_op *out_bw) {
     return lut_eval(*lut, q_x, *in_bw, *out_bw);

@@ -58,6 +58,7 @@ struct GateConsts {
     // point).  hn_clo/hn_chi clamp the new gate's R*h row in the same zero-point-free domain.
     int32_t fi_c[5], fi_lo[5], fi_hi[5];
     int32_t hn_clo, hn_chi;
+    int32_t cell_notie;                   // 1: neither rescale of the fused cell can meet an exact tie (rescale_can_tie)
     qgru_lut lut[3];
 };
 

@@ -141,6 +141,8 @@ __global__ void k_channel_consts(const int32_t *__restrict__ bias_q,
     // acc + corr must stay inside int32 for the one-multiply epilogue
     const int64_t mag = c < 0 ? -c : c;
     if (mag + acc_bound >= 0x7fffffffll) atomicOr(flags, flag_bit);
+    // can this channel's requantization meet an exact tie anywhere in its accumulator range?
+    if (rescale_can_tie(rs[m].mult, rs[m].shift, c - acc_bound, c + acc_bound)) atomicOr(flags, flag_bit << 2);
 }
 
 // ------------------------------------------------ input projection, SIMT dp4a form (a1)

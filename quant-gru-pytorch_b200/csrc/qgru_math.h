@@ -91,16 +91,41 @@ QG_HD int32_t round_tie_even(int64_t t, int32_t e, int32_t emask) {
     return ((((uint32_t)hi & (uint32_t)emask) | lo) == 0u) ? (q & ~1) : q;
 }
 
-// Round-half-even of x * mult / 2^shift through the shift-free form.
+// Round-half-even of x * mult / 2^shift through the shift-free form.  Tie = false drops the
+// tie rule (round half up): equal wherever no operand can produce an exact tie, which the host
+// proves per scale with rescale_can_tie before it picks that form.
+template <bool Tie = true>
 QG_HD int32_t mul_round_hi(int32_t x, const Rescale &r) {
     const int64_t add = (int64_t)(((uint64_t)(uint32_t)r.add_hi << 32) | (uint64_t)r.add_lo);
-    return round_tie_even((int64_t)x * (int64_t)r.mq + add, r.e, r.emask);
+    const int64_t t = (int64_t)x * (int64_t)r.mq + add;
+    if (Tie) return round_tie_even(t, r.e, r.emask);
+    return (int32_t)(t >> 32) >> r.e;
 }
 
 // Round-half-even of (acc + corr) * mult / 2^shift with corr folded into f's addend.
+template <bool Tie = true>
 QG_HD int32_t lin_round(int32_t acc, const FastLin &f) {
     const int64_t k = (int64_t)(((uint64_t)(uint32_t)f.k_hi << 32) | (uint64_t)f.k_lo);
-    return round_tie_even((int64_t)acc * (int64_t)f.mq + k, f.e, f.emask);
+    const int64_t t = (int64_t)acc * (int64_t)f.mq + k;
+    if (Tie) return round_tie_even(t, f.e, f.emask);
+    return (int32_t)(t >> 32) >> f.e;
+}
+
+// Can x * mult / 2^shift be an exact tie (remainder exactly one half) for some integer x in
+// [lo, hi]?  x * mult = q * 2^shift + 2^(shift-1) needs x * mult to hold the factor 2 exactly
+// shift - 1 times: with t = trailing zeros of mult, x must be an odd multiple of
+// 2^(shift-1-t).  No such x in the interval: round-half-even and round-half-up agree on it.
+QG_HD bool rescale_can_tie(int32_t mult, int32_t shift, int64_t lo, int64_t hi) {
+    if (shift <= 0 || mult <= 0 || lo > hi) return false;   // left shift: no remainder
+    int t = 0;
+    while (((mult >> t) & 1) == 0) ++t;
+    const int need = shift - 1 - t;
+    if (need < 0) return false;          // x * mult is a multiple of 2^shift for every x
+    if (need >= 62) return false;        // only x = 0 has that many factors of two, and 0 is no tie
+    // multiples of 2^n in [lo, hi]: floor(hi / 2^n) - ceil(lo / 2^n) + 1
+    const int64_t n1 = (hi >> need) - (-((-lo) >> need)) + 1;
+    const int64_t n2 = (hi >> (need + 1)) - (-((-lo) >> (need + 1))) + 1;
+    return n1 - n2 > 0;
 }
 
 // FastLin of a channel: the scale's shift-free form and its constant corr (|corr| < 2^31).

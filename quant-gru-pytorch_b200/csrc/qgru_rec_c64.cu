@@ -75,7 +75,9 @@ __device__ __forceinline__ int32_t lookup(uint32_t tab, int32_t v, int32_t c, in
     return lds_i32(tab + 4u * (uint32_t)min(max(v + c, lo), hi));
 }
 
-template <typename IhT>
+// Tie = false: the rescales round half up, equal to round-half-even where no operand can be an
+// exact tie (rescale_can_tie, checked on the host).
+template <typename IhT, bool Tie>
 __global__ void __launch_bounds__(REC_THREADS, 1)
 k_recurrence_c64(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_h,
                  const __grid_constant__ GateConsts gc, RecMmaArgs a) {
@@ -319,7 +321,7 @@ k_recurrence_c64(const __grid_constant__ CUtensorMap map_r, const __grid_constan
                     tc::tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
-                        gd[i] = lookup(tab, ihg[i] + lookup(tab, lin_round(acc[i], fl_g), hc_c, hc_lo, hc_hi), gt_c, gt_lo, gt_hi);
+                        gd[i] = lookup(tab, ihg[i] + lookup(tab, lin_round<Tie>(acc[i], fl_g), hc_c, hc_lo, hc_hi), gt_c, gt_lo, gt_hi);
                     // the partner finishes the other two columns: it gets this lane's gate value of those
                     const int32_t rc0 = __shfl_xor_sync(0xffffffffu, half ? gd[0] : gd[2], 16);
                     const int32_t rc1 = __shfl_xor_sync(0xffffffffu, half ? gd[1] : gd[3], 16);
@@ -346,8 +348,8 @@ k_recurrence_c64(const __grid_constant__ CUtensorMap map_r, const __grid_constan
                     const int32_t s3 = __shfl_xor_sync(0xffffffffu, acc[3], 16);
                     const int32_t an0 = half ? s2 : acc[0], an1 = half ? s3 : acc[1];
                     int32_t hn[2];
-                    hn[0] = fused_finish_fast(gc, tab, ihn[0], lin_round(an0, fl_n), zd0, rd0, hold[0]);
-                    hn[1] = fused_finish_fast(gc, tab, ihn[1], lin_round(an1, fl_n), zd1, rd1, hold[1]);
+                    hn[0] = fused_finish_fast<Tie>(gc, tab, ihn[0], lin_round<Tie>(an0, fl_n), zd0, rd0, hold[0]);
+                    hn[1] = fused_finish_fast<Tie>(gc, tab, ihn[1], lin_round<Tie>(an1, fl_n), zd1, rd1, hold[1]);
                     // h_t[b][j] = element (row b, K index j) of the next B tile: gather the bytes of four
                     // consecutive units of one row into a word, store it into this CTA's tile and send it
                     // to the peers' (absent rows and units travel too: the peers count on every byte)
@@ -414,10 +416,10 @@ k_recurrence_c64(const __grid_constant__ CUtensorMap map_r, const __grid_constan
     if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
 }
 
-template <typename IhT>
+template <typename IhT, bool Tie>
 cudaError_t launch64(const CUtensorMap &mr, const CUtensorMap &mh, const GateConsts &gc, RecMmaArgs &a, int grid,
                      size_t smem, cudaStream_t st) {
-    auto kern = k_recurrence_c64<IhT>;
+    auto kern = k_recurrence_c64<IhT, Tie>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
@@ -478,8 +480,8 @@ bool rec_c64_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, 
 }
 
 int rec_c64_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const GateConsts &gc_host, const int8_t *r8,
-                   long long r_rows_alloc, long long h_rows_alloc, bool h_unsigned, int ih_bytes, cudaStream_t stream,
-                   std::string *err) {
+                   long long r_rows_alloc, long long h_rows_alloc, bool h_unsigned, int ih_bytes, bool notie,
+                   cudaStream_t stream, std::string *err) {
     if (r_rows_alloc < a.C + 144) {
         if (err) *err = "packed R lacks the zero rows the 64-unit recurrence reads";
         return QGRU_ERR_UNSUPPORTED;
@@ -512,8 +514,12 @@ int rec_c64_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const Gat
     a.k_parts = pl.k_parts;
     a.b_off = 0;
     a.b_cnt = a.B;
-    const cudaError_t e = ih_bytes == 2 ? launch64<int16_t>(mr, mh, gc_host, a, pl.G * pl.P, pl.smem, stream)
-                                        : launch64<int32_t>(mr, mh, gc_host, a, pl.G * pl.P, pl.smem, stream);
+    const int grid = pl.G * pl.P;
+    const cudaError_t e =
+        notie ? (ih_bytes == 2 ? launch64<int16_t, false>(mr, mh, gc_host, a, grid, pl.smem, stream)
+                               : launch64<int32_t, false>(mr, mh, gc_host, a, grid, pl.smem, stream))
+              : (ih_bytes == 2 ? launch64<int16_t, true>(mr, mh, gc_host, a, grid, pl.smem, stream)
+                               : launch64<int32_t, true>(mr, mh, gc_host, a, grid, pl.smem, stream));
     if (e != cudaSuccess) {
         if (err) *err = std::string("recurrence (64-unit cluster) launch: ") + cudaGetErrorString(e);
         cudaGetLastError();

@@ -117,7 +117,9 @@ constexpr int MAX_NG = 2;                        // sub-groups of batch rows per
 // Floor = true is a measurement aid: the same launch, barriers, state exchange and output stores
 // with the MMAs and the cell left out (h_t = h_{t-1}); its duration is the synchronisation floor
 // the real kernel's time per step is quoted against.
-template <typename IhT, bool Narrow, bool Fused, int MT, bool Floor>
+// Tie = false (branch-free tabulated cell only): the rescales round half up, which equals the
+// reference's round-half-even because none of them can meet an exact tie (rescale_can_tie).
+template <typename IhT, bool Narrow, bool Fused, int MT, bool Floor, bool Tie>
 __global__ void __launch_bounds__(REC_THREADS, 1)
 k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_h,
                      const __grid_constant__ GateConsts gc, RecMmaArgs a) {
@@ -456,7 +458,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                         for (int i = 0; i < CH; ++i)
-                            zd[mt][i] = fused_gate_fast(gc, tab, ACT_Z, ihv[mt][i][0], lin_round(acc[mt][i], fl[mt][0]));
+                            zd[mt][i] = fused_gate_fast(gc, tab, ACT_Z, ihv[mt][i][0], lin_round<Tie>(acc[mt][i], fl[mt][0]));
                     // reset gate
                     if (!waited) {
                         ok = tc::mbar_wait(&md[1], par, WAIT_BUDGET);
@@ -468,7 +470,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                         for (int i = 0; i < CH; ++i)
-                            rd[mt][i] = fused_gate_fast(gc, tab, ACT_R, ihv[mt][i][1], lin_round(acc[mt][i], fl[mt][1]));
+                            rd[mt][i] = fused_gate_fast(gc, tab, ACT_R, ihv[mt][i][1], lin_round<Tie>(acc[mt][i], fl[mt][1]));
                     // new gate and the state update
                     if (!waited) {
                         ok = tc::mbar_wait(&md[2], par, WAIT_BUDGET);
@@ -481,7 +483,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                         for (int i = 0; i < CH; ++i)
-                            hn[mt][i] = fused_finish_fast(gc, tab, ihv[mt][i][2], lin_round(acc[mt][i], fl[mt][2]),
+                            hn[mt][i] = fused_finish_fast<Tie>(gc, tab, ihv[mt][i][2], lin_round<Tie>(acc[mt][i], fl[mt][2]),
                                                           zd[mt][i], rd[mt][i], hold[mt][i]);
                 } else if (!Fused && !Narrow && a.fs_on) {
                     // float-storage forward: float requantization of the exact sums, real sigmoid /
@@ -663,10 +665,10 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
     if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
 }
 
-template <typename IhT, bool Narrow, bool Fused, int MT, bool Floor>
+template <typename IhT, bool Narrow, bool Fused, int MT, bool Floor, bool Tie = true>
 cudaError_t launch_one(const CUtensorMap &mr, const CUtensorMap &mh, const GateConsts &gc, RecMmaArgs &a,
                        int grid, size_t smem, cudaStream_t st) {
-    auto kern = k_recurrence_cluster<IhT, Narrow, Fused, MT, Floor>;
+    auto kern = k_recurrence_cluster<IhT, Narrow, Fused, MT, Floor, Tie>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
@@ -691,13 +693,23 @@ cudaError_t launch_mt(int MT, const CUtensorMap &mr, const CUtensorMap &mh, cons
                    : launch_one<IhT, Narrow, Fused, 1, false>(mr, mh, gc, a, grid, smem, st);
 }
 
-cudaError_t launch_any(bool fused, bool narrow, int ih_bytes, int MT, bool floor, const CUtensorMap &mr,
+template <typename IhT>
+cudaError_t launch_notie(int MT, const CUtensorMap &mr, const CUtensorMap &mh, const GateConsts &gc, RecMmaArgs &a,
+                         int grid, size_t smem, cudaStream_t st) {
+    return MT == 2 ? launch_one<IhT, true, true, 2, false, false>(mr, mh, gc, a, grid, smem, st)
+                   : launch_one<IhT, true, true, 1, false, false>(mr, mh, gc, a, grid, smem, st);
+}
+
+cudaError_t launch_any(bool fused, bool narrow, int ih_bytes, int MT, bool floor, bool notie, const CUtensorMap &mr,
                        const CUtensorMap &mh, const GateConsts &gc, RecMmaArgs &a, int grid, size_t smem,
                        cudaStream_t st) {
     if (floor)   // the synchronisation-floor measurement exists for the one form the benchmark's headline runs
         return (fused && narrow && ih_bytes == 2 && MT == 1)
                    ? launch_one<int16_t, true, true, 1, true>(mr, mh, gc, a, grid, smem, st)
                    : cudaErrorNotSupported;
+    if (fused && narrow && notie)
+        return ih_bytes == 2 ? launch_notie<int16_t>(MT, mr, mh, gc, a, grid, smem, st)
+                             : launch_notie<int32_t>(MT, mr, mh, gc, a, grid, smem, st);
     if (fused && narrow)   // for the fused cell `narrow` carries "every scale is shift-free"
         return ih_bytes == 2 ? launch_mt<int16_t, true, true>(MT, mr, mh, gc, a, grid, smem, st)
                              : launch_mt<int32_t, true, true>(MT, mr, mh, gc, a, grid, smem, st);
@@ -778,7 +790,8 @@ bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_tab
 
 int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const GateConsts &gc_host,
                        const int8_t *r8, long long r_rows_alloc, long long h_rows_alloc, bool h_unsigned,
-                       int ih_bytes, bool narrow, bool fused, bool floor, cudaStream_t stream, std::string *err) {
+                       int ih_bytes, bool narrow, bool fused, bool floor, bool notie, cudaStream_t stream,
+                       std::string *err) {
     if (!s.valid || s.r8 != r8 || s.h8 != a.h8 || s.r_rows != r_rows_alloc || s.h_rows != h_rows_alloc ||
         s.Hpad != a.Hpad || s.NB != pl.NB) {
         if (!make_map_u8_sw128(reinterpret_cast<CUtensorMap *>(s.map_r), r8, (uint64_t)r_rows_alloc, (uint64_t)a.Hpad, 128) ||
@@ -807,7 +820,7 @@ int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const
     a.k_parts = pl.k_parts;
     a.b_off = 0;
     a.b_cnt = a.B;
-    const cudaError_t e = launch_any(fused, narrow, ih_bytes, pl.MT, floor, mr, mh, gc_host, a, pl.G * pl.P, pl.smem, stream);
+    const cudaError_t e = launch_any(fused, narrow, ih_bytes, pl.MT, floor, notie, mr, mh, gc_host, a, pl.G * pl.P, pl.smem, stream);
     if (e == cudaErrorNotSupported && floor) {
         if (err) *err = "the synchronisation-floor probe exists for the fused shift-free cell with 16-bit W*x+bw only";
         return QGRU_ERR_UNSUPPORTED;

@@ -77,7 +77,8 @@ bool rec_cluster_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_tab
 
 int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const GateConsts &gc_host,
                        const int8_t *r8, long long r_rows_alloc, long long h_rows_alloc, bool h_unsigned,
-                       int ih_bytes, bool narrow, bool fused, bool floor, cudaStream_t stream, std::string *err);
+                       int ih_bytes, bool narrow, bool fused, bool floor, bool notie, cudaStream_t stream,
+                       std::string *err);
 
 // The cluster kernel's low-latency form: 64 hidden units per CTA, two sub-groups, the branch-free
 // tabulated cell only (qgru_rec_c64.cu).  The plan fails where it does not apply (H > 512, or - unless
@@ -85,7 +86,7 @@ int rec_cluster_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const
 bool rec_c64_plan(int H, int Hpad, int B, int sms, int smem_optin, int n_table, bool force, RecMmaPlan *out);
 
 int rec_c64_launch(RecMmaState &s, const RecMmaPlan &pl, RecMmaArgs a, const GateConsts &gc_host, const int8_t *r8,
-                   long long r_rows_alloc, long long h_rows_alloc, bool h_unsigned, int ih_bytes, cudaStream_t stream,
-                   std::string *err);
+                   long long r_rows_alloc, long long h_rows_alloc, bool h_unsigned, int ih_bytes, bool notie,
+                   cudaStream_t stream, std::string *err);
 
 }  // namespace qgru

@@ -204,7 +204,8 @@ def test_large_batch_many_groups(oracle, cuda_device):
 def test_bitwidth_configs(oracle, cuda_device, name):
     for seed, (T, B, I, H) in enumerate([(7, 6, 24, 48), (4, 9, 40, 72)]):
         case = make_case(20 + seed, T, B, I, H, oracle, config_named(name), with_h0=(seed == 1))
-        for opts in ((("rec", "mma"),), (("rec", "gemv"),), (("rec", "mma"), ("cell", "fused")),
+        for opts in ((("rec", "mma"),), (("rec", "mma"), ("tie_rule", "always")), (("rec", "gemv"),),
+                     (("rec", "mma"), ("cell", "fused")),
                      (("rec", "mma"), ("cell", "generic")), (("rec", "dp4a"),),
                      (("rec", "mma"), ("exchange", "global")),
                      (("rec", "mma"), ("exchange", "global"), ("cell", "generic"))):

@@ -230,6 +230,35 @@ def test_quant_param_import_accepts_the_reference_parsers_other_encodings():
             params_mod.GRUQuantParams.from_export_dict({"weight_ih": bad}, H)
 
 
+def test_tie_free_ranges_round_half_up_like_half_even():
+    """qgru_rescale_can_tie: exhaustive on small ranges (it says "tie possible" exactly when some x
+    in the range makes round-half-up differ from the reference's rounding ... or hits an even
+    quotient tie, where both agree), and where it says "no tie" the cheap rounding equals
+    qgru_apply_rescale on every x of the range."""
+    lib = _cabi.lib()
+    rng = np.random.default_rng(5)
+    checked_free = 0
+    for _ in range(400):
+        mult = int(rng.integers(32768, 65536)) if rng.random() < 0.7 else int(1 << rng.integers(0, 16)) * int(rng.integers(1, 4))
+        mult = min(mult, 65535)
+        shift = int(rng.integers(17, 40))
+        lo = int(rng.integers(-3000, 0)) * int(rng.integers(1, 300))
+        hi = lo + int(rng.integers(1, 4000))
+        can = bool(lib.qgru_rescale_can_tie(mult, shift, lo, hi))
+        xs = np.arange(lo, hi + 1, dtype=np.int64)
+        rem = (xs * mult) % (1 << shift)
+        has_tie = bool(np.any(rem == (1 << (shift - 1))))
+        assert can == has_tie, (mult, shift, lo, hi)
+        if not can:
+            for x in xs[:: max(1, len(xs) // 200)]:
+                assert lib.qgru_apply_rescale_half_up(int(x), mult, shift) == lib.qgru_apply_rescale(int(x), mult, shift)
+            checked_free += 1
+    assert checked_free > 50
+    # a tie that round-half-up gets wrong is reported: 3 * 2^15 / 2^16 = 1.5 -> 2 (even), 1 * 2^15 / 2^16 = 0.5 -> 0
+    assert lib.qgru_rescale_can_tie(32768, 16, 1, 1) == 1
+    assert lib.qgru_apply_rescale(1, 32768, 16) == 0 and lib.qgru_rshift_round(1 * 32768, 16) == 0
+
+
 def test_decode_effective_scale_matches_encoding(oracle):
     """qgru_decode_effective_scale == multiplier * 2^-shift of encodeMShift (POT2: 2^-round(-log2 s))."""
     import importlib
