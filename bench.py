@@ -17,8 +17,9 @@ the same calls with pinned host buffers (host->device copy of x and device->host
 every output inside the timed region).  After the timed regions every rank compares rows of
 its GPU result, every timestep, bit for bit with the reference's CPU integer path (`check`);
 with N > 1 the per-rank outputs are all-gathered once over NCCL and compared with the local
-shards (`gather`), and the throughput configuration (batch 4096 split evenly over the N
-GPUs, fixed total work) is timed as the `strong` block.  `--impl reference` times the
+shards (`gather`); at every N the throughput configuration (batch 4096 split evenly over the N
+GPUs, fixed total work) is timed as the `strong` block, and the recurrence is run once more
+without its MMAs and cells to give the synchronisation floor of a timestep.  `--impl reference` times the
 reference's own CPU integer path (oracle/_ref, else the C port) on the box's host cores.
 """
 import argparse
@@ -58,7 +59,7 @@ def parse():
     ap.add_argument("--no-check", action="store_true", help="skip the bit-exact comparison with the CPU path")
     ap.add_argument("--check-rows", type=int, default=0,
                     help="batch rows per direction compared with the CPU path (0: as many as ~10 s of CPU buy)")
-    ap.add_argument("--no-strong", action="store_true", help="skip the fixed-total-work block at N > 1")
+    ap.add_argument("--no-strong", action="store_true", help="skip the fixed-total-work (cfg3, batch 4096 over N GPUs) block")
     ap.add_argument("--calib-batches", type=int, default=0,
                     help="override the number of calibration batches (profiling runs only)")
     ap.add_argument("--rows", type=int, default=0,
@@ -366,7 +367,28 @@ def run_ours(args):
     plan = job.plan()
     ih_bytes = 2 if "ih_bytes=2" in plan else (4 if "ih_bytes=4" in plan else 1)
 
-    # ---- outside the timed regions: bit-exact check of this rank's rows, gather check, strong block
+    # ---- outside the timed regions: synchronisation floor, bit-exact check of this rank's rows, gather
+    # check, strong block
+    floor_us = None
+    try:   # the same recurrence launch without its MMAs and cells: exchange, barriers and output stores only
+        for h in job.handles:
+            h[0].set_option("probe_floor", 1)
+        for _ in range(3):
+            job.step()
+        job.synchronize()
+        if "FLOOR PROBE" in job.plan():
+            fw = job.handles[0][0].timing_window(2)
+            floor_us = fw["recurrence_ms"] / max(1, fw["calls"]) * 1e3 / T
+    except Exception:   # forms of the recurrence without the probe
+        floor_us = None
+    finally:
+        for h in job.handles:
+            h[0].set_option("probe_floor", 0)
+        try:
+            job.step()      # leaves the plan text and the timing ring describing the real kernel again
+            job.synchronize()
+        except Exception:
+            pass
     cores = os.cpu_count() or 1
     threads = max(1, cores // world)
     check = None
@@ -388,7 +410,7 @@ def run_ours(args):
     torch.cuda.empty_cache()
 
     strong = None
-    if world > 1 and not args.no_strong and args.workload == "cfg2":
+    if not args.no_strong and args.workload == "cfg2":
         sI, sH, sB, sT = WORKLOADS[STRONG_WORKLOAD][:4]
         sj = Job(args, STRONG_WORKLOAD, torch, dev, local, rank, world, sB, 0, args.option)
         ms_s = timed(sj.step, args.steps, args.warmup)
@@ -402,7 +424,8 @@ def run_ours(args):
         if not args.no_check:
             res = sj.check(args.check_rows or sj.auto_check_rows(threads, 5.0), threads)
             tot = torch.tensor([res["rows"], res["mismatches"]], device=dev, dtype=torch.int64)
-            dist.all_reduce(tot)
+            if world > 1:
+                dist.all_reduce(tot)
             strong["check"] = {"status": "ok" if int(tot[1]) == 0 else "MISMATCH", "checked_rows": int(tot[0]),
                                "timesteps": sT, "against": res["kind"]}
         sj.close()
@@ -450,6 +473,8 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "kernel": kernel + " (one direction)", "achieved": achieved,
                          "peak": hbm, "unit": "GB/s", "frac": achieved / hbm, "peak_kind": peak_kind,
                          "traffic": traffic, "us_per_timestep": rec_ms * 1e3 / T,
+                         "sync_floor_us_per_timestep": floor_us,
+                         "sync_floor_frac": (floor_us / (rec_ms * 1e3 / T)) if floor_us and rec_ms > 0 else None,
                          "input_gemm_ms": gemm_ms, "recurrence_ms": rec_ms,
                          "whole_forward_frac": (tokens_step / world * bytes_per_token(I, H, ih_bytes) * job_handles /
                                                 ((ms_total / args.steps) * 1e-3) / 1e9) / hbm},
