@@ -312,6 +312,16 @@ QGRU_API int qgru_backward(qgru_handle *h, int T, int B, const float *W_t, const
 QGRU_API int qgru_forward_f32(qgru_handle *h, int T, int B, const float *x, const float *h0,
                               float *h_out, int32_t *x_q_out, unsigned flags, void *stream);
 
+/* No counterpart in the reference (its outputs are fp32 or int32 containers).  qgru_forward_f32
+ * with the output left in its native width: h_q8 [(T+1),B,H] holds the quantized states as 8-bit
+ * values (int8, or uint8 when the h operator is unsigned; slot layout as qgru_forward_i32), a
+ * quarter of the fp32 output's bytes for a caller whose link to the result is the bottleneck
+ * (a host behind PCIe).  The caller dequantizes with (q - zero_point) * scale of the h operator
+ * (scale as qgru_decode_effective_scale gives it): exactly the value qgru_forward_f32 writes.
+ * Needs the 8-bit storage plan (else QGRU_ERR_UNSUPPORTED). */
+QGRU_API int qgru_forward_f32_q8(qgru_handle *h, int T, int B, const float *x, const float *h0,
+                                 uint8_t *h_q8, unsigned flags, void *stream);
+
 /* No counterpart in the reference.  The same result as qgru_forward_i32 for callers that must
  * not allocate device memory at call time (a serving loop with a fixed memory budget, a process
  * whose allocator belongs to another framework, a real-time thread that cannot tolerate the
@@ -409,6 +419,9 @@ QGRU_API int qgru_probe_mma_i8_ex(int device, int M, int N, int a_in_tmem, int a
  *                                         cells left out (results are meaningless); the recurrence time of
  *                                         qgru_last_timing is then the per-step synchronisation floor
  *   "sm_limit" n   use at most n SMs (0 = all);  "spin_limit" n   bound of the group barrier
+ *   "test_withhold_arrive" 0 | 1          failure-path test: with the dp4a recurrence on several CTAs per group,
+ *                                         CTA 0 leaves out one arrival, the group's bounded wait runs out and the
+ *                                         forward reports QGRU_ERR_TIMEOUT; nothing faults or hangs
  * Unknown names or values return QGRU_ERR_BAD_ARG. */
 QGRU_API int qgru_set_option(qgru_handle *h, const char *name, const char *value);
 

@@ -93,6 +93,7 @@ SYMBOLS = {
     "qgru_forward_i32_train": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, _P, _P, C.c_uint, _P]),
     "qgru_forward_i32_static": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, C.c_uint, _P]),
     "qgru_forward_f32": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, _P, C.c_uint, _P]),
+    "qgru_forward_f32_q8": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, C.c_uint, _P]),
     "qgru_forward_i32_host": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, C.c_uint, _P]),
     "qgru_forward_f32_host": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, C.c_uint, _P]),
     "qgru_synchronize": (C.c_int, [_P, _P]),

@@ -201,6 +201,8 @@ int qgru_set_option(qgru_handle *h, const char *name, const char *value) {
     } else if (n == "debug_stamps") {
         h->dbg_stamps = reinterpret_cast<long long *>(strtoull(value, nullptr, 10));
 #endif
+    } else if (n == "test_withhold_arrive") {
+        h->opt_withhold = atoi(value) != 0;
     } else if (n == "probe_floor") {
         h->opt_floor = atoi(value) != 0;
     } else if (n == "sm_limit") {
@@ -619,7 +621,7 @@ int launch_gemv(qgru_handle *h, RecArgs &a, bool fused, cudaStream_t st) {
 
 // Shared tail of the two device entry points, 8-bit path: x8 and the initial state are ready.
 int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsigned flags,
-             cudaStream_t st) {
+             cudaStream_t st, uint8_t *h8_out = nullptr) {
     const long long N = (long long)T * B;
     const int C = h->C;
     int rc;
@@ -736,6 +738,7 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
         a.h8 = (uint8_t *)h->h8.p;
         a.hq_out = hq_out;
         a.hf_out = hf_out;
+        a.h8_out = h8_out;
         a.lc = linear_consts(h, 1);
         a.tables = fused ? h->d_ftables : h->d_tables;
         a.n_table = fused ? h->gc_host.ft_ih_off : h->n_table;   // the GEMM-side table stays out of smem
@@ -781,6 +784,7 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
         a.h8 = (uint8_t *)h->h8.p;
         a.hq_out = hq_out;
         a.hf_out = hf_out;
+        a.h8_out = h8_out;
         a.lc = linear_consts(h, 1);
         a.gc = h->d_gc;
         a.tables = h->d_tables;
@@ -788,6 +792,7 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
         a.bar = h->d_bar;
         a.abort_flag = h->d_flags + 1;
         a.spin_limit = h->spin_limit;
+        a.withhold_arrive = h->opt_withhold ? 1 : 0;
         if (use_gemv) {
             if (fused) {
                 a.tables = h->d_ftables;
@@ -889,7 +894,7 @@ int qgru_forward_i32(qgru_handle *h, int T, int B, const int32_t *x_q, const int
     CK(cudaMemsetAsync(h->d_flags, 0, 2 * sizeof(int), st));
     if (use_generic(h)) {
         k_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
-            h0_q, nullptr, nullptr, h_q, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale, ho.zero_point,
+            h0_q, nullptr, nullptr, h_q, nullptr, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale, ho.zero_point,
             op_qmin(ho), op_qmax(ho), h->d_flags);
         h->launches++;
         return run_generic(h, T, B, x_q, h_q, nullptr, flags, st);
@@ -900,7 +905,7 @@ int qgru_forward_i32(qgru_handle *h, int T, int B, const int32_t *x_q, const int
         x_q, (uint8_t *)h->x8.p, N, h->I, h->Ipad, op_qmin(xo), op_qmax(xo), h->d_flags);
     CK(cudaMemsetAsync(h->h8.p, 0, (size_t)(2 * B + 256) * h->Hpad, st));
     k_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
-        h0_q, nullptr, (uint8_t *)h->h8.p, h_q, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale,
+        h0_q, nullptr, (uint8_t *)h->h8.p, h_q, nullptr, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale,
         ho.zero_point, op_qmin(ho), op_qmax(ho), h->d_flags);
     h->launches += 2;
     CK(cudaGetLastError());
@@ -923,7 +928,7 @@ int qgru_forward_i32_train(qgru_handle *h, int T, int B, const int32_t *x_q, con
     CK(cudaMemsetAsync(h->d_flags, 0, 2 * sizeof(int), st));
     // the step-by-step kernels keep every intermediate the training buffer wants
     k_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
-        h0_q, nullptr, nullptr, h_q, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale, ho.zero_point,
+        h0_q, nullptr, nullptr, h_q, nullptr, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale, ho.zero_point,
         op_qmin(ho), op_qmax(ho), h->d_flags);
     h->launches++;
     return run_generic(h, T, B, x_q, h_q, v_q, flags, st, masks);
@@ -954,7 +959,7 @@ int qgru_forward_f32(qgru_handle *h, int T, int B, const float *x, const float *
         k_quantize_f32_i32<<<grid_for(N * h->I, 256, h->sm_count), 256, 0, st>>>(
             x, x32, N * h->I, h->x_scale, xo.zero_point, op_qmin(xo), op_qmax(xo));
         k_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
-            nullptr, h0, nullptr, (int32_t *)h->hq32.p, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale,
+            nullptr, h0, nullptr, (int32_t *)h->hq32.p, nullptr, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale,
             ho.zero_point, op_qmin(ho), op_qmax(ho), h->d_flags);
         h->launches += 2;
         if ((rc = run_generic(h, T, B, x32, (int32_t *)h->hq32.p, nullptr, flags, st))) return rc;
@@ -970,11 +975,40 @@ int qgru_forward_f32(qgru_handle *h, int T, int B, const float *x, const float *
         x, (uint8_t *)h->x8.p, x_q_out, N, h->I, h->Ipad, h->x_scale, xo.zero_point, op_qmin(xo), op_qmax(xo));
     CK(cudaMemsetAsync(h->h8.p, 0, (size_t)(2 * B + 256) * h->Hpad, st));
     k_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
-        nullptr, h0, (uint8_t *)h->h8.p, nullptr, h_out, B, h->H, h->Hpad, init_slot, h->h_scale,
+        nullptr, h0, (uint8_t *)h->h8.p, nullptr, h_out, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale,
         ho.zero_point, op_qmin(ho), op_qmax(ho), h->d_flags);
     h->launches += 2;
     CK(cudaGetLastError());
     return run_fast(h, T, B, nullptr, h_out, flags, st);
+}
+
+int qgru_forward_f32_q8(qgru_handle *h, int T, int B, const float *x, const float *h0, uint8_t *h_q8,
+                        unsigned flags, void *stream) {
+    if (!h || !x || !h_q8) return QGRU_ERR_BAD_ARG;
+    int rc = check_forward_args(h, T, B);
+    if (rc) return rc;
+    if (use_generic(h))
+        return fail(h, QGRU_ERR_UNSUPPORTED, "the 8-bit output needs the 8-bit storage plan (x, h, W, R at most 8 bits)");
+    CK(cudaSetDevice(h->device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const long long N = (long long)T * B;
+    const qgru_op &xo = h->p.op[QGRU_OP_X], &ho = h->p.op[QGRU_OP_H];
+    const long long init_slot = (flags & QGRU_FLAG_REVERSE) ? T : 0;
+    h->ev = h->ring[h->calls % qgru_handle::kRing];
+    h->calls++;
+    CK(cudaEventRecord(h->ev[0], st));
+    CK(cudaMemsetAsync(h->d_flags, 0, 2 * sizeof(int), st));
+    if ((rc = ensure(h, h->x8, (size_t)((N + 127) / 128 * 128) * h->Ipad))) return rc;
+    if ((rc = ensure(h, h->h8, (size_t)(2 * B + 256) * h->Hpad))) return rc;
+    k_quantize_rows_f32<<<grid_for(N * (h->Ipad / 4), 256, h->sm_count), 256, 0, st>>>(
+        x, (uint8_t *)h->x8.p, nullptr, N, h->I, h->Ipad, h->x_scale, xo.zero_point, op_qmin(xo), op_qmax(xo));
+    CK(cudaMemsetAsync(h->h8.p, 0, (size_t)(2 * B + 256) * h->Hpad, st));
+    k_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
+        nullptr, h0, (uint8_t *)h->h8.p, nullptr, nullptr, h_q8, B, h->H, h->Hpad, init_slot, h->h_scale,
+        ho.zero_point, op_qmin(ho), op_qmax(ho), h->d_flags);
+    h->launches += 2;
+    CK(cudaGetLastError());
+    return run_fast(h, T, B, nullptr, nullptr, flags, st, h_q8);
 }
 
 int qgru_synchronize(qgru_handle *h, void *stream) {
@@ -1166,7 +1200,7 @@ extern "C" int qgru_forward_i32_static(qgru_handle *h, int T, int B, const int32
     k_narrow_rows_i32<<<grid_for(N * (h->Ipad / 4), 256, h->sm_count), 256, 0, st>>>(
         x_q, x8, N, h->I, h->Ipad, op_qmin(xo), op_qmax(xo), h->d_flags);
     k_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
-        h0_q, nullptr, h8, h_q, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale, ho.zero_point, op_qmin(ho),
+        h0_q, nullptr, h8, h_q, nullptr, nullptr, B, h->H, h->Hpad, init_slot, h->h_scale, ho.zero_point, op_qmin(ho),
         op_qmax(ho), h->d_flags);
     CK(cudaEventRecord(h->ev[1], st));
     const LinearConsts lcx = linear_consts(h, 0);

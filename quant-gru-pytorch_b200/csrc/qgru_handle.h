@@ -51,6 +51,7 @@ struct qgru_handle {
 #ifdef QGRU_STAMPS
     long long *dbg_stamps = nullptr;
 #endif
+    bool opt_withhold = false;               // failure-path test of the dp4a recurrence's bounded group barrier
     bool opt_floor = false;                  // cluster recurrence: run the synchronisation-floor probe instead
     // device state that lives with the handle
     GateConsts *d_gc = nullptr;

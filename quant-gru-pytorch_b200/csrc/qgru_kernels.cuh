@@ -212,7 +212,8 @@ k_gemm_wx_simt(const uint8_t *__restrict__ x8, const int8_t *__restrict__ w8, Ih
 // the float entry point dequantizes that slot like every other, :704).
 __global__ void k_init_state(const int32_t *__restrict__ h0_q, const float *__restrict__ h0_f,
                              uint8_t *__restrict__ h8, int32_t *__restrict__ hq_out,
-                             float *__restrict__ hf_out, int B, int H, int Hpad, long long slot,
+                             float *__restrict__ hf_out, uint8_t *__restrict__ h8_out, int B, int H, int Hpad,
+                             long long slot,
                              float scale, int32_t zp, int32_t lo, int32_t hi, int *err) {
     const long long total = (long long)B * Hpad;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -231,6 +232,7 @@ __global__ void k_init_state(const int32_t *__restrict__ h0_q, const float *__re
             const long long o = slot * B * H + (long long)b * H + j;
             if (hq_out) hq_out[o] = q;
             if (hf_out) hf_out[o] = (float)(q - zp) * scale;
+            if (h8_out) h8_out[o] = (uint8_t)q;
         }
         if (h8) h8[i] = (uint8_t)q;
     }
@@ -249,6 +251,7 @@ struct RecArgs {
     uint8_t *h8;           // [2][B][Hpad] ping-pong state
     int32_t *hq_out;       // [(T+1)][B][H] or null
     float *hf_out;         // [(T+1)][B][H] or null
+    uint8_t *h8_out = nullptr;   // [(T+1)][B][H] or null: the quantized state in its 8-bit container
     LinearConsts lc;       // R*h + br epilogue
     const GateConsts *gc;  // device copy
     const int32_t *tables; // activation tables, gc->table_off indexes into it
@@ -256,6 +259,7 @@ struct RecArgs {
     unsigned *bar;         // one counter per group, 32 words apart
     int *abort_flag;       // set when a barrier wait ran out; every CTA then leaves
     unsigned spin_limit;
+    int withhold_arrive = 0;   // failure-path test: CTA 0 skips its arrival after step 0, so its group's wait runs out
     // float-storage forward (k_recurrence_gemv with Cell 3): the float cell of the reference's
     // quantGRUForwardFP; fs_chan = [3][C] offset, bias term, scale ratio of R*h + br per channel
     const float *fs_chan = nullptr;
@@ -403,10 +407,11 @@ __global__ void __launch_bounds__(256, 1) k_recurrence_dp4a(RecArgs a) {
                 const size_t o = (size_t)out_slot * BH + (size_t)(b0 + b) * a.H + j;
                 if (a.hq_out) a.hq_out[o] = hn;
                 if (a.hf_out) a.hf_out[o] = (float)(hn - gc->zp_h) * gc->h_scale;
+                if (a.h8_out) a.h8_out[o] = (uint8_t)hn;
             }
         }
         __syncthreads();
-        if (a.P > 1 && tid == 0) {
+        if (a.P > 1 && tid == 0 && !(a.withhold_arrive && blockIdx.x == 0 && s == 0)) {
             __threadfence();
             atomicAdd(bar, 1u);
         }
@@ -554,6 +559,7 @@ __global__ void __launch_bounds__(1024, 1) k_recurrence_gemv(const __grid_consta
             const size_t o = (size_t)out_slot * BH + (size_t)b * a.H + j;
             if (a.hq_out) a.hq_out[o] = hn;
             if (a.hf_out) a.hf_out[o] = (float)(hn - gc.zp_h) * gc.h_scale;
+            if (a.h8_out) a.h8_out[o] = (uint8_t)hn;
         }
         ihv[0] = ihn[0];
         ihv[1] = ihn[1];

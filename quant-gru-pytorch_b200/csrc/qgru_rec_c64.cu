@@ -373,6 +373,7 @@ k_recurrence_c64(const __grid_constant__ CUtensorMap map_r, const __grid_constan
                                 const size_t o = (size_t)out_slot * BH + (size_t)(bg0 + f0 + k) * a.H + j;
                                 if (a.hq_out) a.hq_out[o] = hn[k];
                                 if (a.hf_out) a.hf_out[o] = (float)(hn[k] - gc.zp_h) * gc.h_scale;
+                                if (a.h8_out) a.h8_out[o] = (uint8_t)hn[k];
                             }
                     } else {
                         hn_last[0] = hn[0];
@@ -401,6 +402,7 @@ k_recurrence_c64(const __grid_constant__ CUtensorMap map_r, const __grid_constan
                             const size_t o = (size_t)out_slot * BH + (size_t)(bg0 + f_last + k) * a.H + j;
                             if (a.hq_out) a.hq_out[o] = hn_last[k];
                             if (a.hf_out) a.hf_out[o] = (float)(hn_last[k] - gc.zp_h) * gc.h_scale;
+                            if (a.h8_out) a.h8_out[o] = (uint8_t)hn_last[k];
                         }
                 }
                 STAMP((warp % 15) == 1 && lane == 0, 12 + 8 * (warp / 15));

@@ -617,6 +617,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                             const size_t o = (size_t)out_slot * BH + (size_t)(bg0 + b) * a.H + j;
                             if (a.hq_out) a.hq_out[o] = hn[mt][i];
                             if (a.hf_out) a.hf_out[o] = (float)(hn[mt][i] - gc.zp_h) * gc.h_scale;
+                            if (a.h8_out) a.h8_out[o] = (uint8_t)hn[mt][i];
                         }
                         hn_last[mt][i] = hn[mt][i];
                     }
@@ -649,6 +650,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                             const size_t o = (size_t)out_slot * BH + (size_t)(bg0 + b) * a.H + j;
                             if (a.hq_out) a.hq_out[o] = hn_last[mt][i];
                             if (a.hf_out) a.hf_out[o] = (float)(hn_last[mt][i] - gc.zp_h) * gc.h_scale;
+                            if (a.h8_out) a.h8_out[o] = (uint8_t)hn_last[mt][i];
                         }
                     }
                 }

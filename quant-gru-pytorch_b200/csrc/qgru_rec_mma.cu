@@ -251,6 +251,7 @@ k_recurrence_mma(const __grid_constant__ CUtensorMap map_r, const __grid_constan
                         const size_t o = (size_t)out_slot * BH + (size_t)(b0 + b) * a.H + j;
                         if (a.hq_out) a.hq_out[o] = hn;
                         if (a.hf_out) a.hf_out[o] = (float)(hn - gc.zp_h) * gc.h_scale;
+                        if (a.h8_out) a.h8_out[o] = (uint8_t)hn;
                     }
                 }
             }

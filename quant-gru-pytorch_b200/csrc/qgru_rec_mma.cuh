@@ -29,6 +29,7 @@ struct RecMmaArgs {
     uint8_t *h8;            // [2][B][Hpad] ping-pong state (+ slack rows)
     int32_t *hq_out;        // [(T+1)][B][H] or null
     float *hf_out;          // [(T+1)][B][H] or null
+    uint8_t *h8_out = nullptr;   // [(T+1)][B][H] or null: the quantized state in its 8-bit container
     LinearConsts lc;        // R*h + br epilogue
     const int32_t *tables;  // activation tables (table_off) or, fused, the fused-cell tables (ft_off)
     int n_table;

@@ -75,7 +75,7 @@ int qgru_forward_f32_train(qgru_handle *h, int T, int B, const float *W, const f
         qgru::k_quantize_keep<<<grid_for(N * I, 256, h->sm_count), 256, 0, st>>>(x, N * I, h->x_scale, xo.zero_point,
                                                                              op_qmin(xo), op_qmax(xo), m.x);
     k_init_state<<<grid_for((long long)B * h->Hpad, 256, h->sm_count), 256, 0, st>>>(
-        nullptr, h0, nullptr, (int32_t *)h->hq32.p, nullptr, B, H, h->Hpad, init_slot, h->h_scale, ho.zero_point,
+        nullptr, h0, nullptr, (int32_t *)h->hq32.p, nullptr, nullptr, B, H, h->Hpad, init_slot, h->h_scale, ho.zero_point,
         op_qmin(ho), op_qmax(ho), h->d_flags);
     if (m.h0 && h0)
         qgru::k_quantize_keep<<<grid_for((long long)B * H, 256, h->sm_count), 256, 0, st>>>(

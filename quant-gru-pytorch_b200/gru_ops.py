@@ -198,6 +198,31 @@ class Handle:
             self.synchronize()
         return (h, x_q) if want_x_q else h
 
+    def forward_f32_q8(self, x, h0=None, reverse=False, out=None, sync=True):
+        """forward_f32 with the result left in 8 bits: returns the quantized states
+        [(T+1),B,H] as torch.int8 (torch.uint8 when the h operator is unsigned).  Dequantize
+        with ``h_quant_meta()``: (q - zero_point) * scale is what forward_f32 returns."""
+        x = _check_tensor(x, "x", torch.float32)
+        if x.dim() != 3 or x.shape[2] != self.input_size:
+            raise ValueError("x must have shape [time_steps, batch_size, input_size]")
+        T, B = int(x.shape[0]), int(x.shape[1])
+        if h0 is not None:
+            h0 = _check_tensor(h0, "h0", torch.float32, (B, self.hidden_size))
+        dtype = torch.uint8 if self.h_quant_meta()[2] else torch.int8
+        h = self._out_buffer(out, "out", dtype, (T + 1, B, self.hidden_size))
+        self._ck(self._lib.qgru_forward_f32_q8(self._h, T, B, _ptr(x), _ptr(h0), _ptr(h),
+                                               _cabi.FLAG_REVERSE if reverse else 0, _stream(self._tdev)),
+                 "qgru_forward_f32_q8")
+        if sync:
+            self.synchronize()
+        return h
+
+    def h_quant_meta(self):
+        """(scale, zero_point, is_unsigned) of the state h: the decoded scale the kernels use."""
+        o = self._params.c.op[_cabi.OP_INDEX["h"]]
+        return decode_effective_scale(float(o.scale), bool(self._params.c.use_pot2)), int(o.zero_point), \
+            bool(o.is_unsigned) and o.bits < 32
+
     def forward_fstorage(self, x, h0=None, reverse=False, want_x_q=False, sync=True):
         """Float-storage quantized forward (the reference's forward_quant_float_storage, inference):
         float requantization and real sigmoid / tanh on quantized tensors.  x [T,B,I] fp32 ->

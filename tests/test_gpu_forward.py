@@ -193,6 +193,65 @@ def test_sync_floor_probe_runs(oracle, cuda_device):
     torch.cuda.synchronize()
 
 
+def test_bounded_wait_runs_out_and_the_handle_stays_usable(oracle, cuda_device):
+    """The failure path of the per-step group barrier (dp4a recurrence, two CTAs per group): one CTA
+    leaves out an arrival (a host-set test option), the others' bounded wait runs out after
+    `spin_limit` polls, every CTA leaves, the call reports QGRU_ERR_TIMEOUT - and the next forward on
+    the same handle is bit-exact again.  Nothing faults, traps or waits without a bound."""
+    _cabi = importlib.import_module(PKG_NAME + "._cabi")
+    case = make_case(21, 6, 9, 24, 300, oracle, config_named("default"))
+    want = _want(oracle, case)
+    dev = cuda_device
+    with gru_ops.Handle(case.I, case.H, device=dev.index or 0) as hd:
+        hd.set_option("rec", "dp4a")
+        hd.set_params(case.params)
+        hd.set_weights_i32(*[_t(a, dev) for a in case.wq])
+        x = _t(case.x_q, dev)
+        assert np.array_equal(hd.forward_i32(x).cpu().numpy(), want)
+        assert "rec=dp4a" in hd.describe_plan() and "P=2" in hd.describe_plan()
+        hd.set_option("spin_limit", 2000)
+        hd.set_option("test_withhold_arrive", 1)
+        with pytest.raises(_cabi.QgruError) as err:
+            hd.forward_i32(x)
+        assert err.value.status == _cabi.QGRU_ERR_TIMEOUT
+        hd.set_option("test_withhold_arrive", 0)
+        hd.set_option("spin_limit", 1 << 24)
+        assert np.array_equal(hd.forward_i32(x).cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("opts", [(), (("rec", "gemv"),), (("rec", "dp4a"),), (("rec", "mma"), ("exchange", "global")),
+                                  (("rec", "mma"), ("unit_tile", "64")), (("rec", "mma"), ("cell", "generic"))])
+@pytest.mark.parametrize("cfg", ["cfg2", "unsigned_x"])
+def test_8bit_output_equals_the_float_output(oracle, cuda_device, opts, cfg):
+    """qgru_forward_f32_q8: the quantized states in their 8-bit container; dequantized with the h
+    operator's (scale, zero point) they are the fp32 output of qgru_forward_f32 bit for bit, and
+    they are the oracle's integers."""
+    import torch
+    T, B, I, H = 7, 19, 24, 200
+    case = make_case(23, T, B, I, H, oracle, config_named(cfg), with_h0=True)
+    want = _want(oracle, case)
+    dev = cuda_device
+    with gru_ops.Handle(I, H, device=dev.index or 0) as hd:
+        for k, v in opts:
+            hd.set_option(k, v)
+        hd.set_params(case.params)
+        hd.set_weights_i32(*[_t(a, dev) for a in case.wq])
+        for reverse in (False, True):
+            try:
+                q8 = hd.forward_f32_q8(_t(case.x, dev), _t(case.h0, dev), reverse=reverse)
+            except Exception as e:
+                if "unit_tile=64" in str(e):
+                    pytest.skip("no branch-free tabulated cell for this configuration")
+                raise
+            f32 = hd.forward_f32(_t(case.x, dev), _t(case.h0, dev), reverse=reverse)
+            scale, zp, uns = hd.h_quant_meta()
+            assert q8.dtype == (torch.uint8 if uns else torch.int8)
+            deq = (q8.to(torch.int32) - zp).to(torch.float32) * np.float32(scale)
+            assert torch.equal(deq, f32), hd.describe_plan()
+            if not reverse:
+                assert np.array_equal(q8.cpu().numpy().astype(np.int32), want), hd.describe_plan()
+
+
 def test_large_batch_many_groups(oracle, cuda_device):
     """More batch rows than one wave of groups holds at H = 512: consecutive launches."""
     case = make_case(14, 3, 700, 32, 384, oracle, config_named("default"), calib_batches=1)
