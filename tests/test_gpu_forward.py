@@ -194,7 +194,7 @@ def test_sync_floor_probe_runs(oracle, cuda_device):
 
 
 def test_bounded_wait_runs_out_and_the_handle_stays_usable(oracle, cuda_device):
-    """The failure path of the per-step group barrier (dp4a recurrence, two CTAs per group): one CTA
+    """The failure path of the per-step group barrier (dp4a recurrence, three CTAs per group): one CTA
     leaves out an arrival (a host-set test option), the others' bounded wait runs out after
     `spin_limit` polls, every CTA leaves, the call reports QGRU_ERR_TIMEOUT - and the next forward on
     the same handle is bit-exact again.  Nothing faults, traps or waits without a bound."""
@@ -208,7 +208,7 @@ def test_bounded_wait_runs_out_and_the_handle_stays_usable(oracle, cuda_device):
         hd.set_weights_i32(*[_t(a, dev) for a in case.wq])
         x = _t(case.x_q, dev)
         assert np.array_equal(hd.forward_i32(x).cpu().numpy(), want)
-        assert "rec=dp4a" in hd.describe_plan() and "P=2" in hd.describe_plan()
+        assert "rec=dp4a" in hd.describe_plan() and "P=3" in hd.describe_plan()   # several CTAs per group
         hd.set_option("spin_limit", 2000)
         hd.set_option("test_withhold_arrive", 1)
         with pytest.raises(_cabi.QgruError) as err:
