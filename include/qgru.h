@@ -393,6 +393,11 @@ QGRU_API int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int accu
 QGRU_API int qgru_probe_mma_i8_ex(int device, int M, int N, int a_in_tmem, int accumulators, int mmas,
                                   int ctas, int issuers, int spinners, int neighbour_mode,
                                   double *cycles_per_mma, double *tera_ops);
+/* The same with a tcgen05.commit after every `commit_every` (0, 4 or 8) MMAs of each issuer, as a GEMM
+ * main loop commits to hand its operand stages back. */
+QGRU_API int qgru_probe_mma_i8_commits(int device, int M, int N, int a_in_tmem, int accumulators, int mmas,
+                                       int ctas, int issuers, int spinners, int neighbour_mode,
+                                       int commit_every, double *cycles_per_mma, double *tera_ops);
 
 /* Restrict or force kernel choices (testing).  Names and values:
  *   "gemm"     auto | simt | tcgen05        W*x kernel

@@ -22,6 +22,23 @@
 #include "qgru_device.cuh"
 #include "qgru_tc.cuh"
 
+#ifdef QGRU_STAMPS
+// development builds only: per CTA, cycles spent waiting in each role of the GEMM kernel
+__device__ long long g_gemm_dbg[160 * 8];
+extern "C" __attribute__((visibility("default"))) int qgru_debug_read_gemm(long long *out) {
+    return cudaMemcpyFromSymbol(out, g_gemm_dbg, sizeof(g_gemm_dbg)) == cudaSuccess ? 0 : 2;
+}
+#define WAITED(slot, call)                                   \
+    [&] {                                                    \
+        const long long t0_ = clock64();                     \
+        const bool r_ = (call);                              \
+        dbg_acc[slot] += clock64() - t0_;                    \
+        return r_;                                           \
+    }()
+#else
+#define WAITED(slot, call) (call)
+#endif
+
 namespace qgru {
 
 EncodeTiledFn get_encode_tiled() {
@@ -58,6 +75,7 @@ constexpr int GM = 128;      // channels per tile
 constexpr int GN = 128;      // tokens per tile
 constexpr int KB = 128;      // K bytes per stage
 constexpr int STAGES = 4;
+constexpr int STAGES_A = 8;    // W-stationary form: ring of x slabs (16 KB each)
 constexpr int NACC = 4;        // accumulator buffers in tensor memory (NACC * GN = 512 columns: all of it)
 constexpr int EPI_WARPS = 16;                      // four warps per TMEM lane quadrant
 constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
@@ -69,10 +87,14 @@ constexpr size_t GEMM_SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256 + PRE_TAB
 // Fast: every scale of the epilogue has the shift-free form and the sums fit 32 bits, so the
 // epilogue is branch-free (Rescale::mq, checked by the caller).
 // AStat ("A stationary"): a CTA works on one tile of 128 channels for the whole launch and keeps
-// that slice of W (all K slabs) in shared memory; only token tiles stream through the ring.  The
-// CTAs that share a token-tile sequence (one per channel tile) run side by side, so each x tile
-// is read from L2 by all of them at about the same time.  Halves the operand traffic from L2,
-// which is what bounds the kernel at K = 1024.  Grid = m_tiles * groups CTAs.
+// that slice of W (all K slabs, K <= 1024) in TENSOR memory, 32 columns per 128-byte K slab, staged
+// once through the ring's slots; only token tiles stream through the ring and the MMAs read their
+// A operand from tensor memory.  What this relieves is shared-memory bandwidth, which is what
+// bounds the streaming form at long K: an MMA of 128 x 128 x 32 reads 8 KB of operands from shared
+// memory while TMA writes the next 8 KB into it, against 128 bytes per cycle in total (measured:
+// 165 cycles per MMA instead of 64, the MMA warp busy 85 % of the time, the epilogue idle a
+// third of it); with W in tensor memory both halve.  Grid = m_tiles * groups CTAs; the
+// accumulators take the columns W leaves (two buffers at K = 1024, three below).
 // Tie = false (with Fast): the requantization rounds half up, which equals the reference's
 // round-half-even because no channel can meet an exact tie in its accumulator range (checked
 // when the weights are set: rescale_can_tie).
@@ -84,16 +106,18 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     extern __shared__ unsigned char smem_raw[];
     unsigned char *tiles = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    // AStat: [Kpad/KB resident W slabs of GM*KB bytes][STAGES x tiles of GN*KB bytes]; else the
-    // ring holds a W slab and an x slab per stage
-    const size_t tile_bytes = AStat ? (size_t)(Kpad / KB) * GM * KB + (size_t)STAGES * GN * KB
-                                    : (size_t)STAGES * STAGE_BYTES;
-    unsigned char *ring = AStat ? tiles + (size_t)(Kpad / KB) * GM * KB : tiles;
+    // AStat: the ring holds STAGES_A x slabs of GN*KB bytes (they also stage W on its way to tensor
+    // memory); else the ring holds a W slab and an x slab per stage
+    constexpr int NST = AStat ? STAGES_A : STAGES;            // ring stages
+    const size_t tile_bytes = AStat ? (size_t)STAGES_A * GN * KB : (size_t)STAGES * STAGE_BYTES;
+    unsigned char *ring = tiles;
     uint64_t *bars = reinterpret_cast<uint64_t *>(tiles + tile_bytes);
-    uint64_t *full = bars, *empty = bars + STAGES;
-    uint64_t *acc_full = bars + 2 * STAGES, *acc_empty = bars + 2 * STAGES + NACC;
-    uint64_t *a_full = bars + 2 * STAGES + 2 * NACC;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 2 * NACC + 1);
+    uint64_t *full = bars, *empty = bars + NST;
+    uint64_t *acc_full = bars + 2 * NST, *acc_empty = bars + 2 * NST + NACC;
+    uint64_t *a_full = bars + 2 * NST + 2 * NACC;        // AStat: a pass of W slabs has landed in the slots
+    uint64_t *a_ready = a_full + 1;                      // AStat: the epilogue threads have copied that pass
+    uint64_t *w_done = a_full + 2;                       // AStat: all of W sits in tensor memory
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(a_full + 3);
     int *failed = reinterpret_cast<int *>(tmem_slot + 1);
     int32_t *pre_tab = reinterpret_cast<int32_t *>(tiles + tile_bytes + 256);
     const bool use_tab = ps.enabled && ps.table != nullptr && 3 * ps.table_n <= PRE_TAB_MAX;
@@ -106,6 +130,9 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     const long long n_tiles = (N + GN - 1) / GN;
     const long long total = (long long)m_tiles * n_tiles;   // consecutive tiles share the token tile
     const int groups = AStat ? (int)gridDim.x / m_tiles : 1;
+    // accumulator buffers: all 512 columns in the streaming form; beside W in the stationary form
+    const int nacc = AStat ? (num_kb > 4 ? 2 : 3) : NACC;
+    const uint32_t w_col = (uint32_t)(nacc * GN);          // first tensor-memory column of W
     // the `local`-th tile of this CTA: false when there is none
     auto tile_of = [&](long long local, int &m0, long long &n0) -> bool {
         if (AStat) {
@@ -123,7 +150,7 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     };
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < NST; ++s) {
             tc::mbar_init(&full[s], 1);
             tc::mbar_init(&empty[s], 1);
         }
@@ -132,12 +159,14 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             tc::mbar_init(&acc_empty[b], EPI_WARPS);
         }
         tc::mbar_init(a_full, 1);
+        tc::mbar_init(a_ready, 32 * EPI_WARPS);
+        tc::mbar_init(w_done, 1);
         *failed = 0;
         tc::fence_barrier_init();
         tc::tma_prefetch_desc(&map_w);
         tc::tma_prefetch_desc(&map_x);
     }
-    if (warp == 1) tc::tmem_alloc(tmem_slot, NACC * GN);   // several accumulators: the MMAs run ahead of the epilogue
+    if (warp == 1) tc::tmem_alloc(tmem_slot, 512);   // several accumulators: the MMAs run ahead of the epilogue
     tc::tc_fence_before_sync();
     __syncthreads();
     tc::tc_fence_after_sync();
@@ -149,17 +178,30 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             bool ok = true;
             int m0;
             long long n0;
-            if (AStat && tile_of(0, m0, n0)) {
-                // this CTA's slice of W, once
-                tc::mbar_expect_tx(a_full, (uint32_t)(num_kb * GM * KB));
-                for (int kb = 0; kb < num_kb; ++kb)
-                    tc::tma_load_2d(tiles + (size_t)kb * GM * KB, &map_w, a_full, kb * KB, m0);
+#ifdef QGRU_STAMPS
+            long long dbg_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#endif
+            if (AStat) {
+                // this CTA's slice of W, once: through the ring's slots into tensor memory, a pass of up
+                // to STAGES_A slabs at a time (every CTA takes part, with or without tiles of its own,
+                // so that the barriers below see the same sequence everywhere)
+                m0 = (int)(blockIdx.x % m_tiles) * GM;
+                int pass = 0;
+                for (int done = 0; done < num_kb && ok; ++pass) {
+                    const int cnt = min(STAGES_A, num_kb - done);
+                    tc::mbar_expect_tx(a_full, (uint32_t)(cnt * GM * KB));
+                    for (int i = 0; i < cnt; ++i)
+                        tc::tma_load_2d(ring + (size_t)i * GM * KB, &map_w, a_full, (done + i) * KB, m0);
+                    ok = tc::mbar_wait(a_ready, (uint32_t)(pass & 1), WAIT_BUDGET);
+                    done += cnt;
+                }
+                tc::mbar_arrive(w_done);
             }
             for (long long local = 0; ok && tile_of(local, m0, n0); ++local) {
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = (int)(it % STAGES);
-                    const uint32_t ph = (uint32_t)((it / STAGES) & 1);
-                    if (!tc::mbar_wait(&empty[s], ph ^ 1, WAIT_BUDGET)) { ok = false; break; }
+                    const int s = (int)(it % NST);
+                    const uint32_t ph = (uint32_t)((it / NST) & 1);
+                    if (!WAITED(0, tc::mbar_wait(&empty[s], ph ^ 1, WAIT_BUDGET))) { ok = false; break; }
                     if (AStat) {
                         tc::mbar_expect_tx(&full[s], GN * KB);
                         tc::tma_load_2d(ring + (size_t)s * GN * KB, &map_x, &full[s], kb * KB, (int)n0);
@@ -172,6 +214,9 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                 }
             }
             if (!ok) atomicExch(failed, 1);
+#ifdef QGRU_STAMPS
+            if (blockIdx.x < 160) g_gemm_dbg[blockIdx.x * 8 + 0] = dbg_acc[0];
+#endif
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -180,35 +225,56 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             bool ok = true;
             int m0;
             long long n0;
-            if (AStat && tile_of(0, m0, n0)) {
-                ok = tc::mbar_wait(a_full, 0, WAIT_BUDGET);
+#ifdef QGRU_STAMPS
+            long long dbg_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            const long long t_start = clock64();
+#endif
+            if (AStat) {
+                ok = tc::mbar_wait(w_done, 0, WAIT_BUDGET);
                 tc::tc_fence_after_sync();
             }
             for (long long local = 0; ok && tile_of(local, m0, n0); ++local) {
-                const int buf = (int)(local % NACC);
-                if (!tc::mbar_wait(&acc_empty[buf], (uint32_t)(((local / NACC) & 1) ^ 1), WAIT_BUDGET)) { ok = false; break; }
+                const int buf = (int)(local % nacc);
+                if (!WAITED(2, tc::mbar_wait(&acc_empty[buf], (uint32_t)(((local / nacc) & 1) ^ 1), WAIT_BUDGET))) { ok = false; break; }
                 tc::tc_fence_after_sync();
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = (int)(it % STAGES);
-                    const uint32_t ph = (uint32_t)((it / STAGES) & 1);
-                    if (!tc::mbar_wait(&full[s], ph, WAIT_BUDGET)) { ok = false; break; }
+                    const int s = (int)(it % NST);
+                    const uint32_t ph = (uint32_t)((it / NST) & 1);
+                    if (!WAITED(1, tc::mbar_wait(&full[s], ph, WAIT_BUDGET))) { ok = false; break; }
                     tc::tc_fence_after_sync();
-                    const uint32_t a_addr = AStat ? tc::smem_u32(tiles + (size_t)kb * GM * KB)
-                                                  : tc::smem_u32(tiles + (size_t)s * STAGE_BYTES);
-                    const uint32_t b_addr = AStat ? tc::smem_u32(ring + (size_t)s * GN * KB) : a_addr + GM * KB;
-                    const uint64_t a_desc = tc::smem_desc_sw128(a_addr);
-                    const uint64_t b_desc = tc::smem_desc_sw128(b_addr);
+                    if (AStat) {
+                        const uint64_t b_desc = tc::smem_desc_sw128(tc::smem_u32(ring + (size_t)s * GN * KB));
 #pragma unroll
-                    for (int ks = 0; ks < KB / 32; ++ks)
-                        tc::mma_i8(tmem_base + buf * GN, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (kb | ks) != 0);
+                        for (int ks = 0; ks < KB / 32; ++ks)
+                            tc::mma_i8_ts(tmem_base + buf * GN, tmem_base + w_col + (uint32_t)(kb * 32 + ks * 8), b_desc + 2 * ks,
+                                          idesc, (kb | ks) != 0);
+                    } else {
+                        const uint32_t a_addr = tc::smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                        const uint64_t a_desc = tc::smem_desc_sw128(a_addr);
+                        const uint64_t b_desc = tc::smem_desc_sw128(a_addr + GM * KB);
+#pragma unroll
+                        for (int ks = 0; ks < KB / 32; ++ks)
+                            tc::mma_i8(tmem_base + buf * GN, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (kb | ks) != 0);
+                    }
                     tc::mma_commit(&empty[s]);
                 }
                 if (ok) tc::mma_commit(&acc_full[buf]);
             }
             if (!ok) atomicExch(failed, 1);
+#ifdef QGRU_STAMPS
+            if (blockIdx.x < 160) {
+                g_gemm_dbg[blockIdx.x * 8 + 1] = dbg_acc[1];
+                g_gemm_dbg[blockIdx.x * 8 + 2] = dbg_acc[2];
+                g_gemm_dbg[blockIdx.x * 8 + 3] = clock64() - t_start;
+            }
+#endif
         }
     } else {
         const int q = warp & 3;                     // TMEM lane quadrant of this warp
+#ifdef QGRU_STAMPS
+        long long dbg_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const long long t_start = clock64();
+#endif
         const int part = (warp - 2) >> 2;           // which share of the token columns
         constexpr int COLS = GN / (EPI_WARPS / 4);
         long long local = 0;
@@ -237,11 +303,38 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             c.fs_ratio = fs_ok ? lc.fs[2 * lc.fs_C + m] : 0.f;
             return c;
         };
+        if (AStat) {
+            // W on its way to tensor memory: this thread owns channel row (32 q + lane) of every slab, eight
+            // 16-byte chunks un-swizzled on the way, 32 columns per slab
+            const int u = q * 32 + lane;
+            int pass = 0;
+            for (int done = 0; done < num_kb && ok; ++pass) {
+                const int cnt = min(STAGES_A, num_kb - done);
+                ok = tc::mbar_wait(a_full, (uint32_t)(pass & 1), WAIT_BUDGET);
+                for (int i = part; i < cnt && ok; i += EPI_WARPS / 4) {
+                    const unsigned char *row = ring + (size_t)i * GM * KB + (size_t)(u >> 3) * 1024 + (size_t)(u & 7) * 128;
+                    uint32_t w[32];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const uint4 v = *reinterpret_cast<const uint4 *>(row + ((c ^ (u & 7)) << 4));
+                        w[4 * c + 0] = v.x;
+                        w[4 * c + 1] = v.y;
+                        w[4 * c + 2] = v.z;
+                        w[4 * c + 3] = v.w;
+                    }
+                    tc::tmem_st32(tmem_base + ((uint32_t)(q * 32) << 16) + w_col + (uint32_t)((done + i) * 32), w);
+                }
+                tc::tmem_st_wait();
+                tc::tc_fence_before_sync();
+                tc::mbar_arrive(a_ready);
+                done += cnt;
+            }
+        }
         ChanConsts cur = load_consts(0);
         int m0;
         long long n0;
         for (; ok && tile_of(local, m0, n0); ++local) {
-            const int buf = (int)(local % NACC);
+            const int buf = (int)(local % nacc);
             const int m = m0 + q * 32 + lane;
             const bool m_ok = m < C;
             const ChanConsts nxt = AStat ? cur : load_consts(local + 1);
@@ -253,7 +346,7 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             const Rescale pre_rs = ps.to[gate];
             const int32_t pre_zp = ps.zp_in[gate];
             const int32_t c32 = (int32_t)corr;
-            ok = tc::mbar_wait(&acc_full[buf], (uint32_t)((local / NACC) & 1), WAIT_BUDGET);
+            ok = WAITED(4, tc::mbar_wait(&acc_full[buf], (uint32_t)((local / nacc) & 1), WAIT_BUDGET));
             if (!ok) break;
             tc::tc_fence_after_sync();
             IhT *out = ih + m;
@@ -263,7 +356,13 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             int32_t vv[2][16];
             tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * GN + part * COLS), vv[0]);
             tc::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * GN + part * COLS + 16), vv[1]);
+#ifdef QGRU_STAMPS
+            const long long t_ld = clock64();
+#endif
             tc::tmem_ld_wait();
+#ifdef QGRU_STAMPS
+            dbg_acc[5] += clock64() - t_ld;
+#endif
             tc::tc_fence_before_sync();
             if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
 #pragma unroll
@@ -319,30 +418,37 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
             cur = nxt;
         }
         if (!ok && lane == 0) atomicExch(failed, 1);
+#ifdef QGRU_STAMPS
+        if (warp == 2 && lane == 0 && blockIdx.x < 160) {
+            g_gemm_dbg[blockIdx.x * 8 + 4] = dbg_acc[4];
+            g_gemm_dbg[blockIdx.x * 8 + 5] = dbg_acc[5];
+            g_gemm_dbg[blockIdx.x * 8 + 6] = clock64() - t_start;
+            g_gemm_dbg[blockIdx.x * 8 + 7] = local;
+        }
+#endif
     }
     tc::tc_fence_before_sync();
     __syncthreads();
     if (threadIdx.x == 0 && *failed) atomicOr(abort_flag, 2);
-    if (warp == 1) tc::tmem_dealloc(tmem_base, NACC * GN);
+    if (warp == 1) tc::tmem_dealloc(tmem_base, 512);
 }
 
 constexpr size_t SMEM_LIMIT = 227 * 1024;   // opt-in shared memory per CTA on sm_100
 
-size_t astat_smem(int Kpad) {
-    return (size_t)(Kpad / KB) * GM * KB + (size_t)STAGES * GN * KB + 1024 + 256 + PRE_TAB_MAX * 4;
-}
+size_t astat_smem(int) { return (size_t)STAGES_A * GN * KB + 1024 + 256 + PRE_TAB_MAX * 4; }
 
 template <bool XU, typename IhT, bool Fast, bool Tie>
 cudaError_t launch_f(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long long N, int C, int Kpad,
                      LinearConsts lc, PreScale ps, int *abort_flag, int sms, int order, cudaStream_t st) {
     const int m_tiles = (C + GM - 1) / GM;
     const long long n_tiles = (N + GN - 1) / GN;
-    // W-stationary order: only on request (option gemm_order), where the slice of W fits beside
-    // the ring and every CTA can get a channel tile.  It halves the operand traffic from L2 and
-    // measured the same time as the streaming order at K = 1024 (0.293 ms for 64000 x 3072 x 1024):
-    // the kernel is bound by its epilogue there too, not by operand delivery.
-    const bool fits = astat_smem(Kpad) <= SMEM_LIMIT && m_tiles <= sms;
-    const bool astat = fits && order == 2;
+    // W-stationary form (W in tensor memory): where K is long enough for operand traffic through shared
+    // memory to set the pace (option gemm_order: auto takes it from K = 512), every CTA can get a channel
+    // tile and the token tiles spread evenly enough over the CTA groups
+    const bool fits = Kpad <= 1024 && m_tiles <= sms;
+    const long long grp = std::max<long long>(1, std::min<long long>(sms / m_tiles, n_tiles));
+    const bool balanced = (long long)m_tiles * grp * 10 >= (long long)sms * 8;   // at least 80 % of the SMs get a CTA
+    const bool astat = fits && (order == 2 || (order == 0 && Kpad >= 512 && balanced));
     if (astat) {
         auto kern = k_gemm_wx_tc<XU, IhT, Fast, true, Tie>;
         const size_t smem = astat_smem(Kpad);

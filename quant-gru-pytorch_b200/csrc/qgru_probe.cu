@@ -28,21 +28,21 @@ constexpr long long PROBE_WAIT = 2000000000ll;
 // waiting neighbours cost the issuing threads.  cycles[cta] = clock ticks from the first issue to
 // the completion of the last MMA of the slowest issuer.
 __global__ void __launch_bounds__(1024, 1)
-k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, int issuers, int neighbour_mode, long long *cycles,
-               int *timeouts) {
+k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, int issuers, int neighbour_mode, int commit_every,
+               long long *cycles, int *timeouts) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = tc::smem_u32(smem_raw);
     unsigned char *base = smem_raw + (((raw + 1023u) & ~1023u) - raw);
     unsigned char *a_tile = base;                    // 16 KB
     unsigned char *b_tile = base + 16384;            // up to 32 KB
     uint64_t *bar = reinterpret_cast<uint64_t *>(base + 16384 + 32768);   // [issuers] + one nobody completes
-    uint32_t *slot = reinterpret_cast<uint32_t *>(bar + 8);
+    uint32_t *slot = reinterpret_cast<uint32_t *>(bar + 10);
     volatile int *done = reinterpret_cast<volatile int *>(slot + 1);
-    long long *cyc_w = reinterpret_cast<long long *>(bar + 10);           // [issuers]
+    long long *cyc_w = reinterpret_cast<long long *>(bar + 12);           // [issuers]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int i = threadIdx.x; i < (16384 + 32768) / 4; i += blockDim.x) reinterpret_cast<uint32_t *>(base)[i] = 0u;
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 5; ++i) tc::mbar_init(&bar[i], 1);
+        for (int i = 0; i < 9; ++i) tc::mbar_init(&bar[i], 1);
         *done = 0;
         tc::fence_barrier_init();
     }
@@ -71,15 +71,25 @@ k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, int issuers, in
             }
             const int passes = mmas / 8;
             const long long t0 = clock64();
+            // commit_every = 4 or 8: a tcgen05.commit after every 4 / 8 MMAs, as a GEMM main loop does to hand
+            // its shared-memory stages back (the barrier it arrives on is nobody's concern here)
             if (a_in_tmem) {
                 for (int i = 0; i < passes; ++i) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) tc::mma_i8_ts(dcol[j], acol[j], bd[j], idesc, 1u);
+                    for (int j = 0; j < 8; ++j) {
+                        tc::mma_i8_ts(dcol[j], acol[j], bd[j], idesc, 1u);
+                        if (commit_every == 4 && j == 3) tc::mma_commit(&bar[5 + warp]);
+                    }
+                    if (commit_every == 4 || commit_every == 8) tc::mma_commit(&bar[5 + warp]);
                 }
             } else {
                 for (int i = 0; i < passes; ++i) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) tc::mma_i8(dcol[j], ad[j], bd[j], idesc, 1u);
+                    for (int j = 0; j < 8; ++j) {
+                        tc::mma_i8(dcol[j], ad[j], bd[j], idesc, 1u);
+                        if (commit_every == 4 && j == 3) tc::mma_commit(&bar[5 + warp]);
+                    }
+                    if (commit_every == 4 || commit_every == 8) tc::mma_commit(&bar[5 + warp]);
                 }
             }
             tc::mma_commit(&bar[warp]);
@@ -130,6 +140,13 @@ k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, int issuers, in
 extern "C" int qgru_probe_mma_i8_ex(int device, int M, int N, int a_in_tmem, int accumulators, int mmas, int ctas,
                                     int issuers, int spinners, int neighbour_mode, double *cycles_per_mma,
                                     double *tera_ops) {
+    return qgru_probe_mma_i8_commits(device, M, N, a_in_tmem, accumulators, mmas, ctas, issuers, spinners, neighbour_mode,
+                                     0, cycles_per_mma, tera_ops);
+}
+
+extern "C" int qgru_probe_mma_i8_commits(int device, int M, int N, int a_in_tmem, int accumulators, int mmas, int ctas,
+                                         int issuers, int spinners, int neighbour_mode, int commit_every,
+                                         double *cycles_per_mma, double *tera_ops) {
     using namespace qgru;
     if (!cycles_per_mma || !tera_ops) return QGRU_ERR_BAD_ARG;
     if (!((M == 128 && N % 16 == 0) || (M == 64 && N % 8 == 0)) || N < 8 || N > 256) return QGRU_ERR_BAD_ARG;
@@ -152,9 +169,9 @@ extern "C" int qgru_probe_mma_i8_ex(int device, int M, int N, int a_in_tmem, int
         if (cudaMemset(d_to, 0, sizeof(int)) != cudaSuccess) break;
         if (cudaFuncSetAttribute(k_probe_mma_i8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) break;
         if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) break;
-        k_probe_mma_i8<<<ctas, threads, smem>>>(M, N, a_in_tmem, accumulators, std::min(mmas, 256) / 8 * 8, issuers, neighbour_mode, d_cycles, d_to);   // warm-up
+        k_probe_mma_i8<<<ctas, threads, smem>>>(M, N, a_in_tmem, accumulators, std::min(mmas, 256) / 8 * 8, issuers, neighbour_mode, commit_every, d_cycles, d_to);   // warm-up
         cudaEventRecord(e0);
-        k_probe_mma_i8<<<ctas, threads, smem>>>(M, N, a_in_tmem, accumulators, mmas, issuers, neighbour_mode, d_cycles, d_to);
+        k_probe_mma_i8<<<ctas, threads, smem>>>(M, N, a_in_tmem, accumulators, mmas, issuers, neighbour_mode, commit_every, d_cycles, d_to);
         cudaEventRecord(e1);
         if (cudaEventSynchronize(e1) != cudaSuccess || cudaGetLastError() != cudaSuccess) break;
         float ms = 0.f;

@@ -589,14 +589,14 @@ def forward_calibrate(is_training, time_steps, batch_size, input_size, hidden_si
 
 
 def probe_mma_i8(M=128, N=256, a_in_tmem=False, accumulators=1, mmas=16384, ctas=148, device=0, issuers=1,
-                 spinners=3, neighbour_mode=0):
+                 spinners=3, neighbour_mode=0, commit_every=0):
     """Issue rate of tcgen05.mma kind::i8 for one shape (qgru_probe_mma_i8_ex): returns
     (SM cycles per MMA in a back-to-back chain of one issuing thread, aggregate 1e12 int8 ops/s
     over `ctas` SMs and `issuers` issuing warps); `spinners` neighbour warps wait (mode 0), compute (1) or
     load from shared memory (2) beside them."""
     cyc, tops = C.c_double(), C.c_double()
-    st = _cabi.lib().qgru_probe_mma_i8_ex(int(device), int(M), int(N), int(bool(a_in_tmem)), int(accumulators),
-                                          int(mmas), int(ctas), int(issuers), int(spinners), int(neighbour_mode), C.byref(cyc),
-                                          C.byref(tops))
-    _cabi.check(st, "qgru_probe_mma_i8_ex")
+    st = _cabi.lib().qgru_probe_mma_i8_commits(int(device), int(M), int(N), int(bool(a_in_tmem)), int(accumulators),
+                                               int(mmas), int(ctas), int(issuers), int(spinners), int(neighbour_mode),
+                                               int(commit_every), C.byref(cyc), C.byref(tops))
+    _cabi.check(st, "qgru_probe_mma_i8_commits")
     return cyc.value, tops.value

@@ -423,11 +423,12 @@ def test_training_buffer(oracle, cuda_device, name):
 
 @pytest.mark.parametrize("order", ["stream", "w_stationary"])
 @pytest.mark.parametrize("shape,name", [((3, 50, 20, 40), "default"), ((5, 70, 300, 200), "cfg2"),
-                                        ((2, 300, 1024, 520), "default"), ((4, 33, 640, 136), "cfg3")])
+                                        ((2, 300, 1024, 520), "default"), ((4, 33, 640, 136), "cfg3"),
+                                        ((40, 64, 896, 300), "cfg2"), ((3, 9, 513, 64), "default")])
 def test_input_gemm_tile_orders(oracle, cuda_device, shape, name, order):
     """Both tile orders of the tcgen05 input GEMM (W and x slabs streaming per tile; the slice
-    of W resident in shared memory for the whole launch), K from 128 to 1024 padded bytes, more
-    and fewer token tiles than CTAs per channel tile: bit-exact."""
+    of W resident in tensor memory for the whole launch, the MMAs' A operand read from there), K
+    from 128 to 1024 padded bytes, more and fewer token tiles than CTAs per channel tile: bit-exact."""
     T, B, I, H = shape
     case = make_case(seed=51, T=T, B=B, I=I, H=H, checker=oracle, config=config_named(name))
     got, plan, _ = _run(case, cuda_device, opts=(("gemm", "tcgen05"), ("gemm_order", order)))
