@@ -388,8 +388,11 @@ QGRU_API int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int accu
 /* The same with `issuers` (1..4) warps issuing `mmas` MMAs each into accumulators of their own, and
  * `spinners` further warps beside them that (neighbour_mode 0) poll an mbarrier as a kernel's waiting
  * warps do, (1) run integer arithmetic back to back or (2) run dependent shared-memory loads, as its
- * busy warps do: cycles_per_mma is the slowest issuer's chain time divided by `mmas`, tera_ops counts
- * all issuers. */
+ * busy warps do, (3) drain accumulators with 16-column tensor-memory loads or (4) write 128-bit words
+ * into shared memory: cycles_per_mma is the slowest issuer's chain time divided by `mmas`, tera_ops
+ * counts all issuers.  neighbour_mode + 256 fills the shared-memory operands with pseudo-random bytes
+ * instead of zeros: same instruction stream, the multipliers toggle as in a real product, which
+ * shows what part of the zero-operand peak survives the board's power limit. */
 QGRU_API int qgru_probe_mma_i8_ex(int device, int M, int N, int a_in_tmem, int accumulators, int mmas,
                                   int ctas, int issuers, int spinners, int neighbour_mode,
                                   double *cycles_per_mma, double *tera_ops);
@@ -399,11 +402,17 @@ QGRU_API int qgru_probe_mma_i8_commits(int device, int M, int N, int a_in_tmem, 
                                        int ctas, int issuers, int spinners, int neighbour_mode,
                                        int commit_every, double *cycles_per_mma, double *tera_ops);
 
+/* neighbour_mode 5 of the probes above: the first neighbour warp keeps four 16 KB bulk copies from
+ * global memory into shared memory in flight, as a GEMM's operand loads do.  This returns the bytes
+ * per SM clock that the copies of CTA 0 moved during the last such probe of this process. */
+QGRU_API double qgru_probe_last_bulk_rate(void);
+
 /* Restrict or force kernel choices (testing).  Names and values:
  *   "gemm"     auto | simt | tcgen05        W*x kernel
  *   "gemm_order" auto | stream | w_stationary  tile order of the tcgen05 W*x kernel: W and x slabs
  *                                           stream per tile (auto), or a CTA keeps one slice of W
- *                                           in shared memory for the whole launch
+ *                                           in tensor memory for the whole launch (slower; kept
+ *                                           as a measured alternative)
  *   "rec"      auto | dp4a | mma | generic  recurrence kernel (generic = int32 storage path)
  *   "exchange" auto | global | cluster      how the CTAs of a batch group exchange h_t
  *   "cell"     auto | fused | generic       gate datapath: tabulated (auto also allows its

@@ -104,6 +104,7 @@ SYMBOLS = {
     "qgru_set_option": (C.c_int, [_P, C.c_char_p, C.c_char_p]),
     "qgru_probe_mma_i8": (C.c_int, [C.c_int] * 7 + [C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "qgru_probe_mma_i8_commits": (C.c_int, [C.c_int] * 11 + [C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "qgru_probe_last_bulk_rate": (C.c_double, []),
     "qgru_probe_mma_i8_ex": (C.c_int, [C.c_int] * 10 + [C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "qgru_forward_float": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "qgru_calibrate_minmax": (C.c_int, [_P, C.c_int, C.c_int, _P, _P, _P, _P, _P, _P,

@@ -86,15 +86,16 @@ constexpr size_t GEMM_SMEM = (size_t)STAGES * STAGE_BYTES + 1024 + 256 + PRE_TAB
 
 // Fast: every scale of the epilogue has the shift-free form and the sums fit 32 bits, so the
 // epilogue is branch-free (Rescale::mq, checked by the caller).
-// AStat ("A stationary"): a CTA works on one tile of 128 channels for the whole launch and keeps
-// that slice of W (all K slabs, K <= 1024) in TENSOR memory, 32 columns per 128-byte K slab, staged
-// once through the ring's slots; only token tiles stream through the ring and the MMAs read their
-// A operand from tensor memory.  What this relieves is shared-memory bandwidth, which is what
-// bounds the streaming form at long K: an MMA of 128 x 128 x 32 reads 8 KB of operands from shared
-// memory while TMA writes the next 8 KB into it, against 128 bytes per cycle in total (measured:
-// 165 cycles per MMA instead of 64, the MMA warp busy 85 % of the time, the epilogue idle a
-// third of it); with W in tensor memory both halve.  Grid = m_tiles * groups CTAs; the
-// accumulators take the columns W leaves (two buffers at K = 1024, three below).
+// AStat ("A stationary", option gemm_order=w_stationary only): a CTA works on one tile of 128
+// channels for the whole launch and keeps that slice of W (all K slabs, K <= 1024) in TENSOR memory,
+// 32 columns per 128-byte K slab, staged once through the ring's slots; only token tiles stream
+// through the ring and the MMAs read their A operand from tensor memory.  It halves the operand
+// bytes that cross shared memory, and measures SLOWER than the streaming form at every K (0.31
+// against 0.28 ms at K = 1024, 0.16 against 0.14 at K = 256): shared-memory bandwidth is not what
+// holds the streaming form's MMA rate (about 155 cycles per 128 x 128 x 32 MMA in the kernel, 68
+// for the same instruction stream issued from resident operands), and the fixed channel tile per
+// CTA costs balance.  Grid = m_tiles * groups CTAs; the accumulators take the columns W leaves
+// (two buffers at K = 1024, three below).
 // Tie = false (with Fast): the requantization rounds half up, which equals the reference's
 // round-half-even because no channel can meet an exact tie in its accumulator range (checked
 // when the weights are set: rescale_can_tie).
@@ -221,7 +222,6 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = tc::idesc_i8(GM, GN, true, !XUnsigned);
-            long long it = 0;
             bool ok = true;
             int m0;
             long long n0;
@@ -233,32 +233,51 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                 ok = tc::mbar_wait(w_done, 0, WAIT_BUDGET);
                 tc::tc_fence_after_sync();
             }
+            // The loop below is this thread's whole instruction stream and it shares its scheduler
+            // with four busy epilogue warps: ring position, barrier addresses and descriptor low words
+            // advance by one add each, nothing is recomputed per slab.
+            const uint32_t full0 = tc::smem_u32(full), empty0 = tc::smem_u32(empty);
+            const uint32_t ring_lo0 = tc::smem_desc_sw128_lo(tc::smem_u32(ring));
+            constexpr uint32_t SLOT_LO = (uint32_t)((AStat ? GN * KB : STAGE_BYTES) >> 4);   // descriptor units per ring slot
+            constexpr uint32_t B_LO = AStat ? 0u : (uint32_t)((GM * KB) >> 4);               // x slab behind the W slab
+            int s = 0;
+            uint32_t ph = 0, slot_lo = ring_lo0;
+            int buf = 0;
+            uint32_t acc_ph = 1;   // parity to wait for on acc_empty: buffers start out free
             for (long long local = 0; ok && tile_of(local, m0, n0); ++local) {
-                const int buf = (int)(local % nacc);
-                if (!WAITED(2, tc::mbar_wait(&acc_empty[buf], (uint32_t)(((local / nacc) & 1) ^ 1), WAIT_BUDGET))) { ok = false; break; }
+                if (!WAITED(2, tc::mbar_wait(&acc_empty[buf], acc_ph, WAIT_BUDGET))) { ok = false; break; }
                 tc::tc_fence_after_sync();
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = (int)(it % NST);
-                    const uint32_t ph = (uint32_t)((it / NST) & 1);
-                    if (!WAITED(1, tc::mbar_wait(&full[s], ph, WAIT_BUDGET))) { ok = false; break; }
-                    tc::tc_fence_after_sync();
+                const uint32_t d_col = tmem_base + (uint32_t)(buf * GN);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    // (TMA's writes are ordered before the MMAs by the barrier alone; the tcgen05 fence
+                    // belongs after the accumulator hand-over above, not here)
+                    if (!WAITED(1, tc::mbar_wait_addr(full0 + 8u * (uint32_t)s, ph, WAIT_BUDGET))) { ok = false; break; }
                     if (AStat) {
-                        const uint64_t b_desc = tc::smem_desc_sw128(tc::smem_u32(ring + (size_t)s * GN * KB));
-#pragma unroll
-                        for (int ks = 0; ks < KB / 32; ++ks)
-                            tc::mma_i8_ts(tmem_base + buf * GN, tmem_base + w_col + (uint32_t)(kb * 32 + ks * 8), b_desc + 2 * ks,
-                                          idesc, (kb | ks) != 0);
+                        const uint32_t a_col = tmem_base + w_col + (uint32_t)(kb * 32);
+                        tc::mma_i8_ts_lo(d_col, a_col, slot_lo, idesc, (uint32_t)kb);
+                        tc::mma_i8_ts_lo(d_col, a_col + 8, slot_lo + 2, idesc, 1u);
+                        tc::mma_i8_ts_lo(d_col, a_col + 16, slot_lo + 4, idesc, 1u);
+                        tc::mma_i8_ts_lo(d_col, a_col + 24, slot_lo + 6, idesc, 1u);
                     } else {
-                        const uint32_t a_addr = tc::smem_u32(tiles + (size_t)s * STAGE_BYTES);
-                        const uint64_t a_desc = tc::smem_desc_sw128(a_addr);
-                        const uint64_t b_desc = tc::smem_desc_sw128(a_addr + GM * KB);
-#pragma unroll
-                        for (int ks = 0; ks < KB / 32; ++ks)
-                            tc::mma_i8(tmem_base + buf * GN, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (kb | ks) != 0);
+                        tc::mma_i8_lo(d_col, slot_lo, slot_lo + B_LO, idesc, (uint32_t)kb);
+                        tc::mma_i8_lo(d_col, slot_lo + 2, slot_lo + B_LO + 2, idesc, 1u);
+                        tc::mma_i8_lo(d_col, slot_lo + 4, slot_lo + B_LO + 4, idesc, 1u);
+                        tc::mma_i8_lo(d_col, slot_lo + 6, slot_lo + B_LO + 6, idesc, 1u);
                     }
-                    tc::mma_commit(&empty[s]);
+                    static_assert(KB / 32 == 4, "four MMAs of K = 32 per slab");
+                    tc::mma_commit_addr(empty0 + 8u * (uint32_t)s);
+                    slot_lo += SLOT_LO;
+                    if (++s == NST) {
+                        s = 0;
+                        ph ^= 1u;
+                        slot_lo = ring_lo0;
+                    }
                 }
                 if (ok) tc::mma_commit(&acc_full[buf]);
+                if (++buf == nacc) {
+                    buf = 0;
+                    acc_ph ^= 1u;
+                }
             }
             if (!ok) atomicExch(failed, 1);
 #ifdef QGRU_STAMPS
@@ -442,13 +461,10 @@ cudaError_t launch_f(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, lon
                      LinearConsts lc, PreScale ps, int *abort_flag, int sms, int order, cudaStream_t st) {
     const int m_tiles = (C + GM - 1) / GM;
     const long long n_tiles = (N + GN - 1) / GN;
-    // W-stationary form (W in tensor memory): where K is long enough for operand traffic through shared
-    // memory to set the pace (option gemm_order: auto takes it from K = 512), every CTA can get a channel
-    // tile and the token tiles spread evenly enough over the CTA groups
+    // W-stationary form (W in tensor memory): on request only (option gemm_order=w_stationary), it is
+    // the slower of the two; needs K <= 1024 and a channel tile per CTA
     const bool fits = Kpad <= 1024 && m_tiles <= sms;
-    const long long grp = std::max<long long>(1, std::min<long long>(sms / m_tiles, n_tiles));
-    const bool balanced = (long long)m_tiles * grp * 10 >= (long long)sms * 8;   // at least 80 % of the SMs get a CTA
-    const bool astat = fits && (order == 2 || (order == 0 && Kpad >= 512 && balanced));
+    const bool astat = fits && order == 2;
     if (astat) {
         auto kern = k_gemm_wx_tc<XU, IhT, Fast, true, Tie>;
         const size_t smem = astat_smem(Kpad);

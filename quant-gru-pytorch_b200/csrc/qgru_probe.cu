@@ -29,7 +29,7 @@ constexpr long long PROBE_WAIT = 2000000000ll;
 // the completion of the last MMA of the slowest issuer.
 __global__ void __launch_bounds__(1024, 1)
 k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, int issuers, int neighbour_mode, int commit_every,
-               long long *cycles, int *timeouts) {
+               long long *cycles, int *timeouts, const unsigned char *src) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = tc::smem_u32(smem_raw);
     unsigned char *base = smem_raw + (((raw + 1023u) & ~1023u) - raw);
@@ -40,9 +40,17 @@ k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, int issuers, in
     volatile int *done = reinterpret_cast<volatile int *>(slot + 1);
     long long *cyc_w = reinterpret_cast<long long *>(bar + 12);           // [issuers]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int i = threadIdx.x; i < (16384 + 32768) / 4; i += blockDim.x) reinterpret_cast<uint32_t *>(base)[i] = 0u;
+    // operand bytes: zeros, or (neighbour_mode bit 8) pseudo-random, which is what a real product
+    // toggles in the multipliers - the two differ in power, not in the instruction stream
+    const bool random_fill = (neighbour_mode & 256) != 0;
+    // bit 9: the issuing warps keep all 32 lanes in the loop and one elected lane issues, so that the
+    // control flow around the MMAs is warp-uniform and their operands can live in uniform registers
+    const bool uniform_flow = (neighbour_mode & 512) != 0;
+    neighbour_mode &= 255;
+    for (int i = threadIdx.x; i < (16384 + 32768) / 4; i += blockDim.x)
+        reinterpret_cast<uint32_t *>(base)[i] = random_fill ? ((uint32_t)i * 2654435761u) ^ ((uint32_t)i * 40503u << 13) ^ (blockIdx.x * 97u) : 0u;
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 9; ++i) tc::mbar_init(&bar[i], 1);
+        for (int i = 0; i < 10; ++i) tc::mbar_init(&bar[i], 1);   // 0-3 chain ends, 4 never completes, 5-8 periodic commits, 9 bulk copies
         *done = 0;
         tc::fence_barrier_init();
     }
@@ -51,7 +59,47 @@ k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, int issuers, in
     __syncthreads();
     tc::tc_fence_after_sync();
     const uint32_t tmem = *slot;
-    if (warp < issuers) {
+    if (warp < issuers && uniform_flow) {
+        uint32_t leader;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "elect.sync _|p, 0xffffffff;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(leader));
+        const uint32_t idesc = tc::idesc_i8(M, N, true, true);
+        const uint32_t a_lo = tc::smem_desc_sw128_lo(tc::smem_u32(a_tile));
+        const uint32_t b_lo = tc::smem_desc_sw128_lo(tc::smem_u32(b_tile));
+        const uint32_t a_col = tmem + (uint32_t)(issuers * n_acc * N);
+        const uint32_t d0 = tmem + (uint32_t)(warp * n_acc * N);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        const int passes = mmas / 8;
+        const long long t0 = clock64();
+        uint32_t acc = 0;   // accumulator rotation, advanced in the loop like a GEMM's ring position
+        for (int i = 0; i < passes; ++i) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t d = d0 + acc * (uint32_t)N;
+                if (leader) {
+                    if (a_in_tmem) tc::mma_i8_ts_lo(d, a_col + (uint32_t)(j & 3) * 8, b_lo + 2 * (uint32_t)(j & 3), idesc, 1u);
+                    else tc::mma_i8_lo(d, a_lo + 2 * (uint32_t)(j & 3), b_lo + 2 * (uint32_t)(j & 3), idesc, 1u);
+                }
+                if (++acc == (uint32_t)n_acc) acc = 0;
+                if (commit_every == 4 && j == 3 && leader) tc::mma_commit(&bar[5 + warp]);
+            }
+            if ((commit_every == 4 || commit_every == 8) && leader) tc::mma_commit(&bar[5 + warp]);
+        }
+        if (leader) tc::mma_commit(&bar[warp]);
+        const bool ok = tc::mbar_wait(&bar[warp], 0, PROBE_WAIT);
+        const long long t1 = clock64();
+        if (lane == 0) {
+            cyc_w[warp] = t1 - t0;
+            if (!ok) atomicAdd(timeouts, 1);
+            __threadfence_block();
+            atomicAdd(const_cast<int *>(done), 1);
+        }
+    } else if (warp < issuers) {
         if (lane == 0) {
             const uint32_t idesc = tc::idesc_i8(M, N, true, true);
             const uint64_t adesc = tc::smem_desc_sw128(tc::smem_u32(a_tile));
@@ -107,22 +155,52 @@ k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, int issuers, in
         const long long t0 = clock64();
         uint32_t x = threadIdx.x;
         const uint32_t tb = tc::smem_u32(base);
+        uint32_t bulk_phase = 0;
+        long long bulk_rounds = 0;
         while (*done < issuers && clock64() - t0 < PROBE_WAIT) {
-            if (neighbour_mode == 0) {
+            if (neighbour_mode == 5) {
+                // the copy engine writing shared memory as a GEMM's operand loads do: the first
+                // neighbour warp keeps four 16 KB bulk copies from global memory in flight
+                if (warp == issuers && lane == 0) {
+                    tc::mbar_expect_tx(&bar[9], 65536u);
+                    for (int i = 0; i < 4; ++i)
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+                                     "r"(tb + 49152u + 4096u + (uint32_t)i * 16384u), "l"(src + (size_t)blockIdx.x * 65536 + (size_t)i * 16384),
+                                     "r"(16384u), "r"(tc::smem_u32(&bar[9])) : "memory");
+                    if (!tc::mbar_wait(&bar[9], bulk_phase, PROBE_WAIT)) atomicAdd(timeouts, 1);
+                    bulk_phase ^= 1u;
+                    ++bulk_rounds;
+                } else {
+                    tc::mbar_try_wait(&bar[4], 0);
+                }
+            } else if (neighbour_mode == 0) {
                 tc::mbar_try_wait(&bar[4], 0);
             } else if (neighbour_mode == 1) {
 #pragma unroll
                 for (int i = 0; i < 64; ++i) x = x * 1664525u + 1013904223u;
-            } else {
+            } else if (neighbour_mode == 2) {
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     uint32_t v;
                     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(tb + ((x & 4095u) << 2)));
                     x = x * 1664525u + 1013904223u + v;
                 }
+            } else if (neighbour_mode == 3) {
+                // a warp draining accumulators: 16-column loads from its quadrant of tensor memory
+                int32_t v[16];
+                tc::tmem_ld16(tmem + ((uint32_t)((warp & 3) * 32) << 16), v);
+                tc::tmem_ld_wait();
+                x += (uint32_t)v[0];
+            } else {
+                // a warp writing 128-bit words into the operand tiles' neighbourhood of shared memory
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(tb + 49152u + 4096u + ((threadIdx.x * 16u + i * 16384u) & 65535u)), "r"(0u) : "memory");
+                }
             }
         }
         if (x == 0xdeadbeefu) atomicAdd(timeouts, 0);   // keeps the arithmetic alive
+        if (neighbour_mode == 5 && warp == issuers && lane == 0) cycles[gridDim.x + blockIdx.x] = bulk_rounds * 65536;
     }
     tc::tc_fence_before_sync();
     __syncthreads();
@@ -136,6 +214,10 @@ k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, int issuers, in
 
 }  // namespace
 }  // namespace qgru
+
+static double g_probe_bulk_bytes_per_cycle = 0.0;
+/* bytes per SM clock the copy engine moved into CTA 0's shared memory during the last probe with neighbour_mode 5 */
+extern "C" QGRU_API double qgru_probe_last_bulk_rate(void) { return g_probe_bulk_bytes_per_cycle; }
 
 extern "C" int qgru_probe_mma_i8_ex(int device, int M, int N, int a_in_tmem, int accumulators, int mmas, int ctas,
                                     int issuers, int spinners, int neighbour_mode, double *cycles_per_mma,
@@ -159,33 +241,37 @@ extern "C" int qgru_probe_mma_i8_commits(int device, int M, int N, int a_in_tmem
     ctas = std::min(ctas, sms);
     long long *d_cycles = nullptr;
     int *d_to = nullptr;
+    unsigned char *d_src = nullptr;
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     int rc = QGRU_ERR_CUDA;
-    const size_t smem = 16384 + 32768 + 256 + 1024;
+    const size_t smem = 16384 + 32768 + 4096 + 65536 + 16384 + 1024;
     const int threads = 32 * (issuers + spinners);
     do {
-        if (cudaMalloc(&d_cycles, sizeof(long long) * ctas) != cudaSuccess) break;
+        if (cudaMalloc(&d_cycles, sizeof(long long) * ctas * 2) != cudaSuccess) break;
+        if (cudaMemset(d_cycles, 0, sizeof(long long) * ctas * 2) != cudaSuccess) break;
+        if ((neighbour_mode & 255) == 5 && (cudaMalloc(&d_src, (size_t)ctas * 65536) != cudaSuccess || cudaMemset(d_src, 1, (size_t)ctas * 65536) != cudaSuccess)) break;
         if (cudaMalloc(&d_to, sizeof(int)) != cudaSuccess) break;
         if (cudaMemset(d_to, 0, sizeof(int)) != cudaSuccess) break;
         if (cudaFuncSetAttribute(k_probe_mma_i8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) break;
         if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) break;
-        k_probe_mma_i8<<<ctas, threads, smem>>>(M, N, a_in_tmem, accumulators, std::min(mmas, 256) / 8 * 8, issuers, neighbour_mode, commit_every, d_cycles, d_to);   // warm-up
+        k_probe_mma_i8<<<ctas, threads, smem>>>(M, N, a_in_tmem, accumulators, std::min(mmas, 256) / 8 * 8, issuers, neighbour_mode, commit_every, d_cycles, d_to, d_src);   // warm-up
         cudaEventRecord(e0);
-        k_probe_mma_i8<<<ctas, threads, smem>>>(M, N, a_in_tmem, accumulators, mmas, issuers, neighbour_mode, commit_every, d_cycles, d_to);
+        k_probe_mma_i8<<<ctas, threads, smem>>>(M, N, a_in_tmem, accumulators, mmas, issuers, neighbour_mode, commit_every, d_cycles, d_to, d_src);
         cudaEventRecord(e1);
         if (cudaEventSynchronize(e1) != cudaSuccess || cudaGetLastError() != cudaSuccess) break;
         float ms = 0.f;
         cudaEventElapsedTime(&ms, e0, e1);
-        std::vector<long long> cyc(ctas);
+        std::vector<long long> cyc(ctas * 2);
         int to = 0;
-        if (cudaMemcpy(cyc.data(), d_cycles, sizeof(long long) * ctas, cudaMemcpyDeviceToHost) != cudaSuccess) break;
+        if (cudaMemcpy(cyc.data(), d_cycles, sizeof(long long) * ctas * 2, cudaMemcpyDeviceToHost) != cudaSuccess) break;
         if (cudaMemcpy(&to, d_to, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) break;
         if (to) {
             rc = QGRU_ERR_TIMEOUT;
             break;
         }
         long long worst = 0;
-        for (long long c : cyc) worst = std::max(worst, c);
+        for (int i = 0; i < ctas; ++i) worst = std::max(worst, cyc[i]);
+        g_probe_bulk_bytes_per_cycle = worst > 0 ? (double)cyc[ctas] / (double)worst : 0.0;
         *cycles_per_mma = (double)worst / mmas;
         *tera_ops = 2.0 * M * N * 32.0 * (double)mmas * issuers * ctas / (ms * 1e-3) / 1e12;
         rc = QGRU_OK;
@@ -195,6 +281,7 @@ extern "C" int qgru_probe_mma_i8_commits(int device, int M, int N, int a_in_tmem
     if (e1) cudaEventDestroy(e1);
     cudaFree(d_cycles);
     cudaFree(d_to);
+    cudaFree(d_src);
     return rc;
 }
 

@@ -593,10 +593,17 @@ def probe_mma_i8(M=128, N=256, a_in_tmem=False, accumulators=1, mmas=16384, ctas
     """Issue rate of tcgen05.mma kind::i8 for one shape (qgru_probe_mma_i8_ex): returns
     (SM cycles per MMA in a back-to-back chain of one issuing thread, aggregate 1e12 int8 ops/s
     over `ctas` SMs and `issuers` issuing warps); `spinners` neighbour warps wait (mode 0), compute (1) or
-    load from shared memory (2) beside them."""
+    load from shared memory (2), drain tensor memory (3), store to shared memory (4) or keep bulk
+    copies from global into shared memory in flight (5; `probe_last_bulk_rate()` then gives their
+    bytes per clock) beside them; + 256: pseudo-random operand bytes instead of zeros."""
     cyc, tops = C.c_double(), C.c_double()
     st = _cabi.lib().qgru_probe_mma_i8_commits(int(device), int(M), int(N), int(bool(a_in_tmem)), int(accumulators),
                                                int(mmas), int(ctas), int(issuers), int(spinners), int(neighbour_mode),
                                                int(commit_every), C.byref(cyc), C.byref(tops))
     _cabi.check(st, "qgru_probe_mma_i8_commits")
     return cyc.value, tops.value
+
+
+def probe_last_bulk_rate():
+    """Bytes per SM clock the bulk copies of CTA 0 moved in the last neighbour_mode 5 probe."""
+    return float(_cabi.lib().qgru_probe_last_bulk_rate())
