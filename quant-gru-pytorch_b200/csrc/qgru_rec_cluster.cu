@@ -376,6 +376,42 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
         }
         // the TMA-written initial state must be complete before h_{t-1} is read from the tile
         ok = tc::mbar_wait(h_full, 0, WAIT_BUDGET) && ok;
+        // A warp with one chunk per step (NB <= 4 * EPW rows, one sub-group) computes the same cells every
+        // step, so h_{t-1} of its cells is what it produced a step ago: kept in registers, not read back
+        // from the state tile (one byte load with its swizzled address per cell).
+        const bool keep_h = NG == 1 && nchunks <= EPW;
+        int32_t h_keep[MT][CH];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int i = 0; i < CH; ++i) h_keep[mt][i] = 0;
+        // the CH cells of a chunk to whichever outputs the caller asked for: the choice is made once
+        // per chunk, not per cell; `base` is the element offset of (time slot, first row of the sub-group)
+        auto store_outputs = [&](const int32_t(&v)[MT][CH], int c0, int nb, size_t base) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                if (!j_ok[mt]) continue;
+                const uint32_t oj = (uint32_t)(c0 * a.H + j0 + mt * 128 + u);
+                if (a.hf_out) {
+                    float *o = a.hf_out + base;
+#pragma unroll
+                    for (int i = 0; i < CH; ++i)
+                        if (c0 + i < nb) o[oj + (uint32_t)(i * a.H)] = (float)(v[mt][i] - gc.zp_h) * gc.h_scale;
+                }
+                if (a.hq_out) {
+                    int32_t *o = a.hq_out + base;
+#pragma unroll
+                    for (int i = 0; i < CH; ++i)
+                        if (c0 + i < nb) o[oj + (uint32_t)(i * a.H)] = v[mt][i];
+                }
+                if (a.h8_out) {
+                    uint8_t *o = a.h8_out + base;
+#pragma unroll
+                    for (int i = 0; i < CH; ++i)
+                        if (c0 + i < nb) o[oj + (uint32_t)(i * a.H)] = (uint8_t)v[mt][i];
+                }
+            }
+        };
         for (int s = 0; s < a.T; ++s) {
             const int t = a.reverse ? (a.T - 1 - s) : s;
             const long long out_slot = a.reverse ? (a.T - 1 - s) : (s + 1);
@@ -384,6 +420,11 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
             const int bg0 = b0 + g * a.NB;                                   // first batch row of this sub-group
             const int nb = max(0, min(a.NB, a.b_off + a.b_cnt - bg0));     // its rows that exist
             const unsigned char *h_cur = h_tile + (size_t)(2 * g + (s & 1)) * h_buf_bytes;
+            // this step's rows of W*x+bw and of the outputs: one warp-uniform base each, 32-bit offsets
+            // per cell (a sub-group's rows of one step span far less than 2^32 elements)
+            const IhT *ih_s = ihp + ((size_t)t * a.B + bg0) * a.C;
+            const size_t out_base = (size_t)out_slot * BH + (size_t)bg0 * a.H;
+            const bool from_regs = keep_h && s > 0;
             uint64_t *md = &mma_done[3 * g];
             bool waited = false;
             int32_t hn_last[MT][CH];   // the warp's last chunk: its outputs go to global memory after the arrive
@@ -400,12 +441,16 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     for (int i = 0; i < CH; ++i) {
                         const int b = c0 + i;
                         const bool v_ok = b < nb && j_ok[mt];
-                        const size_t row = (size_t)t * a.B + bg0 + b;
+                        const uint32_t off = (uint32_t)(b * a.C + j);
 #pragma unroll
                         for (int k = 0; k < 3; ++k)
-                            ihv[mt][i][k] = (v_ok && !Floor) ? (int32_t)ihp[row * a.C + k * a.H + j] : 0;
-                        const uint8_t hb = v_ok ? h_cur[sw128_offset(b, j, a.NB)] : (uint8_t)0;
-                        hold[mt][i] = state_byte(hb, h_bits);
+                            ihv[mt][i][k] = (v_ok && !Floor) ? (int32_t)ih_s[off + (uint32_t)(k * a.H)] : 0;
+                        if (from_regs) {
+                            hold[mt][i] = h_keep[mt][i];
+                        } else {
+                            const uint8_t hb = v_ok ? h_cur[sw128_offset(b, j, a.NB)] : (uint8_t)0;
+                            hold[mt][i] = state_byte(hb, h_bits);
+                        }
                     }
                 }
                 // All CH cells of a tile are computed before anything is stored: a byte store into
@@ -607,21 +652,14 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                     for (int r = 0; r < a.P; ++r)
                         if (r != p) st_async_u32(map_to_rank(at, (uint32_t)r), word, map_to_rank(bar_nx, (uint32_t)r));
                 }
+                if (!last) store_outputs(hn, c0, nb, out_base);
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    const int j = j0 + mt * 128 + u;
+                for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                     for (int i = 0; i < CH; ++i) {
-                        const int b = c0 + i;
-                        if (!last && b < nb && j_ok[mt]) {
-                            const size_t o = (size_t)out_slot * BH + (size_t)(bg0 + b) * a.H + j;
-                            if (a.hq_out) a.hq_out[o] = hn[mt][i];
-                            if (a.hf_out) a.hf_out[o] = (float)(hn[mt][i] - gc.zp_h) * gc.h_scale;
-                            if (a.h8_out) a.h8_out[o] = (uint8_t)hn[mt][i];
-                        }
                         hn_last[mt][i] = hn[mt][i];
+                        h_keep[mt][i] = hn[mt][i];
                     }
-                }
                 if (last) c_last = c;
             }
             if (ok && !waited) {
@@ -639,22 +677,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
             if (lane == 0 && s + 1 < a.T) tc::mbar_arrive(&h_ready[2 * g + ((s + 1) & 1)]);
             // Outputs of the last chunk leave for global memory after the arrive: nothing in the next
             // step waits for them, so they overlap the exchange and the next MMAs.
-            if (c_last >= 0) {
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    const int j = j0 + mt * 128 + u;
-#pragma unroll
-                    for (int i = 0; i < CH; ++i) {
-                        const int b = c_last * CH + i;
-                        if (b < nb && j_ok[mt]) {
-                            const size_t o = (size_t)out_slot * BH + (size_t)(bg0 + b) * a.H + j;
-                            if (a.hq_out) a.hq_out[o] = hn_last[mt][i];
-                            if (a.hf_out) a.hf_out[o] = (float)(hn_last[mt][i] - gc.zp_h) * gc.h_scale;
-                            if (a.h8_out) a.h8_out[o] = (uint8_t)hn_last[mt][i];
-                        }
-                    }
-                }
-            }
+            if (c_last >= 0) store_outputs(hn_last, c_last * CH, nb, out_base);
             }   // sub-groups
         }
         if (!ok && lane == 0) atomicOr(a.abort_flag, 1);
