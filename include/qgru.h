@@ -413,6 +413,12 @@ QGRU_API double qgru_probe_last_bulk_rate(void);
  *                                           stream per tile (auto), or a CTA keeps one slice of W
  *                                           in tensor memory for the whole launch (slower; kept
  *                                           as a measured alternative)
+ *   "t_chunk"  auto | 0 | N                 cluster recurrence: W*x+bw is computed and consumed N
+ *                                           timesteps at a time (two chunk buffers instead of the
+ *                                           whole sequence; the next chunk's GEMM runs on a second
+ *                                           stream beside this chunk's recurrence).  0: one chunk;
+ *                                           auto: eight chunks where the recurrence leaves half of
+ *                                           the SMs free and T >= 256
  *   "rec"      auto | dp4a | mma | generic  recurrence kernel (generic = int32 storage path)
  *   "exchange" auto | global | cluster      how the CTAs of a batch group exchange h_t
  *   "cell"     auto | fused | generic       gate datapath: tabulated (auto also allows its

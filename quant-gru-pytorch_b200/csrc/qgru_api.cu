@@ -128,6 +128,12 @@ void qgru_destroy(qgru_handle *h) {
     for (int r = 0; r < qgru_handle::kRing; ++r)
         for (int i = 0; i < 4; ++i)
             if (h->ring[r][i]) cudaEventDestroy(h->ring[r][i]);
+    for (int i = 0; i < 2; ++i) {
+        if (h->ev_g[i]) cudaEventDestroy(h->ev_g[i]);
+        if (h->ev_r[i]) cudaEventDestroy(h->ev_r[i]);
+    }
+    if (h->ev_fork) cudaEventDestroy(h->ev_fork);
+    if (h->aux) cudaStreamDestroy(h->aux);
     cudaFree(h->d_flags);
     if (h->h_flags) cudaFreeHost(h->h_flags);
     cudaFree(h->d_bar);
@@ -203,6 +209,10 @@ int qgru_set_option(qgru_handle *h, const char *name, const char *value) {
 #endif
     } else if (n == "test_withhold_arrive") {
         h->opt_withhold = atoi(value) != 0;
+    } else if (n == "t_chunk") {
+        if (v == "auto") h->opt_tchunk = -1;
+        else if (atoi(value) >= 0) h->opt_tchunk = atoi(value);
+        else return fail(h, QGRU_ERR_BAD_ARG, "t_chunk: auto | 0 (whole sequence) | timesteps per chunk");
     } else if (n == "probe_floor") {
         h->opt_floor = atoi(value) != 0;
     } else if (n == "sm_limit") {
@@ -686,23 +696,63 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
             ps.lo = h->gc_host.ih_lo;
         }
     }
-    if ((rc = ensure(h, h->ih, (size_t)N * C * ih_bytes))) return rc;
+    // ---- chunks of timesteps (cluster recurrence with the tensor-core GEMM): W*x+bw exists for two
+    // chunks at a time instead of the whole sequence, and the GEMM of chunk k+1 runs on a second,
+    // low-priority stream beside the recurrence of chunk k, which picks up its initial state where
+    // the launch before it left it (RecMmaArgs::write_final).  Automatic where the recurrence
+    // leaves at least half of the SMs to the GEMM and the sequence is long enough to pay for the
+    // extra launches; one chunk otherwise.
+    int Tc = T;
+    {
+        const bool can_chunk = use_cluster && !use_c64 && !h->opt_floor && h->opt_gemm != 1 && h->Ipad % 128 == 0 &&
+                               h->w8_rows[0] >= (long long)(C + 127) / 128 * 128;
+        if (can_chunk && h->opt_tchunk > 0) Tc = std::min(T, h->opt_tchunk);
+        else if (can_chunk && h->opt_tchunk < 0 && mp.G * mp.P * 2 <= sms && T >= 256) Tc = (T + 7) / 8;
+    }
+    const int n_chunks = (T + Tc - 1) / Tc;
+    const size_t chunk_bytes = ((size_t)Tc * B * C * ih_bytes + 255) & ~size_t(255);
+    if ((rc = ensure(h, h->ih, n_chunks > 1 ? 2 * chunk_bytes : (size_t)N * C * ih_bytes))) return rc;
+    if (n_chunks > 1 && !h->aux) {
+        int lo = 0, hi = 0;
+        CK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+        CK(cudaStreamCreateWithPriority(&h->aux, cudaStreamNonBlocking, lo));
+        for (int i = 0; i < 2; ++i) {
+            CK(cudaEventCreateWithFlags(&h->ev_g[i], cudaEventDisableTiming));
+            CK(cudaEventCreateWithFlags(&h->ev_r[i], cudaEventDisableTiming));
+        }
+        CK(cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming));
+    }
+    const bool rev_dir = (flags & QGRU_FLAG_REVERSE) != 0;
+    // chunk k covers steps [k*Tc, min(T, (k+1)*Tc)), i.e. timesteps from t_lo(k) on
+    auto chunk_T = [&](int k) { return std::min(T, (k + 1) * Tc) - k * Tc; };
+    auto chunk_t0 = [&](int k) { return rev_dir ? T - (k * Tc + chunk_T(k)) : k * Tc; };
+    auto chunk_ih = [&](int k) { return (void *)((char *)h->ih.p + (n_chunks > 1 ? (size_t)(k & 1) * chunk_bytes : 0)); };
 
     CK(cudaEventRecord(h->ev[1], st));
     const LinearConsts lcx = linear_consts(h, 0);
     bool used_tc = false;
-    if (h->opt_gemm != 1) {
+    // the W*x GEMM of chunk k on stream `gs`
+    auto gemm_chunk = [&](int k, cudaStream_t gs) -> int {
         // branch-free epilogue: 32-bit sums and every scale it applies in shift-free form
         // (the launcher also looks at how the second rescale is applied: table or shift-free scale)
         const bool gemm_fast = lcx.fits32 && h->rs_fast[0] && h->opt_cell != 2;
-        rc = tc_gemm_launch(h->tc, (const uint8_t *)h->x8.p, (N + 127) / 128 * 128, h->d_w8[0], h->w8_rows[0],
-                            h->ih.p, N, C, h->Ipad, h->x_uns, ih_bytes, lcx, ps, gemm_fast, h->lin_notie[0] && h->opt_tie != 1,
-                            h->d_flags + 1, sms, st,
-                            &h->err);
+        const long long Nk = (long long)chunk_T(k) * B;
+        const int r = tc_gemm_launch(h->tc, (const uint8_t *)h->x8.p, (N + 127) / 128 * 128, h->d_w8[0], h->w8_rows[0],
+                                     chunk_ih(k), Nk, C, h->Ipad, h->x_uns, ih_bytes, lcx, ps, gemm_fast,
+                                     h->lin_notie[0] && h->opt_tie != 1, h->d_flags + 1, sms, gs, &h->err,
+                                     (long long)chunk_t0(k) * B);
+        if (r == QGRU_OK) h->launches++;
+        return r;
+    };
+    if (n_chunks > 1) {
+        CK(cudaEventRecord(h->ev_fork, st));
+        CK(cudaStreamWaitEvent(h->aux, h->ev_fork, 0));
+    }
+    if (h->opt_gemm != 1) {
+        rc = gemm_chunk(0, st);
         if (rc == QGRU_OK) {
             used_tc = true;
-            h->launches++;
-        } else if (rc != QGRU_ERR_UNSUPPORTED || h->opt_gemm == 2 || fused) {
+        } else if (rc != QGRU_ERR_UNSUPPORTED || h->opt_gemm == 2 || fused || n_chunks > 1) {
             return rc;
         }
     }
@@ -727,7 +777,7 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
         h->bar_groups = groups;
     }
     CK(cudaMemsetAsync(h->d_bar, 0, (size_t)groups * 32 * sizeof(unsigned), st));
-    char buf[320];
+    char buf[400];
     if (use_mma) {
         RecMmaArgs a;
         a.T = T; a.B = B; a.H = h->H; a.Hpad = h->Hpad; a.C = C;
@@ -759,21 +809,42 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
         if (use_c64)
             rc = rec_c64_launch(h->rec_c64, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256, h->h_uns,
                                 ih_bytes, cell_notie, st, &h->err);
-        else if (use_cluster)
-            rc = rec_cluster_launch(h->rec_cl, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256,
-                                    h->h_uns, ih_bytes, fused ? fast_cell : h->gc_host.narrow != 0, fused, h->opt_floor,
-                                    cell_notie, st, &h->err);
-        else
+        else if (use_cluster) {
+            const size_t BHs = (size_t)B * h->H;
+            for (int k = 0; k < n_chunks && rc == QGRU_OK; ++k) {
+                if (n_chunks > 1) {
+                    // the next chunk's GEMM goes to the second stream first: its buffer is free once the
+                    // recurrence of chunk k-1 has read it
+                    if (k + 1 < n_chunks) {
+                        if (k >= 1) CK(cudaStreamWaitEvent(h->aux, h->ev_r[(k + 1) & 1], 0));
+                        if ((rc = gemm_chunk(k + 1, h->aux))) break;
+                        CK(cudaEventRecord(h->ev_g[(k + 1) & 1], h->aux));
+                    }
+                    if (k >= 1) CK(cudaStreamWaitEvent(st, h->ev_g[k & 1], 0));
+                    const size_t slot0 = (size_t)chunk_t0(k) * BHs;   // first output slot of the chunk (both directions)
+                    a.T = chunk_T(k);
+                    a.ih = chunk_ih(k);
+                    a.hq_out = hq_out ? hq_out + slot0 : nullptr;
+                    a.hf_out = hf_out ? hf_out + slot0 : nullptr;
+                    a.h8_out = h8_out ? h8_out + slot0 : nullptr;
+                    a.write_final = k + 1 < n_chunks ? 1 : 0;
+                }
+                rc = rec_cluster_launch(h->rec_cl, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256,
+                                        h->h_uns, ih_bytes, fused ? fast_cell : h->gc_host.narrow != 0, fused, h->opt_floor,
+                                        cell_notie, st, &h->err);
+                if (n_chunks > 1 && rc == QGRU_OK) CK(cudaEventRecord(h->ev_r[k & 1], st));
+            }
+        } else
             rc = rec_mma_launch(h->rec, mp, a, h->gc_host, h->d_w8[1], h->w8_rows[1], (long long)2 * B + 256,
                                 h->h_uns, ih_bytes, h->gc_host.narrow != 0, fused, h->coop != 0, st, &h->err);
         if (rc) return rc;
         h->launches += h->rec.launches + h->rec_cl.launches + h->rec_c64.launches - before;
-        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 exchange=%s cell=%s%s UT=%d MT=%d NB=%d NG=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d r_in=%s narrow=%d ih_bytes=%d shiftfree=%d%d%d%d tie_free=%d%d",
+        snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=tcgen05_i8 exchange=%s cell=%s%s UT=%d MT=%d NB=%d NG=%d P=%d G=%d per_launch=%d smem=%zu tmem_cols=%d r_in=%s narrow=%d ih_bytes=%d shiftfree=%d%d%d%d tie_free=%d%d t_chunks=%d",
                  used_tc ? "tcgen05_i8" : "simt_dp4a", use_cluster ? "cluster_dsmem" : "global", fast_cell ? "fused_shiftfree" : fused ? "fused" : "generic", (use_cluster && h->opt_floor) ? "(FLOOR PROBE: no MMAs, no cell)" : "", use_c64 ? 64 : 128, mp.MT, mp.NB, mp.NG, mp.P, mp.G,
                  mp.groups_per_launch, mp.smem, mp.tmem_cols, !use_cluster || mp.tmem_tiles == 0 ? "smem" : ((use_c64 || mp.tmem_tiles == mp.MT * 3 * (h->Hpad / 128)) ? "tmem" : "tmem+smem"),
                  h->gc_host.narrow, ih_bytes, (int)a.lc.fits32,
                  (int)h->rs_fast[1], h->gc_host.rh_to_n.mq != 0, h->gc_host.uh_to_h.mq != 0,
-                 (int)(used_tc && h->lin_notie[0] && h->opt_tie != 1), (int)cell_notie);
+                 (int)(used_tc && h->lin_notie[0] && h->opt_tie != 1), (int)cell_notie, n_chunks);
     } else {
         RecArgs a;
         a.T = T; a.B = B; a.H = h->H; a.Hpad = h->Hpad; a.C = C;

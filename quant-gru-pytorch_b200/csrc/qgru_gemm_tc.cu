@@ -103,7 +103,7 @@ template <bool XUnsigned, typename IhT, bool Fast, bool AStat, bool Tie>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
              IhT *__restrict__ ih, long long N, int C, int Kpad, LinearConsts lc, PreScale ps,
-             int *abort_flag) {
+             int *abort_flag, int x_row0) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *tiles = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -205,12 +205,12 @@ k_gemm_wx_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ 
                     if (!WAITED(0, tc::mbar_wait(&empty[s], ph ^ 1, WAIT_BUDGET))) { ok = false; break; }
                     if (AStat) {
                         tc::mbar_expect_tx(&full[s], GN * KB);
-                        tc::tma_load_2d(ring + (size_t)s * GN * KB, &map_x, &full[s], kb * KB, (int)n0);
+                        tc::tma_load_2d(ring + (size_t)s * GN * KB, &map_x, &full[s], kb * KB, (int)n0 + x_row0);
                     } else {
                         unsigned char *a = tiles + (size_t)s * STAGE_BYTES;
                         tc::mbar_expect_tx(&full[s], STAGE_BYTES);
                         tc::tma_load_2d(a, &map_w, &full[s], kb * KB, m0);
-                        tc::tma_load_2d(a + GM * KB, &map_x, &full[s], kb * KB, (int)n0);
+                        tc::tma_load_2d(a + GM * KB, &map_x, &full[s], kb * KB, (int)n0 + x_row0);
                     }
                 }
             }
@@ -458,7 +458,7 @@ size_t astat_smem(int) { return (size_t)STAGES_A * GN * KB + 1024 + 256 + PRE_TA
 
 template <bool XU, typename IhT, bool Fast, bool Tie>
 cudaError_t launch_f(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long long N, int C, int Kpad,
-                     LinearConsts lc, PreScale ps, int *abort_flag, int sms, int order, cudaStream_t st) {
+                     LinearConsts lc, PreScale ps, int *abort_flag, int sms, int order, int x_row0, cudaStream_t st) {
     const int m_tiles = (C + GM - 1) / GM;
     const long long n_tiles = (N + GN - 1) / GN;
     // W-stationary form (W in tensor memory): on request only (option gemm_order=w_stationary), it is
@@ -471,7 +471,7 @@ cudaError_t launch_f(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, lon
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         const long long groups = std::max<long long>(1, std::min<long long>(sms / m_tiles, n_tiles));
-        kern<<<(unsigned)(m_tiles * groups), GEMM_THREADS, smem, st>>>(mw, mx, (IhT *)ih, N, C, Kpad, lc, ps, abort_flag);
+        kern<<<(unsigned)(m_tiles * groups), GEMM_THREADS, smem, st>>>(mw, mx, (IhT *)ih, N, C, Kpad, lc, ps, abort_flag, x_row0);
         return cudaGetLastError();
     }
     auto kern = k_gemm_wx_tc<XU, IhT, Fast, false, Tie>;
@@ -479,17 +479,17 @@ cudaError_t launch_f(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, lon
     if (e != cudaSuccess) return e;
     const long long tiles = (long long)m_tiles * n_tiles;
     const unsigned grid = (unsigned)std::min<long long>(tiles, sms);   // persistent: one CTA per SM
-    kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(mw, mx, (IhT *)ih, N, C, Kpad, lc, ps, abort_flag);
+    kern<<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(mw, mx, (IhT *)ih, N, C, Kpad, lc, ps, abort_flag, x_row0);
     return cudaGetLastError();
 }
 
 template <bool XU, typename IhT>
 cudaError_t launch(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long long N, int C, int Kpad,
                    LinearConsts lc, PreScale ps, bool fast, bool notie, int *abort_flag, int sms, int order,
-                   cudaStream_t st) {
-    if (fast && notie) return launch_f<XU, IhT, true, false>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, order, st);
-    return fast ? launch_f<XU, IhT, true, true>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, order, st)
-                : launch_f<XU, IhT, false, true>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, order, st);
+                   int x_row0, cudaStream_t st) {
+    if (fast && notie) return launch_f<XU, IhT, true, false>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, order, x_row0, st);
+    return fast ? launch_f<XU, IhT, true, true>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, order, x_row0, st)
+                : launch_f<XU, IhT, false, true>(mw, mx, ih, N, C, Kpad, lc, ps, abort_flag, sms, order, x_row0, st);
 }
 
 }  // namespace
@@ -497,8 +497,10 @@ cudaError_t launch(const CUtensorMap &mw, const CUtensorMap &mx, void *ih, long 
 int tc_gemm_launch(TcGemmState &s, const uint8_t *x8, long long x_rows_alloc, const int8_t *w8,
                    long long w_rows_alloc, void *ih, long long N, int C, int Kpad, bool x_unsigned,
                    int ih_bytes, LinearConsts lc, PreScale ps, bool fast, bool notie, int *abort_flag, int sms,
-                   cudaStream_t stream, std::string *err) {
-    if (Kpad % KB != 0 || x_rows_alloc < (N + GN - 1) / GN * GN || w_rows_alloc < (C + GM - 1) / GM * GM) {
+                   cudaStream_t stream, std::string *err, long long x_row0) {
+    // (token tiles that reach past the last allocated row read the tensor map's zero fill)
+    if (Kpad % KB != 0 || x_row0 < 0 || x_row0 + N > x_rows_alloc || x_rows_alloc >= 0x7fffffffll ||
+        (x_row0 == 0 && x_rows_alloc < (N + GN - 1) / GN * GN) || w_rows_alloc < (C + GM - 1) / GM * GM) {
         if (err) *err = "tcgen05 GEMM needs K padded to 128 and operand rows padded to the tile";
         return QGRU_ERR_UNSUPPORTED;
     }
@@ -524,14 +526,14 @@ int tc_gemm_launch(TcGemmState &s, const uint8_t *x8, long long x_rows_alloc, co
     fast = fast && (!ps.enabled || tab || (ps.to[0].mq != 0 && ps.to[1].mq != 0 && ps.to[2].mq != 0));
     cudaError_t e;
     if (ih_bytes == 1)
-        e = x_unsigned ? launch<true, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, stream)
-                       : launch<false, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, stream);
+        e = x_unsigned ? launch<true, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, (int)x_row0, stream)
+                       : launch<false, int8_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, (int)x_row0, stream);
     else if (ih_bytes == 2)
-        e = x_unsigned ? launch<true, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, stream)
-                       : launch<false, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, stream);
+        e = x_unsigned ? launch<true, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, (int)x_row0, stream)
+                       : launch<false, int16_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, (int)x_row0, stream);
     else
-        e = x_unsigned ? launch<true, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, stream)
-                       : launch<false, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, stream);
+        e = x_unsigned ? launch<true, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, (int)x_row0, stream)
+                       : launch<false, int32_t>(mw, mx, ih, N, C, Kpad, lc, ps, fast, notie, abort_flag, sms, s.order, (int)x_row0, stream);
     if (e != cudaSuccess) {
         if (err) *err = std::string("tcgen05 GEMM launch: ") + cudaGetErrorString(e);
         return QGRU_ERR_CUDA;

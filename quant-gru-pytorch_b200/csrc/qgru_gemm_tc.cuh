@@ -25,10 +25,12 @@ struct TcGemmState {
 // scale of the channel's gate (the form the fused recurrence cell consumes).
 // Both operands are [rows][Kpad] bytes with Kpad a multiple of 128 and rows ALLOCATED up to a
 // multiple of 128 (x_rows_alloc, w_rows_alloc) so that no tile load leaves the allocation.
+// x_row0: the launch works on tokens x_row0 .. x_row0 + N - 1 of x8 (a chunk of timesteps); ih then
+// holds those N tokens from its first row on.
 // Returns QGRU_ERR_UNSUPPORTED when the shapes do not meet that, QGRU_ERR_CUDA on failure.
 int tc_gemm_launch(TcGemmState &st, const uint8_t *x8, long long x_rows_alloc, const int8_t *w8,
                    long long w_rows_alloc, void *ih, long long N, int C, int Kpad, bool x_unsigned,
                    int ih_bytes, LinearConsts lc, PreScale ps, bool fast, bool notie, int *abort_flag, int sms,
-                   cudaStream_t stream, std::string *err);
+                   cudaStream_t stream, std::string *err, long long x_row0 = 0);
 
 }  // namespace qgru

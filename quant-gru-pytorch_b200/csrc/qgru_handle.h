@@ -52,6 +52,9 @@ struct qgru_handle {
     long long *dbg_stamps = nullptr;
 #endif
     bool opt_withhold = false;               // failure-path test of the dp4a recurrence's bounded group barrier
+    int opt_tchunk = -1;                     // cluster recurrence: timesteps per GEMM / recurrence chunk (0 whole sequence, -1 auto)
+    cudaStream_t aux = nullptr;              // chunked forward: the stream the next chunk's W*x GEMM runs on
+    cudaEvent_t ev_g[2] = {}, ev_r[2] = {}, ev_fork = nullptr;   // chunked forward: GEMM / recurrence of a buffer done
     bool opt_floor = false;                  // cluster recurrence: run the synchronisation-floor probe instead
     // device state that lives with the handle
     GateConsts *d_gc = nullptr;

@@ -653,6 +653,14 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         if (r != p) st_async_u32(map_to_rank(at, (uint32_t)r), word, map_to_rank(bar_nx, (uint32_t)r));
                 }
                 if (!last) store_outputs(hn, c0, nb, out_base);
+                if (a.write_final && s + 1 == a.T) {
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                        for (int i = 0; i < CH; ++i)
+                            if (c0 + i < nb && j_ok[mt])
+                                a.h8[(size_t)(bg0 + c0 + i) * a.Hpad + j0 + mt * 128 + u] = (uint8_t)hn[mt][i];
+                }
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt)
 #pragma unroll

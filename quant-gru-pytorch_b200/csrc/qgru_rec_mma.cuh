@@ -30,6 +30,8 @@ struct RecMmaArgs {
     int32_t *hq_out;        // [(T+1)][B][H] or null
     float *hf_out;          // [(T+1)][B][H] or null
     uint8_t *h8_out = nullptr;   // [(T+1)][B][H] or null: the quantized state in its 8-bit container
+    int write_final = 0;    // cluster kernel: the last step also writes its state to h8 (rows [B][Hpad]), where the
+                            // launch over the next chunk of timesteps picks it up as its initial state
     LinearConsts lc;        // R*h + br epilogue
     const int32_t *tables;  // activation tables (table_off) or, fused, the fused-cell tables (ft_off)
     int n_table;

@@ -434,3 +434,41 @@ def test_input_gemm_tile_orders(oracle, cuda_device, shape, name, order):
     got, plan, _ = _run(case, cuda_device, opts=(("gemm", "tcgen05"), ("gemm_order", order)))
     assert "gemm=tcgen05_i8" in plan
     assert np.array_equal(got, _want(oracle, case))
+
+
+@pytest.mark.parametrize("shape,chunk", [((11, 20, 32, 128), 4), ((9, 40, 64, 512), 2), ((13, 33, 40, 300), 5),
+                                         ((7, 70, 24, 640), 7), ((10, 5, 16, 256), 1), ((6, 200, 48, 384), 4)])
+@pytest.mark.parametrize("cfg", ["default", "cfg2"])
+def test_timestep_chunks(oracle, cuda_device, shape, chunk, cfg):
+    """W*x+bw computed and consumed a chunk of timesteps at a time (the GEMM of the next chunk on a second
+    stream beside the recurrence of this one, each recurrence launch starting from the state the one
+    before left): same bits as the whole sequence in one launch pair, ragged last chunk, initial state
+    given, both directions, 32-bit, float and 8-bit outputs, two forwards in a row on one handle."""
+    import copy
+    import torch
+    T, B, I, H = shape
+    case = make_case(23, T, B, I, H, oracle, config_named(cfg), with_h0=True)
+    want = _want(oracle, case)
+    opts = (("rec", "mma"), ("exchange", "cluster"), ("t_chunk", str(chunk)))
+    got, plan, _ = _run(case, cuda_device, opts=opts)
+    assert f"t_chunks={-(-T // chunk)}" in plan and np.array_equal(got, want), plan
+    whole, plan1, _ = _run(case, cuda_device, opts=(("rec", "mma"), ("exchange", "cluster"), ("t_chunk", "0")))
+    assert "t_chunks=1" in plan1 and np.array_equal(whole, want), plan1
+    flipped = copy.copy(case)
+    flipped.x_q = np.ascontiguousarray(case.x_q[::-1])
+    rev, plan, _ = _run(case, cuda_device, reverse=True, opts=opts)
+    assert np.array_equal(rev, _want(oracle, flipped)[::-1]), plan
+    with gru_ops.Handle(case.I, case.H, device=cuda_device.index or 0) as hd:
+        for k, v in opts:
+            hd.set_option(k, v)
+        hd.set_params(case.params)
+        hd.set_weights_i32(*[_t(a, cuda_device) for a in case.wq])
+        x, h0 = _t(case.x_q, cuda_device), _t(case.h0_q, cuda_device)
+        first = hd.forward_i32(x, h0).cpu().numpy()
+        second = hd.forward_i32(x, h0).cpu().numpy()
+        assert np.array_equal(first, want) and np.array_equal(second, want)
+        xf, hf = _t(case.x, cuda_device), _t(case.h0, cuda_device)
+        f = hd.forward_f32(xf, hf)
+        q8 = hd.forward_f32_q8(xf, hf)
+        scale, zp, _ = hd.h_quant_meta()
+        assert torch.equal((q8.to(torch.int32) - zp).to(torch.float32) * np.float32(scale), f), hd.describe_plan()
