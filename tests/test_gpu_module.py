@@ -50,8 +50,8 @@ def test_float_mode_matches_torch_gru(cuda_device):
         hx = torch.randn(2 if bidir else 1, 7 if bf else 9, 40) * 0.2
         want_o, want_h = ref(x, hx)
         got_o, got_h = mine.cuda()(x.cuda(), hx.cuda())
-        assert _rel_err(got_o.detach().cpu().numpy(), want_o.detach().numpy()) <= 2e-5
-        assert _rel_err(got_h.detach().cpu().numpy(), want_h.detach().numpy()) <= 2e-5
+        assert _rel_err(got_o.detach().cpu().numpy(), want_o.detach().numpy()) <= FLOAT_RTOL
+        assert _rel_err(got_h.detach().cpu().numpy(), want_h.detach().numpy()) <= FLOAT_RTOL
 
 
 @pytest.mark.parametrize("bidir,bf", [(False, False), (True, True)])
@@ -75,7 +75,7 @@ def test_float_mode_trains_like_torch_gru(cuda_device, bidir, bf):
     xm, hm = x.cuda().requires_grad_(), hx.cuda().requires_grad_()
     o2, hn2 = mine(xm, hm)
     ((o2 * g_o.cuda()).sum() + (hn2 * g_h.cuda()).sum()).backward()
-    assert _rel_err(o2.detach().cpu().numpy(), o.detach().numpy()) <= 2e-5
+    assert _rel_err(o2.detach().cpu().numpy(), o.detach().numpy()) <= FLOAT_RTOL
     assert _rel_err(xm.grad.cpu().numpy(), xr.grad.numpy()) <= 5e-5
     assert _rel_err(hm.grad.cpu().numpy(), hr.grad.numpy()) <= 5e-5
     for (name, p_ref), (_, p_mine) in zip(ref.named_parameters(), mine.named_parameters()):

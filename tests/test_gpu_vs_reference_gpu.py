@@ -155,10 +155,15 @@ def test_collector_equals_reference_gpu_collector(oracle, refgpu, cuda_device):
 def test_calibration_histograms_match_reference_gpu(refgpu, cuda_device, gran):
     """Two batches through the calibration forward of both libraries.  Histograms of tensors that
     are read (x, the weights) are equal bit for bit; histograms of computed tensors agree in
-    total, in range to TF32 precision, and in shape: a TF32 error of 3e-4 of the span is more than
-    half a bin of 2048, so single values change bins freely; the cumulative distributions must
-    stay within 5 % of the total of each other (Kolmogorov-Smirnov distance)."""
-    T, B, I, H = 7, 6, 20, 40
+    total, in range to TF32 precision, and in shape.  The bound on the shape follows from that
+    precision: a value that is off by at most e = TF32_RTOL * span, binned on a grid whose ends are
+    off by at most e as well, lands at most k = ceil(2 e / bin width) + 1 bins from where the
+    reference put it, so the two cumulative counts differ at any bin edge by at most the mass of
+    k neighbouring bins, i.e. by at most k times the fullest bin of the reference's histogram.
+    81 920 samples per tensor, so that the fullest bin is a small part of the total for the
+    bell-shaped tensors (the saturating gate outputs pile up in their end bins and get the
+    correspondingly wider bound)."""
+    T, B, I, H = 20, 64, 32, 64
     rng = np.random.default_rng(9)
     W, R, bw, br = gen_weights(rng, I, H)
     g = {"PER_CHANNEL": _cabi.PER_CHANNEL, "PER_GATE": _cabi.PER_GATE, "PER_TENSOR": _cabi.PER_TENSOR}[gran]
@@ -185,7 +190,8 @@ def test_calibration_histograms_match_reference_gpu(refgpu, cuda_device, gran):
         span = max(abs(mx2 - mn2), 1e-30)
         assert abs(mn1 - mn2) <= TF32_RTOL * span + 1e-7 and abs(mx1 - mx2) <= TF32_RTOL * span + 1e-7, name
         moved = np.abs(np.cumsum(c1.astype(np.float64)) - np.cumsum(c2.astype(np.float64))).max()
-        assert moved <= max(3.0, 5e-2 * t1), (name, moved)
+        k_bins = int(np.ceil(2 * TF32_RTOL * len(c2))) + 1
+        assert moved <= k_bins * float(c2.max()), (name, moved, k_bins, float(c2.max()), t1)
     C3 = 3 * H
     for k, name in enumerate(("W", "R", "bw", "br")):
         if gran == "PER_TENSOR":
