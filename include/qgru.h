@@ -390,7 +390,10 @@ QGRU_API int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int accu
  * warps do, (1) run integer arithmetic back to back or (2) run dependent shared-memory loads, as its
  * busy warps do, (3) drain accumulators with 16-column tensor-memory loads or (4) write 128-bit words
  * into shared memory: cycles_per_mma is the slowest issuer's chain time divided by `mmas`, tera_ops
- * counts all issuers.  neighbour_mode + 256 fills the shared-memory operands with pseudo-random bytes
+ * counts all issuers.  neighbour_mode + 1024 (N <= 128): every MMA of a pass of eight reads operand
+ * tiles of its own, spread over 128 KB of shared memory, as a GEMM that streams its operands does
+ * (without it the four K steps of one tile pair repeat); + 512: all 32 lanes of an issuing warp stay
+ * in the loop and an elected lane issues.  neighbour_mode + 256 fills the shared-memory operands with pseudo-random bytes
  * instead of zeros: same instruction stream, the multipliers toggle as in a real product, which
  * shows what part of the zero-operand peak survives the board's power limit. */
 QGRU_API int qgru_probe_mma_i8_ex(int device, int M, int N, int a_in_tmem, int accumulators, int mmas,

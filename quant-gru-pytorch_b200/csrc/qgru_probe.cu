@@ -46,6 +46,10 @@ k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, int issuers, in
     // bit 9: the issuing warps keep all 32 lanes in the loop and one elected lane issues, so that the
     // control flow around the MMAs is warp-uniform and their operands can live in uniform registers
     const bool uniform_flow = (neighbour_mode & 512) != 0;
+    // bit 10: every MMA of a pass reads operand tiles of its own (eight A and eight B tiles spread over
+    // 128 KB of shared memory), as a GEMM that streams its operands does; without it the four K
+    // steps of one 16 KB tile pair repeat
+    const bool rotate = (neighbour_mode & 1024) != 0;
     neighbour_mode &= 255;
     for (int i = threadIdx.x; i < (16384 + 32768) / 4; i += blockDim.x)
         reinterpret_cast<uint32_t *>(base)[i] = random_fill ? ((uint32_t)i * 2654435761u) ^ ((uint32_t)i * 40503u << 13) ^ (blockIdx.x * 97u) : 0u;
@@ -116,6 +120,11 @@ k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, int issuers, in
                 acol[j] = a_col + (uint32_t)(j & 3) * 8;
                 ad[j] = adesc + 2 * (uint64_t)(j & 3);
                 bd[j] = bdesc + 2 * (uint64_t)(j & 3);
+                if (rotate) {
+                    // tile j of A at base + 16 KB * j (j < 4) and of B behind them: (16384 >> 4) descriptor units apart
+                    ad[j] = tc::smem_desc_sw128(tc::smem_u32(base) + (uint32_t)(j & 3) * 16384u) + 2 * (uint64_t)(j >> 2);
+                    bd[j] = tc::smem_desc_sw128(tc::smem_u32(base) + 65536u + (uint32_t)(j & 3) * 16384u) + 2 * (uint64_t)(j >> 2);
+                }
             }
             const int passes = mmas / 8;
             const long long t0 = clock64();
@@ -233,6 +242,9 @@ extern "C" int qgru_probe_mma_i8_commits(int device, int M, int N, int a_in_tmem
     if (!cycles_per_mma || !tera_ops) return QGRU_ERR_BAD_ARG;
     if (!((M == 128 && N % 16 == 0) || (M == 64 && N % 8 == 0)) || N < 8 || N > 256) return QGRU_ERR_BAD_ARG;
     if (issuers < 1 || issuers > 4 || spinners < 0 || issuers + spinners > 32) return QGRU_ERR_BAD_ARG;
+    // the rotating operand tiles are 16 KB apart: rows of at most 128 tokens
+    if ((neighbour_mode & 1024) != 0 && N > 128) return QGRU_ERR_BAD_ARG;
+    if ((neighbour_mode & 255) == 5 && spinners < 1) return QGRU_ERR_BAD_ARG;
     if (accumulators < 1 || issuers * accumulators * N + (a_in_tmem ? 32 : 0) > 512 || mmas < 8 || mmas % 8 != 0 || mmas > (1 << 22) || ctas < 1)
         return QGRU_ERR_BAD_ARG;
     if (cudaSetDevice(device) != cudaSuccess) return QGRU_ERR_CUDA;
