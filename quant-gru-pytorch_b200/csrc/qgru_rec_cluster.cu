@@ -61,7 +61,7 @@ constexpr int CH = 4;                            // batch columns per chunk
 }  // namespace
 
 struct ClusterSmem {
-    size_t r_tiles, h_tile, bars, tables, total;
+    size_t r_tiles, h_tile, bars, tables, h_priv, total;
 };
 
 // r_slots: 16 KB tile slots for R (staging on the way to tensor memory, then home of the tiles
@@ -72,7 +72,11 @@ __host__ __device__ inline ClusterSmem cluster_smem_layout(int r_slots, int KBn,
     s.h_tile = (size_t)r_slots * 16384;
     s.bars = s.h_tile + (size_t)NG * 2 * KBn * NB * 128;   // two state buffers per sub-group
     s.tables = s.bars + 256;
-    s.total = s.tables + (((size_t)n_table * 4 + 15) & ~size_t(15));
+    s.h_priv = s.tables + (((size_t)n_table * 4 + 15) & ~size_t(15));
+    // warps with several chunks of cells per step keep the state of their own cells here, one word
+    // (four row bytes of the thread's unit) per chunk and thread: [chunks per warp][EPI_THREADS]
+    const int chunks = NB / CH;
+    s.total = s.h_priv + ((NG == 1 && chunks > EPW) ? (size_t)((chunks + EPW - 1) / EPW) * EPI_THREADS * 4 : 0);
     return s;
 }
 
@@ -119,7 +123,7 @@ constexpr int MAX_NG = 2;                        // sub-groups of batch rows per
 // the real kernel's time per step is quoted against.
 // Tie = false (branch-free tabulated cell only): the rescales round half up, which equals the
 // reference's round-half-even because none of them can meet an exact tie (rescale_can_tie).
-template <typename IhT, bool Narrow, bool Fused, int MT, bool Floor, bool Tie>
+template <typename IhT, bool Narrow, bool Fused, int MT, bool Floor, bool Tie, bool Priv>
 __global__ void __launch_bounds__(REC_THREADS, 1)
 k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_h,
                      const __grid_constant__ GateConsts gc, RecMmaArgs a) {
@@ -380,6 +384,14 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
         // step, so h_{t-1} of its cells is what it produced a step ago: kept in registers, not read back
         // from the state tile (one byte load with its swizzled address per cell).
         const bool keep_h = NG == 1 && nchunks <= EPW;
+        // With several chunks per step the same holds per chunk, and the four bytes go through a private
+        // word of shared memory per chunk and thread instead: one conflict-free 32-bit load and four
+        // byte extracts against four byte loads at swizzled addresses of the state tile.
+        // (an instance of its own, template Priv: the one-chunk-per-warp instances carry none of this)
+        const bool priv_h = Priv && MT == 1 && NG == 1 && nchunks > EPW;
+        uint32_t *h_priv = reinterpret_cast<uint32_t *>(base + L.h_priv) + (tid - 32);
+        // byte extract of row i: zero-extended (unsigned state) or with the sign replicated
+        const uint32_t priv_sel = a.h_unsigned ? 0x4440u : 0x8880u;
         int32_t h_keep[MT][CH];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
@@ -425,6 +437,8 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
             const IhT *ih_s = ihp + ((size_t)t * a.B + bg0) * a.C;
             const size_t out_base = (size_t)out_slot * BH + (size_t)bg0 * a.H;
             const bool from_regs = keep_h && s > 0;
+            const bool from_priv = priv_h && s > 0;
+            int kc = 0;   // ordinal of the chunk among this warp's chunks
             uint64_t *md = &mma_done[3 * g];
             bool waited = false;
             int32_t hn_last[MT][CH];   // the warp's last chunk: its outputs go to global memory after the arrive
@@ -434,6 +448,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                 // operands that do not depend on this step's MMA: issued first
                 int32_t ihv[MT][CH][3];
                 int32_t hold[MT][CH];
+                const uint32_t priv_word = from_priv ? h_priv[kc * EPI_THREADS] : 0u;
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
                     const int j = j0 + mt * 128 + u;
@@ -447,6 +462,9 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                             ihv[mt][i][k] = (v_ok && !Floor) ? (int32_t)ih_s[off + (uint32_t)(k * a.H)] : 0;
                         if (from_regs) {
                             hold[mt][i] = h_keep[mt][i];
+                        } else if (from_priv) {
+                            // (prmt with four-bit selectors: 8 | i replicates the sign of byte i)
+                            asm("prmt.b32 %0, %1, %2, %3;" : "=r"(hold[mt][i]) : "r"(priv_word), "r"(0u), "r"(priv_sel + 0x1111u * (uint32_t)i));
                         } else {
                             const uint8_t hb = v_ok ? h_cur[sw128_offset(b, j, a.NB)] : (uint8_t)0;
                             hold[mt][i] = state_byte(hb, h_bits);
@@ -641,6 +659,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                 for (int mt = 0; mt < MT && s + 1 < a.T; ++mt) {
                     const uint32_t packed = ((uint32_t)hn[mt][0] & 0xffu) | (((uint32_t)hn[mt][1] & 0xffu) << 8) |
                                             (((uint32_t)hn[mt][2] & 0xffu) << 16) | ((uint32_t)hn[mt][3] << 24);
+                    if (priv_h) h_priv[kc * EPI_THREADS] = packed;
                     const uint32_t v0 = __shfl_sync(0xffffffffu, packed, 4 * x_word + 0);
                     const uint32_t v1 = __shfl_sync(0xffffffffu, packed, 4 * x_word + 1);
                     const uint32_t v2 = __shfl_sync(0xffffffffu, packed, 4 * x_word + 2);
@@ -669,6 +688,7 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
                         h_keep[mt][i] = hn[mt][i];
                     }
                 if (last) c_last = c;
+                ++kc;
             }
             if (ok && !waited) {
                 // A warp without a chunk still waits for this step's MMAs: it must not arrive twice
@@ -698,10 +718,10 @@ k_recurrence_cluster(const __grid_constant__ CUtensorMap map_r, const __grid_con
     if (warp == 0) tc::tmem_dealloc(tmem_base, tmem_cols);
 }
 
-template <typename IhT, bool Narrow, bool Fused, int MT, bool Floor, bool Tie = true>
+template <typename IhT, bool Narrow, bool Fused, int MT, bool Floor, bool Tie = true, bool Priv = false>
 cudaError_t launch_one(const CUtensorMap &mr, const CUtensorMap &mh, const GateConsts &gc, RecMmaArgs &a,
                        int grid, size_t smem, cudaStream_t st) {
-    auto kern = k_recurrence_cluster<IhT, Narrow, Fused, MT, Floor, Tie>;
+    auto kern = k_recurrence_cluster<IhT, Narrow, Fused, MT, Floor, Tie, Priv>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
@@ -740,6 +760,15 @@ cudaError_t launch_any(bool fused, bool narrow, int ih_bytes, int MT, bool floor
         return (fused && narrow && ih_bytes == 2 && MT == 1)
                    ? launch_one<int16_t, true, true, 1, true>(mr, mh, gc, a, grid, smem, st)
                    : cudaErrorNotSupported;
+    // several chunks of cells per warp and step: the instance that keeps the state of a warp's own cells
+    // in private words of shared memory (branch-free fused cell, one tile per CTA, one sub-group)
+    if (fused && narrow && MT == 1 && a.NG == 1 && a.NB / CH > EPW) {
+        if (notie)
+            return ih_bytes == 2 ? launch_one<int16_t, true, true, 1, false, false, true>(mr, mh, gc, a, grid, smem, st)
+                                 : launch_one<int32_t, true, true, 1, false, false, true>(mr, mh, gc, a, grid, smem, st);
+        return ih_bytes == 2 ? launch_one<int16_t, true, true, 1, false, true, true>(mr, mh, gc, a, grid, smem, st)
+                             : launch_one<int32_t, true, true, 1, false, true, true>(mr, mh, gc, a, grid, smem, st);
+    }
     if (fused && narrow && notie)
         return ih_bytes == 2 ? launch_notie<int16_t>(MT, mr, mh, gc, a, grid, smem, st)
                              : launch_notie<int32_t>(MT, mr, mh, gc, a, grid, smem, st);
