@@ -354,7 +354,11 @@ QGRU_API int qgru_forward_f32_host(qgru_handle *h, int T, int B, const float *x,
 
 /* Blocks until the work queued on `stream` by this handle is done and reports a device-side
  * bounded-wait expiry (QGRU_ERR_TIMEOUT) or CUDA error, as the reference's
- * cudaDeviceSynchronize + cudaGetLastError + throw does (src/gru_interface.cc:594-602). */
+ * cudaDeviceSynchronize + cudaGetLastError + throw does (src/gru_interface.cc:594-602).
+ * The device-side status words belong to the handle and every forward clears them when it starts:
+ * the call reports on the LAST forward queued before it.  A caller that queues several forwards
+ * on one handle without synchronising in between learns the status of the last one only; call
+ * this after each forward whose status matters (the host-buffer entry points do). */
 QGRU_API int qgru_synchronize(qgru_handle *h, void *stream);
 
 /* Timing of the two kernels of the most recent forward, measured with CUDA events on the
