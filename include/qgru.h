@@ -420,6 +420,8 @@ QGRU_API double qgru_probe_last_bulk_rate(void);
  *                                           stream per tile (auto), or a CTA keeps one slice of W
  *                                           in tensor memory for the whole launch (slower; kept
  *                                           as a measured alternative)
+ *   "gemv_r"   auto | smem                  one-CTA-per-row recurrence: R held in registers for all
+ *                                           steps (auto, tabulated cell, H <= 256) or in shared memory
  *   "t_chunk"  auto | 0 | N                 cluster recurrence: W*x+bw is computed and consumed N
  *                                           timesteps at a time (two chunk buffers instead of the
  *                                           whole sequence; the next chunk's GEMM runs on a second

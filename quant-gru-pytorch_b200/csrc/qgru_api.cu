@@ -209,6 +209,10 @@ int qgru_set_option(qgru_handle *h, const char *name, const char *value) {
 #endif
     } else if (n == "test_withhold_arrive") {
         h->opt_withhold = atoi(value) != 0;
+    } else if (n == "gemv_r") {
+        if (v == "auto") h->opt_gemv_r = 0;
+        else if (v == "smem") h->opt_gemv_r = 1;
+        else return fail(h, QGRU_ERR_BAD_ARG, "gemv_r: auto|smem");
     } else if (n == "t_chunk") {
         if (v == "auto") h->opt_tchunk = -1;
         else if (atoi(value) >= 0) h->opt_tchunk = atoi(value);
@@ -616,8 +620,29 @@ bool gemv_fits(const qgru_handle *h) {
     return h->Hpad <= 256 && gemv_smem(h, n_tab) <= (size_t)h->smem_optin;
 }
 
+// The register-resident form of the one-CTA-per-row recurrence: the tabulated branch-free cell, Hpad
+// 128 or 256 (option gemv_r=smem keeps R in shared memory).
+bool gemv_reg_ok(const qgru_handle *h, bool fused) { return fused && h->opt_gemv_r != 1 && (h->Hpad == 128 || h->Hpad == 256); }
+size_t gemv_reg_smem(const qgru_handle *h, int n_table) {
+    const size_t units = (size_t)(h->H + 15) / 16 * 16;
+    return (((size_t)n_table * 4 + 15) & ~size_t(15)) + (size_t)2 * 2 * (h->Hpad / 2 + 16) + 3 * units * sizeof(FastLin);
+}
+
+template <bool HU, typename IhT>
+int launch_gemv_reg(qgru_handle *h, RecArgs &a, cudaStream_t st) {
+    auto kern = h->Hpad == 128 ? k_recurrence_gemv_reg<HU, IhT, 64> : k_recurrence_gemv_reg<HU, IhT, 128>;
+    const size_t smem = gemv_reg_smem(h, a.n_table);
+    CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int threads = 2 * ((h->H + 15) / 16 * 16);
+    kern<<<a.B, threads, smem, st>>>(h->gc_host, a);
+    CK(cudaGetLastError());
+    h->launches++;
+    return QGRU_OK;
+}
+
 template <bool HU, typename IhT>
 int launch_gemv(qgru_handle *h, RecArgs &a, bool fused, cudaStream_t st) {
+    if (gemv_reg_ok(h, fused)) return launch_gemv_reg<HU, IhT>(h, a, st);
     auto kern = fused ? k_recurrence_gemv<HU, IhT, 2>
                       : (h->gc_host.narrow ? k_recurrence_gemv<HU, IhT, 1> : k_recurrence_gemv<HU, IhT, 0>);
     const size_t smem = gemv_smem(h, a.n_table);
@@ -873,9 +898,10 @@ int run_fast(qgru_handle *h, int T, int B, int32_t *hq_out, float *hf_out, unsig
             else if (ih_bytes == 2) rc = h->h_uns ? launch_gemv<true, int16_t>(h, a, fused, st) : launch_gemv<false, int16_t>(h, a, fused, st);
             else rc = h->h_uns ? launch_gemv<true, int32_t>(h, a, fused, st) : launch_gemv<false, int32_t>(h, a, fused, st);
             if (rc) return rc;
-            snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=gemv cell=%s rows_per_cta=1 ctas=%d smem=%zu narrow=%d ih_bytes=%d",
-                     used_tc ? "tcgen05_i8" : "simt_dp4a", fused ? "fused_shiftfree" : "generic", B,
-                     gemv_smem(h, a.n_table), h->gc_host.narrow, ih_bytes);
+            snprintf(buf, sizeof(buf), "path=int8 gemm=%s rec=gemv cell=%s r_in=%s rows_per_cta=1 ctas=%d smem=%zu narrow=%d ih_bytes=%d",
+                     used_tc ? "tcgen05_i8" : "simt_dp4a", fused ? "fused_shiftfree" : "generic",
+                     gemv_reg_ok(h, fused) ? "registers" : "smem", B,
+                     gemv_reg_ok(h, fused) ? gemv_reg_smem(h, a.n_table) : gemv_smem(h, a.n_table), h->gc_host.narrow, ih_bytes);
         } else {
             if (h->ih_bytes == 1) rc = h->h_uns ? launch_rec<true, int8_t>(h, a, pl, st) : launch_rec<false, int8_t>(h, a, pl, st);
             else rc = h->h_uns ? launch_rec<true, int16_t>(h, a, pl, st) : launch_rec<false, int16_t>(h, a, pl, st);

@@ -52,6 +52,7 @@ struct qgru_handle {
     long long *dbg_stamps = nullptr;
 #endif
     bool opt_withhold = false;               // failure-path test of the dp4a recurrence's bounded group barrier
+    int opt_gemv_r = 0;                      // one-CTA-per-row recurrence: 0 auto (R in registers where the form exists), 1 R in shared memory
     int opt_tchunk = -1;                     // cluster recurrence: timesteps per GEMM / recurrence chunk (0 whole sequence, -1 auto)
     cudaStream_t aux = nullptr;              // chunked forward: the stream the next chunk's W*x GEMM runs on
     cudaEvent_t ev_g[2] = {}, ev_r[2] = {}, ev_fork = nullptr;   // chunked forward: GEMM / recurrence of a buffer done

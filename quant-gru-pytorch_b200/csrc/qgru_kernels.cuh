@@ -568,6 +568,109 @@ __global__ void __launch_bounds__(1024, 1) k_recurrence_gemv(const __grid_consta
     }
 }
 
+// The same with R in REGISTERS (tabulated branch-free cell only): a pair of threads owns one hidden
+// unit, each lane half of K for the unit's three gate rows, i.e. 3 * KT bytes of R (KT = Hpad / 2 =
+// 64 or 128) held in 48 or 96 registers for all T steps.  A step then reads only the state (a
+// few hundred bytes, broadcast) from shared memory instead of all of R (196 KB at H = 256, which at
+// 128 bytes per clock is 1536 cycles on its own): KT / 4 * 3 dp4a per thread, one shuffle per
+// gate, the cell on the even lane, one __syncthreads.  The per-unit constants of the R*h + br
+// requantization live in shared memory (the registers belong to R).
+template <bool HUnsigned, typename IhT, int KT>
+__global__ void __launch_bounds__(512, 1) k_recurrence_gemv_reg(const __grid_constant__ GateConsts gc, RecArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    static_assert(KT == 64 || KT == 128, "Hpad = 128 or 256");
+    constexpr int QS = KT + 16;            // the two K halves of a state buffer sit 16 bytes further apart than their length
+    constexpr int HS = 2 * QS;
+    const int NT = blockDim.x;             // 2 * units (units rounded up to 16)
+    int32_t *tables = reinterpret_cast<int32_t *>(smem_raw);
+    size_t off = ((size_t)a.n_table * 4 + 15) & ~size_t(15);
+    unsigned char *hs = smem_raw + off;
+    off += (size_t)2 * HS;
+    FastLin *fls = reinterpret_cast<FastLin *>(smem_raw + off);   // [3][units]
+
+    const int tid = threadIdx.x, half = tid & 1, j = tid >> 1, units = NT >> 1;
+    const int b = blockIdx.x;
+    const bool j_ok = j < a.H;
+
+    for (int i = tid; i < a.n_table; i += NT) tables[i] = a.tables[i];
+    for (int i = tid; i < 2 * KT; i += NT) {
+        const int at = (i / KT) * QS + (i % KT);
+        hs[at] = a.h8[(size_t)b * a.Hpad + i];      // initial state of this row (buffer 0 of h8)
+        hs[HS + at] = 0;
+    }
+    for (int i = tid; i < 3 * units; i += NT) {
+        const int g = i / units, u = i % units;
+        fls[i] = u < a.H ? a.lc.fl[g * a.H + u] : FastLin{0, 0, 0, 0, 0, 0};
+    }
+    const int j_at = (j / KT) * QS + (j % KT);      // where unit j's byte sits in a state buffer
+    uint32_t R[3][KT / 4];
+#pragma unroll
+    for (int g = 0; g < 3; ++g)
+#pragma unroll
+        for (int c = 0; c < KT / 16; ++c) {
+            uint4 w = make_uint4(0u, 0u, 0u, 0u);
+            if (j_ok) w = *reinterpret_cast<const uint4 *>(a.r8 + (size_t)(g * a.H + j) * a.Hpad + half * KT + 16 * c);
+            R[g][4 * c + 0] = w.x;
+            R[g][4 * c + 1] = w.y;
+            R[g][4 * c + 2] = w.z;
+            R[g][4 * c + 3] = w.w;
+        }
+    __syncthreads();
+
+    const size_t BH = (size_t)a.B * a.H;
+    const IhT *ihp = reinterpret_cast<const IhT *>(a.ih);
+    const uint32_t tab = (uint32_t)__cvta_generic_to_shared(tables);
+    const bool worker = half == 0 && j_ok;
+    // W*x + bw of this row: loaded one step ahead, so the cell never waits for global memory
+    auto load_ih = [&](int s, int32_t (&v)[3]) {
+        const int t = a.reverse ? (a.T - 1 - s) : s;
+        const IhT *src = ihp + ((size_t)t * a.B + b) * a.C + j;
+        v[0] = (int32_t)src[0];
+        v[1] = (int32_t)src[a.H];
+        v[2] = (int32_t)src[2 * a.H];
+    };
+    int32_t ihv[3] = {0, 0, 0};
+    if (worker) load_ih(0, ihv);
+    for (int s = 0; s < a.T; ++s) {
+        const long long out_slot = a.reverse ? (a.T - 1 - s) : (s + 1);
+        const unsigned char *h_cur = hs + (size_t)(s & 1) * HS;
+        unsigned char *h_nxt = hs + (size_t)((s + 1) & 1) * HS;
+        int32_t ihn[3] = {0, 0, 0};
+        if (worker && s + 1 < a.T) load_ih(s + 1, ihn);
+        int acc[3] = {0, 0, 0};
+        const uint4 *hq4 = reinterpret_cast<const uint4 *>(h_cur + half * QS);
+#pragma unroll
+        for (int c = 0; c < KT / 16; ++c) {
+            const uint4 hv = hq4[c];
+#pragma unroll
+            for (int g = 0; g < 3; ++g) {
+                acc[g] = dp4a_w<HUnsigned>((int)R[g][4 * c + 0], hv.x, acc[g]);
+                acc[g] = dp4a_w<HUnsigned>((int)R[g][4 * c + 1], hv.y, acc[g]);
+                acc[g] = dp4a_w<HUnsigned>((int)R[g][4 * c + 2], hv.z, acc[g]);
+                acc[g] = dp4a_w<HUnsigned>((int)R[g][4 * c + 3], hv.w, acc[g]);
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < 3; ++g) acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 1);
+        if (worker) {
+            const unsigned char hb = h_cur[j_at];
+            const int32_t h_old = HUnsigned ? (int32_t)hb : (int32_t)(int8_t)hb;
+            const int32_t z_d = fused_gate_fast(gc, tab, ACT_Z, ihv[0], lin_round(acc[0], fls[j]));
+            const int32_t r_d = fused_gate_fast(gc, tab, ACT_R, ihv[1], lin_round(acc[1], fls[units + j]));
+            const int32_t hn = fused_finish_fast(gc, tab, ihv[2], lin_round(acc[2], fls[2 * units + j]), z_d, r_d, h_old);
+            h_nxt[j_at] = (unsigned char)hn;
+            const size_t o = (size_t)out_slot * BH + (size_t)b * a.H + j;
+            if (a.hq_out) a.hq_out[o] = hn;
+            if (a.hf_out) a.hf_out[o] = (float)(hn - gc.zp_h) * gc.h_scale;
+            if (a.h8_out) a.h8_out[o] = (uint8_t)hn;
+        }
+        ihv[0] = ihn[0];
+        ihv[1] = ihn[1];
+        ihv[2] = ihn[2];
+        __syncthreads();
+    }
+}
+
 // --------------------------------------------- generic fallback (any bit width, int32 data)
 
 // out[n][m] = epilogue( sum_k W_q[k][m] * in[n][k] ) with 64-bit accumulation
