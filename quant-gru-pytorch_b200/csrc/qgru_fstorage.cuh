@@ -670,16 +670,31 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
         a.spin_limit = h->spin_limit;
         a.fs_chan = chan + (size_t)3 * C;
         a.fs = fc;
-        auto kern = ih_bytes == 1 ? (h->h_uns ? k_recurrence_gemv<true, int8_t, 3> : k_recurrence_gemv<false, int8_t, 3>)
-                                  : (h->h_uns ? k_recurrence_gemv<true, int16_t, 3> : k_recurrence_gemv<false, int16_t, 3>);
-        const size_t smem = gemv_smem(h, n_tab);
-        CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        const int threads = 4 * ((H + 31) / 32 * 32);
-        kern<<<B, threads, smem, st>>>(h->gc_host, a);
+        // R in registers where the form exists (Hpad 128 or 256; option gemv_r=smem: in shared memory)
+        const bool in_regs = h->opt_gemv_r != 1 && (h->Hpad == 128 || h->Hpad == 256);
+        size_t smem;
+        if (in_regs) {
+            const size_t units = (size_t)(H + 15) / 16 * 16;
+            smem = (((size_t)n_tab * 4 + 15) & ~size_t(15)) + (size_t)2 * 2 * (h->Hpad / 2 + 16) + 9 * units * sizeof(float);
+            auto kern = h->Hpad == 128
+                            ? (ih_bytes == 1 ? (h->h_uns ? k_recurrence_gemv_reg<true, int8_t, 64, 3> : k_recurrence_gemv_reg<false, int8_t, 64, 3>)
+                                             : (h->h_uns ? k_recurrence_gemv_reg<true, int16_t, 64, 3> : k_recurrence_gemv_reg<false, int16_t, 64, 3>))
+                            : (ih_bytes == 1 ? (h->h_uns ? k_recurrence_gemv_reg<true, int8_t, 128, 3> : k_recurrence_gemv_reg<false, int8_t, 128, 3>)
+                                             : (h->h_uns ? k_recurrence_gemv_reg<true, int16_t, 128, 3> : k_recurrence_gemv_reg<false, int16_t, 128, 3>));
+            CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            kern<<<B, 2 * (int)units, smem, st>>>(h->gc_host, a);
+        } else {
+            auto kern = ih_bytes == 1 ? (h->h_uns ? k_recurrence_gemv<true, int8_t, 3> : k_recurrence_gemv<false, int8_t, 3>)
+                                      : (h->h_uns ? k_recurrence_gemv<true, int16_t, 3> : k_recurrence_gemv<false, int16_t, 3>);
+            smem = gemv_smem(h, n_tab);
+            CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            const int threads = 4 * ((H + 31) / 32 * 32);
+            kern<<<B, threads, smem, st>>>(h->gc_host, a);
+        }
         CK(cudaGetLastError());
         h->launches++;
-        snprintf(buf, sizeof(buf), "path=float_storage gemm=%s rec=gemv_float_cell rows_per_cta=1 ctas=%d smem=%zu ih_bytes=%d gates=%s",
-                 used_tc ? "tcgen05_i8" : "simt_dp4a", B, smem, ih_bytes, fc.tab_on ? "tabulated" : "evaluated");
+        snprintf(buf, sizeof(buf), "path=float_storage gemm=%s rec=gemv_float_cell r_in=%s rows_per_cta=1 ctas=%d smem=%zu ih_bytes=%d gates=%s",
+                 used_tc ? "tcgen05_i8" : "simt_dp4a", in_regs ? "registers" : "smem", B, smem, ih_bytes, fc.tab_on ? "tabulated" : "evaluated");
     } else if (h->opt_rec != 3 && plan_recurrence(h, B, &pl)) {
         // the whole recurrence in one launch
         if (pl.G > h->bar_groups) {

@@ -575,8 +575,10 @@ __global__ void __launch_bounds__(1024, 1) k_recurrence_gemv(const __grid_consta
 // 128 bytes per clock is 1536 cycles on its own): KT / 4 * 3 dp4a per thread, one shuffle per
 // gate, the cell on the even lane, one __syncthreads.  The per-unit constants of the R*h + br
 // requantization live in shared memory (the registers belong to R).
-template <bool HUnsigned, typename IhT, int KT>
+// Cell: 2 the tabulated integer cell, 3 the float cell of the float-storage forward (as in k_recurrence_gemv).
+template <bool HUnsigned, typename IhT, int KT, int Cell = 2>
 __global__ void __launch_bounds__(512, 1) k_recurrence_gemv_reg(const __grid_constant__ GateConsts gc, RecArgs a) {
+    static_assert(Cell == 2 || Cell == 3, "the branch-free cells only");
     extern __shared__ __align__(16) unsigned char smem_raw[];
     static_assert(KT == 64 || KT == 128, "Hpad = 128 or 256");
     constexpr int QS = KT + 16;            // the two K halves of a state buffer sit 16 bytes further apart than their length
@@ -586,7 +588,8 @@ __global__ void __launch_bounds__(512, 1) k_recurrence_gemv_reg(const __grid_con
     size_t off = ((size_t)a.n_table * 4 + 15) & ~size_t(15);
     unsigned char *hs = smem_raw + off;
     off += (size_t)2 * HS;
-    FastLin *fls = reinterpret_cast<FastLin *>(smem_raw + off);   // [3][units]
+    FastLin *fls = reinterpret_cast<FastLin *>(smem_raw + off);   // Cell 2: [3][units]
+    float *fsk = reinterpret_cast<float *>(smem_raw + off);       // Cell 3: [3 gates][3 constants][units]
 
     const int tid = threadIdx.x, half = tid & 1, j = tid >> 1, units = NT >> 1;
     const int b = blockIdx.x;
@@ -598,9 +601,16 @@ __global__ void __launch_bounds__(512, 1) k_recurrence_gemv_reg(const __grid_con
         hs[at] = a.h8[(size_t)b * a.Hpad + i];      // initial state of this row (buffer 0 of h8)
         hs[HS + at] = 0;
     }
-    for (int i = tid; i < 3 * units; i += NT) {
-        const int g = i / units, u = i % units;
-        fls[i] = u < a.H ? a.lc.fl[g * a.H + u] : FastLin{0, 0, 0, 0, 0, 0};
+    if constexpr (Cell == 2) {
+        for (int i = tid; i < 3 * units; i += NT) {
+            const int g = i / units, u = i % units;
+            fls[i] = u < a.H ? a.lc.fl[g * a.H + u] : FastLin{0, 0, 0, 0, 0, 0};
+        }
+    } else {
+        for (int i = tid; i < 9 * units; i += NT) {
+            const int gk = i / units, u = i % units, g = gk / 3, k = gk % 3;
+            fsk[i] = u < a.H ? a.fs_chan[(size_t)k * a.C + g * a.H + u] : 0.f;
+        }
     }
     const int j_at = (j / KT) * QS + (j % KT);      // where unit j's byte sits in a state buffer
     uint32_t R[3][KT / 4];
@@ -655,9 +665,22 @@ __global__ void __launch_bounds__(512, 1) k_recurrence_gemv_reg(const __grid_con
         if (worker) {
             const unsigned char hb = h_cur[j_at];
             const int32_t h_old = HUnsigned ? (int32_t)hb : (int32_t)(int8_t)hb;
-            const int32_t z_d = fused_gate_fast(gc, tab, ACT_Z, ihv[0], lin_round(acc[0], fls[j]));
-            const int32_t r_d = fused_gate_fast(gc, tab, ACT_R, ihv[1], lin_round(acc[1], fls[units + j]));
-            const int32_t hn = fused_finish_fast(gc, tab, ihv[2], lin_round(acc[2], fls[2 * units + j]), z_d, r_d, h_old);
+            int32_t hn;
+            if constexpr (Cell == 2) {
+                const int32_t z_d = fused_gate_fast(gc, tab, ACT_Z, ihv[0], lin_round(acc[0], fls[j]));
+                const int32_t r_d = fused_gate_fast(gc, tab, ACT_R, ihv[1], lin_round(acc[1], fls[units + j]));
+                hn = fused_finish_fast(gc, tab, ihv[2], lin_round(acc[2], fls[2 * units + j]), z_d, r_d, h_old);
+            } else {
+                const float fih[3] = {(float)ihv[0], (float)ihv[1], (float)ihv[2]};
+                float fhh[3];
+#pragma unroll
+                for (int g = 0; g < 3; ++g)
+                    fhh[g] = fs_linear(acc[g], fsk[(g * 3 + 0) * units + j], fsk[(g * 3 + 1) * units + j],
+                                       fsk[(g * 3 + 2) * units + j], a.fs.zp_hh, a.fs.hh_lo, a.fs.hh_hi);
+                const float u_g = fs_sigmoid_gate_tab(a.fs, tab, 0, fih[0], fhh[0]);
+                const float r_g = fs_sigmoid_gate_tab(a.fs, tab, 1, fih[1], fhh[1]);
+                hn = (int32_t)fs_finish_tab(a.fs, tab, u_g, r_g, fih[2], fhh[2], (float)h_old);
+            }
             h_nxt[j_at] = (unsigned char)hn;
             const size_t o = (size_t)out_slot * BH + (size_t)b * a.H + j;
             if (a.hq_out) a.hq_out[o] = hn;
