@@ -80,6 +80,15 @@ def test_shapes_default_config(oracle, cuda_device, shape, rec):
     if rec.startswith("mma_cluster"):   # the R slice sits in tensor memory unless told otherwise
         assert ("r_in=tmem" in plan) == (rec == "mma_cluster")
     assert np.array_equal(got, _want(oracle, case)), plan
+    if rec == "gemv":   # R held in registers (the tabulated cell's default) and in shared memory: the same bits
+        assert "r_in=registers" in plan, plan
+        got, plan, _ = _run(case, cuda_device, opts=opts + (("gemv_r", "smem"),))
+        assert "r_in=smem" in plan and np.array_equal(got, _want(oracle, case)), plan
+        rev, plan, _ = _run(case, cuda_device, reverse=True, opts=opts)
+        import copy
+        flipped = copy.copy(case)
+        flipped.x_q = np.ascontiguousarray(case.x_q[::-1])
+        assert "r_in=registers" in plan and np.array_equal(rev, _want(oracle, flipped)[::-1]), plan
 
 
 def test_simt_gemm_and_wide_hidden(oracle, cuda_device):
