@@ -624,8 +624,9 @@ bool gemv_fits(const qgru_handle *h) {
 // 128 or 256 (option gemv_r=smem keeps R in shared memory).
 bool gemv_reg_ok(const qgru_handle *h, bool fused) { return fused && h->opt_gemv_r != 1 && (h->Hpad == 128 || h->Hpad == 256); }
 size_t gemv_reg_smem(const qgru_handle *h, int n_table) {
-    const size_t units = (size_t)(h->H + 15) / 16 * 16;
-    return (((size_t)n_table * 4 + 15) & ~size_t(15)) + (size_t)2 * 2 * (h->Hpad / 2 + 16) + 3 * units * sizeof(FastLin);
+    const size_t units = (size_t)(h->H + 31) / 32 * 32;
+    return (((size_t)n_table * 4 + 15) & ~size_t(15)) + (size_t)2 * 2 * (h->Hpad / 2 + 16) + 3 * units * sizeof(int) +
+           3 * units * sizeof(FastLin);
 }
 
 template <bool HU, typename IhT>
@@ -633,7 +634,7 @@ int launch_gemv_reg(qgru_handle *h, RecArgs &a, cudaStream_t st) {
     auto kern = h->Hpad == 128 ? k_recurrence_gemv_reg<HU, IhT, 64> : k_recurrence_gemv_reg<HU, IhT, 128>;
     const size_t smem = gemv_reg_smem(h, a.n_table);
     CK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const int threads = 2 * ((h->H + 15) / 16 * 16);
+    const int threads = 2 * ((h->H + 31) / 32 * 32);
     kern<<<a.B, threads, smem, st>>>(h->gc_host, a);
     CK(cudaGetLastError());
     h->launches++;

@@ -674,8 +674,9 @@ int fstorage_forward(qgru_handle *h, int T, int B, const float *x, const float *
         const bool in_regs = h->opt_gemv_r != 1 && (h->Hpad == 128 || h->Hpad == 256);
         size_t smem;
         if (in_regs) {
-            const size_t units = (size_t)(H + 15) / 16 * 16;
-            smem = (((size_t)n_tab * 4 + 15) & ~size_t(15)) + (size_t)2 * 2 * (h->Hpad / 2 + 16) + 9 * units * sizeof(float);
+            const size_t units = (size_t)(H + 31) / 32 * 32;
+            smem = (((size_t)n_tab * 4 + 15) & ~size_t(15)) + (size_t)2 * 2 * (h->Hpad / 2 + 16) + 3 * units * sizeof(int) +
+                   9 * units * sizeof(float);
             auto kern = h->Hpad == 128
                             ? (ih_bytes == 1 ? (h->h_uns ? k_recurrence_gemv_reg<true, int8_t, 64, 3> : k_recurrence_gemv_reg<false, int8_t, 64, 3>)
                                              : (h->h_uns ? k_recurrence_gemv_reg<true, int16_t, 64, 3> : k_recurrence_gemv_reg<false, int16_t, 64, 3>))

@@ -568,13 +568,15 @@ __global__ void __launch_bounds__(1024, 1) k_recurrence_gemv(const __grid_consta
     }
 }
 
-// The same with R in REGISTERS (tabulated branch-free cell only): a pair of threads owns one hidden
-// unit, each lane half of K for the unit's three gate rows, i.e. 3 * KT bytes of R (KT = Hpad / 2 =
-// 64 or 128) held in 48 or 96 registers for all T steps.  A step then reads only the state (a
-// few hundred bytes, broadcast) from shared memory instead of all of R (196 KB at H = 256, which at
-// 128 bytes per clock is 1536 cycles on its own): KT / 4 * 3 dp4a per thread, one shuffle per
-// gate, the cell on the even lane, one __syncthreads.  The per-unit constants of the R*h + br
-// requantization live in shared memory (the registers belong to R).
+// The same with R in REGISTERS (the branch-free cells only): two threads own one hidden unit, each
+// half of K for the unit's three gate rows, i.e. 3 * KT bytes of R (KT = Hpad / 2 = 64 or 128) held
+// in 48 or 96 registers for all T steps.  A step then reads only the state (a few hundred bytes,
+// broadcast) from shared memory instead of all of R (196 KB at H = 256, which at 128 bytes per
+// clock is 1536 cycles on its own): KT / 4 * 3 dp4a per thread.  The threads of the upper K half
+// are the upper half of the CTA's warps: they hand their three partial sums over through shared
+// memory (a named barrier they only arrive on), and the lower half's warps run the cell with every
+// lane busy.  The per-unit constants of the R*h + br requantization live in shared memory (the
+// registers belong to R).
 // Cell: 2 the tabulated integer cell, 3 the float cell of the float-storage forward (as in k_recurrence_gemv).
 template <bool HUnsigned, typename IhT, int KT, int Cell = 2>
 __global__ void __launch_bounds__(512, 1) k_recurrence_gemv_reg(const __grid_constant__ GateConsts gc, RecArgs a) {
@@ -583,15 +585,17 @@ __global__ void __launch_bounds__(512, 1) k_recurrence_gemv_reg(const __grid_con
     static_assert(KT == 64 || KT == 128, "Hpad = 128 or 256");
     constexpr int QS = KT + 16;            // the two K halves of a state buffer sit 16 bytes further apart than their length
     constexpr int HS = 2 * QS;
-    const int NT = blockDim.x;             // 2 * units (units rounded up to 16)
+    const int NT = blockDim.x;             // 2 * units (units rounded up to 32: whole warps per K half)
     int32_t *tables = reinterpret_cast<int32_t *>(smem_raw);
     size_t off = ((size_t)a.n_table * 4 + 15) & ~size_t(15);
     unsigned char *hs = smem_raw + off;
     off += (size_t)2 * HS;
+    int *part = reinterpret_cast<int *>(smem_raw + off);          // [3][units]: the upper K half's partial sums
+    off += (size_t)3 * (NT >> 1) * sizeof(int);
     FastLin *fls = reinterpret_cast<FastLin *>(smem_raw + off);   // Cell 2: [3][units]
     float *fsk = reinterpret_cast<float *>(smem_raw + off);       // Cell 3: [3 gates][3 constants][units]
 
-    const int tid = threadIdx.x, half = tid & 1, j = tid >> 1, units = NT >> 1;
+    const int tid = threadIdx.x, units = NT >> 1, half = tid >= units ? 1 : 0, j = tid - half * units;
     const int b = blockIdx.x;
     const bool j_ok = j < a.H;
 
@@ -660,8 +664,16 @@ __global__ void __launch_bounds__(512, 1) k_recurrence_gemv_reg(const __grid_con
                 acc[g] = dp4a_w<HUnsigned>((int)R[g][4 * c + 3], hv.w, acc[g]);
             }
         }
+        if (half) {
+            // hand the partial sums to the lower half's thread of the same unit; nothing to wait for here
 #pragma unroll
-        for (int g = 0; g < 3; ++g) acc[g] += __shfl_xor_sync(0xffffffffu, acc[g], 1);
+            for (int g = 0; g < 3; ++g) part[g * units + j] = acc[g];
+            asm volatile("bar.arrive 1, %0;" ::"r"(NT) : "memory");
+        } else {
+            asm volatile("bar.sync 1, %0;" ::"r"(NT) : "memory");
+#pragma unroll
+            for (int g = 0; g < 3; ++g) acc[g] += part[g * units + j];
+        }
         if (worker) {
             const unsigned char hb = h_cur[j_at];
             const int32_t h_old = HUnsigned ? (int32_t)hb : (int32_t)(int8_t)hb;
