@@ -26,8 +26,9 @@
 //
 // Three warps issue the MMAs, one per gate.  A single thread issues a chain of these small MMAs at
 // one per 53-80 cycles, while the tensor pipe takes MMAs from several threads side by side
-// (qgru_probe_mma_i8_ex) and is bound by streaming the A operand (the R slice, about 115 bytes per
-// cycle): the 48 MMAs of a step at H = 512 take 1700 cycles instead of 3900.  Each issuer commits
+// (qgru_probe_mma_i8_ex): the 48 MMAs of a step at H = 512 take 1700 cycles instead of 3900 (about
+// 115 bytes of R per cycle; the same 48 MMAs from three issuers take 850 cycles in the probe, and
+// six issuers, one per gate and K half, were measured no faster here).  Each issuer commits
 // once per step: a commit holds its thread until the MMAs before it are done, so a thread that
 // commits gate by gate serialises the gates (measured; the form with one issuer per K half and
 // accumulator columns of its own, k_parts = 2, is kept for experiments).  The reset and new
