@@ -182,6 +182,11 @@ k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, int issuers, in
                 } else {
                     tc::mbar_try_wait(&bar[4], 0);
                 }
+            } else if (neighbour_mode == 6) {
+                // warps that follow the issuer's periodic commits as a GEMM's epilogue follows its accumulator
+                // barrier: a suspending wait on the phase that the next commit completes (never blocking
+                // for good: the loop condition ends it)
+                if (tc::mbar_try_wait(&bar[5], bulk_phase)) bulk_phase ^= 1u;
             } else if (neighbour_mode == 0) {
                 tc::mbar_try_wait(&bar[4], 0);
             } else if (neighbour_mode == 1) {
