@@ -394,7 +394,8 @@ QGRU_API int qgru_probe_mma_i8(int device, int M, int N, int a_in_tmem, int accu
  * warps do, (1) run integer arithmetic back to back or (2) run dependent shared-memory loads, as its
  * busy warps do, (3) drain accumulators with 16-column tensor-memory loads or (4) write 128-bit words
  * into shared memory, (6) follow the first issuer's periodic commits with suspending barrier waits,
- * as an epilogue follows its accumulator barrier: cycles_per_mma is the slowest issuer's chain time divided by `mmas`, tera_ops
+ * as an epilogue follows its accumulator barrier, (7) stream global memory (read, add, write back):
+ * cycles_per_mma is the slowest issuer's chain time divided by `mmas`, tera_ops
  * counts all issuers.  neighbour_mode + 1024 (N <= 128): every MMA of a pass of eight reads operand
  * tiles of its own, spread over 128 KB of shared memory, as a GEMM that streams its operands does
  * (without it the four K steps of one tile pair repeat); + 512: all 32 lanes of an issuing warp stay

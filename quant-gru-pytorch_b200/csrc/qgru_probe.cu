@@ -182,6 +182,15 @@ k_probe_mma_i8(int M, int N, int a_in_tmem, int n_acc, int mmas, int issuers, in
                 } else {
                     tc::mbar_try_wait(&bar[4], 0);
                 }
+            } else if (neighbour_mode == 7) {
+                // warps streaming global memory (read, add, write back) over 2 MB per CTA: DRAM and L2 busy
+                // beside the tensor pipe, as in a GEMM whose operands and results move through HBM
+                uint4 *gp = reinterpret_cast<uint4 *>(const_cast<unsigned char *>(src)) + (size_t)blockIdx.x * 131072;
+                const uint32_t at = (x * 32u + (uint32_t)lane + (uint32_t)(warp - issuers) * 8192u) & 131071u;
+                uint4 v = gp[at];
+                v.x += 1u;
+                gp[at] = v;
+                x += 1u;
             } else if (neighbour_mode == 6) {
                 // warps that follow the issuer's periodic commits as a GEMM's epilogue follows its accumulator
                 // barrier: a suspending wait on the phase that the next commit completes (never blocking
@@ -267,6 +276,7 @@ extern "C" int qgru_probe_mma_i8_commits(int device, int M, int N, int a_in_tmem
         if (cudaMalloc(&d_cycles, sizeof(long long) * ctas * 2) != cudaSuccess) break;
         if (cudaMemset(d_cycles, 0, sizeof(long long) * ctas * 2) != cudaSuccess) break;
         if ((neighbour_mode & 255) == 5 && (cudaMalloc(&d_src, (size_t)ctas * 65536) != cudaSuccess || cudaMemset(d_src, 1, (size_t)ctas * 65536) != cudaSuccess)) break;
+        if ((neighbour_mode & 255) == 7 && (cudaMalloc(&d_src, (size_t)ctas * 2097152) != cudaSuccess || cudaMemset(d_src, 1, (size_t)ctas * 2097152) != cudaSuccess)) break;
         if (cudaMalloc(&d_to, sizeof(int)) != cudaSuccess) break;
         if (cudaMemset(d_to, 0, sizeof(int)) != cudaSuccess) break;
         if (cudaFuncSetAttribute(k_probe_mma_i8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) break;
